@@ -1,0 +1,520 @@
+// Backward attention for text queries on tcgen05 tensor cores, as two deterministic
+// kernels that never accumulate across CTAs (no fp32 atomics, no dQ staging buffer,
+// no pre/post-processing launches):
+//
+//   attn_bwd_dq    query-stationary.  One CTA = 128 query rows of one head; for every
+//                  visible key tile: S = Q K^T, dP = dO V^T (tensor cores) ->
+//                  P = exp2(S c - LSE), dS = P (dP - delta) scale (registers) ->
+//                  dQ += dS K (dS is fed to the tensor cores from TMEM).  Also emits
+//                  delta = rowsum(O * dO) for the second kernel.
+//   attn_bwd_dkv   key-stationary.  One CTA = one 128-row key tile (text or summary)
+//                  of one KV head; loops over the query tiles that see it and over
+//                  the query heads of the group: S^T = K Q^T, dP^T = V dO^T ->
+//                  P^T, dS^T -> dV += P^T dO, dK += dS^T Q, all four accumulators
+//                  resident in TMEM (4 x 128 columns), GQA heads summed for free.
+//
+// The reference's sm_100 backward is key-stationary with dQ added into a global
+// fp32 buffer by bulk reduce-adds plus separate pre- and post-processing kernels
+// (FA!flash_attn/cute/flash_bwd_sm100.py:1645-1798, :2422-2636).
+#include "attn_common.cuh"
+#include "host.h"
+
+namespace ksa {
+
+constexpr int kBwdThreads = 192;
+
+template <int HD>
+struct BwdSmem {
+  static constexpr int kTile = 128 * HD * 2;
+  static constexpr int kStationary = 2 * kTile;       // (Q, dO) or (K, V)
+  static constexpr int kStages = 2;
+  static constexpr int kRing = kStages * 2 * kTile;   // (K, V) or (Q, dO) pairs
+  static constexpr int kStats = 2 * 2 * 128 * 4;      // LSE and delta of the current query tile, double-buffered
+  static constexpr int kBar = 256;
+  static constexpr int kTotal = kStationary + kRing + kStats + kBar + 1024;
+};
+
+struct BwdParams {
+  AttnShape s;
+  float scale, scale_log2;
+  const bf16* o;   // [B, Lq, Hq, HD]
+  const bf16* d_o; // same layout as o
+  long long o_row_stride, o_batch_stride;
+  const float* lse;  // [B, Hq, Lq]
+  float* delta;      // [B, Hq, Lq]
+  bf16* dq;          // [B, Lq, Hq, HD] (strides below)
+  long long dq_row_stride, dq_batch_stride;
+  bf16* dk; bf16* dv;     // text key grads [B, Lk, Hkv, HD]
+  long long dk_row_stride, dk_batch_stride, dv_row_stride, dv_batch_stride;
+  bf16* dks; bf16* dvs;   // summary key grads [B, Ns, Hkv, HD]
+  long long dks_row_stride, dks_batch_stride, dvs_row_stride, dvs_batch_stride;
+  int* status;
+};
+
+template <int HD>
+__device__ __forceinline__ void load_tile_b(uint8_t* dst, const CUtensorMap* m, int row0, int h, int b, uint64_t* bar) {
+#pragma unroll
+  for (int half = 0; half < HD / 64; ++half) tma_load_4d(dst + half * 16384, m, half * 64, row0, h, b, bar);
+}
+
+__device__ __forceinline__ void wg_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Store a row of HD fp32 accumulators from TMEM as bf16 to global memory.
+template <int HD>
+__device__ __forceinline__ void store_acc_row(uint32_t taddr, bf16* dst, bool valid, float mul) {
+#pragma unroll
+  for (int c = 0; c < HD / 32; ++c) {
+    uint32_t o[32];
+    tmem_ld32(taddr + c * 32, o);
+    tmem_wait_ld();
+    if (valid) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint4 v;
+        v.x = pack_bf16x2(__uint_as_float(o[i]) * mul, __uint_as_float(o[i + 1]) * mul);
+        v.y = pack_bf16x2(__uint_as_float(o[i + 2]) * mul, __uint_as_float(o[i + 3]) * mul);
+        v.z = pack_bf16x2(__uint_as_float(o[i + 4]) * mul, __uint_as_float(o[i + 5]) * mul);
+        v.w = pack_bf16x2(__uint_as_float(o[i + 6]) * mul, __uint_as_float(o[i + 7]) * mul);
+        *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+      }
+    }
+  }
+}
+
+// ================================================================================ dQ
+template <int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const __grid_constant__ CUtensorMap tmKs, const __grid_constant__ CUtensorMap tmVs, BwdParams p) {
+  using S = BwdSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = smem + S::kTile;
+  uint8_t* sRing = smem + S::kStationary;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kStationary + S::kRing + S::kStats);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;                 // kStages
+  uint64_t* kv_empty = kv_full + S::kStages;    // kStages
+  uint64_t* sp_full = kv_empty + S::kStages;    // 1
+  uint64_t* ds_full = sp_full + 1;              // 1
+  uint64_t* dq_full = ds_full + 1;              // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const WaitGuard guard{abort_flag, p.status};
+  const AttnShape& sh = p.s;
+  const int n_qtiles = (sh.Lq + 127) / 128;
+  const int q_tile = n_qtiles - 1 - (int)blockIdx.x;
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kv_head = head / (sh.Hq / sh.Hkv);
+  const TileRange tr = key_tiles_for_query_tile(sh, q_tile);
+  const int total = tr.total();
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < S::kStages; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    mbar_init(sp_full, 1);
+    mbar_init(ds_full, 128);
+    mbar_init(dq_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 2) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * S::kTile);
+      load_tile_b<HD>(sQ, &tmQ, q_tile * 128, head, b, q_full);
+      load_tile_b<HD>(sdO, &tmdO, q_tile * 128, head, b, q_full);
+      for (int j = 0; j < total; ++j) {
+        const int stage = j % S::kStages;
+        const uint32_t phase = (j / S::kStages) & 1;
+        if (!mbar_wait(&kv_empty[stage], phase ^ 1, guard, kTimeoutStageEmpty)) break;
+        const bool is_sum = j < tr.n_sum_tiles;
+        const int kt = is_sum ? j : tr.text_first + (j - tr.n_sum_tiles);
+        uint8_t* dst = sRing + stage * 2 * S::kTile;
+        mbar_expect_tx(&kv_full[stage], 2 * S::kTile);
+        load_tile_b<HD>(dst, is_sum ? &tmKs : &tmK, kt * 128, kv_head, b, &kv_full[stage]);
+        load_tile_b<HD>(dst + S::kTile, is_sum ? &tmVs : &tmV, kt * 128, kv_head, b, &kv_full[stage]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_dq = umma_idesc_bf16(128, HD, 0, 1);
+      bool ok = mbar_wait(q_full, 0, guard, kTimeoutTmaFull);
+      for (int j = 0; j < total && ok; ++j) {
+        const int stage = j % S::kStages;
+        if (!mbar_wait(&kv_full[stage], (j / S::kStages) & 1, guard, kTimeoutTmaFull)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), doa = smem_u32(sdO);
+        const uint32_t ka = smem_u32(sRing + stage * 2 * S::kTile), va = ka + S::kTile;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tS, smem_desc_kmajor_sw128(qa + off), smem_desc_kmajor_sw128(ka + off), idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tdP, smem_desc_kmajor_sw128(doa + off), smem_desc_kmajor_sw128(va + off), idesc_s, kk != 0);
+        }
+        umma_commit(sp_full);
+        if (!mbar_wait(ds_full, j & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ts(tdQ, tS + kk * 8, smem_desc_mnmajor_sw128(ka + kk * 2048, 16384), idesc_dq, (j | kk) != 0);
+        umma_commit(&kv_empty[stage]);
+      }
+      if (ok) umma_commit(dq_full);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int q_local = q_tile * 128 + r;
+    const bool valid = q_local < sh.Lq;
+    const int t_glob = sh.q_off + q_local;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    // delta = rowsum(O * dO); LSE in log2 units
+    float delta = 0.f, lse2 = INFINITY;
+    if (valid) {
+      const long long off = (long long)b * p.o_batch_stride + (long long)q_local * p.o_row_stride + (long long)head * HD;
+      const uint4* po = reinterpret_cast<const uint4*>(p.o + off);
+      const uint4* pd = reinterpret_cast<const uint4*>(p.d_o + off);
+#pragma unroll 4
+      for (int i = 0; i < HD / 8; ++i) {
+        const uint4 a = po[i], g = pd[i];
+        const uint32_t au[4] = {a.x, a.y, a.z, a.w}, gu[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 x = unpack_bf16x2(au[k]), y = unpack_bf16x2(gu[k]);
+          delta += x.x * y.x + x.y * y.y;
+        }
+      }
+      const long long sidx = ((long long)b * sh.Hq + head) * sh.Lq + q_local;
+      lse2 = p.lse[sidx] * 1.4426950408889634f;
+      p.delta[sidx] = delta;
+    }
+    bool ok = true;
+    for (int j = 0; j < total; ++j) {
+      if (!mbar_wait(sp_full, j & 1, guard, kTimeoutAccFull)) { ok = false; break; }
+      tc_fence_after();
+      const bool is_sum = j < tr.n_sum_tiles;
+      const int kt = is_sum ? j : tr.text_first + (j - tr.n_sum_tiles);
+      int lo, hi;
+      allowed_columns(sh, t_glob, is_sum, kt, lo, hi);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32], dr[32];
+        tmem_ld32(tS + lane_addr + c * 32, sr);
+        tmem_ld32(tdP + lane_addr + c * 32, dr);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = c * 32 + 2 * i + e;
+            const float pr = (col >= lo && col <= hi)
+                                 ? fast_exp2(fmaf(__uint_as_float(sr[2 * i + e]), p.scale_log2, -lse2)) : 0.f;
+            ds[e] = pr * (__uint_as_float(dr[2 * i + e]) - delta) * p.scale;
+          }
+          pk[i] = pack_bf16x2(ds[0], ds[1]);
+        }
+        tmem_st16(tS + lane_addr + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(ds_full);
+    }
+    if (ok) ok = mbar_wait(dq_full, 0, guard, kTimeoutAccFull);
+    if (ok) {
+      tc_fence_after();
+      bf16* dst = p.dq + (long long)b * p.dq_batch_stride + (long long)q_local * p.dq_row_stride + (long long)head * HD;
+      store_acc_row<HD>(tdQ + lane_addr, dst, valid, 1.f);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// ================================================================================ dK / dV
+template <int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                    const __grid_constant__ CUtensorMap tmKs, const __grid_constant__ CUtensorMap tmVs, BwdParams p) {
+  using S = BwdSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + S::kTile;
+  uint8_t* sRing = smem + S::kStationary;
+  float* sLse = reinterpret_cast<float*>(smem + S::kStationary + S::kRing);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kStationary + S::kRing + S::kStats);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;                // kStages
+  uint64_t* q_empty = q_full + S::kStages;    // kStages
+  uint64_t* sp_full = q_empty + S::kStages;
+  uint64_t* pds_full = sp_full + 1;
+  uint64_t* acc_full = pds_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const WaitGuard guard{abort_flag, p.status};
+  const AttnShape& sh = p.s;
+  const int n_text_tiles = (sh.Lk + 127) / 128;
+  const bool is_sum = (int)blockIdx.x >= n_text_tiles;
+  const int kt = is_sum ? (int)blockIdx.x - n_text_tiles : (int)blockIdx.x;
+  const int kv_head = blockIdx.y, b = blockIdx.z;
+  const int G = sh.Hq / sh.Hkv;
+  const QueryRange qr = is_sum ? query_tiles_for_summary_key_tile(sh, kt) : query_tiles_for_text_key_tile(sh, kt);
+  const int n_q = qr.last >= qr.first ? (qr.last - qr.first + 1) : 0;
+  const int total = n_q * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < S::kStages; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    mbar_init(sp_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 2) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 256 + HD;
+
+  if (warp == 0) {
+    if (lane == 0 && total > 0) {
+      mbar_expect_tx(kv_full, 2 * S::kTile);
+      load_tile_b<HD>(sK, is_sum ? &tmKs : &tmK, kt * 128, kv_head, b, kv_full);
+      load_tile_b<HD>(sV, is_sum ? &tmVs : &tmV, kt * 128, kv_head, b, kv_full);
+      for (int i = 0; i < total; ++i) {
+        const int stage = i % S::kStages;
+        if (!mbar_wait(&q_empty[stage], ((i / S::kStages) & 1) ^ 1, guard, kTimeoutStageEmpty)) break;
+        const int qt = qr.first + i / G, head = kv_head * G + i % G;
+        uint8_t* dst = sRing + stage * 2 * S::kTile;
+        mbar_expect_tx(&q_full[stage], 2 * S::kTile);
+        load_tile_b<HD>(dst, &tmQ, qt * 128, head, b, &q_full[stage]);
+        load_tile_b<HD>(dst + S::kTile, &tmdO, qt * 128, head, b, &q_full[stage]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && total > 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);
+      bool ok = mbar_wait(kv_full, 0, guard, kTimeoutTmaFull);
+      for (int i = 0; i < total && ok; ++i) {
+        const int stage = i % S::kStages;
+        if (!mbar_wait(&q_full[stage], (i / S::kStages) & 1, guard, kTimeoutTmaFull)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+        const uint32_t qa = smem_u32(sRing + stage * 2 * S::kTile), doa = qa + S::kTile;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tS, smem_desc_kmajor_sw128(ka + off), smem_desc_kmajor_sw128(qa + off), idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tdP, smem_desc_kmajor_sw128(va + off), smem_desc_kmajor_sw128(doa + off), idesc_s, kk != 0);
+        }
+        umma_commit(sp_full);
+        if (!mbar_wait(pds_full, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ts(tdV, tS + kk * 8, smem_desc_mnmajor_sw128(doa + kk * 2048, 16384), idesc_acc, (i | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_ts(tdK, tdP + kk * 8, smem_desc_mnmajor_sw128(qa + kk * 2048, 16384), idesc_acc, (i | kk) != 0);
+        umma_commit(&q_empty[stage]);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int k_local = kt * 128 + r;
+    const bool valid = k_local < (is_sum ? sh.Ns : sh.Lk);
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    // queries t (global) that may see this key: [t_lo, t_hi]
+    long long t_lo, t_hi;
+    if (is_sum) {
+      const int sg = sh.s_off + k_local;
+      t_lo = (long long)(sg / sh.n_sum + sh.window + 1) * sh.chunk;
+      t_hi = (1LL << 40);
+    } else {
+      const int ug = sh.k_off + k_local;
+      t_lo = ug;
+      t_hi = (sh.window >= (1 << 29)) ? (1LL << 40) : (long long)(ug / sh.chunk + sh.window + 1) * sh.chunk - 1;
+      if (sh.tok_window > 0) t_hi = min(t_hi, (long long)ug + sh.tok_window - 1);
+    }
+    if (!valid) { t_lo = 1; t_hi = 0; }
+    bool ok = true;
+    for (int i = 0; i < total; ++i) {
+      const int qt = qr.first + i / G, head = kv_head * G + i % G;
+      const bool got = mbar_wait(sp_full, i & 1, guard, kTimeoutAccFull);
+      // Stage LSE / delta of this query tile, double-buffered by iteration parity: the buffer written here
+      // was last read two iterations ago, and every thread has passed the barrier of the iteration between.
+      float* lse_s = sLse + (i & 1) * 256;
+      float* delta_s = lse_s + 128;
+      {
+        const int ql = qt * 128 + r;
+        const long long sidx = ((long long)b * sh.Hq + head) * sh.Lq + ql;
+        const bool qv = ql < sh.Lq;
+        lse_s[r] = qv ? p.lse[sidx] * 1.4426950408889634f : INFINITY;
+        delta_s[r] = qv ? p.delta[sidx] : 0.f;
+      }
+      (void)got;  // a failed wait has raised the CTA abort flag before returning
+      wg_sync();
+      if (*abort_flag) { ok = false; break; }  // uniform across the warpgroup: read after the barrier
+      tc_fence_after();
+      const long long tq0 = (long long)sh.q_off + qt * 128;
+      const int lo = (int)max(t_lo - tq0, 0LL), hi = (int)min(t_hi - tq0, 127LL);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32], dr[32];
+        tmem_ld32(tS + lane_addr + c * 32, sr);
+        tmem_ld32(tdP + lane_addr + c * 32, dr);
+        tmem_wait_ld();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          float pr[2], ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = c * 32 + 2 * k + e;
+            pr[e] = (col >= lo && col <= hi)
+                        ? fast_exp2(fmaf(__uint_as_float(sr[2 * k + e]), p.scale_log2, -lse_s[col])) : 0.f;
+            ds[e] = pr[e] * (__uint_as_float(dr[2 * k + e]) - delta_s[col]) * p.scale;
+          }
+          pk[k] = pack_bf16x2(pr[0], pr[1]);
+          dk[k] = pack_bf16x2(ds[0], ds[1]);
+        }
+        tmem_st16(tS + lane_addr + c * 16, pk);
+        tmem_st16(tdP + lane_addr + c * 16, dk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+    }
+    bf16* dk_base = is_sum ? p.dks : p.dk;
+    bf16* dv_base = is_sum ? p.dvs : p.dv;
+    const long long dk_rs = is_sum ? p.dks_row_stride : p.dk_row_stride, dk_bs = is_sum ? p.dks_batch_stride : p.dk_batch_stride;
+    const long long dv_rs = is_sum ? p.dvs_row_stride : p.dv_row_stride, dv_bs = is_sum ? p.dvs_batch_stride : p.dv_batch_stride;
+    bf16* dkp = dk_base + (long long)b * dk_bs + (long long)k_local * dk_rs + (long long)kv_head * HD;
+    bf16* dvp = dv_base + (long long)b * dv_bs + (long long)k_local * dv_rs + (long long)kv_head * HD;
+    if (total == 0) {
+      if (valid) {
+        const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) { reinterpret_cast<uint4*>(dkp)[i] = z; reinterpret_cast<uint4*>(dvp)[i] = z; }
+      }
+    } else {
+      if (ok) ok = mbar_wait(acc_full, 0, guard, kTimeoutAccFull);
+      if (ok) {
+        tc_fence_after();
+        store_acc_row<HD>(tdV + lane_addr, dvp, valid, 1.f);
+        store_acc_row<HD>(tdK + lane_addr, dkp, valid, 1.f);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+static int make_head_tmap_b(CUtensorMap* m, const void* base, int HD, long long T, int H, int B, long long row_stride,
+                            long long batch_stride) {
+  uint64_t dims[4] = {(uint64_t)HD, (uint64_t)(T > 0 ? T : 1), (uint64_t)H, (uint64_t)B};
+  uint64_t str[4] = {2, (uint64_t)row_stride * 2, (uint64_t)HD * 2, (uint64_t)batch_stride * 2};
+  uint32_t box[4] = {64, 128, 1, 1};
+  return make_tmap(m, base, 2, 4, dims, str, box, true);
+}
+
+template <int HD>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv,
+                      const CUtensorMap& tks, const CUtensorMap& tvs, const BwdParams& p, cudaStream_t st) {
+  auto k1 = attn_bwd_dq_kernel<HD>;
+  auto k2 = attn_bwd_dkv_kernel<HD>;
+  static bool attr = false;
+  if (!attr) {
+    KSA_CHECK_CUDA(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<HD>::kTotal));
+    KSA_CHECK_CUDA(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<HD>::kTotal));
+    attr = true;
+  }
+  dim3 g1((p.s.Lq + 127) / 128, p.s.Hq, p.s.B);
+  k1<<<g1, kBwdThreads, BwdSmem<HD>::kTotal, st>>>(tq, tdo, tk, tv, tks, tvs, p);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  dim3 g2((p.s.Lk + 127) / 128 + (p.s.Ns + 127) / 128, p.s.Hkv, p.s.B);
+  k2<<<g2, kBwdThreads, BwdSmem<HD>::kTotal, st>>>(tq, tdo, tk, tv, tks, tvs, p);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace ksa
+
+// Backward of ksa_attn_fwd.  Extra inputs: o, d_o [B, Lq, Hq, HD] (same strides), lse [B, Hq, Lq];
+// outputs dq (strides dq_rs/dq_bs), dk/dv (text keys), dks/dvs (summary keys), and delta [B, Hq, Lq] (scratch the
+// caller provides: rowsum(O*dO), written by the first kernel and read by the second).
+KSA_API int ksa_attn_bwd(const void* q, const void* k, const void* v, const void* ks, const void* vs, const void* o,
+                         const void* d_o, const void* lse, void* delta, void* dq, void* dk, void* dv, void* dks,
+                         void* dvs, int B, int Hq, int Hkv, int HD, int Lq, int Lk, int Ns, long long q_rs,
+                         long long q_bs, long long k_rs, long long k_bs, long long v_rs, long long v_bs,
+                         long long ks_rs, long long ks_bs, long long vs_rs, long long vs_bs, long long o_rs,
+                         long long o_bs, long long dq_rs, long long dq_bs, long long dk_rs, long long dk_bs,
+                         long long dv_rs, long long dv_bs, long long dks_rs, long long dks_bs, long long dvs_rs,
+                         long long dvs_bs, int q_off, int k_off, int s_off, int chunk, int n_sum, int window,
+                         int tok_window, float scale, void* stream) {
+  using namespace ksa;
+  KSA_REQUIRE(HD == 128 || HD == 64, "attn_bwd: head_dim %d unsupported (64 or 128)", HD);
+  KSA_REQUIRE(Hq % Hkv == 0, "attn_bwd: Hq %% Hkv != 0");
+  KSA_REQUIRE(o_rs % 8 == 0 && dq_rs % 8 == 0 && dk_rs % 8 == 0 && dv_rs % 8 == 0, "attn_bwd: row strides must be multiples of 8");
+  if (B == 0 || Lq == 0) return 0;
+  CUtensorMap tq, tdo, tk, tv, tks, tvs;
+  int rc;
+  if ((rc = make_head_tmap_b(&tq, q, HD, Lq, Hq, B, q_rs, q_bs))) return rc;
+  if ((rc = make_head_tmap_b(&tdo, d_o, HD, Lq, Hq, B, o_rs, o_bs))) return rc;
+  if ((rc = make_head_tmap_b(&tk, k, HD, Lk, Hkv, B, k_rs, k_bs))) return rc;
+  if ((rc = make_head_tmap_b(&tv, v, HD, Lk, Hkv, B, v_rs, v_bs))) return rc;
+  if (Ns > 0) {
+    if ((rc = make_head_tmap_b(&tks, ks, HD, Ns, Hkv, B, ks_rs, ks_bs))) return rc;
+    if ((rc = make_head_tmap_b(&tvs, vs, HD, Ns, Hkv, B, vs_rs, vs_bs))) return rc;
+  } else {
+    tks = tk;
+    tvs = tv;
+  }
+  BwdParams p;
+  p.s = AttnShape{B, Hq, Hkv, Lq, Lk, Ns, q_off, k_off, s_off, chunk, n_sum > 0 ? n_sum : 1, window, tok_window};
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.o = (const bf16*)o; p.d_o = (const bf16*)d_o; p.o_row_stride = o_rs; p.o_batch_stride = o_bs;
+  p.lse = (const float*)lse; p.delta = (float*)delta;
+  p.dq = (bf16*)dq; p.dq_row_stride = dq_rs; p.dq_batch_stride = dq_bs;
+  p.dk = (bf16*)dk; p.dv = (bf16*)dv;
+  p.dk_row_stride = dk_rs; p.dk_batch_stride = dk_bs; p.dv_row_stride = dv_rs; p.dv_batch_stride = dv_bs;
+  p.dks = (bf16*)dks; p.dvs = (bf16*)dvs;
+  p.dks_row_stride = dks_rs; p.dks_batch_stride = dks_bs; p.dvs_row_stride = dvs_rs; p.dvs_batch_stride = dvs_bs;
+  p.status = status_word();
+  KSA_REQUIRE(p.status != nullptr, "could not allocate the status word");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return HD == 128 ? launch_bwd<128>(tq, tdo, tk, tv, tks, tvs, p, st) : launch_bwd<64>(tq, tdo, tk, tv, tks, tvs, p, st);
+}

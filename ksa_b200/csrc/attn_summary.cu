@@ -1,0 +1,258 @@
+// Attention for the summary-token queries of Kwai Summary Attention.
+//
+// Summary token j of chunk i attends the C text keys of its own chunk and the
+// summary keys (i, j') with j' <= j.  That is one query against C + S keys per
+// chunk: matrix-vector work, bound by reading the chunk's K and V once, so it
+// runs on the CUDA cores next to the tensor-core kernel that serves the text
+// queries.  The reference pushes these rows through the same block-sparse
+// kernel as a 128-row tile that is almost entirely masked
+// (SA!summary_attn/mask.py:19-31).
+#include "common.cuh"
+#include "host.h"
+
+namespace ksa {
+
+struct SumAttnArgs {
+  const bf16* qs; const bf16* k; const bf16* v; const bf16* ks; const bf16* vs;
+  long long qs_rs, qs_bs, k_rs, k_bs, v_rs, v_bs, ks_rs, ks_bs, vs_rs, vs_bs;
+  bf16* os; long long os_rs, os_bs;   // [B, Nq, Hq, HD]
+  float* lse;                         // [B, Hq, Nq]
+  int B, Hq, Hkv, HD;
+  int Nq;          // local summary query rows (= local chunks * S)
+  int L;           // global text length (ragged last chunk)
+  int chunk, n_sum;
+  int chunk0;      // global chunk index of local summary row 0
+  int k_off;       // global text index of local text key row 0
+  int s_off;       // global summary index of local summary key row 0
+  float scale;
+  // backward only
+  const bf16* d_os; bf16* dqs; long long dqs_rs, dqs_bs;
+  bf16* dk; bf16* dv; bf16* dks; bf16* dvs;
+  long long dk_rs, dk_bs, dv_rs, dv_bs, dks_rs, dks_bs, dvs_rs, dvs_bs;
+};
+
+__device__ __forceinline__ float dot_row(const float* q_s, const bf16* row, int HD) {
+  float acc = 0.f;
+  for (int d = 0; d < HD; d += 8) {
+    const uint4 u = *reinterpret_cast<const uint4*>(row + d);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack_bf16x2(w[i]);
+      acc += q_s[d + 2 * i] * f.x + q_s[d + 2 * i + 1] * f.y;
+    }
+  }
+  return acc;
+}
+
+__device__ __forceinline__ float block_reduce_sum128(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return red[0] + red[1] + red[2] + red[3];
+}
+__device__ __forceinline__ float block_reduce_max128(float v, float* red) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+}
+
+// Key row pointer for key index kk in [0, n_text + j]: text keys first, then the chunk's summary keys.
+__device__ __forceinline__ const bf16* key_row(const bf16* text, long long t_rs, const bf16* sum, long long s_rs,
+                                               int kk, int n_text, int text0_local, int sum0_local) {
+  return kk < n_text ? text + (long long)(text0_local + kk) * t_rs : sum + (long long)(sum0_local + kk - n_text) * s_rs;
+}
+
+// grid (local chunks, Hq, B), 128 threads, dynamic smem = (HD + C + S) floats
+__global__ void __launch_bounds__(128) summary_attn_fwd_kernel(SumAttnArgs a) {
+  extern __shared__ float sm[];
+  __shared__ float red[4];
+  float* q_s = sm;
+  float* sc = sm + a.HD;
+  const int ci = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+  const int kvh = head / (a.Hq / a.Hkv);
+  const int cg = a.chunk0 + ci;
+  const int n_text = min(a.chunk, a.L - cg * a.chunk);
+  const int text0 = cg * a.chunk - a.k_off;
+  const int sum0 = cg * a.n_sum - a.s_off;
+  const bf16* kb = a.k + (long long)b * a.k_bs + (long long)kvh * a.HD;
+  const bf16* vb = a.v + (long long)b * a.v_bs + (long long)kvh * a.HD;
+  const bf16* ksb = a.ks + (long long)b * a.ks_bs + (long long)kvh * a.HD;
+  const bf16* vsb = a.vs + (long long)b * a.vs_bs + (long long)kvh * a.HD;
+  for (int j = 0; j < a.n_sum; ++j) {
+    const int row = ci * a.n_sum + j;
+    const bf16* qp = a.qs + (long long)b * a.qs_bs + (long long)row * a.qs_rs + (long long)head * a.HD;
+    __syncthreads();
+    for (int d = threadIdx.x; d < a.HD; d += 128) q_s[d] = __bfloat162float(qp[d]);
+    __syncthreads();
+    const int nk = n_text + j + 1;
+    float mx = -INFINITY;
+    for (int kk = threadIdx.x; kk < nk; kk += 128) {
+      const float s = dot_row(q_s, key_row(kb, a.k_rs, ksb, a.ks_rs, kk, n_text, text0, sum0), a.HD) * a.scale;
+      sc[kk] = s;
+      mx = fmaxf(mx, s);
+    }
+    mx = block_reduce_max128(mx, red);
+    float sum = 0.f;
+    for (int kk = threadIdx.x; kk < nk; kk += 128) {
+      const float pr = __expf(sc[kk] - mx);
+      sc[kk] = pr;
+      sum += pr;
+    }
+    sum = block_reduce_sum128(sum, red);
+    const float inv = 1.f / sum;
+    for (int d = threadIdx.x; d < a.HD; d += 128) {
+      float acc = 0.f;
+      for (int kk = 0; kk < nk; ++kk)
+        acc += sc[kk] * __bfloat162float(key_row(vb, a.v_rs, vsb, a.vs_rs, kk, n_text, text0, sum0)[d]);
+      a.os[(long long)b * a.os_bs + (long long)row * a.os_rs + (long long)head * a.HD + d] = __float2bfloat16(acc * inv);
+    }
+    if (threadIdx.x == 0 && a.lse) a.lse[((long long)b * a.Hq + head) * a.Nq + row] = mx + __logf(sum);
+  }
+}
+
+// grid (local chunks, Hkv, B), 128 threads.
+// dynamic smem: nq * (2*HD + 2*(C+S)) floats with nq = (Hq/Hkv) * S queries per block.
+// dK/dV of the chunk's text keys and summary keys are ADDED to what the text-query backward wrote.
+__global__ void __launch_bounds__(128) summary_attn_bwd_kernel(SumAttnArgs a) {
+  extern __shared__ float sm[];
+  __shared__ float red[4];
+  const int G = a.Hq / a.Hkv, S = a.n_sum, HD = a.HD;
+  const int nq = G * S;
+  const int nkmax = a.chunk + S;
+  float* q_s = sm;                  // [nq][HD]
+  float* do_s = q_s + nq * HD;      // [nq][HD]
+  float* p_s = do_s + nq * HD;      // [nq][nkmax]
+  float* ds_s = p_s + nq * nkmax;   // [nq][nkmax]
+  const int ci = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int cg = a.chunk0 + ci;
+  const int n_text = min(a.chunk, a.L - cg * a.chunk);
+  const int text0 = cg * a.chunk - a.k_off;
+  const int sum0 = cg * S - a.s_off;
+  const bf16* kb = a.k + (long long)b * a.k_bs + (long long)kvh * HD;
+  const bf16* vb = a.v + (long long)b * a.v_bs + (long long)kvh * HD;
+  const bf16* ksb = a.ks + (long long)b * a.ks_bs + (long long)kvh * HD;
+  const bf16* vsb = a.vs + (long long)b * a.vs_bs + (long long)kvh * HD;
+  for (int qi = 0; qi < nq; ++qi) {
+    const int g = qi / S, j = qi % S;
+    const int head = kvh * G + g, row = ci * S + j;
+    const long long qoff = (long long)b * a.qs_bs + (long long)row * a.qs_rs + (long long)head * HD;
+    const long long ooff = (long long)b * a.os_bs + (long long)row * a.os_rs + (long long)head * HD;
+    float part = 0.f;
+    for (int d = threadIdx.x; d < HD; d += 128) {
+      q_s[qi * HD + d] = __bfloat162float(a.qs[qoff + d]);
+      const float g_o = __bfloat162float(a.d_os[ooff + d]);
+      do_s[qi * HD + d] = g_o;
+      part += g_o * __bfloat162float(a.os[ooff + d]);
+    }
+    const float delta = block_reduce_sum128(part, red);   // also orders the smem writes above
+    const float lse = a.lse[((long long)b * a.Hq + head) * a.Nq + row];
+    const int nk = n_text + j + 1;
+    for (int kk = threadIdx.x; kk < nkmax; kk += 128) {
+      float pr = 0.f, ds = 0.f;
+      if (kk < nk) {
+        const float s = dot_row(q_s + qi * HD, key_row(kb, a.k_rs, ksb, a.ks_rs, kk, n_text, text0, sum0), HD) * a.scale;
+        pr = __expf(s - lse);
+        const float dp = dot_row(do_s + qi * HD, key_row(vb, a.v_rs, vsb, a.vs_rs, kk, n_text, text0, sum0), HD);
+        ds = pr * (dp - delta) * a.scale;
+      }
+      p_s[qi * nkmax + kk] = pr;
+      ds_s[qi * nkmax + kk] = ds;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < HD; d += 128) {
+      float acc = 0.f;
+      for (int kk = 0; kk < nk; ++kk)
+        acc += ds_s[qi * nkmax + kk] * __bfloat162float(key_row(kb, a.k_rs, ksb, a.ks_rs, kk, n_text, text0, sum0)[d]);
+      a.dqs[(long long)b * a.dqs_bs + (long long)row * a.dqs_rs + (long long)head * HD + d] = __float2bfloat16(acc);
+    }
+  }
+  __syncthreads();
+  // dK[kk][d] += sum_qi ds[qi][kk] q[qi][d];  dV[kk][d] += sum_qi p[qi][kk] do[qi][d]
+  const int nk_all = n_text + S;
+  for (int idx = threadIdx.x; idx < nk_all * HD; idx += 128) {
+    const int kk = idx / HD, d = idx % HD;
+    float gk = 0.f, gv = 0.f;
+    for (int qi = 0; qi < nq; ++qi) {
+      gk += ds_s[qi * nkmax + kk] * q_s[qi * HD + d];
+      gv += p_s[qi * nkmax + kk] * do_s[qi * HD + d];
+    }
+    bf16 *pk, *pv;
+    if (kk < n_text) {
+      pk = a.dk + (long long)b * a.dk_bs + (long long)(text0 + kk) * a.dk_rs + (long long)kvh * HD + d;
+      pv = a.dv + (long long)b * a.dv_bs + (long long)(text0 + kk) * a.dv_rs + (long long)kvh * HD + d;
+    } else {
+      pk = a.dks + (long long)b * a.dks_bs + (long long)(sum0 + kk - n_text) * a.dks_rs + (long long)kvh * HD + d;
+      pv = a.dvs + (long long)b * a.dvs_bs + (long long)(sum0 + kk - n_text) * a.dvs_rs + (long long)kvh * HD + d;
+    }
+    *pk = __float2bfloat16(__bfloat162float(*pk) + gk);
+    *pv = __float2bfloat16(__bfloat162float(*pv) + gv);
+  }
+}
+
+}  // namespace ksa
+
+using namespace ksa;
+
+KSA_API int ksa_summary_attn_fwd(const void* qs, const void* k, const void* v, const void* ks, const void* vs, void* os,
+                                 void* lse, int B, int Hq, int Hkv, int HD, int Nq, int L, long long qs_rs,
+                                 long long qs_bs, long long k_rs, long long k_bs, long long v_rs, long long v_bs,
+                                 long long ks_rs, long long ks_bs, long long vs_rs, long long vs_bs, long long os_rs,
+                                 long long os_bs, int chunk, int n_sum, int chunk0, int k_off, int s_off, float scale,
+                                 void* stream) {
+  KSA_REQUIRE(HD % 8 == 0 && Hq % Hkv == 0 && n_sum > 0 && Nq % n_sum == 0, "summary_attn_fwd: bad shape");
+  if (B == 0 || Nq == 0) return 0;
+  SumAttnArgs a{};
+  a.qs = (const bf16*)qs; a.k = (const bf16*)k; a.v = (const bf16*)v; a.ks = (const bf16*)ks; a.vs = (const bf16*)vs;
+  a.qs_rs = qs_rs; a.qs_bs = qs_bs; a.k_rs = k_rs; a.k_bs = k_bs; a.v_rs = v_rs; a.v_bs = v_bs;
+  a.ks_rs = ks_rs; a.ks_bs = ks_bs; a.vs_rs = vs_rs; a.vs_bs = vs_bs;
+  a.os = (bf16*)os; a.os_rs = os_rs; a.os_bs = os_bs; a.lse = (float*)lse;
+  a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.HD = HD; a.Nq = Nq; a.L = L; a.chunk = chunk; a.n_sum = n_sum;
+  a.chunk0 = chunk0; a.k_off = k_off; a.s_off = s_off; a.scale = scale;
+  const size_t smem = (size_t)(HD + chunk + n_sum) * sizeof(float);
+  KSA_REQUIRE(smem <= 48 * 1024, "summary_attn_fwd: chunk %d too large for the SIMT kernel", chunk);
+  dim3 grid(Nq / n_sum, Hq, B);
+  summary_attn_fwd_kernel<<<grid, 128, smem, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+KSA_API int ksa_summary_attn_bwd(const void* qs, const void* k, const void* v, const void* ks, const void* vs,
+                                 const void* os, const void* d_os, const void* lse, void* dqs, void* dk, void* dv,
+                                 void* dks, void* dvs, int B, int Hq, int Hkv, int HD, int Nq, int L, long long qs_rs,
+                                 long long qs_bs, long long k_rs, long long k_bs, long long v_rs, long long v_bs,
+                                 long long ks_rs, long long ks_bs, long long vs_rs, long long vs_bs, long long os_rs,
+                                 long long os_bs, long long dqs_rs, long long dqs_bs, long long dk_rs, long long dk_bs,
+                                 long long dv_rs, long long dv_bs, long long dks_rs, long long dks_bs, long long dvs_rs,
+                                 long long dvs_bs, int chunk, int n_sum, int chunk0, int k_off, int s_off, float scale,
+                                 void* stream) {
+  KSA_REQUIRE(HD % 8 == 0 && Hq % Hkv == 0 && n_sum > 0 && Nq % n_sum == 0, "summary_attn_bwd: bad shape");
+  if (B == 0 || Nq == 0) return 0;
+  SumAttnArgs a{};
+  a.qs = (const bf16*)qs; a.k = (const bf16*)k; a.v = (const bf16*)v; a.ks = (const bf16*)ks; a.vs = (const bf16*)vs;
+  a.qs_rs = qs_rs; a.qs_bs = qs_bs; a.k_rs = k_rs; a.k_bs = k_bs; a.v_rs = v_rs; a.v_bs = v_bs;
+  a.ks_rs = ks_rs; a.ks_bs = ks_bs; a.vs_rs = vs_rs; a.vs_bs = vs_bs;
+  a.os = (bf16*)os; a.os_rs = os_rs; a.os_bs = os_bs; a.lse = (float*)lse;
+  a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.HD = HD; a.Nq = Nq; a.L = L; a.chunk = chunk; a.n_sum = n_sum;
+  a.chunk0 = chunk0; a.k_off = k_off; a.s_off = s_off; a.scale = scale;
+  a.d_os = (const bf16*)d_os; a.dqs = (bf16*)dqs; a.dqs_rs = dqs_rs; a.dqs_bs = dqs_bs;
+  a.dk = (bf16*)dk; a.dv = (bf16*)dv; a.dks = (bf16*)dks; a.dvs = (bf16*)dvs;
+  a.dk_rs = dk_rs; a.dk_bs = dk_bs; a.dv_rs = dv_rs; a.dv_bs = dv_bs;
+  a.dks_rs = dks_rs; a.dks_bs = dks_bs; a.dvs_rs = dvs_rs; a.dvs_bs = dvs_bs;
+  const int nq = (Hq / Hkv) * n_sum;
+  const size_t smem = (size_t)nq * (2 * HD + 2 * (chunk + n_sum)) * sizeof(float);
+  KSA_REQUIRE(smem <= 200 * 1024, "summary_attn_bwd: %zu bytes of shared memory needed (chunk %d, %d queries)", smem,
+              chunk, nq);
+  static bool attr = false;
+  if (!attr) {
+    KSA_CHECK_CUDA(cudaFuncSetAttribute(summary_attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr = true;
+  }
+  dim3 grid(Nq / n_sum, Hkv, B);
+  summary_attn_bwd_kernel<<<grid, 128, smem, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

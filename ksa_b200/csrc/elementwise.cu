@@ -1,0 +1,653 @@
+// Memory-bound fused kernels: (residual add +) RMSNorm, per-head QK-RMSNorm + RoPE,
+// SwiGLU, embedding gather / scatter-add, softmax cross-entropy with in-place
+// gradient, AdamW on fp32 master state.  Each replaces an unfused ATen chain of the
+// reference (muse/layers/rms_norm.py:67-80, muse/layers/position_embeddings.py:245-293,
+// muse/layers/feed_forward.py:70-83, muse/losses/ce.py:32-140, torch.optim.AdamW).
+// All of them move 16 bytes per thread per access and keep their statistics in fp32.
+#include "common.cuh"
+#include "host.h"
+
+namespace ksa {
+
+struct alignas(16) BF8 {
+  uint32_t u[4];
+};
+
+__device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
+  BF8 v = *reinterpret_cast<const BF8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = unpack_bf16x2(v.u[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
+  BF8 v;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v.u[i] = pack_bf16x2(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<BF8*>(p) = v;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < THREADS / 32) ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < THREADS / 32) ? red[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+// ------------------------------------------------------------------------------ RMSNorm
+// One CTA of 256 threads per row; D <= 256 * 8 * kMaxVec.
+constexpr int kNormThreads = 256;
+constexpr int kNormMaxVec = 4;  // D up to 8192
+
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, const bf16* __restrict__ w,
+                   bf16* __restrict__ res_out, bf16* __restrict__ y, float* __restrict__ rstd_out, int rows, int D,
+                   float eps) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  const long long base = (long long)row * D;
+  float v[kNormMaxVec][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int c = (i * kNormThreads + threadIdx.x) * 8;
+    if (c < D) {
+      load8(x + base + c, v[i]);
+      if (delta) {
+        float d[8];
+        load8(delta + base + c, d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] += d[j];
+        // round the residual stream to bf16 first so that norm and stream agree
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16(v[i][j]));
+        if (res_out) store8(res_out + base + c, v[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  ss = block_sum<kNormThreads>(ss, red);
+  const float rstd = rsqrtf(ss / (float)D + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int c = (i * kNormThreads + threadIdx.x) * 8;
+    if (c < D) {
+      float wv[8], o[8];
+      load8(w + c, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * wv[j];
+      store8(y + base + c, o);
+    }
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres); per-CTA partial dw rows in `dw_partial`.
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                   const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int rows, int D) {
+  __shared__ float red[32];
+  float wv[kNormMaxVec][8];
+  float dw[kNormMaxVec][8];
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int c = (i * kNormThreads + threadIdx.x) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw[i][j] = 0.f;
+    if (c < D) load8(w + c, wv[i]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const long long base = (long long)row * D;
+    const float rstd = rstd_in[row];
+    float xh[kNormMaxVec][8], g[kNormMaxVec][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormMaxVec; ++i) {
+      const int c = (i * kNormThreads + threadIdx.x) * 8;
+      if (c < D) {
+        float xv[8], dyv[8];
+        load8(x + base + c, xv);
+        load8(dy + base + c, dyv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = xv[j] * rstd;
+          g[i][j] = dyv[j] * wv[i][j];
+          dot += g[i][j] * xh[i][j];
+          dw[i][j] += dyv[j] * xh[i][j];
+        }
+      }
+    }
+    dot = block_sum<kNormThreads>(dot, red) / (float)D;
+#pragma unroll
+    for (int i = 0; i < kNormMaxVec; ++i) {
+      const int c = (i * kNormThreads + threadIdx.x) * 8;
+      if (c < D) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * dot);
+        if (dres) {
+          float r[8];
+          load8(dres + base + c, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        store8(dx + base + c, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int c = (i * kNormThreads + threadIdx.x) * 8;
+    if (c < D) {
+      float* p = dw_partial + (long long)blockIdx.x * D + c;
+      *reinterpret_cast<float4*>(p) = make_float4(dw[i][0], dw[i][1], dw[i][2], dw[i][3]);
+      *reinterpret_cast<float4*>(p + 4) = make_float4(dw[i][4], dw[i][5], dw[i][6], dw[i][7]);
+    }
+  }
+}
+
+// dw[c] (+)= sum over partial rows.
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nparts, int D,
+                                       int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partial[(long long)p * D + c];
+  dw[c] = accumulate ? dw[c] + s : s;
+}
+
+// ------------------------------------------------------------------------------ QK-norm + RoPE
+// One warp per (row, head); head_dim = 128 (4 elements per lane) or 64 (2 per lane).
+// Lane l owns rotary pairs (p, p + D/2) for p in [l*PAIRS, (l+1)*PAIRS).
+struct QkRopeArgs {
+  const bf16* qkv;       // [rows, in_stride] : q heads | k heads | v heads
+  bf16* out;             // [rows, out_stride]: q heads | k heads
+  const bf16* q_w;       // [D] or null (no q-norm)
+  const bf16* k_w;       // [D] or null
+  const int* pos;        // [rows]
+  float* rstd;           // [rows, Hq+Hkv] (written in fwd, read in bwd)
+  long long in_stride, out_stride;
+  int rows, Hq, Hkv, D;
+  float log2_theta, eps;
+  int interleaved;       // 1: adjacent-pair (Llama) rotary, 0: half-split (HF)
+};
+
+template <int D>
+__global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(QkRopeArgs a) {
+  constexpr int PAIRS = D / 64;  // rotary pairs per lane
+  const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int H = a.Hq + a.Hkv;
+  if (warp_global >= a.rows * H) return;
+  const int row = warp_global / H, head = warp_global % H;
+  const bf16* src = a.qkv + (long long)row * a.in_stride + (long long)head * D;
+  bf16* dst = a.out + (long long)row * a.out_stride + (long long)head * D;
+  const bf16* w = head < a.Hq ? a.q_w : a.k_w;
+  float x1[PAIRS], x2[PAIRS];
+  int i1[PAIRS], i2[PAIRS];
+  float ss = 0.f;
+#pragma unroll
+  for (int p = 0; p < PAIRS; ++p) {
+    const int pi = lane * PAIRS + p;
+    i1[p] = a.interleaved ? 2 * pi : pi;
+    i2[p] = a.interleaved ? 2 * pi + 1 : pi + D / 2;
+    x1[p] = __bfloat162float(src[i1[p]]);
+    x2[p] = __bfloat162float(src[i2[p]]);
+    ss += x1[p] * x1[p] + x2[p] * x2[p];
+  }
+  float rstd = 1.f;
+  if (w) {
+    ss = warp_sum(ss);
+    rstd = rsqrtf(ss / (float)D + a.eps);
+  }
+  if (lane == 0) a.rstd[(long long)row * H + head] = rstd;
+  const float pos = (float)a.pos[row];
+#pragma unroll
+  for (int p = 0; p < PAIRS; ++p) {
+    const int pi = lane * PAIRS + p;
+    float n1 = x1[p] * rstd, n2 = x2[p] * rstd;
+    if (w) {
+      n1 *= __bfloat162float(w[i1[p]]);
+      n2 *= __bfloat162float(w[i2[p]]);
+    }
+    const float inv_freq = exp2f(-a.log2_theta * (2.f * (float)pi / (float)D));
+    float s, c;
+    sincosf(pos * inv_freq, &s, &c);
+    dst[i1[p]] = __float2bfloat16(n1 * c - n2 * s);
+    dst[i2[p]] = __float2bfloat16(n2 * c + n1 * s);
+  }
+}
+
+// Backward: d_out [rows, out_stride] -> d_qkv (q and k parts) [rows, in_stride]; dw accumulated with atomics.
+struct QkRopeBwdArgs {
+  QkRopeArgs f;          // forward arguments (qkv = pre-norm input, rstd = saved)
+  const bf16* d_out;     // gradient w.r.t. rotated q | k
+  bf16* d_qkv;           // gradient w.r.t. pre-norm q | k (packed layout, v part untouched)
+  float* dq_w;           // [D] fp32, accumulated
+  float* dk_w;           // [D] fp32, accumulated
+};
+
+template <int D>
+__global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(QkRopeBwdArgs b) {
+  constexpr int PAIRS = D / 64;
+  const QkRopeArgs& a = b.f;
+  __shared__ float s_dw[2][D];
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&s_dw[0][0])[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int H = a.Hq + a.Hkv;
+  const int total = a.rows * H;
+  for (int wg = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); wg < total; wg += gridDim.x * (blockDim.x >> 5)) {
+    const int row = wg / H, head = wg % H;
+    const bf16* src = a.qkv + (long long)row * a.in_stride + (long long)head * D;
+    const bf16* g = b.d_out + (long long)row * a.out_stride + (long long)head * D;
+    bf16* dst = b.d_qkv + (long long)row * a.in_stride + (long long)head * D;
+    const bf16* w = head < a.Hq ? a.q_w : a.k_w;
+    const float rstd = a.rstd[(long long)row * H + head];
+    const float pos = (float)a.pos[row];
+    float xh1[PAIRS], xh2[PAIRS], gn1[PAIRS], gn2[PAIRS];
+    int i1[PAIRS], i2[PAIRS];
+    float dot = 0.f;
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) {
+      const int pi = lane * PAIRS + p;
+      i1[p] = a.interleaved ? 2 * pi : pi;
+      i2[p] = a.interleaved ? 2 * pi + 1 : pi + D / 2;
+      const float inv_freq = exp2f(-a.log2_theta * (2.f * (float)pi / (float)D));
+      float s, c;
+      sincosf(pos * inv_freq, &s, &c);
+      const float g1 = __bfloat162float(g[i1[p]]), g2 = __bfloat162float(g[i2[p]]);
+      // transpose of the rotation
+      float dn1 = g1 * c + g2 * s;
+      float dn2 = g2 * c - g1 * s;
+      xh1[p] = __bfloat162float(src[i1[p]]) * rstd;
+      xh2[p] = __bfloat162float(src[i2[p]]) * rstd;
+      if (w) {
+        atomicAdd(&s_dw[head < a.Hq ? 0 : 1][i1[p]], dn1 * xh1[p]);
+        atomicAdd(&s_dw[head < a.Hq ? 0 : 1][i2[p]], dn2 * xh2[p]);
+        dn1 *= __bfloat162float(w[i1[p]]);
+        dn2 *= __bfloat162float(w[i2[p]]);
+      }
+      gn1[p] = dn1;
+      gn2[p] = dn2;
+      dot += dn1 * xh1[p] + dn2 * xh2[p];
+    }
+    if (w) {
+      dot = warp_sum(dot) / (float)D;
+#pragma unroll
+      for (int p = 0; p < PAIRS; ++p) {
+        dst[i1[p]] = __float2bfloat16(rstd * (gn1[p] - xh1[p] * dot));
+        dst[i2[p]] = __float2bfloat16(rstd * (gn2[p] - xh2[p] * dot));
+      }
+    } else {
+#pragma unroll
+      for (int p = 0; p < PAIRS; ++p) {
+        dst[i1[p]] = __float2bfloat16(gn1[p]);
+        dst[i2[p]] = __float2bfloat16(gn2[p]);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    if (b.dq_w && s_dw[0][i] != 0.f) atomicAdd(&b.dq_w[i], s_dw[0][i]);
+    if (b.dk_w && s_dw[1][i] != 0.f) atomicAdd(&b.dk_w[i], s_dw[1][i]);
+  }
+}
+
+// ------------------------------------------------------------------------------ SwiGLU
+// gate_up is [rows, 2F] = [gate | up]; out is [rows, F].
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long long rows, int F) {
+  const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int per_row = F / 8;
+  if (vec >= rows * per_row) return;
+  const long long row = vec / per_row;
+  const int c = (int)(vec % per_row) * 8;
+  float g[8], u[8], o[8];
+  load8(gu + row * 2 * F + c, g);
+  load8(gu + row * 2 * F + F + c, u);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+  store8(out + row * F + c, o);
+}
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ dout, bf16* __restrict__ dgu, long long rows,
+                  int F) {
+  const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int per_row = F / 8;
+  if (vec >= rows * per_row) return;
+  const long long row = vec / per_row;
+  const int c = (int)(vec % per_row) * 8;
+  float g[8], u[8], d[8], dg[8], du[8];
+  load8(gu + row * 2 * F + c, g);
+  load8(gu + row * 2 * F + F + c, u);
+  load8(dout + row * F + c, d);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float sig = 1.f / (1.f + __expf(-g[j]));
+    const float silu = g[j] * sig;
+    du[j] = d[j] * silu;
+    dg[j] = d[j] * u[j] * sig * (1.f + g[j] * (1.f - sig));
+  }
+  store8(dgu + row * 2 * F + c, dg);
+  store8(dgu + row * 2 * F + F + c, du);
+}
+
+// ------------------------------------------------------------------------------ embedding
+__global__ void __launch_bounds__(256)
+embedding_fwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ table, bf16* __restrict__ out,
+                     long long rows, int D, long long vocab) {
+  const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int per_row = D / 8;
+  if (vec >= rows * per_row) return;
+  const long long row = vec / per_row;
+  const int c = (int)(vec % per_row) * 8;
+  long long id = ids[row];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  *reinterpret_cast<BF8*>(out + row * D + c) = *reinterpret_cast<const BF8*>(table + id * D + c);
+}
+__global__ void __launch_bounds__(256)
+embedding_bwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ dout, float* __restrict__ dtable,
+                     long long rows, int D, long long vocab) {
+  const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int per_row = D / 8;
+  if (vec >= rows * per_row) return;
+  const long long row = vec / per_row;
+  const int c = (int)(vec % per_row) * 8;
+  long long id = ids[row];
+  if (id < 0 || id >= vocab) return;
+  float g[8];
+  load8(dout + row * D + c, g);
+  float* dst = dtable + id * D + c;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) atomicAdd(dst + j, g[j]);
+}
+
+// ------------------------------------------------------------------------------ cross entropy
+// One CTA per row of bf16 logits [rows, V].  Writes per-row loss (0 for ignored rows) and turns the
+// logits into d(loss)/d(logits) * (*grad_scale) in place.
+constexpr int kCeThreads = 512;
+__global__ void __launch_bounds__(kCeThreads)
+cross_entropy_kernel(bf16* __restrict__ logits, const long long* __restrict__ labels, float* __restrict__ row_loss,
+                     const float* __restrict__ grad_scale, int V, long long ld, int ignore_index, int write_grad) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  bf16* lg = logits + row * ld;
+  const long long label = labels[row];
+  const bool ignored = (label == ignore_index) || label < 0 || label >= V;
+  const int nvec = V / 8;
+  if (ignored) {
+    if (threadIdx.x == 0) row_loss[row] = 0.f;
+    if (write_grad) {
+      BF8 z{{0, 0, 0, 0}};
+      for (int i = threadIdx.x; i < nvec; i += kCeThreads) *reinterpret_cast<BF8*>(lg + i * 8) = z;
+    }
+    return;
+  }
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
+    float f[8];
+    load8(lg + i * 8, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
+  }
+  mx = block_max<kCeThreads>(mx, red);
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
+    float f[8];
+    load8(lg + i * 8, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum += __expf(f[j] - mx);
+  }
+  sum = block_sum<kCeThreads>(sum, red);
+  const float lse = mx + __logf(sum);
+  if (threadIdx.x == 0) row_loss[row] = lse - __bfloat162float(lg[label]);
+  if (!write_grad) return;
+  __syncthreads();
+  const float gs = *grad_scale;
+  const float inv = 1.f / sum;
+  for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
+    float f[8];
+    load8(lg + i * 8, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float p = __expf(f[j] - mx) * inv;
+      if ((long long)i * 8 + j == label) p -= 1.f;
+      f[j] = p * gs;
+    }
+    store8(lg + i * 8, f);
+  }
+}
+
+// n_valid and 1/n_valid (times an extra scale) on the device: no host sync in the step.
+__global__ void count_valid_kernel(const long long* __restrict__ labels, long long n, int ignore_index, float extra_scale,
+                                   float* __restrict__ out /* [0]=count, [1]=extra/count */) {
+  __shared__ float red[32];
+  float c = 0.f;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) c += (labels[i] != ignore_index) ? 1.f : 0.f;
+  c = block_sum<1024>(c, red);
+  if (threadIdx.x == 0) {
+    out[0] = c;
+    out[1] = extra_scale / fmaxf(c, 1.f);
+  }
+}
+
+// ------------------------------------------------------------------------------ AdamW
+// hyper[0]=lr, [1]=1-beta1^t, [2]=1-beta2^t, [3]=gradient scale; read from device memory so that a
+// captured CUDA graph stays valid while the schedule advances.
+__global__ void __launch_bounds__(256)
+adamw_kernel(float* __restrict__ master, const float* __restrict__ grad, float* __restrict__ m, float* __restrict__ v,
+             bf16* __restrict__ out_bf16, long long n, const float* __restrict__ hyper, float beta1, float beta2,
+             float eps, float weight_decay, float clip_value, float* __restrict__ sumsq) {
+  __shared__ float red[32];
+  const float lr = hyper[0], bc1 = hyper[1], bc2 = hyper[2], gscale = hyper[3];
+  float sq = 0.f;
+  const long long nvec = n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float4 g4 = reinterpret_cast<const float4*>(grad)[i];
+    float4 p4 = reinterpret_cast<float4*>(master)[i];
+    float4 m4 = reinterpret_cast<float4*>(m)[i];
+    float4 v4 = reinterpret_cast<float4*>(v)[i];
+    float g[4] = {g4.x, g4.y, g4.z, g4.w}, p[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w},
+          vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float gj = g[j] * gscale;
+      sq += gj * gj;
+      if (clip_value > 0.f) gj = fminf(fmaxf(gj, -clip_value), clip_value);
+      mm[j] = beta1 * mm[j] + (1.f - beta1) * gj;
+      vv[j] = beta2 * vv[j] + (1.f - beta2) * gj * gj;
+      const float denom = sqrtf(vv[j] / bc2) + eps;
+      p[j] = p[j] * (1.f - lr * weight_decay) - lr * (mm[j] / bc1) / denom;
+    }
+    reinterpret_cast<float4*>(master)[i] = make_float4(p[0], p[1], p[2], p[3]);
+    reinterpret_cast<float4*>(m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    if (out_bf16) {
+      uint2 o = make_uint2(pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]));
+      reinterpret_cast<uint2*>(out_bf16)[i] = o;
+    }
+  }
+  if (sumsq) {
+    sq = block_sum<256>(sq, red);
+    if (threadIdx.x == 0) atomicAdd(sumsq, sq);
+  }
+}
+
+// fp32 -> bf16 cast (flat), used to refresh compute weights from master weights.
+__global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float* __restrict__ src, bf16* __restrict__ dst, long long n) {
+  const long long nvec = n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float4 a = reinterpret_cast<const float4*>(src)[i];
+    reinterpret_cast<uint2*>(dst)[i] = make_uint2(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w));
+  }
+}
+
+}  // namespace ksa
+
+using namespace ksa;
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+
+KSA_API int ksa_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* res_out, void* y, void* rstd,
+                            int rows, int D, float eps, void* stream) {
+  KSA_REQUIRE(D % 8 == 0 && D <= kNormThreads * 8 * kNormMaxVec, "rmsnorm: D=%d must be a multiple of 8 and <= %d", D,
+              kNormThreads * 8 * kNormMaxVec);
+  if (rows == 0) return 0;
+  rmsnorm_fwd_kernel<<<rows, kNormThreads, 0, ST(stream)>>>((const bf16*)x, (const bf16*)delta, (const bf16*)w,
+                                                            (bf16*)res_out, (bf16*)y, (float*)rstd, rows, D, eps);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Number of partial rows the backward writes: the caller sizes `dw_partial` as [ksa_rmsnorm_bwd_parts(rows), D] fp32.
+KSA_API int ksa_rmsnorm_bwd_parts(int rows) { return rows < 592 ? (rows > 0 ? rows : 1) : 592; }
+
+KSA_API int ksa_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rstd, const void* dres, void* dx,
+                            void* dw_partial, void* dw, int accumulate_dw, int rows, int D, void* stream) {
+  KSA_REQUIRE(D % 8 == 0 && D <= kNormThreads * 8 * kNormMaxVec, "rmsnorm: D=%d unsupported", D);
+  if (rows == 0) return 0;
+  const int parts = ksa_rmsnorm_bwd_parts(rows);
+  rmsnorm_bwd_kernel<<<parts, kNormThreads, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
+                                                             (const float*)rstd, (const bf16*)dres, (bf16*)dx,
+                                                             (float*)dw_partial, rows, D);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  if (dw) {
+    colsum_partials_kernel<<<(D + 255) / 256, 256, 0, ST(stream)>>>((const float*)dw_partial, (float*)dw, parts, D,
+                                                                    accumulate_dw);
+    KSA_CHECK_CUDA(cudaGetLastError());
+  }
+  return 0;
+}
+
+KSA_API int ksa_qknorm_rope_fwd(const void* qkv, void* out, const void* q_w, const void* k_w, const void* pos,
+                                void* rstd, long long in_stride, long long out_stride, int rows, int Hq, int Hkv, int D,
+                                float theta, float eps, int interleaved, void* stream) {
+  KSA_REQUIRE(D == 128 || D == 64, "qknorm_rope: head_dim %d unsupported (64 or 128)", D);
+  if (rows == 0) return 0;
+  QkRopeArgs a{(const bf16*)qkv, (bf16*)out, (const bf16*)q_w, (const bf16*)k_w, (const int*)pos, (float*)rstd,
+               in_stride, out_stride, rows, Hq, Hkv, D, log2f(theta), eps, interleaved};
+  const long long warps = (long long)rows * (Hq + Hkv);
+  const int blocks = (int)((warps + 7) / 8);
+  if (D == 128) qknorm_rope_fwd_kernel<128><<<blocks, 256, 0, ST(stream)>>>(a);
+  else qknorm_rope_fwd_kernel<64><<<blocks, 256, 0, ST(stream)>>>(a);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+KSA_API int ksa_qknorm_rope_bwd(const void* qkv, const void* d_out, void* d_qkv, const void* q_w, const void* k_w,
+                                const void* pos, const void* rstd, void* dq_w, void* dk_w, long long in_stride,
+                                long long out_stride, int rows, int Hq, int Hkv, int D, float theta, float eps,
+                                int interleaved, void* stream) {
+  KSA_REQUIRE(D == 128 || D == 64, "qknorm_rope: head_dim %d unsupported (64 or 128)", D);
+  if (rows == 0) return 0;
+  QkRopeBwdArgs b{{(const bf16*)qkv, nullptr, (const bf16*)q_w, (const bf16*)k_w, (const int*)pos, (float*)rstd,
+                   in_stride, out_stride, rows, Hq, Hkv, D, log2f(theta), eps, interleaved},
+                  (const bf16*)d_out, (bf16*)d_qkv, (float*)dq_w, (float*)dk_w};
+  const long long warps = (long long)rows * (Hq + Hkv);
+  long long blocks = (warps + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (D == 128) qknorm_rope_bwd_kernel<128><<<(int)blocks, 256, 0, ST(stream)>>>(b);
+  else qknorm_rope_bwd_kernel<64><<<(int)blocks, 256, 0, ST(stream)>>>(b);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+KSA_API int ksa_swiglu_fwd(const void* gu, void* out, long long rows, int F, void* stream) {
+  KSA_REQUIRE(F % 8 == 0, "swiglu: F=%d must be a multiple of 8", F);
+  const long long n = rows * (F / 8);
+  if (n == 0) return 0;
+  swiglu_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ST(stream)>>>((const bf16*)gu, (bf16*)out, rows, F);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+KSA_API int ksa_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long rows, int F, void* stream) {
+  KSA_REQUIRE(F % 8 == 0, "swiglu: F=%d must be a multiple of 8", F);
+  const long long n = rows * (F / 8);
+  if (n == 0) return 0;
+  swiglu_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ST(stream)>>>((const bf16*)gu, (const bf16*)dout, (bf16*)dgu,
+                                                                        rows, F);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+KSA_API int ksa_embedding_fwd(const void* ids, const void* table, void* out, long long rows, int D, long long vocab,
+                              void* stream) {
+  KSA_REQUIRE(D % 8 == 0, "embedding: D=%d must be a multiple of 8", D);
+  const long long n = rows * (D / 8);
+  if (n == 0) return 0;
+  embedding_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ST(stream)>>>((const long long*)ids, (const bf16*)table,
+                                                                           (bf16*)out, rows, D, vocab);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+KSA_API int ksa_embedding_bwd(const void* ids, const void* dout, void* dtable_f32, long long rows, int D,
+                              long long vocab, void* stream) {
+  KSA_REQUIRE(D % 8 == 0, "embedding: D=%d must be a multiple of 8", D);
+  const long long n = rows * (D / 8);
+  if (n == 0) return 0;
+  embedding_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ST(stream)>>>((const long long*)ids, (const bf16*)dout,
+                                                                           (float*)dtable_f32, rows, D, vocab);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+KSA_API int ksa_count_valid(const void* labels, long long n, int ignore_index, float extra_scale, void* out2,
+                            void* stream) {
+  count_valid_kernel<<<1, 1024, 0, ST(stream)>>>((const long long*)labels, n, ignore_index, extra_scale, (float*)out2);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+KSA_API int ksa_cross_entropy(void* logits, const void* labels, void* row_loss, const void* grad_scale, long long rows,
+                              int V, long long ld, int ignore_index, int write_grad, void* stream) {
+  KSA_REQUIRE(V % 8 == 0 && ld % 8 == 0, "cross_entropy: V=%d and ld=%lld must be multiples of 8", V, ld);
+  if (rows == 0) return 0;
+  cross_entropy_kernel<<<(unsigned)rows, kCeThreads, 0, ST(stream)>>>((bf16*)logits, (const long long*)labels,
+                                                                     (float*)row_loss, (const float*)grad_scale, V, ld,
+                                                                     ignore_index, write_grad);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+KSA_API int ksa_adamw(void* master, const void* grad, void* m, void* v, void* out_bf16, long long n, const void* hyper,
+                      float beta1, float beta2, float eps, float weight_decay, float clip_value, void* sumsq,
+                      void* stream) {
+  KSA_REQUIRE(n % 4 == 0, "adamw: n=%lld must be a multiple of 4 (pad the flat buffer)", n);
+  if (n == 0) return 0;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  adamw_kernel<<<(unsigned)blocks, 256, 0, ST(stream)>>>((float*)master, (const float*)grad, (float*)m, (float*)v,
+                                                        (bf16*)out_bf16, n, (const float*)hyper, beta1, beta2, eps,
+                                                        weight_decay, clip_value, (float*)sumsq);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+KSA_API int ksa_cast_f32_bf16(const void* src, void* dst, long long n, void* stream) {
+  KSA_REQUIRE(n % 4 == 0, "cast: n=%lld must be a multiple of 4", n);
+  if (n == 0) return 0;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cast_f32_bf16_kernel<<<(unsigned)blocks, 256, 0, ST(stream)>>>((const float*)src, (bf16*)dst, n);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,107 @@
+// Host-side runtime of the kernel library: last-error string, TMA descriptor
+// encoding, the device status word written by bounded waits.
+#include "host.h"
+
+#include <mutex>
+#include <stdarg.h>
+#include <string.h>
+
+namespace ksa {
+
+static thread_local char g_last_error[512] = "";
+
+void set_last_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+}
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+int make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) {
+    set_last_error("cuTensorMapEncodeTiled is not available from the driver");
+    return kErrNoDriver;
+  }
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[4];
+  cuuint32_t bdim[5];
+  cuuint32_t estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estr[i] = 1;
+    if (i > 0) gstr[i - 1] = strides_bytes[i];
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) {
+    set_last_error("TMA base address %p is not 16-byte aligned", base);
+    return kErrArgument;
+  }
+  for (int i = 1; i < rank; ++i) {
+    if (strides_bytes[i] % 16 != 0) {
+      set_last_error("TMA stride %d = %llu bytes is not a multiple of 16", i, (unsigned long long)strides_bytes[i]);
+      return kErrArgument;
+    }
+  }
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = enc(out, dt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu, box %u x %u)", (int)r,
+                   rank, (unsigned long long)dims[0], (unsigned long long)(rank > 1 ? dims[1] : 0), box[0],
+                   rank > 1 ? box[1] : 0);
+    return kErrCuda;
+  }
+  return kErrNone;
+}
+
+static int* g_status[64] = {nullptr};
+static std::mutex g_status_mu;
+
+int* status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_status_mu);
+  if (!g_status[dev]) {
+    int* p = nullptr;
+    if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, 256);
+    g_status[dev] = p;
+  }
+  return g_status[dev];
+}
+
+}  // namespace ksa
+
+KSA_API const char* ksa_last_error() { return ksa::g_last_error; }
+
+// Address of the status word of the current device (for torch to wrap / read).
+KSA_API void* ksa_status_ptr() { return ksa::status_word(); }
+
+// Read and clear the status word (synchronises the device).  Returns the status, or -1 on a CUDA error.
+KSA_API int ksa_read_status(int clear) {
+  int* p = ksa::status_word();
+  if (!p) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (clear && v != 0) cudaMemset(p, 0, sizeof(int));
+  return v;
+}
+
+KSA_API int ksa_abi_version() { return 1; }

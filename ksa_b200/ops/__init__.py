@@ -1,0 +1,564 @@
+"""Functional ops of the framework.
+
+Every op has two implementations behind one signature:
+
+* CUDA tensors run the hand-written sm_100a kernels of ``ksa_b200/csrc`` through
+  ``torch.autograd.Function`` wrappers (forward and backward are both kernels);
+* CPU tensors run the plain PyTorch formulas of :mod:`ksa_b200.ops.reference`,
+  which are also the numerics oracle of the GPU tests.
+
+There is no third path: a CUDA tensor never falls back to ATen, and a missing
+kernel library on a GPU machine raises.
+
+Weight gradients.  When a weight tensor carries a ``main_grad`` attribute (an
+fp32 buffer owned by the training engine), backward kernels write or accumulate
+the weight gradient straight into it and autograd sees ``None`` for that input;
+``_grad_written`` on the weight tells whether the buffer already holds a
+contribution of the current accumulation window.  Otherwise the gradient is
+returned to autograd in the weight's dtype.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import reference as ref
+from . import _lib
+from .layout import SummaryLayout, get_layout
+
+UNBOUNDED_WINDOW = 1 << 30
+
+
+def _cuda(x: torch.Tensor) -> bool:
+    return x.is_cuda
+
+
+def _require_bf16(*ts):
+    for t in ts:
+        if t is not None and t.dtype != torch.bfloat16:
+            raise TypeError(f"the sm_100a kernels take bf16 activations/weights, got {t.dtype}")
+
+
+# =============================================================================== GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+         accumulate: bool = False, alpha: float = 1.0, sm_limit: int = 0) -> torch.Tensor:
+    """``C[M,N] = alpha * op(A) op(B) (+ C)`` on the tcgen05 GEMM.
+
+    ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn_major``); ``b`` is ``[N,K]`` (or
+    ``[K,N]`` when ``b_mn_major``).  Row strides may exceed the row length
+    (views of packed buffers); the last dimension must be contiguous.
+    """
+    _require_bf16(a, b)
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    M, K = (a.shape[1], a.shape[0]) if a_mn_major else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn_major else (b.shape[0], b.shape[1])
+    assert K == Kb, f"reduction mismatch {K} vs {Kb}"
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    assert out.shape == (M, N) and out.stride(1) == 1
+    _lib.call("ksa_gemm_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
+              int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate),
+              float(alpha), int(sm_limit))
+    return out
+
+
+def _weight_grad(weight: torch.Tensor, compute):
+    """Route a weight gradient: into ``weight.main_grad`` (fp32) or back to autograd.
+
+    ``compute(out, accumulate)`` must fill ``out``; with ``out=None`` it returns a new bf16 tensor.
+    """
+    mg = getattr(weight, "main_grad", None)
+    if mg is not None:
+        first = not getattr(weight, "_grad_written", False)
+        compute(mg, not first)
+        weight._grad_written = True
+        return None
+    return compute(None, False)
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        y = gemm(x2, weight)
+        ctx.save_for_backward(x2, weight)
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1:
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn_major=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            def compute(out, acc):
+                if out is None:
+                    return gemm(dy2, x2, a_mn_major=True, b_mn_major=True)
+                gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=out, accumulate=acc)
+            dw = _weight_grad(weight, compute)
+        return dx, dw
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ weight.T (+ bias)``; the CUDA path is the tcgen05 GEMM for forward, dX and dW."""
+    if not _cuda(x):
+        return ref.linear(x, weight, bias)
+    _require_bf16(x, weight)
+    y = _LinearFn.apply(x, weight)
+    return y if bias is None else y + bias
+
+
+# =============================================================================== RMSNorm
+def _rmsnorm_backward(res, weight, rstd, dy, dres, shape):
+    rows, D = res.shape
+    dy2 = dy.reshape(-1, D)
+    dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+    dres2 = None
+    if dres is not None:
+        dres2 = dres.reshape(-1, D)
+        dres2 = dres2 if dres2.is_contiguous() else dres2.contiguous()
+    dx = torch.empty_like(res)
+    parts = _lib.rmsnorm_bwd_parts(rows)
+    partial = torch.empty((parts, D), dtype=torch.float32, device=res.device)
+
+    def compute(out, acc):
+        if out is None:
+            dwf = torch.empty(D, dtype=torch.float32, device=res.device)
+            _lib.call("ksa_rmsnorm_bwd", dy2, res, weight, rstd, dres2, dx, partial, dwf, 0, rows, D)
+            return dwf.to(weight.dtype)
+        _lib.call("ksa_rmsnorm_bwd", dy2, res, weight, rstd, dres2, dx, partial, out, int(acc), rows, D)
+
+    dw = _weight_grad(weight, compute)
+    return dx.view(shape), dw
+
+
+class _AddRmsNormFn(torch.autograd.Function):
+    """(x, delta) -> (x + delta, norm(x + delta))."""
+
+    @staticmethod
+    def forward(ctx, x, delta, weight, eps):
+        D = x.shape[-1]
+        x2 = x.reshape(-1, D)
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        res = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _lib.call("ksa_rmsnorm_fwd", x2, delta.reshape(-1, D), weight, res, y, rstd, rows, D, float(eps))
+        ctx.save_for_backward(res, weight, rstd)
+        ctx.shape = x.shape
+        return res.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dres, dy):
+        res, weight, rstd = ctx.saved_tensors
+        dx, dw = _rmsnorm_backward(res, weight, rstd, dy, dres, ctx.shape)
+        return dx, dx, dw, None
+
+
+class _RmsNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        D = x.shape[-1]
+        x2 = x.reshape(-1, D)
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _lib.call("ksa_rmsnorm_fwd", x2, None, weight, None, y, rstd, rows, D, float(eps))
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, rstd = ctx.saved_tensors
+        dx, dw = _rmsnorm_backward(x2, weight, rstd, dy, None, ctx.shape)
+        return dx, dw, None
+
+
+def add_rms_norm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                 eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``r = x + delta`` (or ``x``) and ``rms_norm(r)``, one pass over the row."""
+    if not _cuda(x):
+        return ref.add_rms_norm(x, delta, weight, eps)
+    _require_bf16(x, delta, weight)
+    x = x if x.is_contiguous() else x.contiguous()
+    if delta is None:
+        return x, _RmsNormFn.apply(x, weight, eps)
+    delta = delta if delta.is_contiguous() else delta.contiguous()
+    return _AddRmsNormFn.apply(x, delta, weight, eps)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    if not _cuda(x):
+        return ref.rms_norm(x, weight, eps)
+    _require_bf16(x, weight)
+    x = x if x.is_contiguous() else x.contiguous()
+    return _RmsNormFn.apply(x, weight, eps)
+
+
+# =============================================================================== QK-norm + RoPE
+class _QkNormRopeFn(torch.autograd.Function):
+    """Input: packed ``qkv`` rows ``[T, (Hq+2Hkv)*D]``; output: rotated ``[T, (Hq+Hkv)*D]`` (q heads | k heads)."""
+
+    @staticmethod
+    def forward(ctx, qkv, q_w, k_w, pos, Hq, Hkv, D, theta, eps, interleaved):
+        T = qkv.shape[0]
+        out = torch.empty((T, (Hq + Hkv) * D), dtype=qkv.dtype, device=qkv.device)
+        rstd = torch.empty((T, Hq + Hkv), dtype=torch.float32, device=qkv.device)
+        _lib.call("ksa_qknorm_rope_fwd", qkv, out, q_w, k_w, pos, rstd, qkv.stride(0), out.stride(0), T, Hq, Hkv, D,
+                  float(theta), float(eps), int(interleaved))
+        ctx.save_for_backward(qkv, q_w, k_w, pos, rstd)
+        ctx.cfg = (Hq, Hkv, D, theta, eps, interleaved)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        qkv, q_w, k_w, pos, rstd = ctx.saved_tensors
+        Hq, Hkv, D, theta, eps, interleaved = ctx.cfg
+        T = qkv.shape[0]
+        d_out = d_out if d_out.is_contiguous() else d_out.contiguous()
+        d_qkv = torch.zeros_like(qkv)  # the v columns get no gradient from this op
+        targets = []
+        for w in (q_w, k_w):
+            if w is None:
+                targets.append(None)
+                continue
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                if not getattr(w, "_grad_written", False):
+                    mg.zero_()
+                    w._grad_written = True
+                targets.append(mg)
+            else:
+                targets.append(torch.zeros(D, dtype=torch.float32, device=qkv.device))
+        _lib.call("ksa_qknorm_rope_bwd", qkv, d_out, d_qkv, q_w, k_w, pos, rstd, targets[0], targets[1],
+                  qkv.stride(0), d_out.stride(0), T, Hq, Hkv, D, float(theta), float(eps), int(interleaved))
+        grads = []
+        for w, t in zip((q_w, k_w), targets):
+            if w is None or getattr(w, "main_grad", None) is not None:
+                grads.append(None)
+            else:
+                grads.append(t.to(w.dtype))
+        return d_qkv, grads[0], grads[1], None, None, None, None, None, None, None
+
+
+def qk_norm_rope_packed(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                        pos: torch.Tensor, Hq: int, Hkv: int, D: int, theta: float, eps: float = 1e-6,
+                        interleaved: bool = False) -> torch.Tensor:
+    """Per-head RMSNorm of q and k followed by RoPE on packed rows.
+
+    ``qkv`` is ``[T, (Hq+2Hkv)*D]`` (q heads | k heads | v heads), ``pos`` ``[T]``.
+    Returns ``[T, (Hq+Hkv)*D]`` (rotated q heads | rotated k heads); v is read from ``qkv``.
+    """
+    if not _cuda(qkv):
+        T = qkv.shape[0]
+        q = qkv[:, :Hq * D].reshape(1, T, Hq, D)
+        k = qkv[:, Hq * D:(Hq + Hkv) * D].reshape(1, T, Hkv, D)
+        q, k = ref.qk_norm_rope(q, k, q_w, k_w, pos, theta, eps, interleaved)
+        return torch.cat([q.reshape(T, Hq * D), k.reshape(T, Hkv * D)], dim=1)
+    _require_bf16(qkv, q_w, k_w)
+    assert qkv.stride(1) == 1
+    return _QkNormRopeFn.apply(qkv, q_w, k_w, pos.to(torch.int32), Hq, Hkv, D, theta, eps, interleaved)
+
+
+# =============================================================================== SwiGLU
+class _SwiGluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        F2 = gu.shape[-1]
+        g2 = gu.reshape(-1, F2)
+        out = torch.empty((g2.shape[0], F2 // 2), dtype=gu.dtype, device=gu.device)
+        _lib.call("ksa_swiglu_fwd", g2, out, g2.shape[0], F2 // 2)
+        ctx.save_for_backward(g2)
+        ctx.shape = gu.shape
+        return out.view(*gu.shape[:-1], F2 // 2)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (g2,) = ctx.saved_tensors
+        d2 = dout.reshape(-1, dout.shape[-1])
+        d2 = d2 if d2.is_contiguous() else d2.contiguous()
+        dgu = torch.empty_like(g2)
+        _lib.call("ksa_swiglu_bwd", g2, d2, dgu, g2.shape[0], g2.shape[1] // 2)
+        return dgu.view(ctx.shape)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` with ``gate_up = [gate | up]`` along the last dimension."""
+    if not _cuda(gate_up):
+        return ref.swiglu(gate_up)
+    _require_bf16(gate_up)
+    gate_up = gate_up if gate_up.is_contiguous() else gate_up.contiguous()
+    return _SwiGluFn.apply(gate_up)
+
+
+# =============================================================================== embedding
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table):
+        flat = ids.reshape(-1).to(torch.int64).contiguous()
+        D = table.shape[1]
+        out = torch.empty((flat.numel(), D), dtype=table.dtype, device=table.device)
+        _lib.call("ksa_embedding_fwd", flat, table, out, flat.numel(), D, table.shape[0])
+        ctx.save_for_backward(flat, table)
+        return out.view(*ids.shape, D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        flat, table = ctx.saved_tensors
+        D = table.shape[1]
+        d2 = dout.reshape(-1, D)
+        d2 = d2 if d2.is_contiguous() else d2.contiguous()
+        mg = getattr(table, "main_grad", None)
+        if mg is not None:
+            if not getattr(table, "_grad_written", False):
+                mg.zero_()
+                table._grad_written = True
+            _lib.call("ksa_embedding_bwd", flat, d2, mg, flat.numel(), D, table.shape[0])
+            return None, None
+        g = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
+        _lib.call("ksa_embedding_bwd", flat, d2, g, flat.numel(), D, table.shape[0])
+        return None, g.to(table.dtype)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    if not _cuda(table):
+        return ref.embedding(ids, table)
+    _require_bf16(table)
+    return _EmbeddingFn.apply(ids, table)
+
+
+# =============================================================================== attention
+def _strides(t: torch.Tensor):
+    """(row stride, batch stride) in elements of a ``[B, T, H, D]`` view with contiguous heads."""
+    B, T, H, D = t.shape
+    assert t.stride(3) == 1 and t.stride(2) == D, "heads must be contiguous blocks of head_dim"
+    return t.stride(1), (t.stride(0) if B > 1 else t.stride(1) * max(T, 1))
+
+
+class _KsaAttentionFn(torch.autograd.Function):
+    """Text + summary queries over text + summary keys (two-stream KSA); also plain causal attention."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, qs, ks, vs, chunk, n_sum, window, tok_window, scale, q_off, k_off, s_off, seq_len):
+        B, Lq, Hq, D = q.shape
+        Lk, Hkv = k.shape[1], k.shape[2]
+        has_sum = qs is not None and qs.shape[1] > 0
+        Ns_k = ks.shape[1] if ks is not None else 0
+        o = torch.empty((B, Lq, Hq, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, Hq, Lq), dtype=torch.float32, device=q.device)
+        qrs, qbs = _strides(q); krs, kbs = _strides(k); vrs, vbs = _strides(v)
+        if Ns_k > 0:
+            ksrs, ksbs = _strides(ks); vsrs, vsbs = _strides(vs)
+        else:
+            ksrs = ksbs = vsrs = vsbs = 0
+        _lib.call("ksa_attn_fwd", q, k, v, ks if Ns_k > 0 else None, vs if Ns_k > 0 else None, o, lse,
+                  B, Hq, Hkv, D, Lq, Lk, Ns_k, qrs, qbs, krs, kbs, vrs, vbs, ksrs, ksbs, vsrs, vsbs,
+                  o.stride(1), o.stride(0), q_off, k_off, s_off, chunk, max(n_sum, 1), window, tok_window, float(scale))
+        os_ = lse_s = None
+        if has_sum:
+            Nq = qs.shape[1]
+            os_ = torch.empty((B, Nq, Hq, D), dtype=q.dtype, device=q.device)
+            lse_s = torch.empty((B, Hq, Nq), dtype=torch.float32, device=q.device)
+            qsrs, qsbs = _strides(qs)
+            chunk0 = q_off // chunk
+            _lib.call("ksa_summary_attn_fwd", qs, k, v, ks, vs, os_, lse_s, B, Hq, Hkv, D, Nq, seq_len,
+                      qsrs, qsbs, krs, kbs, vrs, vbs, ksrs, ksbs, vsrs, vsbs, os_.stride(1), os_.stride(0),
+                      chunk, n_sum, chunk0, k_off, s_off, float(scale))
+        ctx.save_for_backward(q, k, v, qs, ks, vs, o, lse, os_, lse_s)
+        ctx.cfg = (chunk, n_sum, window, tok_window, scale, q_off, k_off, s_off, seq_len)
+        if has_sum:
+            return o, os_
+        return o, None
+
+    @staticmethod
+    def backward(ctx, do, dos):
+        q, k, v, qs, ks, vs, o, lse, os_, lse_s = ctx.saved_tensors
+        chunk, n_sum, window, tok_window, scale, q_off, k_off, s_off, seq_len = ctx.cfg
+        B, Lq, Hq, D = q.shape
+        Lk, Hkv = k.shape[1], k.shape[2]
+        Ns_k = ks.shape[1] if ks is not None else 0
+        do = do if do.is_contiguous() else do.contiguous()
+        dq = torch.empty_like(o)
+        dk = torch.empty((B, Lk, Hkv, D), dtype=q.dtype, device=q.device)
+        dv = torch.empty_like(dk)
+        dks = dvs = None
+        if Ns_k > 0:
+            dks = torch.empty((B, Ns_k, Hkv, D), dtype=q.dtype, device=q.device)
+            dvs = torch.empty_like(dks)
+        delta = torch.empty_like(lse)
+        if Lq == 0:  # summary-only call: the text-query kernels do not run, start the key grads at zero
+            dk.zero_(); dv.zero_()
+            if dks is not None:
+                dks.zero_(); dvs.zero_()
+        qrs, qbs = _strides(q); krs, kbs = _strides(k); vrs, vbs = _strides(v)
+        if Ns_k > 0:
+            ksrs, ksbs = _strides(ks); vsrs, vsbs = _strides(vs)
+            dksrs, dksbs = dks.stride(1), dks.stride(0)
+        else:
+            ksrs = ksbs = vsrs = vsbs = dksrs = dksbs = 0
+        _lib.call("ksa_attn_bwd", q, k, v, ks if Ns_k > 0 else None, vs if Ns_k > 0 else None, o, do, lse, delta,
+                  dq, dk, dv, dks, dvs, B, Hq, Hkv, D, Lq, Lk, Ns_k,
+                  qrs, qbs, krs, kbs, vrs, vbs, ksrs, ksbs, vsrs, vsbs, o.stride(1), o.stride(0),
+                  dq.stride(1), dq.stride(0), dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0),
+                  dksrs, dksbs, dksrs, dksbs, q_off, k_off, s_off, chunk, max(n_sum, 1), window, tok_window,
+                  float(scale))
+        dqs = None
+        if os_ is not None:
+            Nq = qs.shape[1]
+            dos = dos if dos.is_contiguous() else dos.contiguous()
+            dqs = torch.empty_like(os_)
+            qsrs, qsbs = _strides(qs)
+            _lib.call("ksa_summary_attn_bwd", qs, k, v, ks, vs, os_, dos, lse_s, dqs, dk, dv, dks, dvs,
+                      B, Hq, Hkv, D, Nq, seq_len, qsrs, qsbs, krs, kbs, vrs, vbs, ksrs, ksbs, vsrs, vsbs,
+                      os_.stride(1), os_.stride(0), dqs.stride(1), dqs.stride(0), dk.stride(1), dk.stride(0),
+                      dv.stride(1), dv.stride(0), dksrs, dksbs, dksrs, dksbs, chunk, n_sum, q_off // chunk,
+                      k_off, s_off, float(scale))
+        return (dq, dk, dv, dqs, dks, dvs) + (None,) * 9
+
+
+def ksa_attention(q_t, k_t, v_t, q_s, k_s, v_s, chunk: int, n_sum: int, window: int,
+                  scale: Optional[float] = None, skip_old_summary: bool = False,
+                  q_off: int = 0, k_off: int = 0, s_off: int = 0, seq_len: Optional[int] = None):
+    """Two-stream Kwai Summary Attention; returns ``(o_text, o_summary)``.
+
+    ``q_off/k_off/s_off`` give the global index of local row 0 of the text queries, the text keys and
+    the summary keys (context-parallel shards hold a halo of text keys and all older summary keys).
+    ``seq_len`` is the global text length (defaults to ``k_off + Lk``).
+    """
+    D = q_t.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not _cuda(q_t):
+        assert q_off == 0 and k_off == 0 and s_off == 0, "the CPU path takes whole sequences"
+        return ref.ksa_attention(q_t, k_t, v_t, q_s, k_s, v_s, chunk, n_sum, window, scale, skip_old_summary)
+    _require_bf16(q_t, k_t, v_t, q_s, k_s, v_s)
+    seq_len = seq_len if seq_len is not None else k_off + k_t.shape[1]
+    if skip_old_summary:
+        o_t, _ = _KsaAttentionFn.apply(q_t, k_t, v_t, None, None, None, chunk, n_sum, window, 0, scale,
+                                       q_off, k_off, s_off, seq_len)
+        _, o_s = _KsaAttentionFn.apply(q_t[:, :0], k_t, v_t, q_s, k_s, v_s, chunk, n_sum, window, 0, scale,
+                                       q_off, k_off, s_off, seq_len)
+        return o_t, o_s
+    return _KsaAttentionFn.apply(q_t, k_t, v_t, q_s, k_s, v_s, chunk, n_sum, window, 0, scale,
+                                 q_off, k_off, s_off, seq_len)
+
+
+def causal_attention(q, k, v, scale: Optional[float] = None, window: int = -1,
+                     cu_seqlens: Optional[torch.Tensor] = None, q_off: Optional[int] = None):
+    """Causal attention (``window > 0``: keys with ``q - k < window``) on the same tensor-core kernel."""
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not _cuda(q) or cu_seqlens is not None:
+        if _cuda(q):
+            raise NotImplementedError("packed-document masking runs on the CPU path only")
+        return ref.causal_attention(q, k, v, scale, window, cu_seqlens)
+    _require_bf16(q, k, v)
+    q_off = (k.shape[1] - q.shape[1]) if q_off is None else q_off
+    o, _ = _KsaAttentionFn.apply(q, k, v, None, None, None, 128, 1, UNBOUNDED_WINDOW,
+                                 window if window and window > 0 else 0, scale, q_off, 0, 0, k.shape[1])
+    return o
+
+
+# =============================================================================== fused linear + cross entropy
+class _LinearCrossEntropyFn(torch.autograd.Function):
+    """lm_head GEMM + softmax CE, chunked over tokens so that only one chunk of logits exists."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore_index, chunk_tokens):
+        T, D = hidden.shape
+        V = weight.shape[0]
+        dev = hidden.device
+        labels = labels.reshape(-1).to(torch.int64).contiguous()
+        stats = torch.empty(2, dtype=torch.float32, device=dev)
+        _lib.call("ksa_count_valid", labels, T, ignore_index, 1.0, stats)
+        inv_n = stats[1:2]
+        row_loss = torch.empty(T, dtype=torch.float32, device=dev)
+        need_h = ctx.needs_input_grad[0]
+        need_w = ctx.needs_input_grad[1]
+        dh = torch.empty_like(hidden) if need_h else None
+        mg = getattr(weight, "main_grad", None)
+        if need_w:
+            if mg is not None:
+                dw, acc0 = mg, getattr(weight, "_grad_written", False)
+            else:
+                dw, acc0 = torch.empty((V, D), dtype=torch.float32, device=dev), False
+        logits = torch.empty((min(chunk_tokens, T), V), dtype=torch.bfloat16, device=dev)
+        for i, s in enumerate(range(0, T, chunk_tokens)):
+            e = min(T, s + chunk_tokens)
+            lg = logits[: e - s]
+            gemm(hidden[s:e], weight, out=lg)
+            _lib.call("ksa_cross_entropy", lg, labels[s:e], row_loss[s:e], inv_n, e - s, V, lg.stride(0),
+                      ignore_index, int(need_h or need_w))
+            if need_h:
+                gemm(lg, weight, b_mn_major=True, out=dh[s:e])
+            if need_w:
+                gemm(lg, hidden[s:e], a_mn_major=True, b_mn_major=True, out=dw, accumulate=(acc0 or i > 0))
+        if need_w and mg is not None:
+            weight._grad_written = True
+        loss = (row_loss.sum() * inv_n).reshape(())
+        ctx.dh = dh
+        ctx.dw = None if (not need_w or mg is not None) else dw
+        ctx.w_dtype = weight.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        # Gradients were produced for d(loss) = 1 in forward; scale by the incoming gradient.
+        dh = ctx.dh * dloss.to(ctx.dh.dtype) if ctx.dh is not None else None
+        dw = (ctx.dw * dloss).to(ctx.w_dtype) if ctx.dw is not None else None
+        return dh, dw, None, None, None
+
+
+def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                         ignore_index: int = -100, chunk_tokens: int = 2048) -> torch.Tensor:
+    """Mean next-token CE of ``hidden @ weight.T``; logits never exist for more than one token chunk.
+
+    On CUDA the gradients w.r.t. ``hidden`` and ``weight`` are computed during the forward pass (the
+    softmax is turned into the gradient in place), assuming the loss is the root of the backward pass
+    up to a scalar factor; with ``main_grad`` on the weight that factor must be 1.
+    """
+    if not _cuda(hidden):
+        return ref.linear_cross_entropy(hidden, weight, labels, ignore_index)
+    _require_bf16(hidden, weight)
+    h2 = hidden.reshape(-1, hidden.shape[-1])
+    h2 = h2 if h2.is_contiguous() else h2.contiguous()
+    return _LinearCrossEntropyFn.apply(h2, weight, labels, ignore_index, chunk_tokens)
+
+
+# =============================================================================== optimiser
+def adamw_step(master, grad, m, v, out_bf16, hyper, beta1, beta2, eps, weight_decay, clip_value=0.0,
+               sumsq: Optional[torch.Tensor] = None) -> None:
+    """Fused AdamW over a flat fp32 buffer; ``hyper`` = device tensor ``[lr, 1-b1^t, 1-b2^t, grad_scale]``."""
+    if not _cuda(master):
+        lr, bc1, bc2, gs = [float(x) for x in hyper.tolist()]
+        g = grad.float() * gs
+        if sumsq is not None:
+            sumsq += (g * g).sum()
+        if clip_value > 0:
+            g = g.clamp(-clip_value, clip_value)
+        m.mul_(beta1).add_(g, alpha=1 - beta1)
+        v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+        master.mul_(1 - lr * weight_decay)
+        master.addcdiv_(m / bc1, (v / bc2).sqrt_().add_(eps), value=-lr)
+        if out_bf16 is not None:
+            out_bf16.copy_(master)
+        return
+    n = master.numel()
+    _lib.call("ksa_adamw", master, grad, m, v, out_bf16, n, hyper, float(beta1), float(beta2), float(eps),
+              float(weight_decay), float(clip_value), sumsq)
+
+
+__all__ = [
+    "gemm", "linear", "rms_norm", "add_rms_norm", "qk_norm_rope_packed", "swiglu", "embedding",
+    "ksa_attention", "causal_attention", "linear_cross_entropy", "adamw_step", "UNBOUNDED_WINDOW",
+    "SummaryLayout", "get_layout",
+]

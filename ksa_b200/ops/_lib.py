@@ -1,0 +1,125 @@
+"""ctypes binding of the in-tree sm_100a kernel library (``ksa_b200/_lib/libksa_b200.so``).
+
+The library exports plain C entry points that take raw device pointers, sizes,
+strides in elements and a CUDA stream.  ``call(name, *args)`` launches one on
+torch's current stream and raises with the library's own message on error.  On
+a machine with a GPU a missing library is an error, never a silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+from typing import Dict, Optional, Sequence
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libksa_b200.so"
+_lib: Optional[ctypes.CDLL] = None
+
+P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+# name -> argument ctypes (the trailing stream pointer included)
+_SIGNATURES: Dict[str, Sequence] = {
+    "ksa_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, I, P],
+    "ksa_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "ksa_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
+    "ksa_qknorm_rope_fwd": [P, P, P, P, P, P, L, L, I, I, I, I, F, F, I, P],
+    "ksa_qknorm_rope_bwd": [P, P, P, P, P, P, P, P, P, L, L, I, I, I, I, F, F, I, P],
+    "ksa_swiglu_fwd": [P, P, L, I, P],
+    "ksa_swiglu_bwd": [P, P, P, L, I, P],
+    "ksa_embedding_fwd": [P, P, P, L, I, L, P],
+    "ksa_embedding_bwd": [P, P, P, L, I, L, P],
+    "ksa_count_valid": [P, L, I, F, P, P],
+    "ksa_cross_entropy": [P, P, P, P, L, I, L, I, I, P],
+    "ksa_adamw": [P, P, P, P, P, L, P, F, F, F, F, F, P, P],
+    "ksa_cast_f32_bf16": [P, P, L, P],
+    "ksa_attn_fwd": [P] * 7 + [I] * 7 + [L] * 12 + [I] * 7 + [F, P],
+    "ksa_attn_bwd": [P] * 14 + [I] * 7 + [L] * 22 + [I] * 7 + [F, P],
+    "ksa_summary_attn_fwd": [P] * 7 + [I] * 6 + [L] * 12 + [I] * 5 + [F, P],
+    "ksa_summary_attn_bwd": [P] * 13 + [I] * 6 + [L] * 22 + [I] * 5 + [F, P],
+    "ksa_decode_attn": [P] * 7 + [I] * 7 + [L] * 8 + [F, P],
+    "ksa_kv_cache_append": [P] * 6 + [I] * 6 + [L] * 6 + [P],
+    "ksa_peer_reduce_adamw": [P, P, P, P, P, P, I, L, L, P, F, F, F, F, F, F, P, P],
+    "ksa_peer_gather": [P, P, I, I, L, P, I, P],
+    "ksa_signal_set": [P, I, P],
+    "ksa_signal_wait": [P, I, I, P],
+}
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise RuntimeError(
+            f"{_LIB_PATH} is missing: build it with `python -m ksa_b200.csrc.build` (needs nvcc); "
+            "CUDA tensors cannot be processed without the sm_100a kernel library")
+    lib = ctypes.CDLL(str(_LIB_PATH), mode=ctypes.RTLD_LOCAL)
+    lib.ksa_last_error.restype = ctypes.c_char_p
+    lib.ksa_read_status.argtypes = [I]
+    lib.ksa_read_status.restype = I
+    lib.ksa_rmsnorm_bwd_parts.argtypes = [I]
+    lib.ksa_rmsnorm_bwd_parts.restype = I
+    for name, sig in _SIGNATURES.items():
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.argtypes = list(sig)
+            fn.restype = I
+    _lib = lib
+    return lib
+
+
+_STATUS_TEXT = {
+    1: "a consumer timed out waiting for a TMA-filled stage",
+    2: "the TMA producer timed out waiting for a free stage",
+    3: "an epilogue/softmax warp timed out waiting for an MMA commit",
+    4: "the MMA issuer timed out waiting for the epilogue to drain TMEM",
+    5: "timed out waiting for a flag written by another CTA or GPU",
+    6: "the MMA issuer timed out waiting for the softmax warps",
+    7: "a kernel rejected its arguments",
+}
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, torch.Tensor):
+        return x.data_ptr()
+    return x
+
+
+def call(name: str, *args) -> None:
+    """Launch entry point ``name`` on the current CUDA stream (appended as the last argument)."""
+    lib = load()
+    fn = getattr(lib, name)
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = fn(*[_ptr(a) for a in args], stream)
+    if rc != 0:
+        raise RuntimeError(f"{name} failed ({rc}): {lib.ksa_last_error().decode()}")
+
+
+def call_on(name: str, stream: int, *args) -> None:
+    lib = load()
+    rc = getattr(lib, name)(*[_ptr(a) for a in args], stream)
+    if rc != 0:
+        raise RuntimeError(f"{name} failed ({rc}): {lib.ksa_last_error().decode()}")
+
+
+def check_status(clear: bool = True) -> None:
+    """Synchronise and raise if any kernel's bounded wait gave up since the last check."""
+    st = load().ksa_read_status(1 if clear else 0)
+    if st != 0:
+        raise RuntimeError(f"kernel status {st}: {_STATUS_TEXT.get(st, 'unknown')}")
+
+
+def rmsnorm_bwd_parts(rows: int) -> int:
+    return load().ksa_rmsnorm_bwd_parts(rows)

@@ -1,0 +1,241 @@
+"""Numerics of every sm_100a kernel against the plain PyTorch fp32 formulas (needs a B200)."""
+import math
+
+import pytest
+import torch
+
+from ksa_b200 import ops
+from ksa_b200.ops import _lib, reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(torch.bfloat16)
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+
+
+def check(a, b, tol, what=""):
+    _lib.check_status()
+    assert torch.isfinite(a.float()).all(), f"{what}: non-finite values"
+    e = rel_err(a, b)
+    assert e < tol, f"{what}: relative error {e:.3e} >= {tol}"
+
+
+# ------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 256), (384, 1024, 192), (1000, 264, 72),
+                                   (2048, 4096, 2048), (130, 136, 520)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    if a_mn and M % 8:
+        pytest.skip("an MN-major operand needs its contiguous extent to be a multiple of 8")
+    A = bf(M, K)
+    B = bf(N, K)
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    c = ops.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn)
+    check(c, A.float() @ B.float().t(), 1e-2, f"gemm {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}")
+
+
+def test_gemm_fp32_accumulate_and_strided_views():
+    M, N, K = 512, 768, 320
+    packed = bf(M, 2 * K)
+    A = packed[:, K:]                       # row stride 2K
+    B = bf(N, K)
+    out = torch.randn(M, N, device=DEV)
+    expect = out + 0.5 * (A.float() @ B.float().t())
+    ops.gemm(A, B, out=out, accumulate=True, alpha=0.5)
+    check(out, expect, 5e-3, "gemm fp32 accumulate")
+
+
+def test_linear_autograd():
+    x = bf(3, 200, 256).requires_grad_()
+    w = bf(384, 256, scale=0.05).requires_grad_()
+    y = ops.linear(x, w)
+    g = bf(3, 200, 384)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = ref.linear(xr, wr)
+    yr.backward(g.float())
+    check(y, yr, 1e-2, "linear fwd")
+    check(x.grad, xr.grad, 1e-2, "linear dx")
+    check(w.grad, wr.grad, 1e-2, "linear dw")
+
+
+def test_linear_main_grad_accumulates_in_fp32():
+    x = bf(256, 128)
+    w = bf(256, 128, scale=0.05).requires_grad_()
+    w.main_grad = torch.zeros(256, 128, device=DEV)
+    g = bf(256, 256)
+    for _ in range(2):
+        ops.linear(x, w).backward(g)
+    assert w.grad is None
+    check(w.main_grad, 2 * (g.float().t() @ x.float()), 1e-2, "main_grad accumulation")
+
+
+# ------------------------------------------------------------------ norms / rope / mlp
+@pytest.mark.parametrize("rows,D", [(7, 256), (300, 2048), (1500, 2560)])
+def test_add_rms_norm(rows, D):
+    x, d = bf(rows, D), bf(rows, D)
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16)
+    xs = [t.clone().requires_grad_() for t in (x, d, w)]
+    res, y = ops.add_rms_norm(*xs, 1e-6)
+    gr, gy = bf(rows, D), bf(rows, D)
+    torch.autograd.backward([res, y], [gr, gy])
+    fs = [t.detach().float().requires_grad_() for t in (x, d, w)]
+    r_ref = fs[0] + fs[1]
+    y_ref = ref.rms_norm(r_ref, fs[2])
+    ((r_ref * gr.float()).sum() + (y_ref * gy.float()).sum()).backward()
+    check(res, r_ref, 5e-3, "residual")
+    check(y, y_ref, 1e-2, "rmsnorm y")
+    check(xs[0].grad, fs[0].grad, 1.5e-2, "rmsnorm dx")
+    check(xs[2].grad, fs[2].grad, 2e-2, "rmsnorm dw")
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 16, 8), (64, 4, 2)])
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_qk_norm_rope(D, Hq, Hkv, interleaved):
+    T = 333
+    qkv = bf(T, (Hq + 2 * Hkv) * D).requires_grad_()
+    qw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+    kw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+    pos = torch.randint(0, 100000, (T,), device=DEV)
+    out = ops.qk_norm_rope_packed(qkv, qw, kw, pos, Hq, Hkv, D, 1e6, 1e-6, interleaved)
+    g = bf(T, (Hq + Hkv) * D)
+    out.backward(g)
+    f = [t.detach().float().requires_grad_() for t in (qkv, qw, kw)]
+    q = f[0][:, :Hq * D].reshape(1, T, Hq, D)
+    k = f[0][:, Hq * D:(Hq + Hkv) * D].reshape(1, T, Hkv, D)
+    qr, kr = ref.qk_norm_rope(q, k, f[1], f[2], pos, 1e6, 1e-6, interleaved)
+    o_ref = torch.cat([qr.reshape(T, -1), kr.reshape(T, -1)], 1)
+    o_ref.backward(g.float())
+    check(out, o_ref, 1e-2, "qknorm_rope fwd")
+    check(qkv.grad[:, :(Hq + Hkv) * D], f[0].grad[:, :(Hq + Hkv) * D], 2e-2, "qknorm_rope dqkv")
+    assert qkv.grad[:, (Hq + Hkv) * D:].abs().max() == 0
+    check(qw.grad, f[1].grad, 3e-2, "q_norm dw")
+    check(kw.grad, f[2].grad, 3e-2, "k_norm dw")
+
+
+def test_swiglu():
+    gu = bf(257, 2 * 768).requires_grad_()
+    y = ops.swiglu(gu)
+    g = bf(257, 768)
+    y.backward(g)
+    f = gu.detach().float().requires_grad_()
+    yr = ref.swiglu(f)
+    yr.backward(g.float())
+    check(y, yr, 1e-2, "swiglu fwd")
+    check(gu.grad, f.grad, 1.5e-2, "swiglu bwd")
+
+
+def test_embedding():
+    table = bf(1000, 256).requires_grad_()
+    ids = torch.randint(0, 1000, (4, 77), device=DEV)
+    y = ops.embedding(ids, table)
+    g = bf(4, 77, 256)
+    y.backward(g)
+    f = table.detach().float().requires_grad_()
+    yr = ref.embedding(ids, f)
+    yr.backward(g.float())
+    assert torch.equal(y.float(), yr)
+    check(table.grad, f.grad, 1e-2, "embedding bwd")
+
+
+@pytest.mark.parametrize("T,V,chunk", [(300, 4096, 128), (64, 151936, 64)])
+def test_linear_cross_entropy(T, V, chunk):
+    D = 256
+    h = bf(T, D).requires_grad_()
+    w = bf(V, D, scale=0.05).requires_grad_()
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[::7] = -100
+    loss = ops.linear_cross_entropy(h, w, labels, chunk_tokens=chunk)
+    loss.backward()
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr = ref.linear_cross_entropy(hf, wf, labels)
+    lr.backward()
+    _lib.check_status()
+    assert abs(loss.item() - lr.item()) < 2e-2 * abs(lr.item()), (loss.item(), lr.item())
+    check(h.grad, hf.grad, 3e-2, "linear_ce dh")
+    check(w.grad, wf.grad, 3e-2, "linear_ce dw")
+
+
+def test_adamw():
+    n = 4096 * 3
+    master = torch.randn(n, device=DEV)
+    grad = torch.randn(n, device=DEV)
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    out = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    sumsq = torch.zeros(1, device=DEV)
+    mr, gr_, m_r, v_r = master.clone().cpu(), grad.clone().cpu(), m.clone().cpu(), v.clone().cpu()
+    for step in (1, 2, 3):
+        hyper = torch.tensor([1e-3, 1 - 0.9 ** step, 1 - 0.95 ** step, 0.5], device=DEV)
+        sumsq.zero_()
+        ops.adamw_step(master, grad, m, v, out, hyper, 0.9, 0.95, 1e-8, 0.1, clip_value=1.0, sumsq=sumsq)
+        sq = ref.adamw_step_(mr, gr_, m_r, v_r, 1e-3, 0.9, 0.95, 1e-8, 0.1, step, grad_scale=0.5, clip_value=1.0)
+        assert abs(sumsq.item() - sq.item()) < 1e-3 * sq.item()
+    check(master, mr.to(DEV), 1e-5, "adamw master")
+    check(out, mr.to(DEV), 5e-3, "adamw bf16 copy")
+
+
+# ------------------------------------------------------------------ attention
+def _attn_inputs(B, L, Hq, Hkv, D, C, S):
+    Ns = ((L + C - 1) // C) * S
+    mk = lambda T, H: bf(B, T, H, D)
+    return [mk(L, Hq), mk(L, Hkv), mk(L, Hkv), mk(Ns, Hq), mk(Ns, Hkv), mk(Ns, Hkv)]
+
+
+@pytest.mark.parametrize("B,L,Hq,Hkv,D,C,S,W", [
+    (1, 1024, 4, 2, 128, 128, 1, 2),
+    (2, 2048, 4, 2, 64, 64, 1, 4),
+    (1, 1536, 2, 2, 128, 128, 2, 1),      # Hq/Hkv odd -> single slot
+    (1, 1280, 8, 2, 128, 8, 1, 16),       # chunk smaller than the tile
+    (1, 1000, 4, 2, 128, 128, 1, 3),      # ragged last tile / chunk
+])
+def test_ksa_attention_fwd_bwd(B, L, Hq, Hkv, D, C, S, W):
+    t = _attn_inputs(B, L, Hq, Hkv, D, C, S)
+    xs = [x.clone().requires_grad_() for x in t]
+    o_t, o_s = ops.ksa_attention(*xs, C, S, W)
+    g_t, g_s = bf(*o_t.shape), bf(*o_s.shape)
+    torch.autograd.backward([o_t, o_s], [g_t, g_s])
+    fs = [x.detach().float().requires_grad_() for x in t]
+    r_t, r_s = ref.ksa_attention(*fs, C, S, W)
+    torch.autograd.backward([r_t, r_s], [g_t.float(), g_s.float()])
+    check(o_t, r_t, 1.5e-2, "ksa o_text")
+    check(o_s, r_s, 1.5e-2, "ksa o_summary")
+    names = ["dq_t", "dk_t", "dv_t", "dq_s", "dk_s", "dv_s"]
+    for n, a, b_ in zip(names, xs, fs):
+        check(a.grad, b_.grad, 3e-2, f"ksa {n}")
+
+
+@pytest.mark.parametrize("L,window", [(1024, -1), (1500, -1), (2048, 300)])
+def test_causal_attention_fwd_bwd(L, window):
+    B, Hq, Hkv, D = 2, 4, 2, 128
+    q, k, v = bf(B, L, Hq, D), bf(B, L, Hkv, D), bf(B, L, Hkv, D)
+    xs = [x.clone().requires_grad_() for x in (q, k, v)]
+    o = ops.causal_attention(*xs, window=window)
+    g = bf(*o.shape)
+    o.backward(g)
+    fs = [x.detach().float().requires_grad_() for x in (q, k, v)]
+    r = ref.causal_attention(*fs, window=window)
+    r.backward(g.float())
+    check(o, r, 1.5e-2, "causal o")
+    for n, a, b_ in zip(["dq", "dk", "dv"], xs, fs):
+        check(a.grad, b_.grad, 3e-2, f"causal {n}")
+
+
+def test_attention_reads_packed_qkv_views():
+    """q/k/v as strided views of one packed projection output (what the model passes)."""
+    B, L, Hq, Hkv, D = 1, 512, 4, 2, 128
+    packed = bf(B * L, (Hq + 2 * Hkv) * D)
+    q = packed[:, :Hq * D].view(B, L, Hq, D)
+    k = packed[:, Hq * D:(Hq + Hkv) * D].view(B, L, Hkv, D)
+    v = packed[:, (Hq + Hkv) * D:].view(B, L, Hkv, D)
+    o = ops.causal_attention(q, k, v)
+    r = ref.causal_attention(q.float(), k.float(), v.float())
+    check(o, r, 1.5e-2, "packed views")
