@@ -484,6 +484,7 @@ KSA_API int ksa_attn_bwd(const void* q, const void* k, const void* v, const void
                          long long dv_rs, long long dv_bs, long long dks_rs, long long dks_bs, long long dvs_rs,
                          long long dvs_bs, int q_off, int k_off, int s_off, int chunk, int n_sum, int window,
                          int tok_window, float scale, void* stream) {
+  KSA_ENTER(q);
   using namespace ksa;
   KSA_REQUIRE(HD == 128 || HD == 64, "attn_bwd: head_dim %d unsupported (64 or 128)", HD);
   KSA_REQUIRE(Hq % Hkv == 0, "attn_bwd: Hq %% Hkv != 0");

@@ -328,6 +328,7 @@ KSA_API int ksa_attn_fwd(const void* q, const void* k, const void* v, const void
                          long long ks_rs, long long ks_bs, long long vs_rs, long long vs_bs, long long o_rs,
                          long long o_bs, int q_off, int k_off, int s_off, int chunk, int n_sum, int window,
                          int tok_window, float scale, void* stream) {
+  KSA_ENTER(q);
   using namespace ksa;
   KSA_REQUIRE(HD == 128 || HD == 64, "attn_fwd: head_dim %d unsupported (64 or 128)", HD);
   KSA_REQUIRE(Hq % Hkv == 0, "attn_fwd: Hq %% Hkv != 0");

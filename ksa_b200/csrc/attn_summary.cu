@@ -203,6 +203,7 @@ KSA_API int ksa_summary_attn_fwd(const void* qs, const void* k, const void* v, c
                                  long long ks_rs, long long ks_bs, long long vs_rs, long long vs_bs, long long os_rs,
                                  long long os_bs, int chunk, int n_sum, int chunk0, int k_off, int s_off, float scale,
                                  void* stream) {
+  KSA_ENTER(qs);
   KSA_REQUIRE(HD % 8 == 0 && Hq % Hkv == 0 && n_sum > 0 && Nq % n_sum == 0, "summary_attn_fwd: bad shape");
   if (B == 0 || Nq == 0) return 0;
   SumAttnArgs a{};
@@ -229,6 +230,7 @@ KSA_API int ksa_summary_attn_bwd(const void* qs, const void* k, const void* v, c
                                  long long dv_rs, long long dv_bs, long long dks_rs, long long dks_bs, long long dvs_rs,
                                  long long dvs_bs, int chunk, int n_sum, int chunk0, int k_off, int s_off, float scale,
                                  void* stream) {
+  KSA_ENTER(qs);
   KSA_REQUIRE(HD % 8 == 0 && Hq % Hkv == 0 && n_sum > 0 && Nq % n_sum == 0, "summary_attn_bwd: bad shape");
   if (B == 0 || Nq == 0) return 0;
   SumAttnArgs a{};

@@ -58,10 +58,11 @@ constexpr int kNormMaxVec = 4;  // D up to 8192
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, const bf16* __restrict__ w,
                    bf16* __restrict__ res_out, bf16* __restrict__ y, float* __restrict__ rstd_out, int rows, int D,
-                   float eps) {
+                   float eps, int delta_rows) {
   __shared__ float red[32];
   const int row = blockIdx.x;
   if (row >= rows) return;
+  const bool has_delta = delta != nullptr && row < delta_rows;
   const long long base = (long long)row * D;
   float v[kNormMaxVec][8];
   float ss = 0.f;
@@ -70,7 +71,7 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, c
     const int c = (i * kNormThreads + threadIdx.x) * 8;
     if (c < D) {
       load8(x + base + c, v[i]);
-      if (delta) {
+      if (has_delta) {
         float d[8];
         load8(delta + base + c, d);
 #pragma unroll
@@ -78,8 +79,8 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, c
         // round the residual stream to bf16 first so that norm and stream agree
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16(v[i][j]));
-        if (res_out) store8(res_out + base + c, v[i]);
       }
+      if (res_out) store8(res_out + base + c, v[i]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
     }
@@ -189,6 +190,7 @@ struct QkRopeArgs {
   int rows, Hq, Hkv, D;
   float log2_theta, eps;
   int interleaved;       // 1: adjacent-pair (Llama) rotary, 0: half-split (HF)
+  int copy_v;            // 1: also copy the v heads (input column block 3) to the output
 };
 
 template <int D>
@@ -197,10 +199,17 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(QkRopeArgs a) {
   const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int H = a.Hq + a.Hkv;
-  if (warp_global >= a.rows * H) return;
-  const int row = warp_global / H, head = warp_global % H;
+  const int Hall = H + (a.copy_v ? a.Hkv : 0);
+  if (warp_global >= a.rows * Hall) return;
+  const int row = warp_global / Hall, head = warp_global % Hall;
   const bf16* src = a.qkv + (long long)row * a.in_stride + (long long)head * D;
   bf16* dst = a.out + (long long)row * a.out_stride + (long long)head * D;
+  if (head >= H) {  // v head: plain copy
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p)
+      reinterpret_cast<uint32_t*>(dst)[lane * PAIRS + p] = reinterpret_cast<const uint32_t*>(src)[lane * PAIRS + p];
+    return;
+  }
   const bf16* w = head < a.Hq ? a.q_w : a.k_w;
   float x1[PAIRS], x2[PAIRS];
   int i1[PAIRS], i2[PAIRS];
@@ -255,12 +264,19 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(QkRopeBwdArgs b) {
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const int H = a.Hq + a.Hkv;
-  const int total = a.rows * H;
+  const int Hall = H + (a.copy_v ? a.Hkv : 0);
+  const int total = a.rows * Hall;
   for (int wg = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); wg < total; wg += gridDim.x * (blockDim.x >> 5)) {
-    const int row = wg / H, head = wg % H;
+    const int row = wg / Hall, head = wg % Hall;
     const bf16* src = a.qkv + (long long)row * a.in_stride + (long long)head * D;
     const bf16* g = b.d_out + (long long)row * a.out_stride + (long long)head * D;
     bf16* dst = b.d_qkv + (long long)row * a.in_stride + (long long)head * D;
+    if (head >= H) {  // v head: the gradient passes through
+#pragma unroll
+      for (int p = 0; p < PAIRS; ++p)
+        reinterpret_cast<uint32_t*>(dst)[lane * PAIRS + p] = reinterpret_cast<const uint32_t*>(g)[lane * PAIRS + p];
+      continue;
+    }
     const bf16* w = head < a.Hq ? a.q_w : a.k_w;
     const float rstd = a.rstd[(long long)row * H + head];
     const float pos = (float)a.pos[row];
@@ -507,13 +523,15 @@ __global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float* __restr
 using namespace ksa;
 #define ST(s) reinterpret_cast<cudaStream_t>(s)
 
+// delta (optional) covers the first delta_rows rows only; res_out (optional) receives x (+ delta) for every row.
 KSA_API int ksa_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* res_out, void* y, void* rstd,
-                            int rows, int D, float eps, void* stream) {
+                            int rows, int D, float eps, int delta_rows, void* stream) {
+  KSA_ENTER(x);
   KSA_REQUIRE(D % 8 == 0 && D <= kNormThreads * 8 * kNormMaxVec, "rmsnorm: D=%d must be a multiple of 8 and <= %d", D,
               kNormThreads * 8 * kNormMaxVec);
   if (rows == 0) return 0;
   rmsnorm_fwd_kernel<<<rows, kNormThreads, 0, ST(stream)>>>((const bf16*)x, (const bf16*)delta, (const bf16*)w,
-                                                            (bf16*)res_out, (bf16*)y, (float*)rstd, rows, D, eps);
+                                                            (bf16*)res_out, (bf16*)y, (float*)rstd, rows, D, eps, delta_rows);
   KSA_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -523,6 +541,7 @@ KSA_API int ksa_rmsnorm_bwd_parts(int rows) { return rows < 592 ? (rows > 0 ? ro
 
 KSA_API int ksa_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rstd, const void* dres, void* dx,
                             void* dw_partial, void* dw, int accumulate_dw, int rows, int D, void* stream) {
+  KSA_ENTER(dy);
   KSA_REQUIRE(D % 8 == 0 && D <= kNormThreads * 8 * kNormMaxVec, "rmsnorm: D=%d unsupported", D);
   if (rows == 0) return 0;
   const int parts = ksa_rmsnorm_bwd_parts(rows);
@@ -540,12 +559,13 @@ KSA_API int ksa_rmsnorm_bwd(const void* dy, const void* x, const void* w, const 
 
 KSA_API int ksa_qknorm_rope_fwd(const void* qkv, void* out, const void* q_w, const void* k_w, const void* pos,
                                 void* rstd, long long in_stride, long long out_stride, int rows, int Hq, int Hkv, int D,
-                                float theta, float eps, int interleaved, void* stream) {
+                                float theta, float eps, int interleaved, int copy_v, void* stream) {
+  KSA_ENTER(qkv);
   KSA_REQUIRE(D == 128 || D == 64, "qknorm_rope: head_dim %d unsupported (64 or 128)", D);
   if (rows == 0) return 0;
   QkRopeArgs a{(const bf16*)qkv, (bf16*)out, (const bf16*)q_w, (const bf16*)k_w, (const int*)pos, (float*)rstd,
-               in_stride, out_stride, rows, Hq, Hkv, D, log2f(theta), eps, interleaved};
-  const long long warps = (long long)rows * (Hq + Hkv);
+               in_stride, out_stride, rows, Hq, Hkv, D, log2f(theta), eps, interleaved, copy_v};
+  const long long warps = (long long)rows * (Hq + Hkv + (copy_v ? Hkv : 0));
   const int blocks = (int)((warps + 7) / 8);
   if (D == 128) qknorm_rope_fwd_kernel<128><<<blocks, 256, 0, ST(stream)>>>(a);
   else qknorm_rope_fwd_kernel<64><<<blocks, 256, 0, ST(stream)>>>(a);
@@ -556,13 +576,14 @@ KSA_API int ksa_qknorm_rope_fwd(const void* qkv, void* out, const void* q_w, con
 KSA_API int ksa_qknorm_rope_bwd(const void* qkv, const void* d_out, void* d_qkv, const void* q_w, const void* k_w,
                                 const void* pos, const void* rstd, void* dq_w, void* dk_w, long long in_stride,
                                 long long out_stride, int rows, int Hq, int Hkv, int D, float theta, float eps,
-                                int interleaved, void* stream) {
+                                int interleaved, int copy_v, void* stream) {
+  KSA_ENTER(qkv);
   KSA_REQUIRE(D == 128 || D == 64, "qknorm_rope: head_dim %d unsupported (64 or 128)", D);
   if (rows == 0) return 0;
   QkRopeBwdArgs b{{(const bf16*)qkv, nullptr, (const bf16*)q_w, (const bf16*)k_w, (const int*)pos, (float*)rstd,
-                   in_stride, out_stride, rows, Hq, Hkv, D, log2f(theta), eps, interleaved},
+                   in_stride, out_stride, rows, Hq, Hkv, D, log2f(theta), eps, interleaved, copy_v},
                   (const bf16*)d_out, (bf16*)d_qkv, (float*)dq_w, (float*)dk_w};
-  const long long warps = (long long)rows * (Hq + Hkv);
+  const long long warps = (long long)rows * (Hq + Hkv + (copy_v ? Hkv : 0));
   long long blocks = (warps + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (D == 128) qknorm_rope_bwd_kernel<128><<<(int)blocks, 256, 0, ST(stream)>>>(b);
@@ -572,6 +593,7 @@ KSA_API int ksa_qknorm_rope_bwd(const void* qkv, const void* d_out, void* d_qkv,
 }
 
 KSA_API int ksa_swiglu_fwd(const void* gu, void* out, long long rows, int F, void* stream) {
+  KSA_ENTER(gu);
   KSA_REQUIRE(F % 8 == 0, "swiglu: F=%d must be a multiple of 8", F);
   const long long n = rows * (F / 8);
   if (n == 0) return 0;
@@ -580,6 +602,7 @@ KSA_API int ksa_swiglu_fwd(const void* gu, void* out, long long rows, int F, voi
   return 0;
 }
 KSA_API int ksa_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long rows, int F, void* stream) {
+  KSA_ENTER(gu);
   KSA_REQUIRE(F % 8 == 0, "swiglu: F=%d must be a multiple of 8", F);
   const long long n = rows * (F / 8);
   if (n == 0) return 0;
@@ -591,6 +614,7 @@ KSA_API int ksa_swiglu_bwd(const void* gu, const void* dout, void* dgu, long lon
 
 KSA_API int ksa_embedding_fwd(const void* ids, const void* table, void* out, long long rows, int D, long long vocab,
                               void* stream) {
+  KSA_ENTER(ids);
   KSA_REQUIRE(D % 8 == 0, "embedding: D=%d must be a multiple of 8", D);
   const long long n = rows * (D / 8);
   if (n == 0) return 0;
@@ -601,6 +625,7 @@ KSA_API int ksa_embedding_fwd(const void* ids, const void* table, void* out, lon
 }
 KSA_API int ksa_embedding_bwd(const void* ids, const void* dout, void* dtable_f32, long long rows, int D,
                               long long vocab, void* stream) {
+  KSA_ENTER(ids);
   KSA_REQUIRE(D % 8 == 0, "embedding: D=%d must be a multiple of 8", D);
   const long long n = rows * (D / 8);
   if (n == 0) return 0;
@@ -612,6 +637,7 @@ KSA_API int ksa_embedding_bwd(const void* ids, const void* dout, void* dtable_f3
 
 KSA_API int ksa_count_valid(const void* labels, long long n, int ignore_index, float extra_scale, void* out2,
                             void* stream) {
+  KSA_ENTER(labels);
   count_valid_kernel<<<1, 1024, 0, ST(stream)>>>((const long long*)labels, n, ignore_index, extra_scale, (float*)out2);
   KSA_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -619,6 +645,7 @@ KSA_API int ksa_count_valid(const void* labels, long long n, int ignore_index, f
 
 KSA_API int ksa_cross_entropy(void* logits, const void* labels, void* row_loss, const void* grad_scale, long long rows,
                               int V, long long ld, int ignore_index, int write_grad, void* stream) {
+  KSA_ENTER(logits);
   KSA_REQUIRE(V % 8 == 0 && ld % 8 == 0, "cross_entropy: V=%d and ld=%lld must be multiples of 8", V, ld);
   if (rows == 0) return 0;
   cross_entropy_kernel<<<(unsigned)rows, kCeThreads, 0, ST(stream)>>>((bf16*)logits, (const long long*)labels,
@@ -631,6 +658,7 @@ KSA_API int ksa_cross_entropy(void* logits, const void* labels, void* row_loss, 
 KSA_API int ksa_adamw(void* master, const void* grad, void* m, void* v, void* out_bf16, long long n, const void* hyper,
                       float beta1, float beta2, float eps, float weight_decay, float clip_value, void* sumsq,
                       void* stream) {
+  KSA_ENTER(master);
   KSA_REQUIRE(n % 4 == 0, "adamw: n=%lld must be a multiple of 4 (pad the flat buffer)", n);
   if (n == 0) return 0;
   long long blocks = (n / 4 + 255) / 256;
@@ -643,6 +671,7 @@ KSA_API int ksa_adamw(void* master, const void* grad, void* m, void* v, void* ou
 }
 
 KSA_API int ksa_cast_f32_bf16(const void* src, void* dst, long long n, void* stream) {
+  KSA_ENTER(src);
   KSA_REQUIRE(n % 4 == 0, "cast: n=%lld must be a multiple of 4", n);
   if (n == 0) return 0;
   long long blocks = (n / 4 + 255) / 256;

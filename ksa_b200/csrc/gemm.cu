@@ -291,6 +291,7 @@ static int launch_gemm(const void* a, const void* b, const GemmEpilogue& ep, int
 KSA_API int ksa_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
                           long long ldc, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, float alpha,
                           int sm_limit, void* stream) {
+  KSA_ENTER(a);
   using namespace ksa;
   KSA_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %d x %d x %d", M, N, K);
   KSA_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "gemm: lda/ldb must be multiples of 8 elements (got %lld, %lld)", lda, ldb);

@@ -71,6 +71,26 @@ int make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, cons
   return kErrNone;
 }
 
+int ensure_device(const void* device_ptr) {
+  static thread_local int bound_device = -1;
+  if (bound_device >= 0 || device_ptr == nullptr) return kErrNone;
+  cudaPointerAttributes attr;
+  cudaError_t e = cudaPointerGetAttributes(&attr, device_ptr);
+  if (e != cudaSuccess || (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)) {
+    cudaGetLastError();
+    set_last_error("pointer %p is not device memory (%s)", device_ptr, e == cudaSuccess ? "host pointer" : cudaGetErrorString(e));
+    return kErrArgument;
+  }
+  e = cudaSetDevice(attr.device);
+  if (e != cudaSuccess) {
+    set_last_error("cudaSetDevice(%d) failed: %s", attr.device, cudaGetErrorString(e));
+    return kErrCuda;
+  }
+  cudaFree(0);  // force the primary context to be current on this thread
+  bound_device = attr.device;
+  return kErrNone;
+}
+
 static int* g_status[64] = {nullptr};
 static std::mutex g_status_mu;
 

@@ -35,6 +35,17 @@ int make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, cons
 // Device status word for the current device (allocated once per device on first use).
 int* status_word();
 
+// Make the device that owns `device_ptr` current on the calling thread.  Callers may arrive on threads that have
+// never touched CUDA through this library's runtime (autograd worker threads): without this, descriptor encoding
+// fails for lack of a context and launches would go to device 0.  Cached per thread; returns 0 on success.
+int ensure_device(const void* device_ptr);
+
+#define KSA_ENTER(ptr)                                   \
+  do {                                                   \
+    int _rc = ksa::ensure_device(ptr);                   \
+    if (_rc) return _rc;                                 \
+  } while (0)
+
 #define KSA_CHECK_CUDA(expr)                                                              \
   do {                                                                                    \
     cudaError_t _e = (expr);                                                              \

@@ -117,6 +117,57 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return y if bias is None else y + bias
 
 
+class _DualLinearFn(torch.autograd.Function):
+    """Rows ``[:n_a]`` use ``w_a``, rows ``[n_a:]`` use ``w_b``; one output buffer, two GEMM launches."""
+
+    @staticmethod
+    def forward(ctx, x, w_a, w_b, n_a):
+        R = x.shape[0]
+        y = torch.empty((R, w_a.shape[0]), dtype=x.dtype, device=x.device)
+        if n_a > 0:
+            gemm(x[:n_a], w_a, out=y[:n_a])
+        if R > n_a:
+            gemm(x[n_a:], w_b, out=y[n_a:])
+        ctx.save_for_backward(x, w_a, w_b)
+        ctx.n_a = n_a
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w_a, w_b = ctx.saved_tensors
+        n_a, R = ctx.n_a, x.shape[0]
+        dy = dy if dy.is_contiguous() else dy.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            if n_a > 0:
+                gemm(dy[:n_a], w_a, b_mn_major=True, out=dx[:n_a])
+            if R > n_a:
+                gemm(dy[n_a:], w_b, b_mn_major=True, out=dx[n_a:])
+        grads = []
+        for need, w, lo, hi in ((ctx.needs_input_grad[1], w_a, 0, n_a), (ctx.needs_input_grad[2], w_b, n_a, R)):
+            if not need or hi <= lo:
+                grads.append(None)
+                continue
+            dys, xs = dy[lo:hi], x[lo:hi]
+
+            def compute(out, acc, dys=dys, xs=xs):
+                if out is None:
+                    return gemm(dys, xs, a_mn_major=True, b_mn_major=True)
+                gemm(dys, xs, a_mn_major=True, b_mn_major=True, out=out, accumulate=acc)
+            grads.append(_weight_grad(w, compute))
+        return dx, grads[0], grads[1], None
+
+
+def dual_linear(x: torch.Tensor, w_a: torch.Tensor, w_b: torch.Tensor, n_a: int) -> torch.Tensor:
+    """``cat(x[:n_a] @ w_a.T, x[n_a:] @ w_b.T)`` without the concatenation (text rows | summary rows)."""
+    if not _cuda(x):
+        return torch.cat([ref.linear(x[:n_a], w_a), ref.linear(x[n_a:], w_b)], dim=0)
+    _require_bf16(x, w_a, w_b)
+    x = x if x.is_contiguous() else x.contiguous()
+    return _DualLinearFn.apply(x, w_a, w_b, n_a)
+
+
 # =============================================================================== RMSNorm
 def _rmsnorm_backward(res, weight, rstd, dy, dres, shape):
     rows, D = res.shape
@@ -152,16 +203,24 @@ class _AddRmsNormFn(torch.autograd.Function):
         y = torch.empty_like(x2)
         res = torch.empty_like(x2)
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
-        _lib.call("ksa_rmsnorm_fwd", x2, delta.reshape(-1, D), weight, res, y, rstd, rows, D, float(eps))
+        d2 = delta.reshape(-1, D)
+        _lib.call("ksa_rmsnorm_fwd", x2, d2, weight, res, y, rstd, rows, D, float(eps), d2.shape[0])
         ctx.save_for_backward(res, weight, rstd)
         ctx.shape = x.shape
+        ctx.delta_shape = delta.shape
         return res.view(x.shape), y.view(x.shape)
 
     @staticmethod
     def backward(ctx, dres, dy):
         res, weight, rstd = ctx.saved_tensors
+        if dy is None:
+            dy = torch.zeros_like(res)
         dx, dw = _rmsnorm_backward(res, weight, rstd, dy, dres, ctx.shape)
-        return dx, dx, dw, None
+        n_delta = 1
+        for d in ctx.delta_shape[:-1]:
+            n_delta *= d
+        ddelta = dx.reshape(-1, dx.shape[-1])[:n_delta].view(ctx.delta_shape)
+        return dx, ddelta, dw, None
 
 
 class _RmsNormFn(torch.autograd.Function):
@@ -172,7 +231,7 @@ class _RmsNormFn(torch.autograd.Function):
         rows = x2.shape[0]
         y = torch.empty_like(x2)
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
-        _lib.call("ksa_rmsnorm_fwd", x2, None, weight, None, y, rstd, rows, D, float(eps))
+        _lib.call("ksa_rmsnorm_fwd", x2, None, weight, None, y, rstd, rows, D, float(eps), 0)
         ctx.save_for_backward(x2, weight, rstd)
         ctx.shape = x.shape
         return y.view(x.shape)
@@ -186,8 +245,15 @@ class _RmsNormFn(torch.autograd.Function):
 
 def add_rms_norm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
                  eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``r = x + delta`` (or ``x``) and ``rms_norm(r)``, one pass over the row."""
+    """``r = x + delta`` (or ``x``) and ``rms_norm(r)``, one pass over the row.
+
+    ``x`` is ``[rows, D]``; ``delta`` may cover only the first ``delta.shape[0]`` rows (the text rows of a
+    full-attention layer in a hybrid stack, whose summary rows bypass the layer).
+    """
     if not _cuda(x):
+        if delta is not None and delta.shape[0] != x.shape[0]:
+            pad = x.new_zeros((x.shape[0] - delta.shape[0],) + tuple(x.shape[1:]))
+            delta = torch.cat([delta, pad], dim=0)
         return ref.add_rms_norm(x, delta, weight, eps)
     _require_bf16(x, delta, weight)
     x = x if x.is_contiguous() else x.contiguous()
@@ -207,15 +273,15 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.
 
 # =============================================================================== QK-norm + RoPE
 class _QkNormRopeFn(torch.autograd.Function):
-    """Input: packed ``qkv`` rows ``[T, (Hq+2Hkv)*D]``; output: rotated ``[T, (Hq+Hkv)*D]`` (q heads | k heads)."""
+    """Packed ``qkv`` rows ``[T, (Hq+2Hkv)*D]`` -> same layout with q, k normalised + rotated and v copied."""
 
     @staticmethod
     def forward(ctx, qkv, q_w, k_w, pos, Hq, Hkv, D, theta, eps, interleaved):
         T = qkv.shape[0]
-        out = torch.empty((T, (Hq + Hkv) * D), dtype=qkv.dtype, device=qkv.device)
+        out = torch.empty((T, (Hq + 2 * Hkv) * D), dtype=qkv.dtype, device=qkv.device)
         rstd = torch.empty((T, Hq + Hkv), dtype=torch.float32, device=qkv.device)
         _lib.call("ksa_qknorm_rope_fwd", qkv, out, q_w, k_w, pos, rstd, qkv.stride(0), out.stride(0), T, Hq, Hkv, D,
-                  float(theta), float(eps), int(interleaved))
+                  float(theta), float(eps), int(interleaved), 1)
         ctx.save_for_backward(qkv, q_w, k_w, pos, rstd)
         ctx.cfg = (Hq, Hkv, D, theta, eps, interleaved)
         return out
@@ -226,7 +292,7 @@ class _QkNormRopeFn(torch.autograd.Function):
         Hq, Hkv, D, theta, eps, interleaved = ctx.cfg
         T = qkv.shape[0]
         d_out = d_out if d_out.is_contiguous() else d_out.contiguous()
-        d_qkv = torch.zeros_like(qkv)  # the v columns get no gradient from this op
+        d_qkv = torch.empty_like(qkv)
         targets = []
         for w in (q_w, k_w):
             if w is None:
@@ -241,7 +307,7 @@ class _QkNormRopeFn(torch.autograd.Function):
             else:
                 targets.append(torch.zeros(D, dtype=torch.float32, device=qkv.device))
         _lib.call("ksa_qknorm_rope_bwd", qkv, d_out, d_qkv, q_w, k_w, pos, rstd, targets[0], targets[1],
-                  qkv.stride(0), d_out.stride(0), T, Hq, Hkv, D, float(theta), float(eps), int(interleaved))
+                  qkv.stride(0), d_out.stride(0), T, Hq, Hkv, D, float(theta), float(eps), int(interleaved), 1)
         grads = []
         for w, t in zip((q_w, k_w), targets):
             if w is None or getattr(w, "main_grad", None) is not None:
@@ -254,17 +320,17 @@ class _QkNormRopeFn(torch.autograd.Function):
 def qk_norm_rope_packed(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
                         pos: torch.Tensor, Hq: int, Hkv: int, D: int, theta: float, eps: float = 1e-6,
                         interleaved: bool = False) -> torch.Tensor:
-    """Per-head RMSNorm of q and k followed by RoPE on packed rows.
+    """Per-head RMSNorm of q and k followed by RoPE, on packed projection rows.
 
-    ``qkv`` is ``[T, (Hq+2Hkv)*D]`` (q heads | k heads | v heads), ``pos`` ``[T]``.
-    Returns ``[T, (Hq+Hkv)*D]`` (rotated q heads | rotated k heads); v is read from ``qkv``.
+    ``qkv`` is ``[T, (Hq+2Hkv)*D]`` (q heads | k heads | v heads), ``pos`` ``[T]``.  Returns the same
+    layout: rotated q heads | rotated k heads | v heads unchanged, so that attention has one producer.
     """
     if not _cuda(qkv):
         T = qkv.shape[0]
         q = qkv[:, :Hq * D].reshape(1, T, Hq, D)
         k = qkv[:, Hq * D:(Hq + Hkv) * D].reshape(1, T, Hkv, D)
         q, k = ref.qk_norm_rope(q, k, q_w, k_w, pos, theta, eps, interleaved)
-        return torch.cat([q.reshape(T, Hq * D), k.reshape(T, Hkv * D)], dim=1)
+        return torch.cat([q.reshape(T, Hq * D), k.reshape(T, Hkv * D), qkv[:, (Hq + Hkv) * D:]], dim=1)
     _require_bf16(qkv, q_w, k_w)
     assert qkv.stride(1) == 1
     return _QkNormRopeFn.apply(qkv, q_w, k_w, pos.to(torch.int32), Hq, Hkv, D, theta, eps, interleaved)
@@ -468,6 +534,98 @@ def causal_attention(q, k, v, scale: Optional[float] = None, window: int = -1,
     return o
 
 
+def _packed_views(qkv: torch.Tensor, B: int, T: int, Hq: int, Hkv: int, D: int, row0: int):
+    rows = qkv[row0:row0 + B * T]
+    q = rows[:, :Hq * D].view(B, T, Hq, D)
+    k = rows[:, Hq * D:(Hq + Hkv) * D].view(B, T, Hkv, D)
+    v = rows[:, (Hq + Hkv) * D:].view(B, T, Hkv, D)
+    return q, k, v
+
+
+class _PackedAttentionFn(torch.autograd.Function):
+    """Attention on packed, rotated projection rows.
+
+    ``qkv`` is ``[B*L + B*Ns, (Hq+2Hkv)*D]``: text rows of all sequences first, then summary rows.  The
+    output is ``[B*L + B*Ns, Hq*D]`` in the same row order and the backward kernels write dq, dk, dv
+    straight into the column blocks of one gradient buffer of the input's shape, so autograd never
+    concatenates, pads or adds anything around the attention.  ``Ns = 0`` gives causal attention.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv, B, L, Ns, Hq, Hkv, D, chunk, n_sum, window, tok_window, scale):
+        R = B * (L + Ns)
+        assert qkv.shape[0] == R and qkv.stride(1) == 1
+        q, k, v = _packed_views(qkv, B, L, Hq, Hkv, D, 0)
+        out = torch.empty((R, Hq * D), dtype=qkv.dtype, device=qkv.device)
+        o = out[:B * L].view(B, L, Hq, D)
+        lse = torch.empty((B, Hq, L), dtype=torch.float32, device=qkv.device)
+        rs = qkv.stride(0)
+        if Ns > 0:
+            qs, ks, vs = _packed_views(qkv, B, Ns, Hq, Hkv, D, B * L)
+        else:
+            qs = ks = vs = None
+        _lib.call("ksa_attn_fwd", q, k, v, ks, vs, o, lse, B, Hq, Hkv, D, L, L, Ns,
+                  rs, L * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs, Hq * D, L * Hq * D,
+                  0, 0, 0, chunk, max(n_sum, 1), window, tok_window, float(scale))
+        lse_s = None
+        if Ns > 0:
+            os_ = out[B * L:].view(B, Ns, Hq, D)
+            lse_s = torch.empty((B, Hq, Ns), dtype=torch.float32, device=qkv.device)
+            _lib.call("ksa_summary_attn_fwd", qs, k, v, ks, vs, os_, lse_s, B, Hq, Hkv, D, Ns, L,
+                      rs, Ns * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs, Hq * D, Ns * Hq * D,
+                      chunk, n_sum, 0, 0, 0, float(scale))
+        ctx.save_for_backward(qkv, out, lse, lse_s)
+        ctx.cfg = (B, L, Ns, Hq, Hkv, D, chunk, n_sum, window, tok_window, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, lse_s = ctx.saved_tensors
+        B, L, Ns, Hq, Hkv, D, chunk, n_sum, window, tok_window, scale = ctx.cfg
+        dout = dout if dout.is_contiguous() else dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        rs, drs = qkv.stride(0), dqkv.stride(0)
+        q, k, v = _packed_views(qkv, B, L, Hq, Hkv, D, 0)
+        dq, dk, dv = _packed_views(dqkv, B, L, Hq, Hkv, D, 0)
+        o = out[:B * L].view(B, L, Hq, D)
+        do = dout[:B * L].view(B, L, Hq, D)
+        delta = torch.empty_like(lse)
+        if Ns > 0:
+            qs, ks, vs = _packed_views(qkv, B, Ns, Hq, Hkv, D, B * L)
+            dqs, dks, dvs = _packed_views(dqkv, B, Ns, Hq, Hkv, D, B * L)
+        else:
+            qs = ks = vs = dqs = dks = dvs = None
+        _lib.call("ksa_attn_bwd", q, k, v, ks, vs, o, do, lse, delta, dq, dk, dv, dks, dvs,
+                  B, Hq, Hkv, D, L, L, Ns,
+                  rs, L * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs, Hq * D, L * Hq * D,
+                  drs, L * drs, drs, L * drs, drs, L * drs, drs, Ns * drs, drs, Ns * drs,
+                  0, 0, 0, chunk, max(n_sum, 1), window, tok_window, float(scale))
+        if Ns > 0:
+            os_ = out[B * L:].view(B, Ns, Hq, D)
+            dos = dout[B * L:].view(B, Ns, Hq, D)
+            _lib.call("ksa_summary_attn_bwd", qs, k, v, ks, vs, os_, dos, lse_s, dqs, dk, dv, dks, dvs,
+                      B, Hq, Hkv, D, Ns, L, rs, Ns * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs,
+                      Hq * D, Ns * Hq * D, drs, Ns * drs, drs, L * drs, drs, L * drs, drs, Ns * drs, drs, Ns * drs,
+                      chunk, n_sum, 0, 0, 0, float(scale))
+        return (dqkv,) + (None,) * 11
+
+
+def attention_packed(qkv: torch.Tensor, B: int, L: int, Ns: int, Hq: int, Hkv: int, D: int, chunk: int = 128,
+                     n_sum: int = 1, window: int = UNBOUNDED_WINDOW, tok_window: int = 0,
+                     scale: Optional[float] = None) -> torch.Tensor:
+    """KSA (``Ns > 0``) or causal (``Ns = 0``) attention on packed rotated rows; see :class:`_PackedAttentionFn`."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not _cuda(qkv):
+        q, k, v = _packed_views(qkv, B, L, Hq, Hkv, D, 0)
+        if Ns > 0:
+            qs, ks, vs = _packed_views(qkv, B, Ns, Hq, Hkv, D, B * L)
+            o_t, o_s = ref.ksa_attention(q, k, v, qs, ks, vs, chunk, n_sum, window, scale)
+            return torch.cat([o_t.reshape(B * L, Hq * D), o_s.reshape(B * Ns, Hq * D)], dim=0)
+        return ref.causal_attention(q, k, v, scale, tok_window if tok_window > 0 else -1).reshape(B * L, Hq * D)
+    _require_bf16(qkv)
+    return _PackedAttentionFn.apply(qkv, B, L, Ns, Hq, Hkv, D, chunk, n_sum, window, tok_window, scale)
+
+
 # =============================================================================== fused linear + cross entropy
 class _LinearCrossEntropyFn(torch.autograd.Function):
     """lm_head GEMM + softmax CE, chunked over tokens so that only one chunk of logits exists."""
@@ -558,7 +716,7 @@ def adamw_step(master, grad, m, v, out_bf16, hyper, beta1, beta2, eps, weight_de
 
 
 __all__ = [
-    "gemm", "linear", "rms_norm", "add_rms_norm", "qk_norm_rope_packed", "swiglu", "embedding",
+    "gemm", "linear", "dual_linear", "attention_packed", "rms_norm", "add_rms_norm", "qk_norm_rope_packed", "swiglu", "embedding",
     "ksa_attention", "causal_attention", "linear_cross_entropy", "adamw_step", "UNBOUNDED_WINDOW",
     "SummaryLayout", "get_layout",
 ]

@@ -22,10 +22,10 @@ P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 # name -> argument ctypes (the trailing stream pointer included)
 _SIGNATURES: Dict[str, Sequence] = {
     "ksa_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, I, P],
-    "ksa_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "ksa_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, I, P],
     "ksa_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
-    "ksa_qknorm_rope_fwd": [P, P, P, P, P, P, L, L, I, I, I, I, F, F, I, P],
-    "ksa_qknorm_rope_bwd": [P, P, P, P, P, P, P, P, P, L, L, I, I, I, I, F, F, I, P],
+    "ksa_qknorm_rope_fwd": [P, P, P, P, P, P, L, L, I, I, I, I, F, F, I, I, P],
+    "ksa_qknorm_rope_bwd": [P, P, P, P, P, P, P, P, P, L, L, I, I, I, I, F, F, I, I, P],
     "ksa_swiglu_fwd": [P, P, L, I, P],
     "ksa_swiglu_bwd": [P, P, P, L, I, P],
     "ksa_embedding_fwd": [P, P, P, L, I, L, P],
@@ -97,14 +97,33 @@ def _ptr(x):
     return x
 
 
+# kernels launched by one call of an entry point (default 1)
+_KERNELS_PER_CALL = {"ksa_attn_bwd": 2, "ksa_rmsnorm_bwd": 2}
+_launch_count = 0
+
+
 def call(name: str, *args) -> None:
     """Launch entry point ``name`` on the current CUDA stream (appended as the last argument)."""
+    global _launch_count
     lib = load()
     fn = getattr(lib, name)
     stream = torch.cuda.current_stream().cuda_stream
     rc = fn(*[_ptr(a) for a in args], stream)
     if rc != 0:
         raise RuntimeError(f"{name} failed ({rc}): {lib.ksa_last_error().decode()}")
+    _launch_count += _KERNELS_PER_CALL.get(name, 1)
+
+
+def launch_count() -> int:
+    """Kernels of this library launched (or captured into a graph) so far in this process."""
+    return _launch_count
+
+
+def count_launches(fn) -> int:
+    """Run ``fn()`` and return how many kernels of this library it launched."""
+    before = _launch_count
+    fn()
+    return _launch_count - before
 
 
 def call_on(name: str, stream: int, *args) -> None:

@@ -1,0 +1,328 @@
+"""Training engine: flat parameter storage, fp32 master weights, fused AdamW, CUDA-graph step.
+
+The reference trains with FSDP2 ``fully_shard`` per decoder layer, bf16 compute parameters with fp32
+master copies and fp32 gradient reduction, ``torch.optim.AdamW`` on the sharded fp32 tensors and
+gradient clipping by value (``muse/training/distributed.py:232-287``,
+``recipes/pretrain_kai_summary_unified.py:592-600,1045-1053``).  This engine owns the same state in a
+layout chosen for the kernels:
+
+* one *unit* per decoder layer plus a root unit (embeddings, final norm, head), as the reference's
+  FSDP units; every unit has four flat buffers: compute weights (bf16 on GPU), fp32 master weights,
+  Adam moments, and an fp32 gradient buffer;
+* every ``nn.Parameter`` becomes a view of its unit's compute buffer and gets a ``main_grad`` view of
+  the gradient buffer, so backward kernels write weight gradients in fp32 directly (first write of an
+  accumulation window overwrites, later ones accumulate; no zero-fill pass);
+* the optimizer is one fused kernel launch per unit over the flat buffers (AdamW, clip-by-value,
+  bf16 refresh of the compute weights, sum of squared gradients for the grad-norm metric);
+* learning rate and bias corrections live in a small device tensor, so a whole
+  forward + backward + optimizer step can be captured once as a CUDA graph and replayed.
+
+Data-parallel / FSDP sharding of these units over ranks is layered on top by
+``ksa_b200.parallel.fsdp`` (which replaces ``_reduce_and_update``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+
+_ALIGN = 128  # elements; keeps every parameter view 256-byte aligned in bf16 (TMA wants 16 bytes)
+
+
+def _round_up(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
+
+
+@dataclass
+class ParamSlot:
+    name: str
+    param: nn.Parameter
+    offset: int
+    numel: int
+    shape: torch.Size
+
+
+@dataclass
+class Unit:
+    """One FSDP unit: flat buffers + the parameters that live in them."""
+    name: str
+    slots: List[ParamSlot] = field(default_factory=list)
+    size: int = 0
+    compute: Optional[torch.Tensor] = None   # param_dtype, full size
+    master: Optional[torch.Tensor] = None    # fp32 (full, or this rank's shard under FSDP)
+    exp_avg: Optional[torch.Tensor] = None
+    exp_avg_sq: Optional[torch.Tensor] = None
+    grad: Optional[torch.Tensor] = None      # fp32, full size
+    shard_lo: int = 0                        # [shard_lo, shard_hi): range of the flat buffer owned by this rank
+    shard_hi: int = 0
+
+
+class TrainEngine:
+    def __init__(self, model: nn.Module, lr: float = 4e-4, betas: Tuple[float, float] = (0.9, 0.95),
+                 eps: float = 1e-8, weight_decay: float = 0.1, clip_value: float = 0.0,
+                 param_dtype: Optional[torch.dtype] = None, device: Optional[torch.device] = None,
+                 lr_lambda: Optional[Callable[[int], float]] = None, grad_accum_steps: int = 1,
+                 world_size: int = 1, rank: int = 0):
+        self.model = model
+        self.base_lr = lr
+        self.beta1, self.beta2 = betas
+        self.eps, self.weight_decay, self.clip_value = eps, weight_decay, clip_value
+        self.lr_lambda = lr_lambda
+        self.grad_accum_steps = grad_accum_steps
+        self.world_size, self.rank = world_size, rank
+        self.device = torch.device(device) if device is not None else next(model.parameters()).device
+        self.param_dtype = param_dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
+        self.step_count = 0          # optimizer steps taken
+        self.micro_step = 0          # micro-batches seen in the current accumulation window
+        self.units: List[Unit] = []
+        self._build_units()
+        self.hyper = torch.zeros(4, dtype=torch.float32, device=self.device)
+        self._hyper_host = torch.zeros(4, dtype=torch.float32)
+        if self.device.type == "cuda":
+            self._hyper_host = self._hyper_host.pin_memory()
+        self.grad_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._graphs: Dict[tuple, "_CapturedStep"] = {}
+
+    # ------------------------------------------------------------------ construction
+    def _unit_modules(self) -> List[Tuple[str, List[Tuple[str, nn.Parameter]]]]:
+        model = self.model
+        layer_mods = model.get_layers_to_shard() if hasattr(model, "get_layers_to_shard") else []
+        taken = set()
+        units = []
+        names = {id(p): n for n, p in model.named_parameters()}
+        for i, m in enumerate(layer_mods):
+            ps = [(names[id(p)], p) for p in m.parameters()]
+            taken.update(id(p) for _, p in ps)
+            units.append((f"layer{i}", ps))
+        root = [(n, p) for n, p in model.named_parameters() if id(p) not in taken]
+        units.append(("root", root))
+        return units
+
+    def _shard_range(self, size: int) -> Tuple[int, int]:
+        per = size // self.world_size
+        return self.rank * per, (self.rank + 1) * per
+
+    def _build_units(self) -> None:
+        dev, pd = self.device, self.param_dtype
+        for uname, ps in self._unit_modules():
+            unit = Unit(uname)
+            off = 0
+            for n, p in ps:
+                unit.slots.append(ParamSlot(n, p, off, p.numel(), p.shape))
+                off += _round_up(p.numel(), _ALIGN)
+            unit.size = _round_up(off, _ALIGN * max(self.world_size, 1))
+            self._alloc_unit(unit)
+            with torch.no_grad():
+                for s in unit.slots:
+                    src = s.param.detach().to(device=dev, dtype=torch.float32).reshape(-1)
+                    unit.compute[s.offset:s.offset + s.numel].copy_(src)
+                    self._master_init(unit, s, src)
+                    s.param.data = unit.compute[s.offset:s.offset + s.numel].view(s.shape)
+                    s.param.main_grad = unit.grad[s.offset:s.offset + s.numel].view(s.shape)
+                    s.param._grad_written = False
+            self.units.append(unit)
+
+    def _alloc_unit(self, unit: Unit) -> None:
+        dev = self.device
+        unit.compute = torch.zeros(unit.size, dtype=self.param_dtype, device=dev)
+        unit.grad = torch.zeros(unit.size, dtype=torch.float32, device=dev)
+        unit.shard_lo, unit.shard_hi = self._shard_range(unit.size)
+        n = unit.shard_hi - unit.shard_lo
+        unit.master = torch.zeros(n, dtype=torch.float32, device=dev)
+        unit.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
+        unit.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
+
+    def _master_init(self, unit: Unit, s: ParamSlot, src_f32: torch.Tensor) -> None:
+        lo, hi = max(s.offset, unit.shard_lo), min(s.offset + s.numel, unit.shard_hi)
+        if hi > lo:
+            unit.master[lo - unit.shard_lo:hi - unit.shard_lo].copy_(src_f32[lo - s.offset:hi - s.offset])
+
+    # ------------------------------------------------------------------ schedule
+    def current_lr(self, step: Optional[int] = None) -> float:
+        step = self.step_count if step is None else step
+        return self.base_lr * (self.lr_lambda(step) if self.lr_lambda is not None else 1.0)
+
+    def _write_hyper(self) -> None:
+        t = self.step_count + 1
+        h = self._hyper_host
+        h[0] = self.current_lr()
+        h[1] = 1.0 - self.beta1 ** t
+        h[2] = 1.0 - self.beta2 ** t
+        h[3] = 1.0 / (self.grad_accum_steps * max(self.world_size, 1))
+        self.hyper.copy_(h, non_blocking=True)
+
+    # ------------------------------------------------------------------ gradients
+    def zero_grad(self) -> None:
+        for u in self.units:
+            for s in u.slots:
+                s.param._grad_written = False
+                s.param.grad = None
+
+    def _collect_autograd_grads(self) -> None:
+        """Fold ``.grad`` (ops without a main_grad path, the CPU path) into the fp32 buffers; zero the rest."""
+        for u in self.units:
+            for s in u.slots:
+                p = s.param
+                if p.grad is not None:
+                    if getattr(p, "_grad_written", False):
+                        p.main_grad.add_(p.grad.to(torch.float32))
+                    else:
+                        p.main_grad.copy_(p.grad)
+                        p._grad_written = True
+                    p.grad = None
+                elif not getattr(p, "_grad_written", False):
+                    p.main_grad.zero_()
+                    p._grad_written = True
+
+    # ------------------------------------------------------------------ optimizer
+    def _reduce_and_update(self, unit: Unit) -> None:
+        """Single rank: AdamW over the whole unit.  The FSDP engine overrides this with the fused
+        reduce-scatter + AdamW + weight all-gather."""
+        ops.adamw_step(unit.master, unit.grad, unit.exp_avg, unit.exp_avg_sq,
+                       unit.compute if self.param_dtype != torch.float32 else None,
+                       self.hyper, self.beta1, self.beta2, self.eps, self.weight_decay, self.clip_value, self.grad_sq)
+        if self.param_dtype == torch.float32:
+            unit.compute.copy_(unit.master)
+
+    def optimizer_step(self) -> None:
+        self._collect_autograd_grads()
+        self.grad_sq.zero_()
+        for unit in reversed(self.units):
+            self._reduce_and_update(unit)
+        self._finish_step()
+
+    def _finish_step(self) -> None:
+        pass
+
+    def grad_norm(self) -> torch.Tensor:
+        """Global L2 norm of the (averaged) gradients of the last optimizer step, as a device scalar."""
+        return self.grad_sq.sqrt()
+
+    # ------------------------------------------------------------------ steps
+    def forward_backward(self, tokens: torch.Tensor, labels: torch.Tensor, **kw) -> torch.Tensor:
+        loss = self.model(tokens, labels=labels, **kw)
+        loss.backward()
+        return loss.detach()
+
+    def train_step(self, tokens: torch.Tensor, labels: torch.Tensor, **kw) -> torch.Tensor:
+        """One micro-batch; runs the optimizer at the accumulation boundary.  Returns the loss (device)."""
+        if self.micro_step == 0:
+            self.zero_grad()
+        loss = self.forward_backward(tokens, labels, **kw)
+        self.micro_step += 1
+        if self.micro_step == self.grad_accum_steps:
+            self._write_hyper()
+            self.optimizer_step()
+            self.step_count += 1
+            self.micro_step = 0
+        return loss
+
+    # ------------------------------------------------------------------ CUDA-graph step
+    def graphed_step(self, tokens: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """``train_step`` replayed from a CUDA graph captured on first use for this shape.
+
+        ``tokens``/``labels`` may live in pinned host memory: they are copied into the graph's static
+        inputs on the current stream.  Needs ``grad_accum_steps == 1`` windows to be uniform: a graph is
+        keyed by (shape, first micro-step?, boundary?).
+        """
+        first = self.micro_step == 0
+        boundary = self.micro_step + 1 == self.grad_accum_steps
+        key = (tuple(tokens.shape), first, boundary)
+        cap = self._graphs.get(key)
+        if cap is None:
+            cap = _CapturedStep(self, tokens.shape, first, boundary)
+            self._graphs[key] = cap
+        cap.tokens.copy_(tokens, non_blocking=True)
+        cap.labels.copy_(labels, non_blocking=True)
+        if boundary:
+            self._write_hyper()
+        cap.graph.replay()
+        self.micro_step += 1
+        if boundary:
+            self.step_count += 1
+            self.micro_step = 0
+        return cap.loss
+
+    # ------------------------------------------------------------------ state
+    def named_master_params(self):
+        """(name, fp32 tensor view) for every parameter whose master copy is fully local (single rank)."""
+        for u in self.units:
+            for s in u.slots:
+                if s.offset >= u.shard_lo and s.offset + s.numel <= u.shard_hi:
+                    lo = s.offset - u.shard_lo
+                    yield s.name, u.master[lo:lo + s.numel].view(s.shape)
+
+    def state_dict(self) -> dict:
+        return {
+            "step": self.step_count,
+            "units": {u.name: {"master": u.master, "exp_avg": u.exp_avg, "exp_avg_sq": u.exp_avg_sq,
+                               "shard": (u.shard_lo, u.shard_hi), "size": u.size,
+                               "slots": [(s.name, s.offset, s.numel, tuple(s.shape)) for s in u.slots]}
+                      for u in self.units},
+        }
+
+    def load_state_dict(self, state: dict, load_optimizer: bool = True) -> None:
+        self.step_count = int(state.get("step", 0)) if load_optimizer else self.step_count
+        for u in self.units:
+            su = state["units"][u.name]
+            u.master.copy_(su["master"])
+            if load_optimizer:
+                u.exp_avg.copy_(su["exp_avg"])
+                u.exp_avg_sq.copy_(su["exp_avg_sq"])
+        self.refresh_compute_from_master()
+
+    def refresh_compute_from_master(self) -> None:
+        for u in self.units:
+            if self.world_size == 1:
+                u.compute.copy_(u.master)
+
+    def load_model_weights(self, state: Dict[str, torch.Tensor]) -> None:
+        """Overwrite compute and master weights from a (fused-name) model state dict."""
+        with torch.no_grad():
+            for u in self.units:
+                for s in u.slots:
+                    if s.name not in state:
+                        continue
+                    src = state[s.name].to(device=self.device, dtype=torch.float32).reshape(-1)
+                    u.compute[s.offset:s.offset + s.numel].copy_(src)
+                    self._master_init(u, s, src)
+
+
+class _CapturedStep:
+    def __init__(self, engine: TrainEngine, shape, first: bool, boundary: bool):
+        dev = engine.device
+        self.tokens = torch.zeros(shape, dtype=torch.long, device=dev)
+        self.labels = torch.zeros(shape, dtype=torch.long, device=dev)
+        # Warm up on a side stream (allocator pools, kernel attributes, status words), undoing its effects on state.
+        snap = [(u.master.clone(), u.exp_avg.clone(), u.exp_avg_sq.clone(), u.compute.clone()) for u in engine.units]
+        grads = None if first else [u.grad.clone() for u in engine.units]
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            self._run(engine, first, boundary)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        for u, (ma, m, v, c) in zip(engine.units, snap):
+            u.master.copy_(ma); u.exp_avg.copy_(m); u.exp_avg_sq.copy_(v); u.compute.copy_(c)
+        if grads is not None:
+            for u, g in zip(engine.units, grads):
+                u.grad.copy_(g)
+        del snap, grads
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = self._run(engine, first, boundary)
+
+    def _run(self, engine: TrainEngine, first: bool, boundary: bool) -> torch.Tensor:
+        for u in engine.units:
+            for s in u.slots:
+                s.param._grad_written = not first
+                s.param.grad = None
+        loss = engine.forward_backward(self.tokens, self.labels)
+        if boundary:
+            engine.optimizer_step()
+        return loss

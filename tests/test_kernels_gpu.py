@@ -107,17 +107,17 @@ def test_qk_norm_rope(D, Hq, Hkv, interleaved):
     kw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
     pos = torch.randint(0, 100000, (T,), device=DEV)
     out = ops.qk_norm_rope_packed(qkv, qw, kw, pos, Hq, Hkv, D, 1e6, 1e-6, interleaved)
-    g = bf(T, (Hq + Hkv) * D)
+    g = bf(T, (Hq + 2 * Hkv) * D)
     out.backward(g)
     f = [t.detach().float().requires_grad_() for t in (qkv, qw, kw)]
     q = f[0][:, :Hq * D].reshape(1, T, Hq, D)
     k = f[0][:, Hq * D:(Hq + Hkv) * D].reshape(1, T, Hkv, D)
     qr, kr = ref.qk_norm_rope(q, k, f[1], f[2], pos, 1e6, 1e-6, interleaved)
-    o_ref = torch.cat([qr.reshape(T, -1), kr.reshape(T, -1)], 1)
+    o_ref = torch.cat([qr.reshape(T, -1), kr.reshape(T, -1), f[0][:, (Hq + Hkv) * D:]], 1)
     o_ref.backward(g.float())
     check(out, o_ref, 1e-2, "qknorm_rope fwd")
-    check(qkv.grad[:, :(Hq + Hkv) * D], f[0].grad[:, :(Hq + Hkv) * D], 2e-2, "qknorm_rope dqkv")
-    assert qkv.grad[:, (Hq + Hkv) * D:].abs().max() == 0
+    check(qkv.grad, f[0].grad, 2e-2, "qknorm_rope dqkv")
+    assert torch.equal(qkv.grad[:, (Hq + Hkv) * D:], g[:, (Hq + Hkv) * D:])
     check(qw.grad, f[1].grad, 3e-2, "q_norm dw")
     check(kw.grad, f[2].grad, 3e-2, "k_norm dw")
 
@@ -239,3 +239,53 @@ def test_attention_reads_packed_qkv_views():
     o = ops.causal_attention(q, k, v)
     r = ref.causal_attention(q.float(), k.float(), v.float())
     check(o, r, 1.5e-2, "packed views")
+
+
+def test_dual_linear():
+    R, n_a, K, N = 520, 400, 256, 384
+    x = bf(R, K).requires_grad_()
+    wa, wb = bf(N, K, scale=0.05).requires_grad_(), bf(N, K, scale=0.05).requires_grad_()
+    y = ops.dual_linear(x, wa, wb, n_a)
+    g = bf(R, N)
+    y.backward(g)
+    xf, waf, wbf = [t.detach().float().requires_grad_() for t in (x, wa, wb)]
+    yr = torch.cat([xf[:n_a] @ waf.t(), xf[n_a:] @ wbf.t()])
+    yr.backward(g.float())
+    check(y, yr, 1e-2, "dual y")
+    check(x.grad, xf.grad, 1e-2, "dual dx")
+    check(wa.grad, waf.grad, 1e-2, "dual dwa")
+    check(wb.grad, wbf.grad, 1e-2, "dual dwb")
+
+
+def test_add_rms_norm_partial_delta():
+    rows, n_d, D = 300, 256, 512
+    x, d = bf(rows, D).requires_grad_(), bf(n_d, D).requires_grad_()
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+    res, y = ops.add_rms_norm(x, d, w)
+    gr, gy = bf(rows, D), bf(rows, D)
+    torch.autograd.backward([res, y], [gr, gy])
+    xf, df, wf = [t.detach().float().requires_grad_() for t in (x, d, w)]
+    r_ref = xf + torch.cat([df, torch.zeros(rows - n_d, D, device=DEV)])
+    y_ref = ref.rms_norm(r_ref, wf)
+    ((r_ref * gr.float()).sum() + (y_ref * gy.float()).sum()).backward()
+    check(res, r_ref, 5e-3, "partial residual")
+    check(y, y_ref, 1e-2, "partial y")
+    check(d.grad, df.grad, 1.5e-2, "partial ddelta")
+    check(x.grad, xf.grad, 1.5e-2, "partial dx")
+
+
+@pytest.mark.parametrize("B,L,Hq,Hkv,D,C,S,W", [(2, 1024, 4, 2, 128, 128, 1, 2), (1, 512, 4, 2, 64, 64, 1, 4),
+                                                (2, 768, 4, 2, 128, 128, 0, 0)])
+def test_attention_packed(B, L, Hq, Hkv, D, C, S, W):
+    Ns = (L // C) * S
+    R = B * (L + Ns)
+    qkv = bf(R, (Hq + 2 * Hkv) * D).requires_grad_()
+    kw = dict(chunk=C, n_sum=max(S, 1), window=W) if S > 0 else {}
+    out = ops.attention_packed(qkv, B, L, Ns, Hq, Hkv, D, **kw)
+    g = bf(R, Hq * D)
+    out.backward(g)
+    f = qkv.detach().float().cpu().requires_grad_()
+    o_ref = ops.attention_packed(f, B, L, Ns, Hq, Hkv, D, **kw)
+    o_ref.backward(g.float().cpu())
+    check(out, o_ref.to(DEV), 1.5e-2, "packed attention out")
+    check(qkv.grad, f.grad.to(DEV), 3e-2, "packed attention dqkv")

@@ -1,0 +1,156 @@
+"""CPU semantics: two-stream KSA == the reference's interleaved dense-mask formulation; tiny model trains."""
+import math
+
+import pytest
+import torch
+
+from ksa_b200.config import get_preset, load_config, parse_layer_pattern, Qwen3SummaryAttentionConfig
+from ksa_b200.models import Qwen3SummaryModel, get_model_class
+from ksa_b200.ops import reference as ref
+from ksa_b200.ops.layout import (SummaryLayout, count_attended_pairs, dense_interleaved_mask, get_layout,
+                                 two_stream_masks)
+
+
+def test_pattern_parser():
+    assert parse_layer_pattern("([1]*3+[0]*1)*2") == [1, 1, 1, 0, 1, 1, 1, 0]
+    assert len(parse_layer_pattern("([128]*3+[1024]*1)*6")) == 24
+    with pytest.raises(ValueError):
+        parse_layer_pattern("__import__('os')")
+
+
+def test_config_roundtrip(tmp_path):
+    cfg = get_preset("qwen3-1.9b-ksa")
+    assert sum(cfg.get_layer_is_summary()) == 21 and cfg.num_layers == 28
+    p = tmp_path / "m.json"
+    cfg.save(str(p))
+    again = load_config(str(p))
+    assert isinstance(again, Qwen3SummaryAttentionConfig) and again.to_dict() == cfg.to_dict()
+    assert abs(cfg.num_parameters() - 2.21e9) < 0.05e9
+
+
+def test_shipped_reference_json_loads():
+    import os
+    path = "/root/reference/examples/pretrain/model_config/model_config_1b9_hybrid.json"
+    if not os.path.exists(path):
+        pytest.skip("reference tree not mounted")
+    cfg = load_config(path)
+    assert cfg.summary_chunk_size == 8 and cfg.get_layer_sliding_chunk_num(3) == 1024
+
+
+@pytest.mark.parametrize("L,C,S,W", [(256, 32, 1, 2), (192, 16, 2, 1), (128, 8, 1, 4), (100, 32, 1, 1)])
+def test_two_stream_masks_equal_interleaved(L, C, S, W):
+    lay = SummaryLayout(L, C, S)
+    tt, ts, st, ss = two_stream_masks(L, C, S, W)
+    if L % C == 0:
+        dense = dense_interleaved_mask(lay.expanded_len, C, S, W)
+        ti, si = lay.text_rows_in_expanded(), lay.summary_rows_in_expanded()
+        assert torch.equal(dense[ti][:, ti], tt) and torch.equal(dense[ti][:, si], ts)
+        assert torch.equal(dense[si][:, ti], st) and torch.equal(dense[si][:, si], ss)
+    n = int(tt.sum() + ts.sum() + st.sum() + ss.sum())
+    assert n == count_attended_pairs(L, C, S, W)
+
+
+def test_two_stream_attention_equals_interleaved():
+    torch.manual_seed(0)
+    B, L, Hq, Hkv, D, C, S, W = 2, 256, 4, 2, 16, 32, 2, 2
+    lay = SummaryLayout(L, C, S)
+    T = lay.expanded_len
+    q, k, v = torch.randn(B, T, Hq, D), torch.randn(B, T, Hkv, D), torch.randn(B, T, Hkv, D)
+    o = ref.interleaved_ksa_attention(q, k, v, C, S, W)
+    (qt, qs), (kt, ks), (vt, vs) = lay.split(q), lay.split(k), lay.split(v)
+    ot, os_ = ref.ksa_attention(qt, kt, vt, qs, ks, vs, C, S, W)
+    o_t_ref, o_s_ref = lay.split(o)
+    assert torch.allclose(ot, o_t_ref, atol=1e-5) and torch.allclose(os_, o_s_ref, atol=1e-5)
+
+
+def test_position_ids_match_reference_rule():
+    lay = SummaryLayout(64, 16, 2, "origin", "last_chunk_slice_right")
+    assert lay.summary_position_ids().tolist() == [7, 15, 23, 31, 39, 47, 55, 63]
+    lay1 = SummaryLayout(64, 16, 1, "origin", "last_chunk_slice_right")
+    assert lay1.summary_position_ids().tolist() == [15, 31, 47, 63]
+    assert SummaryLayout(64, 16, 1, "inner_chunk", "zeros").text_position_ids()[17] == 1
+    cu = torch.tensor([0, 20, 64])
+    assert lay1.remap_cu_seqlens(cu).tolist() == [0, 21, 68]
+
+
+def _interleaved_model_forward(model, tokens):
+    """The reference formulation: one interleaved sequence, dense mask, summary rows overwritten per layer."""
+    cfg = model.config
+    B, L = tokens.shape
+    C, S = cfg.summary_chunk_size, cfg.summary_token_num
+    lay = get_layout(L, C, S, cfg.summary_chunk_position_ids_type, cfg.summary_token_position_ids_type)
+    Hq, Hkv, Dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+    x_t = torch.nn.functional.embedding(tokens, model.tok_embeddings.weight)
+    x_s = model.summary_embedding.weight.repeat(B, lay.n_chunks, 1)
+    x = lay.interleave(x_t, x_s)
+    pos = lay.expanded_position_ids()
+    smask = lay.summary_mask_expanded()
+    for i, layer in enumerate(model.layers):
+        a = layer.attn
+        if layer.is_summary_layer:
+            h = ref.rms_norm(x, layer.sa_norm.scale)
+            qkv = h @ a.wqkv.weight.t()
+            qkv[:, smask] = h[:, smask] @ a.wqkv_summary.weight.t()
+            q, k, v = qkv.split([Hq * Dh, Hkv * Dh, Hkv * Dh], -1)
+            q, k = q.reshape(B, -1, Hq, Dh), k.reshape(B, -1, Hkv, Dh)
+            q, k = ref.qk_norm_rope(q, k, a.q_norm.scale, a.k_norm.scale, pos, cfg.rope_base)
+            o = ref.interleaved_ksa_attention(q, k, v.reshape(B, -1, Hkv, Dh), C, S, layer.window_chunks)
+            x = x + o.reshape(B, -1, Hq * Dh) @ a.output_proj.weight.t()
+            h2 = ref.rms_norm(x, layer.mlp_norm.scale)
+            x = x + ref.swiglu(h2 @ layer.mlp.w13.weight.t()) @ layer.mlp.w2.weight.t()
+        else:
+            xt = x[:, ~smask]
+            h = ref.rms_norm(xt, layer.sa_norm.scale)
+            qkv = h @ a.wqkv.weight.t()
+            q, k, v = qkv.split([Hq * Dh, Hkv * Dh, Hkv * Dh], -1)
+            q, k = q.reshape(B, -1, Hq, Dh), k.reshape(B, -1, Hkv, Dh)
+            q, k = ref.qk_norm_rope(q, k, a.q_norm.scale, a.k_norm.scale, pos[~smask], cfg.rope_base)
+            o = ref.causal_attention(q, k, v.reshape(B, -1, Hkv, Dh))
+            xt = xt + o.reshape(B, -1, Hq * Dh) @ a.output_proj.weight.t()
+            h2 = ref.rms_norm(xt, layer.mlp_norm.scale)
+            xt = xt + ref.swiglu(h2 @ layer.mlp.w13.weight.t()) @ layer.mlp.w2.weight.t()
+            x = x.clone()
+            x[:, ~smask] = xt
+    h = ref.rms_norm(x[:, ~smask], model.norm.scale)
+    return h @ model.output.weight.t()
+
+
+def test_tiny_model_matches_interleaved_reference_and_trains():
+    torch.manual_seed(0)
+    cfg = get_preset("qwen3-ksa-tiny")
+    model = get_model_class(cfg.model_class)(cfg)
+    model.init_weights(seed=0)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 512))
+    logits = model(tokens)
+    with torch.no_grad():
+        expect = _interleaved_model_forward(model, tokens)
+    assert torch.allclose(logits, expect, atol=1e-4), (logits - expect).abs().max()
+    labels = torch.roll(tokens, -1, 1)
+    labels[:, -1] = -100
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    losses = []
+    for _ in range(3):
+        loss = model(tokens, labels=labels)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert abs(losses[0] - math.log(cfg.vocab_size)) < 0.5 and losses[-1] < losses[0]
+
+
+def test_muse_and_hf_key_roundtrip():
+    cfg = get_preset("qwen3-ksa-tiny")
+    model = Qwen3SummaryModel(cfg)
+    model.init_weights(seed=1)
+    muse = model.muse_state_dict()
+    assert "model.layers.0.attn.q_proj_summary.weight" in muse and "model.layers.3.attn.q_proj_summary.weight" not in muse
+    assert "model.layers.0.mlp.w1.weight" in muse and "summary_embedding.weight" in muse
+    hf = model.revert_hf_state_dict(model.state_dict())
+    assert hf["model.embed_tokens.weight"].shape[0] == cfg.vocab_size + cfg.summary_token_num
+    assert hf["lm_head.weight"].shape[0] == cfg.vocab_size + cfg.summary_token_num
+    assert "model.layers.0.self_attn.q_proj_summary.weight" in hf and "model.layers.1.mlp.gate_proj.weight" in hf
+    assert "model.layers.2.input_layernorm.weight" in hf and "model.layers.2.self_attn.q_norm.weight" in hf
+    other = Qwen3SummaryModel(cfg)
+    other.load_state_dict(other.convert_hf_state_dict(hf))
+    for (k, a), (_, b) in zip(model.state_dict().items(), other.state_dict().items()):
+        assert torch.equal(a, b), k

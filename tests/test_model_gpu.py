@@ -1,0 +1,90 @@
+"""The model on the sm_100a kernels against the same model in fp32 on the CPU formulas; engine behaviour."""
+import copy
+
+import pytest
+import torch
+
+from ksa_b200.config import get_preset
+from ksa_b200.models import get_model_class
+from ksa_b200.ops import _lib
+from ksa_b200.training.engine import TrainEngine
+
+pytestmark = pytest.mark.gpu
+
+
+def _tiny(head_dim=64, chunk=64, **over):
+    cfg = get_preset("qwen3-ksa-tiny")
+    return cfg.merge({"head_dim": head_dim, "summary_chunk_size": chunk, **over})
+
+
+@pytest.mark.parametrize("head_dim,chunk", [(64, 64), (128, 128)])
+def test_logits_and_loss_match_fp32_cpu(head_dim, chunk):
+    cfg = _tiny(head_dim, chunk)
+    torch.manual_seed(0)
+    ref_model = get_model_class(cfg.model_class)(cfg)
+    ref_model.init_weights(seed=0)
+    # round the weights to bf16 once so that both sides start from identical values
+    with torch.no_grad():
+        for p in ref_model.parameters():
+            p.copy_(p.to(torch.bfloat16).float())
+    gpu_model = copy.deepcopy(ref_model).to("cuda").to(torch.bfloat16)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 1024))
+    labels = torch.roll(tokens, -1, 1)
+    labels[:, -1] = -100
+    logits = gpu_model(tokens.cuda()).float().cpu()
+    expect = ref_model(tokens)
+    _lib.check_status()
+    err = (logits - expect).norm() / expect.norm()
+    assert err < 3e-2, err
+    loss = gpu_model(tokens.cuda(), labels=labels.cuda())
+    loss.backward()
+    loss_ref = ref_model(tokens, labels=labels)
+    loss_ref.backward()
+    _lib.check_status()
+    assert abs(loss.item() - loss_ref.item()) < 2e-2
+    for (n, a), (_, b) in zip(gpu_model.named_parameters(), ref_model.named_parameters()):
+        assert a.grad is not None, n
+        e = (a.grad.float().cpu() - b.grad).norm() / b.grad.norm().clamp_min(1e-6)
+        assert e < 8e-2, (n, e.item())
+
+
+def test_engine_step_and_graph_replay_agree():
+    cfg = _tiny(128, 128, embed_dim=512)
+    torch.manual_seed(0)
+    base = get_model_class(cfg.model_class)(cfg)
+    base.init_weights(seed=0)
+    tokens = torch.randint(0, cfg.vocab_size, (4, 2, 513), device="cuda")
+    results = []
+    for graphed in (False, True):
+        model = copy.deepcopy(base).to("cuda").to(torch.bfloat16)
+        eng = TrainEngine(model, lr=1e-3, weight_decay=0.1, clip_value=1.0)
+        fn = eng.graphed_step if graphed else eng.train_step
+        losses = [float(fn(t[:, :-1].contiguous(), t[:, 1:].contiguous())) for t in tokens]
+        _lib.check_status()
+        results.append((losses, [u.master.clone() for u in eng.units], float(eng.grad_norm())))
+    (l0, m0, g0), (l1, m1, g1) = results
+    assert l0[-1] < l0[0]
+    assert all(abs(a - b) < 2e-2 for a, b in zip(l0, l1)), (l0, l1)
+    assert abs(g0 - g1) < 0.05 * g0
+    for a, b in zip(m0, m1):
+        assert (a - b).norm() <= 2e-2 * a.norm()
+
+
+def test_grad_accumulation_equals_large_batch():
+    cfg = _tiny(64, 64)
+    torch.manual_seed(0)
+    base = get_model_class(cfg.model_class)(cfg)
+    base.init_weights(seed=0)
+    toks = torch.randint(0, cfg.vocab_size, (2, 1, 513), device="cuda")
+    m1 = copy.deepcopy(base).to("cuda").to(torch.bfloat16)
+    e1 = TrainEngine(m1, lr=1e-3, grad_accum_steps=2)
+    for t in toks:
+        e1.train_step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
+    m2 = copy.deepcopy(base).to("cuda").to(torch.bfloat16)
+    e2 = TrainEngine(m2, lr=1e-3)
+    both = toks.reshape(2, 513)
+    e2.train_step(both[:, :-1].contiguous(), both[:, 1:].contiguous())
+    _lib.check_status()
+    assert e1.step_count == 1 and e2.step_count == 1
+    for a, b in zip(e1.units, e2.units):
+        assert (a.master - b.master).norm() <= 3e-3 * b.master.norm()
