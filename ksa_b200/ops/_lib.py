@@ -93,6 +93,8 @@ def _ptr(x):
     if x is None:
         return None
     if isinstance(x, torch.Tensor):
+        if not x.is_cuda:  # a host pointer handed to a kernel is an illegal access on the device
+            raise TypeError("a CPU tensor was passed to an sm_100a kernel entry point")
         return x.data_ptr()
     return x
 

@@ -213,6 +213,9 @@ class TrainEngine:
         """One micro-batch; runs the optimizer at the accumulation boundary.  Returns the loss (device)."""
         if self.micro_step == 0:
             self.zero_grad()
+        if tokens.device != self.device:  # e.g. pinned host batches
+            tokens = tokens.to(self.device, non_blocking=True)
+            labels = labels.to(self.device, non_blocking=True)
         loss = self.forward_backward(tokens, labels, **kw)
         self.micro_step += 1
         if self.micro_step == self.grad_accum_steps:
