@@ -21,7 +21,8 @@
 
 namespace ksa {
 
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;   // TMA warp, MMA warp, two compute warpgroups
+constexpr int kSumSeg = 8;          // query tiles per CTA for a summary-key tile (its query range is split)
 
 template <int HD>
 struct BwdSmem {
@@ -48,6 +49,8 @@ struct BwdParams {
   long long dk_row_stride, dk_batch_stride, dv_row_stride, dv_batch_stride;
   bf16* dks; bf16* dvs;   // summary key grads [B, Ns, Hkv, HD]
   long long dks_row_stride, dks_batch_stride, dvs_row_stride, dvs_batch_stride;
+  float* dks32; float* dvs32;  // fp32 partial sums [B, Ns, Hkv, HD] when a summary tile's query range is split
+  int n_seg;                   // segments per summary key tile (1: no split)
   int* status;
 };
 
@@ -57,7 +60,7 @@ __device__ __forceinline__ void load_tile_b(uint8_t* dst, const CUtensorMap* m, 
   for (int half = 0; half < HD / 64; ++half) tma_load_4d(dst + half * 16384, m, half * 64, row0, h, b, bar);
 }
 
-__device__ __forceinline__ void wg_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void wg_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // Store a row of HD fp32 accumulators from TMEM as bf16 to global memory.
 template <int HD>
@@ -117,7 +120,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(q_full, 1);
     for (int i = 0; i < S::kStages; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     mbar_init(sp_full, 1);
-    mbar_init(ds_full, 128);
+    mbar_init(ds_full, 256);
     mbar_init(dq_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -172,13 +175,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tdQ, tS + kk * 8, smem_desc_mnmajor_sw128(ka + kk * 2048, 16384), idesc_dq, (j | kk) != 0);
+          umma_ts(tdQ, tS + (kk / 4) * 64 + (kk % 4) * 8, smem_desc_mnmajor_sw128(ka + kk * 2048, 16384), idesc_dq,
+                  (j | kk) != 0);
         umma_commit(&kv_empty[stage]);
       }
       if (ok) umma_commit(dq_full);
     }
   } else {
+    // Two warpgroups share the 128 rows: warps 2-5 take score columns 0..63, warps 6-9 columns 64..127.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const int q_local = q_tile * 128 + r;
     const bool valid = q_local < sh.Lq;
@@ -202,7 +208,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       const long long sidx = ((long long)b * sh.Hq + head) * sh.Lq + q_local;
       lse2 = p.lse[sidx] * 1.4426950408889634f;
-      p.delta[sidx] = delta;
+      if (half == 0) p.delta[sidx] = delta;
     }
     bool ok = true;
     for (int j = 0; j < total; ++j) {
@@ -212,8 +218,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int kt = is_sum ? j : tr.text_first + (j - tr.n_sum_tiles);
       int lo, hi;
       allowed_columns(sh, t_glob, is_sum, kt, lo, hi);
+      // dS (bf16, two per column) overwrites the scores this warpgroup has already read:
+      // chunk c goes to columns (c/2)*64 + (c%2)*16.
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t sr[32], dr[32];
         tmem_ld32(tS + lane_addr + c * 32, sr);
         tmem_ld32(tdP + lane_addr + c * 32, dr);
@@ -231,7 +240,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
           pk[i] = pack_bf16x2(ds[0], ds[1]);
         }
-        tmem_st16(tS + lane_addr + c * 16, pk);
+        tmem_st16(tS + lane_addr + half * 64 + cc * 16, pk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -241,7 +250,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (ok) {
       tc_fence_after();
       bf16* dst = p.dq + (long long)b * p.dq_batch_stride + (long long)q_local * p.dq_row_stride + (long long)head * HD;
-      store_acc_row<HD>(tdQ + lane_addr, dst, valid, 1.f);
+      store_acc_row<HD / 2>(tdQ + lane_addr + half * (HD / 2), dst + half * (HD / 2), valid, 1.f);
     }
   }
   tc_fence_before();
@@ -250,6 +259,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }
 
 // ================================================================================ dK / dV
+// Grid x: first every (summary key tile, query segment) pair, then the text key tiles.  A summary key tile is
+// seen by almost every later query tile, so its query range is cut into segments of kSumSeg tiles that run as
+// separate CTAs and add their fp32 partial results into dks32/dvs32 (zeroed by the caller); the summary-query
+// kernel, which runs next, folds those partials into the bf16 gradients.  With a single segment the CTA writes
+// bf16 directly.  Text key tiles are seen by at most window+1 query tiles (all later ones for causal attention,
+// where tile 0 is the heaviest and is scheduled first).
 template <int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
@@ -275,20 +290,28 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const WaitGuard guard{abort_flag, p.status};
   const AttnShape& sh = p.s;
-  const int n_text_tiles = (sh.Lk + 127) / 128;
-  const bool is_sum = (int)blockIdx.x >= n_text_tiles;
-  const int kt = is_sum ? (int)blockIdx.x - n_text_tiles : (int)blockIdx.x;
+  const int n_sum_tiles = (sh.Ns + 127) / 128;
+  const int n_seg = p.n_seg;
+  const int n_sum_ctas = n_sum_tiles * n_seg;
+  const bool is_sum = (int)blockIdx.x < n_sum_ctas;
+  const int kt = is_sum ? (int)blockIdx.x / n_seg : (int)blockIdx.x - n_sum_ctas;
+  const int seg = is_sum ? (int)blockIdx.x % n_seg : 0;
   const int kv_head = blockIdx.y, b = blockIdx.z;
   const int G = sh.Hq / sh.Hkv;
-  const QueryRange qr = is_sum ? query_tiles_for_summary_key_tile(sh, kt) : query_tiles_for_text_key_tile(sh, kt);
+  QueryRange qr = is_sum ? query_tiles_for_summary_key_tile(sh, kt) : query_tiles_for_text_key_tile(sh, kt);
+  if (is_sum && n_seg > 1) {
+    qr.first = max(qr.first, seg * kSumSeg);
+    qr.last = min(qr.last, seg * kSumSeg + kSumSeg - 1);
+  }
   const int n_q = qr.last >= qr.first ? (qr.last - qr.first + 1) : 0;
   const int total = n_q * G;
+  const bool atomic_out = is_sum && n_seg > 1;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < S::kStages; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
     mbar_init(sp_full, 1);
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, 256);
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -341,16 +364,20 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tdV, tS + kk * 8, smem_desc_mnmajor_sw128(doa + kk * 2048, 16384), idesc_acc, (i | kk) != 0);
+          umma_ts(tdV, tS + (kk / 4) * 64 + (kk % 4) * 8, smem_desc_mnmajor_sw128(doa + kk * 2048, 16384), idesc_acc,
+                  (i | kk) != 0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tdK, tdP + kk * 8, smem_desc_mnmajor_sw128(qa + kk * 2048, 16384), idesc_acc, (i | kk) != 0);
+          umma_ts(tdK, tdP + (kk / 4) * 64 + (kk % 4) * 8, smem_desc_mnmajor_sw128(qa + kk * 2048, 16384), idesc_acc,
+                  (i | kk) != 0);
         umma_commit(&q_empty[stage]);
       }
       if (ok) umma_commit(acc_full);
     }
   } else {
+    // Two warpgroups share the 128 key rows: warps 2-5 take query columns 0..63, warps 6-9 columns 64..127.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const int k_local = kt * 128 + r;
     const bool valid = k_local < (is_sum ? sh.Ns : sh.Lk);
@@ -372,25 +399,28 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int i = 0; i < total; ++i) {
       const int qt = qr.first + i / G, head = kv_head * G + i % G;
       const bool got = mbar_wait(sp_full, i & 1, guard, kTimeoutAccFull);
-      // Stage LSE / delta of this query tile, double-buffered by iteration parity: the buffer written here
-      // was last read two iterations ago, and every thread has passed the barrier of the iteration between.
+      // Stage LSE (warpgroup 0) and delta (warpgroup 1) of this query tile, double-buffered by iteration parity:
+      // the buffer written here was last read two iterations ago, and every thread has passed the barrier between.
       float* lse_s = sLse + (i & 1) * 256;
       float* delta_s = lse_s + 128;
       {
         const int ql = qt * 128 + r;
         const long long sidx = ((long long)b * sh.Hq + head) * sh.Lq + ql;
         const bool qv = ql < sh.Lq;
-        lse_s[r] = qv ? p.lse[sidx] * 1.4426950408889634f : INFINITY;
-        delta_s[r] = qv ? p.delta[sidx] : 0.f;
+        if (half == 0) lse_s[r] = qv ? p.lse[sidx] * 1.4426950408889634f : INFINITY;
+        else delta_s[r] = qv ? p.delta[sidx] : 0.f;
       }
       (void)got;  // a failed wait has raised the CTA abort flag before returning
       wg_sync();
-      if (*abort_flag) { ok = false; break; }  // uniform across the warpgroup: read after the barrier
+      if (*abort_flag) { ok = false; break; }  // uniform across both warpgroups: read after the barrier
       tc_fence_after();
       const long long tq0 = (long long)sh.q_off + qt * 128;
       const int lo = (int)max(t_lo - tq0, 0LL), hi = (int)min(t_hi - tq0, 127LL);
+      // P^T and dS^T (bf16, two per column) overwrite scores this warpgroup has already read:
+      // chunk c goes to columns (c/2)*64 + (c%2)*16.
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t sr[32], dr[32];
         tmem_ld32(tS + lane_addr + c * 32, sr);
         tmem_ld32(tdP + lane_addr + c * 32, dr);
@@ -409,31 +439,55 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           pk[k] = pack_bf16x2(pr[0], pr[1]);
           dk[k] = pack_bf16x2(ds[0], ds[1]);
         }
-        tmem_st16(tS + lane_addr + c * 16, pk);
-        tmem_st16(tdP + lane_addr + c * 16, dk);
+        tmem_st16(tS + lane_addr + half * 64 + cc * 16, pk);
+        tmem_st16(tdP + lane_addr + half * 64 + cc * 16, dk);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(pds_full);
     }
-    bf16* dk_base = is_sum ? p.dks : p.dk;
-    bf16* dv_base = is_sum ? p.dvs : p.dv;
-    const long long dk_rs = is_sum ? p.dks_row_stride : p.dk_row_stride, dk_bs = is_sum ? p.dks_batch_stride : p.dk_batch_stride;
-    const long long dv_rs = is_sum ? p.dvs_row_stride : p.dv_row_stride, dv_bs = is_sum ? p.dvs_batch_stride : p.dv_batch_stride;
-    bf16* dkp = dk_base + (long long)b * dk_bs + (long long)k_local * dk_rs + (long long)kv_head * HD;
-    bf16* dvp = dv_base + (long long)b * dv_bs + (long long)k_local * dv_rs + (long long)kv_head * HD;
-    if (total == 0) {
-      if (valid) {
-        const uint4 z = make_uint4(0, 0, 0, 0);
+    // Epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK.
+    const bool do_k = half == 1;
+    const uint32_t t_acc = (do_k ? tdK : tdV) + lane_addr;
+    if (atomic_out) {
+      if (total > 0) {
+        if (ok) ok = mbar_wait(acc_full, 0, guard, kTimeoutAccFull);
+        if (ok) {
+          tc_fence_after();
+          float* base = (do_k ? p.dks32 : p.dvs32) + (((long long)b * sh.Ns + k_local) * sh.Hkv + kv_head) * HD;
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(t_acc + c * 32, o);
+            tmem_wait_ld();
+            if (valid) {
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) { reinterpret_cast<uint4*>(dkp)[i] = z; reinterpret_cast<uint4*>(dvp)[i] = z; }
+              for (int i = 0; i < 32; i += 4)
+                atomicAdd(reinterpret_cast<float4*>(base + c * 32 + i),
+                          make_float4(__uint_as_float(o[i]), __uint_as_float(o[i + 1]), __uint_as_float(o[i + 2]),
+                                      __uint_as_float(o[i + 3])));
+            }
+          }
+        }
       }
     } else {
-      if (ok) ok = mbar_wait(acc_full, 0, guard, kTimeoutAccFull);
-      if (ok) {
-        tc_fence_after();
-        store_acc_row<HD>(tdV + lane_addr, dvp, valid, 1.f);
-        store_acc_row<HD>(tdK + lane_addr, dkp, valid, 1.f);
+      bf16* gbase = is_sum ? (do_k ? p.dks : p.dvs) : (do_k ? p.dk : p.dv);
+      const long long rs = is_sum ? (do_k ? p.dks_row_stride : p.dvs_row_stride) : (do_k ? p.dk_row_stride : p.dv_row_stride);
+      const long long bs = is_sum ? (do_k ? p.dks_batch_stride : p.dvs_batch_stride)
+                                  : (do_k ? p.dk_batch_stride : p.dv_batch_stride);
+      bf16* dst = gbase + (long long)b * bs + (long long)k_local * rs + (long long)kv_head * HD;
+      if (total == 0) {
+        if (valid) {
+          const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int i = 0; i < HD / 8; ++i) reinterpret_cast<uint4*>(dst)[i] = z;
+        }
+      } else {
+        if (ok) ok = mbar_wait(acc_full, 0, guard, kTimeoutAccFull);
+        if (ok) {
+          tc_fence_after();
+          store_acc_row<HD>(t_acc, dst, valid, 1.f);
+        }
       }
     }
   }
@@ -464,13 +518,21 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUten
   dim3 g1((p.s.Lq + 127) / 128, p.s.Hq, p.s.B);
   k1<<<g1, kBwdThreads, BwdSmem<HD>::kTotal, st>>>(tq, tdo, tk, tv, tks, tvs, p);
   KSA_CHECK_CUDA(cudaGetLastError());
-  dim3 g2((p.s.Lk + 127) / 128 + (p.s.Ns + 127) / 128, p.s.Hkv, p.s.B);
+  dim3 g2((p.s.Lk + 127) / 128 + ((p.s.Ns + 127) / 128) * p.n_seg, p.s.Hkv, p.s.B);
   k2<<<g2, kBwdThreads, BwdSmem<HD>::kTotal, st>>>(tq, tdo, tk, tv, tks, tvs, p);
   KSA_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 
 }  // namespace ksa
+
+// Number of CTAs a summary key tile's query range is split into for Lq local query rows.  When it is > 1 the
+// caller passes zeroed fp32 buffers dks32/dvs32 [B, Ns, Hkv, HD] to ksa_attn_bwd and the same buffers to
+// ksa_summary_attn_bwd, which adds them into the bf16 summary-key gradients.
+KSA_API int ksa_attn_bwd_num_segments(int Lq) {
+  const int n_qtiles = (Lq + 127) / 128;
+  return (n_qtiles + ksa::kSumSeg - 1) / ksa::kSumSeg;
+}
 
 // Backward of ksa_attn_fwd.  Extra inputs: o, d_o [B, Lq, Hq, HD] (same strides), lse [B, Hq, Lq];
 // outputs dq (strides dq_rs/dq_bs), dk/dv (text keys), dks/dvs (summary keys), and delta [B, Hq, Lq] (scratch the
@@ -483,7 +545,7 @@ KSA_API int ksa_attn_bwd(const void* q, const void* k, const void* v, const void
                          long long o_bs, long long dq_rs, long long dq_bs, long long dk_rs, long long dk_bs,
                          long long dv_rs, long long dv_bs, long long dks_rs, long long dks_bs, long long dvs_rs,
                          long long dvs_bs, int q_off, int k_off, int s_off, int chunk, int n_sum, int window,
-                         int tok_window, float scale, void* stream) {
+                         int tok_window, float scale, void* dks32, void* dvs32, void* stream) {
   KSA_ENTER(q);
   using namespace ksa;
   KSA_REQUIRE(HD == 128 || HD == 64, "attn_bwd: head_dim %d unsupported (64 or 128)", HD);
@@ -514,6 +576,8 @@ KSA_API int ksa_attn_bwd(const void* q, const void* k, const void* v, const void
   p.dk_row_stride = dk_rs; p.dk_batch_stride = dk_bs; p.dv_row_stride = dv_rs; p.dv_batch_stride = dv_bs;
   p.dks = (bf16*)dks; p.dvs = (bf16*)dvs;
   p.dks_row_stride = dks_rs; p.dks_batch_stride = dks_bs; p.dvs_row_stride = dvs_rs; p.dvs_batch_stride = dvs_bs;
+  p.dks32 = (float*)dks32; p.dvs32 = (float*)dvs32;
+  p.n_seg = (Ns > 0 && dks32 != nullptr && dvs32 != nullptr) ? ksa_attn_bwd_num_segments(Lq) : 1;
   p.status = status_word();
   KSA_REQUIRE(p.status != nullptr, "could not allocate the status word");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

@@ -29,6 +29,8 @@ struct SumAttnArgs {
   const bf16* d_os; bf16* dqs; long long dqs_rs, dqs_bs;
   bf16* dk; bf16* dv; bf16* dks; bf16* dvs;
   long long dk_rs, dk_bs, dv_rs, dv_bs, dks_rs, dks_bs, dvs_rs, dvs_bs;
+  const float* dks32; const float* dvs32;  // optional fp32 partials [B, Nk_sum, Hkv, HD] that replace the bf16 base
+  int Ns_k;                                // rows of the summary key buffer (for the fp32 partial indexing)
 };
 
 __device__ __forceinline__ float dot_row(const float* q_s, const bf16* row, int HD) {
@@ -188,8 +190,14 @@ __global__ void __launch_bounds__(128) summary_attn_bwd_kernel(SumAttnArgs a) {
       pk = a.dks + (long long)b * a.dks_bs + (long long)(sum0 + kk - n_text) * a.dks_rs + (long long)kvh * HD + d;
       pv = a.dvs + (long long)b * a.dvs_bs + (long long)(sum0 + kk - n_text) * a.dvs_rs + (long long)kvh * HD + d;
     }
-    *pk = __float2bfloat16(__bfloat162float(*pk) + gk);
-    *pv = __float2bfloat16(__bfloat162float(*pv) + gv);
+    float base_k = __bfloat162float(*pk), base_v = __bfloat162float(*pv);
+    if (kk >= n_text && a.dks32) {  // the text-query backward left fp32 partial sums instead of bf16 values
+      const long long o = (((long long)b * a.Ns_k + (sum0 + kk - n_text)) * a.Hkv + kvh) * HD + d;
+      base_k = a.dks32[o];
+      base_v = a.dvs32[o];
+    }
+    *pk = __float2bfloat16(base_k + gk);
+    *pv = __float2bfloat16(base_v + gv);
   }
 }
 
@@ -229,7 +237,7 @@ KSA_API int ksa_summary_attn_bwd(const void* qs, const void* k, const void* v, c
                                  long long os_bs, long long dqs_rs, long long dqs_bs, long long dk_rs, long long dk_bs,
                                  long long dv_rs, long long dv_bs, long long dks_rs, long long dks_bs, long long dvs_rs,
                                  long long dvs_bs, int chunk, int n_sum, int chunk0, int k_off, int s_off, float scale,
-                                 void* stream) {
+                                 const void* dks32, const void* dvs32, int Ns_k, void* stream) {
   KSA_ENTER(qs);
   KSA_REQUIRE(HD % 8 == 0 && Hq % Hkv == 0 && n_sum > 0 && Nq % n_sum == 0, "summary_attn_bwd: bad shape");
   if (B == 0 || Nq == 0) return 0;
@@ -244,6 +252,7 @@ KSA_API int ksa_summary_attn_bwd(const void* qs, const void* k, const void* v, c
   a.dk = (bf16*)dk; a.dv = (bf16*)dv; a.dks = (bf16*)dks; a.dvs = (bf16*)dvs;
   a.dk_rs = dk_rs; a.dk_bs = dk_bs; a.dv_rs = dv_rs; a.dv_bs = dv_bs;
   a.dks_rs = dks_rs; a.dks_bs = dks_bs; a.dvs_rs = dvs_rs; a.dvs_bs = dvs_bs;
+  a.dks32 = (const float*)dks32; a.dvs32 = (const float*)dvs32; a.Ns_k = Ns_k;
   const int nq = (Hq / Hkv) * n_sum;
   const size_t smem = (size_t)nq * (2 * HD + 2 * (chunk + n_sum)) * sizeof(float);
   KSA_REQUIRE(smem <= 200 * 1024, "summary_attn_bwd: %zu bytes of shared memory needed (chunk %d, %d queries)", smem,

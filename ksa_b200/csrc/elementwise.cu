@@ -102,61 +102,88 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, c
 }
 
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres); per-CTA partial dw rows in `dw_partial`.
+// NVEC 16-byte vectors per thread cover D <= NVEC * 2048; R rows are in flight per iteration so that enough
+// loads are outstanding to hide DRAM latency, and their R row reductions share one pair of barriers.
+template <int NVEC, int R>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                    const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
                    float* __restrict__ dw_partial, int rows, int D) {
-  __shared__ float red[32];
-  float wv[kNormMaxVec][8];
-  float dw[kNormMaxVec][8];
+  __shared__ float red[R][8];
+  float wv[NVEC][8];
+  float dw[NVEC][8];
 #pragma unroll
-  for (int i = 0; i < kNormMaxVec; ++i) {
+  for (int i = 0; i < NVEC; ++i) {
     const int c = (i * kNormThreads + threadIdx.x) * 8;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dw[i][j] = 0.f;
+    for (int j = 0; j < 8; ++j) { dw[i][j] = 0.f; wv[i][j] = 0.f; }
     if (c < D) load8(w + c, wv[i]);
   }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const long long base = (long long)row * D;
-    const float rstd = rstd_in[row];
-    float xh[kNormMaxVec][8], g[kNormMaxVec][8];
-    float dot = 0.f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R) {
+    float xh[R][NVEC][8], g[R][NVEC][8];
+    float dot[R];
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
-      const int c = (i * kNormThreads + threadIdx.x) * 8;
-      if (c < D) {
-        float xv[8], dyv[8];
-        load8(x + base + c, xv);
-        load8(dy + base + c, dyv);
+    for (int r = 0; r < R; ++r) {
+      dot[r] = 0.f;
+      const int row = row0 + r;
+      const float rstd = row < rows ? rstd_in[row] : 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] = xv[j] * rstd;
-          g[i][j] = dyv[j] * wv[i][j];
-          dot += g[i][j] * xh[i][j];
-          dw[i][j] += dyv[j] * xh[i][j];
+      for (int i = 0; i < NVEC; ++i) {
+        const int c = (i * kNormThreads + threadIdx.x) * 8;
+        if (row < rows && c < D) {
+          float xv[8], dyv[8];
+          load8(x + (long long)row * D + c, xv);
+          load8(dy + (long long)row * D + c, dyv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            xh[r][i][j] = xv[j] * rstd;
+            g[r][i][j] = dyv[j] * wv[i][j];
+            dot[r] += g[r][i][j] * xh[r][i][j];
+            dw[i][j] += dyv[j] * xh[r][i][j];
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { xh[r][i][j] = 0.f; g[r][i][j] = 0.f; }
         }
       }
+      dot[r] = warp_sum(dot[r]);
     }
-    dot = block_sum<kNormThreads>(dot, red) / (float)D;
+    __syncthreads();
+    if (lane == 0) {
 #pragma unroll
-    for (int i = 0; i < kNormMaxVec; ++i) {
-      const int c = (i * kNormThreads + threadIdx.x) * 8;
-      if (c < D) {
-        float o[8];
+      for (int r = 0; r < R; ++r) red[r][warp] = dot[r];
+    }
+    __syncthreads();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * dot);
-        if (dres) {
-          float r[8];
-          load8(dres + base + c, r);
+    for (int r = 0; r < R; ++r) {
+      float t = 0.f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += r[j];
+      for (int k = 0; k < kNormThreads / 32; ++k) t += red[r][k];
+      const float mean = t / (float)D;
+      const int row = row0 + r;
+      if (row >= rows) continue;
+      const float rstd = rstd_in[row];
+#pragma unroll
+      for (int i = 0; i < NVEC; ++i) {
+        const int c = (i * kNormThreads + threadIdx.x) * 8;
+        if (c < D) {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = rstd * (g[r][i][j] - xh[r][i][j] * mean);
+          if (dres) {
+            float rr[8];
+            load8(dres + (long long)row * D + c, rr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += rr[j];
+          }
+          store8(dx + (long long)row * D + c, o);
         }
-        store8(dx + base + c, o);
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < kNormMaxVec; ++i) {
+  for (int i = 0; i < NVEC; ++i) {
     const int c = (i * kNormThreads + threadIdx.x) * 8;
     if (c < D) {
       float* p = dw_partial + (long long)blockIdx.x * D + c;
@@ -166,14 +193,23 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
   }
 }
 
-// dw[c] (+)= sum over partial rows.
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nparts, int D,
-                                       int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+// dw[c] (+)= sum over partial rows.  Block = 32 columns x 8 row groups.
+__global__ void __launch_bounds__(256)
+colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nparts, int D, int accumulate) {
+  __shared__ float red[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(long long)p * D + c];
-  dw[c] = accumulate ? dw[c] + s : s;
+  if (c < D)
+    for (int p = ty; p < nparts; p += 8) s += partial[(long long)p * D + c];
+  red[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][tx];
+    dw[c] = accumulate ? dw[c] + t : t;
+  }
 }
 
 // ------------------------------------------------------------------------------ QK-norm + RoPE
@@ -539,19 +575,33 @@ KSA_API int ksa_rmsnorm_fwd(const void* x, const void* delta, const void* w, voi
 // Number of partial rows the backward writes: the caller sizes `dw_partial` as [ksa_rmsnorm_bwd_parts(rows), D] fp32.
 KSA_API int ksa_rmsnorm_bwd_parts(int rows) { return rows < 592 ? (rows > 0 ? rows : 1) : 592; }
 
+template <int NVEC, int R>
+static int launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rstd, const void* dres,
+                              void* dx, void* dw_partial, int parts, int rows, int D, cudaStream_t st) {
+  int blocks = (rows + R - 1) / R;
+  if (blocks > parts) blocks = parts;
+  // rows beyond `blocks` partial rows stay untouched; zero-fill is not needed because colsum reads `blocks` rows only
+  rmsnorm_bwd_kernel<NVEC, R><<<blocks, kNormThreads, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
+                                                               (const float*)rstd, (const bf16*)dres, (bf16*)dx,
+                                                               (float*)dw_partial, rows, D);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return blocks;
+}
+
 KSA_API int ksa_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rstd, const void* dres, void* dx,
                             void* dw_partial, void* dw, int accumulate_dw, int rows, int D, void* stream) {
   KSA_ENTER(dy);
   KSA_REQUIRE(D % 8 == 0 && D <= kNormThreads * 8 * kNormMaxVec, "rmsnorm: D=%d unsupported", D);
   if (rows == 0) return 0;
   const int parts = ksa_rmsnorm_bwd_parts(rows);
-  rmsnorm_bwd_kernel<<<parts, kNormThreads, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
-                                                             (const float*)rstd, (const bf16*)dres, (bf16*)dx,
-                                                             (float*)dw_partial, rows, D);
-  KSA_CHECK_CUDA(cudaGetLastError());
+  int used;
+  if (D <= 2048) used = launch_rmsnorm_bwd<1, 4>(dy, x, w, rstd, dres, dx, dw_partial, parts, rows, D, ST(stream));
+  else if (D <= 4096) used = launch_rmsnorm_bwd<2, 2>(dy, x, w, rstd, dres, dx, dw_partial, parts, rows, D, ST(stream));
+  else used = launch_rmsnorm_bwd<4, 1>(dy, x, w, rstd, dres, dx, dw_partial, parts, rows, D, ST(stream));
+  if (used < 0) return used;
   if (dw) {
-    colsum_partials_kernel<<<(D + 255) / 256, 256, 0, ST(stream)>>>((const float*)dw_partial, (float*)dw, parts, D,
-                                                                    accumulate_dw);
+    colsum_partials_kernel<<<(D + 31) / 32, 256, 0, ST(stream)>>>((const float*)dw_partial, (float*)dw, used, D,
+                                                                  accumulate_dw);
     KSA_CHECK_CUDA(cudaGetLastError());
   }
   return 0;

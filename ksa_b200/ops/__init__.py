@@ -462,6 +462,10 @@ class _KsaAttentionFn(torch.autograd.Function):
             dks = torch.empty((B, Ns_k, Hkv, D), dtype=q.dtype, device=q.device)
             dvs = torch.empty_like(dks)
         delta = torch.empty_like(lse)
+        part_k = part_v = None
+        if Ns_k > 0 and os_ is not None and Lq > 0 and _lib.attn_bwd_num_segments(Lq) > 1:
+            part_k = torch.zeros((B, Ns_k, Hkv, D), dtype=torch.float32, device=q.device)
+            part_v = torch.zeros_like(part_k)
         if Lq == 0:  # summary-only call: the text-query kernels do not run, start the key grads at zero
             dk.zero_(); dv.zero_()
             if dks is not None:
@@ -477,7 +481,7 @@ class _KsaAttentionFn(torch.autograd.Function):
                   qrs, qbs, krs, kbs, vrs, vbs, ksrs, ksbs, vsrs, vsbs, o.stride(1), o.stride(0),
                   dq.stride(1), dq.stride(0), dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0),
                   dksrs, dksbs, dksrs, dksbs, q_off, k_off, s_off, chunk, max(n_sum, 1), window, tok_window,
-                  float(scale))
+                  float(scale), part_k, part_v)
         dqs = None
         if os_ is not None:
             Nq = qs.shape[1]
@@ -488,7 +492,7 @@ class _KsaAttentionFn(torch.autograd.Function):
                       B, Hq, Hkv, D, Nq, seq_len, qsrs, qsbs, krs, kbs, vrs, vbs, ksrs, ksbs, vsrs, vsbs,
                       os_.stride(1), os_.stride(0), dqs.stride(1), dqs.stride(0), dk.stride(1), dk.stride(0),
                       dv.stride(1), dv.stride(0), dksrs, dksbs, dksrs, dksbs, chunk, n_sum, q_off // chunk,
-                      k_off, s_off, float(scale))
+                      k_off, s_off, float(scale), part_k, part_v, Ns_k)
         return (dq, dk, dv, dqs, dks, dvs) + (None,) * 9
 
 
@@ -590,23 +594,27 @@ class _PackedAttentionFn(torch.autograd.Function):
         o = out[:B * L].view(B, L, Hq, D)
         do = dout[:B * L].view(B, L, Hq, D)
         delta = torch.empty_like(lse)
+        part_k = part_v = None
         if Ns > 0:
             qs, ks, vs = _packed_views(qkv, B, Ns, Hq, Hkv, D, B * L)
             dqs, dks, dvs = _packed_views(dqkv, B, Ns, Hq, Hkv, D, B * L)
+            if _lib.attn_bwd_num_segments(L) > 1:
+                part_k = torch.zeros((B, Ns, Hkv, D), dtype=torch.float32, device=qkv.device)
+                part_v = torch.zeros_like(part_k)
         else:
             qs = ks = vs = dqs = dks = dvs = None
         _lib.call("ksa_attn_bwd", q, k, v, ks, vs, o, do, lse, delta, dq, dk, dv, dks, dvs,
                   B, Hq, Hkv, D, L, L, Ns,
                   rs, L * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs, Hq * D, L * Hq * D,
                   drs, L * drs, drs, L * drs, drs, L * drs, drs, Ns * drs, drs, Ns * drs,
-                  0, 0, 0, chunk, max(n_sum, 1), window, tok_window, float(scale))
+                  0, 0, 0, chunk, max(n_sum, 1), window, tok_window, float(scale), part_k, part_v)
         if Ns > 0:
             os_ = out[B * L:].view(B, Ns, Hq, D)
             dos = dout[B * L:].view(B, Ns, Hq, D)
             _lib.call("ksa_summary_attn_bwd", qs, k, v, ks, vs, os_, dos, lse_s, dqs, dk, dv, dks, dvs,
                       B, Hq, Hkv, D, Ns, L, rs, Ns * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs,
                       Hq * D, Ns * Hq * D, drs, Ns * drs, drs, L * drs, drs, L * drs, drs, Ns * drs, drs, Ns * drs,
-                      chunk, n_sum, 0, 0, 0, float(scale))
+                      chunk, n_sum, 0, 0, 0, float(scale), part_k, part_v, Ns)
         return (dqkv,) + (None,) * 11
 
 

@@ -35,9 +35,9 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_adamw": [P, P, P, P, P, L, P, F, F, F, F, F, P, P],
     "ksa_cast_f32_bf16": [P, P, L, P],
     "ksa_attn_fwd": [P] * 7 + [I] * 7 + [L] * 12 + [I] * 7 + [F, P],
-    "ksa_attn_bwd": [P] * 14 + [I] * 7 + [L] * 22 + [I] * 7 + [F, P],
+    "ksa_attn_bwd": [P] * 14 + [I] * 7 + [L] * 22 + [I] * 7 + [F, P, P, P],
     "ksa_summary_attn_fwd": [P] * 7 + [I] * 6 + [L] * 12 + [I] * 5 + [F, P],
-    "ksa_summary_attn_bwd": [P] * 13 + [I] * 6 + [L] * 22 + [I] * 5 + [F, P],
+    "ksa_summary_attn_bwd": [P] * 13 + [I] * 6 + [L] * 22 + [I] * 5 + [F, P, P, I, P],
     "ksa_decode_attn": [P] * 7 + [I] * 7 + [L] * 8 + [F, P],
     "ksa_kv_cache_append": [P] * 6 + [I] * 6 + [L] * 6 + [P],
     "ksa_peer_reduce_adamw": [P, P, P, P, P, P, I, L, L, P, F, F, F, F, F, F, P, P],
@@ -69,6 +69,8 @@ def load() -> ctypes.CDLL:
     lib.ksa_read_status.restype = I
     lib.ksa_rmsnorm_bwd_parts.argtypes = [I]
     lib.ksa_rmsnorm_bwd_parts.restype = I
+    lib.ksa_attn_bwd_num_segments.argtypes = [I]
+    lib.ksa_attn_bwd_num_segments.restype = I
     for name, sig in _SIGNATURES.items():
         fn = getattr(lib, name, None)
         if fn is not None:
@@ -140,6 +142,10 @@ def check_status(clear: bool = True) -> None:
     st = load().ksa_read_status(1 if clear else 0)
     if st != 0:
         raise RuntimeError(f"kernel status {st}: {_STATUS_TEXT.get(st, 'unknown')}")
+
+
+def attn_bwd_num_segments(lq: int) -> int:
+    return load().ksa_attn_bwd_num_segments(lq)
 
 
 def rmsnorm_bwd_parts(rows: int) -> int:

@@ -82,9 +82,13 @@ class TrainEngine:
         self.units: List[Unit] = []
         self._build_units()
         self.hyper = torch.zeros(4, dtype=torch.float32, device=self.device)
-        self._hyper_host = torch.zeros(4, dtype=torch.float32)
+        # ring of pinned staging slots: the host may run several (graph-replayed) steps ahead of the device,
+        # so a slot is reused only after the copy that read it has completed
+        self._hyper_ring = torch.zeros(32, 4, dtype=torch.float32)
+        self._hyper_events: List[Optional[torch.cuda.Event]] = [None] * 32
+        self._hyper_slot = 0
         if self.device.type == "cuda":
-            self._hyper_host = self._hyper_host.pin_memory()
+            self._hyper_ring = self._hyper_ring.pin_memory()
         self.grad_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._graphs: Dict[tuple, "_CapturedStep"] = {}
 
@@ -149,12 +153,20 @@ class TrainEngine:
 
     def _write_hyper(self) -> None:
         t = self.step_count + 1
-        h = self._hyper_host
+        slot = self._hyper_slot
+        self._hyper_slot = (slot + 1) % len(self._hyper_events)
+        if self._hyper_events[slot] is not None:
+            self._hyper_events[slot].synchronize()
+        h = self._hyper_ring[slot]
         h[0] = self.current_lr()
         h[1] = 1.0 - self.beta1 ** t
         h[2] = 1.0 - self.beta2 ** t
         h[3] = 1.0 / (self.grad_accum_steps * max(self.world_size, 1))
         self.hyper.copy_(h, non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self._hyper_events[slot] = ev
 
     # ------------------------------------------------------------------ gradients
     def zero_grad(self) -> None:

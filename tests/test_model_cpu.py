@@ -60,7 +60,7 @@ def test_two_stream_attention_equals_interleaved():
     (qt, qs), (kt, ks), (vt, vs) = lay.split(q), lay.split(k), lay.split(v)
     ot, os_ = ref.ksa_attention(qt, kt, vt, qs, ks, vs, C, S, W)
     o_t_ref, o_s_ref = lay.split(o)
-    assert torch.allclose(ot, o_t_ref, atol=1e-5) and torch.allclose(os_, o_s_ref, atol=1e-5)
+    assert torch.allclose(ot, o_t_ref, atol=1e-4) and torch.allclose(os_, o_s_ref, atol=1e-4)
 
 
 def test_position_ids_match_reference_rule():
