@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--preset", default="qwen3-1.9b-ksa")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--comm", default=None, choices=["fused", "collective"],
+                    help="multi-GPU back end: fused P2P kernels (default) or NCCL collectives (A/B baseline)")
     return ap.parse_args()
 
 
@@ -133,7 +135,7 @@ def run_ours(args) -> dict:
 
     if world > 1:
         from ksa_b200.parallel.fsdp import FsdpEngine as Engine
-        extra = dict(world_size=world, rank=rank)
+        extra = dict(world_size=world, rank=rank, comm=args.comm)
     else:
         from ksa_b200.training.engine import TrainEngine as Engine
         extra = {}
@@ -148,7 +150,8 @@ def run_ours(args) -> dict:
     dev_in = [t.to(dev) for t in host_in]
     dev_lab = [t.to(dev) for t in host_lab]
 
-    step_fn = engine.train_step if args.no_graph else engine.graphed_step
+    use_graph = not args.no_graph and world == 1
+    step_fn = engine.graphed_step if use_graph else engine.train_step
 
     def barrier():
         if world > 1:
@@ -208,7 +211,7 @@ def run_ours(args) -> dict:
                    "parallelism": f"fsdp{world}" if world > 1 else "single", "layers": cfg.num_layers,
                    "chunk": cfg.summary_chunk_size, "window_chunks": 8, "optimizer": "AdamW fp32 master",
                    "l2": "working set (weights+optimizer state+activations, >30 GB) exceeds L2; no explicit flush",
-                   "cuda_graph": not args.no_graph},
+                   "cuda_graph": use_graph, "comm": getattr(engine, "comm", "none")},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
@@ -216,6 +219,8 @@ def run_ours(args) -> dict:
         "loss_first": loss0, "loss_last": last,
     }
     if world > 1:
+        if hasattr(engine, "close"):
+            engine.close()
         dist.destroy_process_group()
     return out if rank == 0 else None
 

@@ -201,6 +201,179 @@ __global__ void __launch_bounds__(128) summary_attn_bwd_kernel(SumAttnArgs a) {
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Fast path: one CTA per (chunk, KV head) stages the chunk's keys and values (text rows + summary rows) in shared
+// memory once, padded by one 32-bit word per row so that "thread = key" reads are bank-conflict free, and serves
+// all G*S summary queries of the group from there.
+constexpr int kSumThreads = 128;
+
+struct SumSmemLayout {
+  int nk_max, row_words;  // keys per chunk (C+S); 32-bit words per padded row (HD/2 + 1)
+  __host__ __device__ size_t kv_bytes() const { return (size_t)nk_max * row_words * 4; }
+};
+
+__device__ __forceinline__ void stage_rows(uint32_t* dst, int row_words, const bf16* text, long long t_rs,
+                                           const bf16* sum, long long s_rs, int n_text, int nk, int text0, int sum0,
+                                           int HD) {
+  const int vec_per_row = HD / 8;
+  for (int idx = threadIdx.x; idx < nk * vec_per_row; idx += kSumThreads) {
+    const int kk = idx / vec_per_row, v = idx % vec_per_row;
+    const bf16* row = key_row(text, t_rs, sum, s_rs, kk, n_text, text0, sum0);
+    const uint4 u = *reinterpret_cast<const uint4*>(row + v * 8);
+    uint32_t* d = dst + kk * row_words + v * 4;
+    d[0] = u.x; d[1] = u.y; d[2] = u.z; d[3] = u.w;
+  }
+}
+
+__device__ __forceinline__ float dot_smem(const float* q_s, const uint32_t* row, int HD) {
+  float acc = 0.f;
+  for (int w = 0; w < HD / 2; ++w) {
+    const float2 f = unpack_bf16x2(row[w]);
+    acc += q_s[2 * w] * f.x + q_s[2 * w + 1] * f.y;
+  }
+  return acc;
+}
+
+// grid (local chunks, Hkv, B); dynamic smem: K rows | V rows | q[nq][HD] | p[nq][nk_max]
+__global__ void __launch_bounds__(kSumThreads) summary_attn_fwd_fast_kernel(SumAttnArgs a, SumSmemLayout lay) {
+  extern __shared__ uint32_t smw[];
+  __shared__ float red[4];
+  const int G = a.Hq / a.Hkv, S = a.n_sum, HD = a.HD, nq = G * S;
+  uint32_t* k_s = smw;
+  uint32_t* v_s = k_s + lay.nk_max * lay.row_words;
+  float* q_s = reinterpret_cast<float*>(v_s + lay.nk_max * lay.row_words);
+  float* p_s = q_s + nq * HD;
+  const int ci = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int cg = a.chunk0 + ci;
+  const int n_text = min(a.chunk, a.L - cg * a.chunk);
+  const int text0 = cg * a.chunk - a.k_off, sum0 = cg * S - a.s_off;
+  const int nk_all = n_text + S;
+  stage_rows(k_s, lay.row_words, a.k + (long long)b * a.k_bs + (long long)kvh * HD, a.k_rs,
+             a.ks + (long long)b * a.ks_bs + (long long)kvh * HD, a.ks_rs, n_text, nk_all, text0, sum0, HD);
+  stage_rows(v_s, lay.row_words, a.v + (long long)b * a.v_bs + (long long)kvh * HD, a.v_rs,
+             a.vs + (long long)b * a.vs_bs + (long long)kvh * HD, a.vs_rs, n_text, nk_all, text0, sum0, HD);
+  for (int idx = threadIdx.x; idx < nq * HD; idx += kSumThreads) {
+    const int qi = idx / HD, d = idx % HD;
+    const int head = kvh * G + qi / S, row = ci * S + qi % S;
+    q_s[idx] = __bfloat162float(a.qs[(long long)b * a.qs_bs + (long long)row * a.qs_rs + (long long)head * HD + d]);
+  }
+  __syncthreads();
+  for (int qi = 0; qi < nq; ++qi) {
+    const int j = qi % S, head = kvh * G + qi / S, row = ci * S + j;
+    const int nk = n_text + j + 1;
+    float mx = -INFINITY;
+    for (int kk = threadIdx.x; kk < nk; kk += kSumThreads) {
+      const float sc = dot_smem(q_s + qi * HD, k_s + kk * lay.row_words, HD) * a.scale;
+      p_s[qi * lay.nk_max + kk] = sc;
+      mx = fmaxf(mx, sc);
+    }
+    mx = block_reduce_max128(mx, red);
+    float sum = 0.f;
+    for (int kk = threadIdx.x; kk < nk; kk += kSumThreads) {
+      const float pr = __expf(p_s[qi * lay.nk_max + kk] - mx);
+      p_s[qi * lay.nk_max + kk] = pr;
+      sum += pr;
+    }
+    sum = block_reduce_sum128(sum, red);
+    const float inv = 1.f / sum;
+    for (int d = threadIdx.x; d < HD; d += kSumThreads) {
+      float acc = 0.f;
+      const bf16* vcol = reinterpret_cast<const bf16*>(v_s) + d;
+      for (int kk = 0; kk < nk; ++kk) acc += p_s[qi * lay.nk_max + kk] * __bfloat162float(vcol[kk * lay.row_words * 2]);
+      a.os[(long long)b * a.os_bs + (long long)row * a.os_rs + (long long)head * HD + d] = __float2bfloat16(acc * inv);
+    }
+    if (threadIdx.x == 0 && a.lse) a.lse[((long long)b * a.Hq + head) * a.Nq + row] = mx + __logf(sum);
+  }
+}
+
+// grid (local chunks, Hkv, B); dynamic smem: K rows | V rows | q[nq][HD] | do[nq][HD] | p[nq][nk_max] | ds[nq][nk_max]
+__global__ void __launch_bounds__(kSumThreads) summary_attn_bwd_fast_kernel(SumAttnArgs a, SumSmemLayout lay) {
+  extern __shared__ uint32_t smw[];
+  __shared__ float red[4];
+  const int G = a.Hq / a.Hkv, S = a.n_sum, HD = a.HD, nq = G * S;
+  uint32_t* k_s = smw;
+  uint32_t* v_s = k_s + lay.nk_max * lay.row_words;
+  float* q_s = reinterpret_cast<float*>(v_s + lay.nk_max * lay.row_words);
+  float* do_s = q_s + nq * HD;
+  float* p_s = do_s + nq * HD;
+  float* ds_s = p_s + nq * lay.nk_max;
+  const int ci = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int cg = a.chunk0 + ci;
+  const int n_text = min(a.chunk, a.L - cg * a.chunk);
+  const int text0 = cg * a.chunk - a.k_off, sum0 = cg * S - a.s_off;
+  const int nk_all = n_text + S;
+  stage_rows(k_s, lay.row_words, a.k + (long long)b * a.k_bs + (long long)kvh * HD, a.k_rs,
+             a.ks + (long long)b * a.ks_bs + (long long)kvh * HD, a.ks_rs, n_text, nk_all, text0, sum0, HD);
+  stage_rows(v_s, lay.row_words, a.v + (long long)b * a.v_bs + (long long)kvh * HD, a.v_rs,
+             a.vs + (long long)b * a.vs_bs + (long long)kvh * HD, a.vs_rs, n_text, nk_all, text0, sum0, HD);
+  __syncthreads();
+  for (int qi = 0; qi < nq; ++qi) {
+    const int j = qi % S, head = kvh * G + qi / S, row = ci * S + j;
+    const long long qoff = (long long)b * a.qs_bs + (long long)row * a.qs_rs + (long long)head * HD;
+    const long long ooff = (long long)b * a.os_bs + (long long)row * a.os_rs + (long long)head * HD;
+    float part = 0.f;
+    for (int d = threadIdx.x; d < HD; d += kSumThreads) {
+      q_s[qi * HD + d] = __bfloat162float(a.qs[qoff + d]);
+      const float g_o = __bfloat162float(a.d_os[ooff + d]);
+      do_s[qi * HD + d] = g_o;
+      part += g_o * __bfloat162float(a.os[ooff + d]);
+    }
+    const float delta = block_reduce_sum128(part, red);
+    const float lse = a.lse[((long long)b * a.Hq + head) * a.Nq + row];
+    const int nk = n_text + j + 1;
+    for (int kk = threadIdx.x; kk < lay.nk_max; kk += kSumThreads) {
+      float pr = 0.f, ds = 0.f;
+      if (kk < nk) {
+        const float sc = dot_smem(q_s + qi * HD, k_s + kk * lay.row_words, HD) * a.scale;
+        pr = __expf(sc - lse);
+        const float dp = dot_smem(do_s + qi * HD, v_s + kk * lay.row_words, HD);
+        ds = pr * (dp - delta) * a.scale;
+      }
+      p_s[qi * lay.nk_max + kk] = pr;
+      ds_s[qi * lay.nk_max + kk] = ds;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < HD; d += kSumThreads) {
+      float acc = 0.f;
+      const bf16* kcol = reinterpret_cast<const bf16*>(k_s) + d;
+      for (int kk = 0; kk < nk; ++kk) acc += ds_s[qi * lay.nk_max + kk] * __bfloat162float(kcol[kk * lay.row_words * 2]);
+      a.dqs[(long long)b * a.dqs_bs + (long long)row * a.dqs_rs + (long long)head * HD + d] = __float2bfloat16(acc);
+    }
+  }
+  __syncthreads();
+  // dK[kk][d] += sum_qi ds[qi][kk] q[qi][d];  dV[kk][d] += sum_qi p[qi][kk] do[qi][d]   (two columns per thread)
+  const int pairs = HD / 2;
+  for (int idx = threadIdx.x; idx < nk_all * pairs; idx += kSumThreads) {
+    const int kk = idx / pairs, d = (idx % pairs) * 2;
+    float gk0 = 0.f, gk1 = 0.f, gv0 = 0.f, gv1 = 0.f;
+    for (int qi = 0; qi < nq; ++qi) {
+      const float dsv = ds_s[qi * lay.nk_max + kk], pv = p_s[qi * lay.nk_max + kk];
+      gk0 += dsv * q_s[qi * HD + d]; gk1 += dsv * q_s[qi * HD + d + 1];
+      gv0 += pv * do_s[qi * HD + d]; gv1 += pv * do_s[qi * HD + d + 1];
+    }
+    bf16 *pk, *pv;
+    float bk0, bk1, bv0, bv1;
+    if (kk < n_text) {
+      pk = a.dk + (long long)b * a.dk_bs + (long long)(text0 + kk) * a.dk_rs + (long long)kvh * HD + d;
+      pv = a.dv + (long long)b * a.dv_bs + (long long)(text0 + kk) * a.dv_rs + (long long)kvh * HD + d;
+    } else {
+      pk = a.dks + (long long)b * a.dks_bs + (long long)(sum0 + kk - n_text) * a.dks_rs + (long long)kvh * HD + d;
+      pv = a.dvs + (long long)b * a.dvs_bs + (long long)(sum0 + kk - n_text) * a.dvs_rs + (long long)kvh * HD + d;
+    }
+    if (kk >= n_text && a.dks32) {
+      const long long o = (((long long)b * a.Ns_k + (sum0 + kk - n_text)) * a.Hkv + kvh) * HD + d;
+      bk0 = a.dks32[o]; bk1 = a.dks32[o + 1]; bv0 = a.dvs32[o]; bv1 = a.dvs32[o + 1];
+    } else {
+      const float2 fk = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pk));
+      const float2 fv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pv));
+      bk0 = fk.x; bk1 = fk.y; bv0 = fv.x; bv1 = fv.y;
+    }
+    *reinterpret_cast<uint32_t*>(pk) = pack_bf16x2(bk0 + gk0, bk1 + gk1);
+    *reinterpret_cast<uint32_t*>(pv) = pack_bf16x2(bv0 + gv0, bv1 + gv1);
+  }
+}
+
 }  // namespace ksa
 
 using namespace ksa;
@@ -221,6 +394,22 @@ KSA_API int ksa_summary_attn_fwd(const void* qs, const void* k, const void* v, c
   a.os = (bf16*)os; a.os_rs = os_rs; a.os_bs = os_bs; a.lse = (float*)lse;
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.HD = HD; a.Nq = Nq; a.L = L; a.chunk = chunk; a.n_sum = n_sum;
   a.chunk0 = chunk0; a.k_off = k_off; a.s_off = s_off; a.scale = scale;
+  {
+    const int nq = (Hq / Hkv) * n_sum;
+    SumSmemLayout lay{chunk + n_sum, HD / 2 + 1};
+    const size_t fast_smem = 2 * lay.kv_bytes() + (size_t)nq * (HD + lay.nk_max) * sizeof(float);
+    if (fast_smem <= 160 * 1024) {
+      static bool attr = false;
+      if (!attr) {
+        KSA_CHECK_CUDA(cudaFuncSetAttribute(summary_attn_fwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        attr = true;
+      }
+      dim3 fgrid(Nq / n_sum, Hkv, B);
+      summary_attn_fwd_fast_kernel<<<fgrid, kSumThreads, fast_smem, reinterpret_cast<cudaStream_t>(stream)>>>(a, lay);
+      KSA_CHECK_CUDA(cudaGetLastError());
+      return 0;
+    }
+  }
   const size_t smem = (size_t)(HD + chunk + n_sum) * sizeof(float);
   KSA_REQUIRE(smem <= 48 * 1024, "summary_attn_fwd: chunk %d too large for the SIMT kernel", chunk);
   dim3 grid(Nq / n_sum, Hq, B);
@@ -254,6 +443,21 @@ KSA_API int ksa_summary_attn_bwd(const void* qs, const void* k, const void* v, c
   a.dks_rs = dks_rs; a.dks_bs = dks_bs; a.dvs_rs = dvs_rs; a.dvs_bs = dvs_bs;
   a.dks32 = (const float*)dks32; a.dvs32 = (const float*)dvs32; a.Ns_k = Ns_k;
   const int nq = (Hq / Hkv) * n_sum;
+  {
+    SumSmemLayout lay{chunk + n_sum, HD / 2 + 1};
+    const size_t fast_smem = 2 * lay.kv_bytes() + (size_t)nq * (2 * HD + 2 * lay.nk_max) * sizeof(float);
+    if (fast_smem <= 160 * 1024) {
+      static bool fattr = false;
+      if (!fattr) {
+        KSA_CHECK_CUDA(cudaFuncSetAttribute(summary_attn_bwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        fattr = true;
+      }
+      dim3 fgrid(Nq / n_sum, Hkv, B);
+      summary_attn_bwd_fast_kernel<<<fgrid, kSumThreads, fast_smem, reinterpret_cast<cudaStream_t>(stream)>>>(a, lay);
+      KSA_CHECK_CUDA(cudaGetLastError());
+      return 0;
+    }
+  }
   const size_t smem = (size_t)nq * (2 * HD + 2 * (chunk + n_sum)) * sizeof(float);
   KSA_REQUIRE(smem <= 200 * 1024, "summary_attn_bwd: %zu bytes of shared memory needed (chunk %d, %d queries)", smem,
               chunk, nq);

@@ -1,0 +1,156 @@
+// Communication kernels over NVLink / NVSwitch peer memory (P2P loads and stores issued from inside the
+// kernels; no TMA multicast, no library collective):
+//
+//   ksa_peer_gather         pull all-gather: every rank copies the other ranks' shards of a flat bf16 buffer out of
+//                           their memory into its own copy (FSDP parameter all-gather; TP all-gather).
+//   ksa_peer_reduce_adamw   reduce-scatter fused with the optimizer: the owner of a shard reads that shard of every
+//                           rank's fp32 gradient buffer over NVLink, sums and scales it, clips by value, applies
+//                           AdamW to its fp32 master weights and moments, writes the refreshed bf16 weights into its
+//                           shard of the compute buffer and accumulates sum(g^2) for the gradient-norm metric.
+//                           Replaces NCCL reduce-scatter -> foreach AdamW -> cast of the reference
+//                           (muse/training/distributed.py:232-287, recipes/pretrain_kai_summary_unified.py:1045-1053).
+//   ksa_signal_set / wait   release-store a step counter into every peer's signal pad / bounded acquire-wait on it.
+//
+// The same device routines run as "communication CTAs" inside the GEMM kernel (gemm.cu), which is how the
+// parameter all-gather of the next FSDP unit and the reduce-scatter + AdamW of the previous one overlap with the
+// tensor-core tiles of the current GEMM in one launch.
+//
+// Every wait on a peer flag is bounded (about a second) and reports through the status word.
+#include "comm.cuh"
+#include "host.h"
+
+#include <string.h>
+
+namespace ksa {
+
+__global__ void __launch_bounds__(kCommThreads) peer_gather_kernel(GatherJob job, int* status) {
+  run_gather_job(job, blockIdx.x, gridDim.x, status);
+}
+
+__global__ void __launch_bounds__(kCommThreads) peer_reduce_adamw_kernel(ReduceAdamwJob job, int* status) {
+  run_reduce_adamw_job(job, blockIdx.x, gridDim.x, status);
+}
+
+__global__ void signal_set_kernel(SignalTargets t, const uint32_t* epoch_ptr, uint32_t add) {
+  if (threadIdx.x < t.n && t.ptr[threadIdx.x] != nullptr) {
+    __threadfence_system();
+    st_release_sys(t.ptr[threadIdx.x], epoch_target(epoch_ptr, add));
+  }
+}
+
+__global__ void signal_wait_kernel(const uint32_t* flags, int n, const uint32_t* epoch_ptr, uint32_t add, int* status) {
+  if (threadIdx.x < n) flag_wait_ge(flags + threadIdx.x, epoch_target(epoch_ptr, add), status, kTimeoutPeerFlag, true);
+}
+
+}  // namespace ksa
+
+using namespace ksa;
+
+// ------------------------------------------------------------------------------------------ memory + IPC
+KSA_API int ksa_symm_alloc(void** out, long long bytes) {
+  KSA_REQUIRE(bytes > 0, "symm_alloc: bytes must be positive");
+  void* p = nullptr;
+  KSA_CHECK_CUDA(cudaMalloc(&p, (size_t)bytes));
+  KSA_CHECK_CUDA(cudaMemset(p, 0, (size_t)bytes));
+  *out = p;
+  return 0;
+}
+KSA_API int ksa_symm_free(void* p) {
+  if (p) KSA_CHECK_CUDA(cudaFree(p));
+  return 0;
+}
+// handle_out: 64 bytes
+KSA_API int ksa_ipc_get_handle(void* p, void* handle_out) {
+  cudaIpcMemHandle_t h;
+  KSA_CHECK_CUDA(cudaIpcGetMemHandle(&h, p));
+  static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
+  memcpy(handle_out, &h, sizeof(h));
+  return 0;
+}
+KSA_API int ksa_ipc_open_handle(const void* handle, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* p = nullptr;
+  KSA_CHECK_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *out = p;
+  return 0;
+}
+KSA_API int ksa_ipc_close(void* p) {
+  if (p) KSA_CHECK_CUDA(cudaIpcCloseMemHandle(p));
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------ kernels
+// peers: world pointers to the ranks' copies of the flat buffer (peers[rank] = own copy).  Shard r of every copy is
+// elements [r*shard_elems, (r+1)*shard_elems); the call copies every shard r != rank from peers[r] into peers[rank].
+// ready_flags (optional): world flags in OWN memory; shard r is copied once ready_flags[r] >= *epoch_ptr + epoch_add (epoch_ptr: device uint32, may be null = 0).
+KSA_API int ksa_peer_gather(const void* const* peers, int world, int rank, long long shard_elems, int elem_bytes,
+                            const void* ready_flags, const void* epoch_ptr, unsigned epoch_add, int ctas, void* stream) {
+  KSA_ENTER(peers[rank]);
+  KSA_REQUIRE(world >= 1 && world <= kMaxPeers, "peer_gather: world %d out of range (max %d)", world, kMaxPeers);
+  KSA_REQUIRE((shard_elems * elem_bytes) % 16 == 0, "peer_gather: shard bytes must be a multiple of 16");
+  if (world == 1) return 0;
+  GatherJob job{};
+  for (int r = 0; r < world; ++r) job.peers[r] = static_cast<const uint8_t*>(peers[r]);
+  job.world = world; job.rank = rank; job.shard_bytes = shard_elems * elem_bytes;
+  job.ready_flags = static_cast<const uint32_t*>(ready_flags);
+  job.epoch_ptr = static_cast<const uint32_t*>(epoch_ptr); job.epoch_add = epoch_add;
+  int* status = status_word();
+  KSA_REQUIRE(status != nullptr, "could not allocate the status word");
+  if (ctas <= 0) ctas = 16;
+  peer_gather_kernel<<<ctas, kCommThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(job, status);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// grads: world pointers to the ranks' fp32 gradient buffers (full unit); this rank owns [shard_lo, shard_lo + n).
+// master / m / v: this rank's fp32 shard (n elements); out_bf16: OWN full compute buffer (the shard region is written).
+// hyper: device [lr, 1-b1^t, 1-b2^t, grad_scale].  ready_flags (optional): world flags in own memory; the reduction
+// starts once all of them are >= *epoch_ptr + epoch_add (every rank has finished writing this unit's gradients).
+KSA_API int ksa_peer_reduce_adamw(const void* const* grads, int world, int rank, long long shard_lo, long long n,
+                                  void* master, void* m, void* v, void* out_bf16, const void* hyper, float beta1,
+                                  float beta2, float eps, float weight_decay, float clip_value, void* sumsq,
+                                  const void* ready_flags, const void* epoch_ptr, unsigned epoch_add, int ctas,
+                                  void* stream) {
+  KSA_ENTER(master);
+  KSA_REQUIRE(world >= 1 && world <= kMaxPeers, "peer_reduce_adamw: world %d out of range (max %d)", world, kMaxPeers);
+  KSA_REQUIRE(n % 4 == 0 && shard_lo % 4 == 0, "peer_reduce_adamw: shard offset/size must be multiples of 4");
+  if (n == 0) return 0;
+  ReduceAdamwJob job{};
+  for (int r = 0; r < world; ++r) job.grads[r] = static_cast<const float*>(grads[r]);
+  job.world = world; job.rank = rank; job.shard_lo = shard_lo; job.n = n;
+  job.master = (float*)master; job.m = (float*)m; job.v = (float*)v; job.out_bf16 = (bf16*)out_bf16;
+  job.hyper = (const float*)hyper; job.beta1 = beta1; job.beta2 = beta2; job.eps = eps;
+  job.weight_decay = weight_decay; job.clip_value = clip_value; job.sumsq = (float*)sumsq;
+  job.ready_flags = static_cast<const uint32_t*>(ready_flags);
+  job.epoch_ptr = static_cast<const uint32_t*>(epoch_ptr); job.epoch_add = epoch_add;
+  int* status = status_word();
+  KSA_REQUIRE(status != nullptr, "could not allocate the status word");
+  if (ctas <= 0) ctas = 32;
+  peer_reduce_adamw_kernel<<<ctas, kCommThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(job, status);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Store *epoch_ptr + epoch_add (release, system scope) to n flag addresses (own and peer memory), after all prior work of the stream.
+KSA_API int ksa_signal_set(const void* const* flag_ptrs, int n, const void* epoch_ptr, unsigned epoch_add, void* stream) {
+  KSA_REQUIRE(n >= 1 && n <= kMaxPeers, "signal_set: n %d out of range", n);
+  SignalTargets t{};
+  t.n = n;
+  for (int i = 0; i < n; ++i) t.ptr[i] = static_cast<uint32_t*>(const_cast<void*>(flag_ptrs[i]));
+  signal_set_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(t, static_cast<const uint32_t*>(epoch_ptr), epoch_add);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Bounded wait until n consecutive flags in own memory are >= *epoch_ptr + epoch_add (a timeout is reported via the status word).
+KSA_API int ksa_signal_wait(const void* flags, int n, const void* epoch_ptr, unsigned epoch_add, void* stream) {
+  KSA_ENTER(flags);
+  KSA_REQUIRE(n >= 1 && n <= 32, "signal_wait: n %d out of range", n);
+  int* status = status_word();
+  KSA_REQUIRE(status != nullptr, "could not allocate the status word");
+  signal_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>((const uint32_t*)flags, n,
+                                                                            static_cast<const uint32_t*>(epoch_ptr), epoch_add, status);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,153 @@
+// Device routines for communication over peer memory (weak loads ordered after a system-scope acquire of the
+// producer's flag; no read-only/non-coherent path, since the same addresses are rewritten every step), shared by the standalone kernels (comm.cu) and by the
+// communication CTAs of the GEMM kernel (gemm.cu).  All transfers are plain P2P loads/stores of 16 bytes per thread
+// through pointers into other GPUs' memory; waits on peer-written flags are bounded.
+#pragma once
+#include "common.cuh"
+
+namespace ksa {
+
+constexpr int kMaxPeers = 8;
+constexpr int kCommThreads = 512;
+
+struct GatherJob {
+  const uint8_t* peers[kMaxPeers];  // every rank's copy of the flat buffer; peers[rank] is the local (destination) copy
+  int world, rank;
+  long long shard_bytes;
+  const uint32_t* ready_flags;  // optional, own memory: shard r may be read once ready_flags[r] >= target
+  const uint32_t* epoch_ptr;    // target = (epoch_ptr ? *epoch_ptr : 0) + epoch_add; a device-resident epoch keeps
+  uint32_t epoch_add;           // a captured CUDA graph valid from step to step
+};
+
+struct ReduceAdamwJob {
+  const float* grads[kMaxPeers];  // every rank's full fp32 gradient buffer of the unit
+  int world, rank;
+  long long shard_lo, n;          // this rank owns elements [shard_lo, shard_lo + n)
+  float* master; float* m; float* v;  // this rank's shard state
+  bf16* out_bf16;                 // own full compute buffer (written at shard_lo + i), may be null
+  const float* hyper;             // [lr, 1-beta1^t, 1-beta2^t, grad_scale]
+  float beta1, beta2, eps, weight_decay, clip_value;
+  float* sumsq;                   // optional accumulator of sum(g^2) over the shard
+  const uint32_t* ready_flags;    // optional, own memory: all `world` flags must reach the target first
+  const uint32_t* epoch_ptr;      // target = (epoch_ptr ? *epoch_ptr : 0) + epoch_add
+  uint32_t epoch_add;
+};
+
+struct SignalTargets {
+  uint32_t* ptr[kMaxPeers];
+  int n;
+};
+
+__device__ __forceinline__ uint32_t epoch_target(const uint32_t* epoch_ptr, uint32_t add) {
+  return (epoch_ptr ? *reinterpret_cast<const volatile uint32_t*>(epoch_ptr) : 0u) + add;
+}
+
+__device__ __forceinline__ uint4 ld_peer_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_peer_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// CTA `cta` of `nctas` copies its slice of every remote shard.  Returns false if a flag wait timed out.
+__device__ __forceinline__ bool run_gather_job(const GatherJob& j, int cta, int nctas, int* status) {
+  __shared__ int s_ok;
+  const long long vecs = j.shard_bytes / 16;
+  uint8_t* dst_base = const_cast<uint8_t*>(j.peers[j.rank]);
+  const uint32_t target = epoch_target(j.epoch_ptr, j.epoch_add);
+  for (int step = 1; step < j.world; ++step) {
+    const int r = (j.rank + step) % j.world;  // start with the next rank so that ranks do not all hit one peer at once
+    if (j.ready_flags) {
+      if (threadIdx.x == 0) s_ok = flag_wait_ge(j.ready_flags + r, target, status, kTimeoutPeerFlag, true) ? 1 : 0;
+      __syncthreads();
+      const int ok = s_ok;
+      __syncthreads();
+      if (!ok) return false;
+    }
+    const uint8_t* src = j.peers[r] + (long long)r * j.shard_bytes;
+    uint8_t* dst = dst_base + (long long)r * j.shard_bytes;
+    const long long stride = (long long)nctas * blockDim.x;
+    long long i = (long long)cta * blockDim.x + threadIdx.x;
+    // four independent 16-byte loads in flight per thread
+    for (; i + 3 * stride < vecs; i += 4 * stride) {
+      const uint4 a = ld_peer_16(src + i * 16), b = ld_peer_16(src + (i + stride) * 16);
+      const uint4 c = ld_peer_16(src + (i + 2 * stride) * 16), d = ld_peer_16(src + (i + 3 * stride) * 16);
+      *reinterpret_cast<uint4*>(dst + i * 16) = a;
+      *reinterpret_cast<uint4*>(dst + (i + stride) * 16) = b;
+      *reinterpret_cast<uint4*>(dst + (i + 2 * stride) * 16) = c;
+      *reinterpret_cast<uint4*>(dst + (i + 3 * stride) * 16) = d;
+    }
+    for (; i < vecs; i += stride) *reinterpret_cast<uint4*>(dst + i * 16) = ld_peer_16(src + i * 16);
+  }
+  return true;
+}
+
+// CTA `cta` of `nctas` reduces + updates its slice of the owned shard.
+__device__ __forceinline__ bool run_reduce_adamw_job(const ReduceAdamwJob& j, int cta, int nctas, int* status) {
+  __shared__ int s_ok;
+  __shared__ float s_red[32];
+  if (j.ready_flags) {
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < j.world &&
+        !flag_wait_ge(j.ready_flags + threadIdx.x, epoch_target(j.epoch_ptr, j.epoch_add), status, kTimeoutPeerFlag, true))
+      s_ok = 0;
+    __syncthreads();
+    if (!s_ok) return false;
+  }
+  const float lr = j.hyper[0], bc1 = j.hyper[1], bc2 = j.hyper[2], gscale = j.hyper[3];
+  const long long nvec = j.n / 4;
+  float sq = 0.f;
+  for (long long i = (long long)cta * blockDim.x + threadIdx.x; i < nvec; i += (long long)nctas * blockDim.x) {
+    const long long e = j.shard_lo + i * 4;
+    float4 g = ld_peer_f4(j.grads[j.rank] + e);
+#pragma unroll
+    for (int s = 1; s < kMaxPeers; ++s) {
+      if (s < j.world) {
+        const int r = (j.rank + s) % j.world;
+        const float4 t = ld_peer_f4(j.grads[r] + e);
+        g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+      }
+    }
+    float4 p4 = reinterpret_cast<float4*>(j.master)[i];
+    float4 m4 = reinterpret_cast<float4*>(j.m)[i];
+    float4 v4 = reinterpret_cast<float4*>(j.v)[i];
+    float gg[4] = {g.x, g.y, g.z, g.w}, p[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w},
+          vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float gk = gg[k] * gscale;
+      sq += gk * gk;
+      if (j.clip_value > 0.f) gk = fminf(fmaxf(gk, -j.clip_value), j.clip_value);
+      mm[k] = j.beta1 * mm[k] + (1.f - j.beta1) * gk;
+      vv[k] = j.beta2 * vv[k] + (1.f - j.beta2) * gk * gk;
+      const float denom = sqrtf(vv[k] / bc2) + j.eps;
+      p[k] = p[k] * (1.f - lr * j.weight_decay) - lr * (mm[k] / bc1) / denom;
+    }
+    reinterpret_cast<float4*>(j.master)[i] = make_float4(p[0], p[1], p[2], p[3]);
+    reinterpret_cast<float4*>(j.m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(j.v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    if (j.out_bf16)
+      *reinterpret_cast<uint2*>(j.out_bf16 + e) = make_uint2(pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]));
+  }
+  if (j.sumsq) {
+    sq = warp_sum(sq);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = threadIdx.x < (blockDim.x >> 5) ? s_red[threadIdx.x] : 0.f;
+      t = warp_sum(t);
+      if (threadIdx.x == 0) atomicAdd(j.sumsq, t);
+    }
+  }
+  return true;
+}
+
+}  // namespace ksa

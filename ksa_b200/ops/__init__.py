@@ -62,6 +62,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     _lib.call("ksa_gemm_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
               int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate),
               float(alpha), int(sm_limit))
+    _lib.gemm_launched()
     return out
 
 

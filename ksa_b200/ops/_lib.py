@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 from pathlib import Path
 from typing import Dict, Optional, Sequence
 
@@ -40,10 +41,17 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_summary_attn_bwd": [P] * 13 + [I] * 6 + [L] * 22 + [I] * 5 + [F, P, P, I, P],
     "ksa_decode_attn": [P] * 7 + [I] * 7 + [L] * 8 + [F, P],
     "ksa_kv_cache_append": [P] * 6 + [I] * 6 + [L] * 6 + [P],
-    "ksa_peer_reduce_adamw": [P, P, P, P, P, P, I, L, L, P, F, F, F, F, F, F, P, P],
-    "ksa_peer_gather": [P, P, I, I, L, P, I, P],
-    "ksa_signal_set": [P, I, P],
-    "ksa_signal_wait": [P, I, I, P],
+    "ksa_peer_gather": [P, I, I, L, I, P, P, ctypes.c_uint, I, P],
+    "ksa_peer_reduce_adamw": [P, I, I, L, L, P, P, P, P, P, F, F, F, F, F, P, P, P, ctypes.c_uint, I, P],
+    "ksa_gemm_attach_gather": [P, I, I, L, I, P, P, ctypes.c_uint, I],
+    "ksa_gemm_attach_reduce_adamw": [P, I, I, L, L, P, P, P, P, P, F, F, F, F, F, P, P, P, ctypes.c_uint, I],
+    "ksa_signal_set": [P, I, P, ctypes.c_uint, P],
+    "ksa_signal_wait": [P, I, P, ctypes.c_uint, P],
+    "ksa_symm_alloc": [P, L],
+    "ksa_symm_free": [P],
+    "ksa_ipc_get_handle": [P, P],
+    "ksa_ipc_open_handle": [P, P],
+    "ksa_ipc_close": [P],
 }
 
 
@@ -116,6 +124,34 @@ def call(name: str, *args) -> None:
     if rc != 0:
         raise RuntimeError(f"{name} failed ({rc}): {lib.ksa_last_error().decode()}")
     _launch_count += _KERNELS_PER_CALL.get(name, 1)
+
+
+def call_nostream(name: str, *args) -> None:
+    """Call an entry point that takes no stream argument (set-up routines, attach_* calls)."""
+    lib = load()
+    rc = getattr(lib, name)(*[_ptr(a) for a in args])
+    if rc != 0:
+        raise RuntimeError(f"{name} failed ({rc}): {lib.ksa_last_error().decode()}")
+
+
+_tls = threading.local()
+
+
+def attach_to_next_gemm(name: str, args: tuple, after=None) -> None:
+    """Attach a communication job (``ksa_gemm_attach_gather`` / ``ksa_gemm_attach_reduce_adamw``) to the next GEMM
+    launched from this thread; ``after()`` runs right after that launch (e.g. to signal the peers)."""
+    call_nostream(name, *args)
+    _tls.after_gemm = after
+    _tls.attached = True
+
+
+def gemm_launched() -> None:
+    """Called by ``ops.gemm`` after each launch: runs the callback of an attached communication job."""
+    if getattr(_tls, "attached", False):
+        _tls.attached = False
+        cb, _tls.after_gemm = getattr(_tls, "after_gemm", None), None
+        if cb is not None:
+            cb()
 
 
 def launch_count() -> int:

@@ -1,0 +1,291 @@
+"""FSDP (ZeRO-2 style) on top of :class:`ksa_b200.training.engine.TrainEngine`.
+
+Sharding follows the reference (``muse/training/distributed.py:232-287``): one unit per decoder layer plus the
+remaining parameters (here split into an ``embed`` and a ``head`` unit), bf16 compute weights resident on every
+rank (``reshard_after_forward=False``, the reference scripts' default), fp32 master weights, Adam moments and
+gradient reduction in fp32, each rank owning ``1/world`` of every unit's flat buffer.
+
+Two communication back ends behind one engine:
+
+``comm="fused"`` (GPUs, the product path)
+    Compute and gradient buffers live in symmetric memory (``ksa_b200.parallel.symm``).
+    * Gradient reduce-scatter + cast/scale + AdamW is ONE kernel on the shard owner that reads every rank's fp32
+      gradients over NVLink, and it rides along as communication CTAs of the first backward GEMM of the next unit,
+      so the transfer and the optimizer overlap with backward tile by tile.
+    * The parameter all-gather of unit ``u+1`` rides along with the first GEMM (QKV projection) of unit ``u`` in
+      forward: communication CTAs pull the peers' updated bf16 shards over NVLink while the other CTAs run the
+      tensor-core tiles.  The first two units are pulled by the stand-alone gather kernel at the start of the step.
+    * Cross-GPU ordering uses per-(unit, rank) flags in symmetric signal pads carrying the step number; every wait
+      is bounded and reports through the library's status word.
+
+``comm="collective"`` (any backend, incl. gloo on CPU; the NCCL baseline for A/B runs)
+    ``reduce_scatter`` -> AdamW on the shard -> ``all_gather``, per unit, after backward.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..ops import _lib
+from ..training.engine import TrainEngine, Unit
+
+
+class _Boundary(torch.autograd.Function):
+    """Identity on (x, delta) whose backward reports that everything downstream of it has run its backward."""
+
+    @staticmethod
+    def forward(ctx, engine, tag, x, delta):
+        ctx.engine, ctx.tag = engine, tag
+        ctx.has_delta = delta is not None
+        return (x.view_as(x), delta.view_as(delta)) if delta is not None else (x.view_as(x), None)
+
+    @staticmethod
+    def backward(ctx, gx, gd):
+        ctx.engine._backward_reached(ctx.tag)
+        return None, None, gx, (gd if ctx.has_delta else None)
+
+
+class FsdpEngine(TrainEngine):
+    def __init__(self, model: nn.Module, *args, world_size: int = 1, rank: int = 0, group=None, comm: Optional[str] = None,
+                 comm_ctas: int = 8, **kw):
+        self.group = group
+        dev = kw.get("device") or next(model.parameters()).device
+        self.comm = comm or ("fused" if torch.device(dev).type == "cuda" and world_size > 1 else "collective")
+        self.comm_ctas = comm_ctas
+        self._symm = []
+        super().__init__(model, *args, world_size=world_size, rank=rank, **kw)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._epoch_ring = torch.zeros(32, 1, dtype=torch.int32)
+        if self.device.type == "cuda":
+            self._epoch_ring = self._epoch_ring.pin_memory()
+        self._grad_sq_reduced = None
+        if self.comm == "fused":
+            from .symm import SignalPad
+            n = len(self.units) * self.world_size
+            self.pad_grads = SignalPad(n, group, self.device)
+            self.pad_weights = SignalPad(n, group, self.device)
+            self._install_hooks()
+
+    # ------------------------------------------------------------------ storage
+    def _allocate_storage(self, units: List[Unit]) -> None:
+        if self.comm != "fused":
+            return super()._allocate_storage(units)
+        from .symm import SymmetricBuffer
+        item = torch.empty((), dtype=self.param_dtype).element_size()
+        total = sum(u.size for u in units)
+        self._sym_compute = SymmetricBuffer(total * item, self.group, self.device)
+        self._sym_grad = SymmetricBuffer(total * 4, self.group, self.device)
+        self._symm += [self._sym_compute, self._sym_grad]
+        off = 0
+        for u in units:
+            u.compute = self._sym_compute.view(self.param_dtype, off * item, u.size)
+            u.grad = self._sym_grad.view(torch.float32, off * 4, u.size)
+            u.compute_ptrs = self._sym_compute.offset_ptr_array(off * item)
+            u.grad_ptrs = self._sym_grad.offset_ptr_array(off * 4)
+            self._alloc_shard_state(u)
+            off += u.size
+
+    # ------------------------------------------------------------------ hooks
+    def _install_hooks(self) -> None:
+        layers = list(self.model.get_layers_to_shard())
+        self._layer_unit = {}
+        names = [u.name for u in self.units]
+        for i, layer in enumerate(layers):
+            ui = names.index(f"layer{i}")
+            self._layer_unit[i] = ui
+            layer.register_forward_pre_hook(self._make_pre_hook(ui))
+        if layers and "head" in names:
+            layers[-1].register_forward_hook(self._make_post_hook(names.index("head")))
+
+    def _make_pre_hook(self, ui: int):
+        def hook(module, args):
+            x, delta = args[0], args[1]
+            if self._overlap_active:
+                nxt = ui + 1
+                if nxt < len(self.units) and nxt >= 2:
+                    self._attach_gather(nxt)
+                if torch.is_grad_enabled() and x.requires_grad:
+                    x, delta = _Boundary.apply(self, ui, x, delta)
+            return (x, delta) + tuple(args[2:])
+        return hook
+
+    def _make_post_hook(self, head_ui: int):
+        def hook(module, args, output):
+            if self._overlap_active and torch.is_grad_enabled() and output[0].requires_grad:
+                return _Boundary.apply(self, ("before", head_ui), output[0], output[1])
+            return output
+        return hook
+
+    _overlap_active = False
+
+    # ------------------------------------------------------------------ fused communication
+    def _unit_flag_index(self, ui: int) -> int:
+        return ui * self.world_size
+
+    def _attach_gather(self, ui: int) -> None:
+        u = self.units[ui]
+        shard = u.size // self.world_size
+        item = u.compute.element_size()
+        _lib.attach_to_next_gemm("ksa_gemm_attach_gather", (
+            u.compute_ptrs, self.world_size, self.rank, shard, item,
+            self.pad_weights.local_ptr(self._unit_flag_index(ui)), self.epoch, 0, self.comm_ctas))
+
+    def _gather_now(self, ui: int) -> None:
+        u = self.units[ui]
+        _lib.call("ksa_peer_gather", u.compute_ptrs, self.world_size, self.rank, u.size // self.world_size,
+                  u.compute.element_size(), self.pad_weights.local_ptr(self._unit_flag_index(ui)), self.epoch, 0, 32)
+
+    def _reduce_args(self, u: Unit, ui: int):
+        return (u.grad_ptrs, self.world_size, self.rank, u.shard_lo, u.shard_hi - u.shard_lo, u.master, u.exp_avg,
+                u.exp_avg_sq, u.compute if self.param_dtype != torch.float32 else None, self.hyper, self.beta1,
+                self.beta2, self.eps, self.weight_decay, self.clip_value, self.grad_sq,
+                self.pad_grads.local_ptr(self._unit_flag_index(ui)), self.epoch, 1)
+
+    def _signal(self, pad, ui: int) -> None:
+        pad.set_on_all(self._unit_flag_index(ui) + self.rank, self.epoch, 1)
+
+    def _unit_grads_ready(self, ui: int, can_attach: bool) -> None:
+        """All of this rank's gradients of unit ``ui`` have been launched: tell the peers, then reduce + update."""
+        u = self.units[ui]
+        for s in u.slots:  # parameters that received no gradient this window contribute zeros
+            if not getattr(s.param, "_grad_written", False):
+                s.param.main_grad.zero_()
+                s.param._grad_written = True
+        self._signal(self.pad_grads, ui)
+        if can_attach:
+            _lib.attach_to_next_gemm("ksa_gemm_attach_reduce_adamw", self._reduce_args(u, ui) + (self.comm_ctas,),
+                                     after=lambda: self._signal(self.pad_weights, ui))
+        else:
+            _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 32)
+            self._signal(self.pad_weights, ui)
+        self._done_units.add(ui)
+
+    def _backward_reached(self, tag) -> None:
+        if not self._is_boundary_step:
+            return
+        if isinstance(tag, tuple):          # ("before", head): the head's gradients are complete
+            self._unit_grads_ready(tag[1], can_attach=True)
+            return
+        ui = tag                            # backward of layer unit `ui` has been launched
+        first_layer_unit = min(self._layer_unit.values())
+        self._unit_grads_ready(ui, can_attach=ui != first_layer_unit)
+
+    # ------------------------------------------------------------------ step
+    def _write_hyper(self) -> None:
+        super()._write_hyper()
+        slot = (self._hyper_slot - 1) % len(self._hyper_events)   # same slot and event as the hyper-parameters
+        self._epoch_ring[slot, 0] = self.step_count
+        self.epoch.copy_(self._epoch_ring[slot], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self._hyper_events[slot] = ev
+
+    def forward_backward(self, tokens, labels, **kw):
+        if self.comm != "fused":
+            return super().forward_backward(tokens, labels, **kw)
+        self._is_boundary_step = self.micro_step + 1 == self.grad_accum_steps
+        self._done_units = set()
+        self._overlap_active = True
+        try:
+            if self.micro_step == 0:          # refreshed weights of the first two units; later ones ride on GEMMs
+                self._gather_now(0)
+                if len(self.units) > 1:
+                    self._gather_now(1)
+            return super().forward_backward(tokens, labels, **kw)
+        finally:
+            self._overlap_active = False
+
+    def train_step(self, tokens, labels, **kw):
+        self._write_hyper()   # the optimizer runs inside backward and gathers read the epoch: both must be there first
+        if self.micro_step == 0:
+            self.zero_grad()
+        if tokens.device != self.device:
+            tokens = tokens.to(self.device, non_blocking=True)
+            labels = labels.to(self.device, non_blocking=True)
+        if self.micro_step == 0:
+            self.grad_sq.zero_()
+        loss = self.forward_backward(tokens, labels, **kw)
+        self.micro_step += 1
+        if self.micro_step == self.grad_accum_steps:
+            self.optimizer_step()
+            self.step_count += 1
+            self.micro_step = 0
+        return loss
+
+    def optimizer_step(self) -> None:
+        self._grad_sq_reduced = None
+        if self.comm == "fused":
+            self._collect_autograd_grads()
+            for ui in range(len(self.units) - 1, -1, -1):   # whatever backward did not reach (embed; all, if hooks are off)
+                if ui not in self._done_units:
+                    self._unit_grads_ready(ui, can_attach=False)
+            return
+        self._collect_autograd_grads()
+        self.grad_sq.zero_()
+        for unit in reversed(self.units):
+            self._reduce_and_update(unit)
+
+    def _reduce_and_update(self, unit: Unit) -> None:
+        """Collective path: reduce-scatter -> AdamW on the shard -> all-gather of the refreshed weights."""
+        w = self.world_size
+        lo, hi = unit.shard_lo, unit.shard_hi
+        if w > 1:
+            backend = dist.get_backend(self.group)
+            if backend == "nccl":
+                shard = torch.empty(hi - lo, dtype=torch.float32, device=self.device)
+                dist.reduce_scatter_tensor(shard, unit.grad, group=self.group)
+            else:
+                dist.all_reduce(unit.grad, group=self.group)
+                shard = unit.grad[lo:hi]
+        else:
+            shard = unit.grad[lo:hi]
+        out = unit.compute[lo:hi] if self.param_dtype != torch.float32 else None
+        ops.adamw_step(unit.master, shard, unit.exp_avg, unit.exp_avg_sq, out, self.hyper, self.beta1, self.beta2,
+                       self.eps, self.weight_decay, self.clip_value, self.grad_sq)
+        if self.param_dtype == torch.float32:
+            unit.compute[lo:hi].copy_(unit.master)
+        if w > 1:
+            if dist.get_backend(self.group) == "nccl":
+                dist.all_gather_into_tensor(unit.compute, unit.compute[lo:hi].clone(), group=self.group)
+            else:
+                parts = [torch.empty(hi - lo, dtype=unit.compute.dtype, device=self.device) for _ in range(w)]
+                dist.all_gather(parts, unit.compute[lo:hi].contiguous(), group=self.group)
+                unit.compute.copy_(torch.cat(parts))
+
+    def grad_norm(self) -> torch.Tensor:
+        """Global gradient norm: shard-local sums of squares, one scalar all-reduce (``muse/training/common.py:273-326``)."""
+        if self._grad_sq_reduced is None:
+            t = self.grad_sq.clone()
+            if self.world_size > 1:
+                dist.all_reduce(t, group=self.group)
+            self._grad_sq_reduced = t
+        return self._grad_sq_reduced.sqrt()
+
+    def graphed_step(self, tokens, labels):
+        if self.comm == "fused":
+            raise NotImplementedError("graph capture of the fused multi-GPU step is not enabled yet; use train_step")
+        return super().graphed_step(tokens, labels)
+
+    def refresh_compute_from_master(self) -> None:
+        for u in self.units:
+            u.compute[u.shard_lo:u.shard_hi].copy_(u.master)
+            if self.world_size > 1:
+                parts = [torch.empty(u.shard_hi - u.shard_lo, dtype=u.compute.dtype, device=self.device)
+                         for _ in range(self.world_size)]
+                dist.all_gather(parts, u.compute[u.shard_lo:u.shard_hi].contiguous(), group=self.group)
+                u.compute.copy_(torch.cat(parts))
+
+    def close(self) -> None:
+        if self.comm == "fused":
+            torch.cuda.synchronize(self.device)
+            self.pad_grads.close()
+            self.pad_weights.close()
+            for s in self._symm:
+                s.close()
+            self._symm = []

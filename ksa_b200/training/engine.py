@@ -103,24 +103,36 @@ class TrainEngine:
             ps = [(names[id(p)], p) for p in m.parameters()]
             taken.update(id(p) for _, p in ps)
             units.append((f"layer{i}", ps))
+        # what is left is split in two: parameters used before the layers (embeddings) and after them (norm, head)
         root = [(n, p) for n, p in model.named_parameters() if id(p) not in taken]
-        units.append(("root", root))
-        return units
+        embed = [(n, p) for n, p in root if "embedding" in n]
+        head = [(n, p) for n, p in root if "embedding" not in n]
+        out = []
+        if embed:
+            out.append(("embed", embed))
+        out += units
+        if head:
+            out.append(("head", head))
+        return out
 
     def _shard_range(self, size: int) -> Tuple[int, int]:
         per = size // self.world_size
         return self.rank * per, (self.rank + 1) * per
 
     def _build_units(self) -> None:
-        dev, pd = self.device, self.param_dtype
+        dev = self.device
+        planned: List[Unit] = []
         for uname, ps in self._unit_modules():
             unit = Unit(uname)
             off = 0
             for n, p in ps:
                 unit.slots.append(ParamSlot(n, p, off, p.numel(), p.shape))
                 off += _round_up(p.numel(), _ALIGN)
-            unit.size = _round_up(off, _ALIGN * max(self.world_size, 1))
-            self._alloc_unit(unit)
+            unit.size = _round_up(max(off, _ALIGN), _ALIGN * max(self.world_size, 1))
+            unit.shard_lo, unit.shard_hi = self._shard_range(unit.size)
+            planned.append(unit)
+        self._allocate_storage(planned)
+        for unit in planned:
             with torch.no_grad():
                 for s in unit.slots:
                     src = s.param.detach().to(device=dev, dtype=torch.float32).reshape(-1)
@@ -131,12 +143,17 @@ class TrainEngine:
                     s.param._grad_written = False
             self.units.append(unit)
 
-    def _alloc_unit(self, unit: Unit) -> None:
+    def _allocate_storage(self, units: List[Unit]) -> None:
+        """Allocate compute / gradient / optimizer-state buffers of every unit (overridden for symmetric memory)."""
         dev = self.device
-        unit.compute = torch.zeros(unit.size, dtype=self.param_dtype, device=dev)
-        unit.grad = torch.zeros(unit.size, dtype=torch.float32, device=dev)
-        unit.shard_lo, unit.shard_hi = self._shard_range(unit.size)
+        for unit in units:
+            unit.compute = torch.zeros(unit.size, dtype=self.param_dtype, device=dev)
+            unit.grad = torch.zeros(unit.size, dtype=torch.float32, device=dev)
+            self._alloc_shard_state(unit)
+
+    def _alloc_shard_state(self, unit: Unit) -> None:
         n = unit.shard_hi - unit.shard_lo
+        dev = self.device
         unit.master = torch.zeros(n, dtype=torch.float32, device=dev)
         unit.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         unit.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)

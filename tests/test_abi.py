@@ -16,11 +16,14 @@ def _kind_c(arg: str) -> str:
         return "L"
     if "float" in arg:
         return "F"
+    if "unsigned" in arg:
+        return "U"
     return "I"
 
 
 def _kind_py(t) -> str:
-    return {ctypes.c_void_p: "P", ctypes.c_int: "I", ctypes.c_longlong: "L", ctypes.c_float: "F"}[t]
+    return {ctypes.c_void_p: "P", ctypes.c_int: "I", ctypes.c_longlong: "L", ctypes.c_float: "F",
+            ctypes.c_uint: "U"}[t]
 
 
 def test_signatures_match_prototypes():
