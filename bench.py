@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--comm", default=None, choices=["fused", "collective"],
                     help="multi-GPU back end: fused P2P kernels (default) or NCCL collectives (A/B baseline)")
+    ap.add_argument("--overlap", default="stream", choices=["stream", "gemm"],
+                    help="fused back end: communication kernels on a side stream, or as CTAs inside GEMM launches")
     return ap.parse_args()
 
 
@@ -135,7 +137,7 @@ def run_ours(args) -> dict:
 
     if world > 1:
         from ksa_b200.parallel.fsdp import FsdpEngine as Engine
-        extra = dict(world_size=world, rank=rank, comm=args.comm)
+        extra = dict(world_size=world, rank=rank, comm=args.comm, overlap=args.overlap)
     else:
         from ksa_b200.training.engine import TrainEngine as Engine
         extra = {}
@@ -211,7 +213,8 @@ def run_ours(args) -> dict:
                    "parallelism": f"fsdp{world}" if world > 1 else "single", "layers": cfg.num_layers,
                    "chunk": cfg.summary_chunk_size, "window_chunks": 8, "optimizer": "AdamW fp32 master",
                    "l2": "working set (weights+optimizer state+activations, >30 GB) exceeds L2; no explicit flush",
-                   "cuda_graph": use_graph, "comm": getattr(engine, "comm", "none")},
+                   "cuda_graph": use_graph, "comm": getattr(engine, "comm", "none"),
+                   "overlap": getattr(engine, "overlap", "none")},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},

@@ -104,37 +104,60 @@ __device__ __forceinline__ bool run_reduce_adamw_job(const ReduceAdamwJob& j, in
   const float lr = j.hyper[0], bc1 = j.hyper[1], bc2 = j.hyper[2], gscale = j.hyper[3];
   const long long nvec = j.n / 4;
   float sq = 0.f;
-  for (long long i = (long long)cta * blockDim.x + threadIdx.x; i < nvec; i += (long long)nctas * blockDim.x) {
-    const long long e = j.shard_lo + i * 4;
-    float4 g = ld_peer_f4(j.grads[j.rank] + e);
+  constexpr int U = 2;  // vectors per thread per iteration: all peer loads of both are issued before any is used
+  const long long stride = (long long)nctas * blockDim.x;
+  for (long long i0 = (long long)cta * blockDim.x + threadIdx.x; i0 < nvec; i0 += U * stride) {
+    float4 g[U], p4[U], m4[U], v4[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) {
+        const long long e = j.shard_lo + i * 4;
+        g[u] = ld_peer_f4(j.grads[j.rank] + e);
+        p4[u] = reinterpret_cast<float4*>(j.master)[i];
+        m4[u] = reinterpret_cast<float4*>(j.m)[i];
+        v4[u] = reinterpret_cast<float4*>(j.v)[i];
+      }
+    }
 #pragma unroll
     for (int s = 1; s < kMaxPeers; ++s) {
       if (s < j.world) {
         const int r = (j.rank + s) % j.world;
-        const float4 t = ld_peer_f4(j.grads[r] + e);
-        g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+        float4 t[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < nvec) t[u] = ld_peer_f4(j.grads[r] + j.shard_lo + i * 4);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i0 + u * stride < nvec) { g[u].x += t[u].x; g[u].y += t[u].y; g[u].z += t[u].z; g[u].w += t[u].w; }
+        }
       }
     }
-    float4 p4 = reinterpret_cast<float4*>(j.master)[i];
-    float4 m4 = reinterpret_cast<float4*>(j.m)[i];
-    float4 v4 = reinterpret_cast<float4*>(j.v)[i];
-    float gg[4] = {g.x, g.y, g.z, g.w}, p[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w},
-          vv[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float gk = gg[k] * gscale;
-      sq += gk * gk;
-      if (j.clip_value > 0.f) gk = fminf(fmaxf(gk, -j.clip_value), j.clip_value);
-      mm[k] = j.beta1 * mm[k] + (1.f - j.beta1) * gk;
-      vv[k] = j.beta2 * vv[k] + (1.f - j.beta2) * gk * gk;
-      const float denom = sqrtf(vv[k] / bc2) + j.eps;
-      p[k] = p[k] * (1.f - lr * j.weight_decay) - lr * (mm[k] / bc1) / denom;
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+      const long long e = j.shard_lo + i * 4;
+      float gg[4] = {g[u].x, g[u].y, g[u].z, g[u].w}, p[4] = {p4[u].x, p4[u].y, p4[u].z, p4[u].w},
+            mm[4] = {m4[u].x, m4[u].y, m4[u].z, m4[u].w}, vv[4] = {v4[u].x, v4[u].y, v4[u].z, v4[u].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float gk = gg[k] * gscale;
+        sq += gk * gk;
+        if (j.clip_value > 0.f) gk = fminf(fmaxf(gk, -j.clip_value), j.clip_value);
+        mm[k] = j.beta1 * mm[k] + (1.f - j.beta1) * gk;
+        vv[k] = j.beta2 * vv[k] + (1.f - j.beta2) * gk * gk;
+        const float denom = sqrtf(vv[k] / bc2) + j.eps;
+        p[k] = p[k] * (1.f - lr * j.weight_decay) - lr * (mm[k] / bc1) / denom;
+      }
+      reinterpret_cast<float4*>(j.master)[i] = make_float4(p[0], p[1], p[2], p[3]);
+      reinterpret_cast<float4*>(j.m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+      reinterpret_cast<float4*>(j.v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      if (j.out_bf16)
+        *reinterpret_cast<uint2*>(j.out_bf16 + e) = make_uint2(pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]));
     }
-    reinterpret_cast<float4*>(j.master)[i] = make_float4(p[0], p[1], p[2], p[3]);
-    reinterpret_cast<float4*>(j.m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
-    reinterpret_cast<float4*>(j.v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
-    if (j.out_bf16)
-      *reinterpret_cast<uint2*>(j.out_bf16 + e) = make_uint2(pack_bf16x2(p[0], p[1]), pack_bf16x2(p[2], p[3]));
   }
   if (j.sumsq) {
     sq = warp_sum(sq);

@@ -10,11 +10,14 @@ Two communication back ends behind one engine:
 ``comm="fused"`` (GPUs, the product path)
     Compute and gradient buffers live in symmetric memory (``ksa_b200.parallel.symm``).
     * Gradient reduce-scatter + cast/scale + AdamW is ONE kernel on the shard owner that reads every rank's fp32
-      gradients over NVLink, and it rides along as communication CTAs of the first backward GEMM of the next unit,
-      so the transfer and the optimizer overlap with backward tile by tile.
-    * The parameter all-gather of unit ``u+1`` rides along with the first GEMM (QKV projection) of unit ``u`` in
-      forward: communication CTAs pull the peers' updated bf16 shards over NVLink while the other CTAs run the
-      tensor-core tiles.  The first two units are pulled by the stand-alone gather kernel at the start of the step.
+      gradients over NVLink (``ksa_peer_reduce_adamw``); the parameter all-gather is a P2P pull of the peers'
+      updated bf16 shards (``ksa_peer_gather``).  No NCCL collective is on the step's path.
+    * ``overlap="stream"`` (default): both run on a side stream as soon as a unit's backward has been launched
+      (reduce + AdamW) or one unit ahead of the forward pass (gather).  Their CTAs need almost no shared memory, so
+      they are co-resident with the GEMM CTAs on the same SMs and the NVLink / HBM traffic hides under tensor work.
+    * ``overlap="gemm"``: the same device routines run as communication CTAs inside the next GEMM launch (first
+      backward GEMM of the next unit for reduce + AdamW, QKV projection of the previous unit for the gather), one
+      kernel doing both.  Each communication CTA then takes a whole SM away from the GEMM.
     * Cross-GPU ordering uses per-(unit, rank) flags in symmetric signal pads carrying the step number; every wait
       is bounded and reports through the library's status word.
 
@@ -52,8 +55,9 @@ class _Boundary(torch.autograd.Function):
 
 class FsdpEngine(TrainEngine):
     def __init__(self, model: nn.Module, *args, world_size: int = 1, rank: int = 0, group=None, comm: Optional[str] = None,
-                 comm_ctas: int = 8, **kw):
+                 comm_ctas: int = 8, overlap: str = "stream", **kw):
         self.group = group
+        self.overlap = overlap
         dev = kw.get("device") or next(model.parameters()).device
         self.comm = comm or ("fused" if torch.device(dev).type == "cuda" and world_size > 1 else "collective")
         self.comm_ctas = comm_ctas
@@ -69,6 +73,8 @@ class FsdpEngine(TrainEngine):
             n = len(self.units) * self.world_size
             self.pad_grads = SignalPad(n, group, self.device)
             self.pad_weights = SignalPad(n, group, self.device)
+            self.comm_stream = torch.cuda.Stream(device=self.device)
+            self._gather_done = {}
             self._install_hooks()
 
     # ------------------------------------------------------------------ storage
@@ -107,8 +113,15 @@ class FsdpEngine(TrainEngine):
             x, delta = args[0], args[1]
             if self._overlap_active:
                 nxt = ui + 1
-                if nxt < len(self.units) and nxt >= 2:
-                    self._attach_gather(nxt)
+                if self.overlap == "gemm":
+                    if nxt < len(self.units) and nxt >= 2:
+                        self._attach_gather(nxt)
+                else:
+                    ev = self._gather_done.pop(ui, None)     # this unit's weights were pulled one unit ago
+                    if ev is not None:
+                        torch.cuda.current_stream(self.device).wait_event(ev)
+                    if nxt < len(self.units) and nxt >= 2:
+                        self._gather_on_side_stream(nxt)
                 if torch.is_grad_enabled() and x.requires_grad:
                     x, delta = _Boundary.apply(self, ui, x, delta)
             return (x, delta) + tuple(args[2:])
@@ -116,6 +129,10 @@ class FsdpEngine(TrainEngine):
 
     def _make_post_hook(self, head_ui: int):
         def hook(module, args, output):
+            if self._overlap_active and self.overlap != "gemm":
+                ev = self._gather_done.pop(head_ui, None)
+                if ev is not None:
+                    torch.cuda.current_stream(self.device).wait_event(ev)
             if self._overlap_active and torch.is_grad_enabled() and output[0].requires_grad:
                 return _Boundary.apply(self, ("before", head_ui), output[0], output[1])
             return output
@@ -134,6 +151,13 @@ class FsdpEngine(TrainEngine):
         _lib.attach_to_next_gemm("ksa_gemm_attach_gather", (
             u.compute_ptrs, self.world_size, self.rank, shard, item,
             self.pad_weights.local_ptr(self._unit_flag_index(ui)), self.epoch, 0, self.comm_ctas))
+
+    def _gather_on_side_stream(self, ui: int) -> None:
+        with torch.cuda.stream(self.comm_stream):
+            self._gather_now(ui)
+            ev = torch.cuda.Event()
+            ev.record(self.comm_stream)
+        self._gather_done[ui] = ev
 
     def _gather_now(self, ui: int) -> None:
         u = self.units[ui]
@@ -156,13 +180,23 @@ class FsdpEngine(TrainEngine):
             if not getattr(s.param, "_grad_written", False):
                 s.param.main_grad.zero_()
                 s.param._grad_written = True
-        self._signal(self.pad_grads, ui)
-        if can_attach:
-            _lib.attach_to_next_gemm("ksa_gemm_attach_reduce_adamw", self._reduce_args(u, ui) + (self.comm_ctas,),
-                                     after=lambda: self._signal(self.pad_weights, ui))
+        if self.overlap == "gemm":
+            self._signal(self.pad_grads, ui)
+            if can_attach:
+                _lib.attach_to_next_gemm("ksa_gemm_attach_reduce_adamw", self._reduce_args(u, ui) + (self.comm_ctas,),
+                                         after=lambda: self._signal(self.pad_weights, ui))
+            else:
+                _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 64)
+                self._signal(self.pad_weights, ui)
         else:
-            _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 32)
-            self._signal(self.pad_weights, ui)
+            main = torch.cuda.current_stream(self.device)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(ev)
+                self._signal(self.pad_grads, ui)
+                _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 64)
+                self._signal(self.pad_weights, ui)
         self._done_units.add(ui)
 
     def _backward_reached(self, tag) -> None:
@@ -193,7 +227,10 @@ class FsdpEngine(TrainEngine):
         self._done_units = set()
         self._overlap_active = True
         try:
-            if self.micro_step == 0:          # refreshed weights of the first two units; later ones ride on GEMMs
+            if self.micro_step == 0:          # refreshed weights of the first two units; later ones are pulled ahead
+                main = torch.cuda.current_stream(self.device)
+                main.wait_stream(self.comm_stream)   # the previous step's updates of this rank's own shards
+                self.comm_stream.wait_stream(main)
                 self._gather_now(0)
                 if len(self.units) > 1:
                     self._gather_now(1)
@@ -225,6 +262,7 @@ class FsdpEngine(TrainEngine):
             for ui in range(len(self.units) - 1, -1, -1):   # whatever backward did not reach (embed; all, if hooks are off)
                 if ui not in self._done_units:
                     self._unit_grads_ready(ui, can_attach=False)
+            torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
             return
         self._collect_autograd_grads()
         self.grad_sq.zero_()

@@ -1,0 +1,270 @@
+"""Checkpoint save / resume in the reference's layout (``muse/training/checkpoint.py:144-680``).
+
+On disk: ``<output_dir>/global_step{N}/`` is a ``torch.distributed.checkpoint`` (DCP) directory whose logical tree is
+
+    app.model.<reference parameter name>          fp32 master weights (e.g. ``model.layers.3.attn.q_proj.weight``)
+    app.optim.state.<name>.{exp_avg,exp_avg_sq,step}   and   app.optim.param_groups
+    app.training.{step_scheduler,lr_scheduler}
+
+next to a ``latest`` text file naming the newest step directory and ``dataloader_state.pt`` (rank 0).  Parameter
+names are the reference's (q/k/v and w1/w3 split out of the fused tensors), so its converter and ours read the same
+files.  Independent switches choose what a resume restores (weights / optimizer / training state / dataloader), and
+the step numbering continues from the directory name.
+
+The engine keeps master weights and Adam moments as per-rank shards of flat unit buffers; for saving, every unit is
+all-gathered into full fp32 tensors (one unit at a time) and DCP de-duplicates the replicated entries across ranks.
+"""
+from __future__ import annotations
+
+import os
+import re
+import time
+from pathlib import Path
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.distributed.checkpoint as dcp
+from torch.distributed.checkpoint.stateful import Stateful
+
+
+def _rank() -> int:
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
+def _world() -> int:
+    return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+
+
+def _barrier() -> None:
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+
+
+def step_dir_name(step: int) -> str:
+    return f"global_step{int(step)}"
+
+
+def get_checkpoint_path(checkpoint_dir: str, checkpoint_id: Optional[str] = None) -> Optional[str]:
+    """Resolve ``checkpoint_id`` (a step number, a directory name, or None / "latest") to a step directory."""
+    root = Path(checkpoint_dir)
+    if checkpoint_id in (None, "", "latest"):
+        latest = root / "latest"
+        if not latest.exists():
+            return None
+        name = latest.read_text().strip()
+    else:
+        name = str(checkpoint_id)
+        if name.isdigit():
+            name = step_dir_name(int(name))
+    path = root / name
+    return str(path) if path.is_dir() else None
+
+
+def step_from_path(path: str) -> int:
+    m = re.search(r"global_step(\d+)", str(path))
+    return int(m.group(1)) if m else 0
+
+
+# --------------------------------------------------------------------------------------------------- engine <-> tensors
+def _gather_unit(engine, shard: torch.Tensor, unit) -> torch.Tensor:
+    """Full fp32 flat buffer of ``unit`` from every rank's shard."""
+    if engine.world_size == 1:
+        return shard
+    parts = [torch.empty_like(shard) for _ in range(engine.world_size)]
+    dist.all_gather(parts, shard.contiguous(), group=getattr(engine, "group", None))
+    return torch.cat(parts)
+
+
+def engine_full_state(engine, with_optimizer: bool = True) -> Dict[str, Dict[str, torch.Tensor]]:
+    """``{"model": {fused name: fp32}, "exp_avg": {...}, "exp_avg_sq": {...}}`` as CPU tensors."""
+    out: Dict[str, Dict[str, torch.Tensor]] = {"model": {}, "exp_avg": {}, "exp_avg_sq": {}}
+    kinds = [("model", "master")] + ([("exp_avg", "exp_avg"), ("exp_avg_sq", "exp_avg_sq")] if with_optimizer else [])
+    for u in engine.units:
+        for key, attr in kinds:
+            full = _gather_unit(engine, getattr(u, attr), u)
+            for s in u.slots:
+                out[key][s.name] = full[s.offset:s.offset + s.numel].view(s.shape).to("cpu", copy=True)
+    return out
+
+
+def load_engine_full_state(engine, model_state: Optional[Dict[str, torch.Tensor]],
+                           exp_avg: Optional[Dict[str, torch.Tensor]] = None,
+                           exp_avg_sq: Optional[Dict[str, torch.Tensor]] = None, strict: bool = True) -> List[str]:
+    """Write full tensors (fused names) into this rank's shards; returns the names that were missing."""
+    missing: List[str] = []
+    with torch.no_grad():
+        for u in engine.units:
+            for s in u.slots:
+                lo, hi = max(s.offset, u.shard_lo), min(s.offset + s.numel, u.shard_hi)
+                for src, dst in ((model_state, u.master), (exp_avg, u.exp_avg), (exp_avg_sq, u.exp_avg_sq)):
+                    if src is None:
+                        continue
+                    if s.name not in src:
+                        if src is model_state:
+                            missing.append(s.name)
+                        continue
+                    t = src[s.name]
+                    if tuple(t.shape) != tuple(s.shape):
+                        raise ValueError(f"{s.name}: checkpoint shape {tuple(t.shape)} != model shape {tuple(s.shape)}")
+                    if hi > lo:
+                        flat = t.reshape(-1)[lo - s.offset:hi - s.offset].to(device=engine.device, dtype=torch.float32)
+                        dst[lo - u.shard_lo:hi - u.shard_lo].copy_(flat)
+                if model_state is not None and s.name in model_state:
+                    u.compute[s.offset:s.offset + s.numel].copy_(
+                        model_state[s.name].reshape(-1).to(device=engine.device, dtype=torch.float32))
+    if strict and missing:
+        raise KeyError(f"checkpoint lacks {len(missing)} parameters, e.g. {missing[:4]}")
+    return missing
+
+
+class AppState(Stateful):
+    """What one checkpoint holds: model + optimizer (through the engine) and training-loop state."""
+
+    def __init__(self, engine, step_scheduler=None, lr_scheduler=None, skip_optimizer: bool = False,
+                 skip_training_state: bool = False, strict: bool = True):
+        self.engine = engine
+        self.step_scheduler = step_scheduler
+        self.lr_scheduler = lr_scheduler
+        self.skip_optimizer = skip_optimizer
+        self.skip_training_state = skip_training_state
+        self.strict = strict
+
+    def _to_muse(self, fused: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        m = self.engine.model
+        return m.muse_state_dict(fused) if hasattr(m, "muse_state_dict") else fused
+
+    def _from_muse(self, muse: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        m = self.engine.model
+        return m.from_muse_state_dict(muse) if hasattr(m, "from_muse_state_dict") else muse
+
+    def state_dict(self) -> Dict[str, Any]:
+        full = engine_full_state(self.engine, with_optimizer=True)
+        model = self._to_muse(full["model"])
+        m1, m2 = self._to_muse(full["exp_avg"]), self._to_muse(full["exp_avg_sq"])
+        step = torch.tensor(float(self.engine.step_count))
+        optim_state = {k: {"exp_avg": m1[k], "exp_avg_sq": m2[k], "step": step.clone()} for k in model}
+        e = self.engine
+        optim = {"state": optim_state,
+                 "param_groups": [{"lr": e.base_lr, "betas": (e.beta1, e.beta2), "eps": e.eps,
+                                   "weight_decay": e.weight_decay, "params": list(model)}]}
+        training: Dict[str, Any] = {"engine_step": e.step_count}
+        if self.step_scheduler is not None:
+            training["step_scheduler"] = self.step_scheduler.state_dict()
+        if self.lr_scheduler is not None and hasattr(self.lr_scheduler, "state_dict"):
+            training["lr_scheduler"] = self.lr_scheduler.state_dict()
+        return {"model": model, "optim": optim, "training": training}
+
+    def load_state_dict(self, state: Dict[str, Any]) -> None:
+        model = self._from_muse(state["model"]) if "model" in state else None
+        ea = es = None
+        if not self.skip_optimizer and "optim" in state:
+            st = state["optim"]["state"]
+            ea = self._from_muse({k: v["exp_avg"] for k, v in st.items()})
+            es = self._from_muse({k: v["exp_avg_sq"] for k, v in st.items()})
+        load_engine_full_state(self.engine, model, ea, es, strict=self.strict)
+        training = state.get("training", {})
+        if not self.skip_optimizer:
+            self.engine.step_count = int(training.get("engine_step", self.engine.step_count))
+        if not self.skip_training_state:
+            if self.step_scheduler is not None and "step_scheduler" in training:
+                self.step_scheduler.load_state_dict(training["step_scheduler"])
+            if self.lr_scheduler is not None and "lr_scheduler" in training and hasattr(self.lr_scheduler, "load_state_dict"):
+                self.lr_scheduler.load_state_dict(training["lr_scheduler"])
+
+
+class DistributedCheckpointer:
+    """DCP save (sync or async) and load of ``{"app": AppState}``."""
+
+    def __init__(self, thread_count: int = 4, async_save: bool = False):
+        self.thread_count = thread_count
+        self.use_async = async_save
+        self._pending = None
+
+    def wait(self) -> None:
+        if self._pending is not None:
+            self._pending.result()
+            self._pending = None
+
+    def save(self, app_state: AppState, path: str) -> None:
+        self.wait()
+        state = {"app": app_state.state_dict()}   # materialised now so that training may go on during an async save
+        writer = dcp.FileSystemWriter(path, thread_count=self.thread_count)
+        if self.use_async and dist.is_available() and dist.is_initialized():
+            self._pending = dcp.async_save(state, storage_writer=writer)
+        else:
+            dcp.save(state, storage_writer=writer, no_dist=not (dist.is_available() and dist.is_initialized()))
+
+    def load(self, app_state: AppState, path: str) -> None:
+        template = {"app": app_state.state_dict()}
+        if app_state.skip_optimizer:
+            template["app"].pop("optim", None)
+        dcp.load(template, storage_reader=dcp.FileSystemReader(path),
+                 no_dist=not (dist.is_available() and dist.is_initialized()))
+        app_state.load_state_dict(template["app"])
+
+
+def save_checkpoint(app_state: AppState, checkpointer: DistributedCheckpointer, output_dir: str, step: int) -> str:
+    """Write ``global_step{step}``, then point ``latest`` at it (rank 0), with barriers around the collective save."""
+    path = os.path.join(output_dir, step_dir_name(step))
+    if _rank() == 0:
+        os.makedirs(path, exist_ok=True)
+    _barrier()
+    checkpointer.save(app_state, path)
+    _barrier()
+    if _rank() == 0:
+        tmp = os.path.join(output_dir, "latest.tmp")
+        with open(tmp, "w") as f:
+            f.write(step_dir_name(step))
+        os.replace(tmp, os.path.join(output_dir, "latest"))
+    return path
+
+
+def load_checkpoint(app_state: AppState, checkpointer: DistributedCheckpointer, checkpoint_dir: str,
+                    checkpoint_id: Optional[str] = None) -> Optional[int]:
+    path = get_checkpoint_path(checkpoint_dir, checkpoint_id)
+    if path is None:
+        return None
+    checkpointer.load(app_state, path)
+    return step_from_path(path)
+
+
+def save_dataloader_state(dataset, output_dir: str, step: int) -> Optional[str]:
+    """Rank 0 writes the dataset's resumable state next to the step's checkpoint."""
+    if not hasattr(dataset, "state_dict"):
+        return None
+    path = os.path.join(output_dir, step_dir_name(step), "dataloader_state.pt")
+    if _rank() == 0:
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        torch.save(dataset.state_dict(), path)
+    _barrier()
+    return path
+
+
+def load_dataloader_state(dataset, checkpoint_path: str) -> bool:
+    """Soft resume: returns False (and leaves the dataset untouched) when there is no usable state file."""
+    path = os.path.join(checkpoint_path, "dataloader_state.pt")
+    if not os.path.exists(path) or not hasattr(dataset, "load_state_dict"):
+        return False
+    try:
+        state = torch.load(path, map_location="cpu", weights_only=False)
+        dataset.load_state_dict(state)
+        return True
+    except Exception as e:  # noqa: BLE001 - a truncated or foreign file must not kill a resume
+        print(f"[checkpoint] ignoring dataloader state {path}: {type(e).__name__}: {e}")
+        return False
+
+
+def load_hf_checkpoint(model_dir: str, device: str = "cpu") -> Dict[str, torch.Tensor]:
+    """Every tensor of an HF directory (sharded safetensors or ``pytorch_model*.bin``)."""
+    from ..models.base import load_hf_state_dict
+    return load_hf_state_dict(model_dir, device)
+
+
+def dcp_to_state_dict(path: str) -> Dict[str, Any]:
+    """Read a whole DCP directory in one process without a process group (for the converters)."""
+    from torch.distributed.checkpoint.state_dict_loader import _load_state_dict
+    from torch.distributed.checkpoint.default_planner import _EmptyStateDictLoadPlanner
+    sd: Dict[str, Any] = {}
+    _load_state_dict(sd, storage_reader=dcp.FileSystemReader(path), planner=_EmptyStateDictLoadPlanner(), no_dist=True)
+    return sd

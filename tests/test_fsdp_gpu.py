@@ -50,12 +50,13 @@ def _worker(rank, world, port, out_q):
         results = {}
         g = torch.Generator().manual_seed(11)
         data = torch.randint(0, cfg.vocab_size, (3, world, 2, 513), generator=g)
-        for comm in ("collective", "fused"):
+        for comm, overlap in (("collective", "stream"), ("fused", "stream"), ("fused", "gemm")):
             torch.manual_seed(0)
             model = get_model_class(cfg.model_class)(cfg)
             model.init_weights(seed=0)
             model = model.to(dev).to(torch.bfloat16)
-            eng = FsdpEngine(model, lr=1e-3, weight_decay=0.1, clip_value=1.0, world_size=world, rank=rank, comm=comm)
+            eng = FsdpEngine(model, lr=1e-3, weight_decay=0.1, clip_value=1.0, world_size=world, rank=rank, comm=comm,
+                             overlap=overlap)
             losses = []
             for s in range(3):
                 x = data[s, rank].to(dev)
@@ -66,14 +67,16 @@ def _worker(rank, world, port, out_q):
                 for ui in range(len(eng.units)):
                     eng._gather_now(ui)
                 torch.cuda.synchronize(); _lib.check_status(); dist.barrier()
-            results[comm] = (losses, [u.compute.float().clone() for u in eng.units], float(eng.grad_norm()))
+            results[(comm, overlap)] = (losses, [u.compute.float().clone() for u in eng.units], float(eng.grad_norm()))
             if comm == "fused":
                 eng.close()
-        (lc, wc, gc), (lf, wf, gf) = results["collective"], results["fused"]
-        assert all(abs(a - b) < 3e-2 for a, b in zip(lc, lf)), (lc, lf)
-        assert abs(gc - gf) < 0.05 * gc, (gc, gf)
-        for a, b in zip(wc, wf):
-            assert (a - b).norm() <= 1e-2 * a.norm().clamp_min(1e-6)
+        lc, wc, gc = results[("collective", "stream")]
+        for key in (("fused", "stream"), ("fused", "gemm")):
+            lf, wf, gf = results[key]
+            assert all(abs(a - b) < 3e-2 for a, b in zip(lc, lf)), (key, lc, lf)
+            assert abs(gc - gf) < 0.05 * gc, (key, gc, gf)
+            for a, b in zip(wc, wf):
+                assert (a - b).norm() <= 1e-2 * a.norm().clamp_min(1e-6), key
         out_q.put((rank, "ok", lf))
     except Exception as e:  # noqa: BLE001
         import traceback
