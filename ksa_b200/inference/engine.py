@@ -1,0 +1,274 @@
+"""Prefill + decode engine for Qwen3-KSA with the ring-buffer KV cache (batch >= 1).
+
+Prefill runs the training graph once over the prompt (block-sparse KSA attention for summary layers, causal
+attention for full layers), with a trailing partial chunk receiving no summary tokens, and files every layer's
+rotated K/V into the caches.  A decode step feeds one text token per sequence; when that token completes a chunk the
+step also carries the chunk's ``S`` summary tokens (summary embedding, summary projections, position ids of the
+``last_chunk_slice_right`` rule) and afterwards flushes the chunk into the ring and appends the summary K/V
+(``examples/pretrain/hf_template/modeling_qwen3sa.py:1040-1325,1473-1560``).  The reference's decode path supports
+batch 1 only (``:753-754``); here all sequences of a batch advance together and may sit at different chunk phases.
+
+Chunk phases are mirrored on the host (they are a deterministic function of prompt length and steps taken), so a step
+never reads device memory back; slice bounds and slots are computed on the device from the counters.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+from ..ops import _lib, reference as ref
+from .cache import (CacheSpec, CacheState, FullLayerCache, KsaLayerCache, flush_plan, summary_step_slices,
+                    text_step_slices)
+
+
+def _decode_attention(q, k_cache, v_cache, start, length, scale):
+    """q ``[B, Tq, Hq, D]``; every (b, t) attends cache slots ``[start, start+length)``."""
+    if not q.is_cuda:
+        outs = [ref.decode_attention(q[:, t:t + 1], k_cache, v_cache, length[:, t].long(), start[:, t].long(), scale)
+                for t in range(q.shape[1])]
+        return torch.cat(outs, dim=1)
+    B, Tq, Hq, D = q.shape
+    Hkv, cap = k_cache.shape[1], k_cache.shape[2]
+    keys_per_split = 512
+    splits = max(1, min(64, (cap + keys_per_split - 1) // keys_per_split))
+    keys_per_split = (cap + splits - 1) // splits
+    part_o = torch.empty((B, Tq, Hq, splits, D), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((B, Tq, Hq, splits, 2), dtype=torch.float32, device=q.device)
+    out = torch.empty_like(q)
+    _lib.call("ksa_decode_attn", q.contiguous(), k_cache, v_cache, start.contiguous(), length.contiguous(), part_o,
+              part_ml, out, B, Tq, Hq, Hkv, D, cap, splits, keys_per_split, float(scale))
+    return out
+
+
+def _cache_append(k_new, v_new, k_cache, v_cache, slots):
+    """``k_new``/``v_new`` ``[B, T, H, D]`` (views allowed) -> cache ``[B, H, cap, D]`` at ``slots[B, T]`` (< 0: skip)."""
+    if not k_new.is_cuda:
+        B, T, H, D = k_new.shape
+        for b in range(B):
+            for t in range(T):
+                s = int(slots[b, t])
+                if s >= 0:
+                    k_cache[b, :, s] = k_new[b, t]
+                    v_cache[b, :, s] = v_new[b, t]
+        return
+    B, T, H, D = k_new.shape
+    assert k_new.stride(3) == 1 and k_new.stride(2) == D and v_new.stride() == k_new.stride()
+    _lib.call("ksa_kv_cache_append", k_new, v_new, k_cache, v_cache, slots.contiguous(), B, T, H, D, k_cache.shape[2],
+              k_new.stride(1), k_new.stride(0))
+
+
+def _cache_move(k_cache, v_cache, src, dst, enable, rows):
+    if rows == 0:
+        return
+    if not k_cache.is_cuda:
+        for b in range(k_cache.shape[0]):
+            if int(enable[b]):
+                s, d = int(src[b]), int(dst[b])
+                k_cache[b, :, d:d + rows] = k_cache[b, :, s:s + rows].clone()
+                v_cache[b, :, d:d + rows] = v_cache[b, :, s:s + rows].clone()
+        return
+    B, H, cap, D = k_cache.shape
+    _lib.call("ksa_kv_cache_move", k_cache, v_cache, src.contiguous(), dst.contiguous(), enable.contiguous(), B, H, D,
+              cap, rows)
+
+
+class KsaInferenceEngine:
+    def __init__(self, model, max_len: int, batch: int, device=None, dtype=None):
+        self.model = model.eval()
+        self.model.drop_partial_summary = True
+        cfg = model.config
+        self.cfg = cfg
+        p = next(model.parameters())
+        self.device = device or p.device
+        self.dtype = dtype or p.dtype
+        self.batch = batch
+        self.max_len = max_len
+        self.C = cfg.summary_chunk_size if cfg.summary_enabled else max_len
+        self.S = cfg.summary_token_num if cfg.summary_enabled else 0
+        Hkv, Dh = cfg.num_kv_heads, cfg.head_dim
+        self.layer_caches: List[object] = []
+        self.specs: List[Optional[CacheSpec]] = []
+        for layer in model.layers:
+            if layer.is_summary_layer:
+                spec = CacheSpec(self.C, self.S, layer.window_chunks, max_len // self.C + 1)
+                self.specs.append(spec)
+                self.layer_caches.append(KsaLayerCache(spec, batch, Hkv, Dh, self.dtype, self.device))
+            else:
+                self.specs.append(None)
+                self.layer_caches.append(FullLayerCache(max_len, batch, Hkv, Dh, self.dtype, self.device))
+        self.state = CacheState(batch, self.device)
+        self.host_len = [0] * batch
+
+    def cache_bytes(self) -> int:
+        return sum(c.k.numel() * c.k.element_size() * 2 for c in self.layer_caches)
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
+        """``tokens`` ``[B, L]`` (equal lengths) -> logits of the last position ``[B, V]``; caches are filled."""
+        B, L = tokens.shape
+        assert B == self.batch and L <= self.max_len
+        cfg, C, S = self.cfg, self.C, self.S
+        Hq, Hkv, Dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        n_full = L // C if S > 0 else 0      # complete chunks
+        tail = L - n_full * C if S > 0 else L
+        Ns = n_full * S
+
+        def sink(layer_idx, qkv, is_summary_layer):
+            cache = self.layer_caches[layer_idx]
+            k_t = qkv[:B * L, Hq * Dh:(Hq + Hkv) * Dh].view(B, L, Hkv, Dh)
+            v_t = qkv[:B * L, (Hq + Hkv) * Dh:].view(B, L, Hkv, Dh)
+            if not is_summary_layer:
+                cache.k[:, :, :L] = k_t.transpose(1, 2)
+                cache.v[:, :, :L] = v_t.transpose(1, 2)
+                return
+            spec = self.specs[layer_idx]
+            W = spec.window
+            # ring: the last min(W, n_full) complete chunks, chunk c at ring slot (c mod W)
+            for c in range(max(0, n_full - W), n_full):
+                dst = spec.text0 + (c % max(W, 1)) * C
+                cache.k[:, :, dst:dst + C] = k_t[:, c * C:(c + 1) * C].transpose(1, 2)
+                cache.v[:, :, dst:dst + C] = v_t[:, c * C:(c + 1) * C].transpose(1, 2)
+            # current (partial) chunk, right to left: chunk offset o -> slot S + C - 1 - o
+            if tail > 0:
+                lo = n_full * C
+                slots = torch.arange(S + C - 1, S + C - 1 - tail, -1, device=qkv.device)
+                cache.k[:, :, slots] = k_t[:, lo:lo + tail].transpose(1, 2)
+                cache.v[:, :, slots] = v_t[:, lo:lo + tail].transpose(1, 2)
+            if Ns > 0:
+                k_s = qkv[B * L:, Hq * Dh:(Hq + Hkv) * Dh].view(B, Ns, Hkv, Dh)
+                v_s = qkv[B * L:, (Hq + Hkv) * Dh:].view(B, Ns, Hkv, Dh)
+                cache.k[:, :, spec.sum0:spec.sum0 + Ns] = k_s.transpose(1, 2)
+                cache.v[:, :, spec.sum0:spec.sum0 + Ns] = v_s.transpose(1, 2)
+
+        logits = self.model(tokens, kv_sink=sink, last_token_only=True)
+        self.state.text_len.fill_(L)
+        self.state.cbl.fill_(tail if S > 0 else 0)
+        self.state.chunks.fill_(n_full)
+        self.host_len = [L] * B
+        return logits[:, -1].float()
+
+    # ------------------------------------------------------------------ decode
+    @torch.no_grad()
+    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """``tokens`` ``[B]``: the next text token of every sequence -> logits ``[B, V]``."""
+        model, cfg = self.model, self.cfg
+        B, C, S = self.batch, self.C, self.S
+        Hq, Hkv, Dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        scale = Dh ** -0.5
+        st = self.state
+        boundary_host = [S > 0 and (l % C) == C - 1 for l in self.host_len]
+        any_boundary = any(boundary_host)
+        dev = self.device
+        pos_t = st.text_len.clone()                              # position of the new text token
+        x = ops.embedding(tokens.reshape(B), model.tok_embeddings.weight)      # [B, D]
+        if any_boundary:
+            boundary = torch.tensor(boundary_host, dtype=torch.int32, device=dev)
+            xs = model._summary_rows(_OneChunk(B, S), x.dtype)                 # [B*S, D]
+            x = torch.cat([x, xs], dim=0)
+            chunk_start = st.text_len - (C - 1)
+            j = torch.arange(S, device=dev, dtype=torch.int32)
+            if cfg.summary_token_position_ids_type == "zeros":
+                pos_s = torch.zeros(B, S, dtype=torch.int32, device=dev)
+            elif cfg.summary_token_position_ids_type == "last_chunk_slice_right":
+                pos_s = torch.maximum(chunk_start[:, None] + ((j[None, :] + 1) * C) // S - 1, chunk_start[:, None])
+            else:
+                pos_s = torch.maximum(chunk_start[:, None] + (j[None, :] * C) // S - 1, chunk_start[:, None])
+            pos_all = torch.cat([pos_t, pos_s.reshape(-1).to(torch.int32)])
+        else:
+            pos_all = pos_t
+        if cfg.summary_enabled and cfg.summary_chunk_position_ids_type == "inner_chunk":
+            pos_all = pos_all.clone()
+            pos_all[:B] = st.cbl
+        delta = None
+        for li, layer in enumerate(model.layers):
+            a = layer.attn
+            cache = self.layer_caches[li]
+            x, h = ops.add_rms_norm(x, delta, layer.sa_norm.scale, cfg.norm_eps)
+            if layer.is_summary_layer:
+                spec = self.specs[li]
+                if any_boundary:
+                    if layer.sa_norm_summary is not None:
+                        h = torch.cat([h[:B], ops.rms_norm(x[B:], layer.sa_norm_summary.scale, cfg.norm_eps)])
+                    w_s = a.wqkv_summary.weight if a.wqkv_summary is not None else a.wqkv.weight
+                    qkv = ops.dual_linear(h, a.wqkv.weight, w_s, B)
+                else:
+                    qkv = ops.linear(h, a.wqkv.weight)
+                qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), pos_all, Hq, Hkv, Dh,
+                                              cfg.rope_base, cfg.norm_eps, cfg.rope_impl == "llama")
+                slot_t, start_t, len_t = text_step_slices(spec, st)
+                q_t = qkv[:B, :Hq * Dh].view(B, 1, Hq, Dh)
+                k_t = qkv[:B, Hq * Dh:(Hq + Hkv) * Dh].view(B, 1, Hkv, Dh)
+                v_t = qkv[:B, (Hq + Hkv) * Dh:].view(B, 1, Hkv, Dh)
+                _cache_append(k_t, v_t, cache.k, cache.v, slot_t.view(B, 1))
+                if any_boundary:
+                    slot_s, start_s, len_s = summary_step_slices(spec, B, dev)
+                    off = torch.where(boundary[:, None] > 0, slot_s, torch.full_like(slot_s, -1))
+                    q_s = qkv[B:, :Hq * Dh].view(B, S, Hq, Dh)
+                    k_s = qkv[B:, Hq * Dh:(Hq + Hkv) * Dh].view(B, S, Hkv, Dh)
+                    v_s = qkv[B:, (Hq + Hkv) * Dh:].view(B, S, Hkv, Dh)
+                    _cache_append(k_s, v_s, cache.k, cache.v, off)
+                    q_all = torch.cat([q_t, q_s], dim=1)
+                    starts = torch.cat([start_t.view(B, 1), start_s], dim=1).to(torch.int32)
+                    lens = torch.cat([len_t.view(B, 1), len_s * boundary[:, None]], dim=1).to(torch.int32)
+                    att = _decode_attention(q_all, cache.k, cache.v, starts, lens, scale)     # [B, 1+S, Hq, Dh]
+                    att = torch.cat([att[:, 0].reshape(B, Hq * Dh), att[:, 1:].reshape(B * S, Hq * Dh)], dim=0)
+                    # flush: chunk text -> ring, scratch summaries -> summary region (boundary sequences only)
+                    src_t, dst_t, src_s, dst_s = flush_plan(spec, st)
+                    if spec.window > 0:
+                        _cache_move(cache.k, cache.v, src_t, dst_t, boundary, C)
+                    _cache_move(cache.k, cache.v, src_s, dst_s, boundary, S)
+                else:
+                    att = _decode_attention(q_t, cache.k, cache.v, start_t.view(B, 1).to(torch.int32),
+                                            len_t.view(B, 1).to(torch.int32), scale).reshape(B, Hq * Dh)
+                attn_out = ops.linear(att, a.output_proj.weight)
+                x, h2 = ops.add_rms_norm(x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
+                delta = layer.mlp(h2)
+            else:
+                qkv = ops.linear(h[:B], a.wqkv.weight)
+                qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), pos_all[:B], Hq, Hkv, Dh,
+                                              cfg.rope_base, cfg.norm_eps, cfg.rope_impl == "llama")
+                q_t = qkv[:, :Hq * Dh].view(B, 1, Hq, Dh)
+                k_t = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(B, 1, Hkv, Dh)
+                v_t = qkv[:, (Hq + Hkv) * Dh:].view(B, 1, Hkv, Dh)
+                _cache_append(k_t, v_t, cache.k, cache.v, st.text_len.view(B, 1))
+                zeros = torch.zeros(B, 1, dtype=torch.int32, device=dev)
+                att = _decode_attention(q_t, cache.k, cache.v, zeros, (st.text_len + 1).view(B, 1).to(torch.int32),
+                                        scale).reshape(B, Hq * Dh)
+                attn_out = ops.linear(att, a.output_proj.weight)
+                x, h2 = ops.add_rms_norm(x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
+                delta = layer.mlp(h2[:B])
+        _, hN = ops.add_rms_norm(x[:B], delta[:B], model.norm.scale, cfg.norm_eps)
+        logits = ops.linear(hN, model.lm_head_weight)
+        # advance the counters
+        st.text_len += 1
+        if S > 0:
+            if any_boundary:
+                st.chunks += boundary
+                st.cbl = torch.where(boundary > 0, torch.zeros_like(st.cbl), st.cbl + 1)
+            else:
+                st.cbl += 1
+        self.host_len = [l + 1 for l in self.host_len]
+        return logits.float()
+
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, max_new_tokens: int, eos_id: Optional[int] = None) -> torch.Tensor:
+        """Greedy decoding; returns ``[B, L + new]``."""
+        logits = self.prefill(prompt)
+        out = [prompt]
+        nxt = logits.argmax(-1)
+        for i in range(max_new_tokens):
+            out.append(nxt.view(-1, 1))
+            if i + 1 == max_new_tokens or (eos_id is not None and bool((nxt == eos_id).all())):
+                break
+            nxt = self.decode_step(nxt).argmax(-1)
+        return torch.cat(out, dim=1)
+
+
+class _OneChunk:
+    """Shape record for ``_summary_rows``: the summary rows of one chunk per sequence."""
+
+    def __init__(self, B: int, S: int):
+        self.B, self.Ns, self.n_sum = B, S, S

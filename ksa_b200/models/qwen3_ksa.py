@@ -149,6 +149,8 @@ class KsaDecoderLayer(nn.Module):
             else:
                 qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), meta.pos, Hq, Hkv, Dh,
                                               cfg.rope_base, cfg.norm_eps, meta.rope_interleaved)
+            if meta.kv_sink is not None:
+                meta.kv_sink(self.layer_idx, qkv, True)
             att = ops.attention_packed(qkv, meta.B, meta.L, meta.Ns, Hq, Hkv, Dh, meta.chunk, meta.n_sum,
                                        self.window_chunks)
             attn_out = ops.linear(att, a.output_proj.weight)
@@ -160,6 +162,8 @@ class KsaDecoderLayer(nn.Module):
         qkv = ops.linear(h[:n_text], a.wqkv.weight)
         qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), meta.pos[:n_text], Hq, Hkv, Dh,
                                       cfg.rope_base, cfg.norm_eps, meta.rope_interleaved)
+        if meta.kv_sink is not None:
+            meta.kv_sink(self.layer_idx, qkv, False)
         att = ops.attention_packed(qkv, meta.B, meta.L, 0, Hq, Hkv, Dh, tok_window=self.tok_window)
         attn_out = ops.linear(att, a.output_proj.weight)
         if collect is not None:
@@ -191,6 +195,7 @@ class BatchMeta:
         if pos_s is not None and self.Ns > 0:
             parts.append(pos_s.repeat(B))
         self.pos = torch.cat(parts).to(torch.int32)
+        self.kv_sink = None   # optional callable(layer_idx, qkv_rot, is_summary_layer): prefill fills KV caches with it
 
 
 @register_model("Qwen3Model")
@@ -213,6 +218,7 @@ class Qwen3Model(Model):
         self._meta_cache: Dict[tuple, BatchMeta] = {}
         self.skip_output_layer = False
         self.loss_chunk_tokens = 2048
+        self.drop_partial_summary = False   # inference: a trailing partial chunk gets no summary tokens
 
     # ---- configuration helpers ----------------------------------------------------
     def _layer_is_summary(self) -> List[bool]:
@@ -264,7 +270,7 @@ class Qwen3Model(Model):
     def _meta(self, B: int, L: int, device, position_ids) -> BatchMeta:
         if position_ids is not None:
             return BatchMeta(B, L, self._layout(L), device, self.config.rope_impl == "llama", position_ids)
-        key = (B, L, str(device))
+        key = (B, L, str(device), self.drop_partial_summary)
         if key not in self._meta_cache:
             self._meta_cache[key] = BatchMeta(B, L, self._layout(L), device, self.config.rope_impl == "llama")
         return self._meta_cache[key]
@@ -280,7 +286,7 @@ class Qwen3Model(Model):
 
     def forward(self, tokens: torch.Tensor, labels: Optional[torch.Tensor] = None,
                 position_ids: Optional[torch.Tensor] = None, return_hidden: bool = False,
-                collect_attn: bool = False, ignore_index: int = -100):
+                collect_attn: bool = False, ignore_index: int = -100, kv_sink=None, last_token_only: bool = False):
         """``tokens`` ``[B, L]`` -> loss (with ``labels``), hidden ``[B, L, D]`` or logits ``[B, L, V]``.
 
         ``labels`` are already shifted (label of position t is token t+1) with ``ignore_index`` where masked,
@@ -288,12 +294,20 @@ class Qwen3Model(Model):
         """
         B, L = tokens.shape
         meta = self._meta(B, L, tokens.device, position_ids)
+        meta.kv_sink = kv_sink
         x = self.embed(tokens, meta)
         collect = [] if collect_attn else None
         delta = None
         for layer in self.layers:
             x, delta = layer(x, delta, meta, collect)
+        meta.kv_sink = None
         n_text = B * L
+        if last_token_only:   # prefill: only the last position of every sequence feeds the head
+            rows = torch.arange(B, device=x.device) * L + (L - 1)
+            xl = x[rows]
+            dl = delta[rows] if delta is not None else None
+            _, h = ops.add_rms_norm(xl, dl, self.norm.scale, self.config.norm_eps)
+            return ops.linear(h, self.lm_head_weight).view(B, 1, -1)
         # summary rows are dropped before the final norm and the head (modeling.py:243-249)
         _, h = ops.add_rms_norm(x[:n_text], delta[:n_text] if delta is not None else None, self.norm.scale,
                                 self.config.norm_eps)
@@ -488,7 +502,7 @@ class Qwen3SummaryModel(Qwen3Model):
         if not cfg.summary_enabled:
             return None
         return get_layout(L, cfg.summary_chunk_size, cfg.summary_token_num, cfg.summary_chunk_position_ids_type,
-                          cfg.summary_token_position_ids_type)
+                          cfg.summary_token_position_ids_type, self.drop_partial_summary)
 
     def _summary_rows(self, meta: BatchMeta, dtype) -> torch.Tensor:
         cfg = self.config

@@ -39,8 +39,9 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_attn_bwd": [P] * 14 + [I] * 7 + [L] * 22 + [I] * 7 + [F, P, P, P],
     "ksa_summary_attn_fwd": [P] * 7 + [I] * 6 + [L] * 12 + [I] * 5 + [F, P],
     "ksa_summary_attn_bwd": [P] * 13 + [I] * 6 + [L] * 22 + [I] * 5 + [F, P, P, I, P],
-    "ksa_decode_attn": [P] * 7 + [I] * 7 + [L] * 8 + [F, P],
-    "ksa_kv_cache_append": [P] * 6 + [I] * 6 + [L] * 6 + [P],
+    "ksa_decode_attn": [P] * 8 + [I] * 8 + [F, P],
+    "ksa_kv_cache_append": [P] * 5 + [I] * 5 + [L, L, P],
+    "ksa_kv_cache_move": [P] * 5 + [I] * 5 + [P],
     "ksa_peer_gather": [P, I, I, L, I, P, P, ctypes.c_uint, I, P],
     "ksa_peer_reduce_adamw": [P, I, I, L, L, P, P, P, P, P, F, F, F, F, F, P, P, P, ctypes.c_uint, I, P],
     "ksa_gemm_attach_gather": [P, I, I, L, I, P, P, ctypes.c_uint, I],

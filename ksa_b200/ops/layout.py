@@ -24,9 +24,12 @@ class SummaryLayout:
     n_sum: int                # S
     text_pos_type: str = "origin"
     sum_pos_type: str = "last_chunk_slice_right"
+    drop_partial: bool = False  # True: a trailing partial chunk gets no summary tokens (prefill / decoding)
 
     @property
     def n_chunks(self) -> int:
+        if self.drop_partial:
+            return self.seq_len // self.chunk
         return (self.seq_len + self.chunk - 1) // self.chunk
 
     @property
@@ -113,8 +116,8 @@ class SummaryLayout:
 
 @lru_cache(maxsize=64)
 def get_layout(seq_len: int, chunk: int, n_sum: int, text_pos_type: str = "origin",
-               sum_pos_type: str = "last_chunk_slice_right") -> SummaryLayout:
-    return SummaryLayout(seq_len, chunk, n_sum, text_pos_type, sum_pos_type)
+               sum_pos_type: str = "last_chunk_slice_right", drop_partial: bool = False) -> SummaryLayout:
+    return SummaryLayout(seq_len, chunk, n_sum, text_pos_type, sum_pos_type, drop_partial)
 
 
 # --------------------------------------------------------------------------
@@ -146,14 +149,14 @@ def dense_interleaved_mask(expanded_len: int, chunk: int, n_sum: int, window: in
 
 
 def two_stream_masks(seq_len: int, chunk: int, n_sum: int, window: int, device=None,
-                     q_offset: int = 0, q_len: Optional[int] = None):
+                     q_offset: int = 0, q_len: Optional[int] = None, n_summary_rows: Optional[int] = None):
     """Masks of the two-stream formulation.
 
     Returns ``(tt, ts, st, ss)``: text-query x text-key, text-query x summary-key,
     summary-query x text-key, summary-query x summary-key.  ``q_offset``/``q_len``
     restrict the text queries to a slice (context-parallel shards).
     """
-    n_chunks = (seq_len + chunk - 1) // chunk
+    n_chunks = (seq_len + chunk - 1) // chunk if n_summary_rows is None else n_summary_rows // max(n_sum, 1)
     q_len = seq_len - q_offset if q_len is None else q_len
     t = torch.arange(q_offset, q_offset + q_len, device=device)
     u = torch.arange(seq_len, device=device)

@@ -117,7 +117,7 @@ def ksa_attention(q_t, k_t, v_t, q_s, k_s, v_s, chunk: int, n_sum: int, window: 
     B, L, Hq, D = q_t.shape
     n_rep = Hq // k_t.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    tt, ts, st, ss = two_stream_masks(L, chunk, n_sum, window, device=q_t.device)
+    tt, ts, st, ss = two_stream_masks(L, chunk, n_sum, window, device=q_t.device, n_summary_rows=q_s.shape[1])
     if skip_old_summary:
         ts = torch.zeros_like(ts)
     k_all = torch.cat([_expand_kv(k_t, n_rep), _expand_kv(k_s, n_rep)], dim=1)

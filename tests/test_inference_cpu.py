@@ -1,0 +1,50 @@
+"""Ring-buffer decoding equals recomputing the whole sequence with the training graph (CPU, fp32)."""
+import pytest
+import torch
+
+from ksa_b200.config import get_preset
+from ksa_b200.inference import KsaInferenceEngine
+from ksa_b200.models import get_model_class
+
+
+def _model(chunk=8, n_sum=1, window=2, layers=4, freq=None):
+    cfg = get_preset("qwen3-ksa-tiny").merge({
+        "num_layers": layers, "summary_layer_freq": freq or [1, 1, 0, 1][:layers], "embed_dim": 64,
+        "intermediate_dim": 128, "vocab_size": 128, "head_dim": 16, "num_heads": 4, "num_kv_heads": 2,
+        "summary_chunk_size": chunk, "summary_token_num": n_sum, "summary_sliding_chunk_num": window})
+    torch.manual_seed(0)
+    m = get_model_class(cfg.model_class)(cfg)
+    m.init_weights(seed=0)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() >= 2:
+                p.mul_(3.0)   # make attention patterns non-trivial
+    return m.eval()
+
+
+@pytest.mark.parametrize("chunk,n_sum,window,prompt_len", [(8, 1, 2, 21), (8, 2, 1, 16), (4, 1, 3, 5), (8, 1, 0, 19)])
+def test_decode_matches_full_recompute(chunk, n_sum, window, prompt_len):
+    model = _model(chunk, n_sum, window)
+    B, new = 2, 3 * chunk + 2
+    torch.manual_seed(1)
+    prompt = torch.randint(0, model.config.vocab_size, (B, prompt_len))
+    eng = KsaInferenceEngine(model, max_len=prompt_len + new + 4, batch=B)
+    seq = prompt
+    logits = eng.prefill(prompt)
+    model.drop_partial_summary = True
+    for step in range(new):
+        with torch.no_grad():
+            full = model(seq)[:, -1].float()
+        assert torch.allclose(logits, full, atol=2e-4, rtol=1e-3), (step, (logits - full).abs().max())
+        nxt = full.argmax(-1)
+        seq = torch.cat([seq, nxt[:, None]], dim=1)
+        logits = eng.decode_step(nxt)
+
+
+def test_generate_runs_and_cache_is_smaller_than_full_attention():
+    model = _model(8, 1, 2)
+    eng = KsaInferenceEngine(model, max_len=256, batch=1)
+    out = eng.generate(torch.randint(0, 128, (1, 30)), max_new_tokens=20)
+    assert out.shape == (1, 50)
+    full = 2 * 256 * model.config.num_kv_heads * model.config.head_dim * 4 * model.config.num_layers
+    assert eng.cache_bytes() < full

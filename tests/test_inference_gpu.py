@@ -1,0 +1,70 @@
+"""Decode attention / cache kernels and the inference engine on the GPU against the CPU formulas."""
+import copy
+
+import pytest
+import torch
+
+from ksa_b200.config import get_preset
+from ksa_b200.inference import KsaInferenceEngine
+from ksa_b200.inference.engine import _cache_append, _cache_move, _decode_attention
+from ksa_b200.models import get_model_class
+from ksa_b200.ops import _lib, reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,Tq,Hq,Hkv,D,cap", [(2, 1, 8, 2, 128, 1500), (1, 2, 4, 2, 64, 300), (3, 1, 16, 8, 128, 9000)])
+def test_decode_attention_kernel(B, Tq, Hq, Hkv, D, cap):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = torch.randn(B, Tq, Hq, D, device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Hkv, cap, D, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Hkv, cap, D, device="cuda", generator=g).to(torch.bfloat16)
+    start = torch.randint(0, cap // 4, (B, Tq), device="cuda", dtype=torch.int32)
+    length = torch.randint(1, cap // 2, (B, Tq), device="cuda", dtype=torch.int32)
+    out = _decode_attention(q, k, v, start, length, D ** -0.5)
+    _lib.check_status()
+    for t in range(Tq):
+        expect = ref.decode_attention(q[:, t:t + 1].float(), k.float(), v.float(), length[:, t].long(), start[:, t].long(), D ** -0.5)
+        err = (out[:, t:t + 1].float() - expect).norm() / expect.norm()
+        assert err < 1.5e-2, (t, err)
+
+
+def test_cache_append_and_move():
+    B, T, H, D, cap = 2, 3, 2, 128, 64
+    k_new = torch.randn(B, T, H, D, device="cuda").to(torch.bfloat16)
+    v_new = torch.randn(B, T, H, D, device="cuda").to(torch.bfloat16)
+    kc = torch.zeros(B, H, cap, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    slots = torch.tensor([[5, -1, 7], [0, 63, 2]], device="cuda", dtype=torch.int32)
+    _cache_append(k_new, v_new, kc, vc, slots)
+    assert torch.equal(kc[0, :, 5], k_new[0, 0]) and torch.equal(vc[1, :, 63], v_new[1, 1])
+    assert kc[0, :, 6].abs().sum() == 0
+    src = torch.tensor([5, 0], device="cuda", dtype=torch.int32)
+    dst = torch.tensor([20, 30], device="cuda", dtype=torch.int32)
+    en = torch.tensor([1, 0], device="cuda", dtype=torch.int32)
+    _cache_move(kc, vc, src, dst, en, 3)
+    assert torch.equal(kc[0, :, 20:23], kc[0, :, 5:8]) and kc[1, :, 30:33].abs().sum() == 0
+    _lib.check_status()
+
+
+def test_engine_matches_cpu_engine():
+    cfg = get_preset("qwen3-ksa-tiny").merge({"head_dim": 128, "num_heads": 4, "num_kv_heads": 2, "embed_dim": 256,
+                                               "summary_chunk_size": 128, "summary_sliding_chunk_num": 2})
+    torch.manual_seed(0)
+    cpu_model = get_model_class(cfg.model_class)(cfg)
+    cpu_model.init_weights(seed=0)
+    with torch.no_grad():
+        for p in cpu_model.parameters():
+            p.copy_(p.to(torch.bfloat16).float())
+    gpu_model = copy.deepcopy(cpu_model).cuda().to(torch.bfloat16)
+    B, L, new = 2, 300, 100     # crosses the chunk boundary at 384
+    prompt = torch.randint(0, cfg.vocab_size, (B, L))
+    e_cpu = KsaInferenceEngine(cpu_model, max_len=512, batch=B)
+    e_gpu = KsaInferenceEngine(gpu_model, max_len=512, batch=B)
+    lc, lg = e_cpu.prefill(prompt), e_gpu.prefill(prompt.cuda())
+    for step in range(new):
+        err = (lg.cpu() - lc).norm() / lc.norm()
+        assert err < 5e-2, (step, err)
+        nxt = lc.argmax(-1)
+        lc, lg = e_cpu.decode_step(nxt), e_gpu.decode_step(nxt.cuda())
+    _lib.check_status()
