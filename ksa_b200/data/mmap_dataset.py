@@ -9,7 +9,8 @@ File formats and batch contract follow the reference (``muse/data/datasets/kai_m
   RNG; each source hands out its samples in order and wraps around at the end of an epoch; rank/worker ``k``
   takes positions ``k, k+stride, ...`` of the draw;
 * ``state_dict`` holds per-source cursors, epochs, consumed tokens and the RNG state; cursors are rescaled when
-  the sequence length changes between stages (8k -> 32k -> ...);
+  the sequence length changes between stages (8k -> 32k -> ...); a draw that was handed out only in part is part of
+  the state, so a resume continues with exactly the next sample;
 * batches are ``{"input_ids" [1,L], "loss_mask" [1,L], "position_ids" [1,L], "cu_seqlens" [0,L], "data_source",
   "data_domain"}``.
 
@@ -181,6 +182,7 @@ class BlendableWeightedSamplingDataset(torch.utils.data.IterableDataset):
         self.consume_sample = {n: 0 for n in self._datasets}
         self.consume_token = {n: 0 for n in self._datasets}
         self.past_epoch = {n: 0 for n in self._datasets}
+        self._pending = None   # (names, indices, next position) of a draw that has been handed out only in part
 
     @property
     def size(self) -> int:
@@ -192,11 +194,14 @@ class BlendableWeightedSamplingDataset(torch.utils.data.IterableDataset):
             out[name] = {"past_epoch": self.past_epoch[name], "c_sample": self.consume_sample[name],
                          "c_token": self.consume_token[name], "num_tokens": d.size}
         out["rng_state"] = self._rng.bit_generator.state
+        out["pending_draw"] = self._pending
         return out
 
     def load_state_dict(self, state: dict, old_seq_length: Optional[int] = None, seq_length: Optional[int] = None) -> None:
         if "rng_state" in state:
             self._rng.bit_generator.state = state["rng_state"]
+        same_length = not (old_seq_length and seq_length and old_seq_length != seq_length)
+        self._pending = state.get("pending_draw") if same_length else None
         for name in self._datasets:
             if name not in state:
                 continue  # a corpus added since the checkpoint starts from zero
@@ -227,10 +232,18 @@ class BlendableWeightedSamplingDataset(torch.utils.data.IterableDataset):
         info = torch.utils.data.get_worker_info()
         worker = 0 if info is None else info.id
         stride = self._num_workers * self._dp_world_size
+        first = self._dp_rank + worker * self._dp_world_size
         while True:
-            names, index = self._draw()
-            for pos in range(self._dp_rank + worker * self._dp_world_size, self.global_bs, stride):
+            if self._pending is not None:
+                names, index, start = self._pending
+            else:
+                names, index = self._draw()
+                start = first
+            for pos in range(start, self.global_bs, stride):
+                nxt = pos + stride
+                self._pending = (names, index, nxt) if nxt < self.global_bs else None
                 yield self._datasets[names[pos]][index[pos]], names[pos]
+            self._pending = None
 
 
 class KaiMMapDataset(torch.utils.data.IterableDataset):

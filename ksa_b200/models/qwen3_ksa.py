@@ -267,12 +267,13 @@ class Qwen3Model(Model):
                     nn.init.ones_(m.scale)
 
     # ---- forward ----------------------------------------------------------------
-    def _meta(self, B: int, L: int, device, position_ids) -> BatchMeta:
+    def _meta(self, B: int, L: int, device, position_ids, use_summary: bool = True) -> BatchMeta:
+        layout = self._layout(L) if use_summary else None
         if position_ids is not None:
-            return BatchMeta(B, L, self._layout(L), device, self.config.rope_impl == "llama", position_ids)
-        key = (B, L, str(device), self.drop_partial_summary)
+            return BatchMeta(B, L, layout, device, self.config.rope_impl == "llama", position_ids)
+        key = (B, L, str(device), self.drop_partial_summary, use_summary)
         if key not in self._meta_cache:
-            self._meta_cache[key] = BatchMeta(B, L, self._layout(L), device, self.config.rope_impl == "llama")
+            self._meta_cache[key] = BatchMeta(B, L, layout, device, self.config.rope_impl == "llama")
         return self._meta_cache[key]
 
     def embed(self, tokens: torch.Tensor, meta: BatchMeta) -> torch.Tensor:
@@ -286,14 +287,17 @@ class Qwen3Model(Model):
 
     def forward(self, tokens: torch.Tensor, labels: Optional[torch.Tensor] = None,
                 position_ids: Optional[torch.Tensor] = None, return_hidden: bool = False,
-                collect_attn: bool = False, ignore_index: int = -100, kv_sink=None, last_token_only: bool = False):
+                collect_attn: bool = False, ignore_index: int = -100, kv_sink=None, last_token_only: bool = False,
+                use_summary: bool = True):
         """``tokens`` ``[B, L]`` -> loss (with ``labels``), hidden ``[B, L, D]`` or logits ``[B, L, V]``.
 
         ``labels`` are already shifted (label of position t is token t+1) with ``ignore_index`` where masked,
         as the reference trainer builds them (``recipes/pretrain_kai_summary_unified.py:867-873``).
         """
         B, L = tokens.shape
-        meta = self._meta(B, L, tokens.device, position_ids)
+        # use_summary=False runs every layer as plain causal attention on the base projections (the distillation
+        # teacher: same weights, no summary tokens, recipes/pretrain_kai_summary_unified.py:967-997)
+        meta = self._meta(B, L, tokens.device, position_ids, use_summary)
         meta.kv_sink = kv_sink
         x = self.embed(tokens, meta)
         collect = [] if collect_attn else None

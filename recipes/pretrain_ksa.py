@@ -1,0 +1,332 @@
+#!/usr/bin/env python
+"""Pre-training entry point for Qwen3 / Qwen3-KSA (counterpart of ``recipes/pretrain_kai_summary_unified.py``).
+
+One process per GPU, launched with ``torchrun`` (``RANK / LOCAL_RANK / WORLD_SIZE``) or ``mpirun``
+(``OMPI_COMM_WORLD_*``).  The flag set is a superset of the reference recipe's (``:79-261``); flags that configure
+machinery this framework does not have (FlashAttention-2 selection, CPU offload, forward prefetch, resharding) are
+accepted and ignored with a note, so the reference's launch scripts run unchanged.
+
+Flow (``:326-1170`` of the reference): parse -> process group -> model config -> model on the meta device -> engine
+(single GPU, or FSDP with the fused P2P kernels) -> optional weight / optimizer / dataloader resume -> loop of
+``next batch -> labels -> step -> metrics -> periodic checkpoint``.  Differences that matter for speed: summary-token
+layout is closed form (no per-step batch expansion), the loss head is the fused chunked linear+CE, the optimizer is
+fused into the gradient reduction, and nothing in the step reads the device back except at the logging cadence.
+"""
+from __future__ import annotations
+
+import argparse
+import gc
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def get_argument_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(description="Qwen3-KSA pre-training")
+    a = p.add_argument
+    # model / data
+    a("--model-config", required=True, help="model JSON (reference format) or a preset name")
+    a("--dataset-class", default="KaiMMapDataset")
+    a("--dataset-config", default=None, help="dataset JSON; omit (or 'synthetic') for uniform-random token ids")
+    a("--max-length", type=int, default=None, help="overrides the dataset's seq_length")
+    a("--batch-size", type=int, default=1)
+    a("--shuffle-buffer-size", type=int, default=0)
+    a("--use-dataset-load-balance", action="store_true")
+    a("--packing", action="store_true")
+    # checkpoints
+    a("--model-dir", default=None, help="HF directory to initialise the weights from")
+    a("--checkpoint-dir", default=None)
+    a("--checkpoint-id", default=None)
+    a("--resume-weights", action="store_true")
+    a("--resume-optimizer", action="store_true")
+    a("--resume-dataloader", action="store_true")
+    a("--save-checkpoint-per-step", type=int, default=0)
+    a("--save-checkpoint-every-epoch", action="store_true")
+    a("--async-checkpoint", action="store_true")
+    a("--output-dir", required=True)
+    a("--enable-dataset-checkpointing", action="store_true")
+    # precision / sharding
+    a("--model-dtype", default="bfloat16", choices=["bfloat16", "float16", "float32"])
+    a("--cpu-offload", action="store_true")
+    a("--fp32-weight", action="store_true", help="fp32 master weights (always on in this engine)")
+    a("--fp32-reduce", action="store_true", help="fp32 gradient reduction (always on in this engine)")
+    a("--reshard-after-forward", action="store_true")
+    a("--prefetch-params-in-forward", action="store_true")
+    a("--comm", default=None, choices=["fused", "collective"], help="FSDP back end (default: fused on GPUs)")
+    a("--no-cuda-graph", action="store_true")
+    # optimisation
+    a("--lr-scheduler-type", default="wsd", choices=["cosine", "cosine_v2", "wsd", "constant"])
+    a("--num-warmup-steps", type=int, default=0)
+    a("--num-decay-steps", type=int, default=0)
+    a("--num-training-steps", type=int, default=1000)
+    a("--num-epochs", type=int, default=1)
+    a("--min-lr", type=float, default=0.0)
+    a("--learning-rate", type=float, default=4e-4)
+    a("--weight-decay", type=float, default=0.01)
+    a("--beta1", type=float, default=0.9)
+    a("--beta2", type=float, default=0.95)
+    a("--clip-range", type=float, default=1.0)
+    a("--use-flash-attention-2", action="store_true")
+    a("--enable-gradient-checkpointing", action="store_true")
+    a("--gradient-accumulation-steps", type=int, default=1)
+    a("--allow-random-init-params", default="")
+    a("--context-parallel-size", type=int, default=1)
+    a("--chunked-loss-minibatch-size", type=int, default=2048)
+    a("--disable-chunked-loss", action="store_true")
+    # logging
+    a("--logging-per-step", type=int, default=10)
+    a("--monitor-datasource-loss", action="store_true")
+    a("--log-attn-stats", action="store_true")
+    a("--comment", default="")
+    a("--commit-id", default="")
+    a("--seed", type=int, default=None)
+    a("--enable-profile", action="store_true")
+    a("--overfit-batches", type=int, default=0)
+    # distillation
+    a("--enable-distill", action="store_true")
+    a("--distill-lm-loss-factor", type=float, default=1.0)
+    a("--distill-kl-loss-factor", type=float, default=5.0)
+    a("--distill-attn-mse-factor", type=float, default=5.0)
+    a("--distill-attn-cos-factor", type=float, default=0.0)
+    return p
+
+
+def _env_rank():
+    e = os.environ
+    rank = int(e.get("RANK", e.get("OMPI_COMM_WORLD_RANK", "0")))
+    world = int(e.get("WORLD_SIZE", e.get("OMPI_COMM_WORLD_SIZE", "1")))
+    local = int(e.get("LOCAL_RANK", e.get("OMPI_COMM_WORLD_LOCAL_RANK", "0")))
+    return rank, world, local
+
+
+def _load_model_config(spec: str):
+    from ksa_b200.config import get_preset, load_config, PRESETS
+    return get_preset(spec) if spec in PRESETS else load_config(spec)
+
+
+def _build_dataset(args, cfg, dp_rank: int, dp_size: int):
+    from ksa_b200.data.mmap_dataset import KaiMMapDataset, SyntheticTokenDataset
+    if not args.dataset_config or args.dataset_config == "synthetic":
+        return SyntheticTokenDataset(cfg.vocab_size, args.max_length or 8192, args.seed or 0, dp_rank, args.batch_size)
+    dc = json.load(open(args.dataset_config))
+    if dc.pop("name", args.dataset_class) != "KaiMMapDataset":
+        raise ValueError("only KaiMMapDataset (mmap token corpora) and synthetic data are supported")
+    if args.max_length:
+        dc["seq_length"] = args.max_length
+    return KaiMMapDataset(rank=dp_rank, world_size=dp_size, **dc)
+
+
+def train(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    from ksa_b200.data.mmap_dataset import make_labels
+    from ksa_b200.losses import attention_cosine_loss, attention_mse_loss
+    from ksa_b200.models import get_model_class
+    from ksa_b200.parallel import groups
+    from ksa_b200.training import checkpoint as ckpt
+    from ksa_b200.training.activations import set_activation_checkpointing
+    from ksa_b200.training.common import StepScheduler, freeze_params_by_pattern, to_dtype
+    from ksa_b200.training.lr_schedulers import get_lr_lambda
+    from ksa_b200.utils import print_rank_0, set_random_seed
+    from ksa_b200.utils.metrics import CSVBackend, StdoutBackend, initialize_metrics
+    from ksa_b200.utils.mfu import mfu as mfu_report
+
+    gc.disable()
+    rank, world, local = _env_rank()
+    use_cuda = torch.cuda.is_available()
+    if use_cuda:
+        torch.cuda.set_device(local)
+    device = torch.device("cuda", local) if use_cuda else torch.device("cpu")
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl" if use_cuda else "gloo", rank=rank, world_size=world,
+                                **({"device_id": device} if use_cuda else {}))
+    cp = args.context_parallel_size
+    if world > 1:
+        groups.initialize_model_parallel(cp)
+    dp_rank, dp_size = (groups.get_data_parallel_rank(), groups.get_data_parallel_world_size()) if world > 1 else (0, 1)
+    if args.seed is not None:
+        set_random_seed(args.seed)
+    os.makedirs(args.output_dir, exist_ok=True)
+    if rank == 0:
+        json.dump(vars(args), open(os.path.join(args.output_dir, f"args-{int(time.time())}.json"), "w"), indent=2)
+    for flag in ("cpu_offload", "reshard_after_forward", "prefetch_params_in_forward", "use_flash_attention_2", "packing"):
+        if getattr(args, flag):
+            print_rank_0(f"[recipe] --{flag.replace('_', '-')} has no effect in this framework (accepted for compatibility)")
+
+    cfg = _load_model_config(args.model_config)
+    dtype = to_dtype(args.model_dtype) if use_cuda else torch.float32
+    with torch.device("meta"):
+        model = get_model_class(cfg.model_class)(cfg)
+    model = model.to_empty(device=device).to(dtype)
+    if args.model_dir:
+        state = model.convert_hf_state_dict(ckpt.load_hf_checkpoint(args.model_dir))
+        allow = [s for s in args.allow_random_init_params.split(",") if s]
+        model.init_weights(seed=args.seed or 0)
+        missing, unexpected = model.load_state_dict(state, strict=False)
+        bad = [m for m in missing if not any(a in m for a in allow)]
+        if bad:
+            raise RuntimeError(f"{args.model_dir} lacks parameters not listed in --allow-random-init-params: {bad[:5]}")
+    else:
+        # every rank initialises from the same seed: identical weights with no broadcast (the reference initialises on
+        # rank 0 and broadcasts parameter by parameter, muse/training/distributed.py:448-532)
+        model.init_weights(seed=args.seed or 0)
+    model.loss_chunk_tokens = args.chunked_loss_minibatch_size
+    if args.enable_gradient_checkpointing:
+        n = set_activation_checkpointing(model, model.get_checkpointable_module_classes())
+        print_rank_0(f"[recipe] activation checkpointing on {n} layers")
+    if args.enable_distill:
+        stats = freeze_params_by_pattern(model, ["summary_embedding", "_summary"])
+        print_rank_0(f"[recipe] distillation: {stats['trainable']:,} trainable / {stats['frozen']:,} frozen parameters")
+
+    lr_lambda = get_lr_lambda(args.lr_scheduler_type, num_warmup_steps=args.num_warmup_steps,
+                              num_training_steps=args.num_training_steps, num_decay_steps=args.num_decay_steps,
+                              base_lr=args.learning_rate, min_lr=args.min_lr)
+    common = dict(lr=args.learning_rate, betas=(args.beta1, args.beta2), eps=1e-8, weight_decay=args.weight_decay,
+                  clip_value=args.clip_range, lr_lambda=lr_lambda, grad_accum_steps=args.gradient_accumulation_steps)
+    if world > 1:
+        from ksa_b200.parallel.fsdp import FsdpEngine
+        engine = FsdpEngine(model, world_size=world, rank=rank, comm=args.comm, **common)
+    else:
+        from ksa_b200.training.engine import TrainEngine
+        engine = TrainEngine(model, **common)
+    sched = StepScheduler(args.gradient_accumulation_steps, args.logging_per_step, args.save_checkpoint_per_step)
+
+    dataset = _build_dataset(args, cfg, dp_rank, dp_size)
+    seq_len = getattr(dataset, "seq_length", args.max_length or 8192)
+    checkpointer = ckpt.DistributedCheckpointer(async_save=args.async_checkpoint)
+    step_offset = 0
+    if args.checkpoint_dir and (args.resume_weights or args.resume_optimizer):
+        app = ckpt.AppState(engine, sched, skip_optimizer=not args.resume_optimizer,
+                            skip_training_state=not args.resume_optimizer)
+        loaded = ckpt.load_checkpoint(app, checkpointer, args.checkpoint_dir, args.checkpoint_id)
+        if loaded is not None:
+            print_rank_0(f"[recipe] resumed from step {loaded} of {args.checkpoint_dir}")
+            step_offset = loaded - sched.global_step
+            if args.resume_dataloader:
+                ok = ckpt.load_dataloader_state(dataset, ckpt.get_checkpoint_path(args.checkpoint_dir, args.checkpoint_id))
+                print_rank_0(f"[recipe] dataloader state {'restored' if ok else 'not found: starting the stream over'}")
+    metrics = initialize_metrics(seq_len, world, args.logging_per_step,
+                                 [StdoutBackend(), CSVBackend(os.path.join(args.output_dir, "metrics.csv"))])
+    profiler = None
+    if args.enable_profile:
+        from torch.profiler import ProfilerActivity, profile, schedule
+        profiler = profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA],
+                           schedule=schedule(wait=50, warmup=1, active=10, repeat=1),
+                           on_trace_ready=lambda p: p.export_chrome_trace(
+                               os.path.join(args.output_dir, "torch_profile", f"{p.step_num}_w{rank}.json")))
+        os.makedirs(os.path.join(args.output_dir, "torch_profile"), exist_ok=True)
+        profiler.start()
+
+    use_graph = use_cuda and world == 1 and not args.no_cuda_graph and not args.enable_distill \
+        and not args.enable_gradient_checkpointing
+    data_iter = iter(dataset)
+    cached = []
+    last_loss = None
+    t_prev = time.perf_counter()
+    while sched.global_step + step_offset < args.num_training_steps:
+        if args.overfit_batches and len(cached) >= args.overfit_batches:
+            batch = cached[sched.micro_step % args.overfit_batches]
+        else:
+            batch = next(data_iter)
+            if args.overfit_batches:
+                cached.append(batch)
+        ids = batch["input_ids"]
+        labels, _ = make_labels(ids, batch["loss_mask"])
+        if "next_token" in batch:   # the corpus stores L+1 tokens: the last position has a real target
+            labels[:, -1] = batch["next_token"]
+        if hasattr(model, "set_mix_coeff"):
+            model.set_mix_coeff(sched.global_step + step_offset)
+        if args.enable_distill:
+            loss = _distill_step(engine, model, ids.to(device), labels.to(device), args, attention_mse_loss,
+                                 attention_cosine_loss)
+        elif use_graph:
+            loss = engine.graphed_step(ids.pin_memory() if use_cuda else ids, labels.pin_memory() if use_cuda else labels)
+        else:
+            loss = engine.train_step(ids, labels)
+        sched.step()
+        metrics.loss.append(loss)
+        metrics.tokens.append(ids.numel())
+        metrics.samples.append(ids.shape[0])
+        if sched.is_gradient_accumulation_boundary():
+            metrics.grad_norm.append(engine.grad_norm())
+            metrics.learning_rate.append(engine.current_lr(max(engine.step_count - 1, 0)))
+            if use_cuda:
+                torch.cuda.current_stream().synchronize() if sched.should_logging() else None
+            now = time.perf_counter()
+            metrics.step_time.append(now - t_prev)
+            t_prev = now
+        metrics.step()
+        if sched.should_logging():
+            scalars = metrics.write(sched.global_step + step_offset)
+            last_loss = scalars.get("loss", last_loss)
+            if rank == 0 and "tokens_per_sec_per_gpu" in scalars:
+                rep = mfu_report(scalars["tokens_per_sec_per_gpu"], cfg, seq_len,
+                                 grad_checkpointing=args.enable_gradient_checkpointing, distill=args.enable_distill)
+                print(f"[Metrics] step={sched.global_step + step_offset} | " +
+                      " | ".join(f"{k}={v:.4g}" for k, v in rep.items()), flush=True)
+        if args.save_checkpoint_per_step and sched.should_save_checkpoint() and not args.overfit_batches:
+            gc.collect()
+            step = sched.global_step + step_offset
+            ckpt.save_checkpoint(ckpt.AppState(engine, sched), checkpointer, args.output_dir, step)
+            if args.enable_dataset_checkpointing:
+                ckpt.save_dataloader_state(dataset, args.output_dir, step)
+        if profiler is not None:
+            profiler.step()
+    checkpointer.wait()
+    if profiler is not None:
+        profiler.stop()
+    metrics.close()
+    if hasattr(engine, "close"):
+        engine.close()
+    if world > 1:
+        dist.barrier()
+    return {"steps": sched.global_step + step_offset, "loss": last_loss}
+
+
+def _distill_step(engine, model, ids, labels, args, mse_fn, cos_fn):
+    """Student forward (with summaries) + no-grad teacher forward (same weights, no summaries): LM + KL + attention
+    matching losses (``recipes/pretrain_kai_summary_unified.py:967-1013``)."""
+    import torch
+    from ksa_b200.losses import ChunkedDistillLossComputer
+    from ksa_b200.losses.distill import rms_normalize
+    if engine.micro_step == 0:
+        engine.zero_grad()
+    model.skip_output_layer = True
+    with torch.no_grad():
+        t_hidden = model(ids, collect_attn=True, use_summary=False)
+        t_attn = list(model.last_attn_outputs)
+    s_hidden = model(ids, collect_attn=True)
+    s_attn = list(model.last_attn_outputs)
+    model.skip_output_layer = False
+    if getattr(model.config, "summary_distill_attention_norm", False):
+        s_attn, t_attn = [rms_normalize(a) for a in s_attn], [rms_normalize(a) for a in t_attn]
+    extra = args.distill_attn_mse_factor * mse_fn(s_attn, t_attn)
+    if args.distill_attn_cos_factor:
+        extra = extra + args.distill_attn_cos_factor * cos_fn(s_attn, t_attn)
+    comp = ChunkedDistillLossComputer(model.lm_head_weight, args.chunked_loss_minibatch_size,
+                                      args.distill_lm_loss_factor, args.distill_kl_loss_factor, enable_kl=True)
+    out = comp.forward_and_backward(s_hidden, t_hidden, labels, engine.grad_accum_steps, extra_loss=extra)
+    engine.micro_step += 1
+    if engine.micro_step == engine.grad_accum_steps:
+        engine._write_hyper()
+        engine.optimizer_step()
+        engine.step_count += 1
+        engine.micro_step = 0
+    return out["total_loss"]
+
+
+def main(argv=None):
+    args = get_argument_parser().parse_args(argv)
+    out = train(args)
+    if _env_rank()[0] == 0:
+        print(json.dumps({"done": True, **{k: (float(v) if v is not None else None) for k, v in out.items()}}))
+
+
+if __name__ == "__main__":
+    main()
