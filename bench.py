@@ -45,6 +45,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--preset", default="qwen3-1.9b-ksa")
+    ap.add_argument("--cp", type=int, default=1,
+                    help="context-parallel size: --seq-len is the whole sequence, split over groups of this many ranks")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--comm", default=None, choices=["fused", "collective"],
                     help="multi-GPU back end: fused P2P kernels (default) or NCCL collectives (A/B baseline)")
@@ -144,9 +146,22 @@ def run_ours(args) -> dict:
     engine = Engine(model, lr=4e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, clip_value=1.0, **extra)
 
     B, L = 1, args.seq_len
-    g_cpu = torch.Generator().manual_seed(1234 + rank)
+    cp, dp = args.cp, world // max(args.cp, 1)
+    if cp > 1:
+        from ksa_b200.parallel.cp import CpContext
+        if world % cp:
+            raise SystemExit(f"--cp {cp} does not divide {world} ranks")
+        groups = [dist.new_group(list(range(i * cp, (i + 1) * cp))) for i in range(dp)] if dp > 1 else [dist.group.WORLD]
+        full_layers = any(not f for f in model._layer_is_summary())
+        model.cp = CpContext(groups[rank // cp], L, cfg.summary_chunk_size, cfg.summary_token_num, cfg.num_kv_heads,
+                             cfg.head_dim, batch=B, device=dev, full_layers=full_layers,
+                             max_window=cfg.summary_sliding_chunk_num)
+    g_cpu = torch.Generator().manual_seed(1234 + rank // cp)     # one sequence per context-parallel group
     n_batches = max(args.steps, 4)
     host_tokens = [torch.randint(0, cfg.vocab_size, (B, L + 1), generator=g_cpu) for _ in range(n_batches)]
+    if cp > 1:   # this rank's contiguous shard of inputs and (already shifted) labels
+        Ll, r = L // cp, rank % cp
+        host_tokens = [torch.cat([t[:, r * Ll:(r + 1) * Ll], t[:, (r + 1) * Ll:(r + 1) * Ll + 1]], dim=1) for t in host_tokens]
     host_in = [t[:, :-1].contiguous().pin_memory() for t in host_tokens]
     host_lab = [t[:, 1:].contiguous().pin_memory() for t in host_tokens]
     dev_in = [t.to(dev) for t in host_in]
@@ -200,17 +215,18 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_dev, ms_e2e = t.tolist()
-    tokens_per_step = world * B * L
+    tokens_per_step = dp * B * L
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
     e2e_value = tokens_per_step * args.steps / (ms_e2e / 1e3)
-    h2d = 2 * B * L * 8
+    h2d = 2 * B * (L // cp) * 8
     out = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
         "impl": "ours",
-        "config": {"model": MODEL_NAME, "global_batch": world * B, "seq_len": L,
-                   "parallelism": f"fsdp{world}" if world > 1 else "single", "layers": cfg.num_layers,
+        "config": {"model": MODEL_NAME, "global_batch": dp * B, "seq_len": L,
+                   "parallelism": (f"fsdp{world}" + (f"+cp{cp}" if cp > 1 else "")) if world > 1 else "single",
+                   "layers": cfg.num_layers,
                    "chunk": cfg.summary_chunk_size, "window_chunks": 8, "optimizer": "AdamW fp32 master",
                    "l2": "working set (weights+optimizer state+activations, >30 GB) exceeds L2; no explicit flush",
                    "cuda_graph": use_graph, "comm": getattr(engine, "comm", "none"),
@@ -222,6 +238,8 @@ def run_ours(args) -> dict:
         "loss_first": loss0, "loss_last": last,
     }
     if world > 1:
+        if model.cp is not None:
+            model.cp.close()
         if hasattr(engine, "close"):
             engine.close()
         dist.destroy_process_group()

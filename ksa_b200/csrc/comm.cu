@@ -42,6 +42,54 @@ __global__ void signal_wait_kernel(const uint32_t* flags, int n, const uint32_t*
   if (threadIdx.x < n) flag_wait_ge(flags + threadIdx.x, epoch_target(epoch_ptr, add), status, kTimeoutPeerFlag, true);
 }
 
+// dst (local) = src (peer or local) for nbytes (multiple of 16), after an optional bounded wait on a local flag.
+__global__ void __launch_bounds__(kCommThreads)
+peer_copy_kernel(uint8_t* dst, const uint8_t* src, long long nbytes, const uint32_t* flag, const uint32_t* epoch_ptr,
+                 uint32_t add, int* status) {
+  __shared__ int s_ok;
+  if (flag) {
+    if (threadIdx.x == 0) s_ok = flag_wait_ge(flag, epoch_target(epoch_ptr, add), status, kTimeoutPeerFlag, true) ? 1 : 0;
+    __syncthreads();
+    if (!s_ok) return;
+  }
+  const long long vecs = nbytes / 16, stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < vecs; i += 4 * stride) {
+    const uint4 a = ld_peer_16(src + i * 16), b = ld_peer_16(src + (i + stride) * 16);
+    const uint4 c = ld_peer_16(src + (i + 2 * stride) * 16), d = ld_peer_16(src + (i + 3 * stride) * 16);
+    *reinterpret_cast<uint4*>(dst + i * 16) = a;
+    *reinterpret_cast<uint4*>(dst + (i + stride) * 16) = b;
+    *reinterpret_cast<uint4*>(dst + (i + 2 * stride) * 16) = c;
+    *reinterpret_cast<uint4*>(dst + (i + 3 * stride) * 16) = d;
+  }
+  for (; i < vecs; i += stride) *reinterpret_cast<uint4*>(dst + i * 16) = ld_peer_16(src + i * 16);
+}
+
+// dst (local bf16) += src (peer bf16) over n elements (multiple of 8), fp32 adds, after an optional flag wait.
+__global__ void __launch_bounds__(kCommThreads)
+peer_add_bf16_kernel(bf16* dst, const bf16* src, long long n, const uint32_t* flag, const uint32_t* epoch_ptr,
+                     uint32_t add, int* status) {
+  __shared__ int s_ok;
+  if (flag) {
+    if (threadIdx.x == 0) s_ok = flag_wait_ge(flag, epoch_target(epoch_ptr, add), status, kTimeoutPeerFlag, true) ? 1 : 0;
+    __syncthreads();
+    if (!s_ok) return;
+  }
+  const long long vecs = n / 8, stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += stride) {
+    const uint4 a = ld_peer_16(src + i * 8);
+    uint4 d = *reinterpret_cast<uint4*>(dst + i * 8);
+    const uint32_t au[4] = {a.x, a.y, a.z, a.w};
+    uint32_t du[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 x = unpack_bf16x2(au[k]), y = unpack_bf16x2(du[k]);
+      du[k] = pack_bf16x2(x.x + y.x, x.y + y.y);
+    }
+    *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(du[0], du[1], du[2], du[3]);
+  }
+}
+
 }  // namespace ksa
 
 using namespace ksa;
@@ -151,6 +199,37 @@ KSA_API int ksa_signal_wait(const void* flags, int n, const void* epoch_ptr, uns
   KSA_REQUIRE(status != nullptr, "could not allocate the status word");
   signal_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>((const uint32_t*)flags, n,
                                                                             static_cast<const uint32_t*>(epoch_ptr), epoch_add, status);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// dst (own memory) = src (any rank's memory) for nbytes (multiple of 16).  flag (optional, own memory): wait, bounded,
+// until *flag >= *epoch_ptr + epoch_add before reading src.
+KSA_API int ksa_peer_copy(void* dst, const void* src, long long nbytes, const void* flag, const void* epoch_ptr,
+                          unsigned epoch_add, int ctas, void* stream) {
+  KSA_ENTER(dst);
+  KSA_REQUIRE(nbytes % 16 == 0, "peer_copy: nbytes must be a multiple of 16");
+  if (nbytes == 0) return 0;
+  int* status = status_word();
+  KSA_REQUIRE(status != nullptr, "could not allocate the status word");
+  if (ctas <= 0) ctas = 32;
+  peer_copy_kernel<<<ctas, kCommThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (uint8_t*)dst, (const uint8_t*)src, nbytes, (const uint32_t*)flag, (const uint32_t*)epoch_ptr, epoch_add, status);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// dst (own bf16) += src (any rank's bf16) over n elements (multiple of 8), with the same optional flag wait.
+KSA_API int ksa_peer_add_bf16(void* dst, const void* src, long long n, const void* flag, const void* epoch_ptr,
+                              unsigned epoch_add, int ctas, void* stream) {
+  KSA_ENTER(dst);
+  KSA_REQUIRE(n % 8 == 0, "peer_add_bf16: n must be a multiple of 8");
+  if (n == 0) return 0;
+  int* status = status_word();
+  KSA_REQUIRE(status != nullptr, "could not allocate the status word");
+  if (ctas <= 0) ctas = 32;
+  peer_add_bf16_kernel<<<ctas, kCommThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (bf16*)dst, (const bf16*)src, n, (const uint32_t*)flag, (const uint32_t*)epoch_ptr, epoch_add, status);
   KSA_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

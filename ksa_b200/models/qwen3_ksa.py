@@ -151,8 +151,12 @@ class KsaDecoderLayer(nn.Module):
                                               cfg.rope_base, cfg.norm_eps, meta.rope_interleaved)
             if meta.kv_sink is not None:
                 meta.kv_sink(self.layer_idx, qkv, True)
-            att = ops.attention_packed(qkv, meta.B, meta.L, meta.Ns, Hq, Hkv, Dh, meta.chunk, meta.n_sum,
-                                       self.window_chunks)
+            if meta.cp is not None:
+                from ..parallel.cp import cp_attention_packed
+                att = cp_attention_packed(qkv, meta.cp, Hq, Hkv, Dh, self.window_chunks, True)
+            else:
+                att = ops.attention_packed(qkv, meta.B, meta.L, meta.Ns, Hq, Hkv, Dh, meta.chunk, meta.n_sum,
+                                           self.window_chunks)
             attn_out = ops.linear(att, a.output_proj.weight)
             if collect is not None:
                 collect.append(attn_out[:n_text])
@@ -164,7 +168,11 @@ class KsaDecoderLayer(nn.Module):
                                       cfg.rope_base, cfg.norm_eps, meta.rope_interleaved)
         if meta.kv_sink is not None:
             meta.kv_sink(self.layer_idx, qkv, False)
-        att = ops.attention_packed(qkv, meta.B, meta.L, 0, Hq, Hkv, Dh, tok_window=self.tok_window)
+        if meta.cp is not None:
+            from ..parallel.cp import cp_attention_packed
+            att = cp_attention_packed(qkv, meta.cp, Hq, Hkv, Dh, None, False, self.tok_window)
+        else:
+            att = ops.attention_packed(qkv, meta.B, meta.L, 0, Hq, Hkv, Dh, tok_window=self.tok_window)
         attn_out = ops.linear(att, a.output_proj.weight)
         if collect is not None:
             collect.append(attn_out)
@@ -176,9 +184,25 @@ class BatchMeta:
     """Per-shape constants of a batch: sizes and the per-row position ids (text rows, then summary rows)."""
 
     def __init__(self, B: int, L: int, layout: Optional[SummaryLayout], device, rope_interleaved: bool,
-                 position_ids: Optional[torch.Tensor] = None):
+                 position_ids: Optional[torch.Tensor] = None, cp=None):
         self.B, self.L = B, L
         self.rope_interleaved = rope_interleaved
+        self.cp = cp          # context-parallel group state: this rank holds one contiguous shard of the sequence
+        self.kv_sink = None   # optional callable(layer_idx, qkv_rot, is_summary_layer): prefill fills KV caches with it
+        if cp is not None:
+            # ``layout`` describes the whole sequence; keep this shard's rows of its position ids
+            r, Ll = cp.rank, cp.shape.local_len
+            self.L = Ll
+            text = layout.text_position_ids(device) if layout is not None else torch.arange(cp.shape.seq_len, device=device)
+            parts = [text[r * Ll:(r + 1) * Ll].repeat(B)]
+            if layout is not None:
+                self.chunk, self.n_sum = layout.chunk, layout.n_sum
+                self.Ns = cp.shape.local_sum
+                parts.append(layout.summary_position_ids(device)[r * self.Ns:(r + 1) * self.Ns].repeat(B))
+            else:
+                self.Ns, self.chunk, self.n_sum = 0, 128, 1
+            self.pos = torch.cat(parts).to(torch.int32)
+            return
         if layout is not None:
             self.Ns, self.chunk, self.n_sum = layout.n_summary_rows, layout.chunk, layout.n_sum
             pos_t = layout.text_position_ids(device) if position_ids is None else None
@@ -195,7 +219,6 @@ class BatchMeta:
         if pos_s is not None and self.Ns > 0:
             parts.append(pos_s.repeat(B))
         self.pos = torch.cat(parts).to(torch.int32)
-        self.kv_sink = None   # optional callable(layer_idx, qkv_rot, is_summary_layer): prefill fills KV caches with it
 
 
 @register_model("Qwen3Model")
@@ -219,6 +242,7 @@ class Qwen3Model(Model):
         self.skip_output_layer = False
         self.loss_chunk_tokens = 2048
         self.drop_partial_summary = False   # inference: a trailing partial chunk gets no summary tokens
+        self.cp = None                      # parallel.cp.CpContext: ``forward`` then takes this rank's sequence shard
 
     # ---- configuration helpers ----------------------------------------------------
     def _layer_is_summary(self) -> List[bool]:
@@ -268,6 +292,16 @@ class Qwen3Model(Model):
 
     # ---- forward ----------------------------------------------------------------
     def _meta(self, B: int, L: int, device, position_ids, use_summary: bool = True) -> BatchMeta:
+        if self.cp is not None:
+            if position_ids is not None:
+                raise NotImplementedError("explicit position ids are not combined with context parallelism")
+            if L != self.cp.shape.local_len or B != self.cp.batch:
+                raise ValueError(f"context-parallel shard is [{self.cp.batch}, {self.cp.shape.local_len}], got [{B}, {L}]")
+            key = ("cp", B, L, str(device), use_summary)
+            if key not in self._meta_cache:
+                layout = self._layout(self.cp.shape.seq_len) if use_summary else None
+                self._meta_cache[key] = BatchMeta(B, L, layout, device, self.config.rope_impl == "llama", cp=self.cp)
+            return self._meta_cache[key]
         layout = self._layout(L) if use_summary else None
         if position_ids is not None:
             return BatchMeta(B, L, layout, device, self.config.rope_impl == "llama", position_ids)

@@ -539,6 +539,15 @@ def causal_attention(q, k, v, scale: Optional[float] = None, window: int = -1,
     return o
 
 
+def shard_causal_attention(q, k, v, scale: float, tok_window: int, q_off: int, k_off: int, seq_len: int):
+    """Causal attention of a sequence shard: query row ``i`` is global position ``q_off + i``, key row ``j`` is
+    ``k_off + j`` (context-parallel full-attention layers stage every earlier key in front of their own)."""
+    _require_bf16(q, k, v)
+    o, _ = _KsaAttentionFn.apply(q, k, v, None, None, None, 128, 1, UNBOUNDED_WINDOW,
+                                 tok_window if tok_window and tok_window > 0 else 0, scale, q_off, k_off, 0, seq_len)
+    return o
+
+
 def _packed_views(qkv: torch.Tensor, B: int, T: int, Hq: int, Hkv: int, D: int, row0: int):
     rows = qkv[row0:row0 + B * T]
     q = rows[:, :Hq * D].view(B, T, Hq, D)

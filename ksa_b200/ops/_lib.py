@@ -48,6 +48,8 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_gemm_attach_reduce_adamw": [P, I, I, L, L, P, P, P, P, P, F, F, F, F, F, P, P, P, ctypes.c_uint, I],
     "ksa_signal_set": [P, I, P, ctypes.c_uint, P],
     "ksa_signal_wait": [P, I, P, ctypes.c_uint, P],
+    "ksa_peer_copy": [P, P, L, P, P, ctypes.c_uint, I, P],
+    "ksa_peer_add_bf16": [P, P, L, P, P, ctypes.c_uint, I, P],
     "ksa_symm_alloc": [P, L],
     "ksa_symm_free": [P],
     "ksa_ipc_get_handle": [P, P],

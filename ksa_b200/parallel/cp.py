@@ -1,0 +1,314 @@
+"""Context parallelism by locality for Kwai Summary Attention.
+
+The reference shards the sequence with DeepSpeed-Ulysses: four all-to-alls per attention layer move every q, k, v and
+output row between ranks (``muse/training/parallel.py:211-335``, ``muse/models/qwen3_sa/_layers.py:179-224``).  KSA
+needs far less: rank ``r`` of a group of ``P`` owns the contiguous, chunk-aligned text rows
+``[r*Ll, (r+1)*Ll)`` and the summary rows of those chunks, and for a summary-attention layer with a window of ``W``
+chunks its queries only see
+
+* the last ``W*C`` text keys before its shard (a halo owned by rank ``r-1``, and further back only when the window
+  is longer than a shard), and
+* the summary keys of every earlier chunk (``S`` rows per chunk: tiny).
+
+So each rank stages ``[halo | own text]`` and ``[older summaries | own summaries]`` K/V buffers and runs the same
+attention kernels with index offsets (``q_off / k_off / s_off``).  In backward the gradients that land on halo and
+older-summary rows are returned to their owners, who add them.  Full-attention layers of a hybrid stack stage all
+earlier text K/V (the halo is everything before the shard).
+
+Transport:
+* GPUs: every rank publishes its K/V block in a symmetric-memory exchange buffer and the consumers pull the ranges
+  they need with P2P loads issued from kernels (``ksa_peer_copy`` / ``ksa_peer_add_bf16``), ordered by per-rank
+  flags that carry an exchange counter; each wait is bounded.  No NCCL collective is involved.
+* CPU (gloo) ranks, used by the tests: the same staging expressed with ``all_gather`` / ``all_reduce``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import _lib, reference as ref
+from ..ops.layout import two_stream_masks
+
+
+@dataclass
+class CpShape:
+    """Static description of one rank's shard."""
+    rank: int
+    size: int
+    seq_len: int      # global text length L
+    chunk: int
+    n_sum: int
+
+    @property
+    def local_len(self) -> int:
+        return self.seq_len // self.size
+
+    @property
+    def local_chunks(self) -> int:
+        return self.local_len // self.chunk
+
+    @property
+    def local_sum(self) -> int:
+        return self.local_chunks * self.n_sum
+
+    def check(self) -> None:
+        if self.seq_len % self.size or self.local_len % self.chunk:
+            raise ValueError(f"sequence {self.seq_len} must split into {self.size} chunk-aligned shards (chunk {self.chunk})")
+
+    def halo_len(self, window_chunks: Optional[int]) -> int:
+        """Text keys before the shard that its queries can see (``None`` = full attention: everything)."""
+        before = self.rank * self.local_len
+        if window_chunks is None:
+            return before
+        return min(before, window_chunks * self.chunk)
+
+
+class CpContext:
+    """Group, shard shape and (on GPUs) the symmetric exchange buffers of one context-parallel group."""
+
+    def __init__(self, group, seq_len: int, chunk: int, n_sum: int, n_kv_heads: int, head_dim: int, batch: int = 1,
+                 device=None, dtype=torch.bfloat16, full_layers: bool = False, max_window: int = 8):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+        self.shape = CpShape(self.rank, self.size, seq_len, chunk, n_sum)
+        self.shape.check()
+        self.batch = batch
+        self.kv_width = 2 * n_kv_heads * head_dim          # K | V per row
+        self.device = device
+        self.fused = device is not None and torch.device(device).type == "cuda"
+        self.counter = 0                                    # exchanges issued so far (same on every rank)
+        if self.fused:
+            from .symm import SignalPad, SymmetricBuffer
+            rows = batch * (self.shape.local_len + self.shape.local_sum)
+            item = torch.empty((), dtype=dtype).element_size()
+            self.rows = rows
+            self.slot_bytes = rows * self.kv_width * item
+            # two slots for forward K/V blocks, two (sized for the largest halo) for returned gradients
+            self.ret_slot_bytes = max(_ret_rows(self.shape, batch, full_layers, max_window), 1) * self.kv_width * item
+            self.xbuf = SymmetricBuffer(2 * self.slot_bytes + 2 * self.ret_slot_bytes, group, device)
+            self.ready = SignalPad(4 * self.size, group, device)      # [slot][producer rank] <- exchange number + 1
+            self.consumed = SignalPad(4 * self.size, group, device)   # [slot][consumer rank] <- exchange number + 1
+            self.dtype = dtype
+
+    def close(self) -> None:
+        if self.fused:
+            torch.cuda.synchronize(self.device)
+            self.ready.close()
+            self.consumed.close()
+            self.xbuf.close()
+
+    # ------------------------------------------------------------------ ranges
+    def text_sources(self, halo: int) -> List[Tuple[int, int, int]]:
+        """Halo rows as ``(owner rank, first local row, n rows)`` in global order."""
+        Ll = self.shape.local_len
+        out = []
+        start = self.rank * Ll - halo
+        while halo > 0:
+            owner = start // Ll
+            lo = start - owner * Ll
+            n = min(Ll - lo, halo)
+            out.append((owner, lo, n))
+            start += n
+            halo -= n
+        return out
+
+
+def _ret_rows(shape: CpShape, batch: int, full_layers: bool, max_window: int) -> int:
+    halo = (shape.size - 1) * shape.local_len if full_layers else min((shape.size - 1) * shape.local_len,
+                                                                      max_window * shape.chunk)
+    return batch * (halo + (shape.size - 1) * shape.local_sum)
+
+
+class _CpStage(torch.autograd.Function):
+    """``kv_local`` ``[B*Ll + B*Nsl, 2*Hkv*D]`` -> (``[B, halo+Ll, kvw]`` text K|V, ``[B, (r+1)*Nsl, kvw]`` summary K|V).
+
+    Backward returns the gradients of halo / older-summary rows to their owners and adds what later ranks return.
+    """
+
+    @staticmethod
+    def forward(ctx, kv_local, cp: CpContext, window_chunks: Optional[int], summaries: bool):
+        sh, B = cp.shape, cp.batch
+        Ll, Nsl, r, P, kvw = sh.local_len, sh.local_sum, cp.rank, cp.size, cp.kv_width
+        halo = sh.halo_len(window_chunks)
+        ctx.cp, ctx.halo, ctx.summaries = cp, halo, summaries
+        ctx.halo_of = lambda q: CpShape(q, sh.size, sh.seq_len, sh.chunk, sh.n_sum).halo_len(window_chunks)
+        if not summaries:
+            Nsl = 0
+        text_local = kv_local[:B * Ll].view(B, Ll, kvw)
+        sum_local = kv_local[B * Ll:].view(B, Nsl, kvw)
+        st_text = kv_local.new_empty(B, halo + Ll, kvw)
+        st_sum = kv_local.new_empty(B, (r + 1) * Nsl, kvw)
+        st_text[:, halo:] = text_local
+        st_sum[:, r * Nsl:] = sum_local
+        if not cp.fused:
+            parts = [torch.empty_like(kv_local) for _ in range(P)]
+            dist.all_gather(parts, kv_local.contiguous(), group=cp.group)
+            for owner, lo, n in cp.text_sources(halo):
+                off = (owner * Ll + lo) - (r * Ll - halo)
+                st_text[:, off:off + n] = parts[owner][:B * Ll].view(B, Ll, kvw)[:, lo:lo + n]
+            for p in range(r):
+                st_sum[:, p * Nsl:(p + 1) * Nsl] = parts[p][B * Ll:].view(B, Nsl, kvw)
+            return st_text, st_sum
+        e = cp.counter
+        cp.counter += 1
+        slot = e % 2
+        item = kv_local.element_size()
+        row_b = kvw * item
+        if e >= 2:   # every consumer has finished reading this slot's previous contents
+            cp.consumed.wait_local(slot * P, P, None, e - 1)
+        cp.xbuf.view(cp.dtype, slot * cp.slot_bytes, kv_local.numel()).copy_(kv_local.reshape(-1))
+        cp.ready.set_on_all(slot * P + r, None, e + 1)
+        base = slot * cp.slot_bytes
+        for owner, lo, n in cp.text_sources(halo):
+            off = (owner * Ll + lo) - (r * Ll - halo)
+            for b in range(B):
+                _lib.call("ksa_peer_copy", st_text[b, off:off + n], cp.xbuf.peer_ptrs[owner] + base + (b * Ll + lo) * row_b,
+                          n * row_b, cp.ready.local_ptr(slot * P + owner), None, e + 1, 16)
+        if Nsl > 0:
+            for p in range(r):
+                for b in range(B):
+                    _lib.call("ksa_peer_copy", st_sum[b, p * Nsl:(p + 1) * Nsl],
+                              cp.xbuf.peer_ptrs[p] + base + (B * Ll + b * Nsl) * row_b, Nsl * row_b,
+                              cp.ready.local_ptr(slot * P + p), None, e + 1, 8)
+        cp.consumed.set_on_all(slot * P + r, None, e + 1)
+        return st_text, st_sum
+
+    @staticmethod
+    def backward(ctx, g_text, g_sum):
+        cp, halo = ctx.cp, ctx.halo
+        sh, B = cp.shape, cp.batch
+        Ll, Nsl, r, P, kvw = sh.local_len, sh.local_sum, cp.rank, cp.size, cp.kv_width
+        if not ctx.summaries:
+            Nsl = 0
+        g_text = g_text.contiguous()
+        g_sum = g_sum.contiguous()
+        g_local = torch.cat([g_text[:, halo:].reshape(B * Ll, kvw), g_sum[:, r * Nsl:].reshape(B * Nsl, kvw)], dim=0)
+        if not cp.fused:
+            full_t = g_text.new_zeros(P, B, Ll, kvw)
+            full_s = g_text.new_zeros(P, B, max(Nsl, 1), kvw)
+            for owner, lo, n in cp.text_sources(halo):
+                off = (owner * Ll + lo) - (r * Ll - halo)
+                full_t[owner, :, lo:lo + n] = g_text[:, off:off + n]
+            for p in range(r):
+                full_s[p, :, :Nsl] = g_sum[:, p * Nsl:(p + 1) * Nsl]
+            dist.all_reduce(full_t, group=cp.group)
+            dist.all_reduce(full_s, group=cp.group)
+            g_local = g_local.clone()
+            g_local[:B * Ll] += full_t[r].reshape(B * Ll, kvw)
+            if Nsl > 0:
+                g_local[B * Ll:] += full_s[r, :, :Nsl].reshape(B * Nsl, kvw)
+            return g_local, None, None, None
+        e = cp.counter
+        cp.counter += 1
+        slot = 2 + e % 2
+        item = g_text.element_size()
+        row_b = kvw * item
+        base = 2 * cp.slot_bytes + (e % 2) * cp.ret_slot_bytes
+        if e >= 2:
+            cp.consumed.wait_local(slot * P, P, None, e - 1)
+        # publish what belongs to others: [B x halo text rows | B x r*Nsl summary rows]
+        n_pub = B * halo + B * r * Nsl
+        if n_pub * row_b > cp.ret_slot_bytes:
+            raise ValueError("context-parallel gradient return block exceeds the exchange buffer; build CpContext with "
+                             "full_layers=True or a larger max_window")
+        if n_pub > 0:
+            pub = torch.cat([g_text[:, :halo].reshape(B * halo, kvw), g_sum[:, :r * Nsl].reshape(B * r * Nsl, kvw)], dim=0)
+            cp.xbuf.view(cp.dtype, base, pub.numel()).copy_(pub.reshape(-1))
+        cp.ready.set_on_all(slot * P + r, None, e + 1)
+        # collect what later ranks computed for my rows
+        for q in range(r + 1, P):
+            halo_q = ctx.halo_of(q)
+            start_q = q * Ll - halo_q                       # global text index of q's first halo row
+            lo_g, hi_g = max(start_q, r * Ll), min(q * Ll, (r + 1) * Ll)
+            flag = cp.ready.local_ptr(slot * P + q)
+            if hi_g > lo_g:
+                for b in range(B):
+                    src = cp.xbuf.peer_ptrs[q] + base + (b * halo_q + (lo_g - start_q)) * row_b
+                    _lib.call("ksa_peer_add_bf16", g_local[b * Ll + (lo_g - r * Ll):b * Ll + (hi_g - r * Ll)], src,
+                              (hi_g - lo_g) * kvw, flag, None, e + 1, 16)
+            if Nsl > 0:
+                for b in range(B):
+                    src = cp.xbuf.peer_ptrs[q] + base + (B * halo_q + b * q * Nsl + r * Nsl) * row_b
+                    _lib.call("ksa_peer_add_bf16", g_local[B * Ll + b * Nsl:B * Ll + (b + 1) * Nsl], src, Nsl * kvw, flag,
+                              None, e + 1, 8)
+        cp.consumed.set_on_all(slot * P + r, None, e + 1)
+        return g_local, None, None, None
+
+
+def _cpu_shard_attention(q_t, k_t, v_t, q_s, k_s, v_s, sh: CpShape, halo: int, window: Optional[int], tok_window: int,
+                         scale: float):
+    """Dense-mask fp32 attention of one shard: global masks sliced to the staged key ranges."""
+    r, Ll, Nsl, L = sh.rank, sh.local_len, sh.local_sum, sh.seq_len
+    n_rep = q_t.shape[2] // k_t.shape[2]
+    q0, k0 = r * Ll, r * Ll - halo
+    if q_s is None:
+        qi = torch.arange(q0, q0 + Ll)[:, None]
+        ki = torch.arange(k0, q0 + Ll)[None, :]
+        mask = ki <= qi
+        if tok_window and tok_window > 0:
+            mask = mask & (qi - ki < tok_window)
+        o, _ = ref._masked_attention(q_t, ref._expand_kv(k_t, n_rep), ref._expand_kv(v_t, n_rep), mask, scale)
+        return o.to(q_t.dtype), None
+    tt, ts, st, ss = two_stream_masks(L, sh.chunk, sh.n_sum, window)
+    s0, s1 = r * Nsl, (r + 1) * Nsl
+    k_all = torch.cat([ref._expand_kv(k_t, n_rep), ref._expand_kv(k_s, n_rep)], dim=1)
+    v_all = torch.cat([ref._expand_kv(v_t, n_rep), ref._expand_kv(v_s, n_rep)], dim=1)
+    m_t = torch.cat([tt[q0:q0 + Ll, k0:q0 + Ll], ts[q0:q0 + Ll, :s1]], dim=1)
+    m_s = torch.cat([st[s0:s1, k0:q0 + Ll], ss[s0:s1, :s1]], dim=1)
+    o_t, _ = ref._masked_attention(q_t, k_all, v_all, m_t, scale)
+    o_s, _ = ref._masked_attention(q_s, k_all, v_all, m_s, scale)
+    return o_t.to(q_t.dtype), o_s.to(q_s.dtype)
+
+
+def cp_attention_packed(qkv: torch.Tensor, cp: CpContext, Hq: int, Hkv: int, D: int, window_chunks: Optional[int] = None,
+                        summaries: bool = True, tok_window: int = 0, scale: Optional[float] = None) -> torch.Tensor:
+    """Attention of one context-parallel shard on packed, rotated projection rows.
+
+    ``qkv`` is ``[B*Ll (+ B*Nsl), (Hq+2Hkv)*D]``: the shard's text rows, then (summary layers) its summary rows.
+    ``window_chunks=None`` with ``summaries=False`` is a full-attention layer (``tok_window`` optional).  Returns the
+    attention output rows ``[rows, Hq*D]`` in the same order.
+    """
+    sh, B, r = cp.shape, cp.batch, cp.rank
+    Ll = sh.local_len
+    Nsl = sh.local_sum if summaries else 0
+    n_text = B * Ll
+    if qkv.shape[0] != n_text + B * Nsl:
+        raise ValueError(f"expected {n_text + B * Nsl} packed rows for this shard, got {qkv.shape[0]}")
+    scale = scale if scale is not None else D ** -0.5
+    kv = qkv[:, Hq * D:].contiguous()
+    st_text, st_sum = _CpStage.apply(kv, cp, window_chunks, summaries)
+    halo = sh.halo_len(window_chunks)
+    q_t = qkv[:n_text, :Hq * D].view(B, Ll, Hq, D)
+    k_t = st_text[..., :Hkv * D].view(B, halo + Ll, Hkv, D)
+    v_t = st_text[..., Hkv * D:].view(B, halo + Ll, Hkv, D)
+    q_s = k_s = v_s = None
+    if summaries:
+        q_s = qkv[n_text:, :Hq * D].view(B, Nsl, Hq, D)
+        k_s = st_sum[..., :Hkv * D].view(B, (r + 1) * Nsl, Hkv, D)
+        v_s = st_sum[..., Hkv * D:].view(B, (r + 1) * Nsl, Hkv, D)
+    if not cp.fused:
+        o_t, o_s = _cpu_shard_attention(q_t, k_t, v_t, q_s, k_s, v_s, sh, halo, window_chunks, tok_window, scale)
+    elif summaries:
+        o_t, o_s = ops.ksa_attention(q_t, k_t, v_t, q_s, k_s, v_s, sh.chunk, sh.n_sum, window_chunks, scale,
+                                     q_off=r * Ll, k_off=r * Ll - halo, s_off=0, seq_len=sh.seq_len)
+    else:
+        o_t, o_s = ops.shard_causal_attention(q_t, k_t, v_t, scale, tok_window, q_off=r * Ll, k_off=r * Ll - halo,
+                                              seq_len=sh.seq_len), None
+    out = o_t.reshape(n_text, Hq * D)
+    if o_s is not None:
+        out = torch.cat([out, o_s.reshape(B * Nsl, Hq * D)], dim=0)
+    return out
+
+
+def shard_inputs(tokens: torch.Tensor, labels: Optional[torch.Tensor], rank: int, size: int):
+    """This rank's contiguous slice of ``[B, L]`` tokens/labels (``muse/training/parallel.py:431-468`` splits the
+    batch the same way for Ulysses)."""
+    L = tokens.shape[1]
+    Ll = L // size
+    sl = slice(rank * Ll, (rank + 1) * Ll)
+    return tokens[:, sl].contiguous(), (labels[:, sl].contiguous() if labels is not None else None)

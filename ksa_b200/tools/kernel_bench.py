@@ -1,0 +1,193 @@
+"""Micro-benchmarks of the sm_100a kernels against their rooflines (CUDA events, L2 flushed between iterations).
+
+    python -m ksa_b200.tools.kernel_bench gemm --m 8192 --n 4096 --k 2048
+    python -m ksa_b200.tools.kernel_bench attn --seq 8192 [--causal] [--bwd]
+    python -m ksa_b200.tools.kernel_bench decode --cap 131072 --batch 16
+    python -m ksa_b200.tools.kernel_bench norm --rows 8256 --dim 2048
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m ksa_b200.tools.kernel_bench \
+        cp-attn --seq 32768 --bwd          # context-parallel attention: one shard per rank, max over ranks
+
+Each line reports the median time, the achieved TFLOP/s or GB/s and, when ``MEASURED_PEAKS.json`` sits at the
+repository root, the fraction of the measured peak (cuBLAS bf16 burst / STREAM-style copy).  ``--iters 1 --warmup 1
+--no-flush`` gives a short, fixed launch sequence suitable for a profiler capture of one kernel.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from .. import ops
+from ..ops import _lib
+from ..ops.layout import count_attended_pairs
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks() -> dict:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"tflops": d.get("bf16_tflops"), "gbs": d.get("hbm_gbs"), "src": "measured"}
+    return {"tflops": 1590.0, "gbs": 6650.0, "src": "fallback"}
+
+
+def timeit(fn, iters: int, warmup: int, flush: bool) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    times = []
+    for _ in range(iters):
+        if buf is not None:
+            buf.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def report(name: str, ms: float, flops: float = 0.0, bytes_: float = 0.0) -> None:
+    pk = peaks()
+    parts = [f"{name}: {ms:.4f} ms"]
+    if flops:
+        tf = flops / ms / 1e9
+        parts.append(f"{tf:.0f} TFLOP/s ({tf / pk['tflops']:.2f} of {pk['src']} {pk['tflops']:.0f})")
+    if bytes_:
+        gb = bytes_ / ms / 1e6
+        parts.append(f"{gb:.0f} GB/s ({gb / pk['gbs']:.2f} of {pk['src']} {pk['gbs']:.0f})")
+    print(" | ".join(parts), flush=True)
+
+
+def bench_gemm(a) -> None:
+    M, N, K = a.m, a.n, a.k
+    A = torch.randn((K, M) if a.a_mn else (M, K), device="cuda").bfloat16()
+    B = torch.randn((K, N) if a.b_mn else (N, K), device="cuda").bfloat16()
+    C = torch.empty(M, N, device="cuda", dtype=torch.float32 if a.fp32_out else torch.bfloat16)
+    ms = timeit(lambda: ops.gemm(A, B, a_mn_major=a.a_mn, b_mn_major=a.b_mn, out=C), a.iters, a.warmup, not a.no_flush)
+    report(f"gemm {M}x{N}x{K} a_mn={int(a.a_mn)} b_mn={int(a.b_mn)}", ms, flops=2.0 * M * N * K)
+    if a.compare:
+        Am, Bm = (A.t() if a.a_mn else A), (B if a.b_mn else B.t())
+        Cb = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms2 = timeit(lambda: torch.matmul(Am, Bm, out=Cb), a.iters, a.warmup, not a.no_flush)
+        report("  cuBLAS (torch.matmul)", ms2, flops=2.0 * M * N * K)
+
+
+def bench_attn(a) -> None:
+    B, Hq, Hkv, D, C, S, W, L = a.batch, a.hq, a.hkv, a.dim, a.chunk, a.nsum, a.window, a.seq
+    Ns = 0 if a.causal else (L // C) * S
+    R = B * (L + Ns)
+    qkv = torch.randn(R, (Hq + 2 * Hkv) * D, device="cuda").bfloat16().requires_grad_(a.bwd)
+    kw = {} if a.causal else dict(chunk=C, n_sum=S, window=W)
+    pairs = L * (L + 1) // 2 if a.causal else count_attended_pairs(L, C, S, W)
+    fwd_flops = 4.0 * D * Hq * pairs * B
+    out = [None]
+
+    def fwd():
+        out[0] = ops.attention_packed(qkv, B, L, Ns, Hq, Hkv, D, **kw)
+    ms_f = timeit(fwd, a.iters, a.warmup, not a.no_flush)
+    kind = "causal" if a.causal else f"ksa C{C} S{S} W{W}"
+    report(f"attention fwd {kind} L{L} {Hq}q/{Hkv}kv d{D}", ms_f, flops=fwd_flops)
+    if a.bwd:
+        g = torch.randn_like(out[0])
+
+        def fb():
+            fwd()
+            out[0].backward(g)
+        ms_fb = timeit(fb, a.iters, a.warmup, not a.no_flush)
+        report(f"attention bwd {kind} L{L} (fwd+bwd minus fwd; useful FLOPs = 2.5x fwd)", ms_fb - ms_f,
+               flops=2.5 * fwd_flops)
+
+
+def bench_decode(a) -> None:
+    from ..inference.engine import _decode_attention
+    B, Hq, Hkv, D, cap = a.batch, a.hq, a.hkv, a.dim, a.cap
+    q = torch.randn(B, 1, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B, Hkv, cap, D, device="cuda").bfloat16()
+    v = torch.randn_like(k)
+    start = torch.zeros(B, 1, dtype=torch.int32, device="cuda")
+    length = torch.full((B, 1), cap, dtype=torch.int32, device="cuda")
+    ms = timeit(lambda: _decode_attention(q, k, v, start, length, D ** -0.5), a.iters, a.warmup, not a.no_flush)
+    report(f"decode attention B{B} {Hq}q/{Hkv}kv cap {cap}", ms, bytes_=2.0 * k.numel() * 2)
+
+
+def bench_norm(a) -> None:
+    rows, D = a.rows, a.dim
+    x, d = torch.randn(rows, D, device="cuda").bfloat16(), torch.randn(rows, D, device="cuda").bfloat16()
+    w = torch.ones(D, device="cuda").bfloat16()
+    ms = timeit(lambda: ops.add_rms_norm(x, d, w), a.iters, a.warmup, not a.no_flush)
+    report(f"add+rmsnorm fwd {rows}x{D}", ms, bytes_=4.0 * rows * D * 2)
+
+
+def bench_cp_attn(a) -> None:
+    """Context-parallel KSA (or causal) attention: the exchange over peer memory plus the shard's kernels."""
+    import torch.distributed as dist
+    from ..parallel.cp import CpContext, cp_attention_packed
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    B, Hq, Hkv, D, C, S, W, L = a.batch, a.hq, a.hkv, a.dim, a.chunk, a.nsum, a.window, a.seq
+    cp = CpContext(dist.group.WORLD, L, C, S, Hkv, D, batch=B, device=dev, full_layers=a.causal, max_window=W)
+    Ll, Nsl = L // world, 0 if a.causal else (L // world // C) * S
+    qkv = torch.randn(B * (Ll + Nsl), (Hq + 2 * Hkv) * D, device=dev).bfloat16().requires_grad_(a.bwd)
+    out = [None]
+
+    def fwd():
+        out[0] = cp_attention_packed(qkv, cp, Hq, Hkv, D, None if a.causal else W, not a.causal)
+
+    def timed(fn):
+        dist.barrier()
+        t = torch.tensor([timeit(fn, a.iters, a.warmup, not a.no_flush)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+    pairs = L * (L + 1) // 2 if a.causal else count_attended_pairs(L, C, S, W)
+    flops = 4.0 * D * Hq * pairs * B / world       # per GPU (the slowest rank holds the last, densest shard)
+    ms_f = timed(fwd)
+    kind = "causal" if a.causal else f"ksa C{C} S{S} W{W}"
+    if rank == 0:
+        report(f"cp{world} attention fwd {kind} L{L} (max over ranks; mean FLOPs per GPU)", ms_f, flops=flops)
+    if a.bwd:
+        g = torch.randn_like(out[0])
+
+        def fb():
+            fwd()
+            out[0].backward(g)
+        ms_fb = timed(fb)
+        if rank == 0:
+            report(f"cp{world} attention bwd {kind} L{L} (fwd+bwd minus fwd)", ms_fb - ms_f, flops=2.5 * flops)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    cp.close()
+    dist.destroy_process_group()
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("what", choices=["gemm", "attn", "decode", "norm", "cp-attn"])
+    ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--a-mn", action="store_true"); ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--fp32-out", action="store_true"); ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--seq", type=int, default=8192); ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--hq", type=int, default=16); ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--dim", type=int, default=128); ap.add_argument("--chunk", type=int, default=128)
+    ap.add_argument("--nsum", type=int, default=1); ap.add_argument("--window", type=int, default=8)
+    ap.add_argument("--causal", action="store_true"); ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--cap", type=int, default=131072); ap.add_argument("--rows", type=int, default=8256)
+    ap.add_argument("--iters", type=int, default=10); ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args(argv)
+    {"gemm": bench_gemm, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn}[a.what](a)
+    _lib.check_status()
+
+
+if __name__ == "__main__":
+    main()
