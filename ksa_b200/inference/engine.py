@@ -18,6 +18,7 @@ from typing import List, Optional
 import torch
 
 from .. import ops
+from ..models.qwen3_ksa import _add_norm, _row_linear
 from ..ops import _lib, reference as ref
 from .cache import (CacheSpec, CacheState, FullLayerCache, KsaLayerCache, flush_plan, summary_step_slices,
                     text_step_slices)
@@ -155,6 +156,7 @@ class KsaInferenceEngine:
     def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
         """``tokens`` ``[B]``: the next text token of every sequence -> logits ``[B, V]``."""
         model, cfg = self.model, self.cfg
+        tp = getattr(model, "tp", None)      # tensor-parallel shard: cfg holds the local head counts
         B, C, S = self.batch, self.C, self.S
         Hq, Hkv, Dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         scale = Dh ** -0.5
@@ -186,7 +188,7 @@ class KsaInferenceEngine:
         for li, layer in enumerate(model.layers):
             a = layer.attn
             cache = self.layer_caches[li]
-            x, h = ops.add_rms_norm(x, delta, layer.sa_norm.scale, cfg.norm_eps)
+            x, h = _add_norm(tp, x, delta, layer.sa_norm.scale, cfg.norm_eps)
             if layer.is_summary_layer:
                 spec = self.specs[li]
                 if any_boundary:
@@ -223,9 +225,9 @@ class KsaInferenceEngine:
                 else:
                     att = _decode_attention(q_t, cache.k, cache.v, start_t.view(B, 1).to(torch.int32),
                                             len_t.view(B, 1).to(torch.int32), scale).reshape(B, Hq * Dh)
-                attn_out = ops.linear(att, a.output_proj.weight)
-                x, h2 = ops.add_rms_norm(x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
-                delta = layer.mlp(h2)
+                attn_out = _row_linear(tp, att, a.output_proj.weight)
+                x, h2 = _add_norm(tp, x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
+                delta = layer.mlp(h2, tp)
             else:
                 qkv = ops.linear(h[:B], a.wqkv.weight)
                 qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), pos_all[:B], Hq, Hkv, Dh,
@@ -237,11 +239,13 @@ class KsaInferenceEngine:
                 zeros = torch.zeros(B, 1, dtype=torch.int32, device=dev)
                 att = _decode_attention(q_t, cache.k, cache.v, zeros, (st.text_len + 1).view(B, 1).to(torch.int32),
                                         scale).reshape(B, Hq * Dh)
-                attn_out = ops.linear(att, a.output_proj.weight)
-                x, h2 = ops.add_rms_norm(x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
-                delta = layer.mlp(h2[:B])
-        _, hN = ops.add_rms_norm(x[:B], delta[:B], model.norm.scale, cfg.norm_eps)
+                attn_out = _row_linear(tp, att, a.output_proj.weight)
+                x, h2 = _add_norm(tp, x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
+                delta = layer.mlp(h2[:B], tp)
+        _, hN = _add_norm(tp, x[:B], delta[:B], model.norm.scale, cfg.norm_eps)
         logits = ops.linear(hN, model.lm_head_weight)
+        if tp is not None and logits.shape[-1] != cfg.vocab_size:
+            logits = tp.gather_logits(logits)
         # advance the counters
         st.text_len += 1
         if S > 0:

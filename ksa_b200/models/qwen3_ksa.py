@@ -85,6 +85,19 @@ class KsaAttention(nn.Module):
         return None if m is None else m.scale
 
 
+def _row_linear(tp, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Row-parallel projection: with a tensor-parallel group the result is this rank's partial sum."""
+    return ops.linear(x, weight) if tp is None else tp.row_parallel_linear(x, weight)
+
+
+def _add_norm(tp, x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float):
+    """Residual add + RMSNorm; with a tensor-parallel group ``delta`` is a partial sum that is all-reduced in the
+    same kernel."""
+    if tp is None or delta is None:
+        return ops.add_rms_norm(x, delta, weight, eps)
+    return tp.add_rms_norm(x, delta, weight, eps)
+
+
 class SwiGluMlp(nn.Module):
     """``w2(silu(w1 x) * w3 x)`` with w1|w3 fused into ``w13`` (``muse/layers/feed_forward.py:44-83``)."""
 
@@ -93,8 +106,8 @@ class SwiGluMlp(nn.Module):
         self.w13 = FusedLinear(dim, 2 * hidden)
         self.w2 = FusedLinear(hidden, dim)
 
-    def forward(self, x):
-        return self.w2(ops.swiglu(self.w13(x)))
+    def forward(self, x, tp=None):
+        return _row_linear(tp, ops.swiglu(self.w13(x)), self.w2.weight)
 
 
 class KsaDecoderLayer(nn.Module):
@@ -126,7 +139,8 @@ class KsaDecoderLayer(nn.Module):
         cfg, a = self.cfg, self.attn
         Hq, Hkv, Dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         n_text = meta.B * meta.L
-        x, h = ops.add_rms_norm(x, delta, self.sa_norm.scale, cfg.norm_eps)
+        tp = meta.tp
+        x, h = _add_norm(tp, x, delta, self.sa_norm.scale, cfg.norm_eps)
         if self.is_summary_layer and meta.Ns > 0:
             if self.sa_norm_summary is not None:
                 h = torch.cat([h[:n_text], ops.rms_norm(x[n_text:], self.sa_norm_summary.scale, cfg.norm_eps)])
@@ -157,11 +171,11 @@ class KsaDecoderLayer(nn.Module):
             else:
                 att = ops.attention_packed(qkv, meta.B, meta.L, meta.Ns, Hq, Hkv, Dh, meta.chunk, meta.n_sum,
                                            self.window_chunks)
-            attn_out = ops.linear(att, a.output_proj.weight)
+            attn_out = _row_linear(tp, att, a.output_proj.weight)
             if collect is not None:
                 collect.append(attn_out[:n_text])
-            x, h2 = ops.add_rms_norm(x, attn_out, self.mlp_norm.scale, cfg.norm_eps)
-            return x, self.mlp(h2)
+            x, h2 = _add_norm(tp, x, attn_out, self.mlp_norm.scale, cfg.norm_eps)
+            return x, self.mlp(h2, tp)
         # full causal attention on the text rows; summary rows (if any) pass through unchanged
         qkv = ops.linear(h[:n_text], a.wqkv.weight)
         qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), meta.pos[:n_text], Hq, Hkv, Dh,
@@ -173,11 +187,11 @@ class KsaDecoderLayer(nn.Module):
             att = cp_attention_packed(qkv, meta.cp, Hq, Hkv, Dh, None, False, self.tok_window)
         else:
             att = ops.attention_packed(qkv, meta.B, meta.L, 0, Hq, Hkv, Dh, tok_window=self.tok_window)
-        attn_out = ops.linear(att, a.output_proj.weight)
+        attn_out = _row_linear(tp, att, a.output_proj.weight)
         if collect is not None:
             collect.append(attn_out)
-        x, h2 = ops.add_rms_norm(x, attn_out, self.mlp_norm.scale, cfg.norm_eps)
-        return x, self.mlp(h2[:n_text])
+        x, h2 = _add_norm(tp, x, attn_out, self.mlp_norm.scale, cfg.norm_eps)
+        return x, self.mlp(h2[:n_text], tp)
 
 
 class BatchMeta:
@@ -188,6 +202,7 @@ class BatchMeta:
         self.B, self.L = B, L
         self.rope_interleaved = rope_interleaved
         self.cp = cp          # context-parallel group state: this rank holds one contiguous shard of the sequence
+        self.tp = None        # tensor-parallel group state (inference): row-parallel outputs are partial sums
         self.kv_sink = None   # optional callable(layer_idx, qkv_rot, is_summary_layer): prefill fills KV caches with it
         if cp is not None:
             # ``layout`` describes the whole sequence; keep this shard's rows of its position ids
@@ -243,6 +258,7 @@ class Qwen3Model(Model):
         self.loss_chunk_tokens = 2048
         self.drop_partial_summary = False   # inference: a trailing partial chunk gets no summary tokens
         self.cp = None                      # parallel.cp.CpContext: ``forward`` then takes this rank's sequence shard
+        self.tp = None                      # parallel.tp.TpContext: this module holds one tensor-parallel shard
 
     # ---- configuration helpers ----------------------------------------------------
     def _layer_is_summary(self) -> List[bool]:
@@ -333,6 +349,7 @@ class Qwen3Model(Model):
         # teacher: same weights, no summary tokens, recipes/pretrain_kai_summary_unified.py:967-997)
         meta = self._meta(B, L, tokens.device, position_ids, use_summary)
         meta.kv_sink = kv_sink
+        tp = meta.tp = self.tp
         x = self.embed(tokens, meta)
         collect = [] if collect_attn else None
         delta = None
@@ -344,18 +361,24 @@ class Qwen3Model(Model):
             rows = torch.arange(B, device=x.device) * L + (L - 1)
             xl = x[rows]
             dl = delta[rows] if delta is not None else None
-            _, h = ops.add_rms_norm(xl, dl, self.norm.scale, self.config.norm_eps)
-            return ops.linear(h, self.lm_head_weight).view(B, 1, -1)
+            _, h = _add_norm(tp, xl, dl, self.norm.scale, self.config.norm_eps)
+            logits = ops.linear(h, self.lm_head_weight)
+            if tp is not None and logits.shape[-1] != self.config.vocab_size:
+                logits = tp.gather_logits(logits)
+            return logits.view(B, 1, -1)
         # summary rows are dropped before the final norm and the head (modeling.py:243-249)
-        _, h = ops.add_rms_norm(x[:n_text], delta[:n_text] if delta is not None else None, self.norm.scale,
-                                self.config.norm_eps)
+        _, h = _add_norm(tp, x[:n_text], delta[:n_text] if delta is not None else None, self.norm.scale,
+                         self.config.norm_eps)
         self.last_attn_outputs = collect
         if labels is not None and not self.skip_output_layer:
             return ops.linear_cross_entropy(h, self.lm_head_weight, labels.reshape(-1), ignore_index,
                                             self.loss_chunk_tokens)
         if return_hidden or self.skip_output_layer:
             return h.view(B, L, -1)
-        return ops.linear(h, self.lm_head_weight).view(B, L, -1)
+        logits = ops.linear(h, self.lm_head_weight)
+        if tp is not None and logits.shape[-1] != self.config.vocab_size:
+            logits = tp.gather_logits(logits)
+        return logits.view(B, L, -1)
 
     # ---- Muse / HF parameter names ---------------------------------------------------
     def muse_state_dict(self, state: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, torch.Tensor]:

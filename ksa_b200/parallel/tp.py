@@ -1,0 +1,148 @@
+"""Tensor parallelism for inference (TP 1/2/4/8; the reference serves its models through vLLM's tensor-parallel
+workers, ``examples/inference/README.md``; this package carries its own engine).
+
+Each rank holds ``Hq/T`` query heads, ``Hkv/T`` key/value heads (and their KV caches), ``F/T`` feed-forward columns and
+``V/T`` rows of the output head; the residual stream is replicated.  The QKV and gate/up projections are
+column-parallel (no communication).  The attention output and the down projection are row-parallel: every rank's
+GEMM writes its partial ``[rows, D]`` block straight into a symmetric-memory slot, and ONE kernel
+(``ksa_tp_allreduce_add_rmsnorm``) announces the block, waits (bounded) for the peers', sums all partials row by row
+over P2P loads in rank order, adds the residual row and applies the next RMSNorm: the all-reduce never exists as a
+separate pass and every rank keeps a bit-identical residual stream.
+
+CPU (gloo) ranks run the same layout with ``all_reduce`` / ``all_gather`` for the tests.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import _lib
+
+
+class TpContext:
+    """Group + (on GPUs) the symmetric partial-sum slots of one tensor-parallel group."""
+
+    def __init__(self, group, embed_dim: int, max_rows: int, device=None, dtype=torch.bfloat16):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+        self.D = embed_dim
+        self.max_rows = max_rows
+        self.device = device
+        self.dtype = dtype
+        self.fused = device is not None and torch.device(device).type == "cuda"
+        self.counter = 0            # all-reduces issued so far (identical on every rank)
+        if self.fused:
+            from .symm import SignalPad, SymmetricBuffer
+            item = torch.empty((), dtype=dtype).element_size()
+            self.slot_bytes = (max_rows * embed_dim * item + 255) // 256 * 256
+            self.buf = SymmetricBuffer(2 * self.slot_bytes, group, device)
+            self.flags = SignalPad(self.size, group, device)
+            self.flags.flags.zero_()
+            torch.cuda.synchronize(device)
+            dist.barrier(group)
+            self._slot_ptrs = [self.buf.offset_ptr_array(s * self.slot_bytes) for s in range(2)]
+            self._announce = self.flags.flag_ptrs(self.rank)
+
+    def close(self) -> None:
+        if self.fused:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+            self.flags.close()
+            self.buf.close()
+
+    # ------------------------------------------------------------------ row-parallel linear + fused all-reduce
+    def _slot_view(self, rows: int) -> torch.Tensor:
+        if rows > self.max_rows:
+            raise ValueError(f"{rows} rows exceed the tensor-parallel exchange buffer ({self.max_rows} rows)")
+        return self.buf.view(self.dtype, (self.counter % 2) * self.slot_bytes, rows * self.D).view(rows, self.D)
+
+    def row_parallel_linear(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """Partial ``x_local @ weight_local.T``; on GPUs written into the slot the next all-reduce reads."""
+        if not self.fused:
+            return ops.linear(x, weight)
+        out = self._slot_view(x.shape[0])
+        ops.gemm(x if x.is_contiguous() else x.contiguous(), weight, out=out)
+        return out
+
+    def add_rms_norm(self, x: torch.Tensor, partial: torch.Tensor, weight: torch.Tensor,
+                     eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``r = x + sum_ranks(partial)`` on the first ``partial.shape[0]`` rows and ``rms_norm(r)``."""
+        if not self.fused:
+            total = partial.clone()
+            dist.all_reduce(total, group=self.group)
+            return ops.add_rms_norm(x, total, weight, eps)
+        rows_x, rows_d = x.shape[0], partial.shape[0]
+        slot = self._slot_view(rows_d)
+        if partial.data_ptr() != slot.data_ptr():
+            slot.copy_(partial)
+        x = x if x.is_contiguous() else x.contiguous()
+        res = torch.empty_like(x)
+        y = torch.empty_like(x)
+        s = self.counter % 2
+        self.counter += 1
+        _lib.call("ksa_tp_allreduce_add_rmsnorm", x, self._slot_ptrs[s], self._announce, self.flags.local_ptr(0),
+                  self.size, self.rank, weight, res, y, rows_x, rows_d, self.D, float(eps), self.counter)
+        return res, y
+
+    # ------------------------------------------------------------------ vocabulary-parallel head
+    def gather_logits(self, local: torch.Tensor) -> torch.Tensor:
+        """``[..., V/T]`` per rank -> ``[..., V]`` (rank order)."""
+        parts = [torch.empty_like(local) for _ in range(self.size)]
+        dist.all_gather(parts, local.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+
+# ---------------------------------------------------------------------- sharding
+def tp_local_config(cfg, size: int):
+    """The per-rank model configuration: heads and feed-forward columns divided by the group size."""
+    if cfg.num_heads % size or cfg.num_kv_heads % size or cfg.intermediate_dim % size:
+        raise ValueError(f"heads {cfg.num_heads}/{cfg.num_kv_heads} and FFN {cfg.intermediate_dim} must divide by TP {size}")
+    return cfg.merge({"num_heads": cfg.num_heads // size, "num_kv_heads": cfg.num_kv_heads // size,
+                      "intermediate_dim": cfg.intermediate_dim // size})
+
+
+def shard_state_dict(state: Dict[str, torch.Tensor], cfg, rank: int, size: int,
+                     shard_head: bool = True) -> Dict[str, torch.Tensor]:
+    """Slice a whole-model state dict (this package's fused parameter names) for one rank."""
+    Hq, Hkv, Dh, F = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.intermediate_dim
+    hq, hkv, f = Hq // size, Hkv // size, F // size
+    out: Dict[str, torch.Tensor] = {}
+    for k, v in state.items():
+        if k.endswith("attn.wqkv.weight") or k.endswith("attn.wqkv_summary.weight"):
+            q, kk, vv = v[:Hq * Dh], v[Hq * Dh:(Hq + Hkv) * Dh], v[(Hq + Hkv) * Dh:]
+            out[k] = torch.cat([q[rank * hq * Dh:(rank + 1) * hq * Dh], kk[rank * hkv * Dh:(rank + 1) * hkv * Dh],
+                                vv[rank * hkv * Dh:(rank + 1) * hkv * Dh]], dim=0).contiguous()
+        elif k.endswith("attn.output_proj.weight"):
+            out[k] = v[:, rank * hq * Dh:(rank + 1) * hq * Dh].contiguous()
+        elif k.endswith("mlp.w13.weight"):
+            out[k] = torch.cat([v[rank * f:(rank + 1) * f], v[F + rank * f:F + (rank + 1) * f]], dim=0).contiguous()
+        elif k.endswith("mlp.w2.weight"):
+            out[k] = v[:, rank * f:(rank + 1) * f].contiguous()
+        elif k == "output.weight" and shard_head and v.shape[0] % size == 0:
+            n = v.shape[0] // size
+            out[k] = v[rank * n:(rank + 1) * n].contiguous()
+        else:
+            out[k] = v
+    return out
+
+
+def build_tp_model(full_state: Dict[str, torch.Tensor], cfg, tp: TpContext, device=None, dtype=None):
+    """Instantiate this rank's shard of a model from a whole-model state dict and attach ``tp`` to it."""
+    from ..models import get_model_class
+    local_cfg = tp_local_config(cfg, tp.size)
+    with torch.device("meta"):
+        model = get_model_class(cfg.model_class)(local_cfg)
+    shard = shard_state_dict(full_state, cfg, tp.rank, tp.size)
+    if "output.weight" in shard and model.output is not None and shard["output.weight"].shape[0] != cfg.vocab_size:
+        model.output.weight = torch.nn.Parameter(torch.empty(shard["output.weight"].shape, device="meta"))
+    model = model.to_empty(device=device or "cpu")
+    model.load_state_dict(shard, strict=True)
+    if dtype is not None:
+        model = model.to(dtype)
+    model.tp = tp
+    return model
