@@ -111,7 +111,9 @@ class SummaryLayout:
 
     def remap_cu_seqlens(self, cu_seqlens: torch.Tensor) -> torch.Tensor:
         """Document boundaries in text coordinates -> expanded coordinates."""
-        return cu_seqlens + (cu_seqlens // self.chunk) * self.n_sum
+        out = cu_seqlens + (cu_seqlens // self.chunk) * self.n_sum
+        # the end of the sequence also closes a ragged last chunk, whose summary tokens follow it
+        return torch.where(cu_seqlens >= self.seq_len, torch.full_like(out, self.expanded_len), out)
 
 
 @lru_cache(maxsize=64)
