@@ -81,7 +81,9 @@ class CpContext:
         self.kv_width = 2 * n_kv_heads * head_dim          # K | V per row
         self.device = device
         self.fused = device is not None and torch.device(device).type == "cuda"
-        self.counter = 0                                    # exchanges issued so far (same on every rank)
+        self.counter = 0                                    # forward exchanges issued so far (same on every rank)
+        self.counter_bwd = 0                                # backward exchanges (they use their own slots and flags)
+        self.slot_last = [None, None, None, None]           # exchange number of each slot's previous use
         if self.fused:
             from .symm import SignalPad, SymmetricBuffer
             rows = batch * (self.shape.local_len + self.shape.local_sum)
@@ -159,8 +161,9 @@ class _CpStage(torch.autograd.Function):
         slot = e % 2
         item = kv_local.element_size()
         row_b = kvw * item
-        if e >= 2:   # every consumer has finished reading this slot's previous contents
-            cp.consumed.wait_local(slot * P, P, None, e - 1)
+        if cp.slot_last[slot] is not None:   # every consumer has finished reading this slot's previous contents
+            cp.consumed.wait_local(slot * P, P, None, cp.slot_last[slot] + 1)
+        cp.slot_last[slot] = e
         cp.xbuf.view(cp.dtype, slot * cp.slot_bytes, kv_local.numel()).copy_(kv_local.reshape(-1))
         cp.ready.set_on_all(slot * P + r, None, e + 1)
         base = slot * cp.slot_bytes
@@ -203,14 +206,15 @@ class _CpStage(torch.autograd.Function):
             if Nsl > 0:
                 g_local[B * Ll:] += full_s[r, :, :Nsl].reshape(B * Nsl, kvw)
             return g_local, None, None, None
-        e = cp.counter
-        cp.counter += 1
+        e = cp.counter_bwd
+        cp.counter_bwd += 1
         slot = 2 + e % 2
         item = g_text.element_size()
         row_b = kvw * item
         base = 2 * cp.slot_bytes + (e % 2) * cp.ret_slot_bytes
-        if e >= 2:
-            cp.consumed.wait_local(slot * P, P, None, e - 1)
+        if cp.slot_last[slot] is not None:
+            cp.consumed.wait_local(slot * P, P, None, cp.slot_last[slot] + 1)
+        cp.slot_last[slot] = e
         # publish what belongs to others: [B x halo text rows | B x r*Nsl summary rows]
         n_pub = B * halo + B * r * Nsl
         if n_pub * row_b > cp.ret_slot_bytes:

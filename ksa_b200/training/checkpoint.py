@@ -25,6 +25,7 @@ from typing import Any, Dict, List, Optional
 import torch
 import torch.distributed as dist
 import torch.distributed.checkpoint as dcp
+from torch.distributed.checkpoint.api import CheckpointException
 from torch.distributed.checkpoint.stateful import Stateful
 
 
@@ -220,13 +221,41 @@ def save_checkpoint(app_state: AppState, checkpointer: DistributedCheckpointer, 
     return path
 
 
+def list_complete_checkpoints(checkpoint_dir: str) -> List[str]:
+    """Step directories that hold a finished DCP checkpoint (the ``.metadata`` file is written last), newest first."""
+    root = Path(checkpoint_dir)
+    if not root.is_dir():
+        return []
+    steps = [p for p in root.iterdir() if p.is_dir() and re.fullmatch(r"global_step\d+", p.name)
+             and (p / ".metadata").exists()]
+    return [str(p) for p in sorted(steps, key=lambda p: step_from_path(p.name), reverse=True)]
+
+
 def load_checkpoint(app_state: AppState, checkpointer: DistributedCheckpointer, checkpoint_dir: str,
-                    checkpoint_id: Optional[str] = None) -> Optional[int]:
+                    checkpoint_id: Optional[str] = None, fallback: bool = False) -> Optional[int]:
+    """Load ``checkpoint_id`` (default: ``latest``).  With ``fallback`` a checkpoint that is missing, unfinished or
+    unreadable (a crash during the save, a damaged shard) is skipped in favour of the newest older complete one; the
+    choice is a function of the directory contents only, so every rank takes the same path."""
     path = get_checkpoint_path(checkpoint_dir, checkpoint_id)
-    if path is None:
-        return None
-    checkpointer.load(app_state, path)
-    return step_from_path(path)
+    candidates = [path] if path is not None else []
+    if fallback:
+        first = step_from_path(path) if path is not None else None
+        candidates = [p for p in candidates if os.path.exists(os.path.join(p, ".metadata"))]
+        candidates += [p for p in list_complete_checkpoints(checkpoint_dir)
+                       if p not in candidates and (first is None or step_from_path(p) < first)]
+    last_error: Optional[BaseException] = None
+    for cand in candidates:
+        try:
+            checkpointer.load(app_state, cand)
+            return step_from_path(cand)
+        except (Exception, CheckpointException) as e:  # CheckpointException derives from BaseException
+            if not fallback:
+                raise
+            print(f"[checkpoint] cannot load {cand}: {type(e).__name__}: {e}; trying an older one")
+            last_error = e
+    if last_error is not None:
+        raise last_error
+    return None
 
 
 def save_dataloader_state(dataset, output_dir: str, step: int) -> Optional[str]:

@@ -85,6 +85,12 @@ def get_argument_parser() -> argparse.ArgumentParser:
     a("--commit-id", default="")
     a("--seed", type=int, default=None)
     a("--enable-profile", action="store_true")
+    a("--step-timeout", type=float, default=1800.0,
+      help="seconds without a finished step before the watchdog dumps all stacks (0 disables it)")
+    a("--heartbeat-timeout", type=float, default=300.0,
+      help="seconds without a peer's heartbeat before this rank stops between steps (multi-rank runs; 0 disables)")
+    a("--resume-fallback", action="store_true",
+      help="if the newest checkpoint is unfinished or unreadable, resume from the newest older complete one")
     a("--overfit-batches", type=int, default=0)
     # distillation
     a("--enable-distill", action="store_true")
@@ -199,17 +205,33 @@ def train(args) -> dict:
 
     dataset = _build_dataset(args, cfg, dp_rank, dp_size)
     seq_len = getattr(dataset, "seq_length", args.max_length or 8192)
+    cp_rank = 0
+    if cp > 1:
+        # the sequence is cut into ``cp`` contiguous chunk-aligned shards; every rank of a group reads the same
+        # sample (the dataset is indexed by data-parallel rank) and keeps its own slice
+        from ksa_b200.parallel.cp import CpContext
+        cp_rank = groups.get_context_parallel_rank()
+        summary = bool(getattr(cfg, "summary_enabled", False))
+        model.cp = CpContext(groups.get_context_parallel_group(), seq_len,
+                             cfg.summary_chunk_size if summary else 128, cfg.summary_token_num if summary else 0,
+                             cfg.num_kv_heads, cfg.head_dim, batch=args.batch_size,
+                             device=device if use_cuda else None, dtype=dtype,
+                             full_layers=not summary or any(not f for f in model._layer_is_summary()),
+                             max_window=getattr(cfg, "summary_sliding_chunk_num", 8) if summary else 8)
+        if args.enable_distill:
+            raise ValueError("distillation and context parallelism are not combined")
     checkpointer = ckpt.DistributedCheckpointer(async_save=args.async_checkpoint)
     step_offset = 0
     if args.checkpoint_dir and (args.resume_weights or args.resume_optimizer):
         app = ckpt.AppState(engine, sched, skip_optimizer=not args.resume_optimizer,
                             skip_training_state=not args.resume_optimizer)
-        loaded = ckpt.load_checkpoint(app, checkpointer, args.checkpoint_dir, args.checkpoint_id)
+        loaded = ckpt.load_checkpoint(app, checkpointer, args.checkpoint_dir, args.checkpoint_id,
+                                      fallback=args.resume_fallback)
         if loaded is not None:
             print_rank_0(f"[recipe] resumed from step {loaded} of {args.checkpoint_dir}")
             step_offset = loaded - sched.global_step
             if args.resume_dataloader:
-                ok = ckpt.load_dataloader_state(dataset, ckpt.get_checkpoint_path(args.checkpoint_dir, args.checkpoint_id))
+                ok = ckpt.load_dataloader_state(dataset, os.path.join(args.checkpoint_dir, ckpt.step_dir_name(loaded)))
                 print_rank_0(f"[recipe] dataloader state {'restored' if ok else 'not found: starting the stream over'}")
     metrics = initialize_metrics(seq_len, world, args.logging_per_step,
                                  [StdoutBackend(), CSVBackend(os.path.join(args.output_dir, "metrics.csv"))])
@@ -223,6 +245,14 @@ def train(args) -> dict:
         os.makedirs(os.path.join(args.output_dir, "torch_profile"), exist_ok=True)
         profiler.start()
 
+    from ksa_b200.utils.watchdog import FaultInjector, HeartbeatMonitor, StepWatchdog, check_device
+    watchdog = StepWatchdog(args.step_timeout).start() if args.step_timeout > 0 else None
+    heartbeat = None
+    if world > 1 and args.heartbeat_timeout > 0:
+        from torch.distributed.distributed_c10d import _get_default_store
+        heartbeat = HeartbeatMonitor(_get_default_store(), rank, world, args.heartbeat_timeout)
+    faults = FaultInjector(rank=rank)
+
     use_graph = use_cuda and world == 1 and not args.no_cuda_graph and not args.enable_distill \
         and not args.enable_gradient_checkpointing
     data_iter = iter(dataset)
@@ -230,6 +260,15 @@ def train(args) -> dict:
     last_loss = None
     t_prev = time.perf_counter()
     while sched.global_step + step_offset < args.num_training_steps:
+        # between steps, nothing in flight: stop here if a peer died rather than wait for it inside a collective
+        try:
+            faults.at_step(sched.micro_step)
+        except Exception as e:
+            if heartbeat is not None:
+                heartbeat.report_failure(f"{type(e).__name__}: {e}")
+            raise
+        if heartbeat is not None:
+            heartbeat.agree(sched.micro_step)
         if args.overfit_batches and len(cached) >= args.overfit_batches:
             batch = cached[sched.micro_step % args.overfit_batches]
         else:
@@ -240,6 +279,10 @@ def train(args) -> dict:
         labels, _ = make_labels(ids, batch["loss_mask"])
         if "next_token" in batch:   # the corpus stores L+1 tokens: the last position has a real target
             labels[:, -1] = batch["next_token"]
+        if cp > 1:                  # labels are shifted before the split, so a shard's last label is its successor's first token
+            Ll = ids.shape[1] // cp
+            ids = ids[:, cp_rank * Ll:(cp_rank + 1) * Ll].contiguous()
+            labels = labels[:, cp_rank * Ll:(cp_rank + 1) * Ll].contiguous()
         if hasattr(model, "set_mix_coeff"):
             model.set_mix_coeff(sched.global_step + step_offset)
         if args.enable_distill:
@@ -250,6 +293,12 @@ def train(args) -> dict:
         else:
             loss = engine.train_step(ids, labels)
         sched.step()
+        if watchdog is not None:
+            watchdog.beat()
+        if heartbeat is not None:
+            heartbeat.beat(sched.micro_step)
+        if use_cuda and sched.should_logging():
+            check_device()          # a bounded device-side wait that gave up shows here, as an exception
         metrics.loss.append(loss)
         metrics.tokens.append(ids.numel())
         metrics.samples.append(ids.shape[0])
@@ -281,7 +330,11 @@ def train(args) -> dict:
     checkpointer.wait()
     if profiler is not None:
         profiler.stop()
+    if watchdog is not None:
+        watchdog.stop()
     metrics.close()
+    if getattr(model, "cp", None) is not None:
+        model.cp.close()
     if hasattr(engine, "close"):
         engine.close()
     if world > 1:
