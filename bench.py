@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--preset", default="qwen3-1.9b-ksa")
     ap.add_argument("--cp", type=int, default=1,
                     help="context-parallel size: --seq-len is the whole sequence, split over groups of this many ranks")
+    ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"],
+                    help="full-attention layers under --cp: head-parallel resharding or staged earlier keys")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--comm", default=None, choices=["fused", "collective"],
                     help="multi-GPU back end: fused P2P kernels (default) or NCCL collectives (A/B baseline)")
@@ -155,7 +157,8 @@ def run_ours(args) -> dict:
         full_layers = any(not f for f in model._layer_is_summary())
         model.cp = CpContext(groups[rank // cp], L, cfg.summary_chunk_size, cfg.summary_token_num, cfg.num_kv_heads,
                              cfg.head_dim, batch=B, device=dev, full_layers=full_layers,
-                             max_window=cfg.summary_sliding_chunk_num)
+                             max_window=cfg.summary_sliding_chunk_num, n_heads=cfg.num_heads,
+                             full_layer_mode=args.cp_full_layers)
     g_cpu = torch.Generator().manual_seed(1234 + rank // cp)     # one sequence per context-parallel group
     n_batches = max(args.steps, 4)
     host_tokens = [torch.randint(0, cfg.vocab_size, (B, L + 1), generator=g_cpu) for _ in range(n_batches)]

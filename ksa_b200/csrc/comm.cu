@@ -90,6 +90,33 @@ peer_add_bf16_kernel(bf16* dst, const bf16* src, long long n, const uint32_t* fl
   }
 }
 
+// 2-D copy: `rows` rows of `row_bytes` (multiple of 16) from src (any rank's memory, pitch src_pitch) to dst (own
+// memory, pitch dst_pitch), after an optional bounded wait on a local flag.  The building block of the all-to-all
+// that turns sequence shards into head shards and back.
+__global__ void __launch_bounds__(kCommThreads)
+peer_copy2d_kernel(uint8_t* dst, long long dst_pitch, const uint8_t* src, long long src_pitch, long long rows,
+                   int row_vecs, const uint32_t* flag, const uint32_t* epoch_ptr, uint32_t add, int* status) {
+  __shared__ int s_ok;
+  if (flag) {
+    if (threadIdx.x == 0) s_ok = flag_wait_ge(flag, epoch_target(epoch_ptr, add), status, kTimeoutPeerFlag, true) ? 1 : 0;
+    __syncthreads();
+    if (!s_ok) return;
+  }
+  const long long total = rows * row_vecs, stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + stride < total; i += 2 * stride) {
+    const long long r0 = i / row_vecs, c0 = i - r0 * row_vecs;
+    const long long j = i + stride, r1 = j / row_vecs, c1 = j - r1 * row_vecs;
+    const uint4 a = ld_peer_16(src + r0 * src_pitch + c0 * 16), b = ld_peer_16(src + r1 * src_pitch + c1 * 16);
+    *reinterpret_cast<uint4*>(dst + r0 * dst_pitch + c0 * 16) = a;
+    *reinterpret_cast<uint4*>(dst + r1 * dst_pitch + c1 * 16) = b;
+  }
+  for (; i < total; i += stride) {
+    const long long r0 = i / row_vecs, c0 = i - r0 * row_vecs;
+    *reinterpret_cast<uint4*>(dst + r0 * dst_pitch + c0 * 16) = ld_peer_16(src + r0 * src_pitch + c0 * 16);
+  }
+}
+
 }  // namespace ksa
 
 using namespace ksa;
@@ -230,6 +257,26 @@ KSA_API int ksa_peer_add_bf16(void* dst, const void* src, long long n, const voi
   if (ctas <= 0) ctas = 32;
   peer_add_bf16_kernel<<<ctas, kCommThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (bf16*)dst, (const bf16*)src, n, (const uint32_t*)flag, (const uint32_t*)epoch_ptr, epoch_add, status);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// dst (own memory, pitch dst_pitch) = src (any rank's memory, pitch src_pitch): rows x row_bytes, every address and
+// pitch a multiple of 16 bytes, with the same optional flag wait as ksa_peer_copy.
+KSA_API int ksa_peer_copy2d(void* dst, long long dst_pitch, const void* src, long long src_pitch, long long rows,
+                            long long row_bytes, const void* flag, const void* epoch_ptr, unsigned epoch_add, int ctas,
+                            void* stream) {
+  KSA_ENTER(dst);
+  KSA_REQUIRE(row_bytes % 16 == 0 && dst_pitch % 16 == 0 && src_pitch % 16 == 0,
+              "peer_copy2d: row bytes and pitches must be multiples of 16");
+  KSA_REQUIRE(row_bytes <= dst_pitch && row_bytes <= src_pitch, "peer_copy2d: a row is longer than its pitch");
+  if (rows == 0 || row_bytes == 0) return 0;
+  int* status = status_word();
+  KSA_REQUIRE(status != nullptr, "could not allocate the status word");
+  if (ctas <= 0) ctas = 32;
+  peer_copy2d_kernel<<<ctas, kCommThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (uint8_t*)dst, dst_pitch, (const uint8_t*)src, src_pitch, rows, (int)(row_bytes / 16), (const uint32_t*)flag,
+      (const uint32_t*)epoch_ptr, epoch_add, status);
   KSA_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -1,5 +1,7 @@
 from .mmap_dataset import (BlendableWeightedSamplingDataset, KaiMMapDataset, MMapDataset, SyntheticTokenDataset,
                            make_labels, parse_data_prefix, write_corpus)
+from .parquet_dataset import DistributedParquetDataset, ParquetReader, ShuffledParquetReader, expand_sources
 
 __all__ = ["BlendableWeightedSamplingDataset", "KaiMMapDataset", "MMapDataset", "SyntheticTokenDataset", "make_labels",
-           "parse_data_prefix", "write_corpus"]
+           "parse_data_prefix", "write_corpus", "DistributedParquetDataset", "ParquetReader", "ShuffledParquetReader",
+           "expand_sources"]

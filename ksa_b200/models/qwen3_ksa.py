@@ -313,7 +313,7 @@ class Qwen3Model(Model):
                 raise NotImplementedError("explicit position ids are not combined with context parallelism")
             if L != self.cp.shape.local_len or B != self.cp.batch:
                 raise ValueError(f"context-parallel shard is [{self.cp.batch}, {self.cp.shape.local_len}], got [{B}, {L}]")
-            key = ("cp", B, L, str(device), use_summary)
+            key = ("cp", id(self.cp), B, L, str(device), use_summary)
             if key not in self._meta_cache:
                 layout = self._layout(self.cp.shape.seq_len) if use_summary else None
                 self._meta_cache[key] = BatchMeta(B, L, layout, device, self.config.rope_impl == "llama", cp=self.cp)

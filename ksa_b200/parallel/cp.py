@@ -71,7 +71,8 @@ class CpContext:
     """Group, shard shape and (on GPUs) the symmetric exchange buffers of one context-parallel group."""
 
     def __init__(self, group, seq_len: int, chunk: int, n_sum: int, n_kv_heads: int, head_dim: int, batch: int = 1,
-                 device=None, dtype=torch.bfloat16, full_layers: bool = False, max_window: int = 8):
+                 device=None, dtype=torch.bfloat16, full_layers: bool = False, max_window: int = 8,
+                 n_heads: Optional[int] = None, full_layer_mode: str = "auto"):
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
@@ -84,6 +85,19 @@ class CpContext:
         self.counter = 0                                    # forward exchanges issued so far (same on every rank)
         self.counter_bwd = 0                                # backward exchanges (they use their own slots and flags)
         self.slot_last = [None, None, None, None]           # exchange number of each slot's previous use
+        # full-attention layers: "ulysses" reshards sequence -> heads around the attention (balanced causal work),
+        # "halo" stages every earlier key in front of the shard (rank r does (2r+1)/P^2 of the work)
+        self.n_heads, self.n_kv_heads, self.head_dim = n_heads, n_kv_heads, head_dim
+        can_ulysses = n_heads is not None and n_heads % self.size == 0 and n_kv_heads % self.size == 0
+        if full_layer_mode == "auto":
+            full_layer_mode = "ulysses" if can_ulysses else "halo"
+        if full_layer_mode == "ulysses" and not can_ulysses:
+            raise ValueError(f"head-parallel full-attention layers need heads ({n_heads}/{n_kv_heads}) divisible by {self.size}")
+        self.full_layer_mode = full_layer_mode
+        self.a2a_counter = 0
+        self.a2a_slot_last = [None, None]
+        if full_layer_mode == "ulysses":
+            full_layers = False                             # no gradient return blocks of whole shards are needed
         if self.fused:
             from .symm import SignalPad, SymmetricBuffer
             rows = batch * (self.shape.local_len + self.shape.local_sum)
@@ -96,6 +110,13 @@ class CpContext:
             self.ready = SignalPad(4 * self.size, group, device)      # [slot][producer rank] <- exchange number + 1
             self.consumed = SignalPad(4 * self.size, group, device)   # [slot][consumer rank] <- exchange number + 1
             self.dtype = dtype
+            self.a2a_buf = None
+            if self.full_layer_mode == "ulysses":
+                width = (n_heads + 2 * n_kv_heads) * head_dim
+                self.a2a_slot_bytes = batch * self.shape.local_len * width * item
+                self.a2a_buf = SymmetricBuffer(2 * self.a2a_slot_bytes, group, device)
+                self.a2a_ready = SignalPad(2 * self.size, group, device)
+                self.a2a_consumed = SignalPad(2 * self.size, group, device)
 
     def close(self) -> None:
         if self.fused:
@@ -103,6 +124,10 @@ class CpContext:
             self.ready.close()
             self.consumed.close()
             self.xbuf.close()
+            if self.a2a_buf is not None:
+                self.a2a_ready.close()
+                self.a2a_consumed.close()
+                self.a2a_buf.close()
 
     # ------------------------------------------------------------------ ranges
     def text_sources(self, halo: int) -> List[Tuple[int, int, int]]:
@@ -244,6 +269,114 @@ class _CpStage(torch.autograd.Function):
         return g_local, None, None, None
 
 
+# ------------------------------------------------------------------------------------------ sequence <-> head resharding
+def _a2a(cp: CpContext, x: torch.Tensor, to_heads: bool, groups, total_width: int) -> torch.Tensor:
+    """All-to-all between the sequence-sharded layout ``[B*Ll, total_width]`` (all columns of this rank's rows) and the
+    head-sharded layout ``[B*L, w]`` (this rank's column groups of every row).  ``groups(rank)`` lists the
+    ``(first column, width)`` ranges owned by ``rank`` in the full width.
+
+    GPUs: every rank copies its block into a symmetric slot, raises its flag, and pulls what it needs from every peer
+    with 2-D P2P copies (``ksa_peer_copy2d``) that wait, bounded, on the owner's flag.  CPU ranks: ``all_gather``.
+    """
+    sh, B, P, r = cp.shape, cp.batch, cp.size, cp.rank
+    Ll, L = sh.local_len, sh.seq_len
+    w = sum(g[1] for g in groups(r))
+    x = x.contiguous()
+    if to_heads:
+        out = x.new_empty(B * L, w)
+    else:
+        out = x.new_empty(B * Ll, total_width)
+    if not cp.fused:
+        parts = [torch.empty_like(x) for _ in range(P)]
+        dist.all_gather(parts, x, group=cp.group)
+        for p in range(P):
+            if to_heads:
+                src = parts[p].view(B, Ll, total_width)
+                off = 0
+                for c0, cw in groups(r):
+                    out.view(B, L, w)[:, p * Ll:(p + 1) * Ll, off:off + cw] = src[:, :, c0:c0 + cw]
+                    off += cw
+            else:
+                src = parts[p].view(B, L, w)
+                off = 0
+                for c0, cw in groups(p):
+                    out.view(B, Ll, total_width)[:, :, c0:c0 + cw] = src[:, r * Ll:(r + 1) * Ll, off:off + cw]
+                    off += cw
+        return out
+    n = cp.a2a_counter
+    cp.a2a_counter += 1
+    slot = n % 2
+    item = x.element_size()
+    if x.numel() * item > cp.a2a_slot_bytes:
+        raise ValueError("all-to-all block exceeds the exchange buffer")
+    if cp.a2a_slot_last[slot] is not None:
+        cp.a2a_consumed.wait_local(slot * P, P, None, cp.a2a_slot_last[slot] + 1)
+    cp.a2a_slot_last[slot] = n
+    base = slot * cp.a2a_slot_bytes
+    cp.a2a_buf.view(x.dtype, base, x.numel()).copy_(x.reshape(-1))
+    cp.a2a_ready.set_on_all(slot * P + r, None, n + 1)
+    for p in range(P):
+        flag = cp.a2a_ready.local_ptr(slot * P + p)
+        peer = cp.a2a_buf.peer_ptrs[p] + base
+        for b in range(B):
+            off = 0
+            for c0, cw in (groups(r) if to_heads else groups(p)):
+                if to_heads:    # peer p's rows (b, 0..Ll) x my columns -> my rows (b, p*Ll ..)
+                    src = peer + ((b * Ll) * total_width + c0) * item
+                    dst = out[b * L + p * Ll:b * L + (p + 1) * Ll, off:off + cw]
+                    _lib.call("ksa_peer_copy2d", dst, w * item, src, total_width * item, Ll, cw * item, flag, None,
+                              n + 1, 16)
+                else:           # peer p's copy of my rows (b, r*Ll ..) x p's columns -> my rows x p's column ranges
+                    src = peer + ((b * L + r * Ll) * w + off) * item
+                    dst = out[b * Ll:(b + 1) * Ll, c0:c0 + cw]
+                    _lib.call("ksa_peer_copy2d", dst, total_width * item, src, w * item, Ll, cw * item, flag, None,
+                              n + 1, 16)
+                off += cw
+    cp.a2a_consumed.set_on_all(slot * P + r, None, n + 1)
+    return out
+
+
+class _SeqToHead(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cp, groups, total_width):
+        ctx.cp, ctx.groups, ctx.total_width = cp, groups, total_width
+        return _a2a(cp, x, True, groups, total_width)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _a2a(ctx.cp, g, False, ctx.groups, ctx.total_width), None, None, None
+
+
+class _HeadToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cp, groups, total_width):
+        ctx.cp, ctx.groups, ctx.total_width = cp, groups, total_width
+        return _a2a(cp, x, False, groups, total_width)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _a2a(ctx.cp, g, True, ctx.groups, ctx.total_width), None, None, None
+
+
+def cp_full_attention_ulysses(qkv: torch.Tensor, cp: CpContext, Hq: int, Hkv: int, D: int, tok_window: int = 0,
+                              scale: Optional[float] = None) -> torch.Tensor:
+    """Full causal attention of a context-parallel group with balanced work: reshard the packed, rotated projection
+    rows from sequence shards to head shards, run whole-sequence causal attention on ``Hq/P`` heads, reshard the
+    output back (the data movement of DeepSpeed-Ulysses, ``muse/training/parallel.py:211-335``, done with P2P copies
+    instead of four NCCL all-to-alls)."""
+    P, B, L = cp.size, cp.batch, cp.shape.seq_len
+    hq, hkv = Hq // P, Hkv // P
+
+    def qkv_groups(r):
+        return [(r * hq * D, hq * D), (Hq * D + r * hkv * D, hkv * D), ((Hq + Hkv) * D + r * hkv * D, hkv * D)]
+
+    def o_groups(r):
+        return [(r * hq * D, hq * D)]
+    heads = _SeqToHead.apply(qkv, cp, qkv_groups, (Hq + 2 * Hkv) * D)
+    o = ops.attention_packed(heads, B, L, 0, hq, hkv, D, tok_window=tok_window, scale=scale)
+    return _HeadToSeq.apply(o, cp, o_groups, Hq * D)
+
+
 def _cpu_shard_attention(q_t, k_t, v_t, q_s, k_s, v_s, sh: CpShape, halo: int, window: Optional[int], tok_window: int,
                          scale: float):
     """Dense-mask fp32 attention of one shard: global masks sliced to the staged key ranges."""
@@ -281,6 +414,8 @@ def cp_attention_packed(qkv: torch.Tensor, cp: CpContext, Hq: int, Hkv: int, D: 
     Ll = sh.local_len
     Nsl = sh.local_sum if summaries else 0
     n_text = B * Ll
+    if not summaries and window_chunks is None and cp.full_layer_mode == "ulysses":
+        return cp_full_attention_ulysses(qkv, cp, Hq, Hkv, D, tok_window, scale)
     if qkv.shape[0] != n_text + B * Nsl:
         raise ValueError(f"expected {n_text + B * Nsl} packed rows for this shard, got {qkv.shape[0]}")
     scale = scale if scale is not None else D ** -0.5

@@ -1,0 +1,119 @@
+"""Prefill + greedy-decode benchmark of the inference engine (random-init weights, uniform-random prompt).
+
+    python -m ksa_b200.tools.infer_bench --preset ksa-4b --prompt-len 131072 --decode 512 --batch 1
+    python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 -m ksa_b200.tools.infer_bench \\
+        --preset ksa-4b --prompt-len 131072 --decode 512 --batch 16          # tensor parallel over 4 GPUs
+
+Times are CUDA-event times on the launching stream, maximum over ranks; one warm-up prefill and a few warm-up decode
+steps run first.  Prints one JSON line: prefill tokens/s (prompt tokens of all sequences / prefill time), decode
+tokens/s (batch x steps / decode time) and milliseconds per decode step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..config import get_preset
+from ..inference.engine import KsaInferenceEngine
+from ..models import get_model_class
+from ..ops import _lib
+
+
+def _random_model(cfg, device, dtype, seed: int):
+    with torch.device("meta"):
+        model = get_model_class(cfg.model_class)(cfg)
+    model = model.to_empty(device=device).to(dtype)
+    gen = torch.Generator(device=device).manual_seed(seed)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0.0, 0.02, generator=gen)
+            else:
+                p.fill_(1.0)
+    return model
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--preset", default="ksa-4b")
+    ap.add_argument("--prompt-len", type=int, default=131072)
+    ap.add_argument("--decode", type=int, default=512)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--warmup-decode", type=int, default=8)
+    ap.add_argument("--no-warmup-prefill", action="store_true")
+    a = ap.parse_args(argv)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    cfg = get_preset(a.preset)
+    C, S = cfg.summary_chunk_size, cfg.summary_token_num
+    B, L = a.batch, a.prompt_len
+    tp = None
+    local_cfg = cfg
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from ..parallel.tp import TpContext, tp_local_config
+        rows = B * (L + (L // C) * S)
+        tp = TpContext(dist.group.WORLD, cfg.embed_dim, max_rows=rows, device=dev)
+        local_cfg = tp_local_config(cfg, world)
+    model = _random_model(local_cfg, dev, torch.bfloat16, seed=0)   # same seed: replicated tensors agree across ranks
+    if tp is not None:
+        model.tp = tp
+        if model.output is not None and cfg.vocab_size % world == 0:     # vocabulary-parallel head
+            n = cfg.vocab_size // world
+            model.output.weight = torch.nn.Parameter(model.output.weight[rank * n:(rank + 1) * n].clone())
+    eng = KsaInferenceEngine(model, max_len=L + a.decode + a.warmup_decode + C, batch=B)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, min(cfg.vocab_size, 150000), (B, L), generator=g).to(dev)
+
+    def sync_max(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def timed(fn):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        out = fn()
+        e.record()
+        torch.cuda.synchronize()
+        return out, sync_max(s.elapsed_time(e))
+
+    if not a.no_warmup_prefill:
+        eng.prefill(prompt)
+    logits, ms_prefill = timed(lambda: eng.prefill(prompt))
+    nxt = logits.argmax(-1)
+    for _ in range(a.warmup_decode):
+        nxt = eng.decode_step(nxt).argmax(-1)
+
+    def decode():
+        t = nxt
+        for _ in range(a.decode):
+            t = eng.decode_step(t).argmax(-1)
+        return t
+    _, ms_decode = timed(decode)
+    _lib.check_status()
+    if rank == 0:
+        print(json.dumps({
+            "model": a.preset, "tp": world, "batch": B, "prompt_len": L, "decode_steps": a.decode, "dtype": "bf16",
+            "prefill_ms": ms_prefill, "prefill_tokens_per_s": B * L / (ms_prefill / 1e3),
+            "decode_ms_per_step": ms_decode / a.decode, "decode_tokens_per_s": B * a.decode / (ms_decode / 1e3),
+            "kv_cache_gb_per_gpu": eng.cache_bytes() / 1e9, "data": "uniform random prompt, random-init weights"}),
+            flush=True)
+    if tp is not None:
+        tp.close()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -135,7 +135,8 @@ def bench_cp_attn(a) -> None:
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     B, Hq, Hkv, D, C, S, W, L = a.batch, a.hq, a.hkv, a.dim, a.chunk, a.nsum, a.window, a.seq
-    cp = CpContext(dist.group.WORLD, L, C, S, Hkv, D, batch=B, device=dev, full_layers=a.causal, max_window=W)
+    cp = CpContext(dist.group.WORLD, L, C, S, Hkv, D, batch=B, device=dev, full_layers=a.causal, max_window=W,
+                   n_heads=Hq, full_layer_mode=a.cp_full_layers)
     Ll, Nsl = L // world, 0 if a.causal else (L // world // C) * S
     qkv = torch.randn(B * (Ll + Nsl), (Hq + 2 * Hkv) * D, device=dev).bfloat16().requires_grad_(a.bwd)
     out = [None]
@@ -184,6 +185,7 @@ def main(argv=None) -> None:
     ap.add_argument("--cap", type=int, default=131072); ap.add_argument("--rows", type=int, default=8256)
     ap.add_argument("--iters", type=int, default=10); ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"])
     a = ap.parse_args(argv)
     {"gemm": bench_gemm, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn}[a.what](a)
     _lib.check_status()

@@ -217,7 +217,8 @@ def train(args) -> dict:
                              cfg.num_kv_heads, cfg.head_dim, batch=args.batch_size,
                              device=device if use_cuda else None, dtype=dtype,
                              full_layers=not summary or any(not f for f in model._layer_is_summary()),
-                             max_window=getattr(cfg, "summary_sliding_chunk_num", 8) if summary else 8)
+                             max_window=getattr(cfg, "summary_sliding_chunk_num", 8) if summary else 8,
+                             n_heads=cfg.num_heads)
         if args.enable_distill:
             raise ValueError("distillation and context parallelism are not combined")
     checkpointer = ckpt.DistributedCheckpointer(async_save=args.async_checkpoint)

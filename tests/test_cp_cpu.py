@@ -42,7 +42,8 @@ def _worker(rank, world, port, L, chunk, window, n_sum, out_q):
         g = torch.Generator().manual_seed(3)
         toks = torch.randint(0, 200, (B, L + 1), generator=g)
         tokens, labels = shard_inputs(toks[:, :-1], toks[:, 1:], rank, world)
-        model.cp = CpContext(dist.group.WORLD, L, chunk, n_sum, cfg.num_kv_heads, cfg.head_dim, batch=B)
+        model.cp = CpContext(dist.group.WORLD, L, chunk, n_sum, cfg.num_kv_heads, cfg.head_dim, batch=B,
+                             n_heads=cfg.num_heads)
         loss = model(tokens, labels)
         loss.backward()
         grads = {n: p.grad.numpy().copy() for n, p in model.named_parameters() if p.grad is not None}

@@ -37,9 +37,12 @@ def _worker(rank, world, port, out_q):
         dev = torch.device("cuda", rank)
         B, L, C, S, W, Hq, Hkv, D = 2, 2048, 128, 1, 3, 4, 2, 128
         Ns = (L // C) * S
-        cp = CpContext(dist.group.WORLD, L, C, S, Hkv, D, batch=B, device=dev, full_layers=True)
         g = torch.Generator(device="cpu").manual_seed(5)
-        for summaries in (True, False, True):   # the third pass reuses an exchange slot
+        cps = {m: CpContext(dist.group.WORLD, L, C, S, Hkv, D, batch=B, device=dev, full_layers=True, n_heads=Hq,
+                            full_layer_mode=m) for m in ("halo", "ulysses")}
+        # summary layers, then full layers staged (halo) and resharded to heads (ulysses); the last pass reuses slots
+        for summaries, mode in ((True, "halo"), (False, "halo"), (False, "ulysses"), (True, "ulysses"), (False, "ulysses")):
+            cp = cps[mode]
             ns = Ns if summaries else 0
             full = (torch.randn(B * (L + ns), (Hq + 2 * Hkv) * D, generator=g) * 0.5).to(dev).bfloat16()
             go = torch.randn(B * (L + ns), Hq * D, generator=g).to(dev).bfloat16()
@@ -57,8 +60,9 @@ def _worker(rank, world, port, out_q):
             torch.testing.assert_close(o_loc.float(), o_full[rows].float(), atol=2e-2, rtol=2e-2)
             ref_g = x_full.grad[rows].float()
             err = (x_loc.grad.float() - ref_g).norm() / ref_g.norm()
-            assert err < 2e-2, (summaries, float(err))
-        cp.close()
+            assert err < 2e-2, (summaries, mode, float(err))
+        for c in cps.values():
+            c.close()
 
         # whole model: shard loss / gradients against the whole sequence on one GPU
         from ksa_b200.config import get_preset
@@ -75,25 +79,27 @@ def _worker(rank, world, port, out_q):
         loss_full = model(toks[:, :-1].contiguous(), toks[:, 1:].contiguous())
         loss_full.backward()
         ref_grads = {n: p.grad.float().clone() for n, p in model.named_parameters() if p.grad is not None}
-        model.zero_grad(set_to_none=True)
-        model.cp = CpContext(dist.group.WORLD, Lm, 128, cfg.summary_token_num, cfg.num_kv_heads, cfg.head_dim, batch=1,
-                             device=dev, full_layers=True)
         tokens, labels = shard_inputs(toks[:, :-1], toks[:, 1:], rank, world)
-        loss = model(tokens, labels)
-        loss.backward()
-        torch.cuda.synchronize(); _lib.check_status()
-        lsum = loss.detach().float().clone()
-        dist.all_reduce(lsum)
-        assert abs(float(lsum) / world - float(loss_full)) < 3e-2, (float(lsum) / world, float(loss_full))
-        for n, p in model.named_parameters():
-            if p.grad is None:
-                continue
-            gsum = p.grad.float().clone()
-            dist.all_reduce(gsum)
-            gsum /= world
-            err = (gsum - ref_grads[n]).norm() / ref_grads[n].norm().clamp_min(1e-6)
-            assert err < 5e-2, (n, float(err))
-        model.cp.close()
+        for mode in ("halo", "ulysses"):
+            model.zero_grad(set_to_none=True)
+            model.cp = CpContext(dist.group.WORLD, Lm, 128, cfg.summary_token_num, cfg.num_kv_heads, cfg.head_dim, batch=1,
+                                 device=dev, full_layers=True, n_heads=cfg.num_heads, full_layer_mode=mode)
+            loss = model(tokens, labels)
+            loss.backward()
+            torch.cuda.synchronize(); _lib.check_status()
+            lsum = loss.detach().float().clone()
+            dist.all_reduce(lsum)
+            assert abs(float(lsum) / world - float(loss_full)) < 3e-2, (float(lsum) / world, float(loss_full))
+            for n, p in model.named_parameters():
+                if p.grad is None:
+                    continue
+                gsum = p.grad.float().clone()
+                dist.all_reduce(gsum)
+                gsum /= world
+                err = (gsum - ref_grads[n]).norm() / ref_grads[n].norm().clamp_min(1e-6)
+                assert err < 5e-2, (mode, n, float(err))
+            model.cp.close()
+            model.cp = None
         out_q.put((rank, "ok"))
     except Exception as exc:  # report instead of leaving the parent to time out
         import traceback
