@@ -60,7 +60,6 @@ __device__ __forceinline__ void load_tile_b(uint8_t* dst, const CUtensorMap* m, 
   for (int half = 0; half < HD / 64; ++half) tma_load_4d(dst + half * 16384, m, half * 64, row0, h, b, bar);
 }
 
-__device__ __forceinline__ void wg_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // Store a row of HD fp32 accumulators from TMEM as bf16 to global memory.
 template <int HD>
@@ -100,9 +99,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;                 // kStages
   uint64_t* kv_empty = kv_full + S::kStages;    // kStages
-  uint64_t* sp_full = kv_empty + S::kStages;    // 1
-  uint64_t* ds_full = sp_full + 1;              // 1
-  uint64_t* dq_full = ds_full + 1;              // 1
+  uint64_t* sp_full = kv_empty + S::kStages;    // 2: one per key half
+  uint64_t* ds_full = sp_full + 2;              // 2
+  uint64_t* dq_full = ds_full + 2;              // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -119,8 +118,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < S::kStages; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    mbar_init(sp_full, 1);
-    mbar_init(ds_full, 256);
+    for (int h = 0; h < 2; ++h) { mbar_init(&sp_full[h], 1); mbar_init(&ds_full[h], 128); }
     mbar_init(dq_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -151,33 +149,61 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      // The 128 keys of a tile are handled as two halves of 64 (one per softmax warpgroup), software-pipelined:
+      // while a warpgroup turns the scores of its half into dS, the tensor pipe runs the other half's dQ update and
+      // the next tile's S / dP for the half that has just been consumed.  tcgen05 MMAs issued by one thread execute
+      // in order, so S/dP of step j+1 may be issued right behind the dQ MMA that reads dS of step j from the same
+      // TMEM columns.
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, HD, 0, 1);
+      const uint32_t qa = smem_u32(sQ), doa = smem_u32(sdO);
+      auto issue_sdp = [&](int h, uint32_t ka, uint32_t va) {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tS + h * 64, smem_desc_kmajor_sw128(qa + off), smem_desc_kmajor_sw128(ka + h * 8192 + off), idesc_s,
+                  kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tdP + h * 64, smem_desc_kmajor_sw128(doa + off), smem_desc_kmajor_sw128(va + h * 8192 + off), idesc_s,
+                  kk != 0);
+        }
+        umma_commit(&sp_full[h]);
+      };
       bool ok = mbar_wait(q_full, 0, guard, kTimeoutTmaFull);
+      if (ok && total > 0) {
+        ok = mbar_wait(&kv_full[0], 0, guard, kTimeoutTmaFull);
+        if (ok) {
+          tc_fence_after();
+          const uint32_t ka0 = smem_u32(sRing);
+          issue_sdp(0, ka0, ka0 + S::kTile);
+          issue_sdp(1, ka0, ka0 + S::kTile);
+        }
+      }
       for (int j = 0; j < total && ok; ++j) {
         const int stage = j % S::kStages;
-        if (!mbar_wait(&kv_full[stage], (j / S::kStages) & 1, guard, kTimeoutTmaFull)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), doa = smem_u32(sdO);
-        const uint32_t ka = smem_u32(sRing + stage * 2 * S::kTile), va = ka + S::kTile;
+        const uint32_t ka = smem_u32(sRing + stage * 2 * S::kTile);
+        const int nstage = (j + 1) % S::kStages;
+        const uint32_t kan = smem_u32(sRing + nstage * 2 * S::kTile);
+        for (int h = 0; h < 2 && ok; ++h) {
+          if (!mbar_wait(&ds_full[h], j & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tS, smem_desc_kmajor_sw128(qa + off), smem_desc_kmajor_sw128(ka + off), idesc_s, kk != 0);
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const int kk = h * 4 + k4;
+            umma_ts(tdQ, tS + h * 64 + k4 * 8, smem_desc_mnmajor_sw128(ka + kk * 2048, 16384), idesc_dq, (j | kk) != 0);
+          }
+          if (h == 1) umma_commit(&kv_empty[stage]);
+          if (j + 1 < total) {
+            if (h == 0) {
+              if (!mbar_wait(&kv_full[nstage], ((j + 1) / S::kStages) & 1, guard, kTimeoutTmaFull)) { ok = false; break; }
+              tc_fence_after();
+            }
+            issue_sdp(h, kan, kan + S::kTile);
+          }
         }
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tdP, smem_desc_kmajor_sw128(doa + off), smem_desc_kmajor_sw128(va + off), idesc_s, kk != 0);
-        }
-        umma_commit(sp_full);
-        if (!mbar_wait(ds_full, j & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tdQ, tS + (kk / 4) * 64 + (kk % 4) * 8, smem_desc_mnmajor_sw128(ka + kk * 2048, 16384), idesc_dq,
-                  (j | kk) != 0);
-        umma_commit(&kv_empty[stage]);
       }
       if (ok) umma_commit(dq_full);
     }
@@ -212,7 +238,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     bool ok = true;
     for (int j = 0; j < total; ++j) {
-      if (!mbar_wait(sp_full, j & 1, guard, kTimeoutAccFull)) { ok = false; break; }
+      if (!mbar_wait(&sp_full[half], j & 1, guard, kTimeoutAccFull)) { ok = false; break; }
       tc_fence_after();
       const bool is_sum = j < tr.n_sum_tiles;
       const int kt = is_sum ? j : tr.text_first + (j - tr.n_sum_tiles);
@@ -244,7 +270,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(ds_full);
+      mbar_arrive(&ds_full[half]);
     }
     if (ok) ok = mbar_wait(dq_full, 0, guard, kTimeoutAccFull);
     if (ok) {
@@ -281,9 +307,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* kv_full = bars;
   uint64_t* q_full = bars + 1;                // kStages
   uint64_t* q_empty = q_full + S::kStages;    // kStages
-  uint64_t* sp_full = q_empty + S::kStages;
-  uint64_t* pds_full = sp_full + 1;
-  uint64_t* acc_full = pds_full + 1;
+  uint64_t* sp_full = q_empty + S::kStages;   // 2: one per query half
+  uint64_t* pds_full = sp_full + 2;           // 2
+  uint64_t* acc_full = pds_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -310,8 +336,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < S::kStages; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
-    mbar_init(sp_full, 1);
-    mbar_init(pds_full, 256);
+    for (int h = 0; h < 2; ++h) { mbar_init(&sp_full[h], 1); mbar_init(&pds_full[h], 128); }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -340,37 +365,63 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0 && total > 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      // Same software pipeline as the dQ kernel, over the two halves of 64 query columns: warpgroup h turns
+      // S^T / dP^T of its half into P^T / dS^T while the tensor pipe updates dV / dK with the other half and computes
+      // the next step's scores for the half that has just been consumed.
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, 0, 1);
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      auto issue_sdp = [&](int h, uint32_t qa, uint32_t doa) {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tS + h * 64, smem_desc_kmajor_sw128(ka + off), smem_desc_kmajor_sw128(qa + h * 8192 + off), idesc_s,
+                  kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tdP + h * 64, smem_desc_kmajor_sw128(va + off), smem_desc_kmajor_sw128(doa + h * 8192 + off), idesc_s,
+                  kk != 0);
+        }
+        umma_commit(&sp_full[h]);
+      };
       bool ok = mbar_wait(kv_full, 0, guard, kTimeoutTmaFull);
+      if (ok) {
+        ok = mbar_wait(&q_full[0], 0, guard, kTimeoutTmaFull);
+        if (ok) {
+          tc_fence_after();
+          const uint32_t qa0 = smem_u32(sRing);
+          issue_sdp(0, qa0, qa0 + S::kTile);
+          issue_sdp(1, qa0, qa0 + S::kTile);
+        }
+      }
       for (int i = 0; i < total && ok; ++i) {
-        const int stage = i % S::kStages;
-        if (!mbar_wait(&q_full[stage], (i / S::kStages) & 1, guard, kTimeoutTmaFull)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+        const int stage = i % S::kStages, nstage = (i + 1) % S::kStages;
         const uint32_t qa = smem_u32(sRing + stage * 2 * S::kTile), doa = qa + S::kTile;
+        const uint32_t qan = smem_u32(sRing + nstage * 2 * S::kTile);
+        for (int h = 0; h < 2 && ok; ++h) {
+          if (!mbar_wait(&pds_full[h], i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tS, smem_desc_kmajor_sw128(ka + off), smem_desc_kmajor_sw128(qa + off), idesc_s, kk != 0);
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const int kk = h * 4 + k4;
+            umma_ts(tdV, tS + h * 64 + k4 * 8, smem_desc_mnmajor_sw128(doa + kk * 2048, 16384), idesc_acc, (i | kk) != 0);
+          }
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const int kk = h * 4 + k4;
+            umma_ts(tdK, tdP + h * 64 + k4 * 8, smem_desc_mnmajor_sw128(qa + kk * 2048, 16384), idesc_acc, (i | kk) != 0);
+          }
+          if (h == 1) umma_commit(&q_empty[stage]);
+          if (i + 1 < total) {
+            if (h == 0) {
+              if (!mbar_wait(&q_full[nstage], ((i + 1) / S::kStages) & 1, guard, kTimeoutTmaFull)) { ok = false; break; }
+              tc_fence_after();
+            }
+            issue_sdp(h, qan, qan + S::kTile);
+          }
         }
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tdP, smem_desc_kmajor_sw128(va + off), smem_desc_kmajor_sw128(doa + off), idesc_s, kk != 0);
-        }
-        umma_commit(sp_full);
-        if (!mbar_wait(pds_full, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tdV, tS + (kk / 4) * 64 + (kk % 4) * 8, smem_desc_mnmajor_sw128(doa + kk * 2048, 16384), idesc_acc,
-                  (i | kk) != 0);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ts(tdK, tdP + (kk / 4) * 64 + (kk % 4) * 8, smem_desc_mnmajor_sw128(qa + kk * 2048, 16384), idesc_acc,
-                  (i | kk) != 0);
-        umma_commit(&q_empty[stage]);
       }
       if (ok) umma_commit(acc_full);
     }
@@ -396,23 +447,30 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     if (!valid) { t_lo = 1; t_hi = 0; }
     bool ok = true;
-    for (int i = 0; i < total; ++i) {
+    // LSE (threads 0..63 of the warpgroup) or delta (threads 64..127) of query column `half*64 + (r & 63)`; the value
+    // for step i+1 is requested while step i is processed, so its global-memory latency is off the critical path.
+    auto load_stat = [&](int i) -> float {
       const int qt = qr.first + i / G, head = kv_head * G + i % G;
-      const bool got = mbar_wait(sp_full, i & 1, guard, kTimeoutAccFull);
-      // Stage LSE (warpgroup 0) and delta (warpgroup 1) of this query tile, double-buffered by iteration parity:
-      // the buffer written here was last read two iterations ago, and every thread has passed the barrier between.
-      float* lse_s = sLse + (i & 1) * 256;
-      float* delta_s = lse_s + 128;
-      {
-        const int ql = qt * 128 + r;
-        const long long sidx = ((long long)b * sh.Hq + head) * sh.Lq + ql;
-        const bool qv = ql < sh.Lq;
-        if (half == 0) lse_s[r] = qv ? p.lse[sidx] * 1.4426950408889634f : INFINITY;
-        else delta_s[r] = qv ? p.delta[sidx] : 0.f;
-      }
+      const int ql = qt * 128 + half * 64 + (r & 63);
+      if (ql >= sh.Lq) return r < 64 ? INFINITY : 0.f;
+      const long long sidx = ((long long)b * sh.Hq + head) * sh.Lq + ql;
+      return r < 64 ? p.lse[sidx] * 1.4426950408889634f : p.delta[sidx];
+    };
+    float stat_next = total > 0 ? load_stat(0) : 0.f;
+    for (int i = 0; i < total; ++i) {
+      const int qt = qr.first + i / G;
+      const bool got = mbar_wait(&sp_full[half], i & 1, guard, kTimeoutAccFull);
+      // Staged per warpgroup and double-buffered by iteration parity: the buffer written here was last read two
+      // iterations ago, and every thread of the warpgroup has passed its barrier between.
+      // Layout per parity: [half][lse 64 | delta 64].
+      float* lse_s = sLse + (i & 1) * 256 + half * 128;
+      float* delta_s = lse_s + 64;
+      lse_s[r] = stat_next;                   // r < 64: lse_s[r]; r >= 64: delta_s[r - 64]
+      if (i + 1 < total) stat_next = load_stat(i + 1);
       (void)got;  // a failed wait has raised the CTA abort flag before returning
-      wg_sync();
-      if (*abort_flag) { ok = false; break; }  // uniform across both warpgroups: read after the barrier
+      if (half == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+      else asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (*abort_flag) { ok = false; break; }  // a raised flag stays raised: the other warpgroup sees it at its next step
       tc_fence_after();
       const long long tq0 = (long long)sh.q_off + qt * 128;
       const int lo = (int)max(t_lo - tq0, 0LL), hi = (int)min(t_hi - tq0, 127LL);
@@ -433,8 +491,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int e = 0; e < 2; ++e) {
             const int col = c * 32 + 2 * k + e;
             pr[e] = (col >= lo && col <= hi)
-                        ? fast_exp2(fmaf(__uint_as_float(sr[2 * k + e]), p.scale_log2, -lse_s[col])) : 0.f;
-            ds[e] = pr[e] * (__uint_as_float(dr[2 * k + e]) - delta_s[col]) * p.scale;
+                        ? fast_exp2(fmaf(__uint_as_float(sr[2 * k + e]), p.scale_log2, -lse_s[col - half * 64])) : 0.f;
+            ds[e] = pr[e] * (__uint_as_float(dr[2 * k + e]) - delta_s[col - half * 64]) * p.scale;
           }
           pk[k] = pack_bf16x2(pr[0], pr[1]);
           dk[k] = pack_bf16x2(ds[0], ds[1]);
@@ -444,7 +502,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(pds_full);
+      mbar_arrive(&pds_full[half]);
     }
     // Epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK.
     const bool do_k = half == 1;

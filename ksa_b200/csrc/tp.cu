@@ -20,27 +20,14 @@ struct TpReduceArgs {
   bf16* y;                         // normalised output [rows_x, D]
   int rows_x, delta_rows, D;
   float eps;
-  uint32_t target;
+  const uint32_t* epoch;           // device counter of finished all-reduces; this call's flag value is *epoch + 1
+  uint32_t* done;                  // CTAs of this launch that have finished (the last one advances *epoch)
 };
 
 constexpr int kTpThreads = 256;
 constexpr int kTpMaxVec = 4;  // D <= 8192
 
-__global__ void __launch_bounds__(kTpThreads) tp_allreduce_add_rmsnorm_kernel(TpReduceArgs a, int* status) {
-  __shared__ float red[32];
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  // the partial block was written by the previous kernel of this stream: publish it, then wait for every peer's
-  if (blockIdx.x == 0 && threadIdx.x < a.world) {
-    __threadfence_system();
-    st_release_sys(a.announce[threadIdx.x], a.target);
-  }
-  if (threadIdx.x < a.world) {
-    if (!flag_wait_ge(a.local_flags + threadIdx.x, a.target, status, kTimeoutPeerFlag, true)) s_ok = 0;
-  }
-  __syncthreads();
-  if (!s_ok) return;
+__device__ __forceinline__ void tp_reduce_rows(const TpReduceArgs& a, float* red) {
   for (int row = blockIdx.x; row < a.rows_x; row += gridDim.x) {
     const long long base = (long long)row * a.D;
     const bool has_delta = row < a.delta_rows;
@@ -89,15 +76,45 @@ __global__ void __launch_bounds__(kTpThreads) tp_allreduce_add_rmsnorm_kernel(Tp
   }
 }
 
+__global__ void __launch_bounds__(kTpThreads) tp_allreduce_add_rmsnorm_kernel(TpReduceArgs a, int* status) {
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  // The exchange number lives on the device so that a captured CUDA graph stays valid from replay to replay: every
+  // CTA reads it before it can finish, and only the last CTA to finish advances it.
+  const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(a.epoch) + 1u;
+  // the partial block was written by the previous kernel of this stream: publish it, then wait for every peer's
+  if (blockIdx.x == 0 && threadIdx.x < a.world) {
+    __threadfence_system();
+    st_release_sys(a.announce[threadIdx.x], target);
+  }
+  if (threadIdx.x < a.world) {
+    if (!flag_wait_ge(a.local_flags + threadIdx.x, target, status, kTimeoutPeerFlag, true)) s_ok = 0;
+  }
+  __syncthreads();
+  if (s_ok) tp_reduce_rows(a, red);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(a.done, 1u) == gridDim.x - 1) {   // a timed-out launch still advances: the ranks stay in step
+      *a.done = 0u;
+      __threadfence();
+      *const_cast<uint32_t*>(a.epoch) = target;
+    }
+  }
+}
+
 }  // namespace ksa
 
 using namespace ksa;
 
 // partial_ptrs[r]: rank r's partial block; announce_ptrs[r]: &flags[rank] on rank r; local_flags: own flags[0..world).
-// target: the exchange number (monotonically increasing per call sequence, identical on every rank).
+// epoch: device uint32, the number of all-reduces finished so far (identical on every rank; advanced by the kernel);
+// done: device uint32 scratch counter, zero between launches.
 KSA_API int ksa_tp_allreduce_add_rmsnorm(const void* x, const void* const* partial_ptrs, const void* const* announce_ptrs,
                                          const void* local_flags, int world, int rank, const void* w, void* res_out,
-                                         void* y, int rows_x, int delta_rows, int D, float eps, unsigned target,
+                                         void* y, int rows_x, int delta_rows, int D, float eps, void* epoch, void* done,
                                          void* stream) {
   KSA_ENTER(x);
   KSA_REQUIRE(world >= 1 && world <= kMaxPeers, "tp all-reduce: world %d out of range", world);
@@ -114,7 +131,9 @@ KSA_API int ksa_tp_allreduce_add_rmsnorm(const void* x, const void* const* parti
   a.local_flags = static_cast<const uint32_t*>(local_flags);
   a.world = world; a.rank = rank;
   a.x = (const bf16*)x; a.w = (const bf16*)w; a.res_out = (bf16*)res_out; a.y = (bf16*)y;
-  a.rows_x = rows_x; a.delta_rows = delta_rows; a.D = D; a.eps = eps; a.target = target;
+  a.rows_x = rows_x; a.delta_rows = delta_rows; a.D = D; a.eps = eps;
+  a.epoch = static_cast<const uint32_t*>(epoch); a.done = static_cast<uint32_t*>(done);
+  KSA_REQUIRE(a.epoch != nullptr && a.done != nullptr, "tp all-reduce: epoch and done counters are required");
   // every CTA must be resident while it waits for the peers: at most 4 CTAs of 256 threads per SM are launched
   int sms = 148;
   int dev = 0;

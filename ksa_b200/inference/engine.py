@@ -32,9 +32,11 @@ def _decode_attention(q, k_cache, v_cache, start, length, scale):
         return torch.cat(outs, dim=1)
     B, Tq, Hq, D = q.shape
     Hkv, cap = k_cache.shape[1], k_cache.shape[2]
-    keys_per_split = 512
+    # short slices (the ring + summaries of a summary layer) are latency-bound: cut them into many small splits so
+    # that every SM holds several CTAs; long caches get at most 64 splits
+    keys_per_split = 128
     splits = max(1, min(64, (cap + keys_per_split - 1) // keys_per_split))
-    keys_per_split = (cap + splits - 1) // splits
+    keys_per_split = ((cap + splits - 1) // splits + 63) // 64 * 64
     part_o = torch.empty((B, Tq, Hq, splits, D), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((B, Tq, Hq, splits, 2), dtype=torch.float32, device=q.device)
     out = torch.empty_like(q)
@@ -76,8 +78,15 @@ def _cache_move(k_cache, v_cache, src, dst, enable, rows):
 
 
 class KsaInferenceEngine:
-    def __init__(self, model, max_len: int, batch: int, device=None, dtype=None):
+    def __init__(self, model, max_len: int, batch: int, device=None, dtype=None, cuda_graph: bool = True):
         self.model = model.eval()
+        # steps that do not cross a chunk boundary replay one captured CUDA graph (all indices come from device
+        # counters, so the launch sequence is the same every step); boundary steps (1 in ``chunk``) run eagerly
+        self.cuda_graph = cuda_graph
+        self._graph = None
+        self._graph_tokens = None
+        self._graph_logits = None
+        self._plain_steps = 0
         self.model.drop_partial_summary = True
         cfg = model.config
         self.cfg = cfg
@@ -155,13 +164,46 @@ class KsaInferenceEngine:
     @torch.no_grad()
     def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
         """``tokens`` ``[B]``: the next text token of every sequence -> logits ``[B, V]``."""
+        C, S = self.C, self.S
+        boundary_host = [S > 0 and (l % C) == C - 1 for l in self.host_len]
+        tp = getattr(self.model, "tp", None)
+        graphable = self.cuda_graph and tokens.is_cuda and not any(boundary_host)
+        # with tensor parallelism the graph ends at the final norm: the vocabulary-parallel head and the gather of
+        # its logits (a library collective) run after the replay
+        head_in_graph = tp is None
+        if not graphable:
+            logits = self._decode_impl(tokens, boundary_host)
+        elif self._graph is None and self._plain_steps == 0:
+            self._plain_steps += 1          # first-call set-up of the kernels happens outside a capture
+            logits = self._decode_impl(tokens, boundary_host)
+        else:
+            if self._graph is None:
+                self._graph_tokens = tokens.reshape(self.batch).clone()
+                torch.cuda.synchronize(self.device)
+                self._graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self._graph):
+                    self._graph_logits = self._decode_impl(self._graph_tokens, boundary_host, head_in_graph)
+            self._graph_tokens.copy_(tokens.reshape(self.batch))
+            self._graph.replay()
+            logits = self._graph_logits.clone() if head_in_graph else self._head(self._graph_logits)
+        self.host_len = [l + 1 for l in self.host_len]
+        return logits
+
+    def _head(self, hidden: torch.Tensor) -> torch.Tensor:
+        model, tp = self.model, getattr(self.model, "tp", None)
+        logits = ops.linear(hidden, model.lm_head_weight)
+        if tp is not None and logits.shape[-1] != self.cfg.vocab_size:
+            logits = tp.gather_logits(logits)
+        return logits.float()
+
+    def _decode_impl(self, tokens: torch.Tensor, boundary_host, with_head: bool = True) -> torch.Tensor:
+        """Device work of one decode step (launches only; the host mirror of the lengths is advanced by the caller)."""
         model, cfg = self.model, self.cfg
         tp = getattr(model, "tp", None)      # tensor-parallel shard: cfg holds the local head counts
         B, C, S = self.batch, self.C, self.S
         Hq, Hkv, Dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         scale = Dh ** -0.5
         st = self.state
-        boundary_host = [S > 0 and (l % C) == C - 1 for l in self.host_len]
         any_boundary = any(boundary_host)
         dev = self.device
         pos_t = st.text_len.clone()                              # position of the new text token
@@ -185,6 +227,7 @@ class KsaInferenceEngine:
             pos_all = pos_all.clone()
             pos_all[:B] = st.cbl
         delta = None
+        slices_of = {}      # layers with the same cache geometry share the step's slot / slice tensors
         for li, layer in enumerate(model.layers):
             a = layer.attn
             cache = self.layer_caches[li]
@@ -200,11 +243,16 @@ class KsaInferenceEngine:
                     qkv = ops.linear(h, a.wqkv.weight)
                 qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), pos_all, Hq, Hkv, Dh,
                                               cfg.rope_base, cfg.norm_eps, cfg.rope_impl == "llama")
-                slot_t, start_t, len_t = text_step_slices(spec, st)
+                skey = (spec.chunk, spec.n_sum, spec.window, spec.max_chunks)
+                if skey not in slices_of:
+                    slot_t, start_t, len_t = text_step_slices(spec, st)
+                    slices_of[skey] = (slot_t.view(B, 1), start_t.view(B, 1).to(torch.int32).contiguous(),
+                                       len_t.view(B, 1).to(torch.int32).contiguous(), start_t, len_t)
+                slot_t1, start_t1, len_t1, start_t, len_t = slices_of[skey]
                 q_t = qkv[:B, :Hq * Dh].view(B, 1, Hq, Dh)
                 k_t = qkv[:B, Hq * Dh:(Hq + Hkv) * Dh].view(B, 1, Hkv, Dh)
                 v_t = qkv[:B, (Hq + Hkv) * Dh:].view(B, 1, Hkv, Dh)
-                _cache_append(k_t, v_t, cache.k, cache.v, slot_t.view(B, 1))
+                _cache_append(k_t, v_t, cache.k, cache.v, slot_t1)
                 if any_boundary:
                     slot_s, start_s, len_s = summary_step_slices(spec, B, dev)
                     off = torch.where(boundary[:, None] > 0, slot_s, torch.full_like(slot_s, -1))
@@ -223,8 +271,7 @@ class KsaInferenceEngine:
                         _cache_move(cache.k, cache.v, src_t, dst_t, boundary, C)
                     _cache_move(cache.k, cache.v, src_s, dst_s, boundary, S)
                 else:
-                    att = _decode_attention(q_t, cache.k, cache.v, start_t.view(B, 1).to(torch.int32),
-                                            len_t.view(B, 1).to(torch.int32), scale).reshape(B, Hq * Dh)
+                    att = _decode_attention(q_t, cache.k, cache.v, start_t1, len_t1, scale).reshape(B, Hq * Dh)
                 attn_out = _row_linear(tp, att, a.output_proj.weight)
                 x, h2 = _add_norm(tp, x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
                 delta = layer.mlp(h2, tp)
@@ -243,19 +290,15 @@ class KsaInferenceEngine:
                 x, h2 = _add_norm(tp, x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
                 delta = layer.mlp(h2[:B], tp)
         _, hN = _add_norm(tp, x[:B], delta[:B], model.norm.scale, cfg.norm_eps)
-        logits = ops.linear(hN, model.lm_head_weight)
-        if tp is not None and logits.shape[-1] != cfg.vocab_size:
-            logits = tp.gather_logits(logits)
         # advance the counters
         st.text_len += 1
         if S > 0:
             if any_boundary:
                 st.chunks += boundary
-                st.cbl = torch.where(boundary > 0, torch.zeros_like(st.cbl), st.cbl + 1)
+                st.cbl.copy_(torch.where(boundary > 0, torch.zeros_like(st.cbl), st.cbl + 1))
             else:
                 st.cbl += 1
-        self.host_len = [l + 1 for l in self.host_len]
-        return logits.float()
+        return self._head(hN) if with_head else hN
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, max_new_tokens: int, eos_id: Optional[int] = None) -> torch.Tensor:

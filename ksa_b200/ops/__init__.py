@@ -59,6 +59,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     assert out.shape == (M, N) and out.stride(1) == 1
+    if (M <= 16 and not a_mn_major and not b_mn_major and out.dtype == torch.bfloat16 and not accumulate
+            and alpha == 1.0 and K % 8 == 0 and not _lib.comm_pending()):
+        # decoding: a few activation rows against a whole weight matrix is a stream of the weights, served by the
+        # bandwidth-shaped kernel instead of 128-row tensor-core tiles
+        _lib.call("ksa_gemv_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0))
+        return out
     _lib.call("ksa_gemm_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
               int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate),
               float(alpha), int(sm_limit))

@@ -23,6 +23,7 @@ P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 # name -> argument ctypes (the trailing stream pointer included)
 _SIGNATURES: Dict[str, Sequence] = {
     "ksa_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, I, P],
+    "ksa_gemv_bf16": [P, P, P, I, I, I, L, L, L, P],
     "ksa_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, I, P],
     "ksa_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
     "ksa_qknorm_rope_fwd": [P, P, P, P, P, P, L, L, I, I, I, I, F, F, I, I, P],
@@ -51,7 +52,7 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_peer_copy": [P, P, L, P, P, ctypes.c_uint, I, P],
     "ksa_peer_add_bf16": [P, P, L, P, P, ctypes.c_uint, I, P],
     "ksa_peer_copy2d": [P, L, P, L, L, L, P, P, ctypes.c_uint, I, P],
-    "ksa_tp_allreduce_add_rmsnorm": [P, P, P, P, I, I, P, P, P, I, I, I, F, ctypes.c_uint, P],
+    "ksa_tp_allreduce_add_rmsnorm": [P, P, P, P, I, I, P, P, P, I, I, I, F, P, P, P],
     "ksa_symm_alloc": [P, L],
     "ksa_symm_free": [P],
     "ksa_ipc_get_handle": [P, P],
@@ -148,6 +149,11 @@ def attach_to_next_gemm(name: str, args: tuple, after=None) -> None:
     call_nostream(name, *args)
     _tls.after_gemm = after
     _tls.attached = True
+
+
+def comm_pending() -> bool:
+    """True while a communication job is attached and waiting for the next tensor-core GEMM launch."""
+    return bool(getattr(_tls, "attached", False))
 
 
 def gemm_launched() -> None:

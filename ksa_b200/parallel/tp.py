@@ -47,6 +47,9 @@ class TpContext:
             dist.barrier(group)
             self._slot_ptrs = [self.buf.offset_ptr_array(s * self.slot_bytes) for s in range(2)]
             self._announce = self.flags.flag_ptrs(self.rank)
+            # [finished all-reduces, finished CTAs of the running one]: on the device, so that a captured CUDA graph
+            # of a decode step stays valid while the exchange number advances
+            self._epoch = torch.zeros(2, dtype=torch.int32, device=device)
 
     def close(self) -> None:
         if self.fused:
@@ -86,7 +89,8 @@ class TpContext:
         s = self.counter % 2
         self.counter += 1
         _lib.call("ksa_tp_allreduce_add_rmsnorm", x, self._slot_ptrs[s], self._announce, self.flags.local_ptr(0),
-                  self.size, self.rank, weight, res, y, rows_x, rows_d, self.D, float(eps), self.counter)
+                  self.size, self.rank, weight, res, y, rows_x, rows_d, self.D, float(eps), self._epoch[0:1],
+                  self._epoch[1:2])
         return res, y
 
     # ------------------------------------------------------------------ vocabulary-parallel head

@@ -79,6 +79,16 @@ def bench_gemm(a) -> None:
         report("  cuBLAS (torch.matmul)", ms2, flops=2.0 * M * N * K)
 
 
+def bench_gemv(a) -> None:
+    """Decode-shaped projection: ``--m`` activation rows (<= 16) against an ``[n, k]`` weight; bytes = the weight."""
+    M, N, K = a.m, a.n, a.k
+    A = torch.randn(M, K, device="cuda").bfloat16()
+    B = torch.randn(N, K, device="cuda").bfloat16()
+    C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: ops.gemm(A, B, out=C), a.iters, a.warmup, not a.no_flush)
+    report(f"skinny gemm {M}x{N}x{K}", ms, bytes_=2.0 * N * K)
+
+
 def bench_attn(a) -> None:
     B, Hq, Hkv, D, C, S, W, L = a.batch, a.hq, a.hkv, a.dim, a.chunk, a.nsum, a.window, a.seq
     Ns = 0 if a.causal else (L // C) * S
@@ -172,7 +182,7 @@ def bench_cp_attn(a) -> None:
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "attn", "decode", "norm", "cp-attn"])
+    ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn"])
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--a-mn", action="store_true"); ap.add_argument("--b-mn", action="store_true")
@@ -187,7 +197,7 @@ def main(argv=None) -> None:
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"])
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn}[a.what](a)
+    {"gemm": bench_gemm, "gemv": bench_gemv, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn}[a.what](a)
     _lib.check_status()
 
 

@@ -53,6 +53,19 @@ def test_gemm_fp32_accumulate_and_strided_views():
     check(out, expect, 5e-3, "gemm fp32 accumulate")
 
 
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 16])
+@pytest.mark.parametrize("N,K", [(2560, 4096), (19456, 2560), (264, 9728), (151936, 2560)])
+def test_skinny_gemm_for_decoding(M, N, K):
+    packed = bf(M, K + 64)
+    A = packed[:, 32:32 + K]                # strided view with a 64-byte column offset
+    B = bf(N, K, scale=0.05)
+    out = torch.empty(M, N + 8, device=DEV, dtype=torch.bfloat16)[:, :N]
+    before = _lib.launch_count()
+    c = ops.gemm(A, B, out=out)
+    assert _lib.launch_count() == before + 1
+    check(c, A.float() @ B.float().t(), 1e-2, f"skinny gemm {M}x{N}x{K}")
+
+
 def test_linear_autograd():
     x = bf(3, 200, 256).requires_grad_()
     w = bf(384, 256, scale=0.05).requires_grad_()
