@@ -22,13 +22,15 @@ struct TpReduceArgs {
   float eps;
   const uint32_t* epoch;           // device counter of finished all-reduces; this call's flag value is *epoch + 1
   uint32_t* done;                  // CTAs of this launch that have finished (the last one advances *epoch)
+  int row_lo, row_hi;              // rows reduced by this rank (all of them, or its shard in the two-phase form)
+  uint32_t* notify[kMaxPeers];     // two-phase form: flag2[rank] on every rank, raised when the shard is written
 };
 
 constexpr int kTpThreads = 256;
 constexpr int kTpMaxVec = 4;  // D <= 8192
 
 __device__ __forceinline__ void tp_reduce_rows(const TpReduceArgs& a, float* red) {
-  for (int row = blockIdx.x; row < a.rows_x; row += gridDim.x) {
+  for (int row = a.row_lo + blockIdx.x; row < a.row_hi; row += gridDim.x) {
     const long long base = (long long)row * a.D;
     const bool has_delta = row < a.delta_rows;
     float v[kTpMaxVec][8];
@@ -101,6 +103,10 @@ __global__ void __launch_bounds__(kTpThreads) tp_allreduce_add_rmsnorm_kernel(Tp
       *a.done = 0u;
       __threadfence();
       *const_cast<uint32_t*>(a.epoch) = target;
+      // every CTA's rows were fenced before its increment of `done`: the shard is complete, tell the peers
+      __threadfence_system();
+      for (int r = 0; r < a.world; ++r)
+        if (a.notify[r] != nullptr) st_release_sys(a.notify[r], target);
     }
   }
 }
@@ -108,6 +114,41 @@ __global__ void __launch_bounds__(kTpThreads) tp_allreduce_add_rmsnorm_kernel(Tp
 }  // namespace ksa
 
 using namespace ksa;
+
+static int tp_launch(const void* x, const void* const* partial_ptrs, const void* const* announce_ptrs,
+                     const void* local_flags, int world, int rank, const void* w, void* res_out, void* y, int rows_x,
+                     int delta_rows, int D, float eps, void* epoch, void* done, int row_lo, int row_hi,
+                     const void* const* notify_ptrs, void* stream) {
+  KSA_REQUIRE(world >= 1 && world <= kMaxPeers, "tp all-reduce: world %d out of range", world);
+  KSA_REQUIRE(D % 8 == 0 && D <= kTpThreads * 8 * kTpMaxVec, "tp all-reduce: D=%d unsupported", D);
+  KSA_REQUIRE(delta_rows <= rows_x, "tp all-reduce: delta rows exceed residual rows");
+  KSA_REQUIRE(row_lo >= 0 && row_hi <= rows_x, "tp all-reduce: row range out of bounds");
+  if (rows_x == 0) return 0;
+  int* status = status_word();
+  KSA_REQUIRE(status != nullptr, "could not allocate the status word");
+  TpReduceArgs a{};
+  for (int r = 0; r < world; ++r) {
+    a.partial[r] = static_cast<const bf16*>(partial_ptrs[r]);
+    a.announce[r] = static_cast<uint32_t*>(const_cast<void*>(announce_ptrs[r]));
+    a.notify[r] = notify_ptrs ? static_cast<uint32_t*>(const_cast<void*>(notify_ptrs[r])) : nullptr;
+  }
+  a.local_flags = static_cast<const uint32_t*>(local_flags);
+  a.world = world; a.rank = rank;
+  a.x = (const bf16*)x; a.w = (const bf16*)w; a.res_out = (bf16*)res_out; a.y = (bf16*)y;
+  a.rows_x = rows_x; a.delta_rows = delta_rows; a.D = D; a.eps = eps;
+  a.epoch = static_cast<const uint32_t*>(epoch); a.done = static_cast<uint32_t*>(done);
+  a.row_lo = row_lo; a.row_hi = row_hi;
+  KSA_REQUIRE(a.epoch != nullptr && a.done != nullptr, "tp all-reduce: epoch and done counters are required");
+  // every CTA must be resident while it waits for the peers: at most 4 CTAs of 256 threads per SM are launched
+  int sms = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int rows = row_hi - row_lo;
+  int grid = rows < sms * 4 ? (rows > 0 ? rows : 1) : sms * 4;
+  tp_allreduce_add_rmsnorm_kernel<<<grid, kTpThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a, status);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
 
 // partial_ptrs[r]: rank r's partial block; announce_ptrs[r]: &flags[rank] on rank r; local_flags: own flags[0..world).
 // epoch: device uint32, the number of all-reduces finished so far (identical on every rank; advanced by the kernel);
@@ -117,29 +158,21 @@ KSA_API int ksa_tp_allreduce_add_rmsnorm(const void* x, const void* const* parti
                                          void* y, int rows_x, int delta_rows, int D, float eps, void* epoch, void* done,
                                          void* stream) {
   KSA_ENTER(x);
-  KSA_REQUIRE(world >= 1 && world <= kMaxPeers, "tp all-reduce: world %d out of range", world);
-  KSA_REQUIRE(D % 8 == 0 && D <= kTpThreads * 8 * kTpMaxVec, "tp all-reduce: D=%d unsupported", D);
-  KSA_REQUIRE(delta_rows <= rows_x, "tp all-reduce: delta rows exceed residual rows");
-  if (rows_x == 0) return 0;
-  int* status = status_word();
-  KSA_REQUIRE(status != nullptr, "could not allocate the status word");
-  TpReduceArgs a{};
-  for (int r = 0; r < world; ++r) {
-    a.partial[r] = static_cast<const bf16*>(partial_ptrs[r]);
-    a.announce[r] = static_cast<uint32_t*>(const_cast<void*>(announce_ptrs[r]));
-  }
-  a.local_flags = static_cast<const uint32_t*>(local_flags);
-  a.world = world; a.rank = rank;
-  a.x = (const bf16*)x; a.w = (const bf16*)w; a.res_out = (bf16*)res_out; a.y = (bf16*)y;
-  a.rows_x = rows_x; a.delta_rows = delta_rows; a.D = D; a.eps = eps;
-  a.epoch = static_cast<const uint32_t*>(epoch); a.done = static_cast<uint32_t*>(done);
-  KSA_REQUIRE(a.epoch != nullptr && a.done != nullptr, "tp all-reduce: epoch and done counters are required");
-  // every CTA must be resident while it waits for the peers: at most 4 CTAs of 256 threads per SM are launched
-  int sms = 148;
-  int dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  int grid = rows_x < sms * 4 ? rows_x : sms * 4;
-  tp_allreduce_add_rmsnorm_kernel<<<grid, kTpThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a, status);
-  KSA_CHECK_CUDA(cudaGetLastError());
-  return 0;
+  return tp_launch(x, partial_ptrs, announce_ptrs, local_flags, world, rank, w, res_out, y, rows_x, delta_rows, D, eps,
+                   epoch, done, 0, rows_x, nullptr, stream);
+}
+
+// Two-phase form for many rows (prefill): this rank reduces only rows [row_lo, row_hi) - reduce-scatter + residual add
+// + RMSNorm - into res_out / y, which are the same symmetric buffers on every rank, then raises notify_ptrs[r] (its
+// flag in every rank's second flag array).  The peers' shards are fetched afterwards with ksa_peer_gather waiting on
+// those flags.  Each rank reads rows*D partial elements instead of world*rows*D.
+KSA_API int ksa_tp_reduce_scatter_add_rmsnorm(const void* x, const void* const* partial_ptrs,
+                                              const void* const* announce_ptrs, const void* local_flags, int world,
+                                              int rank, const void* w, void* res_out, void* y, int rows_x, int delta_rows,
+                                              int D, float eps, void* epoch, void* done, int row_lo, int row_hi,
+                                              const void* const* notify_ptrs, void* stream) {
+  KSA_ENTER(x);
+  KSA_REQUIRE(notify_ptrs != nullptr, "tp reduce-scatter: notify flags are required");
+  return tp_launch(x, partial_ptrs, announce_ptrs, local_flags, world, rank, w, res_out, y, rows_x, delta_rows, D, eps,
+                   epoch, done, row_lo, row_hi, notify_ptrs, stream);
 }

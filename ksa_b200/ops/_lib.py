@@ -53,6 +53,7 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_peer_add_bf16": [P, P, L, P, P, ctypes.c_uint, I, P],
     "ksa_peer_copy2d": [P, L, P, L, L, L, P, P, ctypes.c_uint, I, P],
     "ksa_tp_allreduce_add_rmsnorm": [P, P, P, P, I, I, P, P, P, I, I, I, F, P, P, P],
+    "ksa_tp_reduce_scatter_add_rmsnorm": [P, P, P, P, I, I, P, P, P, I, I, I, F, P, P, I, I, P, P],
     "ksa_symm_alloc": [P, L],
     "ksa_symm_free": [P],
     "ksa_ipc_get_handle": [P, P],

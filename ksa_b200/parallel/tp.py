@@ -26,7 +26,8 @@ from ..ops import _lib
 class TpContext:
     """Group + (on GPUs) the symmetric partial-sum slots of one tensor-parallel group."""
 
-    def __init__(self, group, embed_dim: int, max_rows: int, device=None, dtype=torch.bfloat16):
+    def __init__(self, group, embed_dim: int, max_rows: int, device=None, dtype=torch.bfloat16,
+                 two_phase_rows: int = 2048, two_phase_min_size: int = 3):
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
@@ -50,6 +51,20 @@ class TpContext:
             # [finished all-reduces, finished CTAs of the running one]: on the device, so that a captured CUDA graph
             # of a decode step stays valid while the exchange number advances
             self._epoch = torch.zeros(2, dtype=torch.int32, device=device)
+            # Two-phase all-reduce for many rows (prefill) on groups of 3 or more: reduce-scatter + add + norm of this
+            # rank's row shard into symmetric residual / normalised buffers, then a P2P gather of the peers' shards.
+            # Each rank then reads 3 x rows x D elements instead of T x rows x D.
+            self.two_phase_rows = (two_phase_rows if self.size >= two_phase_min_size and two_phase_rows > 0
+                                   and max_rows >= two_phase_rows else 0)
+            if self.two_phase_rows:
+                self.rows_pad = (max_rows + self.size - 1) // self.size * self.size
+                plane = (self.rows_pad * embed_dim * item + 255) // 256 * 256
+                self._plane_bytes = plane
+                self.sp_buf = SymmetricBuffer(2 * plane, group, device)          # [residual | normalised]
+                self.flags2 = SignalPad(self.size, group, device)
+                self._notify = self.flags2.flag_ptrs(self.rank)
+                self._res_ptrs = self.sp_buf.offset_ptr_array(0)
+                self._y_ptrs = self.sp_buf.offset_ptr_array(plane)
 
     def close(self) -> None:
         if self.fused:
@@ -57,6 +72,9 @@ class TpContext:
             dist.barrier(self.group)
             self.flags.close()
             self.buf.close()
+            if self.two_phase_rows:
+                self.flags2.close()
+                self.sp_buf.close()
 
     # ------------------------------------------------------------------ row-parallel linear + fused all-reduce
     def _slot_view(self, rows: int) -> torch.Tensor:
@@ -84,14 +102,33 @@ class TpContext:
         if partial.data_ptr() != slot.data_ptr():
             slot.copy_(partial)
         x = x if x.is_contiguous() else x.contiguous()
-        res = torch.empty_like(x)
-        y = torch.empty_like(x)
         s = self.counter % 2
         self.counter += 1
+        if self.two_phase_rows and rows_x >= self.two_phase_rows:
+            return self._two_phase(x, s, weight, rows_x, rows_d, eps)
+        res = torch.empty_like(x)
+        y = torch.empty_like(x)
         _lib.call("ksa_tp_allreduce_add_rmsnorm", x, self._slot_ptrs[s], self._announce, self.flags.local_ptr(0),
                   self.size, self.rank, weight, res, y, rows_x, rows_d, self.D, float(eps), self._epoch[0:1],
                   self._epoch[1:2])
         return res, y
+
+    def _two_phase(self, x, s, weight, rows_x, rows_d, eps):
+        """Reduce-scatter + add + norm of this rank's rows, then gather of the peers' rows.  The results live in the
+        symmetric buffers until the next call of this kind (the callers consume them before that)."""
+        T, D = self.size, self.D
+        shard = (rows_x + T - 1) // T
+        lo, hi = min(self.rank * shard, rows_x), min((self.rank + 1) * shard, rows_x)
+        res = self.sp_buf.view(self.dtype, 0, self.rows_pad * D).view(self.rows_pad, D)
+        y = self.sp_buf.view(self.dtype, self._plane_bytes, self.rows_pad * D).view(self.rows_pad, D)
+        _lib.call("ksa_tp_reduce_scatter_add_rmsnorm", x, self._slot_ptrs[s], self._announce, self.flags.local_ptr(0),
+                  T, self.rank, weight, res, y, rows_x, rows_d, D, float(eps), self._epoch[0:1], self._epoch[1:2],
+                  lo, hi, self._notify)
+        # the epoch was advanced by the kernel above (stream order): a peer's shard is complete once its flag reached it
+        for ptrs in (self._res_ptrs, self._y_ptrs):
+            _lib.call("ksa_peer_gather", ptrs, T, self.rank, shard * D, x.element_size(), self.flags2.local_ptr(0),
+                      self._epoch[0:1], 0, 32)
+        return res[:rows_x], y[:rows_x]
 
     # ------------------------------------------------------------------ vocabulary-parallel head
     def gather_logits(self, local: torch.Tensor) -> torch.Tensor:

@@ -94,3 +94,30 @@ def test_halo_sources_cover_window_across_owners():
     assert cp.text_sources(32) == [(2, 96, 32)]
     assert cp.text_sources(320) == [(0, 64, 64), (1, 0, 128), (2, 0, 128)]
     assert CpShape(0, 4, 512, 16, 1).halo_len(8) == 0
+
+
+def test_recipe_runs_with_context_parallel_ranks(tmp_path):
+    """The pre-training recipe on two gloo ranks with --context-parallel-size 2: each rank trains on its half of every
+    sequence and the run finishes with matching step counts."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = _cfg(16, 2, 1)
+    mc = tmp_path / "model.json"
+    cfg.save(str(mc))
+    port = _free_port()
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
+        procs.append(subprocess.Popen(
+            [sys.executable, os.path.join(root, "recipes", "pretrain_ksa.py"), "--model-config", str(mc), "--output-dir",
+             str(tmp_path / "out"), "--max-length", "128", "--seed", "1", "--model-dtype", "float32", "--learning-rate",
+             "1e-3", "--lr-scheduler-type", "constant", "--num-training-steps", "3", "--context-parallel-size", "2",
+             "--comm", "collective", "--logging-per-step", "1", "--heartbeat-timeout", "30"],
+            env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs[0][-2000:]
+    done = json.loads([l for l in outs[0].splitlines() if l.startswith('{"done"')][-1])
+    assert done["steps"] == 3 and done["loss"] is not None and done["loss"] < 7.0

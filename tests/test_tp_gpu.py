@@ -31,20 +31,28 @@ def _worker(rank, world, port, out_q):
         dev = torch.device("cuda", rank)
         # --- the fused kernel alone: partial sums of known values, more residual rows than delta rows
         D, rows_x, rows_d = 512, 300, 260
-        tp = TpContext(dist.group.WORLD, D, max_rows=4096, device=dev)
         g = torch.Generator().manual_seed(3)
         x = torch.randn(rows_x, D, generator=g).to(dev).bfloat16()
         parts = [torch.randn(rows_d, D, generator=g).to(dev).bfloat16() for _ in range(world)]
         w = (1 + 0.1 * torch.randn(D, generator=g)).to(dev).bfloat16()
-        for it in range(3):   # three calls: both slots and a slot reuse
-            res, y = tp.add_rms_norm(x, parts[rank], w, 1e-6)
-            total = sum(p.float() for p in parts)
-            pad = torch.cat([total, total.new_zeros(rows_x - rows_d, D)])
-            res_ref, y_ref = ref.add_rms_norm(x.float(), pad, w.float(), 1e-6)
+        total = sum(p.float() for p in parts)
+        pad = torch.cat([total, total.new_zeros(rows_x - rows_d, D)])
+        res_ref, y_ref = ref.add_rms_norm(x.float(), pad, w.float(), 1e-6)
+        # one-shot form, then the two-phase form (reduce-scatter of a row shard + gather), forced on for 2 ranks
+        for kw in ({}, {"two_phase_rows": 256, "two_phase_min_size": 2}):
+            tp = TpContext(dist.group.WORLD, D, max_rows=4096, device=dev, **kw)
+            assert bool(tp.two_phase_rows) == bool(kw)
+            for it in range(3):   # three calls: both slots and a slot reuse
+                res, y = tp.add_rms_norm(x, parts[rank], w, 1e-6)
+                torch.cuda.synchronize(); _lib.check_status()
+                torch.testing.assert_close(res.float(), res_ref, atol=3e-2, rtol=2e-2)
+                torch.testing.assert_close(y.float(), y_ref, atol=3e-2, rtol=2e-2)
+            # chained use: the residual output of one call is the input of the next (in place for the two-phase form)
+            res2, _ = tp.add_rms_norm(res, parts[rank], w, 1e-6)
             torch.cuda.synchronize(); _lib.check_status()
-            torch.testing.assert_close(res.float(), res_ref, atol=3e-2, rtol=2e-2)
-            torch.testing.assert_close(y.float(), y_ref, atol=3e-2, rtol=2e-2)
-        tp.close()
+            res2_ref, _ = ref.add_rms_norm(res_ref.bfloat16().float(), pad, w.float(), 1e-6)
+            torch.testing.assert_close(res2.float(), res2_ref, atol=6e-2, rtol=3e-2)
+            tp.close()
         # --- engine: TP=2 shard against the whole model on the same GPU
         cfg = get_preset("qwen3-ksa-tiny").merge({"head_dim": 128, "num_heads": 4, "num_kv_heads": 2, "embed_dim": 512,
                                                   "summary_chunk_size": 128, "summary_sliding_chunk_num": 2,
