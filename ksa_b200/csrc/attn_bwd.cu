@@ -245,14 +245,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       int lo, hi;
       allowed_columns(sh, t_glob, is_sum, kt, lo, hi);
       // dS (bf16, two per column) overwrites the scores this warpgroup has already read:
-      // chunk c goes to columns (c/2)*64 + (c%2)*16.
+      // chunk c goes to columns (c/2)*64 + (c%2)*16.  All four loads are issued before the single wait, so the
+      // TMEM latency is paid once per step.
+      uint32_t sr[2][32], dr[2][32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        tmem_ld32(tS + lane_addr + (half * 2 + cc) * 32, sr[cc]);
+        tmem_ld32(tdP + lane_addr + (half * 2 + cc) * 32, dr[cc]);
+      }
+      tmem_wait_ld();
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
-        uint32_t sr[32], dr[32];
-        tmem_ld32(tS + lane_addr + c * 32, sr);
-        tmem_ld32(tdP + lane_addr + c * 32, dr);
-        tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -261,8 +265,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           for (int e = 0; e < 2; ++e) {
             const int col = c * 32 + 2 * i + e;
             const float pr = (col >= lo && col <= hi)
-                                 ? fast_exp2(fmaf(__uint_as_float(sr[2 * i + e]), p.scale_log2, -lse2)) : 0.f;
-            ds[e] = pr * (__uint_as_float(dr[2 * i + e]) - delta) * p.scale;
+                                 ? fast_exp2(fmaf(__uint_as_float(sr[cc][2 * i + e]), p.scale_log2, -lse2)) : 0.f;
+            ds[e] = pr * (__uint_as_float(dr[cc][2 * i + e]) - delta) * p.scale;
           }
           pk[i] = pack_bf16x2(ds[0], ds[1]);
         }
@@ -475,14 +479,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const long long tq0 = (long long)sh.q_off + qt * 128;
       const int lo = (int)max(t_lo - tq0, 0LL), hi = (int)min(t_hi - tq0, 127LL);
       // P^T and dS^T (bf16, two per column) overwrite scores this warpgroup has already read:
-      // chunk c goes to columns (c/2)*64 + (c%2)*16.
+      // chunk c goes to columns (c/2)*64 + (c%2)*16.  All four loads are issued before the single wait.
+      uint32_t sr[2][32], dr[2][32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        tmem_ld32(tS + lane_addr + (half * 2 + cc) * 32, sr[cc]);
+        tmem_ld32(tdP + lane_addr + (half * 2 + cc) * 32, dr[cc]);
+      }
+      tmem_wait_ld();
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
-        uint32_t sr[32], dr[32];
-        tmem_ld32(tS + lane_addr + c * 32, sr);
-        tmem_ld32(tdP + lane_addr + c * 32, dr);
-        tmem_wait_ld();
         uint32_t pk[16], dk[16];
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
@@ -491,8 +498,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int e = 0; e < 2; ++e) {
             const int col = c * 32 + 2 * k + e;
             pr[e] = (col >= lo && col <= hi)
-                        ? fast_exp2(fmaf(__uint_as_float(sr[2 * k + e]), p.scale_log2, -lse_s[col - half * 64])) : 0.f;
-            ds[e] = pr[e] * (__uint_as_float(dr[2 * k + e]) - delta_s[col - half * 64]) * p.scale;
+                        ? fast_exp2(fmaf(__uint_as_float(sr[cc][2 * k + e]), p.scale_log2, -lse_s[col - half * 64])) : 0.f;
+            ds[e] = pr[e] * (__uint_as_float(dr[cc][2 * k + e]) - delta_s[col - half * 64]) * p.scale;
           }
           pk[k] = pack_bf16x2(pr[0], pr[1]);
           dk[k] = pack_bf16x2(ds[0], ds[1]);
