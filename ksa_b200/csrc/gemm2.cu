@@ -1,0 +1,339 @@
+// bf16 GEMM with CTA pairs (tcgen05 cta_group::2): two CTAs of a cluster, on the two SMs of one TPC, share a
+// 256 x 256 output tile.  Each CTA stages its own 128 rows of A and its own 128 of the 256 rows of B, the leader CTA
+// issues one MMA for the pair, and each CTA's tensor memory receives its 128 x 256 half of the accumulator.  Per SM and
+// k-step that is 8 KB of shared-memory operands for a 128 x 256 x 16 product instead of 12 KB with single-CTA MMAs,
+// which is what keeps the tensor pipe fed (a 128 x 256 single-CTA MMA needs more operand bytes per clock than shared
+// memory delivers).
+//
+// Roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only), warps 2..5 epilogue.
+// Barriers: `full` lives in the leader and collects the bytes of both CTAs' loads (the peer's TMA loads name the
+// leader's barrier); `empty` and `acc_full` exist in both CTAs and are signalled for both by one multicast
+// tcgen05.commit; `acc_empty` lives in the leader and collects one arrival per epilogue warp of both CTAs.
+// No TMA load here uses cluster multicast.  Every wait is bounded.
+#include "common.cuh"
+#include "host.h"
+
+namespace ksa {
+
+constexpr int k2BM = 128;          // rows of A (and of the accumulator) per CTA
+constexpr int k2BN = 256;          // accumulator columns per pair
+constexpr int k2BNh = 128;         // rows of B staged per CTA
+constexpr int k2BK = 64;
+constexpr int k2Threads = 192;
+constexpr int k2Stages = 6;
+constexpr int k2GroupM = 8;        // pair-tile rows per scheduling group
+constexpr int k2ABytes = k2BM * k2BK * 2;
+constexpr int k2BBytes = k2BNh * k2BK * 2;
+constexpr int k2StageBytes = k2ABytes + k2BBytes;
+constexpr int k2SmemTotal = k2Stages * k2StageBytes + 256 + 1024;
+
+struct Gemm2Epilogue {
+  void* c;
+  long long ldc;
+  int out_fp32, accumulate;
+  float alpha;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local_smem_addr` in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// TMA tile load whose completion bytes are counted by a barrier that may sit in the peer CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m, int x, int y, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(m), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair once all MMAs issued so far are done.
+__device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(mask)
+      : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(k2Threads, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Gemm2Epilogue ep,
+                  int M, int N, int K, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_base = smem + k2Stages * k2StageBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);   // used in the leader
+  uint64_t* empty = full + k2Stages;                         // both CTAs
+  uint64_t* acc_full = empty + k2Stages;                     // both CTAs, 2 buffers
+  uint64_t* acc_empty = acc_full + 2;                        // used in the leader, 2 buffers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();     // 0 = leader
+  const WaitGuard guard{abort_flag, status};
+  const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
+  const int tiles_m = (M + 2 * k2BM - 1) / (2 * k2BM);
+  const int tiles_n = (N + k2BN - 1) / k2BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + k2BK - 1) / k2BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < k2Stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 8); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 2) { tmem_alloc2(tmem_slot, 512); tmem_relinquish2(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // both CTAs' barriers are initialised before any remote arrival
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](int tile, int& mb, int& nb) {
+    const int per_group = k2GroupM * tiles_n;
+    const int group = tile / per_group;
+    const int first_m = group * k2GroupM;
+    const int group_rows = min(tiles_m - first_m, k2GroupM);
+    const int in_group = tile - group * per_group;
+    mb = first_m + in_group % group_rows;
+    nb = in_group / group_rows;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        int mb, nb;
+        tile_coords(tile, mb, nb);
+        const int row0 = mb * 2 * k2BM + (int)rank * k2BM;      // this CTA's rows of A
+        const int col0 = nb * k2BN + (int)rank * k2BNh;         // this CTA's rows of B
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, guard, kTimeoutStageEmpty)) { ok = false; break; }
+          uint8_t* sa = smem + stage * k2StageBytes;
+          uint8_t* sb = sa + k2ABytes;
+          const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * k2StageBytes);
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &tmA, kb * k2BK, row0, bar);
+          } else {
+#pragma unroll
+            for (int a = 0; a < k2BM / 64; ++a) tma_load_2d_pair(sa + a * 8192, &tmA, row0 + a * 64, kb * k2BK, bar);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &tmB, kb * k2BK, col0, bar);
+          } else {
+#pragma unroll
+            for (int a = 0; a < k2BNh / 64; ++a) tma_load_2d_pair(sb + a * 8192, &tmB, col0 + a * 64, kb * k2BK, bar);
+          }
+          if (++stage == k2Stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * k2BM, k2BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++local) {
+        const int buf = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, guard, kTimeoutAccEmpty)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * k2BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, guard, kTimeoutTmaFull)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * k2StageBytes);
+          const uint32_t sb = sa + k2ABytes;
+#pragma unroll
+          for (int k = 0; k < k2BK / 16; ++k) {
+            const uint64_t da = A_MN ? smem_desc_mnmajor_sw128(sa + k * 2048, 8192) : smem_desc_kmajor_sw128(sa + k * 32);
+            const uint64_t db = B_MN ? smem_desc_mnmajor_sw128(sb + k * 2048, 8192) : smem_desc_kmajor_sw128(sb + k * 32);
+            umma2_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma2_commit_both(&empty[stage]);
+          if (++stage == k2Stages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma2_commit_both(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    int local = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++local) {
+      int mb, nb;
+      tile_coords(tile, mb, nb);
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[buf], acc_phase, guard, kTimeoutAccFull)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mb * 2 * k2BM + (int)rank * k2BM + quad * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * k2BN;
+#pragma unroll 1
+      for (int c = 0; c < k2BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        tmem_wait_ld();
+        const int col0 = nb * k2BN + c * 32;
+        if (row < M && col0 < N) {
+          if (ep.out_fp32) {
+            float* dst = reinterpret_cast<float*>(ep.c) + (long long)row * ep.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col0 + j < N) {
+                float4 v = make_float4(__uint_as_float(r[j]) * ep.alpha, __uint_as_float(r[j + 1]) * ep.alpha,
+                                       __uint_as_float(r[j + 2]) * ep.alpha, __uint_as_float(r[j + 3]) * ep.alpha);
+                float4* p = reinterpret_cast<float4*>(dst + j);
+                if (ep.accumulate) {
+                  const float4 o = *p;
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *p = v;
+              }
+            }
+          } else {
+            bf16* dst = reinterpret_cast<bf16*>(ep.c) + (long long)row * ep.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < N) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[j]) * ep.alpha, __uint_as_float(r[j + 1]) * ep.alpha);
+                v.y = pack_bf16x2(__uint_as_float(r[j + 2]) * ep.alpha, __uint_as_float(r[j + 3]) * ep.alpha);
+                v.z = pack_bf16x2(__uint_as_float(r[j + 4]) * ep.alpha, __uint_as_float(r[j + 5]) * ep.alpha);
+                v.w = pack_bf16x2(__uint_as_float(r[j + 6]) * ep.alpha, __uint_as_float(r[j + 7]) * ep.alpha);
+                *reinterpret_cast<uint4*>(dst + j) = v;
+              }
+            }
+          }
+        }
+      }
+      // one arrival per epilogue warp of either CTA on the leader's barrier: this accumulator buffer may be rewritten
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+    }
+  }
+
+  // The peer's tensor memory and barriers are written by the leader's MMAs and commits: nobody leaves, and nothing
+  // is deallocated, before both CTAs are done.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, 512);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_gemm2(const void* a, const void* b, const Gemm2Epilogue& ep, int M, int N, int K, long long lda,
+                        long long ldb, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t str[2] = {2, (uint64_t)lda * 2};
+    uint32_t box[2] = {k2BK, k2BM};
+    rc = make_tmap(&tmA, a, 2, 2, dims, str, box, true);
+  } else {
+    uint64_t dims[2] = {(uint64_t)M, (uint64_t)K};
+    uint64_t str[2] = {2, (uint64_t)lda * 2};
+    uint32_t box[2] = {64, k2BK};
+    rc = make_tmap(&tmA, a, 2, 2, dims, str, box, true);
+  }
+  if (rc) return rc;
+  if (!B_MN) {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t str[2] = {2, (uint64_t)ldb * 2};
+    uint32_t box[2] = {k2BK, k2BNh};
+    rc = make_tmap(&tmB, b, 2, 2, dims, str, box, true);
+  } else {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)K};
+    uint64_t str[2] = {2, (uint64_t)ldb * 2};
+    uint32_t box[2] = {64, k2BK};
+    rc = make_tmap(&tmB, b, 2, 2, dims, str, box, true);
+  }
+  if (rc) return rc;
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    KSA_CHECK_CUDA(cudaGetDevice(&dev));
+    KSA_CHECK_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    KSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, k2SmemTotal));
+    attr_set = true;
+  }
+  const int tiles = ((M + 2 * k2BM - 1) / (2 * k2BM)) * ((N + k2BN - 1) / k2BN);
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  int* status = status_word();
+  KSA_REQUIRE(status != nullptr, "could not allocate the status word");
+  kern<<<2 * pairs, k2Threads, k2SmemTotal, stream>>>(tmA, tmB, ep, M, N, K, status);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace ksa
+
+// Same contract as ksa_gemm_bf16 (without sm_limit and without attached communication work), on CTA pairs.
+KSA_API int ksa_gemm2_bf16(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
+                           long long ldc, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, float alpha,
+                           void* stream) {
+  KSA_ENTER(a);
+  using namespace ksa;
+  KSA_REQUIRE(M > 0 && N > 0 && K > 0, "gemm2: empty problem %d x %d x %d", M, N, K);
+  KSA_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "gemm2: lda/ldb must be multiples of 8 elements (got %lld, %lld)", lda, ldb);
+  KSA_REQUIRE(N % 8 == 0 && ldc % (out_fp32 ? 4 : 8) == 0, "gemm2: N and ldc must keep 16-byte row alignment");
+  KSA_REQUIRE((reinterpret_cast<uintptr_t>(c) & 15) == 0, "gemm2: C must be 16-byte aligned");
+  KSA_REQUIRE(!(accumulate && !out_fp32), "gemm2: accumulate needs an fp32 output");
+  Gemm2Epilogue ep{c, ldc, out_fp32, accumulate, alpha};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (!a_mn_major && !b_mn_major) return launch_gemm2<false, false>(a, b, ep, M, N, K, lda, ldb, st);
+  if (!a_mn_major && b_mn_major) return launch_gemm2<false, true>(a, b, ep, M, N, K, lda, ldb, st);
+  if (a_mn_major && !b_mn_major) return launch_gemm2<true, false>(a, b, ep, M, N, K, lda, ldb, st);
+  return launch_gemm2<true, true>(a, b, ep, M, N, K, lda, ldb, st);
+}

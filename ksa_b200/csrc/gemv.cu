@@ -103,6 +103,106 @@ static int launch_gemv(const void* a, const void* b, void* c, int M, int N, int 
   return 0;
 }
 
+// ------------------------------------------------------------------------------------------ tensor-core variant
+// For 5..16 activation rows the SIMT kernel above is bound by its FMA issue rate, so the dot products go to the tensor
+// cores with warp-level mma.sync m16n8k16 (the 128-row tcgen05 tile has no use for 16 rows): a CTA owns 16 weight
+// rows, its 8 warps take the 32-wide k blocks round-robin, and the partial sums meet in shared memory.  Both operands
+// are read as 16 contiguous bytes per lane along k; a lane's 8 elements are given to the instruction as its k slots
+// {2t, 2t+1, 2t+8, 2t+9} of two MMAs.  That permutes k inside a 32-block, identically for weights and activations,
+// which a dot product does not see.
+constexpr int kMmaKTile = 1024;               // activation columns staged per pass (32 blocks of 32)
+constexpr int kMmaRowStride = kMmaKTile + 32;  // +64 bytes: the two row groups of a quarter warp hit different banks
+
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NB>   // batch blocks of 8 rows: 1 (M <= 8) or 2 (M <= 16)
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, int M, int N, int K,
+                long long lda, long long ldb, long long ldc) {
+  extern __shared__ __align__(16) uint8_t gemv_smem[];
+  bf16* sX = reinterpret_cast<bf16*>(gemv_smem);                       // [NB*8][kMmaRowStride]
+  float* sRed = reinterpret_cast<float*>(gemv_smem);                   // reused after the k loop: [8 warps][16][NB*8]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);       // clamped: rows past N are never written
+  float acc[NB][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[b][i] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += kMmaKTile) {
+    const int kt = min(kMmaKTile, K - k0);   // multiple of 32
+    __syncthreads();
+    for (int i = threadIdx.x; i < NB * 8 * (kMmaKTile / 8); i += kGemvThreads) {
+      const int m = i / (kMmaKTile / 8), c = (i % (kMmaKTile / 8)) * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (m < M && c < kt) v = *reinterpret_cast<const uint4*>(A + (long long)m * lda + k0 + c);
+      *reinterpret_cast<uint4*>(sX + m * kMmaRowStride + c) = v;
+    }
+    __syncthreads();
+    // this warp's 32-wide blocks of the tile: warp, warp + 8, warp + 16, warp + 24; all weight loads first
+    uint4 w0[4], w1[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = (warp + 8 * u) * 32 + t * 8;
+      w0[u] = make_uint4(0, 0, 0, 0);
+      w1[u] = make_uint4(0, 0, 0, 0);
+      if (c < kt) {
+        w0[u] = ld_stream_16(B + (long long)r0 * ldb + k0 + c);
+        w1[u] = ld_stream_16(B + (long long)r1 * ldb + k0 + c);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = (warp + 8 * u) * 32 + t * 8;
+      if (c >= kt) break;
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const uint4 x = *reinterpret_cast<const uint4*>(sX + (b * 8 + g) * kMmaRowStride + c);
+        mma_bf16_16x8x16(acc[b], w0[u].x, w1[u].x, w0[u].y, w1[u].y, x.x, x.y);
+        mma_bf16_16x8x16(acc[b], w0[u].z, w1[u].z, w0[u].w, w1[u].w, x.z, x.w);
+      }
+    }
+  }
+  // acc[b] = {C[g][2t], C[g][2t+1], C[g+8][2t], C[g+8][2t+1]} with rows = weight rows, columns = batch b*8 + ...
+  __syncthreads();
+  constexpr int NBATCH = NB * 8;
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    float* dst = sRed + warp * 16 * NBATCH;
+    dst[g * NBATCH + b * 8 + 2 * t] = acc[b][0];
+    dst[g * NBATCH + b * 8 + 2 * t + 1] = acc[b][1];
+    dst[(g + 8) * NBATCH + b * 8 + 2 * t] = acc[b][2];
+    dst[(g + 8) * NBATCH + b * 8 + 2 * t + 1] = acc[b][3];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 16 * NBATCH; i += kGemvThreads) {
+    const int row = i % 16, m = i / 16;          // consecutive threads -> consecutive output columns
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGemvThreads / 32; ++w) v += sRed[w * 16 * NBATCH + row * NBATCH + m];
+    if (m < M && n0 + row < N) C[(long long)m * ldc + n0 + row] = __float2bfloat16(v);
+  }
+}
+
+template <int NB>
+static int launch_gemv_mma(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
+                           long long ldc, cudaStream_t st) {
+  const size_t smem = (size_t)NB * 8 * kMmaRowStride * sizeof(bf16);    // >= the 8 KB / 16 KB of the final reduction
+  gemv_mma_kernel<NB><<<(N + 15) / 16, kGemvThreads, smem, st>>>((const bf16*)a, (const bf16*)b, (bf16*)c, M, N, K, lda,
+                                                                 ldb, ldc);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 }  // namespace ksa
 
 // C[M, N] (bf16, ldc) = A[M, K] (bf16, lda) * B[N, K]^T (bf16, ldb) for 1 <= M <= 16; K, lda, ldb multiples of 8.
@@ -113,6 +213,10 @@ KSA_API int ksa_gemv_bf16(const void* a, const void* b, void* c, int M, int N, i
   KSA_REQUIRE(M >= 1 && M <= 16, "gemv: M=%d out of range (1..16)", M);
   KSA_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0, "gemv: K, lda, ldb must be multiples of 8");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (M > 4 && K % 32 == 0) {
+    return M <= 8 ? launch_gemv_mma<1>(a, b, c, M, N, K, lda, ldb, ldc, st)
+                  : launch_gemv_mma<2>(a, b, c, M, N, K, lda, ldb, ldc, st);
+  }
   // rows per warp: fewer for narrow outputs so that the grid still covers every SM a few times
   const bool narrow = N <= 8192;
   if (M == 1) return narrow ? launch_gemv<1, 1>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<1, 4>(a, b, c, M, N, K, lda, ldb, ldc, st);

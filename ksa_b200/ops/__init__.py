@@ -29,6 +29,8 @@ from . import _lib
 from .layout import SummaryLayout, get_layout
 
 UNBOUNDED_WINDOW = 1 << 30
+# GEMMs with at least this many 256 x 256 tiles run on CTA pairs (tcgen05 cta_group::2); 0 disables the pair kernel
+GEMM_PAIR_MIN_TILES = int(__import__("os").environ.get("KSA_GEMM_PAIR_MIN_TILES", "0"))
 
 
 def _cuda(x: torch.Tensor) -> bool:
@@ -44,7 +46,8 @@ def _require_bf16(*ts):
 # =============================================================================== GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
-         accumulate: bool = False, alpha: float = 1.0, sm_limit: int = 0) -> torch.Tensor:
+         accumulate: bool = False, alpha: float = 1.0, sm_limit: int = 0,
+         pair: Optional[bool] = None) -> torch.Tensor:
     """``C[M,N] = alpha * op(A) op(B) (+ C)`` on the tcgen05 GEMM.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn_major``); ``b`` is ``[N,K]`` (or
@@ -64,6 +67,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
         # decoding: a few activation rows against a whole weight matrix is a stream of the weights, served by the
         # bandwidth-shaped kernel instead of 128-row tensor-core tiles
         _lib.call("ksa_gemv_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0))
+        return out
+    if pair is None:
+        pair = (GEMM_PAIR_MIN_TILES > 0 and sm_limit == 0 and not _lib.comm_pending()
+                and ((M + 255) // 256) * ((N + 255) // 256) >= GEMM_PAIR_MIN_TILES)
+    if pair:
+        _lib.call("ksa_gemm2_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
+                  int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate), float(alpha))
         return out
     _lib.call("ksa_gemm_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
               int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate),

@@ -6,6 +6,8 @@
     python -m ksa_b200.tools.kernel_bench norm --rows 8256 --dim 2048
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m ksa_b200.tools.kernel_bench \
         cp-attn --seq 32768 --bwd          # context-parallel attention: one shard per rank, max over ranks
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m ksa_b200.tools.kernel_bench comm
+    python -m ksa_b200.tools.kernel_bench comm --world 2      # the same kernels over buffers of one GPU
 
 Each line reports the median time, the achieved TFLOP/s or GB/s and, when ``MEASURED_PEAKS.json`` sits at the
 repository root, the fraction of the measured peak (cuBLAS bf16 burst / STREAM-style copy).  ``--iters 1 --warmup 1
@@ -70,8 +72,10 @@ def bench_gemm(a) -> None:
     A = torch.randn((K, M) if a.a_mn else (M, K), device="cuda").bfloat16()
     B = torch.randn((K, N) if a.b_mn else (N, K), device="cuda").bfloat16()
     C = torch.empty(M, N, device="cuda", dtype=torch.float32 if a.fp32_out else torch.bfloat16)
-    ms = timeit(lambda: ops.gemm(A, B, a_mn_major=a.a_mn, b_mn_major=a.b_mn, out=C), a.iters, a.warmup, not a.no_flush)
-    report(f"gemm {M}x{N}x{K} a_mn={int(a.a_mn)} b_mn={int(a.b_mn)}", ms, flops=2.0 * M * N * K)
+    ms = timeit(lambda: ops.gemm(A, B, a_mn_major=a.a_mn, b_mn_major=a.b_mn, out=C, pair=a.pair), a.iters, a.warmup,
+                not a.no_flush)
+    report(f"gemm {M}x{N}x{K} a_mn={int(a.a_mn)} b_mn={int(a.b_mn)}" + (" (CTA pairs)" if a.pair else ""), ms,
+           flops=2.0 * M * N * K)
     if a.compare:
         Am, Bm = (A.t() if a.a_mn else A), (B if a.b_mn else B.t())
         Cb = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
@@ -180,13 +184,87 @@ def bench_cp_attn(a) -> None:
     dist.destroy_process_group()
 
 
+def bench_comm(a) -> None:
+    """The fused communication kernels alone.
+
+    Under ``torch.distributed.run`` every rank is a GPU and the kernels read the peers' buffers over NVLink (times are
+    the maximum over ranks, fractions are of the measured 770 GB/s peer-copy bandwidth per direction).  Started as one
+    process, the ``--world`` "ranks" are buffers of the same GPU served by one launch (the form a profiler can
+    capture); the bytes then come from local HBM.
+    """
+    import ctypes
+    import torch.distributed as dist
+    multi = "RANK" in os.environ and int(os.environ.get("WORLD_SIZE", "1")) > 1
+    link_gbs = 770.0
+    if multi:
+        from ..parallel.symm import SymmetricBuffer
+        rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        rank, world = 0, a.world
+    dev = torch.device("cuda", torch.cuda.current_device())
+    n = (a.mbytes << 20) // 4 // world * world            # fp32 elements of a "unit" (gradient buffer)
+    shard = n // world
+
+    def buffers(nbytes):
+        if multi:
+            sb = SymmetricBuffer(nbytes)
+            return sb, sb.ptr_array, sb.view(torch.uint8)
+        ts = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(world)]
+        return ts, (ctypes.c_void_p * world)(*[t.data_ptr() for t in ts]), ts[0]
+
+    def timed(fn):
+        if multi:
+            dist.barrier()
+        t = torch.tensor([timeit(fn, a.iters, a.warmup, not a.no_flush)], device=dev, dtype=torch.float64)
+        if multi:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def show(name, ms, remote_bytes, local_bytes):
+        if rank != 0:
+            return
+        if multi:
+            gb = remote_bytes / ms / 1e6
+            print(f"{name}: {ms:.4f} ms | {gb:.0f} GB/s over NVLink per GPU ({gb / link_gbs:.2f} of measured {link_gbs:.0f} peer copy)",
+                  flush=True)
+        else:
+            report(name + f" ({world} local buffers)", ms, bytes_=remote_bytes + local_bytes)
+
+    # parameter all-gather: every rank pulls the other ranks' bf16 shards
+    hold_w, w_ptrs, _ = buffers(n * 2)
+    ms = timed(lambda: _lib.call("ksa_peer_gather", w_ptrs, world, rank, shard, 2, None, None, 0, a.ctas))
+    show(f"peer gather {n * 2 >> 20} MiB bf16 unit, world {world}", ms, (world - 1) * shard * 2, (world - 1) * shard * 2)
+    # gradient reduce-scatter + AdamW: the owner reads its slice of every rank's fp32 gradients
+    hold_g, g_ptrs, g0 = buffers(n * 4)
+    g0.view(torch.float32).normal_(0, 1e-3)
+    master = torch.zeros(shard, device=dev)
+    m1, m2 = torch.zeros_like(master), torch.zeros_like(master)
+    out = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    hyper = torch.tensor([1e-4, 0.1, 0.05, 1.0 / world], device=dev)
+    sumsq = torch.zeros(1, device=dev)
+    if multi:
+        dist.barrier()
+    ms = timed(lambda: _lib.call("ksa_peer_reduce_adamw", g_ptrs, world, rank, rank * shard, shard, master, m1, m2, out,
+                                 hyper, 0.9, 0.95, 1e-8, 0.1, 1.0, sumsq, None, None, 0, a.ctas))
+    show(f"peer reduce-scatter + AdamW {n * 4 >> 20} MiB fp32 unit, world {world}", ms, (world - 1) * shard * 4,
+         shard * 4 + shard * 4 * 6 + shard * 2)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    if multi:
+        hold_w.close(); hold_g.close()
+        dist.destroy_process_group()
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn"])
+    ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn", "comm"])
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--a-mn", action="store_true"); ap.add_argument("--b-mn", action="store_true")
     ap.add_argument("--fp32-out", action="store_true"); ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--pair", action="store_true", help="gemm: run on CTA pairs (tcgen05 cta_group::2)")
     ap.add_argument("--seq", type=int, default=8192); ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--hq", type=int, default=16); ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--dim", type=int, default=128); ap.add_argument("--chunk", type=int, default=128)
@@ -195,9 +273,12 @@ def main(argv=None) -> None:
     ap.add_argument("--cap", type=int, default=131072); ap.add_argument("--rows", type=int, default=8256)
     ap.add_argument("--iters", type=int, default=10); ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--world", type=int, default=2, help="comm: emulated ranks when started as one process")
+    ap.add_argument("--mbytes", type=int, default=256, help="comm: size of the fp32 gradient unit in MiB")
+    ap.add_argument("--ctas", type=int, default=64, help="comm: CTAs of the communication kernels")
     ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"])
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "gemv": bench_gemv, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn}[a.what](a)
+    {"gemm": bench_gemm, "gemv": bench_gemv, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn, "comm": bench_comm}[a.what](a)
     _lib.check_status()
 
 

@@ -42,6 +42,23 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     check(c, A.float() @ B.float().t(), 1e-2, f"gemm {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}")
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 256), (1000, 264, 72), (2048, 4096, 2048), (8256, 2048, 520)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_cta_pairs(M, N, K, a_mn, b_mn):
+    if a_mn and M % 8:
+        pytest.skip("an MN-major operand needs its contiguous extent to be a multiple of 8")
+    A = bf(M, K)
+    B = bf(N, K)
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    c = ops.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, pair=True)
+    check(c, A.float() @ B.float().t(), 1e-2, f"pair gemm {M}x{N}x{K} a_mn={a_mn} b_mn={b_mn}")
+    out = torch.randn(M, N, device=DEV)
+    expect = out + 0.5 * (A.float() @ B.float().t())
+    ops.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=out, accumulate=True, alpha=0.5, pair=True)
+    check(out, expect, 5e-3, "pair gemm fp32 accumulate")
+
+
 def test_gemm_fp32_accumulate_and_strided_views():
     M, N, K = 512, 768, 320
     packed = bf(M, 2 * K)
