@@ -181,7 +181,8 @@ class KsaDecoderLayer(nn.Module):
         qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), meta.pos[:n_text], Hq, Hkv, Dh,
                                       cfg.rope_base, cfg.norm_eps, meta.rope_interleaved)
         if meta.kv_sink is not None:
-            meta.kv_sink(self.layer_idx, qkv, False)
+            # a summary layer lands here when the prompt has no complete chunk yet: its cache keeps its own layout
+            meta.kv_sink(self.layer_idx, qkv, self.is_summary_layer)
         if meta.cp is not None:
             from ..parallel.cp import cp_attention_packed
             att = cp_attention_packed(qkv, meta.cp, Hq, Hkv, Dh, None, False, self.tok_window)

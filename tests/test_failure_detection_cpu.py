@@ -133,3 +133,21 @@ def test_resume_falls_back_over_a_damaged_checkpoint(tmp_path):
         def load_state_dict(self, s):
             raise AssertionError("must not be reached")
     assert ckpt.load_dataloader_state(_DS(), str(out / "global_step2")) is False
+
+
+def test_checkpoint_survives_a_change_of_world_size(tmp_path):
+    """Saved by two FSDP ranks, resumed by one process (and the step counter, optimizer state and LR schedule go on)."""
+    from recipes.pretrain_ksa import get_argument_parser, train
+    out = tmp_path / "run"
+    base = ["--model-config", _model_json(tmp_path), "--output-dir", str(out), "--max-length", "64", "--seed", "1",
+            "--model-dtype", "float32", "--learning-rate", "1e-3", "--lr-scheduler-type", "constant",
+            "--save-checkpoint-per-step", "2", "--comm", "collective"]
+    port = _free_port()
+    procs = [_launch(r, 2, port, base + ["--num-training-steps", "4", "--heartbeat-timeout", "30"], {}) for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs[0][-2000:]
+    assert (out / "latest").read_text() == "global_step4"
+    r = train(get_argument_parser().parse_args(base + ["--num-training-steps", "6", "--checkpoint-dir", str(out),
+                                                        "--resume-weights", "--resume-optimizer", "--logging-per-step", "1"]))
+    assert r["steps"] == 6 and r["loss"] is not None and r["loss"] < 6.5
+    assert (out / "latest").read_text() == "global_step6"

@@ -48,3 +48,36 @@ def test_generate_runs_and_cache_is_smaller_than_full_attention():
     assert out.shape == (1, 50)
     full = 2 * 256 * model.config.num_kv_heads * model.config.head_dim * 4 * model.config.num_layers
     assert eng.cache_bytes() < full
+
+
+def test_cache_state_machine_against_recompute_on_random_schedules():
+    """Random chunk sizes, windows, summary counts, prompt lengths and step counts (hypothesis): after every step the
+    cached decode equals a full recompute, across chunk boundaries, ring wrap-around and a second prefill that reuses
+    the engine."""
+    from hypothesis import given, settings, strategies as st
+
+    models = {}
+
+    @settings(max_examples=12, deadline=None)
+    @given(chunk=st.sampled_from([4, 8]), n_sum=st.sampled_from([1, 2]), window=st.integers(0, 3),
+           prompt_len=st.integers(1, 30), steps=st.integers(1, 20), second=st.integers(1, 12))
+    def run(chunk, n_sum, window, prompt_len, steps, second):
+        key = (chunk, n_sum, window)
+        if key not in models:
+            models[key] = _model(chunk, n_sum, window, layers=2, freq=[1, 0])
+        model = models[key]
+        eng = KsaInferenceEngine(model, max_len=64, batch=1)
+        model.drop_partial_summary = True
+        g = torch.Generator().manual_seed(prompt_len * 31 + steps)
+        for plen, n in ((prompt_len, steps), (second, 3)):       # the second round checks that prefill resets the state
+            seq = torch.randint(0, model.config.vocab_size, (1, plen), generator=g)
+            logits = eng.prefill(seq)
+            for _ in range(n):
+                with torch.no_grad():
+                    full = model(seq)[:, -1].float()
+                assert torch.allclose(logits, full, atol=3e-4, rtol=1e-3)
+                nxt = full.argmax(-1)
+                seq = torch.cat([seq, nxt[:, None]], dim=1)
+                logits = eng.decode_step(nxt)
+
+    run()
