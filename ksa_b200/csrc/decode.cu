@@ -162,6 +162,181 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeArgs a) 
   }
 }
 
+// ------------------------------------------------------------------------------------------ tensor-core variant
+// Same interface and the same split / combine scheme, but a key is read from global memory exactly once and never
+// staged in shared memory.  Scores: warp-level mma.sync m16n8k16 with the (up to 16) queries of the KV group as the
+// 16-row operand and 8 keys as the 8-column operand; a lane loads 16 contiguous bytes of a key (and of a query) and
+// hands them to two MMAs as k slots {2t, 2t+1, 2t+8, 2t+9}, a permutation of the head dimension that is the same on
+// both sides.  Probabilities go through a 1 KB per-warp shared buffer so that the P.V product runs with
+// "lane = 4 head dimensions" (V rows are read as 8 bytes per lane, coalesced) on the FMA units.
+__device__ __forceinline__ void mma_qk(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NQ>   // queries served per CTA, padded: 4, 8 or 16
+__global__ void __launch_bounds__(kDecThreads) decode_attn_mma_kernel(DecodeArgs a) {
+  constexpr int D = 128, KPI = 16;                 // keys per warp iteration
+  __shared__ __align__(16) float s_p[4][KPI][NQ];  // per warp: probabilities, [key][query]
+  __shared__ float s_m[4][NQ], s_l[4][NQ];
+  __shared__ __align__(16) float s_o[4][NQ][D];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int G = a.Hq / a.Hkv;
+  const int nq = G * a.Tq;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  // per-row (g and g+8) slice bounds, and the CTA's key range
+  int st0 = 0, en0 = 0, st1 = 0, en1 = 0, lo = a.cap, hi = 0;
+  for (int qi = 0; qi < nq; ++qi) {
+    const int s = a.start[b * a.Tq + qi / G], e = s + a.len[b * a.Tq + qi / G];
+    lo = min(lo, s); hi = max(hi, e);
+    if (qi == g) { st0 = s; en0 = e; }
+    if (qi == g + 8) { st1 = s; en1 = e; }
+  }
+  const int k0 = lo + split * a.keys_per_split;
+  const int k1 = min(hi, k0 + a.keys_per_split);
+  // query fragments: row g and row g+8, 4 blocks of 32 head dimensions
+  uint4 qa[4], qb[4];
+#pragma unroll
+  for (int blk = 0; blk < 4; ++blk) {
+    qa[blk] = make_uint4(0, 0, 0, 0);
+    qb[blk] = make_uint4(0, 0, 0, 0);
+    if (g < nq) {
+      const int tq = g / G, gg = g % G;
+      qa[blk] = *reinterpret_cast<const uint4*>(a.q + (((long long)b * a.Tq + tq) * a.Hq + kvh * G + gg) * D + blk * 32 + t * 8);
+    }
+    if (NQ > 8 && g + 8 < nq) {
+      const int tq = (g + 8) / G, gg = (g + 8) % G;
+      qb[blk] = *reinterpret_cast<const uint4*>(a.q + (((long long)b * a.Tq + tq) * a.Hq + kvh * G + gg) * D + blk * 32 + t * 8);
+    }
+  }
+  const bf16* kb = a.k_cache + ((long long)b * a.Hkv + kvh) * a.cap * D;
+  const bf16* vb = a.v_cache + ((long long)b * a.Hkv + kvh) * a.cap * D;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // running max / partial sums of rows g and g+8
+  float acc[NQ][4];
+#pragma unroll
+  for (int q = 0; q < NQ; ++q)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[q][i] = 0.f;
+  const float sc = a.scale * 1.4426950408889634f;              // scores in log2 units
+
+  for (int kbase = k0 + warp * KPI; kbase < k1; kbase += 4 * KPI) {
+    // ---- scores of 16 keys
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int key = min(kbase + j * 8 + g, a.cap - 1);
+      const bf16* krow = kb + (long long)key * D + t * 8;
+      uint4 kk[4];
+#pragma unroll
+      for (int blk = 0; blk < 4; ++blk) kk[blk] = *reinterpret_cast<const uint4*>(krow + blk * 32);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
+#pragma unroll
+      for (int blk = 0; blk < 4; ++blk) {
+        mma_qk(s[j], qa[blk].x, qb[blk].x, qa[blk].y, qb[blk].y, kk[blk].x, kk[blk].y);
+        mma_qk(s[j], qa[blk].z, qb[blk].z, qa[blk].w, qb[blk].w, kk[blk].z, kk[blk].w);
+      }
+    }
+    // ---- V rows of the same keys: lane owns head dimensions 4*lane .. 4*lane+3 (requested before the softmax math)
+    uint2 vv[KPI];
+#pragma unroll
+    for (int k = 0; k < KPI; ++k) {
+      const int key = min(kbase + k, a.cap - 1);
+      vv[k] = *reinterpret_cast<const uint2*>(vb + (long long)key * D + lane * 4);
+    }
+    // ---- mask, online softmax (rows g and g+8; this lane's columns are keys j*8 + 2t, 2t+1)
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = kbase + j * 8 + 2 * t + e;
+        const bool in = key < k1;
+        s[j][e] = (in && key >= st0 && key < en0) ? s[j][e] * sc : -INFINITY;
+        s[j][2 + e] = (in && key >= st1 && key < en1) ? s[j][2 + e] * sc : -INFINITY;
+        mx0 = fmaxf(mx0, s[j][e]);
+        mx1 = fmaxf(mx1, s[j][2 + e]);
+      }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    const float u0 = n0 == -INFINITY ? 0.f : n0, u1 = n1 == -INFINITY ? 0.f : n1;
+    const float c0 = m0 == -INFINITY ? 0.f : exp2f(m0 - u0), c1 = m1 == -INFINITY ? 0.f : exp2f(m1 - u1);
+    m0 = n0; m1 = n1;
+    l0 *= c0; l1 *= c1;
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float p0 = exp2f(s[j][e] - u0), p1 = exp2f(s[j][2 + e] - u1);
+        l0 += p0; l1 += p1;
+        if (g < NQ) s_p[warp][j * 8 + 2 * t + e][g] = p0;
+        if (NQ > 8) s_p[warp][j * 8 + 2 * t + e][g + 8] = p1;
+      }
+    // correction factors of all queries: row q lives in lanes 4*(q%8) .. +3
+    float corr[NQ];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) corr[q] = __shfl_sync(0xffffffffu, q < 8 ? c0 : c1, (q & 7) * 4);
+    __syncwarp();
+    // ---- O += P V on the FMA units
+#pragma unroll
+    for (int q = 0; q < NQ; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[q][i] *= corr[q];
+#pragma unroll
+    for (int k = 0; k < KPI; ++k) {
+      const float2 v01 = unpack_bf16x2(vv[k].x), v23 = unpack_bf16x2(vv[k].y);
+#pragma unroll
+      for (int q4 = 0; q4 < NQ / 4; ++q4) {
+        const float4 p = *reinterpret_cast<const float4*>(&s_p[warp][k][q4 * 4]);
+        const float pq[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[q4 * 4 + i][0] = fmaf(pq[i], v01.x, acc[q4 * 4 + i][0]);
+          acc[q4 * 4 + i][1] = fmaf(pq[i], v01.y, acc[q4 * 4 + i][1]);
+          acc[q4 * 4 + i][2] = fmaf(pq[i], v23.x, acc[q4 * 4 + i][2]);
+          acc[q4 * 4 + i][3] = fmaf(pq[i], v23.y, acc[q4 * 4 + i][3]);
+        }
+      }
+    }
+  }
+  // ---- merge the four warps, write this split's partial result
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (t == 0) {
+    if (g < NQ) { s_m[warp][g] = m0; s_l[warp][g] = l0; }
+    if (NQ > 8) { s_m[warp][g + 8] = m1; s_l[warp][g + 8] = l1; }
+  }
+#pragma unroll
+  for (int q = 0; q < NQ; ++q) *reinterpret_cast<float4*>(&s_o[warp][q][lane * 4]) = make_float4(acc[q][0], acc[q][1], acc[q][2], acc[q][3]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < nq * D; i += kDecThreads) {
+    const int q = i / D, d = i % D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, s_m[w][q]);
+    float o = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = s_m[w][q] == -INFINITY ? 0.f : exp2f(s_m[w][q] - m);
+      o += s_o[w][q][d] * f;
+      l += s_l[w][q] * f;
+    }
+    const int tq = q / G, gg = q % G;
+    const long long base = ((((long long)b * a.Tq + tq) * a.Hq + kvh * G + gg) * a.splits + split);
+    a.part_o[base * D + d] = o;
+    if (d == 0) {
+      a.part_ml[base * 2] = m == -INFINITY ? -INFINITY : m * 0.6931471805599453f;   // natural-log units for the combine
+      a.part_ml[base * 2 + 1] = l;
+    }
+  }
+}
+
 // one CTA per (b, t, head): merge the splits
 __global__ void __launch_bounds__(128) decode_combine_kernel(DecodeArgs a) {
   const long long row = blockIdx.x;  // (b * Tq + t) * Hq + h
@@ -238,7 +413,10 @@ KSA_API int ksa_decode_attn(const void* q, const void* k_cache, const void* v_ca
                (float*)part_o, (float*)part_ml, (bf16*)out, B, Tq, Hq, Hkv, D, cap, splits, keys_per_split, scale};
   dim3 grid(splits, Hkv, B);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (D == 128) decode_attn_kernel<128><<<grid, kDecThreads, 0, st>>>(a);
+  const int nq = (Hq / Hkv) * Tq;
+  if (D == 128 && nq <= 4) decode_attn_mma_kernel<4><<<grid, kDecThreads, 0, st>>>(a);
+  else if (D == 128 && nq <= 8) decode_attn_mma_kernel<8><<<grid, kDecThreads, 0, st>>>(a);
+  else if (D == 128) decode_attn_mma_kernel<16><<<grid, kDecThreads, 0, st>>>(a);
   else decode_attn_kernel<64><<<grid, kDecThreads, 0, st>>>(a);
   KSA_CHECK_CUDA(cudaGetLastError());
   decode_combine_kernel<<<B * Tq * Hq, 128, 0, st>>>(a);

@@ -257,9 +257,34 @@ def bench_comm(a) -> None:
         dist.destroy_process_group()
 
 
+def bench_tp_reduce(a) -> None:
+    """The fused all-reduce + residual add + RMSNorm of tensor-parallel inference as ONE launch over ``--world``
+    partial buffers of this GPU (the peers' flags are set beforehand, so nothing waits): the form a profiler can
+    capture.  Across GPUs the same kernel is timed by ``infer_bench`` under torchrun."""
+    import ctypes
+    world, rows, D = a.world, a.rows, a.dim
+    dev = torch.device("cuda", torch.cuda.current_device())
+    parts = [torch.randn(rows, D, device=dev).bfloat16() for _ in range(world)]
+    x = torch.randn(rows, D, device=dev).bfloat16()
+    w = torch.ones(D, device=dev).bfloat16()
+    res, y = torch.empty_like(x), torch.empty_like(x)
+    flags = torch.full((world,), 1 << 30, dtype=torch.int32, device=dev)     # already "announced" for every epoch
+    scratch = torch.zeros(world, dtype=torch.int32, device=dev)             # the kernel's own announcements land here
+    epoch = torch.zeros(2, dtype=torch.int32, device=dev)
+    part_ptrs = (ctypes.c_void_p * world)(*[p.data_ptr() for p in parts])
+    ann_ptrs = (ctypes.c_void_p * world)(*[scratch.data_ptr() + 4 * r for r in range(world)])
+    ms = timeit(lambda: _lib.call("ksa_tp_allreduce_add_rmsnorm", x, part_ptrs, ann_ptrs, flags, world, 0, w, res, y,
+                                  rows, rows, D, 1e-6, epoch[0:1], epoch[1:2]), a.iters, a.warmup, not a.no_flush)
+    report(f"all-reduce + add + rmsnorm {rows}x{D}, {world} partials (local buffers)", ms,
+           bytes_=(world + 3.0) * rows * D * 2)
+    ref = x.float() + sum(p.float() for p in parts)
+    err = (res.float() - ref).abs().max().item()
+    print(f"  max abs error of the residual stream vs fp32: {err:.3e}", flush=True)
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn", "comm"])
+    ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn", "comm", "tp-reduce"])
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--a-mn", action="store_true"); ap.add_argument("--b-mn", action="store_true")
@@ -278,7 +303,7 @@ def main(argv=None) -> None:
     ap.add_argument("--ctas", type=int, default=64, help="comm: CTAs of the communication kernels")
     ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"])
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "gemv": bench_gemv, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn, "comm": bench_comm}[a.what](a)
+    {"gemm": bench_gemm, "gemv": bench_gemv, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn, "comm": bench_comm, "tp-reduce": bench_tp_reduce}[a.what](a)
     _lib.check_status()
 
 

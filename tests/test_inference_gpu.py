@@ -13,7 +13,9 @@ from ksa_b200.ops import _lib, reference as ref
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("B,Tq,Hq,Hkv,D,cap", [(2, 1, 8, 2, 128, 1500), (1, 2, 4, 2, 64, 300), (3, 1, 16, 8, 128, 9000)])
+@pytest.mark.parametrize("B,Tq,Hq,Hkv,D,cap", [(2, 1, 8, 2, 128, 1500), (1, 2, 4, 2, 64, 300), (3, 1, 16, 8, 128, 9000),
+                                               (2, 2, 8, 2, 128, 777), (2, 3, 8, 2, 128, 2200), (1, 2, 32, 4, 128, 640),
+                                               (4, 1, 32, 8, 128, 131)])
 def test_decode_attention_kernel(B, Tq, Hq, Hkv, D, cap):
     g = torch.Generator(device="cuda").manual_seed(0)
     q = torch.randn(B, Tq, Hq, D, device="cuda", generator=g).to(torch.bfloat16)
