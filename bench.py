@@ -49,6 +49,7 @@ def parse_args():
                     help="context-parallel size: --seq-len is the whole sequence, split over groups of this many ranks")
     ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"],
                     help="full-attention layers under --cp: head-parallel resharding or staged earlier keys")
+    ap.add_argument("--graph-multi", action="store_true", help="replay the fused multi-GPU step from a CUDA graph too")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--comm", default=None, choices=["fused", "collective"],
                     help="multi-GPU back end: fused P2P kernels (default) or NCCL collectives (A/B baseline)")
@@ -170,7 +171,8 @@ def run_ours(args) -> dict:
     dev_in = [t.to(dev) for t in host_in]
     dev_lab = [t.to(dev) for t in host_lab]
 
-    use_graph = not args.no_graph and world == 1
+    # one CUDA graph per rank for the whole step; context parallelism numbers its exchanges on the host, so it stays eager
+    use_graph = not args.no_graph and (world == 1 or (args.graph_multi and cp == 1 and args.comm != "collective"))
     step_fn = engine.graphed_step if use_graph else engine.train_step
 
     def barrier():

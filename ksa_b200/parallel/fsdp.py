@@ -63,6 +63,7 @@ class FsdpEngine(TrainEngine):
         self.comm_ctas = comm_ctas
         self._symm = []
         super().__init__(model, *args, world_size=world_size, rank=rank, **kw)
+        self._graph_warm = set()
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._epoch_ring = torch.zeros(32, 1, dtype=torch.int32)
         if self.device.type == "cuda":
@@ -224,12 +225,17 @@ class FsdpEngine(TrainEngine):
         if self.comm != "fused":
             return super().forward_backward(tokens, labels, **kw)
         self._is_boundary_step = self.micro_step + 1 == self.grad_accum_steps
+        if self.micro_step == 0:
+            self.grad_sq.zero_()
         self._done_units = set()
         self._overlap_active = True
         try:
             if self.micro_step == 0:          # refreshed weights of the first two units; later ones are pulled ahead
                 main = torch.cuda.current_stream(self.device)
-                main.wait_stream(self.comm_stream)   # the previous step's updates of this rank's own shards
+                if not torch.cuda.is_current_stream_capturing():
+                    # the previous step's updates of this rank's own shards; inside a graph the previous replay has
+                    # joined the side stream already, and a stream outside the capture cannot be waited on
+                    main.wait_stream(self.comm_stream)
                 self.comm_stream.wait_stream(main)
                 self._gather_now(0)
                 if len(self.units) > 1:
@@ -306,9 +312,33 @@ class FsdpEngine(TrainEngine):
         return self._grad_sq_reduced.sqrt()
 
     def graphed_step(self, tokens, labels):
-        if self.comm == "fused":
-            raise NotImplementedError("graph capture of the fused multi-GPU step is not enabled yet; use train_step")
-        return super().graphed_step(tokens, labels)
+        """The fused step as one CUDA graph per rank.  Flag values come from the device-resident step counter, so a
+        replay waits for the peers' current step like the eager step does.  The first step of each shape runs eagerly
+        (it is the warm-up: a captured run executes nothing, and a discarded trial step would leave this step's flags
+        already raised on the peers)."""
+        if self.comm != "fused":
+            return super().graphed_step(tokens, labels)
+        from ..training.engine import _CapturedStep
+        first = self.micro_step == 0
+        boundary = self.micro_step + 1 == self.grad_accum_steps
+        key = (tuple(tokens.shape), first, boundary)
+        cap = self._graphs.get(key)
+        if cap is None:
+            if key not in self._graph_warm:
+                self._graph_warm.add(key)
+                return self.train_step(tokens, labels)
+            torch.cuda.synchronize(self.device)
+            cap = _CapturedStep(self, tokens.shape, first, boundary, warmup=False)
+            self._graphs[key] = cap
+        cap.tokens.copy_(tokens, non_blocking=True)
+        cap.labels.copy_(labels, non_blocking=True)
+        self._write_hyper()
+        cap.graph.replay()
+        self.micro_step += 1
+        if boundary:
+            self.step_count += 1
+            self.micro_step = 0
+        return cap.loss
 
     def refresh_compute_from_master(self) -> None:
         for u in self.units:

@@ -326,11 +326,20 @@ class TrainEngine:
 
 
 class _CapturedStep:
-    def __init__(self, engine: TrainEngine, shape, first: bool, boundary: bool):
+    def __init__(self, engine: TrainEngine, shape, first: bool, boundary: bool, warmup: bool = True):
         dev = engine.device
         self.tokens = torch.zeros(shape, dtype=torch.long, device=dev)
         self.labels = torch.zeros(shape, dtype=torch.long, device=dev)
-        # Warm up on a side stream (allocator pools, kernel attributes, status words), undoing its effects on state.
+        if warmup:
+            self._warm_up(engine, first, boundary)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = self._run(engine, first, boundary)
+
+    def _warm_up(self, engine: TrainEngine, first: bool, boundary: bool) -> None:
+        """One uncaptured run on a side stream (allocator pools, kernel attributes, status words), undoing its effects
+        on the training state.  Engines whose step talks to other ranks warm up with a real step instead."""
+        dev = engine.device
         snap = [(u.master.clone(), u.exp_avg.clone(), u.exp_avg_sq.clone(), u.compute.clone()) for u in engine.units]
         grads = None if first else [u.grad.clone() for u in engine.units]
         side = torch.cuda.Stream(device=dev)
@@ -345,9 +354,6 @@ class _CapturedStep:
             for u, g in zip(engine.units, grads):
                 u.grad.copy_(g)
         del snap, grads
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.loss = self._run(engine, first, boundary)
 
     def _run(self, engine: TrainEngine, first: bool, boundary: bool) -> torch.Tensor:
         for u in engine.units:

@@ -85,6 +85,7 @@ def get_argument_parser() -> argparse.ArgumentParser:
     a("--commit-id", default="")
     a("--seed", type=int, default=None)
     a("--enable-profile", action="store_true")
+    a("--nvtx", action="store_true", help="NVTX ranges around data loading, the step and checkpoint saves")
     a("--step-timeout", type=float, default=1800.0,
       help="seconds without a finished step before the watchdog dumps all stacks (0 disables it)")
     a("--heartbeat-timeout", type=float, default=300.0,
@@ -246,7 +247,9 @@ def train(args) -> dict:
         os.makedirs(os.path.join(args.output_dir, "torch_profile"), exist_ok=True)
         profiler.start()
 
+    from ksa_b200.utils.tracing import StepTimer, nvtx_range
     from ksa_b200.utils.watchdog import FaultInjector, HeartbeatMonitor, StepWatchdog, check_device
+    step_timer = StepTimer(device)
     watchdog = StepWatchdog(args.step_timeout).start() if args.step_timeout > 0 else None
     heartbeat = None
     if world > 1 and args.heartbeat_timeout > 0:
@@ -270,12 +273,13 @@ def train(args) -> dict:
             raise
         if heartbeat is not None:
             heartbeat.agree(sched.micro_step)
-        if args.overfit_batches and len(cached) >= args.overfit_batches:
-            batch = cached[sched.micro_step % args.overfit_batches]
-        else:
-            batch = next(data_iter)
-            if args.overfit_batches:
-                cached.append(batch)
+        with nvtx_range("data", args.nvtx):
+            if args.overfit_batches and len(cached) >= args.overfit_batches:
+                batch = cached[sched.micro_step % args.overfit_batches]
+            else:
+                batch = next(data_iter)
+                if args.overfit_batches:
+                    cached.append(batch)
         ids = batch["input_ids"]
         labels, _ = make_labels(ids, batch["loss_mask"])
         if "next_token" in batch:   # the corpus stores L+1 tokens: the last position has a real target
@@ -286,13 +290,16 @@ def train(args) -> dict:
             labels = labels[:, cp_rank * Ll:(cp_rank + 1) * Ll].contiguous()
         if hasattr(model, "set_mix_coeff"):
             model.set_mix_coeff(sched.global_step + step_offset)
-        if args.enable_distill:
-            loss = _distill_step(engine, model, ids.to(device), labels.to(device), args, attention_mse_loss,
-                                 attention_cosine_loss)
-        elif use_graph:
-            loss = engine.graphed_step(ids.pin_memory() if use_cuda else ids, labels.pin_memory() if use_cuda else labels)
-        else:
-            loss = engine.train_step(ids, labels)
+        with nvtx_range("step", args.nvtx):
+            if args.enable_distill:
+                loss = _distill_step(engine, model, ids.to(device), labels.to(device), args, attention_mse_loss,
+                                     attention_cosine_loss)
+            elif use_graph:
+                loss = engine.graphed_step(ids.pin_memory() if use_cuda else ids,
+                                           labels.pin_memory() if use_cuda else labels)
+            else:
+                loss = engine.train_step(ids, labels)
+        step_timer.tick()
         sched.step()
         if watchdog is not None:
             watchdog.beat()
@@ -340,7 +347,10 @@ def train(args) -> dict:
         engine.close()
     if world > 1:
         dist.barrier()
-    return {"steps": sched.global_step + step_offset, "loss": last_loss}
+    timing = step_timer.summary(skip=min(3, max(sched.micro_step - 1, 0)))
+    if rank == 0 and timing:
+        print("[recipe] device time per micro-step: " + ", ".join(f"{k}={v:.3f}" for k, v in timing.items()), flush=True)
+    return {"steps": sched.global_step + step_offset, "loss": last_loss, "step_ms": timing.get("median_ms")}
 
 
 def _distill_step(engine, model, ids, labels, args, mse_fn, cos_fn):

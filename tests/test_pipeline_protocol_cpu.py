@@ -1,0 +1,178 @@
+"""Host-side model of the mbarrier protocol of the GEMM kernels (single CTA and CTA pair).
+
+The kernels' roles (TMA producer, MMA issuer, epilogue) are written here as Python generators that perform the same
+waits, arrivals and phase flips as the device loops in ``ksa_b200/csrc/gemm.cu`` and ``gemm2.cu``; a scheduler
+interleaves them at random.  The model checks what the phase bits are supposed to guarantee: nobody overwrites a
+stage that has not been consumed, nothing is consumed before it was fully produced, accumulator buffers are not
+rewritten before the epilogue has drained them, and every role terminates (no deadlock) for any interleaving.
+"""
+import random
+
+import pytest
+
+
+class MBar:
+    """``mbarrier`` with an arrival count and a transaction-byte count; a phase completes when both reach zero."""
+
+    def __init__(self, count):
+        self.count, self.pending, self.tx, self.phase = count, count, 0, 0
+
+    def _maybe_flip(self):
+        if self.pending == 0 and self.tx == 0:
+            self.phase ^= 1
+            self.pending = self.count
+
+    def arrive(self, expect_tx=0):
+        assert self.pending > 0, "more arrivals than the barrier was initialised for"
+        self.tx += expect_tx
+        self.pending -= 1
+        self._maybe_flip()
+
+    def complete_tx(self, nbytes):
+        self.tx -= nbytes
+        self._maybe_flip()
+
+    def done(self, parity):          # try_wait.parity: has the phase with this parity completed?
+        return self.phase != parity
+
+
+def run(roles, rng, limit=200000):
+    live = list(roles)
+    for _ in range(limit):
+        if not live:
+            return
+        r = rng.choice(live)
+        try:
+            next(r)
+        except StopIteration:
+            live.remove(r)
+    raise AssertionError("roles did not finish: deadlock or livelock in the protocol")
+
+
+def wait(bar, parity):
+    while not bar.done(parity):
+        yield
+
+
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("stages,tiles,kblocks", [(4, 5, 3), (6, 3, 13), (2, 7, 1), (6, 1, 6)])
+def test_gemm_pipeline_protocol(pair, stages, tiles, kblocks):
+    n_cta = 2 if pair else 1
+    stage_bytes = 100
+    for seed in range(20):
+        rng = random.Random(seed)
+        full = [MBar(1) for _ in range(stages)]                        # lives in the leader
+        empty = [[MBar(1) for _ in range(stages)] for _ in range(n_cta)]
+        acc_full = [[MBar(1) for _ in range(2)] for _ in range(n_cta)]
+        acc_empty = [MBar(4 * n_cta) for _ in range(2)]                # leader: one arrival per epilogue warp
+        smem = [[None] * stages for _ in range(n_cta)]                 # what each stage currently holds
+        inflight = []                                                  # TMA copies issued but not yet landed
+        tmem = [[None, None] for _ in range(n_cta)]                    # accumulator buffers: list of consumed k-blocks
+        results = [[] for _ in range(n_cta)]
+
+        def producer(cta):
+            stage, phase = 0, 0
+            for tile in range(tiles):
+                for kb in range(kblocks):
+                    yield from wait(empty[cta][stage], phase ^ 1)
+                    assert smem[cta][stage] is None, "stage overwritten before the MMA consumed it"
+                    if cta == 0:
+                        full[stage].arrive(expect_tx=stage_bytes * n_cta)
+                    inflight.append((cta, stage, (tile, kb)))
+                    stage += 1
+                    if stage == stages:
+                        stage, phase = 0, phase ^ 1
+                    yield
+
+        def tma_engine():
+            while True:
+                if inflight:
+                    cta, stage, what = inflight.pop(rng.randrange(len(inflight)))
+                    smem[cta][stage] = what
+                    full[stage].complete_tx(stage_bytes)               # the peer's bytes land on the leader's barrier
+                elif all(p is None for p in prods):
+                    return
+                yield
+
+        def mma():
+            stage, phase = 0, 0
+            for local, tile in enumerate(range(tiles)):
+                buf, acc_phase = local & 1, (local >> 1) & 1
+                yield from wait(acc_empty[buf], acc_phase ^ 1)
+                for c in range(n_cta):
+                    assert tmem[c][buf] is None, "accumulator rewritten before the epilogue drained it"
+                    tmem[c][buf] = []
+                for kb in range(kblocks):
+                    yield from wait(full[stage], phase)
+                    for c in range(n_cta):
+                        assert smem[c][stage] == (tile, kb), "MMA read a stage that was not (fully) produced"
+                        tmem[c][buf].append((tile, kb))
+                        smem[c][stage] = None
+                    for c in range(n_cta):                              # one multicast commit frees the stage in both
+                        empty[c][stage].arrive()
+                    stage += 1
+                    if stage == stages:
+                        stage, phase = 0, phase ^ 1
+                    yield
+                for c in range(n_cta):
+                    acc_full[c][buf].arrive()
+
+        def epilogue(cta, warp):
+            for local, tile in enumerate(range(tiles)):
+                buf, acc_phase = local & 1, (local >> 1) & 1
+                yield from wait(acc_full[cta][buf], acc_phase)
+                assert tmem[cta][buf] == [(tile, kb) for kb in range(kblocks)]
+                if warp == 0:
+                    results[cta].append(tile)
+                yield
+                drained[cta][buf] += 1
+                if drained[cta][buf] == 4:                              # last warp of this CTA: buffer is free here
+                    drained[cta][buf] = 0
+                    tmem[cta][buf] = None
+                acc_empty[buf].arrive()
+
+        drained = [[0, 0] for _ in range(n_cta)]
+        prods = [producer(c) for c in range(n_cta)]
+
+        def tracked(i):
+            yield from prods[i]
+            prods[i] = None
+        roles = [tracked(c) for c in range(n_cta)] + [tma_engine(), mma()]
+        roles += [epilogue(c, w) for c in range(n_cta) for w in range(4)]
+        run(roles, rng)
+        assert all(r == list(range(tiles)) for r in results)
+
+
+def test_model_detects_a_missing_phase_flip():
+    """The model is not vacuous: a producer that forgets to flip its phase bit is caught."""
+    rng = random.Random(0)
+    empty, full = [MBar(1) for _ in range(2)], [MBar(1) for _ in range(2)]
+    smem = [None, None]
+
+    def producer():
+        stage = 0
+        for i in range(6):
+            yield from wait(empty[stage], 1)      # bug: always waits for parity 1
+            assert smem[stage] is None, "stage overwritten before it was consumed"
+            smem[stage] = i
+            full[stage].arrive()
+            stage ^= 1
+            yield
+
+    def consumer():
+        stage, phase = 0, 0
+        for i in range(6):
+            yield from wait(full[stage], phase)
+            smem[stage] = None
+            empty[stage].arrive()
+            stage ^= 1
+            if stage == 0:
+                phase ^= 1
+            yield
+
+    with pytest.raises(AssertionError):
+        for seed in range(50):
+            rng = random.Random(seed)
+            empty, full = [MBar(1) for _ in range(2)], [MBar(1) for _ in range(2)]
+            smem = [None, None]
+            run([producer(), consumer()], rng, limit=5000)
