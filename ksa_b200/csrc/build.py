@@ -27,6 +27,11 @@ NVCC_FLAGS = [
 ]
 
 
+def _flags() -> list:
+    """Release flags, plus the device-side bounds checks when ``KSA_DEBUG=1`` is set."""
+    return NVCC_FLAGS + (["-DKSA_DEBUG_CHECKS"] if os.environ.get("KSA_DEBUG") == "1" else [])
+
+
 def _nvcc() -> str:
     cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not Path(cand).exists():
@@ -48,7 +53,7 @@ def _compile(src: Path, force: bool, verbose: bool) -> Path:
     newest = max(src.stat().st_mtime, _headers_mtime())
     if not force and obj.exists() and obj.stat().st_mtime >= newest:
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *_flags(), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     r = subprocess.run(cmd, capture_output=True, text=True)
@@ -62,6 +67,12 @@ def _compile(src: Path, force: bool, verbose: bool) -> Path:
 def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ_DIR.mkdir(exist_ok=True)
     LIB_DIR.mkdir(exist_ok=True)
+    # objects built with other flags (release vs debug checks) are stale whatever their time stamps say
+    stamp = OBJ_DIR / "flags.txt"
+    flags_text = " ".join(_flags())
+    if not stamp.exists() or stamp.read_text() != flags_text:
+        force = True
+    stamp.write_text(flags_text)
     srcs = sources()
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(lambda s: _compile(s, force, verbose), srcs))

@@ -63,6 +63,7 @@ __device__ __forceinline__ bool run_gather_job(const GatherJob& j, int cta, int 
   const uint32_t target = epoch_target(j.epoch_ptr, j.epoch_add);
   for (int step = 1; step < j.world; ++step) {
     const int r = (j.rank + step) % j.world;  // start with the next rank so that ranks do not all hit one peer at once
+    if (!KSA_DEV_CHECK(r >= 0 && r < kMaxPeers && j.peers[r] != nullptr && (j.shard_bytes & 15) == 0, status)) return false;
     if (j.ready_flags) {
       if (threadIdx.x == 0) s_ok = flag_wait_ge(j.ready_flags + r, target, status, kTimeoutPeerFlag, true) ? 1 : 0;
       __syncthreads();

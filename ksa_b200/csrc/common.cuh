@@ -28,7 +28,18 @@ enum KernelStatus : int {
   kTimeoutPeerFlag = 5,    // waited on a flag written by another CTA or GPU
   kTimeoutSoftmax = 6,     // MMA waited for P / dS from the softmax warps
   kBadArgument = 7,
+  kDebugCheck = 8,         // a debug-build bounds check failed: the status word holds 8 | (source line << 8)
 };
+
+// Bounds checks of the debug build (`KSA_DEBUG=1 python -m ksa_b200.csrc.build`): tile indices, TMEM columns, smem
+// stage indices and signal slots.  A failing check records its source line in the status word and the guarded
+// access is skipped; nothing traps.  The release build compiles the condition away.
+#ifdef KSA_DEBUG_CHECKS
+#define KSA_DEV_CHECK(cond, status_ptr) \
+  ((cond) ? true : (atomicCAS((status_ptr), 0, (int)kDebugCheck | (__LINE__ << 8)), false))
+#else
+#define KSA_DEV_CHECK(cond, status_ptr) (true)
+#endif
 
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second at 2 GHz
 

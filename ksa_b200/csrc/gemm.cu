@@ -128,6 +128,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int tile = cta_first; tile < num_tiles && ok; tile += cta_stride) {
         int mb, nb;
         tile_coords(tile, mb, nb);
+        if (!KSA_DEV_CHECK(mb >= 0 && mb < tiles_m && nb >= 0 && nb < tiles_n && stage < S::kStages, status)) break;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, guard, kTimeoutStageEmpty)) { ok = false; break; }
           uint8_t* sa = smem + stage * S::kStageBytes;
@@ -165,6 +166,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, guard, kTimeoutAccEmpty)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
+        if (!KSA_DEV_CHECK((d_tmem & 0xFFFF) + BN <= (tmem_base & 0xFFFF) + 2 * BN, status)) break;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full[stage], phase, guard, kTimeoutTmaFull)) { ok = false; break; }
           tc_fence_after();

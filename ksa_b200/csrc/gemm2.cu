@@ -141,6 +141,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
         int mb, nb;
         tile_coords(tile, mb, nb);
+        if (!KSA_DEV_CHECK(mb >= 0 && mb < tiles_m && nb >= 0 && nb < tiles_n && rank < 2 && stage < k2Stages, status)) break;
         const int row0 = mb * 2 * k2BM + (int)rank * k2BM;      // this CTA's rows of A
         const int col0 = nb * k2BN + (int)rank * k2BNh;         // this CTA's rows of B
         for (int kb = 0; kb < num_kb; ++kb) {

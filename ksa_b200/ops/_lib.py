@@ -190,6 +190,8 @@ def check_status(clear: bool = True) -> None:
     """Synchronise and raise if any kernel's bounded wait gave up since the last check."""
     st = load().ksa_read_status(1 if clear else 0)
     if st != 0:
+        if st & 0xFF == 8:
+            raise RuntimeError(f"kernel status {st}: a debug-build bounds check failed at source line {st >> 8}")
         raise RuntimeError(f"kernel status {st}: {_STATUS_TEXT.get(st, 'unknown')}")
 
 
