@@ -49,7 +49,8 @@ def parse_args():
                     help="context-parallel size: --seq-len is the whole sequence, split over groups of this many ranks")
     ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"],
                     help="full-attention layers under --cp: head-parallel resharding or staged earlier keys")
-    ap.add_argument("--graph-multi", action="store_true", help="replay the fused multi-GPU step from a CUDA graph too")
+    ap.add_argument("--eager-multi", action="store_true",
+                    help="launch the multi-GPU step kernel by kernel (default: one CUDA graph per rank, as on 1 GPU)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--comm", default=None, choices=["fused", "collective"],
                     help="multi-GPU back end: fused P2P kernels (default) or NCCL collectives (A/B baseline)")
@@ -172,7 +173,7 @@ def run_ours(args) -> dict:
     dev_lab = [t.to(dev) for t in host_lab]
 
     # one CUDA graph per rank for the whole step; context parallelism numbers its exchanges on the host, so it stays eager
-    use_graph = not args.no_graph and (world == 1 or (args.graph_multi and cp == 1 and args.comm != "collective"))
+    use_graph = not args.no_graph and (world == 1 or (not args.eager_multi and cp == 1 and args.comm != "collective"))
     step_fn = engine.graphed_step if use_graph else engine.train_step
 
     def barrier():

@@ -257,8 +257,10 @@ def train(args) -> dict:
         heartbeat = HeartbeatMonitor(_get_default_store(), rank, world, args.heartbeat_timeout)
     faults = FaultInjector(rank=rank)
 
-    use_graph = use_cuda and world == 1 and not args.no_cuda_graph and not args.enable_distill \
-        and not args.enable_gradient_checkpointing
+    # one CUDA graph per step: single GPU, or the fused FSDP step (context parallelism numbers its exchanges on the
+    # host and stays eager)
+    use_graph = use_cuda and not args.no_cuda_graph and not args.enable_distill \
+        and not args.enable_gradient_checkpointing and (world == 1 or (cp == 1 and args.comm != "collective"))
     data_iter = iter(dataset)
     cached = []
     last_loss = None
