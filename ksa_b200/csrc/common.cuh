@@ -120,10 +120,16 @@ __device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ bool flag_wait_ge(const uint32_t* flag, uint32_t target, int* status, int code,
                                              bool system_scope) {
   const long long t0 = clock64();
+  // flags of other GPUs: the limit is word 1 of the status buffer (units of 2^20 cycles; the host sets it)
+  long long limit = kWaitLimitCycles;
+  if (system_scope) {
+    const int units = reinterpret_cast<const volatile int*>(status)[1];
+    if (units > 0) limit = (long long)units << 20;
+  }
   while (true) {
     uint32_t v = system_scope ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
     if (v >= target) return true;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > limit) {
       atomicCAS(status, 0, code);
       return false;
     }

@@ -327,6 +327,188 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(QkRopeBwdArgs b) {
   }
 }
 
+// ---- head_dim 128: one warp per row walks all heads of the row.  A lane owns two 32-bit words A and B of every head
+// (half-split rotary: elements {2l, 2l+1} and {2l+64, 2l+65}; interleaved: {4l, 4l+1} and {4l+2, 4l+3}), i.e. the
+// rotary pairs with frequency indices 2l and 2l+1, whose sine / cosine are computed once per row.  Loads of four heads
+// are in flight together.
+struct RopeLane {
+  int offA, offB;          // 32-bit word offsets inside a head
+  float c0, s0, c1, s1;    // cos / sin of the two pairs
+  float wq[4], wk[4];      // norm weights of this lane's 4 elements (q and k), 1 if there is no weight
+};
+
+__device__ __forceinline__ RopeLane rope_lane_setup(const QkRopeArgs& a, int row, int lane) {
+  RopeLane r;
+  r.offA = a.interleaved ? 2 * lane : lane;
+  r.offB = a.interleaved ? 2 * lane + 1 : lane + 32;
+  const float pos = (float)a.pos[row];
+  const float f0 = exp2f(-a.log2_theta * (2.f * (float)(2 * lane) / 128.f));
+  const float f1 = exp2f(-a.log2_theta * (2.f * (float)(2 * lane + 1) / 128.f));
+  sincosf(pos * f0, &r.s0, &r.c0);
+  sincosf(pos * f1, &r.s1, &r.c1);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { r.wq[i] = 1.f; r.wk[i] = 1.f; }
+  if (a.q_w) {
+    const float2 x = unpack_bf16x2(reinterpret_cast<const uint32_t*>(a.q_w)[r.offA]);
+    const float2 y = unpack_bf16x2(reinterpret_cast<const uint32_t*>(a.q_w)[r.offB]);
+    r.wq[0] = x.x; r.wq[1] = x.y; r.wq[2] = y.x; r.wq[3] = y.y;
+  }
+  if (a.k_w) {
+    const float2 x = unpack_bf16x2(reinterpret_cast<const uint32_t*>(a.k_w)[r.offA]);
+    const float2 y = unpack_bf16x2(reinterpret_cast<const uint32_t*>(a.k_w)[r.offB]);
+    r.wk[0] = x.x; r.wk[1] = x.y; r.wk[2] = y.x; r.wk[3] = y.y;
+  }
+  return r;
+}
+
+// v = {A.lo, A.hi, B.lo, B.hi}; pair p rotates (v[i1], v[i2]) by the angle of frequency index 2l + p
+template <bool IL>
+__device__ __forceinline__ void rope_pair_idx(int p, int& i1, int& i2) {
+  if (IL) { i1 = 2 * p; i2 = 2 * p + 1; }
+  else { i1 = p; i2 = p + 2; }
+}
+
+template <bool IL>
+__global__ void __launch_bounds__(256) qknorm_rope_fwd128_kernel(QkRopeArgs a) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= a.rows) return;
+  const int H = a.Hq + a.Hkv;
+  const int Hall = H + (a.copy_v ? a.Hkv : 0);
+  const RopeLane r = rope_lane_setup(a, row, lane);
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(a.qkv + (long long)row * a.in_stride);
+  uint32_t* dst = reinterpret_cast<uint32_t*>(a.out + (long long)row * a.out_stride);
+  for (int h0 = 0; h0 < Hall; h0 += 4) {
+    uint32_t ua[4], ub[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int head = min(h0 + u, Hall - 1);
+      ua[u] = src[head * 64 + r.offA];
+      ub[u] = src[head * 64 + r.offB];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int head = h0 + u;
+      if (head >= Hall) break;
+      if (head >= H) {      // v head: plain copy
+        dst[head * 64 + r.offA] = ua[u];
+        dst[head * 64 + r.offB] = ub[u];
+        continue;
+      }
+      const float2 fa = unpack_bf16x2(ua[u]), fb = unpack_bf16x2(ub[u]);
+      float v[4] = {fa.x, fa.y, fb.x, fb.y};
+      float rstd = 1.f;
+      const bool has_w = head < a.Hq ? a.q_w != nullptr : a.k_w != nullptr;
+      if (has_w) {
+        const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+        rstd = rsqrtf(ss / 128.f + a.eps);
+      }
+      if (lane == 0) a.rstd[(long long)row * H + head] = rstd;
+      const float* w = head < a.Hq ? r.wq : r.wk;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * w[i];
+      float o[4];
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        int i1, i2;
+        rope_pair_idx<IL>(p, i1, i2);
+        const float c = p ? r.c1 : r.c0, sn = p ? r.s1 : r.s0;
+        o[i1] = v[i1] * c - v[i2] * sn;
+        o[i2] = v[i2] * c + v[i1] * sn;
+      }
+      dst[head * 64 + r.offA] = pack_bf16x2(o[0], o[1]);
+      dst[head * 64 + r.offB] = pack_bf16x2(o[2], o[3]);
+    }
+  }
+}
+
+template <bool IL>
+__global__ void __launch_bounds__(256) qknorm_rope_bwd128_kernel(QkRopeBwdArgs b) {
+  const QkRopeArgs& a = b.f;
+  __shared__ float s_dw[2][128];
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) (&s_dw[0][0])[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int H = a.Hq + a.Hkv;
+  const int Hall = H + (a.copy_v ? a.Hkv : 0);
+  float dwq[4] = {0.f, 0.f, 0.f, 0.f}, dwk[4] = {0.f, 0.f, 0.f, 0.f};   // this lane's 4 elements, summed over rows
+  int offA = 0, offB = 0;
+  for (int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < a.rows; row += gridDim.x * (blockDim.x >> 5)) {
+    const RopeLane r = rope_lane_setup(a, row, lane);
+    offA = r.offA; offB = r.offB;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.qkv + (long long)row * a.in_stride);
+    const uint32_t* g = reinterpret_cast<const uint32_t*>(b.d_out + (long long)row * a.out_stride);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(b.d_qkv + (long long)row * a.in_stride);
+    for (int h0 = 0; h0 < Hall; h0 += 4) {
+      uint32_t xa[4], xb[4], ga[4], gb[4];
+      float rs[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int head = min(h0 + u, Hall - 1);
+        ga[u] = g[head * 64 + r.offA];
+        gb[u] = g[head * 64 + r.offB];
+        xa[u] = head < H ? src[head * 64 + r.offA] : 0u;
+        xb[u] = head < H ? src[head * 64 + r.offB] : 0u;
+        rs[u] = head < H ? a.rstd[(long long)row * H + head] : 1.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int head = h0 + u;
+        if (head >= Hall) break;
+        if (head >= H) {    // v head: the gradient passes through
+          dst[head * 64 + r.offA] = ga[u];
+          dst[head * 64 + r.offB] = gb[u];
+          continue;
+        }
+        const bool is_q = head < a.Hq;
+        const bool has_w = is_q ? a.q_w != nullptr : a.k_w != nullptr;
+        const float* w = is_q ? r.wq : r.wk;
+        const float2 g0 = unpack_bf16x2(ga[u]), g1 = unpack_bf16x2(gb[u]);
+        const float2 x0 = unpack_bf16x2(xa[u]), x1 = unpack_bf16x2(xb[u]);
+        const float gv[4] = {g0.x, g0.y, g1.x, g1.y};
+        const float xh[4] = {x0.x * rs[u], x0.y * rs[u], x1.x * rs[u], x1.y * rs[u]};
+        float dn[4];
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {   // transpose of the rotation
+          int i1, i2;
+          rope_pair_idx<IL>(p, i1, i2);
+          const float c = p ? r.c1 : r.c0, sn = p ? r.s1 : r.s0;
+          dn[i1] = gv[i1] * c + gv[i2] * sn;
+          dn[i2] = gv[i2] * c - gv[i1] * sn;
+        }
+        float o[4];
+        if (has_w) {
+          float dot = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (is_q) dwq[i] += dn[i] * xh[i]; else dwk[i] += dn[i] * xh[i];
+            dn[i] *= w[i];
+            dot += dn[i] * xh[i];
+          }
+          dot = warp_sum(dot) / 128.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) o[i] = rs[u] * (dn[i] - xh[i] * dot);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) o[i] = dn[i];
+        }
+        dst[head * 64 + r.offA] = pack_bf16x2(o[0], o[1]);
+        dst[head * 64 + r.offB] = pack_bf16x2(o[2], o[3]);
+      }
+    }
+  }
+  // this lane's elements: words offA, offB -> elements 2*offA, 2*offA+1, 2*offB, 2*offB+1
+  atomicAdd(&s_dw[0][2 * offA], dwq[0]); atomicAdd(&s_dw[0][2 * offA + 1], dwq[1]);
+  atomicAdd(&s_dw[0][2 * offB], dwq[2]); atomicAdd(&s_dw[0][2 * offB + 1], dwq[3]);
+  atomicAdd(&s_dw[1][2 * offA], dwk[0]); atomicAdd(&s_dw[1][2 * offA + 1], dwk[1]);
+  atomicAdd(&s_dw[1][2 * offB], dwk[2]); atomicAdd(&s_dw[1][2 * offB + 1], dwk[3]);
+  __syncthreads();
+  for (int i = threadIdx.x; i < 128; i += blockDim.x) {
+    if (b.dq_w && s_dw[0][i] != 0.f) atomicAdd(&b.dq_w[i], s_dw[0][i]);
+    if (b.dk_w && s_dw[1][i] != 0.f) atomicAdd(&b.dk_w[i], s_dw[1][i]);
+  }
+}
+
 // ------------------------------------------------------------------------------ SwiGLU
 // gate_up is [rows, 2F] = [gate | up]; out is [rows, F].
 __global__ void __launch_bounds__(256)
@@ -579,7 +761,8 @@ KSA_API int ksa_qknorm_rope_fwd(const void* qkv, void* out, const void* q_w, con
                in_stride, out_stride, rows, Hq, Hkv, D, log2f(theta), eps, interleaved, copy_v};
   const long long warps = (long long)rows * (Hq + Hkv + (copy_v ? Hkv : 0));
   const int blocks = (int)((warps + 7) / 8);
-  if (D == 128) qknorm_rope_fwd_kernel<128><<<blocks, 256, 0, ST(stream)>>>(a);
+  if (D == 128 && interleaved) qknorm_rope_fwd128_kernel<true><<<(rows + 7) / 8, 256, 0, ST(stream)>>>(a);
+  else if (D == 128) qknorm_rope_fwd128_kernel<false><<<(rows + 7) / 8, 256, 0, ST(stream)>>>(a);
   else qknorm_rope_fwd_kernel<64><<<blocks, 256, 0, ST(stream)>>>(a);
   KSA_CHECK_CUDA(cudaGetLastError());
   return 0;
@@ -598,8 +781,14 @@ KSA_API int ksa_qknorm_rope_bwd(const void* qkv, const void* d_out, void* d_qkv,
   const long long warps = (long long)rows * (Hq + Hkv + (copy_v ? Hkv : 0));
   long long blocks = (warps + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  if (D == 128) qknorm_rope_bwd_kernel<128><<<(int)blocks, 256, 0, ST(stream)>>>(b);
-  else qknorm_rope_bwd_kernel<64><<<(int)blocks, 256, 0, ST(stream)>>>(b);
+  if (D == 128) {
+    int rb = (rows + 7) / 8;
+    if (rb > 148 * 8) rb = 148 * 8;
+    if (interleaved) qknorm_rope_bwd128_kernel<true><<<rb, 256, 0, ST(stream)>>>(b);
+    else qknorm_rope_bwd128_kernel<false><<<rb, 256, 0, ST(stream)>>>(b);
+  } else {
+    qknorm_rope_bwd_kernel<64><<<(int)blocks, 256, 0, ST(stream)>>>(b);
+  }
   KSA_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

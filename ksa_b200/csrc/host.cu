@@ -4,6 +4,7 @@
 
 #include <mutex>
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace ksa {
@@ -91,6 +92,7 @@ int ensure_device(const void* device_ptr) {
   return kErrNone;
 }
 
+constexpr long long kDefaultPeerWaitMs = 10000;   // 10 s
 static int* g_status[64] = {nullptr};
 static std::mutex g_status_mu;
 
@@ -102,6 +104,15 @@ int* status_word() {
     int* p = nullptr;
     if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
     cudaMemset(p, 0, 256);
+    // word 1: limit of waits on flags written by OTHER GPUs, in units of 2^20 clock cycles (0 = the built-in limit).
+    // Ranks drift apart on the host (graph capture, a slow data loader), so this limit is longer than the one of the
+    // waits inside a kernel; KSA_PEER_WAIT_MS overrides it, ksa_set_peer_wait_ms changes it at run time.
+    int units = (int)(kDefaultPeerWaitMs * 2000LL / 1049);      // ~2 GHz: 2e6 cycles per ms
+    if (const char* e = getenv("KSA_PEER_WAIT_MS")) {
+      const long long ms = atoll(e);
+      if (ms > 0) units = (int)(ms * 2000LL / 1049 + 1);
+    }
+    cudaMemcpy(p + 1, &units, sizeof(int), cudaMemcpyHostToDevice);
     g_status[dev] = p;
   }
   return g_status[dev];
@@ -122,6 +133,14 @@ KSA_API int ksa_read_status(int clear) {
   if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
   if (clear && v != 0) cudaMemset(p, 0, sizeof(int));
   return v;
+}
+
+// Limit (milliseconds at ~2 GHz) of device-side waits on flags written by other GPUs, for the current device.
+KSA_API int ksa_set_peer_wait_ms(int ms) {
+  int* p = ksa::status_word();
+  if (!p || ms <= 0) return -1;
+  const int units = (int)((long long)ms * 2000LL / 1049 + 1);
+  return cudaMemcpy(p + 1, &units, sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess ? 0 : -1;
 }
 
 KSA_API int ksa_abi_version() { return 1; }

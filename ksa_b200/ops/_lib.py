@@ -195,6 +195,12 @@ def check_status(clear: bool = True) -> None:
         raise RuntimeError(f"kernel status {st}: {_STATUS_TEXT.get(st, 'unknown')}")
 
 
+def set_peer_wait_ms(ms: int) -> None:
+    """Limit of device-side waits on flags written by other GPUs (current device; default 10 s, or KSA_PEER_WAIT_MS)."""
+    if load().ksa_set_peer_wait_ms(int(ms)) != 0:
+        raise RuntimeError("could not set the peer wait limit")
+
+
 def attn_bwd_num_segments(lq: int) -> int:
     return load().ksa_attn_bwd_num_segments(lq)
 

@@ -330,6 +330,10 @@ class FsdpEngine(TrainEngine):
             torch.cuda.synchronize(self.device)
             cap = _CapturedStep(self, tokens.shape, first, boundary, warmup=False)
             self._graphs[key] = cap
+            # capturing takes a second or so of host time and not the same on every rank: replay together, so that
+            # no rank's kernels sit waiting for a peer that is still capturing
+            if self.world_size > 1:
+                dist.barrier(group=self.group)
         cap.tokens.copy_(tokens, non_blocking=True)
         cap.labels.copy_(labels, non_blocking=True)
         self._write_hyper()

@@ -319,3 +319,28 @@ def test_attention_packed(B, L, Hq, Hkv, D, C, S, W):
     o_ref.backward(g.float().cpu())
     check(out, o_ref.to(DEV), 1.5e-2, "packed attention out")
     check(qkv.grad, f.grad.to(DEV), 3e-2, "packed attention dqkv")
+
+
+# ------------------------------------------------------------------ bounded waits
+def test_wait_on_a_flag_nobody_sets_runs_out_and_reports():
+    """A device-side wait on a peer flag that nothing ever raises gives up after its limit, leaves a status code that
+    the host reads as an exception, and the context stays usable (no trap, no hang)."""
+    import time
+    flags = torch.zeros(4, dtype=torch.int32, device=DEV)
+    _lib.check_status()
+    _lib.set_peer_wait_ms(300)
+    try:
+        t0 = time.perf_counter()
+        _lib.call("ksa_signal_wait", flags, 2, None, 7)          # waits for flags[0..1] >= 7
+        with pytest.raises(RuntimeError, match="timed out waiting for a flag"):
+            _lib.check_status()
+        dt = time.perf_counter() - t0
+        assert 0.1 < dt < 5.0, dt
+        _lib.check_status()                                      # cleared: the next check is clean
+        flags.fill_(7)
+        _lib.call("ksa_signal_wait", flags, 2, None, 7)          # satisfied at once
+        _lib.check_status()
+        x = bf(64, 128)
+        check(ops.rms_norm(x, torch.ones(128, device=DEV, dtype=torch.bfloat16)), ref.rms_norm(x.float(), torch.ones(128, device=DEV)), 1e-2)
+    finally:
+        _lib.set_peer_wait_ms(10000)
