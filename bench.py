@@ -49,8 +49,6 @@ def parse_args():
                     help="context-parallel size: --seq-len is the whole sequence, split over groups of this many ranks")
     ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"],
                     help="full-attention layers under --cp: head-parallel resharding or staged earlier keys")
-    ap.add_argument("--eager-multi", action="store_true",
-                    help="launch the multi-GPU step kernel by kernel (default: one CUDA graph per rank, as on 1 GPU)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--comm", default=None, choices=["fused", "collective"],
                     help="multi-GPU back end: fused P2P kernels (default) or NCCL collectives (A/B baseline)")
@@ -172,8 +170,9 @@ def run_ours(args) -> dict:
     dev_in = [t.to(dev) for t in host_in]
     dev_lab = [t.to(dev) for t in host_lab]
 
-    # one CUDA graph per rank for the whole step; context parallelism numbers its exchanges on the host, so it stays eager
-    use_graph = not args.no_graph and (world == 1 or (not args.eager_multi and cp == 1 and args.comm != "collective"))
+    # one CUDA graph for the whole step on one GPU; the multi-GPU step stays eager (its communication kernels wait on
+    # other GPUs' flags from a side stream, an ordering that a graph replay does not promise to keep)
+    use_graph = not args.no_graph and world == 1
     step_fn = engine.graphed_step if use_graph else engine.train_step
 
     def barrier():

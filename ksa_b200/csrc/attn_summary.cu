@@ -342,18 +342,23 @@ __global__ void __launch_bounds__(kSumThreads) summary_attn_bwd_fast_kernel(SumA
     }
   }
   __syncthreads();
-  // dK[kk][d] += sum_qi ds[qi][kk] q[qi][d];  dV[kk][d] += sum_qi p[qi][kk] do[qi][d]   (two columns per thread)
-  const int pairs = HD / 2;
-  for (int idx = threadIdx.x; idx < nk_all * pairs; idx += kSumThreads) {
-    const int kk = idx / pairs, d = (idx % pairs) * 2;
-    float gk0 = 0.f, gk1 = 0.f, gv0 = 0.f, gv1 = 0.f;
+  // dK[kk][d] += sum_qi ds[qi][kk] q[qi][d];  dV[kk][d] += sum_qi p[qi][kk] do[qi][d]: eight columns (16 bytes) per
+  // thread and read-modify-write, so that the two global round trips per key row are 16 accesses instead of 64
+  const int vecs = HD / 8;
+  for (int idx = threadIdx.x; idx < nk_all * vecs; idx += kSumThreads) {
+    const int kk = idx / vecs, d = (idx % vecs) * 8;
+    float gk[8], gv[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { gk[e] = 0.f; gv[e] = 0.f; }
     for (int qi = 0; qi < nq; ++qi) {
       const float dsv = ds_s[qi * lay.nk_max + kk], pv = p_s[qi * lay.nk_max + kk];
-      gk0 += dsv * q_s[qi * HD + d]; gk1 += dsv * q_s[qi * HD + d + 1];
-      gv0 += pv * do_s[qi * HD + d]; gv1 += pv * do_s[qi * HD + d + 1];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        gk[e] += dsv * q_s[qi * HD + d + e];
+        gv[e] += pv * do_s[qi * HD + d + e];
+      }
     }
     bf16 *pk, *pv;
-    float bk0, bk1, bv0, bv1;
     if (kk < n_text) {
       pk = a.dk + (long long)b * a.dk_bs + (long long)(text0 + kk) * a.dk_rs + (long long)kvh * HD + d;
       pv = a.dv + (long long)b * a.dv_bs + (long long)(text0 + kk) * a.dv_rs + (long long)kvh * HD + d;
@@ -361,16 +366,29 @@ __global__ void __launch_bounds__(kSumThreads) summary_attn_bwd_fast_kernel(SumA
       pk = a.dks + (long long)b * a.dks_bs + (long long)(sum0 + kk - n_text) * a.dks_rs + (long long)kvh * HD + d;
       pv = a.dvs + (long long)b * a.dvs_bs + (long long)(sum0 + kk - n_text) * a.dvs_rs + (long long)kvh * HD + d;
     }
+    float bk[8], bv[8];
     if (kk >= n_text && a.dks32) {
       const long long o = (((long long)b * a.Ns_k + (sum0 + kk - n_text)) * a.Hkv + kvh) * HD + d;
-      bk0 = a.dks32[o]; bk1 = a.dks32[o + 1]; bv0 = a.dvs32[o]; bv1 = a.dvs32[o + 1];
+      const float4 k0 = *reinterpret_cast<const float4*>(a.dks32 + o), k1 = *reinterpret_cast<const float4*>(a.dks32 + o + 4);
+      const float4 v0 = *reinterpret_cast<const float4*>(a.dvs32 + o), v1 = *reinterpret_cast<const float4*>(a.dvs32 + o + 4);
+      bk[0] = k0.x; bk[1] = k0.y; bk[2] = k0.z; bk[3] = k0.w; bk[4] = k1.x; bk[5] = k1.y; bk[6] = k1.z; bk[7] = k1.w;
+      bv[0] = v0.x; bv[1] = v0.y; bv[2] = v0.z; bv[3] = v0.w; bv[4] = v1.x; bv[5] = v1.y; bv[6] = v1.z; bv[7] = v1.w;
     } else {
-      const float2 fk = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pk));
-      const float2 fv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pv));
-      bk0 = fk.x; bk1 = fk.y; bv0 = fv.x; bv1 = fv.y;
+      const uint4 uk = *reinterpret_cast<const uint4*>(pk), uv = *reinterpret_cast<const uint4*>(pv);
+      const uint32_t ku[4] = {uk.x, uk.y, uk.z, uk.w}, vu[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fk = unpack_bf16x2(ku[e]), fv = unpack_bf16x2(vu[e]);
+        bk[2 * e] = fk.x; bk[2 * e + 1] = fk.y; bv[2 * e] = fv.x; bv[2 * e + 1] = fv.y;
+      }
     }
-    *reinterpret_cast<uint32_t*>(pk) = pack_bf16x2(bk0 + gk0, bk1 + gk1);
-    *reinterpret_cast<uint32_t*>(pv) = pack_bf16x2(bv0 + gv0, bv1 + gv1);
+    uint4 ok, ov;
+    ok.x = pack_bf16x2(bk[0] + gk[0], bk[1] + gk[1]); ok.y = pack_bf16x2(bk[2] + gk[2], bk[3] + gk[3]);
+    ok.z = pack_bf16x2(bk[4] + gk[4], bk[5] + gk[5]); ok.w = pack_bf16x2(bk[6] + gk[6], bk[7] + gk[7]);
+    ov.x = pack_bf16x2(bv[0] + gv[0], bv[1] + gv[1]); ov.y = pack_bf16x2(bv[2] + gv[2], bv[3] + gv[3]);
+    ov.z = pack_bf16x2(bv[4] + gv[4], bv[5] + gv[5]); ov.w = pack_bf16x2(bv[6] + gv[6], bv[7] + gv[7]);
+    *reinterpret_cast<uint4*>(pk) = ok;
+    *reinterpret_cast<uint4*>(pv) = ov;
   }
 }
 

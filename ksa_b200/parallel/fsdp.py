@@ -63,7 +63,6 @@ class FsdpEngine(TrainEngine):
         self.comm_ctas = comm_ctas
         self._symm = []
         super().__init__(model, *args, world_size=world_size, rank=rank, **kw)
-        self._graph_warm = set()
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._epoch_ring = torch.zeros(32, 1, dtype=torch.int32)
         if self.device.type == "cuda":
@@ -312,37 +311,14 @@ class FsdpEngine(TrainEngine):
         return self._grad_sq_reduced.sqrt()
 
     def graphed_step(self, tokens, labels):
-        """The fused step as one CUDA graph per rank.  Flag values come from the device-resident step counter, so a
-        replay waits for the peers' current step like the eager step does.  The first step of each shape runs eagerly
-        (it is the warm-up: a captured run executes nothing, and a discarded trial step would leave this step's flags
-        already raised on the peers)."""
-        if self.comm != "fused":
-            return super().graphed_step(tokens, labels)
-        from ..training.engine import _CapturedStep
-        first = self.micro_step == 0
-        boundary = self.micro_step + 1 == self.grad_accum_steps
-        key = (tuple(tokens.shape), first, boundary)
-        cap = self._graphs.get(key)
-        if cap is None:
-            if key not in self._graph_warm:
-                self._graph_warm.add(key)
-                return self.train_step(tokens, labels)
-            torch.cuda.synchronize(self.device)
-            cap = _CapturedStep(self, tokens.shape, first, boundary, warmup=False)
-            self._graphs[key] = cap
-            # capturing takes a second or so of host time and not the same on every rank: replay together, so that
-            # no rank's kernels sit waiting for a peer that is still capturing
-            if self.world_size > 1:
-                dist.barrier(group=self.group)
-        cap.tokens.copy_(tokens, non_blocking=True)
-        cap.labels.copy_(labels, non_blocking=True)
-        self._write_hyper()
-        cap.graph.replay()
-        self.micro_step += 1
-        if boundary:
-            self.step_count += 1
-            self.micro_step = 0
-        return cap.loss
+        """Only the collective back end can be replayed from a CUDA graph.  The fused step is not captured: its
+        communication kernels wait on flags raised by other GPUs and sit on a side-stream branch; a graph replay is
+        free to order independent branches as it likes, and with four ranks it ordered a waiting kernel ahead of the
+        kernel its peers were waiting for (a distributed deadlock that only the bounded waits ended).  The eager step
+        with explicit streams keeps the launch order that the protocol assumes."""
+        if self.comm == "fused":
+            return self.train_step(tokens, labels)
+        return super().graphed_step(tokens, labels)
 
     def refresh_compute_from_master(self) -> None:
         for u in self.units:

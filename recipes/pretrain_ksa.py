@@ -257,10 +257,9 @@ def train(args) -> dict:
         heartbeat = HeartbeatMonitor(_get_default_store(), rank, world, args.heartbeat_timeout)
     faults = FaultInjector(rank=rank)
 
-    # one CUDA graph per step: single GPU, or the fused FSDP step (context parallelism numbers its exchanges on the
-    # host and stays eager)
-    use_graph = use_cuda and not args.no_cuda_graph and not args.enable_distill \
-        and not args.enable_gradient_checkpointing and (world == 1 or (cp == 1 and args.comm != "collective"))
+    # one CUDA graph per step on a single GPU; multi-GPU steps stay eager (see FsdpEngine.graphed_step)
+    use_graph = use_cuda and world == 1 and not args.no_cuda_graph and not args.enable_distill \
+        and not args.enable_gradient_checkpointing
     data_iter = iter(dataset)
     cached = []
     last_loss = None

@@ -77,34 +77,6 @@ def _worker(rank, world, port, out_q):
             assert abs(gc - gf) < 0.05 * gc, (key, gc, gf)
             for a, b in zip(wc, wf):
                 assert (a - b).norm() <= 1e-2 * a.norm().clamp_min(1e-6), key
-        # --- the fused step replayed from a CUDA graph against the eager fused step: same data, 5 steps
-        data2 = torch.randint(0, cfg.vocab_size, (5, world, 2, 513), generator=g)
-        runs = {}
-        for mode in ("eager", "graph"):
-            torch.manual_seed(0)
-            model = get_model_class(cfg.model_class)(cfg)
-            model.init_weights(seed=0)
-            model = model.to(dev).to(torch.bfloat16)
-            eng = FsdpEngine(model, lr=1e-3, weight_decay=0.1, clip_value=1.0, world_size=world, rank=rank, comm="fused")
-            step = eng.graphed_step if mode == "graph" else eng.train_step
-            losses = []
-            for s in range(5):
-                x = data2[s, rank].to(dev)
-                losses.append(float(step(x[:, :-1].contiguous(), x[:, 1:].contiguous())))
-            torch.cuda.synchronize(); _lib.check_status(); dist.barrier()
-            if mode == "graph":
-                assert len(eng._graphs) == 1
-            eng._write_hyper(); eng._overlap_active = False
-            for ui in range(len(eng.units)):
-                eng._gather_now(ui)
-            torch.cuda.synchronize(); _lib.check_status(); dist.barrier()
-            runs[mode] = (losses, [u.compute.float().clone() for u in eng.units])
-            eng.close()
-        le, we = runs["eager"]
-        lg, wg = runs["graph"]
-        assert all(abs(a - b) < 3e-2 for a, b in zip(le, lg)), (le, lg)
-        for a, b in zip(we, wg):
-            assert (a - b).norm() <= 1e-2 * a.norm().clamp_min(1e-6), "graph replay diverged from the eager step"
         out_q.put((rank, "ok", lf))
     except Exception as e:  # noqa: BLE001
         import traceback
