@@ -29,12 +29,17 @@ def test_config_roundtrip(tmp_path):
 
 
 def test_shipped_reference_json_loads():
+    """A model JSON in the reference's own format (pattern strings, ``__class__`` dispatch) loads unchanged; with
+    ``KSA_REFERENCE_DIR`` set, the file that the reference ships is loaded too."""
     import os
-    path = "/root/reference/examples/pretrain/model_config/model_config_1b9_hybrid.json"
-    if not os.path.exists(path):
-        pytest.skip("reference tree not mounted")
-    cfg = load_config(path)
-    assert cfg.summary_chunk_size == 8 and cfg.get_layer_sliding_chunk_num(3) == 1024
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    paths = [os.path.join(here, "examples", "pretrain", "model_config", "model_config_1b9_shipped_shape.json")]
+    ref_dir = os.environ.get("KSA_REFERENCE_DIR")
+    if ref_dir:
+        paths.append(os.path.join(ref_dir, "examples", "pretrain", "model_config", "model_config_1b9_hybrid.json"))
+    for path in paths:
+        cfg = load_config(path)
+        assert cfg.summary_chunk_size == 8 and cfg.get_layer_sliding_chunk_num(3) == 1024
 
 
 @pytest.mark.parametrize("L,C,S,W", [(256, 32, 1, 2), (192, 16, 2, 1), (128, 8, 1, 4), (100, 32, 1, 1)])
