@@ -1,0 +1,145 @@
+"""Host-side models of the cross-GPU flag protocols (context-parallel exchange slots, tensor-parallel partial slots).
+
+Each rank is a generator that performs the waits, writes and flag stores of ``ksa_b200/parallel/cp.py`` /
+``ksa_b200/parallel/tp.py`` (and of the kernels they launch) in program order; a scheduler interleaves the ranks at
+random.  The models check that no rank ever reads a slot that holds another exchange's data, that every run ends, and
+that a withheld flag ends in an error status after the bounded wait instead of a stale read or an endless spin.
+"""
+import random
+
+import pytest
+
+WAIT_LIMIT = 400      # scheduler turns a model "kernel" spins before it gives up, like the cycle limit on the device
+
+
+class Timeout(Exception):
+    pass
+
+
+def wait_ge(read, target, status, rank):
+    spins = 0
+    while read() < target:
+        spins += 1
+        if spins > WAIT_LIMIT:
+            status[rank] = 5          # the status code of a peer-flag timeout
+            raise Timeout()
+        yield
+
+
+def run(ranks, rng, limit=400000):
+    live = list(ranks)
+    for _ in range(limit):
+        if not live:
+            return
+        r = rng.choice(live)
+        try:
+            next(r)
+        except (StopIteration, Timeout):
+            live.remove(r)
+    raise AssertionError("ranks did not finish")
+
+
+def cp_rank(rank, P, E, slots, ready, consumed, status, withhold=None):
+    """Exchange e: publish into slot e % 2, pull from every earlier rank, tell everybody the slot was read."""
+    last_use = [None, None]
+    for e in range(E):
+        s = e % 2
+        if last_use[s] is not None:
+            for p in range(P):
+                yield from wait_ge(lambda p=p: consumed[rank][s][p], last_use[s] + 1, status, rank)
+        last_use[s] = e
+        slots[rank][s] = ("data", rank, e)
+        yield
+        if withhold != (rank, e):
+            for p in range(P):
+                ready[p][s][rank] = e + 1
+                yield
+        for owner in range(rank):                      # halo and summaries come from earlier ranks
+            yield from wait_ge(lambda o=owner: ready[rank][s][o], e + 1, status, rank)
+            assert slots[owner][s] == ("data", owner, e), f"rank {rank} read a stale or future block of rank {owner}"
+            yield
+        for p in range(P):
+            consumed[p][s][rank] = e + 1
+            yield
+
+
+@pytest.mark.parametrize("P,E", [(2, 7), (4, 6), (8, 4)])
+def test_context_parallel_exchange_slots(P, E):
+    for seed in range(15):
+        rng = random.Random(seed)
+        slots = [[None, None] for _ in range(P)]
+        ready = [[[0] * P for _ in range(2)] for _ in range(P)]        # ready[on rank][slot][producer]
+        consumed = [[[0] * P for _ in range(2)] for _ in range(P)]     # consumed[on rank][slot][consumer]
+        status = [0] * P
+        run([cp_rank(r, P, E, slots, ready, consumed, status) for r in range(P)], rng)
+        assert status == [0] * P
+
+
+def test_context_parallel_withheld_flag_times_out_without_a_stale_read():
+    P, E = 4, 6
+    rng = random.Random(1)
+    slots = [[None, None] for _ in range(P)]
+    ready = [[[0] * P for _ in range(2)] for _ in range(P)]
+    consumed = [[[0] * P for _ in range(2)] for _ in range(P)]
+    status = [0] * P
+    run([cp_rank(r, P, E, slots, ready, consumed, status, withhold=(1, 3)) for r in range(P)], rng)
+    assert status[2] == 5 and status[3] == 5        # the ranks behind the silent one report a peer-flag timeout
+    assert status[0] in (0, 5)                       # rank 0 reads nobody; it may time out later on a full slot
+
+
+def tp_rank(rank, T, E, partial, flags, status, withhold=None):
+    """All-reduce e (1-based flag value): the GEMM writes the partial block into slot (e-1) % 2, the fused kernel
+    announces it, waits for every peer's announcement and reads all blocks."""
+    for e in range(1, E + 1):
+        s = (e - 1) % 2
+        partial[rank][s] = ("partial", rank, e)
+        yield
+        if withhold != (rank, e):
+            for p in range(T):
+                flags[p][rank] = max(flags[p][rank], e)
+                yield
+        for p in range(T):
+            yield from wait_ge(lambda p=p: flags[rank][p], e, status, rank)
+        for p in range(T):
+            assert partial[p][s] == ("partial", p, e), f"rank {rank} summed a block of another all-reduce from rank {p}"
+            yield
+
+
+@pytest.mark.parametrize("T", [2, 4, 8])
+def test_tensor_parallel_partial_slots(T):
+    for seed in range(15):
+        rng = random.Random(seed)
+        partial = [[None, None] for _ in range(T)]
+        flags = [[0] * T for _ in range(T)]            # flags[on rank][announcing rank]
+        status = [0] * T
+        run([tp_rank(r, T, 9, partial, flags, status) for r in range(T)], rng)
+        assert status == [0] * T
+    # a rank that never announces all-reduce 4: everybody else gives up with the timeout status, nobody sums garbage
+    rng = random.Random(3)
+    partial = [[None, None] for _ in range(T)]
+    flags = [[0] * T for _ in range(T)]
+    status = [0] * T
+    run([tp_rank(r, T, 9, partial, flags, status, withhold=(0, 4)) for r in range(T)], rng)
+    assert all(status[r] == 5 for r in range(1, T))
+
+
+def test_one_slot_would_not_be_enough():
+    """The models are not vacuous: with a single slot a fast rank overwrites a block that a slow peer still reads."""
+    def tp_one_slot(rank, T, E, partial, flags, status):
+        for e in range(1, E + 1):
+            partial[rank][0] = ("partial", rank, e)
+            yield
+            for p in range(T):
+                flags[p][rank] = max(flags[p][rank], e)
+                yield
+            for p in range(T):
+                yield from wait_ge(lambda p=p: flags[rank][p], e, status, rank)
+            for p in range(T):
+                assert partial[p][0] == ("partial", p, e)
+                yield
+    with pytest.raises(AssertionError):
+        for seed in range(40):
+            rng = random.Random(seed)
+            partial = [[None] for _ in range(3)]
+            flags = [[0] * 3 for _ in range(3)]
+            run([tp_one_slot(r, 3, 6, partial, flags, [0] * 3) for r in range(3)], rng)
