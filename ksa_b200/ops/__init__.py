@@ -29,9 +29,9 @@ from . import _lib
 from .layout import SummaryLayout, get_layout
 
 UNBOUNDED_WINDOW = 1 << 30
-# GEMMs with at least this many 256 x 256 tiles (one wave of 74 CTA pairs) run on CTA pairs (tcgen05 cta_group::2,
-# csrc/gemm2.cu); smaller ones use the single-CTA kernel with 128-row tiles.  0 disables the pair kernel.
-GEMM_PAIR_MIN_TILES = int(__import__("os").environ.get("KSA_GEMM_PAIR_MIN_TILES", "74"))
+# GEMMs with at least this many 256 x 256 tiles run on CTA pairs (tcgen05 cta_group::2, csrc/gemm2.cu; 74 pairs per
+# GPU); below that the single-CTA kernel with 128-row tiles has more CTAs to spread.  0 disables the pair kernel.
+GEMM_PAIR_MIN_TILES = int(__import__("os").environ.get("KSA_GEMM_PAIR_MIN_TILES", "32"))
 
 
 def _cuda(x: torch.Tensor) -> bool:
