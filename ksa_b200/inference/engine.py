@@ -301,17 +301,44 @@ class KsaInferenceEngine:
         return self._head(hN) if with_head else hN
 
     @torch.no_grad()
-    def generate(self, prompt: torch.Tensor, max_new_tokens: int, eos_id: Optional[int] = None) -> torch.Tensor:
-        """Greedy decoding; returns ``[B, L + new]``."""
+    def generate(self, prompt: torch.Tensor, max_new_tokens: int, eos_id: Optional[int] = None,
+                 temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
+                 generator: Optional[torch.Generator] = None) -> torch.Tensor:
+        """Decode ``max_new_tokens`` tokens; returns ``[B, L + new]``.  ``temperature == 0`` is greedy decoding;
+        otherwise tokens are sampled from the temperature-scaled distribution restricted to the ``top_k`` most likely
+        tokens and / or the smallest set whose probability mass reaches ``top_p``
+        (``muse/models/qwen3/modeling.py:473-605``)."""
         logits = self.prefill(prompt)
         out = [prompt]
-        nxt = logits.argmax(-1)
+        done = torch.zeros(prompt.shape[0], dtype=torch.bool, device=prompt.device)
+        nxt = sample_next(logits, temperature, top_k, top_p, generator)
         for i in range(max_new_tokens):
+            if eos_id is not None:
+                nxt = torch.where(done, torch.full_like(nxt, eos_id), nxt)
+                done = done | (nxt == eos_id)
             out.append(nxt.view(-1, 1))
-            if i + 1 == max_new_tokens or (eos_id is not None and bool((nxt == eos_id).all())):
+            if i + 1 == max_new_tokens or (eos_id is not None and bool(done.all())):
                 break
-            nxt = self.decode_step(nxt).argmax(-1)
+            nxt = sample_next(self.decode_step(nxt), temperature, top_k, top_p, generator)
         return torch.cat(out, dim=1)
+
+
+def sample_next(logits: torch.Tensor, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
+                generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    """``logits`` ``[B, V]`` -> token ids ``[B]`` (greedy when ``temperature <= 0``)."""
+    if temperature <= 0.0:
+        return logits.argmax(-1)
+    logits = logits.float() / temperature
+    if top_k and top_k < logits.shape[-1]:
+        kth = logits.topk(top_k, dim=-1).values[..., -1:]
+        logits = logits.masked_fill(logits < kth, float("-inf"))
+    if top_p < 1.0:
+        sorted_logits, order = logits.sort(dim=-1, descending=True)
+        probs = sorted_logits.softmax(-1)
+        drop = probs.cumsum(-1) - probs >= top_p            # keep tokens until the mass before them reaches top_p
+        sorted_logits = sorted_logits.masked_fill(drop, float("-inf"))
+        logits = torch.full_like(logits, float("-inf")).scatter(-1, order, sorted_logits)
+    return torch.multinomial(logits.softmax(-1), 1, generator=generator).squeeze(-1)
 
 
 class _OneChunk:

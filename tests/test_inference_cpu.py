@@ -81,3 +81,24 @@ def test_cache_state_machine_against_recompute_on_random_schedules():
                 logits = eng.decode_step(nxt)
 
     run()
+
+
+def test_sampling_restricts_to_top_k_and_top_p_and_stops_at_eos():
+    from ksa_b200.inference.engine import sample_next
+    logits = torch.tensor([[4.0, 3.0, 2.0, 1.0, 0.0, -1.0]]).repeat(64, 1)
+    g = torch.Generator().manual_seed(0)
+    assert sample_next(logits).tolist() == [0] * 64                                   # greedy
+    assert set(sample_next(logits, 1.0, top_k=2, generator=g).tolist()) <= {0, 1}
+    # softmax mass: 0.64, 0.24, 0.09, ...: top_p = 0.7 keeps tokens 0 and 1
+    assert set(sample_next(logits, 1.0, top_p=0.7, generator=g).tolist()) <= {0, 1}
+    assert set(sample_next(logits, 1.0, top_p=0.5, generator=g).tolist()) == {0}
+    assert len(set(sample_next(logits, 5.0, generator=g).tolist())) > 2               # a hot distribution spreads
+    model = _model(8, 1, 2, layers=2, freq=[1, 0])
+    eng = KsaInferenceEngine(model, max_len=64, batch=2)
+    prompt = torch.randint(0, 128, (2, 9))
+    first = eng.generate(prompt, 3)[:, 9]
+    out = eng.generate(prompt, 12, eos_id=int(first[0]))
+    assert out.shape[1] <= 21 and (out[0, 9:] == int(first[0])).all()                   # a finished row keeps emitting eos
+    s1 = eng.generate(prompt, 6, temperature=0.8, top_k=20, generator=torch.Generator().manual_seed(5))
+    s2 = eng.generate(prompt, 6, temperature=0.8, top_k=20, generator=torch.Generator().manual_seed(5))
+    assert torch.equal(s1, s2)
