@@ -17,6 +17,7 @@ struct GatherJob {
   const uint32_t* ready_flags;  // optional, own memory: shard r may be read once ready_flags[r] >= target
   const uint32_t* epoch_ptr;    // target = (epoch_ptr ? *epoch_ptr : 0) + epoch_add; a device-resident epoch keeps
   uint32_t epoch_add;           // a captured CUDA graph valid from step to step
+  uint32_t* done;               // optional, own memory: done[r] += 1 by every CTA once its part of shard r has landed
 };
 
 struct ReduceAdamwJob {
@@ -87,6 +88,101 @@ __device__ __forceinline__ bool run_gather_job(const GatherJob& j, int cta, int 
     for (; i < vecs; i += stride) *reinterpret_cast<uint4*>(dst + i * 16) = ld_peer_16(src + i * 16);
   }
   return true;
+}
+
+// ----------------------------------------------------------------------------------------------
+// The same gather driven by the copy engine of the SM instead of by load/store instructions: ONE thread per CTA
+// issues untiled bulk copies peer memory -> shared-memory ring -> own memory.  A ring of kBulkStages x 32 KB keeps
+// 160 KB in flight per CTA, which a CTA of 192 threads cannot do with register loads (12 KB), so a handful of CTAs
+// inside a tensor-core launch are enough to fill the NVLink ports.  Both addresses of every copy are 16-byte
+// aligned and every size is a multiple of 16 bytes (shard_bytes is; the chunk size is).
+constexpr int kBulkChunk = 32768;
+constexpr int kBulkStages = 5;
+constexpr int kBulkRingBytes = kBulkStages * kBulkChunk + 64;   // + the ring's mbarriers and the abort flag
+
+__device__ __forceinline__ void bulk_load_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_wait_read_all_but_one() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
+// writes of the copy engine (async proxy) ordered before later generic-proxy accesses and the other way round
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// CTA `cta` of `nctas` moves chunks cta, cta + nctas, ... of every remote shard.  `ring` is 1024-byte aligned shared
+// memory of kBulkRingBytes.  Only thread 0 works; the call returns for all threads of the CTA (the others at once).
+// Returns false if a wait gave up; nothing is left in flight either way.
+__device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta, int nctas, uint8_t* ring, int* status) {
+  if (threadIdx.x != 0) return true;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + kBulkStages * kBulkChunk);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kBulkStages);
+  for (int s = 0; s < kBulkStages; ++s) mbar_init(&bars[s], 1);
+  *abort_flag = 0;
+  fence_mbar_init();
+  const WaitGuard guard{abort_flag, status};
+  uint8_t* dst_base = const_cast<uint8_t*>(j.peers[j.rank]);
+  const uint32_t target = epoch_target(j.epoch_ptr, j.epoch_add);
+  // Chunks are numbered in the order this CTA moves them, across shards: chunk n uses stage n % kBulkStages and
+  // the (n / kBulkStages)-th phase of that stage's barrier.
+  long long issued = 0;    // loads issued
+  long long stored = 0;    // stores issued
+  long long freed = 0;     // stores known to have finished reading their stage
+  bool ok = true;
+  for (int step = 1; step < j.world && ok; ++step) {
+    const int r = (j.rank + step) % j.world;
+    if (!KSA_DEV_CHECK(r >= 0 && r < kMaxPeers && j.peers[r] != nullptr && (j.shard_bytes & 15) == 0, status)) { ok = false; break; }
+    if (j.ready_flags && !flag_wait_ge(j.ready_flags + r, target, status, kTimeoutPeerFlag, true)) { ok = false; break; }
+    const uint8_t* src = j.peers[r] + (long long)r * j.shard_bytes;
+    uint8_t* dst = dst_base + (long long)r * j.shard_bytes;
+    const long long n_chunks = (j.shard_bytes + kBulkChunk - 1) / kBulkChunk;
+    long long next_load = cta, next_store = cta;
+    while (next_store < n_chunks) {
+      while (next_load < n_chunks && issued - freed < kBulkStages) {
+        const int s = (int)(issued % kBulkStages);
+        const long long off = next_load * kBulkChunk;
+        const uint32_t bytes = (uint32_t)min((long long)kBulkChunk, j.shard_bytes - off);
+        mbar_expect_tx(&bars[s], bytes);
+        bulk_load_g2s(ring + s * kBulkChunk, src + off, bytes, &bars[s]);
+        ++issued;
+        next_load += nctas;
+      }
+      const int s = (int)(stored % kBulkStages);
+      if (!mbar_wait(&bars[s], (uint32_t)((stored / kBulkStages) & 1), guard, kTimeoutTmaFull)) { ok = false; break; }
+      const long long off = next_store * kBulkChunk;
+      const uint32_t bytes = (uint32_t)min((long long)kBulkChunk, j.shard_bytes - off);
+      fence_proxy_async();
+      bulk_store_s2g(dst + off, ring + s * kBulkChunk, bytes);
+      tma_store_commit();
+      ++stored;
+      next_store += nctas;
+      bulk_wait_read_all_but_one();     // every store but the newest has read its stage: those stages may be refilled
+      freed = stored - 1;
+    }
+    if (!ok) break;
+    tma_store_wait0();                  // this CTA's part of shard r is written
+    freed = stored;
+    if (j.done) {
+      fence_proxy_async_all();
+      __threadfence();
+      red_release_gpu_add(j.done + r, 1u);
+    }
+  }
+  if (!ok) {
+    // give loads that are still in flight a bounded time to land (their destination is this CTA's shared memory)
+    for (long long n = stored; n < issued; ++n) {
+      const int s = (int)(n % kBulkStages);
+      const uint32_t parity = (uint32_t)((n / kBulkStages) & 1);
+      for (int spin = 0; spin < (1 << 22) && !mbar_try_wait(&bars[s], parity); ++spin) {}
+    }
+    tma_store_wait0();
+  }
+  return ok;
 }
 
 // CTA `cta` of `nctas` reduces + updates its slice of the owned shard.

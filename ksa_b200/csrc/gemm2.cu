@@ -10,7 +10,14 @@
 // leader's barrier); `empty` and `acc_full` exist in both CTAs and are signalled for both by one multicast
 // tcgen05.commit; `acc_empty` lives in the leader and collects one arrival per epilogue warp of both CTAs.
 // No TMA load here uses cluster multicast.  Every wait is bounded.
-#include "common.cuh"
+//
+// All-gather -> GEMM in one launch (ksa_gemm2_gather_bf16): the first `comm.n_pairs` CTA pairs of the grid do no math.
+// One thread of each of their CTAs pulls the other ranks' shards of an operand out of the peers' memory with bulk
+// copies through its shared memory (run_gather_job_bulk) and counts every finished shard in `done[r]`; the TMA
+// producers of the math pairs wait (bounded) for the shards that hold the rows of their next tile, and the tile order
+// starts at this rank's own rows and follows the order in which the shards arrive.  The NVLink transfer of shard
+// r+1 therefore runs under the tensor-core tiles of shard r.
+#include "comm.cuh"
 #include "host.h"
 
 namespace ksa {
@@ -32,6 +39,17 @@ struct Gemm2Epilogue {
   long long ldc;
   int out_fp32, accumulate;
   float alpha;
+};
+
+// Communication work riding in a pair-GEMM launch, and what the math pairs wait for.
+struct Comm2Work {
+  int n_pairs;               // CTA pairs at the front of the grid that gather instead of computing (0: none)
+  GatherJob gather;          // gather.done is required when dep_operand != 0
+  int dep_operand;           // 0: the math does not read the gathered buffer; 1: A rows live in it; 2: B rows
+  long long dep_offset;      // byte offset of the operand's row 0 inside the gathered buffer
+  long long dep_row_bytes;   // bytes from one operand row to the next
+  uint32_t dep_target;       // shard r is complete once done[r] >= dep_target
+  int m_rotate;              // pair-tile row that is worked on first
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -87,9 +105,14 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(k2Threads, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Gemm2Epilogue ep,
-                  int M, int N, int K, int* status) {
+                  int M, int N, int K, int* status, const __grid_constant__ Comm2Work comm) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if ((int)(blockIdx.x >> 1) < comm.n_pairs) {
+    // communication pair: both CTAs gather on their own; no tensor memory, no cluster barrier, no pipeline barriers
+    run_gather_job_bulk(comm.gather, (int)blockIdx.x, 2 * comm.n_pairs, smem, status);
+    return;
+  }
   uint8_t* bar_base = smem + k2Stages * k2StageBytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);   // used in the leader
   uint64_t* empty = full + k2Stages;                         // both CTAs
@@ -101,7 +124,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();     // 0 = leader
   const WaitGuard guard{abort_flag, status};
-  const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
+  const int pair = ((int)blockIdx.x >> 1) - comm.n_pairs, n_pairs = ((int)gridDim.x >> 1) - comm.n_pairs;
   const int tiles_m = (M + 2 * k2BM - 1) / (2 * k2BM);
   const int tiles_n = (N + k2BN - 1) / k2BN;
   const int num_tiles = tiles_m * tiles_n;
@@ -128,7 +151,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int first_m = group * k2GroupM;
     const int group_rows = min(tiles_m - first_m, k2GroupM);
     const int in_group = tile - group * per_group;
-    mb = first_m + in_group % group_rows;
+    mb = first_m + in_group % group_rows + comm.m_rotate;
+    if (mb >= tiles_m) mb -= tiles_m;
     nb = in_group / group_rows;
   };
 
@@ -137,6 +161,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t shards_seen = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
         int mb, nb;
@@ -144,6 +169,26 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (!KSA_DEV_CHECK(mb >= 0 && mb < tiles_m && nb >= 0 && nb < tiles_n && rank < 2 && stage < k2Stages, status)) break;
         const int row0 = mb * 2 * k2BM + (int)rank * k2BM;      // this CTA's rows of A
         const int col0 = nb * k2BN + (int)rank * k2BNh;         // this CTA's rows of B
+        if (comm.dep_operand != 0) {
+          // the rows of this tile that live in the gathered buffer: wait for the shards that hold them
+          const long long r_lo = comm.dep_operand == 1 ? row0 : col0;
+          const long long r_end = comm.dep_operand == 1 ? min(row0 + k2BM, M) : min(col0 + k2BNh, N);
+          if (r_lo < r_end) {
+            const int s_lo = (int)((comm.dep_offset + r_lo * comm.dep_row_bytes) / comm.gather.shard_bytes);
+            const int s_hi = min((int)((comm.dep_offset + r_end * comm.dep_row_bytes - 1) / comm.gather.shard_bytes),
+                                 comm.gather.world - 1);
+            for (int s = max(s_lo, 0); s <= s_hi && ok; ++s) {
+              if (s == comm.gather.rank || ((shards_seen >> s) & 1u)) continue;
+              if (!flag_wait_ge(comm.gather.done + s, comm.dep_target, status, kTimeoutPeerFlag, true)) {
+                *abort_flag = 1;
+                ok = false;
+              }
+              shards_seen |= 1u << s;
+            }
+            if (!ok) break;
+            fence_proxy_async_all();     // the shard was written by other CTAs' bulk stores; TMA reads it next
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, guard, kTimeoutStageEmpty)) { ok = false; break; }
           uint8_t* sa = smem + stage * k2StageBytes;
@@ -269,7 +314,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 template <bool A_MN, bool B_MN>
 static int launch_gemm2(const void* a, const void* b, const Gemm2Epilogue& ep, int M, int N, int K, long long lda,
-                        long long ldb, cudaStream_t stream) {
+                        long long ldb, cudaStream_t stream, const Comm2Work& comm) {
   CUtensorMap tmA, tmB;
   int rc;
   if (!A_MN) {
@@ -309,11 +354,12 @@ static int launch_gemm2(const void* a, const void* b, const Gemm2Epilogue& ep, i
     attr_set = true;
   }
   const int tiles = ((M + 2 * k2BM - 1) / (2 * k2BM)) * ((N + k2BN - 1) / k2BN);
-  int pairs = num_sms / 2;
+  int pairs = num_sms / 2 - comm.n_pairs;     // the communication pairs take their SMs out of the same single wave
+  KSA_REQUIRE(pairs >= 1, "gemm2: %d communication pairs leave no SM for the math", comm.n_pairs);
   if (tiles < pairs) pairs = tiles;
   int* status = status_word();
   KSA_REQUIRE(status != nullptr, "could not allocate the status word");
-  kern<<<2 * pairs, k2Threads, k2SmemTotal, stream>>>(tmA, tmB, ep, M, N, K, status);
+  kern<<<2 * (pairs + comm.n_pairs), k2Threads, k2SmemTotal, stream>>>(tmA, tmB, ep, M, N, K, status, comm);
   KSA_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -333,8 +379,63 @@ KSA_API int ksa_gemm2_bf16(const void* a, const void* b, void* c, int M, int N, 
   KSA_REQUIRE(!(accumulate && !out_fp32), "gemm2: accumulate needs an fp32 output");
   Gemm2Epilogue ep{c, ldc, out_fp32, accumulate, alpha};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (!a_mn_major && !b_mn_major) return launch_gemm2<false, false>(a, b, ep, M, N, K, lda, ldb, st);
-  if (!a_mn_major && b_mn_major) return launch_gemm2<false, true>(a, b, ep, M, N, K, lda, ldb, st);
-  if (a_mn_major && !b_mn_major) return launch_gemm2<true, false>(a, b, ep, M, N, K, lda, ldb, st);
-  return launch_gemm2<true, true>(a, b, ep, M, N, K, lda, ldb, st);
+  const Comm2Work none{};
+  if (!a_mn_major && !b_mn_major) return launch_gemm2<false, false>(a, b, ep, M, N, K, lda, ldb, st, none);
+  if (!a_mn_major && b_mn_major) return launch_gemm2<false, true>(a, b, ep, M, N, K, lda, ldb, st, none);
+  if (a_mn_major && !b_mn_major) return launch_gemm2<true, false>(a, b, ep, M, N, K, lda, ldb, st, none);
+  return launch_gemm2<true, true>(a, b, ep, M, N, K, lda, ldb, st, none);
+}
+
+// All-gather -> GEMM in one launch.  The GEMM arguments are those of ksa_gemm2_bf16; both operands K-major.
+//   peers/world/rank/shard_bytes/ready_flags/epoch_ptr/epoch_add: the gather, as in ksa_peer_gather (shard r of every
+//     rank's buffer is bytes [r*shard_bytes, (r+1)*shard_bytes); shards r != rank are pulled into peers[rank]).
+//   done: `world` uint32 counters in own memory; every launch adds 2*comm_pairs to each done[r != rank].
+//     done_target is the value that means "complete" for THIS launch (the caller keeps the running total).
+//   dep_operand: 1 if A (the [M, K] operand) lies inside the gathered buffer, 2 if B does, 0 if neither (the
+//     gather then only shares the launch); dep_offset: byte offset of that operand's first row in the buffer; the
+//     row pitch is lda (ldb) elements.
+//   comm_pairs: CTA pairs (of 74) that gather instead of computing.
+KSA_API int ksa_gemm2_gather_bf16(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
+                                  long long ldb, long long ldc, int out_fp32, int accumulate, float alpha,
+                                  const void* const* peers, int world, int rank, long long shard_bytes,
+                                  const void* ready_flags, const void* epoch_ptr, unsigned epoch_add, void* done,
+                                  unsigned done_target, int dep_operand, long long dep_offset, int comm_pairs,
+                                  void* stream) {
+  KSA_ENTER(a);
+  using namespace ksa;
+  KSA_REQUIRE(M > 0 && N > 0 && K > 0, "gemm2_gather: empty problem %d x %d x %d", M, N, K);
+  KSA_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "gemm2_gather: lda/ldb must be multiples of 8 elements (got %lld, %lld)", lda, ldb);
+  KSA_REQUIRE(N % 8 == 0 && ldc % (out_fp32 ? 4 : 8) == 0, "gemm2_gather: N and ldc must keep 16-byte row alignment");
+  KSA_REQUIRE((reinterpret_cast<uintptr_t>(c) & 15) == 0, "gemm2_gather: C must be 16-byte aligned");
+  KSA_REQUIRE(!(accumulate && !out_fp32), "gemm2_gather: accumulate needs an fp32 output");
+  KSA_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, "gemm2_gather: rank %d of %d out of range", rank, world);
+  KSA_REQUIRE(shard_bytes > 0 && shard_bytes % 16 == 0, "gemm2_gather: shard bytes must be a positive multiple of 16");
+  KSA_REQUIRE(dep_operand >= 0 && dep_operand <= 2 && dep_offset >= 0, "gemm2_gather: bad dependency description");
+  KSA_REQUIRE(comm_pairs >= 1 && comm_pairs <= 16, "gemm2_gather: comm_pairs %d out of range", comm_pairs);
+  KSA_REQUIRE(dep_operand == 0 || done != nullptr, "gemm2_gather: a dependency needs the done counters");
+  Gemm2Epilogue ep{c, ldc, out_fp32, accumulate, alpha};
+  Comm2Work comm{};
+  if (world > 1) {
+    comm.n_pairs = comm_pairs;
+    for (int r = 0; r < world; ++r) {
+      KSA_REQUIRE(peers[r] != nullptr && (reinterpret_cast<uintptr_t>(peers[r]) & 15) == 0, "gemm2_gather: peer %d buffer missing or misaligned", r);
+      comm.gather.peers[r] = static_cast<const uint8_t*>(peers[r]);
+    }
+    comm.gather.world = world; comm.gather.rank = rank; comm.gather.shard_bytes = shard_bytes;
+    comm.gather.ready_flags = static_cast<const uint32_t*>(ready_flags);
+    comm.gather.epoch_ptr = static_cast<const uint32_t*>(epoch_ptr); comm.gather.epoch_add = epoch_add;
+    comm.gather.done = static_cast<uint32_t*>(done);
+    comm.dep_operand = dep_operand;
+    comm.dep_offset = dep_offset;
+    comm.dep_row_bytes = (dep_operand == 2 ? ldb : lda) * 2;
+    comm.dep_target = done_target;
+    if (dep_operand == 1) {
+      // start with the first tile row that lies entirely in this rank's own rows; a tile row that straddles the
+      // boundary to the previous rank's shard (the last one to arrive) then comes last
+      const long long first_row = ((long long)rank * shard_bytes - dep_offset + comm.dep_row_bytes - 1) / comm.dep_row_bytes;
+      const int tiles_m = (M + 2 * k2BM - 1) / (2 * k2BM);
+      if (first_row > 0 && first_row < M) comm.m_rotate = (int)((first_row + 2 * k2BM - 1) / (2 * k2BM)) % tiles_m;
+    }
+  }
+  return launch_gemm2<false, false>(a, b, ep, M, N, K, lda, ldb, reinterpret_cast<cudaStream_t>(stream), comm);
 }

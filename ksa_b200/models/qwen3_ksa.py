@@ -90,12 +90,19 @@ def _row_linear(tp, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return ops.linear(x, weight) if tp is None else tp.row_parallel_linear(x, weight)
 
 
-def _add_norm(tp, x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float):
+def _add_norm(tp, x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+              defer: bool = False):
     """Residual add + RMSNorm; with a tensor-parallel group ``delta`` is a partial sum that is all-reduced in the
-    same kernel."""
+    same kernel.  ``defer``: the normalised rows go to ``_col_linear`` next and the residual rows are not read before
+    the next ``_add_norm`` / ``_row_linear`` (the group may then overlap its gathers with that projection)."""
     if tp is None or delta is None:
         return ops.add_rms_norm(x, delta, weight, eps)
-    return tp.add_rms_norm(x, delta, weight, eps)
+    return tp.add_rms_norm(x, delta, weight, eps, defer_gather=defer)
+
+
+def _col_linear(tp, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Column-parallel projection (no communication of its own; may carry a deferred gather of ``x``)."""
+    return ops.linear(x, weight) if tp is None else tp.col_parallel_linear(x, weight)
 
 
 class SwiGluMlp(nn.Module):
@@ -107,7 +114,7 @@ class SwiGluMlp(nn.Module):
         self.w2 = FusedLinear(hidden, dim)
 
     def forward(self, x, tp=None):
-        return _row_linear(tp, ops.swiglu(self.w13(x)), self.w2.weight)
+        return _row_linear(tp, ops.swiglu(_col_linear(tp, x, self.w13.weight)), self.w2.weight)
 
 
 class KsaDecoderLayer(nn.Module):
@@ -140,18 +147,28 @@ class KsaDecoderLayer(nn.Module):
         Hq, Hkv, Dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         n_text = meta.B * meta.L
         tp = meta.tp
-        x, h = _add_norm(tp, x, delta, self.sa_norm.scale, cfg.norm_eps)
-        if self.is_summary_layer and meta.Ns > 0:
+        summary_path = self.is_summary_layer and meta.Ns > 0
+        # the normalised rows go straight into the column-parallel projection unless the summary rows have a norm of
+        # their own
+        plain = not summary_path or self.sa_norm_summary is None
+        x, h = _add_norm(tp, x, delta, self.sa_norm.scale, cfg.norm_eps, defer=plain)
+        if summary_path:
             if self.sa_norm_summary is not None:
                 h = torch.cat([h[:n_text], ops.rms_norm(x[n_text:], self.sa_norm_summary.scale, cfg.norm_eps)])
             if a.wqkv_summary is not None:
-                qkv = ops.dual_linear(h, a.wqkv.weight, a.wqkv_summary.weight, n_text)
+                if tp is not None and tp.fused_gather and not torch.is_grad_enabled():
+                    # text rows: projection that carries the gather of h; summary rows: their own weights, afterwards
+                    qkv = torch.empty((h.shape[0], a.wqkv.weight.shape[0]), dtype=h.dtype, device=h.device)
+                    tp.col_parallel_linear(h[:n_text], a.wqkv.weight, out=qkv[:n_text])
+                    ops.gemm(h[n_text:], a.wqkv_summary.weight, out=qkv[n_text:])
+                else:
+                    qkv = ops.dual_linear(h, a.wqkv.weight, a.wqkv_summary.weight, n_text)
                 if a.mix_coeff < 1.0:  # anneal summary projections towards the base projections
                     base_s = ops.linear(h[n_text:], a.wqkv.weight)
                     mixed = a.mix_coeff * qkv[n_text:].float() + (1.0 - a.mix_coeff) * base_s.float()
                     qkv = torch.cat([qkv[:n_text], mixed.to(qkv.dtype)])
             else:
-                qkv = ops.linear(h, a.wqkv.weight)
+                qkv = _col_linear(tp, h, a.wqkv.weight)
             if a.q_norm_summary is not None:
                 qkv = torch.cat([
                     ops.qk_norm_rope_packed(qkv[:n_text].contiguous(), a._norm_w(a.q_norm), a._norm_w(a.k_norm),
@@ -174,10 +191,10 @@ class KsaDecoderLayer(nn.Module):
             attn_out = _row_linear(tp, att, a.output_proj.weight)
             if collect is not None:
                 collect.append(attn_out[:n_text])
-            x, h2 = _add_norm(tp, x, attn_out, self.mlp_norm.scale, cfg.norm_eps)
+            x, h2 = _add_norm(tp, x, attn_out, self.mlp_norm.scale, cfg.norm_eps, defer=True)
             return x, self.mlp(h2, tp)
         # full causal attention on the text rows; summary rows (if any) pass through unchanged
-        qkv = ops.linear(h[:n_text], a.wqkv.weight)
+        qkv = _col_linear(tp, h[:n_text], a.wqkv.weight)
         qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), meta.pos[:n_text], Hq, Hkv, Dh,
                                       cfg.rope_base, cfg.norm_eps, meta.rope_interleaved)
         if meta.kv_sink is not None:
@@ -191,7 +208,7 @@ class KsaDecoderLayer(nn.Module):
         attn_out = _row_linear(tp, att, a.output_proj.weight)
         if collect is not None:
             collect.append(attn_out)
-        x, h2 = _add_norm(tp, x, attn_out, self.mlp_norm.scale, cfg.norm_eps)
+        x, h2 = _add_norm(tp, x, attn_out, self.mlp_norm.scale, cfg.norm_eps, defer=True)
         return x, self.mlp(h2[:n_text], tp)
 
 
@@ -356,6 +373,8 @@ class Qwen3Model(Model):
         delta = None
         for layer in self.layers:
             x, delta = layer(x, delta, meta, collect)
+        if tp is not None:
+            tp.flush()      # the residual rows are read directly below
         meta.kv_sink = None
         n_text = B * L
         if last_token_only:   # prefill: only the last position of every sequence feeds the head

@@ -83,6 +83,32 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     return out
 
 
+def gemm_gather(a: torch.Tensor, b: torch.Tensor, peers, world: int, rank: int, shard_bytes: int, ready_flags,
+                epoch: Optional[torch.Tensor], done: torch.Tensor, done_target: int, *, dep_operand: int = 1,
+                dep_offset: int = 0, comm_pairs: int = 4, epoch_add: int = 0,
+                out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """All-gather -> GEMM in one launch: ``C = A B^T`` (both K-major) on CTA pairs while ``comm_pairs`` further pairs
+    of the same launch pull the other ranks' shards of the gathered buffer over NVLink.
+
+    ``peers``: ctypes array of every rank's pointer to the buffer (``peers[rank]`` is this rank's copy, which the
+    gather completes); shard ``r`` is bytes ``[r*shard_bytes, (r+1)*shard_bytes)``.  ``dep_operand`` 1 (2) says that
+    ``a`` (``b``) lies in this rank's copy at byte ``dep_offset``: its tiles are read only once their shard has
+    landed.  ``done`` is a ``world``-element int32 device tensor to which every launch adds ``2*comm_pairs`` per remote
+    shard; ``done_target`` is the running total after this launch.
+    """
+    _require_bf16(a, b)
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1 and a.shape[1] == b.shape[1]
+    M, K = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    assert out.shape == (M, N) and out.stride(1) == 1
+    _lib.call("ksa_gemm2_gather_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
+              int(out.dtype == torch.float32), 0, 1.0, peers, world, rank, shard_bytes, ready_flags, epoch, epoch_add,
+              done, done_target, dep_operand, dep_offset, comm_pairs)
+    return out
+
+
 def _weight_grad(weight: torch.Tensor, compute):
     """Route a weight gradient: into ``weight.main_grad`` (fp32) or back to autograd.
 

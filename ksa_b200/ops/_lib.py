@@ -24,6 +24,8 @@ P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 _SIGNATURES: Dict[str, Sequence] = {
     "ksa_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, I, P],
     "ksa_gemm2_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, P],
+    "ksa_gemm2_gather_bf16": [P, P, P, I, I, I, L, L, L, I, I, F, P, I, I, L, P, P, ctypes.c_uint, P, ctypes.c_uint, I, L,
+                              I, P],
     "ksa_gemv_bf16": [P, P, P, I, I, I, L, L, L, P],
     "ksa_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, I, P],
     "ksa_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],

@@ -14,6 +14,7 @@ CPU (gloo) ranks run the same layout with ``all_reduce`` / ``all_gather`` for th
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -27,7 +28,14 @@ class TpContext:
     """Group + (on GPUs) the symmetric partial-sum slots of one tensor-parallel group."""
 
     def __init__(self, group, embed_dim: int, max_rows: int, device=None, dtype=torch.bfloat16,
-                 two_phase_rows: int = 2048, two_phase_min_size: int = 3):
+                 two_phase_rows: int = 2048, two_phase_min_size: Optional[int] = None,
+                 fused_gather: Optional[bool] = None, gather_pairs: Optional[int] = None):
+        if two_phase_min_size is None:
+            two_phase_min_size = int(os.environ.get("KSA_TP_TWO_PHASE_MIN", "3"))
+        if fused_gather is None:
+            fused_gather = os.environ.get("KSA_TP_FUSED_GATHER", "0") == "1"
+        if gather_pairs is None:
+            gather_pairs = int(os.environ.get("KSA_TP_GATHER_PAIRS", "4"))
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
@@ -37,6 +45,10 @@ class TpContext:
         self.dtype = dtype
         self.fused = device is not None and torch.device(device).type == "cuda"
         self.counter = 0            # all-reduces issued so far (identical on every rank)
+        self.two_phase_rows = 0
+        self.fused_gather = False
+        self._pending = None          # (data_ptr of the normalised rows, shard rows, rows) awaiting their gather
+        self._res_event = None        # end of the residual gather on the side stream
         if self.fused:
             from .symm import SignalPad, SymmetricBuffer
             item = torch.empty((), dtype=dtype).element_size()
@@ -65,9 +77,18 @@ class TpContext:
                 self._notify = self.flags2.flag_ptrs(self.rank)
                 self._res_ptrs = self.sp_buf.offset_ptr_array(0)
                 self._y_ptrs = self.sp_buf.offset_ptr_array(plane)
+            # All-gather -> GEMM in one launch for the normalised rows (the column-parallel projection that follows
+            # reads them shard by shard as they land); the residual rows travel on a side stream meanwhile.
+            self.fused_gather = bool(fused_gather) and bool(self.two_phase_rows)
+            self.gather_pairs = gather_pairs
+            if self.fused_gather:
+                self._done = torch.zeros(self.size, dtype=torch.int32, device=device)
+                self._done_total = 0
+                self._side = torch.cuda.Stream(device=device)
 
     def close(self) -> None:
         if self.fused:
+            self.flush()
             torch.cuda.synchronize(self.device)
             dist.barrier(self.group)
             self.flags.close()
@@ -86,17 +107,23 @@ class TpContext:
         """Partial ``x_local @ weight_local.T``; on GPUs written into the slot the next all-reduce reads."""
         if not self.fused:
             return ops.linear(x, weight)
+        self.flush()
         out = self._slot_view(x.shape[0])
         ops.gemm(x if x.is_contiguous() else x.contiguous(), weight, out=out)
         return out
 
     def add_rms_norm(self, x: torch.Tensor, partial: torch.Tensor, weight: torch.Tensor,
-                     eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
-        """``r = x + sum_ranks(partial)`` on the first ``partial.shape[0]`` rows and ``rms_norm(r)``."""
+                     eps: float, defer_gather: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``r = x + sum_ranks(partial)`` on the first ``partial.shape[0]`` rows and ``rms_norm(r)``.
+
+        ``defer_gather``: the caller promises that the next reader of the normalised rows is
+        ``col_parallel_linear`` and that it reads the residual rows only after another call into this object (or
+        ``flush``); the gathers of the two-phase form may then overlap with what follows."""
         if not self.fused:
             total = partial.clone()
             dist.all_reduce(total, group=self.group)
             return ops.add_rms_norm(x, total, weight, eps)
+        self.flush()
         rows_x, rows_d = x.shape[0], partial.shape[0]
         slot = self._slot_view(rows_d)
         if partial.data_ptr() != slot.data_ptr():
@@ -105,7 +132,7 @@ class TpContext:
         s = self.counter % 2
         self.counter += 1
         if self.two_phase_rows and rows_x >= self.two_phase_rows:
-            return self._two_phase(x, s, weight, rows_x, rows_d, eps)
+            return self._two_phase(x, s, weight, rows_x, rows_d, eps, defer_gather and self.fused_gather)
         res = torch.empty_like(x)
         y = torch.empty_like(x)
         _lib.call("ksa_tp_allreduce_add_rmsnorm", x, self._slot_ptrs[s], self._announce, self.flags.local_ptr(0),
@@ -113,7 +140,7 @@ class TpContext:
                   self._epoch[1:2])
         return res, y
 
-    def _two_phase(self, x, s, weight, rows_x, rows_d, eps):
+    def _two_phase(self, x, s, weight, rows_x, rows_d, eps, defer=False):
         """Reduce-scatter + add + norm of this rank's rows, then gather of the peers' rows.  The results live in the
         symmetric buffers until the next call of this kind (the callers consume them before that)."""
         T, D = self.size, self.D
@@ -125,14 +152,59 @@ class TpContext:
                   T, self.rank, weight, res, y, rows_x, rows_d, D, float(eps), self._epoch[0:1], self._epoch[1:2],
                   lo, hi, self._notify)
         # the epoch was advanced by the kernel above (stream order): a peer's shard is complete once its flag reached it
+        if defer:
+            main = torch.cuda.current_stream()
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                _lib.call("ksa_peer_gather", self._res_ptrs, T, self.rank, shard * D, x.element_size(),
+                          self.flags2.local_ptr(0), self._epoch[0:1], 0, 16)
+                self._res_event = torch.cuda.Event()
+                self._res_event.record(self._side)
+            self._pending = (y.data_ptr(), shard, rows_x)
+            return res[:rows_x], y[:rows_x]
         for ptrs in (self._res_ptrs, self._y_ptrs):
             _lib.call("ksa_peer_gather", ptrs, T, self.rank, shard * D, x.element_size(), self.flags2.local_ptr(0),
                       self._epoch[0:1], 0, 32)
         return res[:rows_x], y[:rows_x]
 
+    # ------------------------------------------------------------------ deferred gathers of the two-phase form
+    def flush(self) -> None:
+        """Complete what ``add_rms_norm(..., defer_gather=True)`` left open: gather the normalised rows now if no
+        projection took them along, and make the current stream wait for the residual rows."""
+        if not self.fused_gather:
+            return
+        if self._pending is not None:
+            _, shard, _ = self._pending
+            self._pending = None
+            _lib.call("ksa_peer_gather", self._y_ptrs, self.size, self.rank, shard * self.D,
+                      torch.empty((), dtype=self.dtype).element_size(), self.flags2.local_ptr(0), self._epoch[0:1], 0, 32)
+        if self._res_event is not None:
+            torch.cuda.current_stream().wait_event(self._res_event)
+            self._res_event = None
+
+    def col_parallel_linear(self, h: torch.Tensor, weight: torch.Tensor,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``h @ weight_local.T``.  When ``h`` is the normalised output of a deferred two-phase ``add_rms_norm``, the
+        gather of the other ranks' rows of ``h`` runs inside the GEMM launch (``ksa_gemm2_gather_bf16``)."""
+        p = self._pending if self.fused_gather else None
+        if (p is None or h.data_ptr() != p[0] or h.dim() != 2 or not h.is_contiguous() or h.shape[0] > p[2]
+                or h.shape[1] != self.D or weight.stride(1) != 1
+                or (torch.is_grad_enabled() and (h.requires_grad or weight.requires_grad))):
+            self.flush()
+            if out is not None:
+                return ops.gemm(h, weight, out=out)
+            return ops.linear(h, weight)
+        _, shard, _ = p
+        self._pending = None
+        self._done_total += 2 * self.gather_pairs
+        return ops.gemm_gather(h, weight, self._y_ptrs, self.size, self.rank, shard * self.D * h.element_size(),
+                               self.flags2.local_ptr(0), self._epoch[0:1], self._done, self._done_total,
+                               dep_operand=1, dep_offset=0, comm_pairs=self.gather_pairs, out=out)
+
     # ------------------------------------------------------------------ vocabulary-parallel head
     def gather_logits(self, local: torch.Tensor) -> torch.Tensor:
         """``[..., V/T]`` per rank -> ``[..., V]`` (rank order)."""
+        self.flush()
         parts = [torch.empty_like(local) for _ in range(self.size)]
         dist.all_gather(parts, local.contiguous(), group=self.group)
         return torch.cat(parts, dim=-1)

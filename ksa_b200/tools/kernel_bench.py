@@ -8,6 +8,8 @@
         cp-attn --seq 32768 --bwd          # context-parallel attention: one shard per rank, max over ranks
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m ksa_b200.tools.kernel_bench comm
     python -m ksa_b200.tools.kernel_bench comm --world 2      # the same kernels over buffers of one GPU
+    python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 -m ksa_b200.tools.kernel_bench \
+        ag-gemm --m 33024 --n 1536 --k 2560          # all-gather -> GEMM in one launch vs gather kernel + GEMM
 
 Each line reports the median time, the achieved TFLOP/s or GB/s and, when ``MEASURED_PEAKS.json`` sits at the
 repository root, the fraction of the measured peak (cuBLAS bf16 burst / STREAM-style copy).  ``--iters 1 --warmup 1
@@ -257,6 +259,80 @@ def bench_comm(a) -> None:
         dist.destroy_process_group()
 
 
+def bench_ag_gemm(a) -> None:
+    """All-gather -> GEMM: a row-sharded ``[m, k]`` activation (every rank holds ``m / world`` rows) times a local
+    ``[n, k]`` weight, as tensor-parallel prefill runs it.  Compares the stand-alone gather kernel followed by the
+    CTA-pair GEMM with the single launch in which ``--comm-pairs`` CTA pairs pull the peers' rows with bulk copies
+    while the other pairs compute on the rows that have landed.
+
+    Under ``torch.distributed.run`` the peers are GPUs (maximum over ranks; roofline = the slower of the FLOPs at the
+    measured GEMM peak and the remote bytes at the measured 770 GB/s peer-copy bandwidth).  Started as one process the
+    ``--world`` copies live on this GPU (the form a profiler can capture).
+    """
+    import ctypes
+    import torch.distributed as dist
+    multi = "RANK" in os.environ and int(os.environ.get("WORLD_SIZE", "1")) > 1
+    if multi:
+        from ..parallel.symm import SymmetricBuffer
+        rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        rank, world = 0, a.world
+    dev = torch.device("cuda", torch.cuda.current_device())
+    M, N, K = a.m, a.n, a.k
+    shard = (M + world - 1) // world
+    nbytes = shard * world * K * 2
+    if multi:
+        hold = SymmetricBuffer(nbytes)
+        ptrs, own = hold.ptr_array, hold.view(torch.bfloat16, 0, shard * world * K).view(shard * world, K)
+    else:
+        hold = [torch.empty(shard * world, K, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        ptrs, own = (ctypes.c_void_p * world)(*[t.data_ptr() for t in hold]), hold[0]
+        for t in hold:
+            t.normal_()
+    own.normal_()
+    W = torch.randn(N, K, device=dev).bfloat16()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    done = torch.zeros(world, dtype=torch.int32, device=dev)
+    total = [0]
+
+    def separate():
+        _lib.call("ksa_peer_gather", ptrs, world, rank, shard * K, 2, None, None, 0, a.ctas)
+        ops.gemm(own[:M], W, out=out, pair=True)
+
+    def fused():
+        total[0] += 2 * a.comm_pairs
+        ops.gemm_gather(own[:M], W, ptrs, world, rank, shard * K * 2, None, None, done, total[0], dep_operand=1,
+                        comm_pairs=a.comm_pairs, out=out)
+
+    def timed(fn):
+        if multi:
+            torch.cuda.synchronize()
+            dist.barrier()
+        t = torch.tensor([timeit(fn, a.iters, a.warmup, not a.no_flush)], device=dev, dtype=torch.float64)
+        if multi:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    t_sep, t_fused = timed(separate), timed(fused)
+    ref = own[:M].float() @ W.float().t() if M * N <= (1 << 26) else None
+    err = (out.float() - ref).abs().max().item() / ref.abs().max().item() if ref is not None else float("nan")
+    _lib.check_status()
+    if rank == 0:
+        pk = peaks()
+        flops, remote = 2.0 * M * N * K, (world - 1) * shard * K * 2.0
+        t_math, t_link = flops / (pk["tflops"] * 1e9), remote / (770.0 * 1e6)
+        where = "GPUs" if multi else "local buffers"
+        print(f"all-gather -> gemm {M}x{N}x{K}, world {world} ({where}): gather kernel + pair GEMM {t_sep:.4f} ms | "
+              f"one launch with {a.comm_pairs} communication pairs {t_fused:.4f} ms ({t_sep / t_fused:.2f}x)", flush=True)
+        print(f"  roofline: math {t_math:.4f} ms at {pk['src']} {pk['tflops']:.0f} TFLOP/s, link {t_link:.4f} ms at measured "
+              f"770 GB/s -> {max(t_math, t_link) / t_fused:.2f} of the slower one; max rel error {err:.2e}", flush=True)
+    if multi:
+        hold.close()
+        dist.destroy_process_group()
+
+
 def bench_tp_reduce(a) -> None:
     """The fused all-reduce + residual add + RMSNorm of tensor-parallel inference as ONE launch over ``--world``
     partial buffers of this GPU (the peers' flags are set beforehand, so nothing waits): the form a profiler can
@@ -284,7 +360,7 @@ def bench_tp_reduce(a) -> None:
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn", "comm", "tp-reduce"])
+    ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn", "comm", "tp-reduce", "ag-gemm"])
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--a-mn", action="store_true"); ap.add_argument("--b-mn", action="store_true")
@@ -302,8 +378,10 @@ def main(argv=None) -> None:
     ap.add_argument("--mbytes", type=int, default=256, help="comm: size of the fp32 gradient unit in MiB")
     ap.add_argument("--ctas", type=int, default=64, help="comm: CTAs of the communication kernels")
     ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"])
+    ap.add_argument("--comm-pairs", type=int, default=4, help="ag-gemm: CTA pairs that gather instead of computing")
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "gemv": bench_gemv, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn, "comm": bench_comm, "tp-reduce": bench_tp_reduce}[a.what](a)
+    {"gemm": bench_gemm, "gemv": bench_gemv, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn, "comm": bench_comm, "tp-reduce": bench_tp_reduce,
+     "ag-gemm": bench_ag_gemm}[a.what](a)
     _lib.check_status()
 
 

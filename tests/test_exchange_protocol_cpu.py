@@ -143,3 +143,78 @@ def test_one_slot_would_not_be_enough():
             partial = [[None] for _ in range(3)]
             flags = [[0] * 3 for _ in range(3)]
             run([tp_one_slot(r, 3, 6, partial, flags, [0] * 3) for r in range(3)], rng)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# All-gather -> GEMM in one launch (ksa_b200/csrc/gemm2.cu + run_gather_job_bulk in comm.cuh): communication CTAs copy
+# the remote shards chunk by chunk and add 1 to done[shard] when their part of a shard is written; the producers of the
+# math CTAs walk the tile rows starting at the first row block that lies entirely in the rank's own shard and wait for
+# done[s] >= target for every shard s that a row block touches.
+def _ag_gemm_roles(world, rank, rows, shard_rows, tile_rows, n_comm, n_math, ring, landed, done, status, reads,
+                   ready=True):
+    target = n_comm
+    tiles_m = (rows + tile_rows - 1) // tile_rows
+    first_row = rank * shard_rows
+    rotate = ((first_row + tile_rows - 1) // tile_rows) % tiles_m if 0 < first_row < rows else 0
+    chunk = 3                                             # rows per bulk copy
+
+    def comm_cta(cta):
+        for step in range(1, world):
+            r = (rank + step) % world
+            yield from wait_ge(lambda: 1 if ready else 0, 1, status, 0)       # the shard's ready flag
+            n_chunks = (shard_rows + chunk - 1) // chunk
+            inflight = []
+            for c in range(cta, n_chunks, n_comm):
+                while len(inflight) >= ring:                                   # a stage frees when its store was read
+                    landed[r].update(inflight.pop(0))
+                    yield
+                inflight.append(range(r * shard_rows + c * chunk, min(r * shard_rows + (c + 1) * chunk, (r + 1) * shard_rows)))
+                yield
+            for rows_ in inflight:                                             # wait_group 0: everything is written
+                landed[r].update(rows_)
+                yield
+            done[r] += 1
+            yield
+
+    def math_pair(pair):
+        seen = set()
+        for t in range(pair, tiles_m, n_math):
+            mb = (t + rotate) % tiles_m
+            lo, hi = mb * tile_rows, min((mb + 1) * tile_rows, rows)
+            for s in range(lo // shard_rows, (hi - 1) // shard_rows + 1):
+                if s == rank or s in seen:
+                    continue
+                yield from wait_ge(lambda s=s: done[s], target, status, 1)
+                seen.add(s)
+            for row in range(lo, hi):                                          # the TMA loads of this tile
+                s = row // shard_rows
+                assert s == rank or row in landed[s], f"tile row {mb} read row {row} before shard {s} had landed"
+            reads.append(mb)
+            yield
+    return [comm_cta(c) for c in range(n_comm)] + [math_pair(p) for p in range(n_math)]
+
+
+@pytest.mark.parametrize("world,rank,rows,tile_rows", [(4, 1, 130, 8), (2, 0, 64, 8), (8, 7, 129, 4), (4, 3, 50, 16)])
+def test_all_gather_gemm_dependencies(world, rank, rows, tile_rows):
+    shard_rows = (rows + world - 1) // world
+    for seed in range(20):
+        rng = random.Random(seed)
+        landed = [set() for _ in range(world)]
+        done = [0] * world
+        status = [0, 0]
+        reads = []
+        run(_ag_gemm_roles(world, rank, rows, shard_rows, tile_rows, 3, 5, 2, landed, done, status, reads), rng)
+        assert status == [0, 0]
+        assert sorted(reads) == list(range((rows + tile_rows - 1) // tile_rows))      # every tile row exactly once
+        # the walk starts inside the own shard: no wait can precede the first tile of a pair that starts there
+        first = reads[0] * tile_rows
+        assert first // shard_rows == rank or world == 1 or rank * shard_rows >= rows
+
+
+def test_all_gather_gemm_gives_up_when_shards_never_become_ready():
+    world, rank, rows, tile_rows = 4, 0, 64, 8
+    rng = random.Random(0)
+    landed, done, status, reads = [set() for _ in range(world)], [0] * world, [0, 0], []
+    run(_ag_gemm_roles(world, rank, rows, 16, tile_rows, 2, 3, 2, landed, done, status, reads, ready=False), rng)
+    assert status == [5, 5]                                   # the gather and then the math report the flag timeout
+    assert all(mb * tile_rows < 16 for mb in reads)           # only tiles of the own shard were computed

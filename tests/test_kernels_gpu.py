@@ -321,6 +321,80 @@ def test_attention_packed(B, L, Hq, Hkv, D, C, S, W):
     check(qkv.grad, f.grad.to(DEV), 3e-2, "packed attention dqkv")
 
 
+# ------------------------------------------------------------------ all-gather -> GEMM in one launch
+def _gather_case(world, rank, rows, K):
+    """Every rank's copy of a row-sharded [rows_pad, K] buffer as separate tensors of this GPU: a copy holds its own
+    shard and junk elsewhere, like the symmetric buffers of a tensor-parallel group before the gather."""
+    import ctypes
+    shard = (rows + world - 1) // world
+    full = bf(shard * world, K)
+    copies = []
+    for r in range(world):
+        c = torch.full_like(full, 7.0)
+        c[r * shard:(r + 1) * shard] = full[r * shard:(r + 1) * shard]
+        copies.append(c)
+    peers = (ctypes.c_void_p * world)(*[c.data_ptr() for c in copies])
+    return full, copies, peers, shard
+
+
+@pytest.mark.parametrize("world,rank,rows,N,K,pairs", [(4, 1, 8548, 1536, 512, 4), (2, 0, 4096, 512, 1024, 2),
+                                                        (8, 7, 8256, 768, 264, 3), (4, 3, 600, 256, 128, 1)])
+def test_all_gather_gemm_one_launch(world, rank, rows, N, K, pairs):
+    """The math pairs read A out of this rank's copy while communication pairs of the same launch fill it from the
+    other copies (which here live on the same GPU); two launches in a row check the running completion count."""
+    full, copies, peers, shard = _gather_case(world, rank, rows, K)
+    W = bf(N, K)
+    ready = torch.zeros(world, dtype=torch.int32, device=DEV)
+    done = torch.zeros(world, dtype=torch.int32, device=DEV)
+    want = full[:rows].float() @ W.float().t()
+    for launch in (1, 2):
+        if launch == 2:                       # junk again in the remote shards of the own copy
+            keep = copies[rank][rank * shard:(rank + 1) * shard].clone()
+            copies[rank].fill_(-3.0)
+            copies[rank][rank * shard:(rank + 1) * shard] = keep
+        a = copies[rank][:rows]
+        out = ops.gemm_gather(a, W, peers, world, rank, shard * K * 2, ready, None, done, 2 * pairs * launch,
+                              dep_operand=1, dep_offset=0, comm_pairs=pairs)
+        check(out, want, 1e-2, f"all-gather gemm launch {launch}")
+        assert torch.equal(copies[rank], full), "the gather did not complete the own copy"
+        expect = torch.full((world,), 2 * pairs * launch, dtype=torch.int32, device=DEV)
+        expect[rank] = 0
+        assert torch.equal(done, expect)
+
+
+def test_gather_rides_along_without_dependency():
+    """dep_operand=0: the gather only shares the launch; the GEMM reads unrelated operands."""
+    full, copies, peers, shard = _gather_case(4, 2, 4096, 256)
+    A, W = bf(1000, 264), bf(520, 264)
+    ready = torch.zeros(4, dtype=torch.int32, device=DEV)
+    done = torch.zeros(4, dtype=torch.int32, device=DEV)
+    out = ops.gemm_gather(A, W, peers, 4, 2, shard * 256 * 2, ready, None, done, 4, dep_operand=0, comm_pairs=2)
+    check(out, A.float() @ W.float().t(), 1e-2, "gemm with a gather riding along")
+    assert torch.equal(copies[2], full)
+
+
+def test_all_gather_gemm_gives_up_when_a_shard_never_becomes_ready():
+    """The ready flag of the shards is never raised: the communication CTAs and then the math producers run out of
+    their bounded waits, the launch ends with the flag-timeout status, and the next launch works."""
+    full, copies, peers, shard = _gather_case(2, 0, 2048, 256)
+    W = bf(256, 256)
+    ready = torch.zeros(2, dtype=torch.int32, device=DEV)
+    done = torch.zeros(2, dtype=torch.int32, device=DEV)
+    _lib.check_status()
+    _lib.set_peer_wait_ms(200)
+    try:
+        ops.gemm_gather(copies[0][:2048], W, peers, 2, 0, shard * 256 * 2, ready, None, done, 2,
+                        dep_operand=1, comm_pairs=1, epoch_add=1)          # waits for ready[1] >= 1
+        with pytest.raises(RuntimeError, match="timed out waiting for a flag"):
+            _lib.check_status()
+        ready.fill_(1)
+        out = ops.gemm_gather(copies[0][:2048], W, peers, 2, 0, shard * 256 * 2, ready, None, done, 2,
+                              dep_operand=1, comm_pairs=1, epoch_add=1)
+        check(out, full[:2048].float() @ W.float().t(), 1e-2, "all-gather gemm after a timed-out launch")
+    finally:
+        _lib.set_peer_wait_ms(10000)
+
+
 # ------------------------------------------------------------------ bounded waits
 def test_wait_on_a_flag_nobody_sets_runs_out_and_reports():
     """A device-side wait on a peer flag that nothing ever raises gives up after its limit, leaves a status code that

@@ -53,6 +53,32 @@ def _worker(rank, world, port, out_q):
             res2_ref, _ = ref.add_rms_norm(res_ref.bfloat16().float(), pad, w.float(), 1e-6)
             torch.testing.assert_close(res2.float(), res2_ref, atol=6e-2, rtol=3e-2)
             tp.close()
+        # --- two-phase form with the gather of the normalised rows inside the projection that consumes them
+        tp = TpContext(dist.group.WORLD, D, max_rows=4096, device=dev, two_phase_rows=256, two_phase_min_size=2,
+                       fused_gather=True, gather_pairs=2)
+        assert tp.fused_gather
+        wc = (0.05 * torch.randn(384, D, generator=g)).to(dev).bfloat16()
+        proj_ref = y_ref.bfloat16().float() @ wc.float().t()
+        for it in range(3):
+            res, y = tp.add_rms_norm(x, parts[rank], w, 1e-6, defer_gather=True)
+            proj = tp.col_parallel_linear(y, wc)                  # all-gather -> GEMM in one launch
+            tp.flush()                                            # residual rows (side stream) joined
+            torch.cuda.synchronize(); _lib.check_status()
+            torch.testing.assert_close(proj.float(), proj_ref, atol=6e-2, rtol=3e-2)
+            torch.testing.assert_close(res.float(), res_ref, atol=3e-2, rtol=2e-2)
+            torch.testing.assert_close(y.float(), y_ref, atol=3e-2, rtol=2e-2)
+        res, y = tp.add_rms_norm(x, parts[rank], w, 1e-6, defer_gather=True)
+        tp.flush()                                                # nobody took the gather along: flush does it
+        torch.cuda.synchronize(); _lib.check_status()
+        torch.testing.assert_close(y.float(), y_ref, atol=3e-2, rtol=2e-2)
+        res, y = tp.add_rms_norm(x, parts[rank], w, 1e-6, defer_gather=True)
+        proj = tp.col_parallel_linear(y[:200], wc)                # fewer rows than were normalised
+        res2, _ = tp.add_rms_norm(res, parts[rank], w, 1e-6)      # chained, joins the residual gather by itself
+        torch.cuda.synchronize(); _lib.check_status()
+        torch.testing.assert_close(proj.float(), proj_ref[:200], atol=6e-2, rtol=3e-2)
+        res2_ref, _ = ref.add_rms_norm(res_ref.bfloat16().float(), pad, w.float(), 1e-6)
+        torch.testing.assert_close(res2.float(), res2_ref, atol=6e-2, rtol=3e-2)
+        tp.close()
         # --- engine: TP=2 shard against the whole model on the same GPU
         cfg = get_preset("qwen3-ksa-tiny").merge({"head_dim": 128, "num_heads": 4, "num_kv_heads": 2, "embed_dim": 512,
                                                   "summary_chunk_size": 128, "summary_sliding_chunk_num": 2,
@@ -75,13 +101,14 @@ def _worker(rank, world, port, out_q):
             return torch.stack(outs), toks
         ref_toks = None
         ref_out, ref_toks = run(full)
-        tp = TpContext(dist.group.WORLD, cfg.embed_dim, max_rows=2 * (300 + 8), device=dev)
-        model = build_tp_model(full.state_dict(), cfg, tp, device=dev, dtype=torch.bfloat16)
-        out, _ = run(model)
-        torch.cuda.synchronize(); _lib.check_status()
-        err = (out - ref_out).abs().max() / ref_out.abs().max()
-        assert err < 4e-2, float(err)
-        tp.close()
+        for kw in ({}, {"two_phase_rows": 256, "two_phase_min_size": 2, "fused_gather": True, "gather_pairs": 2}):
+            tp = TpContext(dist.group.WORLD, cfg.embed_dim, max_rows=2 * (300 + 8), device=dev, **kw)
+            model = build_tp_model(full.state_dict(), cfg, tp, device=dev, dtype=torch.bfloat16)
+            out, _ = run(model)
+            torch.cuda.synchronize(); _lib.check_status()
+            err = (out - ref_out).abs().max() / ref_out.abs().max()
+            assert err < 4e-2, (kw, float(err))
+            tp.close()
         out_q.put((rank, "ok"))
     except Exception as exc:  # report instead of leaving the parent to time out
         import traceback
