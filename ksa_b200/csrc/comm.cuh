@@ -17,7 +17,7 @@ struct GatherJob {
   const uint32_t* ready_flags;  // optional, own memory: shard r may be read once ready_flags[r] >= target
   const uint32_t* epoch_ptr;    // target = (epoch_ptr ? *epoch_ptr : 0) + epoch_add; a device-resident epoch keeps
   uint32_t epoch_add;           // a captured CUDA graph valid from step to step
-  uint32_t* done;               // optional, own memory: done[r] += 1 by every CTA once its part of shard r has landed
+  uint32_t* done;               // optional, own memory: bulk gather only, done[r] += chunks of shard r a CTA has landed
 };
 
 struct ReduceAdamwJob {
@@ -91,14 +91,19 @@ __device__ __forceinline__ bool run_gather_job(const GatherJob& j, int cta, int 
 }
 
 // ----------------------------------------------------------------------------------------------
-// The same gather driven by the copy engine of the SM instead of by load/store instructions: ONE thread per CTA
-// issues untiled bulk copies peer memory -> shared-memory ring -> own memory.  A ring of kBulkStages x 32 KB keeps
-// 160 KB in flight per CTA, which a CTA of 192 threads cannot do with register loads (12 KB), so a handful of CTAs
-// inside a tensor-core launch are enough to fill the NVLink ports.  Both addresses of every copy are 16-byte
-// aligned and every size is a multiple of 16 bytes (shard_bytes is; the chunk size is).
-constexpr int kBulkChunk = 32768;
-constexpr int kBulkStages = 5;
-constexpr int kBulkRingBytes = kBulkStages * kBulkChunk + 64;   // + the ring's mbarriers and the abort flag
+// The same gather driven by the copy engine of the SM instead of by load/store instructions, for use by ONE spare
+// thread of a CTA whose other warps do tensor-core work: untiled bulk copies peer memory -> small shared-memory ring ->
+// own memory.  A single SM copies about 40 GB/s this way (measured: 8 CTAs doing nothing else moved 320 GB/s, 12 moved
+// 440 GB/s, whatever the ring's shape), so the transfer is spread over every CTA of the launch, a few GB/s each,
+// instead of taking whole SMs away from the math.  Both addresses of every copy are 16-byte aligned and every size is
+// a multiple of 16 bytes (shard_bytes and the chunk size are).
+constexpr int kBulkChunk = 8192;
+constexpr int kBulkStages = 4;
+constexpr int kBulkRingBytes = kBulkStages * kBulkChunk + 64;   // + the ring's mbarriers and its abort flag
+
+__host__ __device__ constexpr long long bulk_chunks(long long shard_bytes) {
+  return (shard_bytes + kBulkChunk - 1) / kBulkChunk;
+}
 
 __device__ __forceinline__ void bulk_load_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -115,11 +120,13 @@ __device__ __forceinline__ void bulk_wait_read_all_but_one() {
 // writes of the copy engine (async proxy) ordered before later generic-proxy accesses and the other way round
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
-// CTA `cta` of `nctas` moves chunks cta, cta + nctas, ... of every remote shard.  `ring` is 1024-byte aligned shared
-// memory of kBulkRingBytes.  Only thread 0 works; the call returns for all threads of the CTA (the others at once).
-// Returns false if a wait gave up; nothing is left in flight either way.
+// Called by ONE thread.  CTA `cta` of `nctas` moves chunks cta, cta + nctas, ... of every remote shard through `ring`
+// (16-byte aligned shared memory of kBulkRingBytes that nobody else touches) and adds the number of chunks it moved
+// to done[r] once they are written: shard r is complete when done[r] has grown by bulk_chunks(shard_bytes).
+// Chunks are numbered in the order this CTA moves them, across shards: chunk n uses stage n % kBulkStages and the
+// (n / kBulkStages)-th phase of that stage's barrier.  Returns false if a wait gave up; nothing is left in flight
+// either way.
 __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta, int nctas, uint8_t* ring, int* status) {
-  if (threadIdx.x != 0) return true;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + kBulkStages * kBulkChunk);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kBulkStages);
   for (int s = 0; s < kBulkStages; ++s) mbar_init(&bars[s], 1);
@@ -128,8 +135,7 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
   const WaitGuard guard{abort_flag, status};
   uint8_t* dst_base = const_cast<uint8_t*>(j.peers[j.rank]);
   const uint32_t target = epoch_target(j.epoch_ptr, j.epoch_add);
-  // Chunks are numbered in the order this CTA moves them, across shards: chunk n uses stage n % kBulkStages and
-  // the (n / kBulkStages)-th phase of that stage's barrier.
+  const long long n_chunks = bulk_chunks(j.shard_bytes);
   long long issued = 0;    // loads issued
   long long stored = 0;    // stores issued
   long long freed = 0;     // stores known to have finished reading their stage
@@ -140,8 +146,8 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
     if (j.ready_flags && !flag_wait_ge(j.ready_flags + r, target, status, kTimeoutPeerFlag, true)) { ok = false; break; }
     const uint8_t* src = j.peers[r] + (long long)r * j.shard_bytes;
     uint8_t* dst = dst_base + (long long)r * j.shard_bytes;
-    const long long n_chunks = (j.shard_bytes + kBulkChunk - 1) / kBulkChunk;
     long long next_load = cta, next_store = cta;
+    uint32_t moved = 0;
     while (next_store < n_chunks) {
       while (next_load < n_chunks && issued - freed < kBulkStages) {
         const int s = (int)(issued % kBulkStages);
@@ -160,6 +166,7 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
       bulk_store_s2g(dst + off, ring + s * kBulkChunk, bytes);
       tma_store_commit();
       ++stored;
+      ++moved;
       next_store += nctas;
       bulk_wait_read_all_but_one();     // every store but the newest has read its stage: those stages may be refilled
       freed = stored - 1;
@@ -167,10 +174,10 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
     if (!ok) break;
     tma_store_wait0();                  // this CTA's part of shard r is written
     freed = stored;
-    if (j.done) {
+    if (j.done && moved) {
       fence_proxy_async_all();
       __threadfence();
-      red_release_gpu_add(j.done + r, 1u);
+      red_release_gpu_add(j.done + r, moved);
     }
   }
   if (!ok) {

@@ -5,18 +5,20 @@
 // which is what keeps the tensor pipe fed (a 128 x 256 single-CTA MMA needs more operand bytes per clock than shared
 // memory delivers).
 //
-// Roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only), warps 2..5 epilogue.
+// Roles per CTA (224 threads): warp 0 TMA producer, warp 1 MMA issuer (leader CTA only), warps 2..5 epilogue,
+// warp 6 communication (idle in a plain GEMM).
 // Barriers: `full` lives in the leader and collects the bytes of both CTAs' loads (the peer's TMA loads name the
 // leader's barrier); `empty` and `acc_full` exist in both CTAs and are signalled for both by one multicast
 // tcgen05.commit; `acc_empty` lives in the leader and collects one arrival per epilogue warp of both CTAs.
 // No TMA load here uses cluster multicast.  Every wait is bounded.
 //
-// All-gather -> GEMM in one launch (ksa_gemm2_gather_bf16): the first `comm.n_pairs` CTA pairs of the grid do no math.
-// One thread of each of their CTAs pulls the other ranks' shards of an operand out of the peers' memory with bulk
-// copies through its shared memory (run_gather_job_bulk) and counts every finished shard in `done[r]`; the TMA
-// producers of the math pairs wait (bounded) for the shards that hold the rows of their next tile, and the tile order
-// starts at this rank's own rows and follows the order in which the shards arrive.  The NVLink transfer of shard
-// r+1 therefore runs under the tensor-core tiles of shard r.
+// All-gather -> GEMM in one launch (ksa_gemm2_gather_bf16): warp 6 of every CTA is a communication warp.  One of
+// its threads pulls this CTA's share of the other ranks' shards of an operand out of the peers' memory with bulk
+// copies through a small shared-memory ring (run_gather_job_bulk) and counts the landed chunks of every shard in
+// `done[r]`; the TMA producers wait (bounded) for the shards that hold the rows of their next tile, and the tile order
+// starts at this rank's own rows and follows the order in which the shards arrive.  The NVLink transfer of shard r+1
+// therefore runs under the tensor-core tiles of shard r, and no SM is taken away from the math: one SM copies only
+// about 40 GB/s, so the transfer is spread over all 148.
 #include "comm.cuh"
 #include "host.h"
 
@@ -26,24 +28,31 @@ constexpr int k2BM = 128;          // rows of A (and of the accumulator) per CTA
 constexpr int k2BN = 256;          // accumulator columns per pair
 constexpr int k2BNh = 128;         // rows of B staged per CTA
 constexpr int k2BK = 64;
-constexpr int k2Threads = 192;
+constexpr int k2Threads = 224;      // warps 0..5 as described above, warp 6 for communication
 constexpr int k2Stages = 6;
 constexpr int k2GroupM = 8;        // pair-tile rows per scheduling group
 constexpr int k2ABytes = k2BM * k2BK * 2;
 constexpr int k2BBytes = k2BNh * k2BK * 2;
 constexpr int k2StageBytes = k2ABytes + k2BBytes;
-constexpr int k2SmemTotal = k2Stages * k2StageBytes + 256 + 1024;
+constexpr int k2BarrierBytes = 256;
+constexpr int k2SmemTotal = k2Stages * k2StageBytes + k2BarrierBytes + kBulkRingBytes + 1024;
+static_assert(k2SmemTotal <= 232448, "the operand ring, the barriers and the copy ring must fit 227 KB");
 
 struct Gemm2Epilogue {
   void* c;
   long long ldc;
   int out_fp32, accumulate;
   float alpha;
+  // GEMM -> reduce-scatter (bf16 output only): output row `row` belongs to rank row / c_shard_rows and is stored, from
+  // the epilogue, straight into that rank's memory at c_peer[owner] + (row - owner * c_shard_rows) * ldc.
+  int c_shard_rows;          // 0: every row goes to `c`
+  int c_world;
+  void* c_peer[kMaxPeers];
 };
 
-// Communication work riding in a pair-GEMM launch, and what the math pairs wait for.
+// Communication work riding in a pair-GEMM launch, and what the math waits for.
 struct Comm2Work {
-  int n_pairs;               // CTA pairs at the front of the grid that gather instead of computing (0: none)
+  int active;                // 1: warp 6 of every CTA gathers
   GatherJob gather;          // gather.done is required when dep_operand != 0
   int dep_operand;           // 0: the math does not read the gathered buffer; 1: A rows live in it; 2: B rows
   long long dep_offset;      // byte offset of the operand's row 0 inside the gathered buffer
@@ -104,15 +113,11 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
 
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(k2Threads, 1)
-gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Gemm2Epilogue ep,
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ Gemm2Epilogue ep,
                   int M, int N, int K, int* status, const __grid_constant__ Comm2Work comm) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  if ((int)(blockIdx.x >> 1) < comm.n_pairs) {
-    // communication pair: both CTAs gather on their own; no tensor memory, no cluster barrier, no pipeline barriers
-    run_gather_job_bulk(comm.gather, (int)blockIdx.x, 2 * comm.n_pairs, smem, status);
-    return;
-  }
   uint8_t* bar_base = smem + k2Stages * k2StageBytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);   // used in the leader
   uint64_t* empty = full + k2Stages;                         // both CTAs
@@ -124,7 +129,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();     // 0 = leader
   const WaitGuard guard{abort_flag, status};
-  const int pair = ((int)blockIdx.x >> 1) - comm.n_pairs, n_pairs = ((int)gridDim.x >> 1) - comm.n_pairs;
+  const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
   const int tiles_m = (M + 2 * k2BM - 1) / (2 * k2BM);
   const int tiles_n = (N + k2BN - 1) / k2BN;
   const int num_tiles = tiles_m * tiles_n;
@@ -242,6 +247,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (ok) umma2_commit_both(&acc_full[buf]);
       }
     }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------ communication warp (both CTAs, one thread)
+    if (lane == 0 && comm.active)
+      run_gather_job_bulk(comm.gather, (int)blockIdx.x, (int)gridDim.x, smem + k2Stages * k2StageBytes + k2BarrierBytes,
+                          status);
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int quad = warp & 3;
@@ -279,7 +289,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               }
             }
           } else {
-            bf16* dst = reinterpret_cast<bf16*>(ep.c) + (long long)row * ep.ldc + col0;
+            bf16* dst;
+            if (ep.c_shard_rows > 0) {
+              const int owner = min(row / ep.c_shard_rows, ep.c_world - 1);
+              dst = reinterpret_cast<bf16*>(ep.c_peer[owner]) + (long long)(row - owner * ep.c_shard_rows) * ep.ldc + col0;
+            } else {
+              dst = reinterpret_cast<bf16*>(ep.c) + (long long)row * ep.ldc + col0;
+            }
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < N) {
@@ -354,12 +370,11 @@ static int launch_gemm2(const void* a, const void* b, const Gemm2Epilogue& ep, i
     attr_set = true;
   }
   const int tiles = ((M + 2 * k2BM - 1) / (2 * k2BM)) * ((N + k2BN - 1) / k2BN);
-  int pairs = num_sms / 2 - comm.n_pairs;     // the communication pairs take their SMs out of the same single wave
-  KSA_REQUIRE(pairs >= 1, "gemm2: %d communication pairs leave no SM for the math", comm.n_pairs);
+  int pairs = num_sms / 2;
   if (tiles < pairs) pairs = tiles;
   int* status = status_word();
   KSA_REQUIRE(status != nullptr, "could not allocate the status word");
-  kern<<<2 * (pairs + comm.n_pairs), k2Threads, k2SmemTotal, stream>>>(tmA, tmB, ep, M, N, K, status, comm);
+  kern<<<2 * pairs, k2Threads, k2SmemTotal, stream>>>(tmA, tmB, ep, M, N, K, status, comm);
   KSA_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -377,7 +392,8 @@ KSA_API int ksa_gemm2_bf16(const void* a, const void* b, void* c, int M, int N, 
   KSA_REQUIRE(N % 8 == 0 && ldc % (out_fp32 ? 4 : 8) == 0, "gemm2: N and ldc must keep 16-byte row alignment");
   KSA_REQUIRE((reinterpret_cast<uintptr_t>(c) & 15) == 0, "gemm2: C must be 16-byte aligned");
   KSA_REQUIRE(!(accumulate && !out_fp32), "gemm2: accumulate needs an fp32 output");
-  Gemm2Epilogue ep{c, ldc, out_fp32, accumulate, alpha};
+  Gemm2Epilogue ep{};
+  ep.c = c; ep.ldc = ldc; ep.out_fp32 = out_fp32; ep.accumulate = accumulate; ep.alpha = alpha;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const Comm2Work none{};
   if (!a_mn_major && !b_mn_major) return launch_gemm2<false, false>(a, b, ep, M, N, K, lda, ldb, st, none);
@@ -389,18 +405,17 @@ KSA_API int ksa_gemm2_bf16(const void* a, const void* b, void* c, int M, int N, 
 // All-gather -> GEMM in one launch.  The GEMM arguments are those of ksa_gemm2_bf16; both operands K-major.
 //   peers/world/rank/shard_bytes/ready_flags/epoch_ptr/epoch_add: the gather, as in ksa_peer_gather (shard r of every
 //     rank's buffer is bytes [r*shard_bytes, (r+1)*shard_bytes); shards r != rank are pulled into peers[rank]).
-//   done: `world` uint32 counters in own memory; every launch adds 2*comm_pairs to each done[r != rank].
-//     done_target is the value that means "complete" for THIS launch (the caller keeps the running total).
+//   done: `world` uint32 counters in own memory; every launch adds ksa_gather_chunks(shard_bytes) to each
+//     done[r != rank].  done_target is the value that means "complete" for THIS launch (the caller keeps the running
+//     total).
 //   dep_operand: 1 if A (the [M, K] operand) lies inside the gathered buffer, 2 if B does, 0 if neither (the
 //     gather then only shares the launch); dep_offset: byte offset of that operand's first row in the buffer; the
 //     row pitch is lda (ldb) elements.
-//   comm_pairs: CTA pairs (of 74) that gather instead of computing.
 KSA_API int ksa_gemm2_gather_bf16(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
                                   long long ldb, long long ldc, int out_fp32, int accumulate, float alpha,
                                   const void* const* peers, int world, int rank, long long shard_bytes,
                                   const void* ready_flags, const void* epoch_ptr, unsigned epoch_add, void* done,
-                                  unsigned done_target, int dep_operand, long long dep_offset, int comm_pairs,
-                                  void* stream) {
+                                  unsigned done_target, int dep_operand, long long dep_offset, void* stream) {
   KSA_ENTER(a);
   using namespace ksa;
   KSA_REQUIRE(M > 0 && N > 0 && K > 0, "gemm2_gather: empty problem %d x %d x %d", M, N, K);
@@ -411,12 +426,12 @@ KSA_API int ksa_gemm2_gather_bf16(const void* a, const void* b, void* c, int M, 
   KSA_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, "gemm2_gather: rank %d of %d out of range", rank, world);
   KSA_REQUIRE(shard_bytes > 0 && shard_bytes % 16 == 0, "gemm2_gather: shard bytes must be a positive multiple of 16");
   KSA_REQUIRE(dep_operand >= 0 && dep_operand <= 2 && dep_offset >= 0, "gemm2_gather: bad dependency description");
-  KSA_REQUIRE(comm_pairs >= 1 && comm_pairs <= 16, "gemm2_gather: comm_pairs %d out of range", comm_pairs);
   KSA_REQUIRE(dep_operand == 0 || done != nullptr, "gemm2_gather: a dependency needs the done counters");
-  Gemm2Epilogue ep{c, ldc, out_fp32, accumulate, alpha};
+  Gemm2Epilogue ep{};
+  ep.c = c; ep.ldc = ldc; ep.out_fp32 = out_fp32; ep.accumulate = accumulate; ep.alpha = alpha;
   Comm2Work comm{};
   if (world > 1) {
-    comm.n_pairs = comm_pairs;
+    comm.active = 1;
     for (int r = 0; r < world; ++r) {
       KSA_REQUIRE(peers[r] != nullptr && (reinterpret_cast<uintptr_t>(peers[r]) & 15) == 0, "gemm2_gather: peer %d buffer missing or misaligned", r);
       comm.gather.peers[r] = static_cast<const uint8_t*>(peers[r]);
@@ -438,4 +453,29 @@ KSA_API int ksa_gemm2_gather_bf16(const void* a, const void* b, void* c, int M, 
     }
   }
   return launch_gemm2<false, false>(a, b, ep, M, N, K, lda, ldb, reinterpret_cast<cudaStream_t>(stream), comm);
+}
+
+// Number by which one ksa_gemm2_gather_bf16 launch raises every done[r != rank].
+KSA_API long long ksa_gather_chunks(long long shard_bytes) { return ksa::bulk_chunks(shard_bytes); }
+
+// GEMM -> reduce-scatter, producer side: C = A B^T (both K-major, bf16 output) whose row block r (rows
+// [r*shard_rows, (r+1)*shard_rows), the last block takes the remainder) is written by the epilogue directly into
+// rank r's memory at c_peers[r] (row pitch ldc elements) with P2P stores, so the transfer runs under the remaining
+// tiles and the reduction that follows reads only local memory.  c_peers[r] must be 16-byte aligned.
+KSA_API int ksa_gemm2_scatter_bf16(const void* a, const void* b, int M, int N, int K, long long lda, long long ldb,
+                                   long long ldc, const void* const* c_peers, int world, int shard_rows, void* stream) {
+  KSA_ENTER(a);
+  using namespace ksa;
+  KSA_REQUIRE(M > 0 && N > 0 && K > 0, "gemm2_scatter: empty problem %d x %d x %d", M, N, K);
+  KSA_REQUIRE(lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0 && N % 8 == 0, "gemm2_scatter: leading dimensions and N must be multiples of 8");
+  KSA_REQUIRE(world >= 1 && world <= kMaxPeers && shard_rows > 0, "gemm2_scatter: world %d / shard rows %d out of range", world, shard_rows);
+  KSA_REQUIRE((long long)shard_rows * world >= M, "gemm2_scatter: %d shards of %d rows do not cover %d rows", world, shard_rows, M);
+  Gemm2Epilogue ep{};
+  ep.ldc = ldc; ep.alpha = 1.f; ep.c_shard_rows = shard_rows; ep.c_world = world;
+  for (int r = 0; r < world; ++r) {
+    KSA_REQUIRE(c_peers[r] != nullptr && (reinterpret_cast<uintptr_t>(c_peers[r]) & 15) == 0, "gemm2_scatter: output of rank %d missing or misaligned", r);
+    ep.c_peer[r] = const_cast<void*>(c_peers[r]);
+  }
+  ep.c = ep.c_peer[0];
+  return launch_gemm2<false, false>(a, b, ep, M, N, K, lda, ldb, reinterpret_cast<cudaStream_t>(stream), Comm2Work{});
 }

@@ -85,9 +85,11 @@ class KsaAttention(nn.Module):
         return None if m is None else m.scale
 
 
-def _row_linear(tp, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """Row-parallel projection: with a tensor-parallel group the result is this rank's partial sum."""
-    return ops.linear(x, weight) if tp is None else tp.row_parallel_linear(x, weight)
+def _row_linear(tp, x: torch.Tensor, weight: torch.Tensor, residual_rows: Optional[int] = None) -> torch.Tensor:
+    """Row-parallel projection: with a tensor-parallel group the result is this rank's partial sum.
+    ``residual_rows``: rows of the residual stream that the ``_add_norm`` consuming the result gets (lets the group
+    scatter the rows to their owners from the GEMM; the result may then only be handed to that ``_add_norm``)."""
+    return ops.linear(x, weight) if tp is None else tp.row_parallel_linear(x, weight, residual_rows)
 
 
 def _add_norm(tp, x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -113,8 +115,8 @@ class SwiGluMlp(nn.Module):
         self.w13 = FusedLinear(dim, 2 * hidden)
         self.w2 = FusedLinear(hidden, dim)
 
-    def forward(self, x, tp=None):
-        return _row_linear(tp, ops.swiglu(_col_linear(tp, x, self.w13.weight)), self.w2.weight)
+    def forward(self, x, tp=None, residual_rows: Optional[int] = None):
+        return _row_linear(tp, ops.swiglu(_col_linear(tp, x, self.w13.weight)), self.w2.weight, residual_rows)
 
 
 class KsaDecoderLayer(nn.Module):
@@ -148,6 +150,10 @@ class KsaDecoderLayer(nn.Module):
         n_text = meta.B * meta.L
         tp = meta.tp
         summary_path = self.is_summary_layer and meta.Ns > 0
+        # rows of the residual stream, for row-parallel outputs that go straight into the next _add_norm; the last
+        # layer's MLP output is sliced by the caller first, and collected attention outputs are read as they are
+        rows_attn = x.shape[0] if collect is None else None
+        rows_mlp = x.shape[0] if self.layer_idx != cfg.num_layers - 1 else None
         # the normalised rows go straight into the column-parallel projection unless the summary rows have a norm of
         # their own
         plain = not summary_path or self.sa_norm_summary is None
@@ -188,11 +194,11 @@ class KsaDecoderLayer(nn.Module):
             else:
                 att = ops.attention_packed(qkv, meta.B, meta.L, meta.Ns, Hq, Hkv, Dh, meta.chunk, meta.n_sum,
                                            self.window_chunks)
-            attn_out = _row_linear(tp, att, a.output_proj.weight)
+            attn_out = _row_linear(tp, att, a.output_proj.weight, rows_attn)
             if collect is not None:
                 collect.append(attn_out[:n_text])
             x, h2 = _add_norm(tp, x, attn_out, self.mlp_norm.scale, cfg.norm_eps, defer=True)
-            return x, self.mlp(h2, tp)
+            return x, self.mlp(h2, tp, rows_mlp)
         # full causal attention on the text rows; summary rows (if any) pass through unchanged
         qkv = _col_linear(tp, h[:n_text], a.wqkv.weight)
         qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), meta.pos[:n_text], Hq, Hkv, Dh,
@@ -205,11 +211,11 @@ class KsaDecoderLayer(nn.Module):
             att = cp_attention_packed(qkv, meta.cp, Hq, Hkv, Dh, None, False, self.tok_window)
         else:
             att = ops.attention_packed(qkv, meta.B, meta.L, 0, Hq, Hkv, Dh, tok_window=self.tok_window)
-        attn_out = _row_linear(tp, att, a.output_proj.weight)
+        attn_out = _row_linear(tp, att, a.output_proj.weight, rows_attn)
         if collect is not None:
             collect.append(attn_out)
         x, h2 = _add_norm(tp, x, attn_out, self.mlp_norm.scale, cfg.norm_eps, defer=True)
-        return x, self.mlp(h2[:n_text], tp)
+        return x, self.mlp(h2[:n_text], tp, rows_mlp)
 
 
 class BatchMeta:

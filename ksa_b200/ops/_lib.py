@@ -25,7 +25,8 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, I, P],
     "ksa_gemm2_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, P],
     "ksa_gemm2_gather_bf16": [P, P, P, I, I, I, L, L, L, I, I, F, P, I, I, L, P, P, ctypes.c_uint, P, ctypes.c_uint, I, L,
-                              I, P],
+                              P],
+    "ksa_gemm2_scatter_bf16": [P, P, I, I, I, L, L, L, P, I, I, P],
     "ksa_gemv_bf16": [P, P, P, I, I, I, L, L, L, P],
     "ksa_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, I, P],
     "ksa_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
@@ -89,6 +90,8 @@ def load() -> ctypes.CDLL:
     lib.ksa_rmsnorm_bwd_parts.restype = I
     lib.ksa_attn_bwd_num_segments.argtypes = [I]
     lib.ksa_attn_bwd_num_segments.restype = I
+    lib.ksa_gather_chunks.argtypes = [L]
+    lib.ksa_gather_chunks.restype = L
     for name, sig in _SIGNATURES.items():
         fn = getattr(lib, name, None)
         if fn is not None:
@@ -169,6 +172,40 @@ def gemm_launched() -> None:
             cb()
 
 
+def attach_pair_gather(job: dict) -> None:
+    """Hand a parameter all-gather to the next CTA-pair GEMM of this thread that can carry it (``ops.gemm`` runs it
+    inside that launch with ``ksa_gemm2_gather_bf16``).  The caller must call ``flush_pair_gather`` before the gathered
+    data is needed, in case no such GEMM came by.
+
+    ``job``: ``peers`` (ctypes pointer array), ``world``, ``rank``, ``shard_bytes``, ``ready`` (address of the ready
+    flags), ``epoch`` (device tensor or None), ``epoch_add``, ``state`` (dict with ``done``: int32 device tensor of
+    ``world`` counters and ``total``: the running completion count), ``base`` / ``nbytes`` (this rank's copy of the
+    gathered buffer), ``min_flops`` (smallest GEMM that may carry it)."""
+    flush_pair_gather()
+    _tls.pair_gather = job
+
+
+def pair_gather_pending() -> bool:
+    return getattr(_tls, "pair_gather", None) is not None
+
+
+def peek_pair_gather() -> Optional[dict]:
+    return getattr(_tls, "pair_gather", None)
+
+
+def take_pair_gather() -> Optional[dict]:
+    job, _tls.pair_gather = getattr(_tls, "pair_gather", None), None
+    return job
+
+
+def flush_pair_gather() -> None:
+    """Run a gather that is still waiting for a GEMM as a kernel of its own, now."""
+    job = take_pair_gather()
+    if job is not None:
+        call("ksa_peer_gather", job["peers"], job["world"], job["rank"], job["shard_bytes"], 1, job["ready"],
+             job["epoch"], job["epoch_add"], 32)
+
+
 def launch_count() -> int:
     """Kernels of this library launched (or captured into a graph) so far in this process."""
     return _launch_count
@@ -201,6 +238,11 @@ def set_peer_wait_ms(ms: int) -> None:
     """Limit of device-side waits on flags written by other GPUs (current device; default 10 s, or KSA_PEER_WAIT_MS)."""
     if load().ksa_set_peer_wait_ms(int(ms)) != 0:
         raise RuntimeError("could not set the peer wait limit")
+
+
+def gather_chunks(shard_bytes: int) -> int:
+    """By how much one ``ksa_gemm2_gather_bf16`` launch raises the completion counter of every remote shard."""
+    return int(load().ksa_gather_chunks(int(shard_bytes)))
 
 
 def attn_bwd_num_segments(lq: int) -> int:

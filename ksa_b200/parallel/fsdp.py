@@ -18,6 +18,11 @@ Two communication back ends behind one engine:
     * ``overlap="gemm"``: the same device routines run as communication CTAs inside the next GEMM launch (first
       backward GEMM of the next unit for reduce + AdamW, QKV projection of the previous unit for the gather), one
       kernel doing both.  Each communication CTA then takes a whole SM away from the GEMM.
+    * ``overlap="gemm2"``: the gather of the next unit rides inside the gate/up projection of the current layer (the
+      longest forward GEMM): a communication warp in every CTA of that CTA-pair GEMM moves the peers' shards with
+      bulk copies through a small shared-memory ring while the other warps compute (``ksa_gemm2_gather_bf16``).  A unit cannot be pulled inside
+      its own first GEMM, because the RMSNorm in front of the QKV projection already reads the unit's scale vector.
+      Reduce + AdamW stays on the side stream.
     * Cross-GPU ordering uses per-(unit, rank) flags in symmetric signal pads carrying the step number; every wait
       is bounded and reports through the library's status word.
 
@@ -55,9 +60,10 @@ class _Boundary(torch.autograd.Function):
 
 class FsdpEngine(TrainEngine):
     def __init__(self, model: nn.Module, *args, world_size: int = 1, rank: int = 0, group=None, comm: Optional[str] = None,
-                 comm_ctas: int = 8, overlap: str = "stream", **kw):
+                 comm_ctas: int = 8, overlap: str = "stream", pair_gather_min_flops: float = 3e11, **kw):
         self.group = group
         self.overlap = overlap
+        self.pair_gather_min_flops = pair_gather_min_flops    # only a GEMM at least this long carries a gather
         dev = kw.get("device") or next(model.parameters()).device
         self.comm = comm or ("fused" if torch.device(dev).type == "cuda" and world_size > 1 else "collective")
         self.comm_ctas = comm_ctas
@@ -116,6 +122,10 @@ class FsdpEngine(TrainEngine):
                 if self.overlap == "gemm":
                     if nxt < len(self.units) and nxt >= 2:
                         self._attach_gather(nxt)
+                elif self.overlap == "gemm2":
+                    _lib.flush_pair_gather()              # this unit's weights, if no GEMM of the last layer took them
+                    if nxt < len(self.units) and nxt >= 2:
+                        self._attach_pair_gather(nxt)
                 else:
                     ev = self._gather_done.pop(ui, None)     # this unit's weights were pulled one unit ago
                     if ev is not None:
@@ -129,7 +139,9 @@ class FsdpEngine(TrainEngine):
 
     def _make_post_hook(self, head_ui: int):
         def hook(module, args, output):
-            if self._overlap_active and self.overlap != "gemm":
+            if self._overlap_active and self.overlap == "gemm2":
+                _lib.flush_pair_gather()
+            elif self._overlap_active and self.overlap != "gemm":
                 ev = self._gather_done.pop(head_ui, None)
                 if ev is not None:
                     torch.cuda.current_stream(self.device).wait_event(ev)
@@ -151,6 +163,20 @@ class FsdpEngine(TrainEngine):
         _lib.attach_to_next_gemm("ksa_gemm_attach_gather", (
             u.compute_ptrs, self.world_size, self.rank, shard, item,
             self.pad_weights.local_ptr(self._unit_flag_index(ui)), self.epoch, 0, self.comm_ctas))
+
+    def _attach_pair_gather(self, ui: int) -> None:
+        u = self.units[ui]
+        item = u.compute.element_size()
+        states = self.__dict__.setdefault("_pair_gather_state", {})
+        st = states.get(ui)
+        if st is None:
+            st = states[ui] = {"done": torch.zeros(self.world_size, dtype=torch.int32, device=self.device), "total": 0}
+        _lib.attach_pair_gather({
+            "peers": u.compute_ptrs, "world": self.world_size, "rank": self.rank,
+            "shard_bytes": (u.size // self.world_size) * item,
+            "ready": self.pad_weights.local_ptr(self._unit_flag_index(ui)), "epoch": self.epoch, "epoch_add": 0,
+            "state": st, "base": u.compute.data_ptr(), "nbytes": u.size * item,
+            "min_flops": self.pair_gather_min_flops})
 
     def _gather_on_side_stream(self, ui: int) -> None:
         with torch.cuda.stream(self.comm_stream):
@@ -331,6 +357,7 @@ class FsdpEngine(TrainEngine):
 
     def close(self) -> None:
         if self.comm == "fused":
+            _lib.take_pair_gather()     # a gather still waiting for a GEMM would name buffers that are freed below
             torch.cuda.synchronize(self.device)
             self.pad_grads.close()
             self.pad_weights.close()

@@ -29,13 +29,13 @@ class TpContext:
 
     def __init__(self, group, embed_dim: int, max_rows: int, device=None, dtype=torch.bfloat16,
                  two_phase_rows: int = 2048, two_phase_min_size: Optional[int] = None,
-                 fused_gather: Optional[bool] = None, gather_pairs: Optional[int] = None):
+                 fused_gather: Optional[bool] = None, push_partials: Optional[bool] = None):
         if two_phase_min_size is None:
             two_phase_min_size = int(os.environ.get("KSA_TP_TWO_PHASE_MIN", "3"))
         if fused_gather is None:
             fused_gather = os.environ.get("KSA_TP_FUSED_GATHER", "0") == "1"
-        if gather_pairs is None:
-            gather_pairs = int(os.environ.get("KSA_TP_GATHER_PAIRS", "4"))
+        if push_partials is None:
+            push_partials = os.environ.get("KSA_TP_PUSH_PARTIALS", "0") == "1"
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
@@ -49,10 +49,13 @@ class TpContext:
         self.fused_gather = False
         self._pending = None          # (data_ptr of the normalised rows, shard rows, rows) awaiting their gather
         self._res_event = None        # end of the residual gather on the side stream
+        self.push_partials = False
+        self._pushed = None           # (slot, shard rows, residual rows) of a row-parallel GEMM that scattered its rows
         if self.fused:
             from .symm import SignalPad, SymmetricBuffer
             item = torch.empty((), dtype=dtype).element_size()
-            self.slot_bytes = (max_rows * embed_dim * item + 255) // 256 * 256
+            # + size rows: the scattered layout of a slot holds size blocks of ceil(rows / size) rows
+            self.slot_bytes = ((max_rows + self.size) * embed_dim * item + 255) // 256 * 256
             self.buf = SymmetricBuffer(2 * self.slot_bytes, group, device)
             self.flags = SignalPad(self.size, group, device)
             self.flags.flags.zero_()
@@ -80,7 +83,8 @@ class TpContext:
             # All-gather -> GEMM in one launch for the normalised rows (the column-parallel projection that follows
             # reads them shard by shard as they land); the residual rows travel on a side stream meanwhile.
             self.fused_gather = bool(fused_gather) and bool(self.two_phase_rows)
-            self.gather_pairs = gather_pairs
+            # GEMM -> reduce-scatter: the row-parallel GEMM's epilogue stores every row block into its owner's slot
+            self.push_partials = bool(push_partials) and bool(self.two_phase_rows)
             if self.fused_gather:
                 self._done = torch.zeros(self.size, dtype=torch.int32, device=device)
                 self._done_total = 0
@@ -103,13 +107,32 @@ class TpContext:
             raise ValueError(f"{rows} rows exceed the tensor-parallel exchange buffer ({self.max_rows} rows)")
         return self.buf.view(self.dtype, (self.counter % 2) * self.slot_bytes, rows * self.D).view(rows, self.D)
 
-    def row_parallel_linear(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-        """Partial ``x_local @ weight_local.T``; on GPUs written into the slot the next all-reduce reads."""
+    def row_parallel_linear(self, x: torch.Tensor, weight: torch.Tensor,
+                            residual_rows: Optional[int] = None) -> torch.Tensor:
+        """Partial ``x_local @ weight_local.T``; on GPUs written into the slot the next all-reduce reads.
+
+        ``residual_rows``: rows of the residual stream that the following ``add_rms_norm`` will get.  With it the
+        two-phase form is known in advance and the GEMM can scatter its row blocks into the owners' slots
+        (``ksa_gemm2_scatter_bf16``); the returned tensor is then only a token for ``add_rms_norm``."""
         if not self.fused:
             return ops.linear(x, weight)
         self.flush()
         out = self._slot_view(x.shape[0])
-        ops.gemm(x if x.is_contiguous() else x.contiguous(), weight, out=out)
+        x = x if x.is_contiguous() else x.contiguous()
+        if (self.push_partials and residual_rows is not None and residual_rows >= self.two_phase_rows
+                and residual_rows >= x.shape[0] and weight.stride(1) == 1):
+            T, D, item = self.size, self.D, x.element_size()
+            s = self.counter % 2
+            shard = (residual_rows + T - 1) // T
+            # rank r's slot s holds T blocks of `shard` rows: block q is rank q's partial of r's rows
+            targets = (ctypes.c_void_p * T)(*[p + s * self.slot_bytes + self.rank * shard * D * item
+                                              for p in self.buf.peer_ptrs])
+            _lib.call("ksa_gemm2_scatter_bf16", x, weight, x.shape[0], weight.shape[0], x.shape[1], x.stride(0),
+                      weight.stride(0), D, targets, T, shard)
+            self._pushed = (s, shard, residual_rows)
+            return out
+        self._pushed = None
+        ops.gemm(x, weight, out=out)
         return out
 
     def add_rms_norm(self, x: torch.Tensor, partial: torch.Tensor, weight: torch.Tensor,
@@ -126,13 +149,19 @@ class TpContext:
         self.flush()
         rows_x, rows_d = x.shape[0], partial.shape[0]
         slot = self._slot_view(rows_d)
+        pushed, self._pushed = self._pushed, None
         if partial.data_ptr() != slot.data_ptr():
+            pushed = None
             slot.copy_(partial)
         x = x if x.is_contiguous() else x.contiguous()
         s = self.counter % 2
         self.counter += 1
+        if pushed is not None and (pushed[0] != s or pushed[2] != rows_x):
+            raise RuntimeError(f"the row-parallel GEMM scattered its rows for a residual of {pushed[2]} rows, "
+                               f"but add_rms_norm got {rows_x}")
         if self.two_phase_rows and rows_x >= self.two_phase_rows:
-            return self._two_phase(x, s, weight, rows_x, rows_d, eps, defer_gather and self.fused_gather)
+            return self._two_phase(x, s, weight, rows_x, rows_d, eps, defer_gather and self.fused_gather,
+                                   pushed is not None)
         res = torch.empty_like(x)
         y = torch.empty_like(x)
         _lib.call("ksa_tp_allreduce_add_rmsnorm", x, self._slot_ptrs[s], self._announce, self.flags.local_ptr(0),
@@ -140,7 +169,7 @@ class TpContext:
                   self._epoch[1:2])
         return res, y
 
-    def _two_phase(self, x, s, weight, rows_x, rows_d, eps, defer=False):
+    def _two_phase(self, x, s, weight, rows_x, rows_d, eps, defer=False, pushed=False):
         """Reduce-scatter + add + norm of this rank's rows, then gather of the peers' rows.  The results live in the
         symmetric buffers until the next call of this kind (the callers consume them before that)."""
         T, D = self.size, self.D
@@ -148,7 +177,14 @@ class TpContext:
         lo, hi = min(self.rank * shard, rows_x), min((self.rank + 1) * shard, rows_x)
         res = self.sp_buf.view(self.dtype, 0, self.rows_pad * D).view(self.rows_pad, D)
         y = self.sp_buf.view(self.dtype, self._plane_bytes, self.rows_pad * D).view(self.rows_pad, D)
-        _lib.call("ksa_tp_reduce_scatter_add_rmsnorm", x, self._slot_ptrs[s], self._announce, self.flags.local_ptr(0),
+        partials = self._slot_ptrs[s]
+        if pushed:
+            # every rank's partial of MY rows already sits in my own slot (block q from rank q): local reads only.
+            # The kernel indexes by global row, hence the bias by the first own row.
+            item = x.element_size()
+            base = self.buf.local_ptr + s * self.slot_bytes - lo * D * item
+            partials = (ctypes.c_void_p * T)(*[base + q * shard * D * item for q in range(T)])
+        _lib.call("ksa_tp_reduce_scatter_add_rmsnorm", x, partials, self._announce, self.flags.local_ptr(0),
                   T, self.rank, weight, res, y, rows_x, rows_d, D, float(eps), self._epoch[0:1], self._epoch[1:2],
                   lo, hi, self._notify)
         # the epoch was advanced by the kernel above (stream order): a peer's shard is complete once its flag reached it
@@ -196,10 +232,10 @@ class TpContext:
             return ops.linear(h, weight)
         _, shard, _ = p
         self._pending = None
-        self._done_total += 2 * self.gather_pairs
-        return ops.gemm_gather(h, weight, self._y_ptrs, self.size, self.rank, shard * self.D * h.element_size(),
-                               self.flags2.local_ptr(0), self._epoch[0:1], self._done, self._done_total,
-                               dep_operand=1, dep_offset=0, comm_pairs=self.gather_pairs, out=out)
+        shard_bytes = shard * self.D * h.element_size()
+        self._done_total += _lib.gather_chunks(shard_bytes)
+        return ops.gemm_gather(h, weight, self._y_ptrs, self.size, self.rank, shard_bytes, self.flags2.local_ptr(0),
+                               self._epoch[0:1], self._done, self._done_total, dep_operand=1, dep_offset=0, out=out)
 
     # ------------------------------------------------------------------ vocabulary-parallel head
     def gather_logits(self, local: torch.Tensor) -> torch.Tensor:

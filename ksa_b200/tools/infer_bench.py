@@ -45,6 +45,12 @@ def main(argv=None) -> None:
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--warmup-decode", type=int, default=8)
     ap.add_argument("--no-warmup-prefill", action="store_true")
+    ap.add_argument("--tp-two-phase-min", type=int, default=None,
+                    help="smallest group that uses the reduce-scatter + gather form for prefill (default 3)")
+    ap.add_argument("--tp-fused-gather", action="store_true",
+                    help="gather the normalised rows inside the projection that consumes them (one launch)")
+    ap.add_argument("--tp-push-partials", action="store_true",
+                    help="row-parallel GEMMs scatter their row blocks into the owners' memory from the epilogue")
     a = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -59,7 +65,9 @@ def main(argv=None) -> None:
         dist.init_process_group("nccl", device_id=dev)
         from ..parallel.tp import TpContext, tp_local_config
         rows = B * (L + (L // C) * S)
-        tp = TpContext(dist.group.WORLD, cfg.embed_dim, max_rows=rows, device=dev)
+        tp = TpContext(dist.group.WORLD, cfg.embed_dim, max_rows=rows, device=dev,
+                       two_phase_min_size=a.tp_two_phase_min, fused_gather=a.tp_fused_gather or None,
+                       push_partials=a.tp_push_partials or None)
         local_cfg = tp_local_config(cfg, world)
     model = _random_model(local_cfg, dev, torch.bfloat16, seed=0)   # same seed: replicated tensors agree across ranks
     if tp is not None:
@@ -93,7 +101,7 @@ def main(argv=None) -> None:
         eng.prefill(prompt)
     logits, ms_prefill = timed(lambda: eng.prefill(prompt))
     nxt = logits.argmax(-1)
-    for _ in range(a.warmup_decode):
+    for _ in range(a.warmup_decode if a.decode > 0 else 0):
         nxt = eng.decode_step(nxt).argmax(-1)
 
     def decode():
@@ -101,13 +109,18 @@ def main(argv=None) -> None:
         for _ in range(a.decode):
             t = eng.decode_step(t).argmax(-1)
         return t
-    _, ms_decode = timed(decode)
+    ms_decode = timed(decode)[1] if a.decode > 0 else None
     _lib.check_status()
     if rank == 0:
+        steps = max(a.decode, 1)
         print(json.dumps({
             "model": a.preset, "tp": world, "batch": B, "prompt_len": L, "decode_steps": a.decode, "dtype": "bf16",
+            "tp_prefill": (None if tp is None else
+                           {"two_phase": bool(tp.two_phase_rows), "fused_gather": tp.fused_gather,
+                            "push_partials": tp.push_partials}),
             "prefill_ms": ms_prefill, "prefill_tokens_per_s": B * L / (ms_prefill / 1e3),
-            "decode_ms_per_step": ms_decode / a.decode, "decode_tokens_per_s": B * a.decode / (ms_decode / 1e3),
+            "decode_ms_per_step": None if ms_decode is None else ms_decode / steps,
+            "decode_tokens_per_s": None if ms_decode is None else B * a.decode / (ms_decode / 1e3),
             "kv_cache_gb_per_gpu": eng.cache_bytes() / 1e9, "data": "uniform random prompt, random-init weights"}),
             flush=True)
     if tp is not None:

@@ -262,8 +262,8 @@ def bench_comm(a) -> None:
 def bench_ag_gemm(a) -> None:
     """All-gather -> GEMM: a row-sharded ``[m, k]`` activation (every rank holds ``m / world`` rows) times a local
     ``[n, k]`` weight, as tensor-parallel prefill runs it.  Compares the stand-alone gather kernel followed by the
-    CTA-pair GEMM with the single launch in which ``--comm-pairs`` CTA pairs pull the peers' rows with bulk copies
-    while the other pairs compute on the rows that have landed.
+    CTA-pair GEMM with the single launch in which a communication warp of every CTA pulls the peers' rows with bulk
+    copies while the other warps compute on the rows that have landed.
 
     Under ``torch.distributed.run`` the peers are GPUs (maximum over ranks; roofline = the slower of the FLOPs at the
     measured GEMM peak and the remote bytes at the measured 770 GB/s peer-copy bandwidth).  Started as one process the
@@ -302,9 +302,9 @@ def bench_ag_gemm(a) -> None:
         ops.gemm(own[:M], W, out=out, pair=True)
 
     def fused():
-        total[0] += 2 * a.comm_pairs
+        total[0] += _lib.gather_chunks(shard * K * 2)
         ops.gemm_gather(own[:M], W, ptrs, world, rank, shard * K * 2, None, None, done, total[0], dep_operand=1,
-                        comm_pairs=a.comm_pairs, out=out)
+                        out=out)
 
     def timed(fn):
         if multi:
@@ -325,7 +325,7 @@ def bench_ag_gemm(a) -> None:
         t_math, t_link = flops / (pk["tflops"] * 1e9), remote / (770.0 * 1e6)
         where = "GPUs" if multi else "local buffers"
         print(f"all-gather -> gemm {M}x{N}x{K}, world {world} ({where}): gather kernel + pair GEMM {t_sep:.4f} ms | "
-              f"one launch with {a.comm_pairs} communication pairs {t_fused:.4f} ms ({t_sep / t_fused:.2f}x)", flush=True)
+              f"one launch {t_fused:.4f} ms ({t_sep / t_fused:.2f}x)", flush=True)
         print(f"  roofline: math {t_math:.4f} ms at {pk['src']} {pk['tflops']:.0f} TFLOP/s, link {t_link:.4f} ms at measured "
               f"770 GB/s -> {max(t_math, t_link) / t_fused:.2f} of the slower one; max rel error {err:.2e}", flush=True)
     if multi:
@@ -378,7 +378,6 @@ def main(argv=None) -> None:
     ap.add_argument("--mbytes", type=int, default=256, help="comm: size of the fp32 gradient unit in MiB")
     ap.add_argument("--ctas", type=int, default=64, help="comm: CTAs of the communication kernels")
     ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"])
-    ap.add_argument("--comm-pairs", type=int, default=4, help="ag-gemm: CTA pairs that gather instead of computing")
     a = ap.parse_args(argv)
     {"gemm": bench_gemm, "gemv": bench_gemv, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn, "comm": bench_comm, "tp-reduce": bench_tp_reduce,
      "ag-gemm": bench_ag_gemm}[a.what](a)

@@ -57,6 +57,8 @@ def get_argument_parser() -> argparse.ArgumentParser:
     a("--reshard-after-forward", action="store_true")
     a("--prefetch-params-in-forward", action="store_true")
     a("--comm", default=None, choices=["fused", "collective"], help="FSDP back end (default: fused on GPUs)")
+    a("--overlap", default="stream", choices=["stream", "gemm", "gemm2"],
+      help="fused back end: communication kernels on a side stream, or inside GEMM launches")
     a("--no-cuda-graph", action="store_true")
     # optimisation
     a("--lr-scheduler-type", default="wsd", choices=["cosine", "cosine_v2", "wsd", "constant"])
@@ -198,7 +200,7 @@ def train(args) -> dict:
                   clip_value=args.clip_range, lr_lambda=lr_lambda, grad_accum_steps=args.gradient_accumulation_steps)
     if world > 1:
         from ksa_b200.parallel.fsdp import FsdpEngine
-        engine = FsdpEngine(model, world_size=world, rank=rank, comm=args.comm, **common)
+        engine = FsdpEngine(model, world_size=world, rank=rank, comm=args.comm, overlap=args.overlap, **common)
     else:
         from ksa_b200.training.engine import TrainEngine
         engine = TrainEngine(model, **common)

@@ -146,17 +146,17 @@ def test_one_slot_would_not_be_enough():
 
 
 # ---------------------------------------------------------------------------------------------------------------------
-# All-gather -> GEMM in one launch (ksa_b200/csrc/gemm2.cu + run_gather_job_bulk in comm.cuh): communication CTAs copy
-# the remote shards chunk by chunk and add 1 to done[shard] when their part of a shard is written; the producers of the
-# math CTAs walk the tile rows starting at the first row block that lies entirely in the rank's own shard and wait for
-# done[s] >= target for every shard s that a row block touches.
+# All-gather -> GEMM in one launch (ksa_b200/csrc/gemm2.cu + run_gather_job_bulk in comm.cuh): the communication warps
+# copy the remote shards chunk by chunk and add the number of chunks they moved to done[shard] once those are written;
+# the TMA producers walk the tile rows starting at the first row block that lies entirely in the rank's own shard and
+# wait until done[s] has grown by the shard's chunk count for every shard s that a row block touches.
 def _ag_gemm_roles(world, rank, rows, shard_rows, tile_rows, n_comm, n_math, ring, landed, done, status, reads,
                    ready=True):
-    target = n_comm
+    chunk = 3                                             # rows per bulk copy
+    target = (shard_rows + chunk - 1) // chunk            # chunks of one shard
     tiles_m = (rows + tile_rows - 1) // tile_rows
     first_row = rank * shard_rows
     rotate = ((first_row + tile_rows - 1) // tile_rows) % tiles_m if 0 < first_row < rows else 0
-    chunk = 3                                             # rows per bulk copy
 
     def comm_cta(cta):
         for step in range(1, world):
@@ -164,7 +164,9 @@ def _ag_gemm_roles(world, rank, rows, shard_rows, tile_rows, n_comm, n_math, rin
             yield from wait_ge(lambda: 1 if ready else 0, 1, status, 0)       # the shard's ready flag
             n_chunks = (shard_rows + chunk - 1) // chunk
             inflight = []
+            moved = 0
             for c in range(cta, n_chunks, n_comm):
+                moved += 1
                 while len(inflight) >= ring:                                   # a stage frees when its store was read
                     landed[r].update(inflight.pop(0))
                     yield
@@ -173,7 +175,7 @@ def _ag_gemm_roles(world, rank, rows, shard_rows, tile_rows, n_comm, n_math, rin
             for rows_ in inflight:                                             # wait_group 0: everything is written
                 landed[r].update(rows_)
                 yield
-            done[r] += 1
+            done[r] += moved
             yield
 
     def math_pair(pair):

@@ -50,13 +50,14 @@ def _worker(rank, world, port, out_q):
         results = {}
         g = torch.Generator().manual_seed(11)
         data = torch.randint(0, cfg.vocab_size, (3, world, 2, 513), generator=g)
-        for comm, overlap in (("collective", "stream"), ("fused", "stream"), ("fused", "gemm")):
+        for comm, overlap in (("collective", "stream"), ("fused", "stream"), ("fused", "gemm"), ("fused", "gemm2")):
             torch.manual_seed(0)
             model = get_model_class(cfg.model_class)(cfg)
             model.init_weights(seed=0)
             model = model.to(dev).to(torch.bfloat16)
+            # gemm2: every GEMM of the tiny model may carry the gather of the next unit
             eng = FsdpEngine(model, lr=1e-3, weight_decay=0.1, clip_value=1.0, world_size=world, rank=rank, comm=comm,
-                             overlap=overlap)
+                             overlap=overlap, pair_gather_min_flops=0.0)
             losses = []
             for s in range(3):
                 x = data[s, rank].to(dev)
@@ -71,7 +72,7 @@ def _worker(rank, world, port, out_q):
             if comm == "fused":
                 eng.close()
         lc, wc, gc = results[("collective", "stream")]
-        for key in (("fused", "stream"), ("fused", "gemm")):
+        for key in (("fused", "stream"), ("fused", "gemm"), ("fused", "gemm2")):
             lf, wf, gf = results[key]
             assert all(abs(a - b) < 3e-2 for a, b in zip(lc, lf)), (key, lc, lf)
             assert abs(gc - gf) < 0.05 * gc, (key, gc, gf)

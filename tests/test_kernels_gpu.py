@@ -337,27 +337,28 @@ def _gather_case(world, rank, rows, K):
     return full, copies, peers, shard
 
 
-@pytest.mark.parametrize("world,rank,rows,N,K,pairs", [(4, 1, 8548, 1536, 512, 4), (2, 0, 4096, 512, 1024, 2),
-                                                        (8, 7, 8256, 768, 264, 3), (4, 3, 600, 256, 128, 1)])
-def test_all_gather_gemm_one_launch(world, rank, rows, N, K, pairs):
-    """The math pairs read A out of this rank's copy while communication pairs of the same launch fill it from the
+@pytest.mark.parametrize("world,rank,rows,N,K", [(4, 1, 8548, 1536, 512), (2, 0, 4096, 512, 1024),
+                                                  (8, 7, 8256, 768, 264), (4, 3, 600, 256, 128)])
+def test_all_gather_gemm_one_launch(world, rank, rows, N, K):
+    """The math warps read A out of this rank's copy while the communication warps of the same launch fill it from the
     other copies (which here live on the same GPU); two launches in a row check the running completion count."""
     full, copies, peers, shard = _gather_case(world, rank, rows, K)
     W = bf(N, K)
     ready = torch.zeros(world, dtype=torch.int32, device=DEV)
     done = torch.zeros(world, dtype=torch.int32, device=DEV)
     want = full[:rows].float() @ W.float().t()
+    per_launch = _lib.gather_chunks(shard * K * 2)
     for launch in (1, 2):
         if launch == 2:                       # junk again in the remote shards of the own copy
             keep = copies[rank][rank * shard:(rank + 1) * shard].clone()
             copies[rank].fill_(-3.0)
             copies[rank][rank * shard:(rank + 1) * shard] = keep
         a = copies[rank][:rows]
-        out = ops.gemm_gather(a, W, peers, world, rank, shard * K * 2, ready, None, done, 2 * pairs * launch,
-                              dep_operand=1, dep_offset=0, comm_pairs=pairs)
+        out = ops.gemm_gather(a, W, peers, world, rank, shard * K * 2, ready, None, done, per_launch * launch,
+                              dep_operand=1, dep_offset=0)
         check(out, want, 1e-2, f"all-gather gemm launch {launch}")
         assert torch.equal(copies[rank], full), "the gather did not complete the own copy"
-        expect = torch.full((world,), 2 * pairs * launch, dtype=torch.int32, device=DEV)
+        expect = torch.full((world,), per_launch * launch, dtype=torch.int32, device=DEV)
         expect[rank] = 0
         assert torch.equal(done, expect)
 
@@ -368,7 +369,7 @@ def test_gather_rides_along_without_dependency():
     A, W = bf(1000, 264), bf(520, 264)
     ready = torch.zeros(4, dtype=torch.int32, device=DEV)
     done = torch.zeros(4, dtype=torch.int32, device=DEV)
-    out = ops.gemm_gather(A, W, peers, 4, 2, shard * 256 * 2, ready, None, done, 4, dep_operand=0, comm_pairs=2)
+    out = ops.gemm_gather(A, W, peers, 4, 2, shard * 256 * 2, ready, None, done, 0, dep_operand=0)
     check(out, A.float() @ W.float().t(), 1e-2, "gemm with a gather riding along")
     assert torch.equal(copies[2], full)
 
@@ -383,16 +384,34 @@ def test_all_gather_gemm_gives_up_when_a_shard_never_becomes_ready():
     _lib.check_status()
     _lib.set_peer_wait_ms(200)
     try:
-        ops.gemm_gather(copies[0][:2048], W, peers, 2, 0, shard * 256 * 2, ready, None, done, 2,
-                        dep_operand=1, comm_pairs=1, epoch_add=1)          # waits for ready[1] >= 1
+        target = _lib.gather_chunks(shard * 256 * 2)
+        ops.gemm_gather(copies[0][:2048], W, peers, 2, 0, shard * 256 * 2, ready, None, done, target,
+                        dep_operand=1, epoch_add=1)                        # waits for ready[1] >= 1
         with pytest.raises(RuntimeError, match="timed out waiting for a flag"):
             _lib.check_status()
         ready.fill_(1)
-        out = ops.gemm_gather(copies[0][:2048], W, peers, 2, 0, shard * 256 * 2, ready, None, done, 2,
-                              dep_operand=1, comm_pairs=1, epoch_add=1)
+        out = ops.gemm_gather(copies[0][:2048], W, peers, 2, 0, shard * 256 * 2, ready, None, done, target,
+                              dep_operand=1, epoch_add=1)
         check(out, full[:2048].float() @ W.float().t(), 1e-2, "all-gather gemm after a timed-out launch")
     finally:
         _lib.set_peer_wait_ms(10000)
+
+
+@pytest.mark.parametrize("world,M,N,K,shard", [(4, 1000, 512, 264, 260), (2, 4096, 2560, 512, 2048), (8, 8256, 256, 128, 1056)])
+def test_gemm_scatters_row_blocks_to_their_owners(world, M, N, K, shard):
+    """GEMM -> reduce-scatter, producer side: row block r of the product lands in the r-th output buffer (here all
+    on one GPU), whatever the alignment of the block boundaries to the 128-row tiles."""
+    import ctypes
+    A, W = bf(M, K), bf(N, K)
+    outs = [torch.full((shard, N), 9.0, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[o.data_ptr() for o in outs])
+    _lib.call("ksa_gemm2_scatter_bf16", A, W, M, N, K, A.stride(0), W.stride(0), N, ptrs, world, shard)
+    want = A.float() @ W.float().t()
+    for r in range(world):
+        lo, hi = min(r * shard, M), min((r + 1) * shard, M)
+        if hi > lo:
+            check(outs[r][:hi - lo], want[lo:hi], 1e-2, f"row block {r}")
+        assert (outs[r][hi - lo:] == 9.0).all(), "rows beyond the block were written"
 
 
 # ------------------------------------------------------------------ bounded waits

@@ -176,3 +176,80 @@ def test_model_detects_a_missing_phase_flip():
             empty, full = [MBar(1) for _ in range(2)], [MBar(1) for _ in range(2)]
             smem = [None, None]
             run([producer(), consumer()], rng, limit=5000)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# The shared-memory ring of the communication warp (run_gather_job_bulk in ksa_b200/csrc/comm.cuh): ONE thread issues
+# bulk loads into stage n % S while fewer than S chunks are between "load issued" and "store has read its stage",
+# waits for the oldest load, issues its bulk store, and then waits until every store but the newest has read its
+# stage (wait_group.read 1); at the end of a shard it waits for all stores (wait_group 0).
+def _ring_thread(S, shards, rng, state, forget_store_wait=False):
+    full = [MBar(1) for _ in range(S)]
+    ring = [None] * S                 # chunk a stage holds (None: free)
+    loads, stores = [], []            # copies in flight
+    out = state["out"]
+
+    def thread():
+        issued = stored = freed = 0
+        for shard, chunks in enumerate(shards):
+            next_load = next_store = 0
+            while next_store < chunks:
+                while next_load < chunks and issued - freed < S:
+                    s = issued % S
+                    assert ring[s] is None and all(st != s for st, _ in stores), \
+                        "a stage was refilled while a store still reads it"
+                    full[s].arrive(expect_tx=1)
+                    loads.append((s, (shard, next_load)))
+                    issued += 1
+                    next_load += 1
+                    yield
+                s = stored % S
+                yield from wait(full[s], (stored // S) & 1)
+                assert ring[s] == (shard, next_store), "a store read a stage before its load had landed"
+                stores.append((s, (shard, next_store)))
+                stored += 1
+                next_store += 1
+                if not forget_store_wait:
+                    while len(stores) > 1:                 # wait_group.read 1
+                        yield
+                freed = stored - 1
+                yield
+            while stores:                                  # wait_group 0 at the end of a shard
+                yield
+            freed = stored
+            state["done"].append(shard)
+        state["stop"] = True
+
+    def engine():
+        while not state["stop"]:
+            if loads and (not stores or rng.random() < 0.5):
+                s, what = loads.pop(rng.randrange(len(loads)))
+                ring[s] = what
+                full[s].complete_tx(1)
+            elif stores:
+                s, what = stores.pop(0)                    # stores of one thread complete in order
+                out.append(what)
+                ring[s] = None
+            yield
+
+    return thread(), engine()
+
+
+@pytest.mark.parametrize("S", [4, 2, 3, 8])
+def test_bulk_ring_protocol(S):
+    shards = [7, 1, 0, 13]
+    for seed in range(25):
+        rng = random.Random(seed)
+        state = {"out": [], "done": [], "stop": False}
+        run(list(_ring_thread(S, shards, rng, state)), rng)
+        assert state["out"] == [(sh, c) for sh, n in enumerate(shards) for c in range(n)]
+        assert state["done"] == list(range(len(shards)))
+
+
+def test_bulk_ring_model_catches_a_missing_store_wait():
+    """Not vacuous: without the wait for the older stores a stage is refilled while the copy engine still reads it."""
+    with pytest.raises(AssertionError, match="refilled|before its load"):
+        for seed in range(40):
+            rng = random.Random(seed)
+            state = {"out": [], "done": [], "stop": False}
+            run(list(_ring_thread(2, [9, 9], rng, state, forget_store_wait=True)), rng)

@@ -55,7 +55,7 @@ def _worker(rank, world, port, out_q):
             tp.close()
         # --- two-phase form with the gather of the normalised rows inside the projection that consumes them
         tp = TpContext(dist.group.WORLD, D, max_rows=4096, device=dev, two_phase_rows=256, two_phase_min_size=2,
-                       fused_gather=True, gather_pairs=2)
+                       fused_gather=True)
         assert tp.fused_gather
         wc = (0.05 * torch.randn(384, D, generator=g)).to(dev).bfloat16()
         proj_ref = y_ref.bfloat16().float() @ wc.float().t()
@@ -79,6 +79,29 @@ def _worker(rank, world, port, out_q):
         res2_ref, _ = ref.add_rms_norm(res_ref.bfloat16().float(), pad, w.float(), 1e-6)
         torch.testing.assert_close(res2.float(), res2_ref, atol=6e-2, rtol=3e-2)
         tp.close()
+        # --- GEMM -> reduce-scatter: the row-parallel GEMM scatters its row blocks into the owners' slots
+        acts = [torch.randn(rows_d, 256, generator=g).to(dev).bfloat16() for _ in range(world)]
+        wrs = [(0.05 * torch.randn(D, 256, generator=g)).to(dev).bfloat16() for _ in range(world)]
+        total2 = sum((acts[r].float() @ wrs[r].float().t()).bfloat16().float() for r in range(world))
+        pad2 = torch.cat([total2, total2.new_zeros(rows_x - rows_d, D)])
+        res_ref2, y_ref2 = ref.add_rms_norm(x.float(), pad2, w.float(), 1e-6)
+        for fused in (False, True):
+            tp = TpContext(dist.group.WORLD, D, max_rows=4096, device=dev, two_phase_rows=256, two_phase_min_size=2,
+                           push_partials=True, fused_gather=fused)
+            assert tp.push_partials
+            for it in range(3):
+                token = tp.row_parallel_linear(acts[rank], wrs[rank], residual_rows=rows_x)
+                res, y = tp.add_rms_norm(x, token, w, 1e-6, defer_gather=fused)
+                tp.flush()
+                torch.cuda.synchronize(); _lib.check_status()
+                torch.testing.assert_close(res.float(), res_ref2, atol=4e-2, rtol=2e-2)
+                torch.testing.assert_close(y.float(), y_ref2, atol=4e-2, rtol=2e-2)
+            # without the hint the same object falls back to the pulled layout
+            partial = tp.row_parallel_linear(acts[rank], wrs[rank])
+            res, y = tp.add_rms_norm(x, partial, w, 1e-6)
+            torch.cuda.synchronize(); _lib.check_status()
+            torch.testing.assert_close(res.float(), res_ref2, atol=4e-2, rtol=2e-2)
+            tp.close()
         # --- engine: TP=2 shard against the whole model on the same GPU
         cfg = get_preset("qwen3-ksa-tiny").merge({"head_dim": 128, "num_heads": 4, "num_kv_heads": 2, "embed_dim": 512,
                                                   "summary_chunk_size": 128, "summary_sliding_chunk_num": 2,
@@ -101,7 +124,9 @@ def _worker(rank, world, port, out_q):
             return torch.stack(outs), toks
         ref_toks = None
         ref_out, ref_toks = run(full)
-        for kw in ({}, {"two_phase_rows": 256, "two_phase_min_size": 2, "fused_gather": True, "gather_pairs": 2}):
+        for kw in ({}, {"two_phase_rows": 256, "two_phase_min_size": 2, "fused_gather": True},
+                   {"two_phase_rows": 256, "two_phase_min_size": 2, "fused_gather": True,
+                    "push_partials": True}):
             tp = TpContext(dist.group.WORLD, cfg.embed_dim, max_rows=2 * (300 + 8), device=dev, **kw)
             model = build_tp_model(full.state_dict(), cfg, tp, device=dev, dtype=torch.bfloat16)
             out, _ = run(model)
