@@ -33,7 +33,7 @@ class TpContext:
         if two_phase_min_size is None:
             two_phase_min_size = int(os.environ.get("KSA_TP_TWO_PHASE_MIN", "3"))
         if fused_gather is None:
-            fused_gather = os.environ.get("KSA_TP_FUSED_GATHER", "0") == "1"
+            fused_gather = os.environ.get("KSA_TP_FUSED_GATHER", "1") == "1"
         if push_partials is None:
             push_partials = os.environ.get("KSA_TP_PUSH_PARTIALS", "0") == "1"
         self.group = group

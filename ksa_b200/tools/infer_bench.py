@@ -47,8 +47,9 @@ def main(argv=None) -> None:
     ap.add_argument("--no-warmup-prefill", action="store_true")
     ap.add_argument("--tp-two-phase-min", type=int, default=None,
                     help="smallest group that uses the reduce-scatter + gather form for prefill (default 3)")
-    ap.add_argument("--tp-fused-gather", action="store_true",
-                    help="gather the normalised rows inside the projection that consumes them (one launch)")
+    ap.add_argument("--tp-separate-gather", action="store_true",
+                    help="gather the normalised rows with kernels of their own instead of inside the projection "
+                         "that consumes them (for A/B runs)")
     ap.add_argument("--tp-push-partials", action="store_true",
                     help="row-parallel GEMMs scatter their row blocks into the owners' memory from the epilogue")
     a = ap.parse_args(argv)
@@ -66,7 +67,7 @@ def main(argv=None) -> None:
         from ..parallel.tp import TpContext, tp_local_config
         rows = B * (L + (L // C) * S)
         tp = TpContext(dist.group.WORLD, cfg.embed_dim, max_rows=rows, device=dev,
-                       two_phase_min_size=a.tp_two_phase_min, fused_gather=a.tp_fused_gather or None,
+                       two_phase_min_size=a.tp_two_phase_min, fused_gather=False if a.tp_separate_gather else None,
                        push_partials=a.tp_push_partials or None)
         local_cfg = tp_local_config(cfg, world)
     model = _random_model(local_cfg, dev, torch.bfloat16, seed=0)   # same seed: replicated tensors agree across ranks

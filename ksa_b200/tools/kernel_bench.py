@@ -9,7 +9,7 @@
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m ksa_b200.tools.kernel_bench comm
     python -m ksa_b200.tools.kernel_bench comm --world 2      # the same kernels over buffers of one GPU
     python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 -m ksa_b200.tools.kernel_bench \
-        ag-gemm --m 33024 --n 1536 --k 2560          # all-gather -> GEMM in one launch vs gather kernel + GEMM
+        ag-gemm --gemm-m 33024 --gemm-n 1536 --gemm-k 2560   # all-gather -> GEMM in one launch vs gather kernel + GEMM
 
 Each line reports the median time, the achieved TFLOP/s or GB/s and, when ``MEASURED_PEAKS.json`` sits at the
 repository root, the fraction of the measured peak (cuBLAS bf16 burst / STREAM-style copy).  ``--iters 1 --warmup 1
@@ -361,8 +361,10 @@ def bench_tp_reduce(a) -> None:
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn", "comm", "tp-reduce", "ag-gemm"])
-    ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=4096)
-    ap.add_argument("--k", type=int, default=2048)
+    # the long spellings are for use under torch.distributed.run, whose own parser claims --m and --n as prefixes
+    ap.add_argument("--m", "--gemm-m", dest="m", type=int, default=8192)
+    ap.add_argument("--n", "--gemm-n", dest="n", type=int, default=4096)
+    ap.add_argument("--k", "--gemm-k", dest="k", type=int, default=2048)
     ap.add_argument("--a-mn", action="store_true"); ap.add_argument("--b-mn", action="store_true")
     ap.add_argument("--fp32-out", action="store_true"); ap.add_argument("--compare", action="store_true")
     ap.add_argument("--pair", action="store_true", help="gemm: run on CTA pairs (tcgen05 cta_group::2)")
