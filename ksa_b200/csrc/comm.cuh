@@ -17,7 +17,8 @@ struct GatherJob {
   const uint32_t* ready_flags;  // optional, own memory: shard r may be read once ready_flags[r] >= target
   const uint32_t* epoch_ptr;    // target = (epoch_ptr ? *epoch_ptr : 0) + epoch_add; a device-resident epoch keeps
   uint32_t epoch_add;           // a captured CUDA graph valid from step to step
-  uint32_t* done;               // optional, own memory: bulk gather only, done[r] += chunks of shard r a CTA has landed
+  uint32_t* done;               // optional, own memory: bulk gather only, kMaxPeers x kBulkSegs counters (zero at
+                                // launch): done[r * kBulkSegs + g] += chunks of segment g of shard r that have landed
 };
 
 struct ReduceAdamwJob {
@@ -101,8 +102,23 @@ constexpr int kBulkChunk = 8192;
 constexpr int kBulkStages = 4;
 constexpr int kBulkRingBytes = kBulkStages * kBulkChunk + 64;   // + the ring's mbarriers and its abort flag
 
+// A shard is moved and reported in kBulkSegs segments of (almost) equal numbers of chunks, so that a consumer of the
+// first rows of a shard does not wait for its last ones.
+constexpr int kBulkSegs = 4;
+
 __host__ __device__ constexpr long long bulk_chunks(long long shard_bytes) {
   return (shard_bytes + kBulkChunk - 1) / kBulkChunk;
+}
+// first chunk of segment g (g = kBulkSegs gives the number of chunks)
+__host__ __device__ constexpr long long bulk_seg_begin(long long n_chunks, int g) {
+  return (n_chunks * g + kBulkSegs - 1) / kBulkSegs;
+}
+// segment that chunk c belongs to: the largest g with bulk_seg_begin(g) <= c
+__host__ __device__ constexpr int bulk_seg_of(long long n_chunks, long long c) {
+  int g = (int)(c * kBulkSegs / n_chunks);
+  while (g + 1 < kBulkSegs && bulk_seg_begin(n_chunks, g + 1) <= c) ++g;
+  while (g > 0 && bulk_seg_begin(n_chunks, g) > c) --g;
+  return g;
 }
 
 __device__ __forceinline__ void bulk_load_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -121,8 +137,9 @@ __device__ __forceinline__ void bulk_wait_read_all_but_one() {
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // Called by ONE thread.  CTA `cta` of `nctas` moves chunks cta, cta + nctas, ... of every remote shard through `ring`
-// (16-byte aligned shared memory of kBulkRingBytes that nobody else touches) and adds the number of chunks it moved
-// to done[r] once they are written: shard r is complete when done[r] has grown by bulk_chunks(shard_bytes).
+// (16-byte aligned shared memory of kBulkRingBytes that nobody else touches) and, whenever it leaves a segment of a
+// shard, adds the number of chunks of that segment it has written to done[r * kBulkSegs + segment]: the segment is
+// complete when the counter has reached bulk_seg_begin(n, g + 1) - bulk_seg_begin(n, g).
 // Chunks are numbered in the order this CTA moves them, across shards: chunk n uses stage n % kBulkStages and the
 // (n / kBulkStages)-th phase of that stage's barrier.  Returns false if a wait gave up; nothing is left in flight
 // either way.
@@ -147,7 +164,8 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
     const uint8_t* src = j.peers[r] + (long long)r * j.shard_bytes;
     uint8_t* dst = dst_base + (long long)r * j.shard_bytes;
     long long next_load = cta, next_store = cta;
-    uint32_t moved = 0;
+    uint32_t moved = 0;                                   // chunks of segment `seg` stored by this CTA
+    int seg = next_store < n_chunks ? bulk_seg_of(n_chunks, next_store) : 0;
     while (next_store < n_chunks) {
       while (next_load < n_chunks && issued - freed < kBulkStages) {
         const int s = (int)(issued % kBulkStages);
@@ -168,17 +186,23 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
       ++stored;
       ++moved;
       next_store += nctas;
-      bulk_wait_read_all_but_one();     // every store but the newest has read its stage: those stages may be refilled
-      freed = stored - 1;
+      const bool leaves = next_store >= n_chunks || next_store >= bulk_seg_begin(n_chunks, seg + 1);
+      if (!leaves) {
+        bulk_wait_read_all_but_one();   // every store but the newest has read its stage: those stages may be refilled
+        freed = stored - 1;
+      } else {
+        tma_store_wait0();              // this CTA's part of the segment is written: report it
+        freed = stored;
+        if (j.done) {
+          fence_proxy_async_all();
+          __threadfence();
+          red_release_gpu_add(j.done + r * kBulkSegs + seg, moved);
+        }
+        moved = 0;
+        if (next_store < n_chunks) seg = bulk_seg_of(n_chunks, next_store);
+      }
     }
     if (!ok) break;
-    tma_store_wait0();                  // this CTA's part of shard r is written
-    freed = stored;
-    if (j.done && moved) {
-      fence_proxy_async_all();
-      __threadfence();
-      red_release_gpu_add(j.done + r, moved);
-    }
   }
   if (!ok) {
     // give loads that are still in flight a bounded time to land (their destination is this CTA's shared memory)

@@ -36,6 +36,7 @@ constexpr int k2BBytes = k2BNh * k2BK * 2;
 constexpr int k2StageBytes = k2ABytes + k2BBytes;
 constexpr int k2BarrierBytes = 256;
 constexpr int k2SmemTotal = k2Stages * k2StageBytes + k2BarrierBytes + kBulkRingBytes + 1024;
+static_assert(kMaxPeers * kBulkSegs <= 32, "one bit per segment in the producers' bookkeeping");
 static_assert(k2SmemTotal <= 232448, "the operand ring, the barriers and the copy ring must fit 227 KB");
 
 struct Gemm2Epilogue {
@@ -57,7 +58,6 @@ struct Comm2Work {
   int dep_operand;           // 0: the math does not read the gathered buffer; 1: A rows live in it; 2: B rows
   long long dep_offset;      // byte offset of the operand's row 0 inside the gathered buffer
   long long dep_row_bytes;   // bytes from one operand row to the next
-  uint32_t dep_target;       // shard r is complete once done[r] >= dep_target
   int m_rotate;              // pair-tile row that is worked on first
 };
 
@@ -166,7 +166,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t shards_seen = 0;
+      uint32_t segs_seen = 0;       // kMaxPeers x kBulkSegs = 32 segments
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
         int mb, nb;
@@ -175,23 +175,34 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int row0 = mb * 2 * k2BM + (int)rank * k2BM;      // this CTA's rows of A
         const int col0 = nb * k2BN + (int)rank * k2BNh;         // this CTA's rows of B
         if (comm.dep_operand != 0) {
-          // the rows of this tile that live in the gathered buffer: wait for the shards that hold them
+          // the rows of this tile that live in the gathered buffer: wait for the segments of the shards that hold them
           const long long r_lo = comm.dep_operand == 1 ? row0 : col0;
           const long long r_end = comm.dep_operand == 1 ? min(row0 + k2BM, M) : min(col0 + k2BNh, N);
           if (r_lo < r_end) {
-            const int s_lo = (int)((comm.dep_offset + r_lo * comm.dep_row_bytes) / comm.gather.shard_bytes);
-            const int s_hi = min((int)((comm.dep_offset + r_end * comm.dep_row_bytes - 1) / comm.gather.shard_bytes),
-                                 comm.gather.world - 1);
-            for (int s = max(s_lo, 0); s <= s_hi && ok; ++s) {
-              if (s == comm.gather.rank || ((shards_seen >> s) & 1u)) continue;
-              if (!flag_wait_ge(comm.gather.done + s, comm.dep_target, status, kTimeoutPeerFlag, true)) {
-                *abort_flag = 1;
-                ok = false;
+            const long long sb = comm.gather.shard_bytes;
+            const long long n_chunks = bulk_chunks(sb);
+            const long long b_lo = comm.dep_offset + r_lo * comm.dep_row_bytes;
+            const long long b_hi = comm.dep_offset + r_end * comm.dep_row_bytes - 1;          // last byte read
+            const int s_lo = max((int)(b_lo / sb), 0), s_hi = min((int)(b_hi / sb), comm.gather.world - 1);
+            bool waited = false;
+            for (int s = s_lo; s <= s_hi && ok; ++s) {
+              if (s == comm.gather.rank) continue;
+              const long long in_lo = max(b_lo - s * sb, 0LL), in_hi = min(b_hi - s * sb, sb - 1);
+              const int g_lo = bulk_seg_of(n_chunks, in_lo / kBulkChunk), g_hi = bulk_seg_of(n_chunks, in_hi / kBulkChunk);
+              for (int g = g_lo; g <= g_hi && ok; ++g) {
+                const int idx = s * kBulkSegs + g;
+                if ((segs_seen >> idx) & 1u) continue;
+                const uint32_t need = (uint32_t)(bulk_seg_begin(n_chunks, g + 1) - bulk_seg_begin(n_chunks, g));
+                if (!flag_wait_ge(comm.gather.done + idx, need, status, kTimeoutPeerFlag, true)) {
+                  *abort_flag = 1;
+                  ok = false;
+                }
+                segs_seen |= 1u << idx;
+                waited = true;
               }
-              shards_seen |= 1u << s;
             }
             if (!ok) break;
-            fence_proxy_async_all();     // the shard was written by other CTAs' bulk stores; TMA reads it next
+            if (waited) fence_proxy_async_all();     // written by other CTAs' bulk stores; TMA reads it next
           }
         }
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -405,9 +416,8 @@ KSA_API int ksa_gemm2_bf16(const void* a, const void* b, void* c, int M, int N, 
 // All-gather -> GEMM in one launch.  The GEMM arguments are those of ksa_gemm2_bf16; both operands K-major.
 //   peers/world/rank/shard_bytes/ready_flags/epoch_ptr/epoch_add: the gather, as in ksa_peer_gather (shard r of every
 //     rank's buffer is bytes [r*shard_bytes, (r+1)*shard_bytes); shards r != rank are pulled into peers[rank]).
-//   done: `world` uint32 counters in own memory; every launch adds ksa_gather_chunks(shard_bytes) to each
-//     done[r != rank].  done_target is the value that means "complete" for THIS launch (the caller keeps the running
-//     total).
+//   done: 32 uint32 counters in own memory, used by this launch only (the call zeroes them on the stream first):
+//     landed chunks per (shard, segment).  Required when dep_operand != 0.
 //   dep_operand: 1 if A (the [M, K] operand) lies inside the gathered buffer, 2 if B does, 0 if neither (the
 //     gather then only shares the launch); dep_offset: byte offset of that operand's first row in the buffer; the
 //     row pitch is lda (ldb) elements.
@@ -415,7 +425,7 @@ KSA_API int ksa_gemm2_gather_bf16(const void* a, const void* b, void* c, int M, 
                                   long long ldb, long long ldc, int out_fp32, int accumulate, float alpha,
                                   const void* const* peers, int world, int rank, long long shard_bytes,
                                   const void* ready_flags, const void* epoch_ptr, unsigned epoch_add, void* done,
-                                  unsigned done_target, int dep_operand, long long dep_offset, void* stream) {
+                                  int dep_operand, long long dep_offset, void* stream) {
   KSA_ENTER(a);
   using namespace ksa;
   KSA_REQUIRE(M > 0 && N > 0 && K > 0, "gemm2_gather: empty problem %d x %d x %d", M, N, K);
@@ -443,7 +453,8 @@ KSA_API int ksa_gemm2_gather_bf16(const void* a, const void* b, void* c, int M, 
     comm.dep_operand = dep_operand;
     comm.dep_offset = dep_offset;
     comm.dep_row_bytes = (dep_operand == 2 ? ldb : lda) * 2;
-    comm.dep_target = done_target;
+    if (done != nullptr)
+      KSA_CHECK_CUDA(cudaMemsetAsync(done, 0, sizeof(uint32_t) * kMaxPeers * kBulkSegs, reinterpret_cast<cudaStream_t>(stream)));
     if (dep_operand == 1) {
       // start with the first tile row that lies entirely in this rank's own rows; a tile row that straddles the
       // boundary to the previous rank's shard (the last one to arrive) then comes last
@@ -454,9 +465,6 @@ KSA_API int ksa_gemm2_gather_bf16(const void* a, const void* b, void* c, int M, 
   }
   return launch_gemm2<false, false>(a, b, ep, M, N, K, lda, ldb, reinterpret_cast<cudaStream_t>(stream), comm);
 }
-
-// Number by which one ksa_gemm2_gather_bf16 launch raises every done[r != rank].
-KSA_API long long ksa_gather_chunks(long long shard_bytes) { return ksa::bulk_chunks(shard_bytes); }
 
 // GEMM -> reduce-scatter, producer side: C = A B^T (both K-major, bf16 output) whose row block r (rows
 // [r*shard_rows, (r+1)*shard_rows), the last block takes the remainder) is written by the epilogue directly into

@@ -70,14 +70,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
                 and sm_limit == 0 and M > 16 and not _lib.comm_pending()
                 and 2.0 * M * N * K >= _lib.peek_pair_gather().get("min_flops", 0.0)):
             job = _lib.take_pair_gather()
-            st = job["state"]
-            st["total"] += _lib.gather_chunks(job["shard_bytes"])
             # does the weight operand live in the buffer that is being gathered?  Then its tiles wait for their shards.
             inside = job["base"] <= b.data_ptr() < job["base"] + job["nbytes"]
             _lib.call("ksa_gemm2_gather_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0), 0, 0, 1.0,
                       job["peers"], job["world"], job["rank"], job["shard_bytes"], job["ready"], job["epoch"],
-                      job["epoch_add"], st["done"], st["total"], 2 if inside else 0,
-                      b.data_ptr() - job["base"] if inside else 0)
+                      job["epoch_add"], job["done"], 2 if inside else 0, b.data_ptr() - job["base"] if inside else 0)
             return out
     if (M <= 16 and not a_mn_major and not b_mn_major and out.dtype == torch.bfloat16 and not accumulate
             and alpha == 1.0 and K % 8 == 0 and not _lib.comm_pending()):
@@ -100,7 +97,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
 
 
 def gemm_gather(a: torch.Tensor, b: torch.Tensor, peers, world: int, rank: int, shard_bytes: int, ready_flags,
-                epoch: Optional[torch.Tensor], done: torch.Tensor, done_target: int, *, dep_operand: int = 1,
+                epoch: Optional[torch.Tensor], done: Optional[torch.Tensor], *, dep_operand: int = 1,
                 dep_offset: int = 0, epoch_add: int = 0, out: Optional[torch.Tensor] = None,
                 out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """All-gather -> GEMM in one launch: ``C = A B^T`` (both K-major) on CTA pairs while a communication warp in
@@ -108,12 +105,13 @@ def gemm_gather(a: torch.Tensor, b: torch.Tensor, peers, world: int, rank: int, 
 
     ``peers``: ctypes array of every rank's pointer to the buffer (``peers[rank]`` is this rank's copy, which the
     gather completes); shard ``r`` is bytes ``[r*shard_bytes, (r+1)*shard_bytes)``.  ``dep_operand`` 1 (2) says that
-    ``a`` (``b``) lies in this rank's copy at byte ``dep_offset``: its tiles are read only once their shard has
-    landed.  ``done`` is a ``world``-element int32 device tensor to which every launch adds
-    ``_lib.gather_chunks(shard_bytes)`` per remote shard; ``done_target`` is the running total after this launch.
+    ``a`` (``b``) lies in this rank's copy at byte ``dep_offset``: its tiles are read only once the part of the shard
+    that holds them has landed.  ``done``: int32 device tensor of ``_lib.GATHER_COUNTERS`` scratch counters (zeroed
+    by the call).
     """
     _require_bf16(a, b)
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1 and a.shape[1] == b.shape[1]
+    assert done is None or done.numel() >= _lib.GATHER_COUNTERS
     M, K = a.shape
     N = b.shape[0]
     if out is None:
@@ -121,7 +119,7 @@ def gemm_gather(a: torch.Tensor, b: torch.Tensor, peers, world: int, rank: int, 
     assert out.shape == (M, N) and out.stride(1) == 1
     _lib.call("ksa_gemm2_gather_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
               int(out.dtype == torch.float32), 0, 1.0, peers, world, rank, shard_bytes, ready_flags, epoch, epoch_add,
-              done, done_target, dep_operand, dep_offset)
+              done, dep_operand, dep_offset)
     return out
 
 

@@ -24,8 +24,7 @@ P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 _SIGNATURES: Dict[str, Sequence] = {
     "ksa_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, I, P],
     "ksa_gemm2_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, P],
-    "ksa_gemm2_gather_bf16": [P, P, P, I, I, I, L, L, L, I, I, F, P, I, I, L, P, P, ctypes.c_uint, P, ctypes.c_uint, I, L,
-                              P],
+    "ksa_gemm2_gather_bf16": [P, P, P, I, I, I, L, L, L, I, I, F, P, I, I, L, P, P, ctypes.c_uint, P, I, L, P],
     "ksa_gemm2_scatter_bf16": [P, P, I, I, I, L, L, L, P, I, I, P],
     "ksa_gemv_bf16": [P, P, P, I, I, I, L, L, L, P],
     "ksa_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, I, P],
@@ -90,8 +89,6 @@ def load() -> ctypes.CDLL:
     lib.ksa_rmsnorm_bwd_parts.restype = I
     lib.ksa_attn_bwd_num_segments.argtypes = [I]
     lib.ksa_attn_bwd_num_segments.restype = I
-    lib.ksa_gather_chunks.argtypes = [L]
-    lib.ksa_gather_chunks.restype = L
     for name, sig in _SIGNATURES.items():
         fn = getattr(lib, name, None)
         if fn is not None:
@@ -178,9 +175,9 @@ def attach_pair_gather(job: dict) -> None:
     data is needed, in case no such GEMM came by.
 
     ``job``: ``peers`` (ctypes pointer array), ``world``, ``rank``, ``shard_bytes``, ``ready`` (address of the ready
-    flags), ``epoch`` (device tensor or None), ``epoch_add``, ``state`` (dict with ``done``: int32 device tensor of
-    ``world`` counters and ``total``: the running completion count), ``base`` / ``nbytes`` (this rank's copy of the
-    gathered buffer), ``min_flops`` (smallest GEMM that may carry it)."""
+    flags), ``epoch`` (device tensor or None), ``epoch_add``, ``done`` (int32 device tensor of ``GATHER_COUNTERS``
+    completion counters), ``base`` / ``nbytes`` (this rank's copy of the gathered buffer), ``min_flops`` (smallest
+    GEMM that may carry it)."""
     flush_pair_gather()
     _tls.pair_gather = job
 
@@ -240,9 +237,7 @@ def set_peer_wait_ms(ms: int) -> None:
         raise RuntimeError("could not set the peer wait limit")
 
 
-def gather_chunks(shard_bytes: int) -> int:
-    """By how much one ``ksa_gemm2_gather_bf16`` launch raises the completion counter of every remote shard."""
-    return int(load().ksa_gather_chunks(int(shard_bytes)))
+GATHER_COUNTERS = 32   # int32 completion counters a ``ksa_gemm2_gather_bf16`` launch uses (8 shards x 4 segments)
 
 
 def attn_bwd_num_segments(lq: int) -> int:

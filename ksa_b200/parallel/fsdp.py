@@ -167,15 +167,13 @@ class FsdpEngine(TrainEngine):
     def _attach_pair_gather(self, ui: int) -> None:
         u = self.units[ui]
         item = u.compute.element_size()
-        states = self.__dict__.setdefault("_pair_gather_state", {})
-        st = states.get(ui)
-        if st is None:
-            st = states[ui] = {"done": torch.zeros(self.world_size, dtype=torch.int32, device=self.device), "total": 0}
+        if getattr(self, "_pair_gather_done", None) is None:     # one scratch array: the launches are stream-ordered
+            self._pair_gather_done = torch.zeros(_lib.GATHER_COUNTERS, dtype=torch.int32, device=self.device)
         _lib.attach_pair_gather({
             "peers": u.compute_ptrs, "world": self.world_size, "rank": self.rank,
             "shard_bytes": (u.size // self.world_size) * item,
             "ready": self.pad_weights.local_ptr(self._unit_flag_index(ui)), "epoch": self.epoch, "epoch_add": 0,
-            "state": st, "base": u.compute.data_ptr(), "nbytes": u.size * item,
+            "done": self._pair_gather_done, "base": u.compute.data_ptr(), "nbytes": u.size * item,
             "min_flops": self.pair_gather_min_flops})
 
     def _gather_on_side_stream(self, ui: int) -> None:

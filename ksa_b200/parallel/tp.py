@@ -86,8 +86,7 @@ class TpContext:
             # GEMM -> reduce-scatter: the row-parallel GEMM's epilogue stores every row block into its owner's slot
             self.push_partials = bool(push_partials) and bool(self.two_phase_rows)
             if self.fused_gather:
-                self._done = torch.zeros(self.size, dtype=torch.int32, device=device)
-                self._done_total = 0
+                self._done = torch.zeros(_lib.GATHER_COUNTERS, dtype=torch.int32, device=device)
                 self._side = torch.cuda.Stream(device=device)
 
     def close(self) -> None:
@@ -232,10 +231,9 @@ class TpContext:
             return ops.linear(h, weight)
         _, shard, _ = p
         self._pending = None
-        shard_bytes = shard * self.D * h.element_size()
-        self._done_total += _lib.gather_chunks(shard_bytes)
-        return ops.gemm_gather(h, weight, self._y_ptrs, self.size, self.rank, shard_bytes, self.flags2.local_ptr(0),
-                               self._epoch[0:1], self._done, self._done_total, dep_operand=1, dep_offset=0, out=out)
+        return ops.gemm_gather(h, weight, self._y_ptrs, self.size, self.rank, shard * self.D * h.element_size(),
+                               self.flags2.local_ptr(0), self._epoch[0:1], self._done, dep_operand=1, dep_offset=0,
+                               out=out)
 
     # ------------------------------------------------------------------ vocabulary-parallel head
     def gather_logits(self, local: torch.Tensor) -> torch.Tensor:

@@ -294,17 +294,14 @@ def bench_ag_gemm(a) -> None:
     own.normal_()
     W = torch.randn(N, K, device=dev).bfloat16()
     out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-    done = torch.zeros(world, dtype=torch.int32, device=dev)
-    total = [0]
+    done = torch.zeros(_lib.GATHER_COUNTERS, dtype=torch.int32, device=dev)
 
     def separate():
         _lib.call("ksa_peer_gather", ptrs, world, rank, shard * K, 2, None, None, 0, a.ctas)
         ops.gemm(own[:M], W, out=out, pair=True)
 
     def fused():
-        total[0] += _lib.gather_chunks(shard * K * 2)
-        ops.gemm_gather(own[:M], W, ptrs, world, rank, shard * K * 2, None, None, done, total[0], dep_operand=1,
-                        out=out)
+        ops.gemm_gather(own[:M], W, ptrs, world, rank, shard * K * 2, None, None, done, dep_operand=1, out=out)
 
     def timed(fn):
         if multi:

@@ -147,76 +147,107 @@ def test_one_slot_would_not_be_enough():
 
 # ---------------------------------------------------------------------------------------------------------------------
 # All-gather -> GEMM in one launch (ksa_b200/csrc/gemm2.cu + run_gather_job_bulk in comm.cuh): the communication warps
-# copy the remote shards chunk by chunk and add the number of chunks they moved to done[shard] once those are written;
-# the TMA producers walk the tile rows starting at the first row block that lies entirely in the rank's own shard and
-# wait until done[s] has grown by the shard's chunk count for every shard s that a row block touches.
-def _ag_gemm_roles(world, rank, rows, shard_rows, tile_rows, n_comm, n_math, ring, landed, done, status, reads,
-                   ready=True):
+# copy the remote shards chunk by chunk; whenever a warp leaves one of the SEGS segments of a shard it waits for its
+# stores and adds the number of chunks of that segment it wrote to done[shard][segment].  The TMA producers walk the
+# tile rows starting at the first row block that lies entirely in the rank's own shard and wait, for every segment a
+# row block touches, until its counter has reached the segment's chunk count.
+SEGS = 4
+
+
+def seg_begin(n_chunks, g):
+    return (n_chunks * g + SEGS - 1) // SEGS
+
+
+def seg_of(n_chunks, c):
+    return max(g for g in range(SEGS) if seg_begin(n_chunks, g) <= c)
+
+
+def _ag_gemm_roles(world, rank, rows, shard_rows, tile_rows, n_cta, ring, landed, done, status, reads, ready=True):
     chunk = 3                                             # rows per bulk copy
-    target = (shard_rows + chunk - 1) // chunk            # chunks of one shard
+    n_chunks = (shard_rows + chunk - 1) // chunk
     tiles_m = (rows + tile_rows - 1) // tile_rows
     first_row = rank * shard_rows
     rotate = ((first_row + tile_rows - 1) // tile_rows) % tiles_m if 0 < first_row < rows else 0
 
-    def comm_cta(cta):
+    def comm_warp(cta):
         for step in range(1, world):
             r = (rank + step) % world
             yield from wait_ge(lambda: 1 if ready else 0, 1, status, 0)       # the shard's ready flag
-            n_chunks = (shard_rows + chunk - 1) // chunk
-            inflight = []
-            moved = 0
-            for c in range(cta, n_chunks, n_comm):
-                moved += 1
+            inflight, moved, seg = [], 0, None
+            for c in range(cta, n_chunks, n_cta):
+                if seg is None:
+                    seg = seg_of(n_chunks, c)
                 while len(inflight) >= ring:                                   # a stage frees when its store was read
                     landed[r].update(inflight.pop(0))
                     yield
                 inflight.append(range(r * shard_rows + c * chunk, min(r * shard_rows + (c + 1) * chunk, (r + 1) * shard_rows)))
+                moved += 1
                 yield
-            for rows_ in inflight:                                             # wait_group 0: everything is written
-                landed[r].update(rows_)
-                yield
-            done[r] += moved
-            yield
+                nxt = c + n_cta
+                if nxt >= n_chunks or nxt >= seg_begin(n_chunks, seg + 1):     # leaves the segment: wait_group 0, report
+                    for rows_ in inflight:
+                        landed[r].update(rows_)
+                        yield
+                    inflight = []
+                    done[r][seg] += moved
+                    moved, seg = 0, (seg_of(n_chunks, nxt) if nxt < n_chunks else None)
+                    yield
 
-    def math_pair(pair):
+    def producer(pair, n_pairs):
         seen = set()
-        for t in range(pair, tiles_m, n_math):
+        for t in range(pair, tiles_m, n_pairs):
             mb = (t + rotate) % tiles_m
             lo, hi = mb * tile_rows, min((mb + 1) * tile_rows, rows)
             for s in range(lo // shard_rows, (hi - 1) // shard_rows + 1):
-                if s == rank or s in seen:
+                if s == rank:
                     continue
-                yield from wait_ge(lambda s=s: done[s], target, status, 1)
-                seen.add(s)
+                in_lo, in_hi = max(lo - s * shard_rows, 0), min(hi - 1 - s * shard_rows, shard_rows - 1)
+                for g in range(seg_of(n_chunks, in_lo // chunk), seg_of(n_chunks, in_hi // chunk) + 1):
+                    if (s, g) in seen:
+                        continue
+                    need = seg_begin(n_chunks, g + 1) - seg_begin(n_chunks, g)
+                    yield from wait_ge(lambda s=s, g=g: done[s][g], need, status, 1)
+                    seen.add((s, g))
             for row in range(lo, hi):                                          # the TMA loads of this tile
                 s = row // shard_rows
-                assert s == rank or row in landed[s], f"tile row {mb} read row {row} before shard {s} had landed"
+                assert s == rank or row in landed[s], f"tile row {mb} read row {row} before that part of shard {s} had landed"
             reads.append(mb)
             yield
-    return [comm_cta(c) for c in range(n_comm)] + [math_pair(p) for p in range(n_math)]
+    n_pairs = max(n_cta // 2, 1)
+    return [comm_warp(c) for c in range(n_cta)] + [producer(p, n_pairs) for p in range(n_pairs)]
 
 
-@pytest.mark.parametrize("world,rank,rows,tile_rows", [(4, 1, 130, 8), (2, 0, 64, 8), (8, 7, 129, 4), (4, 3, 50, 16)])
+@pytest.mark.parametrize("world,rank,rows,tile_rows", [(4, 1, 130, 8), (2, 0, 64, 8), (8, 7, 129, 4), (4, 3, 50, 16),
+                                                       (2, 1, 300, 16)])
 def test_all_gather_gemm_dependencies(world, rank, rows, tile_rows):
     shard_rows = (rows + world - 1) // world
+    n_chunks = (shard_rows + 2) // 3
     for seed in range(20):
         rng = random.Random(seed)
         landed = [set() for _ in range(world)]
-        done = [0] * world
+        done = [[0] * SEGS for _ in range(world)]
         status = [0, 0]
         reads = []
-        run(_ag_gemm_roles(world, rank, rows, shard_rows, tile_rows, 3, 5, 2, landed, done, status, reads), rng)
+        run(_ag_gemm_roles(world, rank, rows, shard_rows, tile_rows, 6, 2, landed, done, status, reads), rng)
         assert status == [0, 0]
         assert sorted(reads) == list(range((rows + tile_rows - 1) // tile_rows))      # every tile row exactly once
-        # the walk starts inside the own shard: no wait can precede the first tile of a pair that starts there
-        first = reads[0] * tile_rows
-        assert first // shard_rows == rank or world == 1 or rank * shard_rows >= rows
+        for r in range(world):                                                         # every chunk counted once
+            assert sum(done[r]) == (0 if r == rank else n_chunks)
 
 
 def test_all_gather_gemm_gives_up_when_shards_never_become_ready():
     world, rank, rows, tile_rows = 4, 0, 64, 8
     rng = random.Random(0)
-    landed, done, status, reads = [set() for _ in range(world)], [0] * world, [0, 0], []
-    run(_ag_gemm_roles(world, rank, rows, 16, tile_rows, 2, 3, 2, landed, done, status, reads, ready=False), rng)
+    landed, done, status, reads = [set() for _ in range(world)], [[0] * SEGS for _ in range(world)], [0, 0], []
+    run(_ag_gemm_roles(world, rank, rows, 16, tile_rows, 4, 2, landed, done, status, reads, ready=False), rng)
     assert status == [5, 5]                                   # the gather and then the math report the flag timeout
     assert all(mb * tile_rows < 16 for mb in reads)           # only tiles of the own shard were computed
+
+
+def test_segment_arithmetic_covers_every_chunk_once():
+    for n in list(range(1, 40)) + [5160, 5161]:
+        begins = [seg_begin(n, g) for g in range(SEGS + 1)]
+        assert begins[0] == 0 and begins[-1] == n and begins == sorted(begins)
+        for c in range(min(n, 64)):
+            g = seg_of(n, c)
+            assert begins[g] <= c < begins[g + 1]

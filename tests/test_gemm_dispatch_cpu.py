@@ -1,5 +1,5 @@
 """Host-side dispatch of ``ops.gemm``: which entry point a GEMM goes to, and how a parameter all-gather that waits for
-a GEMM is attached to it (operand inside the gathered buffer or not, running completion count, flush).  The kernel
+a GEMM is attached to it (operand inside the gathered buffer or not, flush).  The kernel
 library is replaced by a recorder, so this runs without a GPU."""
 import ctypes
 
@@ -14,7 +14,6 @@ from ksa_b200.ops import _lib
 def calls(monkeypatch):
     rec = []
     monkeypatch.setattr(_lib, "call", lambda name, *args: rec.append((name, args)))
-    monkeypatch.setattr(_lib, "gather_chunks", lambda shard_bytes: (shard_bytes + 8191) // 8192)
     monkeypatch.setattr(ops, "_cuda", lambda *t: True, raising=False)
     _lib.take_pair_gather()
     yield rec
@@ -24,7 +23,7 @@ def calls(monkeypatch):
 def _job(buf: torch.Tensor, world=4, rank=1, min_flops=0.0):
     nbytes = buf.numel() * buf.element_size()
     return {"peers": (ctypes.c_void_p * world)(), "world": world, "rank": rank, "shard_bytes": nbytes // world,
-            "ready": 0, "epoch": None, "epoch_add": 0, "state": {"done": None, "total": 5}, "base": buf.data_ptr(),
+            "ready": 0, "epoch": None, "epoch_add": 0, "done": None, "base": buf.data_ptr(),
             "nbytes": nbytes, "min_flops": min_flops}
 
 
@@ -40,10 +39,8 @@ def test_pending_gather_rides_in_the_first_suitable_gemm(calls):
     ops.gemm(x, w, out=torch.empty(128, 64, dtype=torch.bfloat16))
     name, args = calls[-1]
     assert name == "ksa_gemm2_gather_bf16" and not _lib.pair_gather_pending()
-    per_launch = (job["shard_bytes"] + 8191) // 8192
-    assert job["state"]["total"] == 5 + per_launch
-    # ..., done, done_target, dep_operand, dep_offset
-    assert args[-3] == 5 + per_launch and args[-2] == 2 and args[-1] == 512 * 2
+    # ..., done, dep_operand, dep_offset
+    assert args[-2] == 2 and args[-1] == 512 * 2
     # the next GEMM is a plain one again
     ops.gemm(x, w, out=torch.empty(128, 64, dtype=torch.bfloat16))
     assert calls[-1][0] in ("ksa_gemm_bf16", "ksa_gemm2_bf16")
@@ -70,7 +67,6 @@ def test_short_gemms_do_not_take_the_gather_and_flush_runs_it_alone(calls):
     _lib.flush_pair_gather()
     name, args = calls[-1]
     assert name == "ksa_peer_gather" and args[1:5] == (4, 1, job["shard_bytes"], 1) and not _lib.pair_gather_pending()
-    assert job["state"]["total"] == 5                  # the counters belong to the in-GEMM form only
     # attaching a second job while one is pending runs the first one alone
     _lib.attach_pair_gather(_job(unit))
     n = len(calls)

@@ -345,22 +345,23 @@ def test_all_gather_gemm_one_launch(world, rank, rows, N, K):
     full, copies, peers, shard = _gather_case(world, rank, rows, K)
     W = bf(N, K)
     ready = torch.zeros(world, dtype=torch.int32, device=DEV)
-    done = torch.zeros(world, dtype=torch.int32, device=DEV)
+    done = torch.zeros(_lib.GATHER_COUNTERS, dtype=torch.int32, device=DEV)
     want = full[:rows].float() @ W.float().t()
-    per_launch = _lib.gather_chunks(shard * K * 2)
+    n_chunks = (shard * K * 2 + 8191) // 8192
     for launch in (1, 2):
         if launch == 2:                       # junk again in the remote shards of the own copy
             keep = copies[rank][rank * shard:(rank + 1) * shard].clone()
             copies[rank].fill_(-3.0)
             copies[rank][rank * shard:(rank + 1) * shard] = keep
         a = copies[rank][:rows]
-        out = ops.gemm_gather(a, W, peers, world, rank, shard * K * 2, ready, None, done, per_launch * launch,
-                              dep_operand=1, dep_offset=0)
+        out = ops.gemm_gather(a, W, peers, world, rank, shard * K * 2, ready, None, done, dep_operand=1, dep_offset=0)
         check(out, want, 1e-2, f"all-gather gemm launch {launch}")
         assert torch.equal(copies[rank], full), "the gather did not complete the own copy"
-        expect = torch.full((world,), per_launch * launch, dtype=torch.int32, device=DEV)
+        per_shard = done.view(8, 4).sum(1)               # landed chunks per shard: counted afresh by every launch
+        expect = torch.zeros(8, dtype=torch.int64, device=DEV)
+        expect[:world] = n_chunks
         expect[rank] = 0
-        assert torch.equal(done, expect)
+        assert torch.equal(per_shard, expect)
 
 
 def test_gather_rides_along_without_dependency():
@@ -368,8 +369,7 @@ def test_gather_rides_along_without_dependency():
     full, copies, peers, shard = _gather_case(4, 2, 4096, 256)
     A, W = bf(1000, 264), bf(520, 264)
     ready = torch.zeros(4, dtype=torch.int32, device=DEV)
-    done = torch.zeros(4, dtype=torch.int32, device=DEV)
-    out = ops.gemm_gather(A, W, peers, 4, 2, shard * 256 * 2, ready, None, done, 0, dep_operand=0)
+    out = ops.gemm_gather(A, W, peers, 4, 2, shard * 256 * 2, ready, None, None, dep_operand=0)
     check(out, A.float() @ W.float().t(), 1e-2, "gemm with a gather riding along")
     assert torch.equal(copies[2], full)
 
@@ -380,17 +380,16 @@ def test_all_gather_gemm_gives_up_when_a_shard_never_becomes_ready():
     full, copies, peers, shard = _gather_case(2, 0, 2048, 256)
     W = bf(256, 256)
     ready = torch.zeros(2, dtype=torch.int32, device=DEV)
-    done = torch.zeros(2, dtype=torch.int32, device=DEV)
+    done = torch.zeros(_lib.GATHER_COUNTERS, dtype=torch.int32, device=DEV)
     _lib.check_status()
     _lib.set_peer_wait_ms(200)
     try:
-        target = _lib.gather_chunks(shard * 256 * 2)
-        ops.gemm_gather(copies[0][:2048], W, peers, 2, 0, shard * 256 * 2, ready, None, done, target,
+        ops.gemm_gather(copies[0][:2048], W, peers, 2, 0, shard * 256 * 2, ready, None, done,
                         dep_operand=1, epoch_add=1)                        # waits for ready[1] >= 1
         with pytest.raises(RuntimeError, match="timed out waiting for a flag"):
             _lib.check_status()
         ready.fill_(1)
-        out = ops.gemm_gather(copies[0][:2048], W, peers, 2, 0, shard * 256 * 2, ready, None, done, target,
+        out = ops.gemm_gather(copies[0][:2048], W, peers, 2, 0, shard * 256 * 2, ready, None, done,
                               dep_operand=1, epoch_add=1)
         check(out, full[:2048].float() @ W.float().t(), 1e-2, "all-gather gemm after a timed-out launch")
     finally:
