@@ -102,22 +102,29 @@ constexpr int kBulkChunk = 8192;
 constexpr int kBulkStages = 4;
 constexpr int kBulkRingBytes = kBulkStages * kBulkChunk + 64;   // + the ring's mbarriers and its abort flag
 
-// A shard is moved and reported in kBulkSegs segments of (almost) equal numbers of chunks, so that a consumer of the
-// first rows of a shard does not wait for its last ones.
+// A shard is moved and reported in up to kBulkSegs segments of (almost) equal numbers of chunks, so that a consumer of
+// the first rows of a shard does not wait for its last ones.  Leaving a segment costs the copying thread a full wait
+// for its stores, so a shard is only split while every CTA still moves kBulkMinPerSeg chunks or more per segment.
 constexpr int kBulkSegs = 4;
+constexpr int kBulkMinPerSeg = 12;
 
 __host__ __device__ constexpr long long bulk_chunks(long long shard_bytes) {
   return (shard_bytes + kBulkChunk - 1) / kBulkChunk;
 }
-// first chunk of segment g (g = kBulkSegs gives the number of chunks)
-__host__ __device__ constexpr long long bulk_seg_begin(long long n_chunks, int g) {
-  return (n_chunks * g + kBulkSegs - 1) / kBulkSegs;
+// segments a shard of n_chunks is split into when nctas CTAs move it
+__host__ __device__ constexpr int bulk_segs(long long n_chunks, int nctas) {
+  const long long g = n_chunks / ((long long)nctas * kBulkMinPerSeg);
+  return g < 1 ? 1 : (g > kBulkSegs ? kBulkSegs : (int)g);
+}
+// first chunk of segment g of `segs` (g = segs gives the number of chunks)
+__host__ __device__ constexpr long long bulk_seg_begin(long long n_chunks, int segs, int g) {
+  return (n_chunks * g + segs - 1) / segs;
 }
 // segment that chunk c belongs to: the largest g with bulk_seg_begin(g) <= c
-__host__ __device__ constexpr int bulk_seg_of(long long n_chunks, long long c) {
-  int g = (int)(c * kBulkSegs / n_chunks);
-  while (g + 1 < kBulkSegs && bulk_seg_begin(n_chunks, g + 1) <= c) ++g;
-  while (g > 0 && bulk_seg_begin(n_chunks, g) > c) --g;
+__host__ __device__ constexpr int bulk_seg_of(long long n_chunks, int segs, long long c) {
+  int g = (int)(c * segs / n_chunks);
+  while (g + 1 < segs && bulk_seg_begin(n_chunks, segs, g + 1) <= c) ++g;
+  while (g > 0 && bulk_seg_begin(n_chunks, segs, g) > c) --g;
   return g;
 }
 
@@ -139,7 +146,8 @@ __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.pr
 // Called by ONE thread.  CTA `cta` of `nctas` moves chunks cta, cta + nctas, ... of every remote shard through `ring`
 // (16-byte aligned shared memory of kBulkRingBytes that nobody else touches) and, whenever it leaves a segment of a
 // shard, adds the number of chunks of that segment it has written to done[r * kBulkSegs + segment]: the segment is
-// complete when the counter has reached bulk_seg_begin(n, g + 1) - bulk_seg_begin(n, g).
+// complete when the counter has reached bulk_seg_begin(n, segs, g + 1) - bulk_seg_begin(n, segs, g), with
+// segs = bulk_segs(n, nctas).
 // Chunks are numbered in the order this CTA moves them, across shards: chunk n uses stage n % kBulkStages and the
 // (n / kBulkStages)-th phase of that stage's barrier.  Returns false if a wait gave up; nothing is left in flight
 // either way.
@@ -153,6 +161,7 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
   uint8_t* dst_base = const_cast<uint8_t*>(j.peers[j.rank]);
   const uint32_t target = epoch_target(j.epoch_ptr, j.epoch_add);
   const long long n_chunks = bulk_chunks(j.shard_bytes);
+  const int segs = bulk_segs(n_chunks, nctas);
   long long issued = 0;    // loads issued
   long long stored = 0;    // stores issued
   long long freed = 0;     // stores known to have finished reading their stage
@@ -165,7 +174,7 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
     uint8_t* dst = dst_base + (long long)r * j.shard_bytes;
     long long next_load = cta, next_store = cta;
     uint32_t moved = 0;                                   // chunks of segment `seg` stored by this CTA
-    int seg = next_store < n_chunks ? bulk_seg_of(n_chunks, next_store) : 0;
+    int seg = next_store < n_chunks ? bulk_seg_of(n_chunks, segs, next_store) : 0;
     while (next_store < n_chunks) {
       while (next_load < n_chunks && issued - freed < kBulkStages) {
         const int s = (int)(issued % kBulkStages);
@@ -186,7 +195,7 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
       ++stored;
       ++moved;
       next_store += nctas;
-      const bool leaves = next_store >= n_chunks || next_store >= bulk_seg_begin(n_chunks, seg + 1);
+      const bool leaves = next_store >= n_chunks || next_store >= bulk_seg_begin(n_chunks, segs, seg + 1);
       if (!leaves) {
         bulk_wait_read_all_but_one();   // every store but the newest has read its stage: those stages may be refilled
         freed = stored - 1;
@@ -199,7 +208,7 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
           red_release_gpu_add(j.done + r * kBulkSegs + seg, moved);
         }
         moved = 0;
-        if (next_store < n_chunks) seg = bulk_seg_of(n_chunks, next_store);
+        if (next_store < n_chunks) seg = bulk_seg_of(n_chunks, segs, next_store);
       }
     }
     if (!ok) break;

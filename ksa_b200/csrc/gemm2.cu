@@ -181,6 +181,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (r_lo < r_end) {
             const long long sb = comm.gather.shard_bytes;
             const long long n_chunks = bulk_chunks(sb);
+            const int segs = bulk_segs(n_chunks, (int)gridDim.x);
             const long long b_lo = comm.dep_offset + r_lo * comm.dep_row_bytes;
             const long long b_hi = comm.dep_offset + r_end * comm.dep_row_bytes - 1;          // last byte read
             const int s_lo = max((int)(b_lo / sb), 0), s_hi = min((int)(b_hi / sb), comm.gather.world - 1);
@@ -188,11 +189,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int s = s_lo; s <= s_hi && ok; ++s) {
               if (s == comm.gather.rank) continue;
               const long long in_lo = max(b_lo - s * sb, 0LL), in_hi = min(b_hi - s * sb, sb - 1);
-              const int g_lo = bulk_seg_of(n_chunks, in_lo / kBulkChunk), g_hi = bulk_seg_of(n_chunks, in_hi / kBulkChunk);
+              const int g_lo = bulk_seg_of(n_chunks, segs, in_lo / kBulkChunk);
+              const int g_hi = bulk_seg_of(n_chunks, segs, in_hi / kBulkChunk);
               for (int g = g_lo; g <= g_hi && ok; ++g) {
                 const int idx = s * kBulkSegs + g;
                 if ((segs_seen >> idx) & 1u) continue;
-                const uint32_t need = (uint32_t)(bulk_seg_begin(n_chunks, g + 1) - bulk_seg_begin(n_chunks, g));
+                const uint32_t need = (uint32_t)(bulk_seg_begin(n_chunks, segs, g + 1) - bulk_seg_begin(n_chunks, segs, g));
                 if (!flag_wait_ge(comm.gather.done + idx, need, status, kTimeoutPeerFlag, true)) {
                   *abort_flag = 1;
                   ok = false;
