@@ -48,7 +48,14 @@ struct Gemm2Epilogue {
   // the epilogue, straight into that rank's memory at c_peer[owner] + (row - owner * c_shard_rows) * ldc.
   int c_shard_rows;          // 0: every row goes to `c`
   int c_world;
+  int c_tma;                 // 1: 32-row blocks that lie in one owner's rows leave through TMA stores (c_map)
   void* c_peer[kMaxPeers];
+};
+
+// Tensor maps over the owners' output buffers ([rows of that owner, N] bf16, box 64 columns x 32 rows, 128-byte
+// swizzle) for the scattering epilogue.
+struct ScatterMaps {
+  CUtensorMap m[kMaxPeers];
 };
 
 // Communication work riding in a pair-GEMM launch, and what the math waits for.
@@ -115,10 +122,13 @@ template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(k2Threads, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ Gemm2Epilogue ep,
-                  int M, int N, int K, int* status, const __grid_constant__ Comm2Work comm) {
+                  int M, int N, int K, int* status, const __grid_constant__ Comm2Work comm,
+                  const __grid_constant__ ScatterMaps smaps) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* bar_base = smem + k2Stages * k2StageBytes;
+  uint8_t* ring = smem + k2Stages * k2StageBytes;      // copy ring of the communication warp, or the epilogue's
+                                                       // staging for TMA stores (1024-byte aligned)
+  uint8_t* bar_base = ring + kBulkRingBytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);   // used in the leader
   uint64_t* empty = full + k2Stages;                         // both CTAs
   uint64_t* acc_full = empty + k2Stages;                     // both CTAs, 2 buffers
@@ -263,8 +273,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else if (warp == 6) {
     // ------------------------------------------------------------ communication warp (both CTAs, one thread)
     if (lane == 0 && comm.active)
-      run_gather_job_bulk(comm.gather, (int)blockIdx.x, (int)gridDim.x, smem + k2Stages * k2StageBytes + k2BarrierBytes,
-                          status);
+      run_gather_job_bulk(comm.gather, (int)blockIdx.x, (int)gridDim.x, ring, status);
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int quad = warp & 3;
@@ -277,14 +286,55 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait(&acc_full[buf], acc_phase, guard, kTimeoutAccFull)) { ok = false; break; }
       tc_fence_after();
-      const int row = mb * 2 * k2BM + (int)rank * k2BM + quad * 32 + lane;
+      const int row_w = mb * 2 * k2BM + (int)rank * k2BM + quad * 32;   // first of this warp's 32 rows
+      const int row = row_w + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * k2BN;
+      // scattering epilogue: a 32-row block that lies in ONE owner's rows leaves through shared memory and TMA
+      // stores of 64 columns x 32 rows (128-byte rows on the wire); a block that straddles two owners' rows
+      // falls back to the per-row stores below
+      int owner_w = 0;
+      bool tma_block = false;
+      if (ep.c_tma && row_w < M) {
+        owner_w = min(row_w / ep.c_shard_rows, ep.c_world - 1);
+        tma_block = min(min(row_w + 31, M - 1) / ep.c_shard_rows, ep.c_world - 1) == owner_w;
+      }
 #pragma unroll 1
       for (int c = 0; c < k2BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(t_row + c * 32, r);
         tmem_wait_ld();
         const int col0 = nb * k2BN + c * 32;
+        if (tma_block) {
+          const int piece = c >> 1, half = c & 1;                   // 64-column piece, 32-column half of it
+          uint8_t* stage = ring + ((warp - 2) * 2 + (piece & 1)) * 4096;
+          const bool live = nb * k2BN + piece * 64 < N;             // N is a multiple of 64 on this path
+          if (half == 0) {
+            // this buffer was read by the store issued two pieces ago; at most the newest store may be pending
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+          }
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * j]) * ep.alpha, __uint_as_float(r[8 * j + 1]) * ep.alpha);
+              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * ep.alpha, __uint_as_float(r[8 * j + 3]) * ep.alpha);
+              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * ep.alpha, __uint_as_float(r[8 * j + 5]) * ep.alpha);
+              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * ep.alpha, __uint_as_float(r[8 * j + 7]) * ep.alpha);
+              const int chunk = (half * 4 + j) ^ (lane & 7);        // 128-byte swizzle: 16-byte chunk ^ (row mod 8)
+              *reinterpret_cast<uint4*>(stage + lane * 128 + chunk * 16) = v;
+            }
+          }
+          if (half == 1) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && live) {
+              tma_store_2d(&smaps.m[owner_w], stage, nb * k2BN + piece * 64, row_w - owner_w * ep.c_shard_rows);
+              tma_store_commit();
+            }
+          }
+          continue;
+        }
         if (row < M && col0 < N) {
           if (ep.out_fp32) {
             float* dst = reinterpret_cast<float*>(ep.c) + (long long)row * ep.ldc + col0;
@@ -330,6 +380,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   }
 
+  // TMA stores of the scattering epilogue have written their destination before the kernel ends
+  if (ep.c_tma && warp >= 2 && warp < 6 && lane == 0) tma_store_wait0();
   // The peer's tensor memory and barriers are written by the leader's MMAs and commits: nobody leaves, and nothing
   // is deallocated, before both CTAs are done.
   tc_fence_before();
@@ -341,9 +393,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
+static const ScatterMaps kNoScatterMaps{};
+
 template <bool A_MN, bool B_MN>
 static int launch_gemm2(const void* a, const void* b, const Gemm2Epilogue& ep, int M, int N, int K, long long lda,
-                        long long ldb, cudaStream_t stream, const Comm2Work& comm) {
+                        long long ldb, cudaStream_t stream, const Comm2Work& comm,
+                        const ScatterMaps& smaps = kNoScatterMaps) {
   CUtensorMap tmA, tmB;
   int rc;
   if (!A_MN) {
@@ -387,7 +442,7 @@ static int launch_gemm2(const void* a, const void* b, const Gemm2Epilogue& ep, i
   if (tiles < pairs) pairs = tiles;
   int* status = status_word();
   KSA_REQUIRE(status != nullptr, "could not allocate the status word");
-  kern<<<2 * pairs, k2Threads, k2SmemTotal, stream>>>(tmA, tmB, ep, M, N, K, status, comm);
+  kern<<<2 * pairs, k2Threads, k2SmemTotal, stream>>>(tmA, tmB, ep, M, N, K, status, comm, smaps);
   KSA_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -471,7 +526,9 @@ KSA_API int ksa_gemm2_gather_bf16(const void* a, const void* b, void* c, int M, 
 // GEMM -> reduce-scatter, producer side: C = A B^T (both K-major, bf16 output) whose row block r (rows
 // [r*shard_rows, (r+1)*shard_rows), the last block takes the remainder) is written by the epilogue directly into
 // rank r's memory at c_peers[r] (row pitch ldc elements) with P2P stores, so the transfer runs under the remaining
-// tiles and the reduction that follows reads only local memory.  c_peers[r] must be 16-byte aligned.
+// tiles and the reduction that follows reads only local memory.  c_peers[r] must be 16-byte aligned.  With N a
+// multiple of 64, every 32-row block that lies within one rank's rows goes through shared memory and TMA stores
+// (128-byte rows over NVLink instead of 16-byte register stores).
 KSA_API int ksa_gemm2_scatter_bf16(const void* a, const void* b, int M, int N, int K, long long lda, long long ldb,
                                    long long ldc, const void* const* c_peers, int world, int shard_rows, void* stream) {
   KSA_ENTER(a);
@@ -487,5 +544,20 @@ KSA_API int ksa_gemm2_scatter_bf16(const void* a, const void* b, int M, int N, i
     ep.c_peer[r] = const_cast<void*>(c_peers[r]);
   }
   ep.c = ep.c_peer[0];
-  return launch_gemm2<false, false>(a, b, ep, M, N, K, lda, ldb, reinterpret_cast<cudaStream_t>(stream), Comm2Work{});
+  ScatterMaps smaps{};
+  if (N % 64 == 0) {
+    // one tensor map per owner over the rows it really gets: rows past the end of the product are clipped by the map
+    ep.c_tma = 1;
+    for (int r = 0; r < world; ++r) {
+      const long long rows_r = (long long)M - (long long)r * shard_rows;
+      if (rows_r <= 0) break;
+      uint64_t dims[2] = {(uint64_t)N, (uint64_t)(rows_r < shard_rows ? rows_r : shard_rows)};
+      uint64_t str[2] = {2, (uint64_t)ldc * 2};
+      uint32_t box[2] = {64, 32};
+      const int rc = make_tmap(&smaps.m[r], ep.c_peer[r], 2, 2, dims, str, box, true);
+      if (rc) return rc;
+    }
+  }
+  return launch_gemm2<false, false>(a, b, ep, M, N, K, lda, ldb, reinterpret_cast<cudaStream_t>(stream), Comm2Work{},
+                                    smaps);
 }

@@ -396,10 +396,13 @@ def test_all_gather_gemm_gives_up_when_a_shard_never_becomes_ready():
         _lib.set_peer_wait_ms(10000)
 
 
-@pytest.mark.parametrize("world,M,N,K,shard", [(4, 1000, 512, 264, 260), (2, 4096, 2560, 512, 2048), (8, 8256, 256, 128, 1056)])
+@pytest.mark.parametrize("world,M,N,K,shard", [(4, 1000, 512, 264, 260), (2, 4096, 2560, 512, 2048), (8, 8256, 256, 128, 1056),
+                                               (4, 1000, 264, 72, 260), (3, 700, 320, 64, 256)])
 def test_gemm_scatters_row_blocks_to_their_owners(world, M, N, K, shard):
     """GEMM -> reduce-scatter, producer side: row block r of the product lands in the r-th output buffer (here all
-    on one GPU), whatever the alignment of the block boundaries to the 128-row tiles."""
+    on one GPU), whatever the alignment of the block boundaries to the 128-row tiles.  With N a multiple of 64 the
+    32-row blocks inside one owner's rows leave through TMA stores, the straddling ones and every other N through
+    per-row stores."""
     import ctypes
     A, W = bf(M, K), bf(N, K)
     outs = [torch.full((shard, N), 9.0, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
