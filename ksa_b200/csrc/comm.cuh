@@ -17,6 +17,7 @@ struct GatherJob {
   const uint32_t* ready_flags;  // optional, own memory: shard r may be read once ready_flags[r] >= target
   const uint32_t* epoch_ptr;    // target = (epoch_ptr ? *epoch_ptr : 0) + epoch_add; a device-resident epoch keeps
   uint32_t epoch_add;           // a captured CUDA graph valid from step to step
+  int max_segs;                 // bulk gather only: most segments a shard is reported in (1..kBulkSegs)
   uint32_t* done;               // optional, own memory: bulk gather only, kMaxPeers x kBulkSegs counters (zero at
                                 // launch): done[r * kBulkSegs + g] += chunks of segment g of shard r that have landed
 };
@@ -111,10 +112,10 @@ constexpr int kBulkMinPerSeg = 12;
 __host__ __device__ constexpr long long bulk_chunks(long long shard_bytes) {
   return (shard_bytes + kBulkChunk - 1) / kBulkChunk;
 }
-// segments a shard of n_chunks is split into when nctas CTAs move it
-__host__ __device__ constexpr int bulk_segs(long long n_chunks, int nctas) {
+// segments a shard of n_chunks is split into when nctas CTAs move it (at most max_segs <= kBulkSegs)
+__host__ __device__ constexpr int bulk_segs(long long n_chunks, int nctas, int max_segs) {
   const long long g = n_chunks / ((long long)nctas * kBulkMinPerSeg);
-  return g < 1 ? 1 : (g > kBulkSegs ? kBulkSegs : (int)g);
+  return g < 1 ? 1 : (g > max_segs ? max_segs : (int)g);
 }
 // first chunk of segment g of `segs` (g = segs gives the number of chunks)
 __host__ __device__ constexpr long long bulk_seg_begin(long long n_chunks, int segs, int g) {
@@ -147,7 +148,7 @@ __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.pr
 // (16-byte aligned shared memory of kBulkRingBytes that nobody else touches) and, whenever it leaves a segment of a
 // shard, adds the number of chunks of that segment it has written to done[r * kBulkSegs + segment]: the segment is
 // complete when the counter has reached bulk_seg_begin(n, segs, g + 1) - bulk_seg_begin(n, segs, g), with
-// segs = bulk_segs(n, nctas).
+// segs = bulk_segs(n, nctas, max_segs).
 // Chunks are numbered in the order this CTA moves them, across shards: chunk n uses stage n % kBulkStages and the
 // (n / kBulkStages)-th phase of that stage's barrier.  Returns false if a wait gave up; nothing is left in flight
 // either way.
@@ -161,7 +162,7 @@ __device__ __forceinline__ bool run_gather_job_bulk(const GatherJob& j, int cta,
   uint8_t* dst_base = const_cast<uint8_t*>(j.peers[j.rank]);
   const uint32_t target = epoch_target(j.epoch_ptr, j.epoch_add);
   const long long n_chunks = bulk_chunks(j.shard_bytes);
-  const int segs = bulk_segs(n_chunks, nctas);
+  const int segs = bulk_segs(n_chunks, nctas, j.max_segs);
   long long issued = 0;    // loads issued
   long long stored = 0;    // stores issued
   long long freed = 0;     // stores known to have finished reading their stage

@@ -22,6 +22,8 @@
 #include "comm.cuh"
 #include "host.h"
 
+#include <stdlib.h>
+
 namespace ksa {
 
 constexpr int k2BM = 128;          // rows of A (and of the accumulator) per CTA
@@ -191,7 +193,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (r_lo < r_end) {
             const long long sb = comm.gather.shard_bytes;
             const long long n_chunks = bulk_chunks(sb);
-            const int segs = bulk_segs(n_chunks, (int)gridDim.x);
+            const int segs = bulk_segs(n_chunks, (int)gridDim.x, comm.gather.max_segs);
             const long long b_lo = comm.dep_offset + r_lo * comm.dep_row_bytes;
             const long long b_hi = comm.dep_offset + r_end * comm.dep_row_bytes - 1;          // last byte read
             const int s_lo = max((int)(b_lo / sb), 0), s_hi = min((int)(b_hi / sb), comm.gather.world - 1);
@@ -507,6 +509,13 @@ KSA_API int ksa_gemm2_gather_bf16(const void* a, const void* b, void* c, int M, 
     comm.gather.ready_flags = static_cast<const uint32_t*>(ready_flags);
     comm.gather.epoch_ptr = static_cast<const uint32_t*>(epoch_ptr); comm.gather.epoch_add = epoch_add;
     comm.gather.done = static_cast<uint32_t*>(done);
+    static int max_segs = 0;               // KSA_BULK_SEGS=1..4 caps the segments per shard (for A/B runs)
+    if (max_segs == 0) {
+      const char* e = getenv("KSA_BULK_SEGS");
+      max_segs = e ? atoi(e) : kBulkSegs;
+      if (max_segs < 1 || max_segs > kBulkSegs) max_segs = kBulkSegs;
+    }
+    comm.gather.max_segs = max_segs;
     comm.dep_operand = dep_operand;
     comm.dep_offset = dep_offset;
     comm.dep_row_bytes = (dep_operand == 2 ? ldb : lda) * 2;

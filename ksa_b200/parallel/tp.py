@@ -35,7 +35,7 @@ class TpContext:
         if fused_gather is None:
             fused_gather = os.environ.get("KSA_TP_FUSED_GATHER", "1") == "1"
         if push_partials is None:
-            push_partials = os.environ.get("KSA_TP_PUSH_PARTIALS", "0") == "1"
+            push_partials = os.environ.get("KSA_TP_PUSH_PARTIALS", "1") == "1"
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)

@@ -50,8 +50,9 @@ def main(argv=None) -> None:
     ap.add_argument("--tp-separate-gather", action="store_true",
                     help="gather the normalised rows with kernels of their own instead of inside the projection "
                          "that consumes them (for A/B runs)")
-    ap.add_argument("--tp-push-partials", action="store_true",
-                    help="row-parallel GEMMs scatter their row blocks into the owners' memory from the epilogue")
+    ap.add_argument("--tp-pull-partials", action="store_true",
+                    help="the reduce-scatter pulls the partial blocks from the peers instead of the row-parallel GEMMs "
+                         "scattering them into the owners' memory from the epilogue (for A/B runs)")
     a = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -68,7 +69,7 @@ def main(argv=None) -> None:
         rows = B * (L + (L // C) * S)
         tp = TpContext(dist.group.WORLD, cfg.embed_dim, max_rows=rows, device=dev,
                        two_phase_min_size=a.tp_two_phase_min, fused_gather=False if a.tp_separate_gather else None,
-                       push_partials=a.tp_push_partials or None)
+                       push_partials=False if a.tp_pull_partials else None)
         local_cfg = tp_local_config(cfg, world)
     model = _random_model(local_cfg, dev, torch.bfloat16, seed=0)   # same seed: replicated tensors agree across ranks
     if tp is not None:

@@ -74,6 +74,18 @@ def bench_gemm(a) -> None:
     A = torch.randn((K, M) if a.a_mn else (M, K), device="cuda").bfloat16()
     B = torch.randn((K, N) if a.b_mn else (N, K), device="cuda").bfloat16()
     C = torch.empty(M, N, device="cuda", dtype=torch.float32 if a.fp32_out else torch.bfloat16)
+    if a.scatter_world > 0:
+        # GEMM -> reduce-scatter, producer side, as one process: the row blocks go to --scatter-world buffers of this GPU
+        import ctypes
+        W = a.scatter_world
+        shard = (M + W - 1) // W
+        outs = [torch.empty(shard, N, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+        ptrs = (ctypes.c_void_p * W)(*[o.data_ptr() for o in outs])
+        ms = timeit(lambda: _lib.call("ksa_gemm2_scatter_bf16", A, B, M, N, K, A.stride(0), B.stride(0), N, ptrs, W, shard),
+                    a.iters, a.warmup, not a.no_flush)
+        report(f"gemm {M}x{N}x{K} scattering its row blocks to {W} local buffers (CTA pairs, TMA stores)", ms,
+               flops=2.0 * M * N * K)
+        return
     ms = timeit(lambda: ops.gemm(A, B, a_mn_major=a.a_mn, b_mn_major=a.b_mn, out=C, pair=a.pair), a.iters, a.warmup,
                 not a.no_flush)
     report(f"gemm {M}x{N}x{K} a_mn={int(a.a_mn)} b_mn={int(a.b_mn)}" + (" (CTA pairs)" if a.pair else ""), ms,
@@ -330,6 +342,54 @@ def bench_ag_gemm(a) -> None:
         dist.destroy_process_group()
 
 
+def bench_gemm_rs(a) -> None:
+    """GEMM -> reduce-scatter + residual add + RMSNorm of tensor-parallel prefill, under ``torch.distributed.run``:
+    the row-parallel GEMM (``--m`` rows, ``--k`` local reduction length, ``--dim`` model width) followed by
+    ``ksa_tp_reduce_scatter_add_rmsnorm``, (a) with the partial blocks pulled from the peers by the reduction kernel
+    and (b) with the GEMM epilogue scattering every row block into its owner's memory (TMA stores), so that the
+    reduction reads local memory only.  Maximum over ranks; the gathers that follow are not part of either time."""
+    import torch.distributed as dist
+    from ..parallel.tp import TpContext
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    M, K, D = a.m, a.k, a.dim
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = (0.02 * torch.randn(D, K, device=dev)).bfloat16()
+    res_in = torch.randn(M, D, device=dev).bfloat16()
+    scale = torch.ones(D, device=dev).bfloat16()
+    out = {}
+    for push in (False, True):
+        tp = TpContext(dist.group.WORLD, D, max_rows=M, device=dev, two_phase_rows=256, two_phase_min_size=2,
+                       fused_gather=True, push_partials=push)
+
+        def step():
+            token = tp.row_parallel_linear(x, w, residual_rows=M if push else None)
+            tp.add_rms_norm(res_in, token, scale, 1e-6, defer_gather=True)
+            tp._pending, tp._res_event = None, None          # the gathers are not timed: drop them
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([timeit(step, a.iters, a.warmup, not a.no_flush)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[push] = float(t)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        dist.barrier()
+        tp.close()
+    if rank == 0:
+        pk = peaks()
+        flops = 2.0 * M * D * K
+        remote = (world - 1) * ((M + world - 1) // world) * D * 2.0
+        t_math, t_link = flops / (pk["tflops"] * 1e9), remote / (770.0 * 1e6)
+        print(f"gemm -> reduce-scatter + add + rmsnorm {M}x{D}x{K}, world {world}: pulled by the reduction "
+              f"{out[False]:.4f} ms | scattered by the GEMM epilogue {out[True]:.4f} ms ({out[False] / out[True]:.2f}x)",
+              flush=True)
+        print(f"  roofline of the pair: math {t_math:.4f} ms at {pk['src']} {pk['tflops']:.0f} TFLOP/s, link {t_link:.4f} ms "
+              f"at measured 770 GB/s -> {max(t_math, t_link) / out[True]:.2f} of the slower one", flush=True)
+    dist.destroy_process_group()
+
+
 def bench_tp_reduce(a) -> None:
     """The fused all-reduce + residual add + RMSNorm of tensor-parallel inference as ONE launch over ``--world``
     partial buffers of this GPU (the peers' flags are set beforehand, so nothing waits): the form a profiler can
@@ -357,7 +417,8 @@ def bench_tp_reduce(a) -> None:
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn", "comm", "tp-reduce", "ag-gemm"])
+    ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn", "comm", "tp-reduce", "ag-gemm",
+                                     "gemm-rs"])
     # the long spellings are for use under torch.distributed.run, whose own parser claims --m and --n as prefixes
     ap.add_argument("--m", "--gemm-m", dest="m", type=int, default=8192)
     ap.add_argument("--n", "--gemm-n", dest="n", type=int, default=4096)
@@ -365,6 +426,8 @@ def main(argv=None) -> None:
     ap.add_argument("--a-mn", action="store_true"); ap.add_argument("--b-mn", action="store_true")
     ap.add_argument("--fp32-out", action="store_true"); ap.add_argument("--compare", action="store_true")
     ap.add_argument("--pair", action="store_true", help="gemm: run on CTA pairs (tcgen05 cta_group::2)")
+    ap.add_argument("--scatter-world", type=int, default=0,
+                    help="gemm: scatter the row blocks of the product to this many buffers from the epilogue")
     ap.add_argument("--seq", type=int, default=8192); ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--hq", type=int, default=16); ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--dim", type=int, default=128); ap.add_argument("--chunk", type=int, default=128)
@@ -379,7 +442,7 @@ def main(argv=None) -> None:
     ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"])
     a = ap.parse_args(argv)
     {"gemm": bench_gemm, "gemv": bench_gemv, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn, "comm": bench_comm, "tp-reduce": bench_tp_reduce,
-     "ag-gemm": bench_ag_gemm}[a.what](a)
+     "ag-gemm": bench_ag_gemm, "gemm-rs": bench_gemm_rs}[a.what](a)
     _lib.check_status()
 
 
