@@ -10,6 +10,9 @@
     python -m ksa_b200.tools.kernel_bench comm --world 2      # the same kernels over buffers of one GPU
     python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 -m ksa_b200.tools.kernel_bench \
         ag-gemm --gemm-m 33024 --gemm-n 1536 --gemm-k 2560   # all-gather -> GEMM in one launch vs gather kernel + GEMM
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m ksa_b200.tools.kernel_bench \
+        gemm-rs --gemm-m 33024 --gemm-k 2048 --dim 2560      # GEMM -> reduce-scatter: scattered by the epilogue vs pulled
+    python -m ksa_b200.tools.kernel_bench gemm --pair --scatter-world 4 --m 33024 --n 2560 --k 2048   # the same GEMM alone
 
 Each line reports the median time, the achieved TFLOP/s or GB/s and, when ``MEASURED_PEAKS.json`` sits at the
 repository root, the fraction of the measured peak (cuBLAS bf16 burst / STREAM-style copy).  ``--iters 1 --warmup 1
