@@ -43,7 +43,7 @@ class TpContext:
         self.max_rows = max_rows
         self.device = device
         self.dtype = dtype
-        self.fused = device is not None and torch.device(device).type == "cuda"
+        self.fused = self._on_gpus(device)
         self.counter = 0            # all-reduces issued so far (identical on every rank)
         self.two_phase_rows = 0
         self.fused_gather = False
@@ -88,6 +88,11 @@ class TpContext:
             if self.fused_gather:
                 self._done = torch.zeros(_lib.GATHER_COUNTERS, dtype=torch.int32, device=device)
                 self._side = torch.cuda.Stream(device=device)
+
+    @staticmethod
+    def _on_gpus(device) -> bool:
+        """Whether the group exchanges through symmetric memory and the fused kernels (else: collectives)."""
+        return device is not None and torch.device(device).type == "cuda"
 
     def close(self) -> None:
         if self.fused:
