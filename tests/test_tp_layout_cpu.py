@@ -300,3 +300,57 @@ def test_few_rows_take_the_one_shot_all_reduce(fake_gpu, monkeypatch, T):
         torch.testing.assert_close(results[rank][0].float(), want_res.float(), atol=3e-2, rtol=3e-2)
         torch.testing.assert_close(results[rank][1].float(), want_y.float(), atol=3e-2, rtol=3e-2)
     assert "ksa_tp_allreduce_add_rmsnorm" in log and "ksa_gemm2_scatter_bf16" not in log and "gemm_gather" not in log
+
+
+@pytest.mark.parametrize("T", [2, 4])
+def test_sharded_model_prefill_matches_the_whole_model(fake_gpu, monkeypatch, T):
+    """The model's tensor-parallel wiring (deferred gathers, scattered row-parallel outputs, the last layer's
+    exception, the flush before the head) on 2 and 4 ranks against the unsharded model, logits of a whole prompt."""
+    from ksa_b200.config import get_preset
+    from ksa_b200.models import get_model_class
+    from ksa_b200.parallel.tp import build_tp_model
+    cfg = get_preset("qwen3-ksa-tiny").merge({"num_heads": 4, "num_kv_heads": 4, "head_dim": 32, "embed_dim": 128,
+                                              "intermediate_dim": 256, "num_layers": 3, "vocab_size": 512,
+                                              "summary_layer_freq": [1, 0, 1], "summary_chunk_size": 32,
+                                              "summary_sliding_chunk_num": 2, "summary_token_begin": 512})
+    torch.manual_seed(0)
+    full = get_model_class(cfg.model_class)(cfg)
+    full.init_weights(seed=0)
+    full = full.to(BF).eval()
+    tokens = torch.randint(0, cfg.vocab_size, (1, 96), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        want = full(tokens).float()
+    state = {k: v.clone() for k, v in full.state_dict().items()}
+    log, results = [], {}
+
+    def all_gather(parts, local, group=None):
+        sh = group.shared
+        sh.setdefault("ag", {})[group.rank] = local.clone()
+        sh["barrier"].wait()
+        for r in range(group.size):
+            parts[r].copy_(sh["ag"][r])
+        sh["barrier"].wait()
+    monkeypatch.setattr(dist, "all_gather", all_gather)
+
+    def body(rank, group):
+        if rank == 0:
+            call, gemm, gemm_gather = make_kernels(group.shared["mem"], group.shared["barrier"], log)
+            monkeypatch.setattr(_lib, "call", call)
+            monkeypatch.setattr(ops, "gemm", gemm)
+            monkeypatch.setattr(ops, "gemm_gather", gemm_gather)
+        group.shared["barrier"].wait()
+        rows = 96 + 3
+        tp = TpContext(group, cfg.embed_dim, max_rows=rows, device="cuda", two_phase_rows=32, two_phase_min_size=2,
+                       fused_gather=True, push_partials=True)
+        model = build_tp_model(state, cfg, tp, dtype=BF).eval()
+        with torch.no_grad():
+            results[rank] = model(tokens).float()
+        group.shared["barrier"].wait()
+        tp.close()
+
+    _run_ranks(T, body)
+    for rank in range(T):
+        err = (results[rank] - want).abs().max() / want.abs().max()
+        assert err < 5e-2, (rank, float(err))
+        assert torch.equal(results[rank], results[0]), "the ranks disagree about the logits"
+    assert "ksa_gemm2_scatter_bf16" in log and "gemm_gather" in log and "ksa_tp_reduce_scatter_add_rmsnorm" in log
