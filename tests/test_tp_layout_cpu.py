@@ -354,3 +354,64 @@ def test_sharded_model_prefill_matches_the_whole_model(fake_gpu, monkeypatch, T)
         assert err < 5e-2, (rank, float(err))
         assert torch.equal(results[rank], results[0]), "the ranks disagree about the logits"
     assert "ksa_gemm2_scatter_bf16" in log and "gemm_gather" in log and "ksa_tp_reduce_scatter_add_rmsnorm" in log
+
+
+def test_sharded_engine_prefill_and_decode_on_four_ranks(fake_gpu, monkeypatch):
+    """Prefill (two-phase form with both fused paths) and a few decode steps (one-shot all-reduce) of the inference
+    engine on 4 emulated ranks against the unsharded engine, fed with the same tokens."""
+    from ksa_b200.config import get_preset
+    from ksa_b200.inference.engine import KsaInferenceEngine
+    from ksa_b200.models import get_model_class
+    from ksa_b200.parallel.tp import build_tp_model
+    T = 4
+    cfg = get_preset("qwen3-ksa-tiny").merge({"num_heads": 4, "num_kv_heads": 4, "head_dim": 32, "embed_dim": 128,
+                                              "intermediate_dim": 256, "num_layers": 2, "vocab_size": 512,
+                                              "summary_layer_freq": [1, 0], "summary_chunk_size": 32,
+                                              "summary_sliding_chunk_num": 2, "summary_token_begin": 512})
+    torch.manual_seed(0)
+    full = get_model_class(cfg.model_class)(cfg)
+    full.init_weights(seed=0)
+    full = full.to(BF).eval()
+    prompt = torch.randint(0, cfg.vocab_size, (2, 80), generator=torch.Generator().manual_seed(9))
+    steps = 3
+
+    def run(model, feed=None):
+        eng = KsaInferenceEngine(model, max_len=256, batch=2)
+        outs = [eng.prefill(prompt)]
+        toks = [feed[0] if feed else outs[0].argmax(-1)]
+        for _ in range(steps):
+            outs.append(eng.decode_step(toks[-1]))
+            toks.append(feed[len(toks)] if feed else outs[-1].argmax(-1))
+        return torch.stack([o.float() for o in outs]), toks
+    want, toks = run(full)
+    state = {k: v.clone() for k, v in full.state_dict().items()}
+    log, results = [], {}
+
+    def all_gather(parts, local, group=None):
+        sh = group.shared
+        sh.setdefault("ag", {})[group.rank] = local.clone()
+        sh["barrier"].wait()
+        for r in range(group.size):
+            parts[r].copy_(sh["ag"][r])
+        sh["barrier"].wait()
+    monkeypatch.setattr(dist, "all_gather", all_gather)
+
+    def body(rank, group):
+        if rank == 0:
+            call, gemm, gemm_gather = make_kernels(group.shared["mem"], group.shared["barrier"], log)
+            monkeypatch.setattr(_lib, "call", call)
+            monkeypatch.setattr(ops, "gemm", gemm)
+            monkeypatch.setattr(ops, "gemm_gather", gemm_gather)
+        group.shared["barrier"].wait()
+        tp = TpContext(group, cfg.embed_dim, max_rows=2 * (80 + 3), device="cuda", two_phase_rows=32,
+                       two_phase_min_size=2, fused_gather=True, push_partials=True)
+        model = build_tp_model(state, cfg, tp, dtype=BF).eval()
+        results[rank] = run(model, feed=toks)[0]
+        group.shared["barrier"].wait()
+        tp.close()
+
+    _run_ranks(T, body)
+    for rank in range(T):
+        err = (results[rank] - want).abs().max() / want.abs().max()
+        assert err < 6e-2, (rank, float(err))
+    assert "ksa_gemm2_scatter_bf16" in log and "gemm_gather" in log and "ksa_tp_allreduce_add_rmsnorm" in log
