@@ -1,7 +1,11 @@
-// Device routines for communication over peer memory (weak loads ordered after a system-scope acquire of the
-// producer's flag; no read-only/non-coherent path, since the same addresses are rewritten every step), shared by the standalone kernels (comm.cu) and by the
-// communication CTAs of the GEMM kernel (gemm.cu).  All transfers are plain P2P loads/stores of 16 bytes per thread
-// through pointers into other GPUs' memory; waits on peer-written flags are bounded.
+// Device routines for communication over peer memory, shared by the standalone kernels (comm.cu) and by the
+// communication CTAs / communication warps of the GEMM kernels (gemm.cu, gemm2.cu).  Two transports:
+//   * plain P2P loads/stores of 16 bytes per thread through pointers into other GPUs' memory (weak loads ordered after
+//     a system-scope acquire of the producer's flag; no read-only/non-coherent path, since the same addresses are
+//     rewritten every step);
+//   * untiled bulk copies driven by one thread (peer memory -> shared-memory ring -> own memory), for a spare warp of
+//     a CTA whose other warps do tensor-core work.
+// Waits on peer-written flags and on the copy ring's barriers are bounded.
 #pragma once
 #include "common.cuh"
 
