@@ -1,6 +1,8 @@
 #!/usr/bin/env python
-"""Load a converted checkpoint with HF ``trust_remote_code`` and generate (counterpart of
-``examples/inference/inference.py`` of the reference): prints the completion and decode tokens/s."""
+"""Load a converted checkpoint and generate (counterpart of ``examples/inference/inference.py`` of the reference):
+prints the completion and tokens/s.  By default the checkpoint's ``trust_remote_code`` model runs under
+``transformers`` ``generate``, as in the reference; ``--engine`` runs this package's inference engine instead
+(ring-buffer KV cache, sm_100a kernels and CUDA-graph decode on a GPU)."""
 import argparse
 import time
 
@@ -18,9 +20,17 @@ def main():
     ap.add_argument("--temperature", type=float, default=0.7)
     ap.add_argument("--top-p", type=float, default=0.9)
     ap.add_argument("--greedy", action="store_true")
+    ap.add_argument("--engine", action="store_true", help="generate with ksa_b200's inference engine instead of HF generate")
     a = ap.parse_args()
     dtype = torch.bfloat16 if a.device.startswith("cuda") else torch.float32
-    model = AutoModelForCausalLM.from_pretrained(a.model_path, trust_remote_code=True, torch_dtype=dtype).to(a.device).eval()
+    if a.engine:
+        import os
+        import sys
+        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))   # repository root
+        from ksa_b200.tools.convert import load_hf_checkpoint
+        model = load_hf_checkpoint(a.model_path, device=a.device, dtype=dtype).eval()
+    else:
+        model = AutoModelForCausalLM.from_pretrained(a.model_path, trust_remote_code=True, torch_dtype=dtype).to(a.device).eval()
     tok = None
     if a.prompt_ids:
         ids = torch.tensor([[int(t) for t in a.prompt_ids.split(",")]], device=a.device)
@@ -32,8 +42,15 @@ def main():
             text = tok.apply_chat_template([{"role": "user", "content": a.prompt}], tokenize=False, add_generation_prompt=True)
         ids = tok(text, return_tensors="pt").input_ids.to(a.device)
     t0 = time.perf_counter()
-    out = model.generate(ids, max_new_tokens=a.max_new_tokens, do_sample=not a.greedy, temperature=a.temperature,
-                         top_p=a.top_p)
+    if a.engine:
+        from ksa_b200.inference import KsaInferenceEngine
+        eng = KsaInferenceEngine(model, max_len=ids.shape[1] + a.max_new_tokens + model.config.summary_chunk_size, batch=1)
+        with torch.no_grad():
+            out = eng.generate(ids, a.max_new_tokens, eos_id=model.config.eos_token_id,
+                               temperature=0.0 if a.greedy else a.temperature, top_p=a.top_p)
+    else:
+        out = model.generate(ids, max_new_tokens=a.max_new_tokens, do_sample=not a.greedy, temperature=a.temperature,
+                             top_p=a.top_p)
     if a.device.startswith("cuda"):
         torch.cuda.synchronize()
     dt = time.perf_counter() - t0

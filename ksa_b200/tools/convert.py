@@ -123,6 +123,47 @@ def hf_config_from_model_config(cfg) -> dict:
     return out
 
 
+def model_config_from_hf_config(hf: dict):
+    """The framework model config for an HF ``config.json`` written by ``hf_config_from_model_config`` (its inverse).
+
+    With independent summary parameters the HF embedding holds the summary-token rows after the text vocabulary
+    (``sync_vocab_size`` records that row count), so the text vocabulary ends where the summary tokens begin."""
+    from ..config.model_config import Qwen3Config, Qwen3SummaryAttentionConfig
+    common = dict(
+        vocab_size=hf["vocab_size"], embed_dim=hf["hidden_size"], intermediate_dim=hf["intermediate_size"],
+        num_layers=hf["num_hidden_layers"], num_heads=hf["num_attention_heads"],
+        num_kv_heads=hf.get("num_key_value_heads", hf["num_attention_heads"]),
+        head_dim=hf.get("head_dim", hf["hidden_size"] // hf["num_attention_heads"]),
+        norm_eps=hf.get("rms_norm_eps", 1e-6), rope_base=hf.get("rope_theta", 10000.0),
+        max_seq_len=hf.get("max_position_embeddings", 131072), tie_word_embeddings=hf.get("tie_word_embeddings", False),
+        q_norm=True, k_norm=True, rope_impl="hf")
+    if hf.get("eos_token_id") is not None:
+        common["eos_token_id"] = hf["eos_token_id"]
+    if not hf.get("use_summary_attention", False):
+        return Qwen3Config(**common)
+    n_sum, begin = hf.get("summary_token_num", 1), hf.get("summary_token_begin")
+    independent = hf.get("summary_independent_parameters", False)
+    if independent and begin is not None and begin + n_sum == hf["vocab_size"]:
+        common["vocab_size"] = begin
+    return Qwen3SummaryAttentionConfig(
+        use_summary_attention=True, summary_chunk_size=hf["summary_chunk_size"], summary_token_num=n_sum,
+        summary_token_begin=begin if begin is not None else common["vocab_size"],
+        summary_sliding_chunk_num=hf["summary_sliding_chunk_num"], summary_layer_freq=hf["summary_layer_freq"],
+        summary_chunk_position_ids_type=hf.get("summary_chunk_position_ids_type", "origin"),
+        summary_token_position_ids_type=hf.get("summary_token_position_ids_type", "last_chunk_slice_right"),
+        summary_independent_parameters=independent,
+        summary_independent_attention_layernorm=hf.get("summary_independent_attention_layernorm", False),
+        summary_independent_qk_norm=hf.get("summary_independent_qk_norm", False), **common)
+
+
+def load_hf_checkpoint(model_dir: str, device: str = "cpu", dtype=None):
+    """Build this package's model (for ``KsaInferenceEngine``) from a converted checkpoint directory: the architecture
+    from its ``config.json``, the weights from its safetensors under the Hugging Face parameter names."""
+    from ..models import get_model_class
+    cfg = model_config_from_hf_config(json.load(open(os.path.join(model_dir, "config.json"))))
+    return get_model_class(cfg.model_class).from_pretrained(model_dir, config=cfg, device=device, dtype=dtype)
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--dcp_path", required=True, help="training output dir containing global_step* subdirs")

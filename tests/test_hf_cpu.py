@@ -7,7 +7,8 @@ import torch
 from ksa_b200.config import get_preset
 from ksa_b200.inference import KsaInferenceEngine
 from ksa_b200.models import get_model_class
-from ksa_b200.tools.convert import convert_dcp_to_hf, hf_config_from_model_config
+from ksa_b200.tools.convert import (convert_dcp_to_hf, hf_config_from_model_config, load_hf_checkpoint,
+                                    model_config_from_hf_config)
 from ksa_b200.training.checkpoint import AppState, DistributedCheckpointer, save_checkpoint
 from ksa_b200.training.engine import TrainEngine
 
@@ -47,3 +48,21 @@ def test_hf_roundtrip_logits_and_generation(tmp_path):
     gen = hf.generate(tokens, max_new_tokens=12, eos_token_id=-1)
     ref = KsaInferenceEngine(model, max_len=64, batch=2).generate(tokens, 12)
     assert torch.equal(gen, ref)
+
+
+def test_converted_directory_loads_into_the_engine(tmp_path):
+    """The converted directory is enough to rebuild this package's model: config.json maps back to the model config
+    and the engine generates the same tokens as the model that was exported."""
+    import json
+    cfg, model, out = _export(tmp_path)
+    back = model_config_from_hf_config(json.load(open(os.path.join(out, "config.json"))))
+    for f in ("vocab_size", "embed_dim", "intermediate_dim", "num_layers", "num_heads", "num_kv_heads", "head_dim",
+              "summary_chunk_size", "summary_token_num", "summary_token_begin", "summary_sliding_chunk_num",
+              "summary_independent_parameters", "rope_base", "tie_word_embeddings"):
+        assert getattr(back, f) == getattr(cfg, f), f
+    assert list(back.get_layer_is_summary()) == list(cfg.get_layer_is_summary())
+    loaded = load_hf_checkpoint(out, dtype=torch.float32)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 37))
+    want = KsaInferenceEngine(model, max_len=64, batch=2).generate(tokens, 12)
+    got = KsaInferenceEngine(loaded, max_len=64, batch=2).generate(tokens, 12)
+    assert torch.equal(got, want)
