@@ -251,3 +251,44 @@ def test_segment_arithmetic_covers_every_chunk_once():
         for c in range(min(n, 64)):
             g = seg_of(n, c)
             assert begins[g] <= c < begins[g + 1]
+
+
+def test_device_segment_helpers_agree_with_the_model(tmp_path):
+    """``bulk_segs`` / ``bulk_seg_begin`` / ``bulk_seg_of`` of ``ksa_b200/csrc/comm.cuh`` (``__host__ __device__``),
+    compiled for the host, against the definitions above: every chunk lies in exactly the segment the helpers name,
+    for every segment count up to the maximum."""
+    import os
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("no nvcc on this machine")
+    csrc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "ksa_b200", "csrc")
+    src = tmp_path / "segcheck.cu"
+    src.write_text(r"""
+#include "comm.cuh"
+#include <cstdio>
+using namespace ksa;
+int main() {
+  long long bad = 0;
+  for (long long n = 1; n < 1500; ++n)
+    for (int S = 1; S <= kBulkSegs; ++S) {
+      if (bulk_seg_begin(n, S, 0) != 0 || bulk_seg_begin(n, S, S) != n) ++bad;
+      for (long long c = 0; c < n; ++c) {
+        const int g = bulk_seg_of(n, S, c);
+        if (g < 0 || g >= S || bulk_seg_begin(n, S, g) > c || bulk_seg_begin(n, S, g + 1) <= c) ++bad;
+      }
+    }
+  printf("%lld %d %d %d %d %d\n", bad, kBulkSegs, bulk_segs(10320, 148, 4), bulk_segs(5160, 148, 4), bulk_segs(2580, 148, 4),
+         bulk_segs(10320, 148, 1));
+  return 0;
+}
+""")
+    exe = tmp_path / "segcheck"
+    subprocess.run([nvcc, "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", csrc, "-o", str(exe), str(src)],
+                   check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert out[0] == "0", f"{out[0]} chunks fall outside the segment the helpers name"
+    assert int(out[1]) == SEGS
+    # 84.5 MB, 42 MB and 21 MB shards moved by 148 CTAs: 4, 2 and 1 segments; a cap of 1 gives per-shard counters
+    assert [int(v) for v in out[2:]] == [4, 2, 1, 1]
