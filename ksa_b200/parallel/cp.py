@@ -81,7 +81,7 @@ class CpContext:
         self.batch = batch
         self.kv_width = 2 * n_kv_heads * head_dim          # K | V per row
         self.device = device
-        self.fused = device is not None and torch.device(device).type == "cuda"
+        self.fused = self._on_gpus(device)
         self.counter = 0                                    # forward exchanges issued so far (same on every rank)
         self.counter_bwd = 0                                # backward exchanges (they use their own slots and flags)
         self.slot_last = [None, None, None, None]           # exchange number of each slot's previous use
@@ -117,6 +117,11 @@ class CpContext:
                 self.a2a_buf = SymmetricBuffer(2 * self.a2a_slot_bytes, group, device)
                 self.a2a_ready = SignalPad(2 * self.size, group, device)
                 self.a2a_consumed = SignalPad(2 * self.size, group, device)
+
+    @staticmethod
+    def _on_gpus(device) -> bool:
+        """Whether the group exchanges through symmetric memory and P2P kernels (else: collectives)."""
+        return device is not None and torch.device(device).type == "cuda"
 
     def close(self) -> None:
         if self.fused:
