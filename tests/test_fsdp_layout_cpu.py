@@ -1,0 +1,158 @@
+"""The fused FSDP back end (``ksa_b200/parallel/fsdp.py`` with ``comm="fused"``: symmetric parameter and gradient
+buffers, per-unit flags, pull all-gather, reduce-scatter + AdamW on the shard owner) on 2 and 4 ranks without a GPU.
+
+Every rank is a thread with its own engine; symmetric buffers are CPU tensors reachable through their addresses and
+the communication kernels are Python stand-ins that honour the same pointers, shard ranges, hyper-parameter vector and
+flag values.  On CPU the weight gradients reach the fp32 buffers only after backward (autograd ``.grad``), so the
+hooks that start a unit's reduction in the middle of backward are switched off and every unit is reduced at the
+optimizer step: what is checked is the sharding, the flag protocol and the gather schedule of each overlap mode, not
+the overlap itself.  The result is compared with single-process training on the same micro-batches.
+"""
+import contextlib
+import copy
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from ksa_b200.models import get_model_class
+from ksa_b200.ops import _lib
+from ksa_b200.parallel import symm
+from ksa_b200.parallel.fsdp import FsdpEngine
+from ksa_b200.training.engine import TrainEngine
+
+from test_cp_layout_cpu import ZeroedSymm, _raw, make_cp_kernels
+from test_fsdp_cpu import _tiny
+from test_tp_layout_cpu import _FakeEvent, _FakeStream, _ptrs, _run_ranks
+
+
+def make_fsdp_kernels(mem, log):
+    base = make_cp_kernels(mem, log)          # ksa_signal_set / ksa_signal_wait and the flag helpers' semantics
+
+    def flag_value(ptr):
+        return int(_raw(mem, ptr, 4).view(torch.int32)[0])
+
+    def wait(ptr, target):
+        import time
+        t0 = time.monotonic()
+        while flag_value(ptr) < target:
+            if time.monotonic() - t0 > 60:
+                raise AssertionError(f"a wait for flag value {target} ran out (flag holds {flag_value(ptr)})")
+            time.sleep(0.0005)
+
+    def target_of(epoch, add):
+        return (int(epoch[0]) if epoch is not None else 0) + add
+
+    def call(name, *a):
+        if name == "ksa_peer_gather":
+            log.append(name)
+            ptrs, world, rank, shard_elems, elem_bytes, ready, epoch, add, _ctas = a
+            ptrs, n = _ptrs(ptrs, world), shard_elems * elem_bytes
+            for step in range(1, world):
+                r = (rank + step) % world
+                if ready is not None:
+                    wait(ready + 4 * r, target_of(epoch, add))
+                _raw(mem, ptrs[rank] + r * n, n).copy_(_raw(mem, ptrs[r] + r * n, n))
+        elif name == "ksa_peer_reduce_adamw":
+            log.append(name)
+            (grads, world, rank, shard_lo, n, master, m, v, out, hyper, b1, b2, eps, wd, clip, sumsq, ready, epoch, add,
+             _ctas) = a
+            if ready is not None:
+                for r in range(world):
+                    wait(ready + 4 * r, target_of(epoch, add))
+            g = torch.zeros(n)
+            for p in _ptrs(grads, world):
+                g += _raw(mem, p + 4 * shard_lo, 4 * n).view(torch.float32)
+            lr, bc1, bc2, gscale = (float(x) for x in hyper)
+            g = g * gscale
+            if sumsq is not None:
+                sumsq += (g * g).sum()
+            if clip > 0:
+                g = g.clamp(-clip, clip)
+            m.mul_(b1).add_(g, alpha=1 - b1)
+            v.mul_(b2).addcmul_(g, g, value=1 - b2)
+            master.mul_(1 - lr * wd).sub_(lr * (m / bc1) / ((v / bc2).sqrt() + eps))
+            if out is not None:
+                out[shard_lo:shard_lo + n].copy_(master)
+        else:
+            base(name, *a)
+    return call
+
+
+@pytest.fixture
+def fake_fsdp_gpu(monkeypatch):
+    monkeypatch.setattr(symm, "SymmetricBuffer", ZeroedSymm)
+    monkeypatch.setattr(dist, "get_rank", lambda g=None: g.rank)
+    monkeypatch.setattr(dist, "get_world_size", lambda g=None: g.size)
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda device=None: None)
+    monkeypatch.setattr(torch.cuda, "Stream", lambda device=None: _FakeStream())
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda device=None: _FakeStream())
+    monkeypatch.setattr(torch.cuda, "stream", lambda s: contextlib.nullcontext())
+    monkeypatch.setattr(torch.cuda, "Event", lambda **kw: _FakeEvent())
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
+    # CPU autograd fills .grad after the boundary hooks have fired: reduce every unit at the optimizer step instead
+    monkeypatch.setattr(FsdpEngine, "_backward_reached", lambda self, tag: None)
+    yield
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("overlap", ["stream", "gemm2"])
+def test_fused_fsdp_matches_single_process_training(fake_fsdp_gpu, monkeypatch, world, overlap):
+    steps = 3
+    cfg = _tiny()
+    torch.manual_seed(0)
+    base = get_model_class(cfg.model_class)(cfg)
+    base.init_weights(seed=0)
+    base = base.to(torch.bfloat16)
+    g = torch.Generator().manual_seed(7)
+    data = torch.randint(0, cfg.vocab_size, (steps, world, 1, 257), generator=g)
+    log, results = [], {}
+
+    def body(rank, group):
+        if rank == 0:
+            monkeypatch.setattr(_lib, "call", make_fsdp_kernels(group.shared["mem"], log))
+        group.shared["barrier"].wait()
+        model = copy.deepcopy(base)
+        eng = FsdpEngine(model, lr=1e-2, weight_decay=0.1, clip_value=1.0, world_size=world, rank=rank, group=group,
+                         comm="fused", overlap=overlap, param_dtype=torch.bfloat16, device="cpu",
+                         pair_gather_min_flops=0.0)
+        losses = []
+        for s in range(steps):
+            t = data[s, rank]
+            losses.append(float(eng.train_step(t[:, :-1].contiguous(), t[:, 1:].contiguous())))
+        group.shared["barrier"].wait()
+        eng._write_hyper()                   # pull the last update of every unit, as the next forward would
+        eng._overlap_active = False
+        for ui in range(len(eng.units)):
+            eng._gather_now(ui)
+        group.shared["barrier"].wait()
+        results[rank] = (losses, {n: p.detach().float().clone() for n, p in model.named_parameters()},
+                         float(eng.grad_sq))
+        eng.close()
+
+    _run_ranks(world, body)
+    ref_model = copy.deepcopy(base)
+    ref = TrainEngine(ref_model, lr=1e-2, weight_decay=0.1, clip_value=1.0, grad_accum_steps=world,
+                      param_dtype=torch.bfloat16)
+    ref_losses = []
+    for s in range(steps):
+        for r in range(world):
+            t = data[s, r]
+            ref_losses.append(float(ref.train_step(t[:, :-1].contiguous(), t[:, 1:].contiguous())))
+    for r in range(world):
+        for s in range(steps):
+            assert abs(results[r][0][s] - ref_losses[s * world + r]) < 3e-2, (r, s, results[r][0], ref_losses)
+    want = {n: p.detach().float() for n, p in ref_model.named_parameters()}
+    for r in range(world):
+        for n, w in want.items():
+            got = results[r][1][n]
+            # The single process adds its micro-batch gradients up in bf16 (.grad), the ranks' gradients are summed in
+            # fp32: where the sum is close to zero the first Adam steps (size lr, sign of the gradient) can differ.
+            # A shard that was not reduced, updated or gathered would be off in a quarter or more of the elements.
+            off = int(((got - w).abs() > 1.2e-2).sum())       # more than one step of size lr, or one bf16 ulp at 1.0
+            assert off <= max(2, got.numel() // 100), (r, n, off, got.numel())
+            assert (got - w).norm() <= 6e-2 * w.norm().clamp_min(1e-3), (r, n, float((got - w).norm()), float(w.norm()))
+            assert torch.equal(got, results[0][1][n]), f"ranks disagree about {n}"
+    total_sq = sum(results[r][2] for r in range(world))        # every rank holds the sum over its shards
+    assert abs(total_sq ** 0.5 - float(ref.grad_norm())) < 5e-2 * float(ref.grad_norm())
+    assert "ksa_peer_gather" in log and "ksa_peer_reduce_adamw" in log and "ksa_signal_set" in log
