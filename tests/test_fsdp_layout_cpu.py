@@ -1,5 +1,5 @@
 """The fused FSDP back end (``ksa_b200/parallel/fsdp.py`` with ``comm="fused"``: symmetric parameter and gradient
-buffers, per-unit flags, pull all-gather, reduce-scatter + AdamW on the shard owner) on 2 and 4 ranks without a GPU.
+buffers, per-unit flags, pull all-gather, reduce-scatter + AdamW on the shard owner) on 2, 4 and 8 ranks without a GPU.
 
 Every rank is a thread with its own engine; symmetric buffers are CPU tensors reachable through their addresses and
 the communication kernels are Python stand-ins that honour the same pointers, shard ranges, hyper-parameter vector and
@@ -95,8 +95,7 @@ def fake_fsdp_gpu(monkeypatch):
     yield
 
 
-@pytest.mark.parametrize("world", [2, 4])
-@pytest.mark.parametrize("overlap", ["stream", "gemm2"])
+@pytest.mark.parametrize("world,overlap", [(2, "stream"), (2, "gemm2"), (4, "stream"), (4, "gemm2"), (8, "stream")])
 def test_fused_fsdp_matches_single_process_training(fake_fsdp_gpu, monkeypatch, world, overlap):
     steps = 3
     cfg = _tiny()
