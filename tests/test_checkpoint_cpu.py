@@ -84,3 +84,36 @@ def test_convert_dcp_to_hf(tmp_path):
     model.load_state_dict(model.convert_hf_state_dict(hf))
     for (n, a), (_, b) in zip(model.state_dict().items(), eng.model.state_dict().items()):
         assert torch.allclose(a, b.float()), n
+
+
+def test_dcp2torch_single_file_and_safetensors(tmp_path):
+    """``python -m ksa_b200.tools.dcp2torch``: a checkpoint becomes one ``torch.save`` file (model only, or everything)
+    or sharded safetensors, with the parameter names (the reference's) and values of the model that was saved."""
+    from safetensors.torch import load_file
+    from ksa_b200.tools import dcp2torch
+    eng, cfg = _engine()
+    _train(eng, cfg, 2)
+    save_checkpoint(AppState(eng), DistributedCheckpointer(), str(tmp_path), 2)
+    dcp = get_checkpoint_path(str(tmp_path), 2) if callable(get_checkpoint_path) else os.path.join(str(tmp_path), "global_step2")
+    want = {k: v.detach() for k, v in eng.model.muse_state_dict().items()}    # checkpoints use the reference's names
+    # one file, model only
+    dcp2torch.main([dcp, str(tmp_path / "model.pt")])
+    got = torch.load(str(tmp_path / "model.pt"), weights_only=True)
+    assert set(got) == set(want)
+    for k in want:
+        assert torch.equal(got[k].to(want[k].dtype), want[k]), k
+    # one file, everything: optimizer and training state travel too
+    dcp2torch.main([dcp, str(tmp_path / "all.pt"), "--all"])
+    everything = torch.load(str(tmp_path / "all.pt"), weights_only=False)
+    flat = json.dumps(sorted(str(k) for k in everything))
+    assert "app" in flat
+    # sharded safetensors into a directory
+    dcp2torch.main([dcp, str(tmp_path / "st"), "--safetensors"])
+    files = [f for f in os.listdir(tmp_path / "st") if f.endswith(".safetensors")]
+    assert files
+    loaded = {}
+    for f in files:
+        loaded.update(load_file(str(tmp_path / "st" / f)))
+    assert set(loaded) == set(want)
+    for k in want:
+        assert torch.equal(loaded[k].to(want[k].dtype), want[k]), k
