@@ -418,7 +418,7 @@ def bench_tp_reduce(a) -> None:
     print(f"  max abs error of the residual stream vs fp32: {err:.3e}", flush=True)
 
 
-def main(argv=None) -> None:
+def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn", "comm", "tp-reduce", "ag-gemm",
                                      "gemm-rs"])
@@ -443,7 +443,11 @@ def main(argv=None) -> None:
     ap.add_argument("--mbytes", type=int, default=256, help="comm: size of the fp32 gradient unit in MiB")
     ap.add_argument("--ctas", type=int, default=64, help="comm: CTAs of the communication kernels")
     ap.add_argument("--cp-full-layers", default="auto", choices=["auto", "ulysses", "halo"])
-    a = ap.parse_args(argv)
+    return ap
+
+
+def main(argv=None) -> None:
+    a = build_parser().parse_args(argv)
     {"gemm": bench_gemm, "gemv": bench_gemv, "attn": bench_attn, "decode": bench_decode, "norm": bench_norm, "cp-attn": bench_cp_attn, "comm": bench_comm, "tp-reduce": bench_tp_reduce,
      "ag-gemm": bench_ag_gemm, "gemm-rs": bench_gemm_rs}[a.what](a)
     _lib.check_status()

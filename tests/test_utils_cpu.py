@@ -215,3 +215,24 @@ def test_small_helpers():
         st.tick()
     s = st.summary()
     assert s["steps"] == 3 and s["min_ms"] >= 1.0
+
+
+def test_benchmark_flags_survive_the_torchrun_parser():
+    """``torch.distributed.run`` parses abbreviations of its own options before the script's arguments are split off
+    (``--m`` is ambiguous there): the multi-GPU benchmark modes are documented with spellings that pass through."""
+    from torch.distributed.run import get_args_parser
+    from ksa_b200.tools import infer_bench, kernel_bench
+    launcher = get_args_parser()
+    for module, argv in (
+            ("ksa_b200.tools.kernel_bench", ["ag-gemm", "--gemm-m", "33024", "--gemm-n", "1536", "--gemm-k", "2560"]),
+            ("ksa_b200.tools.kernel_bench", ["gemm-rs", "--gemm-m", "33024", "--gemm-k", "2048", "--dim", "2560"]),
+            ("ksa_b200.tools.kernel_bench", ["cp-attn", "--seq", "32768", "--bwd"]),
+            ("ksa_b200.tools.infer_bench", ["--prompt-len", "32768", "--decode", "0", "--tp-two-phase-min", "2",
+                                            "--tp-separate-gather", "--tp-pull-partials"])):
+        a = launcher.parse_args(["--nproc-per-node", "2", "--master-addr", "127.0.0.1", "-m", module] + argv)
+        assert a.training_script == module and a.training_script_args == argv
+    k = kernel_bench.build_parser().parse_args(["ag-gemm", "--gemm-m", "33024", "--gemm-n", "1536", "--gemm-k", "2560"])
+    assert (k.m, k.n, k.k) == (33024, 1536, 2560)
+    k = kernel_bench.build_parser().parse_args(["gemm", "--m", "128", "--pair", "--scatter-world", "4"])
+    assert k.m == 128 and k.pair and k.scatter_world == 4
+    assert infer_bench is not None
