@@ -123,6 +123,45 @@ def test_tensor_parallel_partial_slots(T):
     assert all(status[r] == 5 for r in range(1, T))
 
 
+def tp_rank_scatter(rank, T, E, recv, flags, status, slots=2):
+    """All-reduce e in the scattered form: the row-parallel GEMM of rank r stores its partial of p's rows into block r
+    of slot (e-1) % slots ON RANK p (P2P stores from the epilogue), the reduction kernel then announces, waits for every
+    peer's announcement and reads only its own slot."""
+    for e in range(1, E + 1):
+        s = (e - 1) % slots
+        for p in range(T):                                   # the epilogue's stores land one owner after the other
+            recv[p][s][rank] = ("partial", rank, e)
+            yield
+        for p in range(T):
+            flags[p][rank] = max(flags[p][rank], e)
+            yield
+        for p in range(T):
+            yield from wait_ge(lambda p=p: flags[rank][p], e, status, rank)
+        for q in range(T):
+            assert recv[rank][s][q] == ("partial", q, e), f"rank {rank} summed a block of another all-reduce from rank {q}"
+            yield
+
+
+@pytest.mark.parametrize("T", [2, 4, 8])
+def test_tensor_parallel_scattered_partials_two_slots(T):
+    """The peers write into a rank's slot while it may still be reducing the previous all-reduce: two slots are enough,
+    because a peer can only start the GEMM of all-reduce e+2 after this rank has announced e+1, i.e. after its
+    reduction of e has ended."""
+    for seed in range(20):
+        rng = random.Random(seed)
+        recv = [[[None] * T for _ in range(2)] for _ in range(T)]      # recv[on rank][slot][from rank]
+        flags = [[0] * T for _ in range(T)]
+        status = [0] * T
+        run([tp_rank_scatter(r, T, 9, recv, flags, status) for r in range(T)], rng)
+        assert status == [0] * T
+    with pytest.raises(AssertionError, match="another all-reduce"):
+        for seed in range(40):
+            rng = random.Random(seed)
+            recv = [[[None] * 3 for _ in range(1)] for _ in range(3)]
+            flags = [[0] * 3 for _ in range(3)]
+            run([tp_rank_scatter(r, 3, 6, recv, flags, [0] * 3, slots=1) for r in range(3)], rng)
+
+
 def test_one_slot_would_not_be_enough():
     """The models are not vacuous: with a single slot a fast rank overwrites a block that a slow peer still reads."""
     def tp_one_slot(rank, T, E, partial, flags, status):
