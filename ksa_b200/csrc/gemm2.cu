@@ -546,6 +546,7 @@ KSA_API int ksa_gemm2_scatter_bf16(const void* a, const void* b, int M, int N, i
   KSA_REQUIRE(lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0 && N % 8 == 0, "gemm2_scatter: leading dimensions and N must be multiples of 8");
   KSA_REQUIRE(world >= 1 && world <= kMaxPeers && shard_rows > 0, "gemm2_scatter: world %d / shard rows %d out of range", world, shard_rows);
   KSA_REQUIRE((long long)shard_rows * world >= M, "gemm2_scatter: %d shards of %d rows do not cover %d rows", world, shard_rows, M);
+  KSA_REQUIRE(ldc >= N, "gemm2_scatter: row pitch %lld of the owners' buffers is smaller than N = %d", ldc, N);
   Gemm2Epilogue ep{};
   ep.ldc = ldc; ep.alpha = 1.f; ep.c_shard_rows = shard_rows; ep.c_world = world;
   for (int r = 0; r < world; ++r) {
