@@ -253,3 +253,51 @@ def test_bulk_ring_model_catches_a_missing_store_wait():
             rng = random.Random(seed)
             state = {"out": [], "done": [], "stop": False}
             run(list(_ring_thread(2, [9, 9], rng, state, forget_store_wait=True)), rng)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Staging buffers of the scattering epilogue (ksa_b200/csrc/gemm2.cu): every epilogue warp owns two 4 KB buffers; piece
+# p of the accumulator is packed into buffer p % 2 and sent with a TMA store that reads the buffer asynchronously.
+# Before the first write of a piece the warp waits until at most the newest store is still reading
+# (cp.async.bulk.wait_group.read 1), which is the store of piece p - 1, in the other buffer.
+def _staging_warp(pieces, rng, state, wait_allowance=1):
+    stores = []                      # (buffer, piece) stores that still read their buffer, oldest first
+    buf = [None, None]
+
+    def warp():
+        for p in range(pieces):
+            b = p % 2
+            while len(stores) > wait_allowance:          # wait_group.read <allowance>
+                yield
+            assert all(sb != b for sb, _ in stores), "a staging buffer was rewritten while a store still reads it"
+            buf[b] = ("half0", p)
+            yield
+            buf[b] = ("full", p)
+            stores.append((b, p))
+            yield
+        while stores:                                    # wait_group 0 before the kernel ends
+            yield
+        state["stop"] = True
+
+    def engine():
+        while not state["stop"]:
+            if stores and rng.random() < 0.4:
+                b, p = stores.pop(0)
+                assert buf[b] == ("full", p), "a store read a buffer that holds another piece"
+                state["out"].append(p)
+            yield
+    return warp(), engine()
+
+
+def test_epilogue_staging_buffers():
+    for seed in range(30):
+        rng = random.Random(seed)
+        state = {"out": [], "stop": False}
+        run(list(_staging_warp(13, rng, state)), rng)
+        assert state["out"] == list(range(13))
+    # not vacuous: allowing two stores in flight lets piece p overwrite the buffer that the store of piece p - 2 reads
+    with pytest.raises(AssertionError, match="rewritten|another piece"):
+        for seed in range(40):
+            rng = random.Random(seed)
+            state = {"out": [], "stop": False}
+            run(list(_staging_warp(13, rng, state, wait_allowance=2)), rng)
