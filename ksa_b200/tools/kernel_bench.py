@@ -328,6 +328,17 @@ def bench_ag_gemm(a) -> None:
         return float(t)
 
     t_sep, t_fused = timed(separate), timed(fused)
+    t_lib = None
+    if multi and a.compare:
+        # the library pair: NCCL all-gather of the row shards into a fresh buffer, then cuBLAS (torch.matmul)
+        mine = own[rank * shard:(rank + 1) * shard].clone()
+        gathered = torch.empty(shard * world, K, dtype=torch.bfloat16, device=dev)
+        out_lib = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+
+        def library():
+            dist.all_gather_into_tensor(gathered, mine)
+            torch.matmul(gathered[:M], W.t(), out=out_lib)
+        t_lib = timed(library)
     ref = own[:M].float() @ W.float().t() if M * N <= (1 << 26) else None
     err = (out.float() - ref).abs().max().item() / ref.abs().max().item() if ref is not None else float("nan")
     _lib.check_status()
@@ -338,6 +349,8 @@ def bench_ag_gemm(a) -> None:
         where = "GPUs" if multi else "local buffers"
         print(f"all-gather -> gemm {M}x{N}x{K}, world {world} ({where}): gather kernel + pair GEMM {t_sep:.4f} ms | "
               f"one launch {t_fused:.4f} ms ({t_sep / t_fused:.2f}x)", flush=True)
+        if t_lib is not None:
+            print(f"  NCCL all-gather + cuBLAS (torch.matmul): {t_lib:.4f} ms ({t_lib / t_fused:.2f}x the one launch)", flush=True)
         print(f"  roofline: math {t_math:.4f} ms at {pk['src']} {pk['tflops']:.0f} TFLOP/s, link {t_link:.4f} ms at measured "
               f"770 GB/s -> {max(t_math, t_link) / t_fused:.2f} of the slower one; max rel error {err:.2e}", flush=True)
     if multi:
