@@ -193,7 +193,7 @@ class KsaDecoderLayer(nn.Module):
                 att = cp_attention_packed(qkv, meta.cp, Hq, Hkv, Dh, self.window_chunks, True)
             else:
                 att = ops.attention_packed(qkv, meta.B, meta.L, meta.Ns, Hq, Hkv, Dh, meta.chunk, meta.n_sum,
-                                           self.window_chunks)
+                                           self.window_chunks, mode=getattr(cfg, "summary_attention_mode", "kernel"))
             attn_out = _row_linear(tp, att, a.output_proj.weight, rows_attn)
             if collect is not None:
                 collect.append(attn_out[:n_text])

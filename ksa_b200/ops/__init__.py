@@ -687,14 +687,22 @@ class _PackedAttentionFn(torch.autograd.Function):
 
 def attention_packed(qkv: torch.Tensor, B: int, L: int, Ns: int, Hq: int, Hkv: int, D: int, chunk: int = 128,
                      n_sum: int = 1, window: int = UNBOUNDED_WINDOW, tok_window: int = 0,
-                     scale: Optional[float] = None) -> torch.Tensor:
-    """KSA (``Ns > 0``) or causal (``Ns = 0``) attention on packed rotated rows; see :class:`_PackedAttentionFn`."""
+                     scale: Optional[float] = None, mode: str = "kernel") -> torch.Tensor:
+    """KSA (``Ns > 0``) or causal (``Ns = 0``) attention on packed rotated rows; see :class:`_PackedAttentionFn`.
+
+    ``mode`` selects the summary-attention implementation like the reference's ``summary_attention_mode``
+    (``muse/layers/summary_attention_func.py:506-584``): ``"kernel"`` (the sm_100a kernels on a GPU, the dense oracle
+    on CPU), ``"mask"`` (dense boolean mask, plain PyTorch, any device) or ``"block"`` (query blocks with gathered
+    keys, plain PyTorch, any device)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if not _cuda(qkv):
+    if mode not in ("kernel", "mask", "block"):
+        raise ValueError(f"unknown summary attention mode {mode!r}")
+    if not _cuda(qkv) or (Ns > 0 and mode != "kernel"):
         q, k, v = _packed_views(qkv, B, L, Hq, Hkv, D, 0)
         if Ns > 0:
             qs, ks, vs = _packed_views(qkv, B, Ns, Hq, Hkv, D, B * L)
-            o_t, o_s = ref.ksa_attention(q, k, v, qs, ks, vs, chunk, n_sum, window, scale)
+            fn = ref.ksa_attention_blockwise if mode == "block" else ref.ksa_attention
+            o_t, o_s = fn(q, k, v, qs, ks, vs, chunk, n_sum, window, scale)
             return torch.cat([o_t.reshape(B * L, Hq * D), o_s.reshape(B * Ns, Hq * D)], dim=0)
         return ref.causal_attention(q, k, v, scale, tok_window if tok_window > 0 else -1).reshape(B * L, Hq * D)
     _require_bf16(qkv)

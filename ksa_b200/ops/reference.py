@@ -127,6 +127,54 @@ def ksa_attention(q_t, k_t, v_t, q_s, k_s, v_s, chunk: int, n_sum: int, window: 
     return o_t.to(q_t.dtype), o_s.to(q_s.dtype)
 
 
+def ksa_attention_blockwise(q_t, k_t, v_t, q_s, k_s, v_s, chunk: int, n_sum: int, window: int,
+                            scale: Optional[float] = None, q_block: int = 4096):
+    """The same attention as :func:`ksa_attention` without the ``O(L^2)`` mask: the queries are processed in blocks of
+    ``q_block`` rows, and every block gathers only the keys it can see (the text of its own chunks and of the
+    ``window`` chunks before them, the summaries of older chunks) with a compact mask of that size (the reference's
+    ``"block"`` mode, ``muse/layers/summary_attention_func.py:194-457``).  Memory is ``O(q_block * (window * chunk +
+    q_block + L / chunk * n_sum))``; plain PyTorch, differentiable, any device."""
+    B, L, Hq, D = q_t.shape
+    Ns = q_s.shape[1]
+    n_rep = Hq // k_t.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    q_block = max(chunk, q_block // chunk * chunk)                 # whole chunks per block
+    dev = q_t.device
+    out_t = []
+    for q0 in range(0, L, q_block):
+        q1 = min(L, q0 + q_block)
+        c0, c1 = q0 // chunk, (q1 - 1) // chunk                    # first and last chunk of the block
+        k0 = max(0, c0 - window) * chunk                           # first visible text key
+        s1 = min(max(0, c1 - window) * n_sum, Ns)                  # summaries of chunks older than the last chunk's window
+        tq = torch.arange(q0, q1, device=dev)[:, None]
+        tk = torch.arange(k0, q1, device=dev)[None, :]
+        m_text = (tk <= tq) & (tq // chunk - tk // chunk <= window)
+        sk = torch.arange(s1, device=dev)[None, :] // max(n_sum, 1)
+        m_sum = (tq // chunk - sk) > window
+        k_all = torch.cat([_expand_kv(k_t[:, k0:q1], n_rep), _expand_kv(k_s[:, :s1], n_rep)], dim=1)
+        v_all = torch.cat([_expand_kv(v_t[:, k0:q1], n_rep), _expand_kv(v_s[:, :s1], n_rep)], dim=1)
+        o, _ = _masked_attention(q_t[:, q0:q1], k_all, v_all, torch.cat([m_text, m_sum], dim=1), scale)
+        out_t.append(o)
+    out_s = []
+    s_block = max(n_sum, q_block // chunk * n_sum)                 # summary rows of q_block text rows
+    for r0 in range(0, Ns, s_block):
+        r1 = min(Ns, r0 + s_block)
+        c0, c1 = r0 // n_sum, (r1 - 1) // n_sum
+        t0, t1 = c0 * chunk, min(L, (c1 + 1) * chunk)              # the text of the block's own chunks
+        sq = torch.arange(r0, r1, device=dev)[:, None]
+        tk = torch.arange(t0, t1, device=dev)[None, :]
+        sk = torch.arange(r0, r1, device=dev)[None, :]
+        m_text = (sq // n_sum) == (tk // chunk)
+        m_sum = ((sq // n_sum) == (sk // n_sum)) & ((sk % n_sum) <= (sq % n_sum))
+        k_all = torch.cat([_expand_kv(k_t[:, t0:t1], n_rep), _expand_kv(k_s[:, r0:r1], n_rep)], dim=1)
+        v_all = torch.cat([_expand_kv(v_t[:, t0:t1], n_rep), _expand_kv(v_s[:, r0:r1], n_rep)], dim=1)
+        o, _ = _masked_attention(q_s[:, r0:r1], k_all, v_all, torch.cat([m_text, m_sum], dim=1), scale)
+        out_s.append(o)
+    o_t = torch.cat(out_t, dim=1).to(q_t.dtype)
+    o_s = (torch.cat(out_s, dim=1) if out_s else q_s.new_zeros(q_s.shape)).to(q_s.dtype)
+    return o_t, o_s
+
+
 def causal_attention(q, k, v, scale: Optional[float] = None, window: int = -1,
                      cu_seqlens: Optional[torch.Tensor] = None):
     """Causal (optionally token-sliding-window, optionally packed-document) attention.

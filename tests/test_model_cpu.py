@@ -159,3 +159,37 @@ def test_muse_and_hf_key_roundtrip():
     other.load_state_dict(other.convert_hf_state_dict(hf))
     for (k, a), (_, b) in zip(model.state_dict().items(), other.state_dict().items()):
         assert torch.equal(a, b), k
+
+
+def test_summary_attention_modes_agree():
+    """``summary_attention_mode`` "mask" (dense mask) and "block" (query blocks with gathered keys) give the same model
+    output and gradients as the default; the block form alone is also checked against the dense oracle on ragged
+    shapes."""
+    import torch
+    from ksa_b200.config import get_preset
+    from ksa_b200.models import get_model_class
+    from ksa_b200.ops import reference as ref
+    torch.manual_seed(0)
+    for (L, C, S, W, qb) in [(256, 32, 1, 2, 64), (192, 16, 2, 1, 48), (100, 32, 1, 1, 32), (257, 16, 2, 3, 64)]:
+        B, Hq, Hkv, D = 2, 4, 2, 16
+        Ns = ((L + C - 1) // C) * S
+        q, k, v = torch.randn(B, L, Hq, D), torch.randn(B, L, Hkv, D), torch.randn(B, L, Hkv, D)
+        qs, ks, vs = torch.randn(B, Ns, Hq, D), torch.randn(B, Ns, Hkv, D), torch.randn(B, Ns, Hkv, D)
+        a = ref.ksa_attention(q, k, v, qs, ks, vs, C, S, W)
+        b = ref.ksa_attention_blockwise(q, k, v, qs, ks, vs, C, S, W, q_block=qb)
+        assert torch.allclose(a[0], b[0], atol=2e-6) and torch.allclose(a[1], b[1], atol=2e-6)
+    base = get_preset("qwen3-ksa-tiny").merge({"num_layers": 2, "summary_layer_freq": [1, 0], "embed_dim": 64,
+                                               "intermediate_dim": 128, "vocab_size": 256, "head_dim": 16,
+                                               "summary_chunk_size": 16, "summary_sliding_chunk_num": 2})
+    tokens = torch.randint(0, 200, (2, 80))
+    outs = {}
+    for mode in ("kernel", "mask", "block"):
+        cfg = base.merge({"summary_attention_mode": mode})
+        model = get_model_class(cfg.model_class)(cfg)
+        model.init_weights(seed=0)
+        loss = model(tokens[:, :-1], tokens[:, 1:])
+        loss.backward()
+        outs[mode] = (float(loss.detach()), model.layers[0].attn.wqkv.weight.grad.clone())
+    for mode in ("mask", "block"):
+        assert abs(outs[mode][0] - outs["kernel"][0]) < 1e-5
+        assert torch.allclose(outs[mode][1], outs["kernel"][1], atol=1e-5)
