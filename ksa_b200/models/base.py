@@ -81,6 +81,27 @@ def save_sharded_safetensors(state: Dict[str, torch.Tensor], out_dir: str, max_s
     return index
 
 
+def save_sharded_bin(state: Dict[str, torch.Tensor], out_dir: str, max_shard_size: str = "5GB") -> dict:
+    """The ``torch.save`` form of the same layout: ``pytorch_model.bin``, or ``pytorch_model-0000i-of-0000n.bin`` +
+    ``pytorch_model.bin.index.json`` (``muse/models/base.py:253-306``)."""
+    out = Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    state = {k: v.detach().to("cpu").contiguous() for k, v in state.items()}
+    shards = shard_state_dict(state, parse_size(max_shard_size))
+    n = len(shards)
+    weight_map, total = {}, 0
+    for i, shard in enumerate(shards, 1):
+        name = "pytorch_model.bin" if n == 1 else f"pytorch_model-{i:05d}-of-{n:05d}.bin"
+        torch.save(shard, str(out / name))
+        for k, t in shard.items():
+            weight_map[k] = name
+            total += t.numel() * t.element_size()
+    index = {"metadata": {"total_size": total}, "weight_map": weight_map}
+    if n > 1:
+        (out / "pytorch_model.bin.index.json").write_text(json.dumps(index, indent=2))
+    return index
+
+
 def load_hf_state_dict(model_dir: str, device: str = "cpu") -> Dict[str, torch.Tensor]:
     """Read every ``*.safetensors`` (or ``pytorch_model*.bin``) of an HF directory into one dict."""
     d = Path(model_dir)
@@ -164,11 +185,14 @@ class Model(nn.Module):
             model = model.to(dtype)
         return model.to(device)
 
-    def save_pretrained(self, out_dir: str, max_shard_size: str = "5GB", dtype=None) -> None:
+    def save_pretrained(self, out_dir: str, max_shard_size: str = "5GB", dtype=None,
+                        save_safetensors: bool = True) -> None:
+        """HF-layout directory: weights under the Hugging Face names in shards of ``max_shard_size`` (safetensors, or
+        ``torch.save`` files with ``save_safetensors=False``, ``muse/models/base.py:151-196``) plus the model config."""
         state = self.revert_hf_state_dict({k: v for k, v in self.state_dict().items()})
         if dtype is not None:
             state = {k: v.to(dtype) for k, v in state.items()}
-        save_sharded_safetensors(state, out_dir, max_shard_size)
+        (save_sharded_safetensors if save_safetensors else save_sharded_bin)(state, out_dir, max_shard_size)
         self.config.save(os.path.join(out_dir, "muse_config.json"))
 
     def num_parameters(self) -> int:

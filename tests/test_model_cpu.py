@@ -193,3 +193,27 @@ def test_summary_attention_modes_agree():
     for mode in ("mask", "block"):
         assert abs(outs[mode][0] - outs["kernel"][0]) < 1e-5
         assert torch.allclose(outs[mode][1], outs["kernel"][1], atol=1e-5)
+
+
+@pytest.mark.parametrize("safetensors,shard", [(True, "5GB"), (True, "1MB"), (False, "5GB"), (False, "1MB")])
+def test_save_pretrained_and_from_pretrained_roundtrip(tmp_path, safetensors, shard):
+    """HF-layout directories in both weight formats, one file or sharded with an index, load back bit for bit."""
+    import json
+    import os
+    cfg = get_preset("qwen3-ksa-tiny")
+    model = Qwen3SummaryModel(cfg)
+    model.init_weights(seed=2)
+    model.save_pretrained(str(tmp_path), max_shard_size=shard, save_safetensors=safetensors)
+    files = sorted(os.listdir(tmp_path))
+    ext = ".safetensors" if safetensors else ".bin"
+    weights = [f for f in files if f.endswith(ext)]
+    if shard == "5GB":
+        assert weights == ["model.safetensors" if safetensors else "pytorch_model.bin"]
+    else:
+        index_name = "model.safetensors.index.json" if safetensors else "pytorch_model.bin.index.json"
+        assert len(weights) > 1 and index_name in files
+        index = json.load(open(tmp_path / index_name))
+        assert set(index["weight_map"].values()) == set(weights)
+    back = Qwen3SummaryModel.from_pretrained(str(tmp_path))
+    for (k, a), (_, b) in zip(model.state_dict().items(), back.state_dict().items()):
+        assert torch.equal(a, b), k
