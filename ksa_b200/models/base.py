@@ -137,9 +137,16 @@ class Model(nn.Module):
     def get_checkpointable_module_classes(self) -> Tuple[type, ...]:
         return tuple({type(m) for m in self.get_layers_to_shard()})
 
-    def get_optimizer_grouped_parameters(self, weight_decay: float) -> List[dict]:
-        """One group, weight decay on every parameter (``muse/models/base.py:369-388``)."""
-        return [{"params": [p for p in self.parameters() if p.requires_grad], "weight_decay": weight_decay}]
+    def get_optimizer_grouped_parameters(self, weight_decay: float, learning_rate: Optional[float] = None) -> List[dict]:
+        """One group, weight decay on every parameter, the learning rate when given (``muse/models/base.py:369-388``)."""
+        group = {"params": [p for p in self.parameters() if p.requires_grad], "weight_decay": weight_decay}
+        if learning_rate is not None:
+            group["lr"] = learning_rate
+        return [group]
+
+    def get_hf_state_dict(self, state: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, torch.Tensor]:
+        """The state dict under the Hugging Face parameter names (``muse/models/base.py:404-407``)."""
+        return self.revert_hf_state_dict(state if state is not None else dict(self.state_dict()))
 
     def get_initializer(self) -> Callable[[nn.Module], None]:
         std = 0.02

@@ -217,3 +217,16 @@ def test_save_pretrained_and_from_pretrained_roundtrip(tmp_path, safetensors, sh
     back = Qwen3SummaryModel.from_pretrained(str(tmp_path))
     for (k, a), (_, b) in zip(model.state_dict().items(), back.state_dict().items()):
         assert torch.equal(a, b), k
+
+
+def test_optimizer_groups_and_hf_state_dict_helpers():
+    """One parameter group with weight decay on everything (the reference's choice), usable by torch.optim.AdamW."""
+    cfg = get_preset("qwen3-ksa-tiny")
+    model = Qwen3SummaryModel(cfg)
+    model.init_weights(seed=0)
+    groups = model.get_optimizer_grouped_parameters(0.1, learning_rate=3e-4)
+    assert len(groups) == 1 and groups[0]["weight_decay"] == 0.1 and groups[0]["lr"] == 3e-4
+    assert len(groups[0]["params"]) == len(list(model.parameters()))
+    assert "lr" not in model.get_optimizer_grouped_parameters(0.1)[0]
+    torch.optim.AdamW(groups)
+    assert set(model.get_hf_state_dict()) == set(model.revert_hf_state_dict(dict(model.state_dict())))
