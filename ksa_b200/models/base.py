@@ -120,6 +120,54 @@ def load_hf_state_dict(model_dir: str, device: str = "cpu") -> Dict[str, torch.T
     return out
 
 
+def load_full_state_dict(model: nn.Module, state: Dict[str, torch.Tensor], allow_random_init_params=None,
+                         skip_load_params=None, verbose: Optional[Callable[[str], None]] = None) -> Dict[str, List[str]]:
+    """Load a whole-model state dict into an initialised model with the reference's rules
+    (``muse/training/distributed.py:290-420``):
+
+    * a parameter named in ``allow_random_init_params`` (exact names; a list or a comma-separated string) may be
+      missing from ``state`` or have another shape there: it keeps its random initialisation;
+    * a parameter whose name contains one of ``skip_load_params`` (substrings) is never loaded, even if present;
+    * any other missing parameter, any other shape mismatch and any key of ``state`` the model does not have is an error.
+
+    The model must already hold its initial values (``init_weights``).  Returns the names that kept them, by reason.
+    """
+    def as_list(v):
+        if v is None:
+            return []
+        if isinstance(v, str):
+            return [p.strip() for p in v.split(",") if p.strip()]
+        return list(v)
+    allow, skip = set(as_list(allow_random_init_params)), as_list(skip_load_params)
+    own = model.state_dict()
+    unexpected = sorted(set(state) - set(own))
+    if unexpected:
+        raise RuntimeError(f"the state dict holds {len(unexpected)} keys the model does not have: {unexpected[:5]}")
+    kept: Dict[str, List[str]] = {"skipped": [], "missing": [], "shape": []}
+    problems, to_load = [], {}
+    for k, target in own.items():
+        if any(p in k for p in skip):
+            kept["skipped"].append(k)
+        elif k not in state:
+            (kept["missing"] if k in allow else problems).append(k)
+        elif tuple(state[k].shape) != tuple(target.shape):
+            if k in allow:
+                kept["shape"].append(k)
+            else:
+                problems.append(f"{k}: model {tuple(target.shape)} vs state dict {tuple(state[k].shape)}")
+        else:
+            to_load[k] = state[k]
+    if problems:
+        raise RuntimeError("parameters missing from the state dict or of another shape; name them in "
+                           f"allow_random_init_params or skip_load_params to keep their initialisation: {problems[:8]}")
+    model.load_state_dict(to_load, strict=False)
+    if verbose is not None:
+        for reason, names in kept.items():
+            for k in names:
+                verbose(f"[load] {k}: kept its random initialisation ({reason})")
+    return kept
+
+
 class Model(nn.Module):
     """Base of every trainable model of the framework."""
 

@@ -75,7 +75,9 @@ def get_argument_parser() -> argparse.ArgumentParser:
     a("--use-flash-attention-2", action="store_true")
     a("--enable-gradient-checkpointing", action="store_true")
     a("--gradient-accumulation-steps", type=int, default=1)
-    a("--allow-random-init-params", default="")
+    a("--allow-random-init-params", default="", help="comma-separated parameter names that may be missing from "
+      "--model-dir (or have another shape there) and keep their random initialisation")
+    a("--skip-load-params", default="", help="comma-separated substrings: matching parameters are never loaded")
     a("--context-parallel-size", type=int, default=1)
     a("--chunked-loss-minibatch-size", type=int, default=2048)
     a("--disable-chunked-loss", action="store_true")
@@ -135,6 +137,7 @@ def train(args) -> dict:
     from ksa_b200.data.mmap_dataset import make_labels
     from ksa_b200.losses import attention_cosine_loss, attention_mse_loss
     from ksa_b200.models import get_model_class
+    from ksa_b200.models.base import load_full_state_dict
     from ksa_b200.parallel import groups
     from ksa_b200.training import checkpoint as ckpt
     from ksa_b200.training.activations import set_activation_checkpointing
@@ -175,12 +178,8 @@ def train(args) -> dict:
     model = model.to_empty(device=device).to(dtype)
     if args.model_dir:
         state = model.convert_hf_state_dict(ckpt.load_hf_checkpoint(args.model_dir))
-        allow = [s for s in args.allow_random_init_params.split(",") if s]
         model.init_weights(seed=args.seed or 0)
-        missing, unexpected = model.load_state_dict(state, strict=False)
-        bad = [m for m in missing if not any(a in m for a in allow)]
-        if bad:
-            raise RuntimeError(f"{args.model_dir} lacks parameters not listed in --allow-random-init-params: {bad[:5]}")
+        load_full_state_dict(model, state, args.allow_random_init_params, args.skip_load_params, verbose=print_rank_0)
     else:
         # every rank initialises from the same seed: identical weights with no broadcast (the reference initialises on
         # rank 0 and broadcasts parameter by parameter, muse/training/distributed.py:448-532)

@@ -230,3 +230,43 @@ def test_optimizer_groups_and_hf_state_dict_helpers():
     assert "lr" not in model.get_optimizer_grouped_parameters(0.1)[0]
     torch.optim.AdamW(groups)
     assert set(model.get_hf_state_dict()) == set(model.revert_hf_state_dict(dict(model.state_dict())))
+
+
+def test_load_full_state_dict_allow_and_skip_rules():
+    """Missing or reshaped parameters keep their initialisation only when named; skipped ones are never loaded;
+    anything else is an error (the reference's ``load_from_full_model_state_dict`` rules)."""
+    from ksa_b200.models.base import load_full_state_dict
+    cfg = get_preset("qwen3-ksa-tiny")
+    src = Qwen3SummaryModel(cfg)
+    src.init_weights(seed=1)
+    state = {k: v.clone() for k, v in src.state_dict().items()}
+
+    def fresh():
+        m = Qwen3SummaryModel(cfg)
+        m.init_weights(seed=2)
+        return m
+    # complete state dict: everything is taken
+    m = fresh()
+    kept = load_full_state_dict(m, state)
+    assert kept == {"skipped": [], "missing": [], "shape": []}
+    assert all(torch.equal(a, b) for a, b in zip(m.state_dict().values(), src.state_dict().values()))
+    # a missing parameter and a reshaped one
+    partial = dict(state)
+    del partial["summary_embedding.weight"]
+    partial["tok_embeddings.weight"] = state["tok_embeddings.weight"][:-8]
+    with pytest.raises(RuntimeError, match="allow_random_init_params"):
+        load_full_state_dict(fresh(), partial)
+    m, init = fresh(), fresh()
+    kept = load_full_state_dict(m, partial, allow_random_init_params="summary_embedding.weight,tok_embeddings.weight")
+    assert kept["missing"] == ["summary_embedding.weight"] and kept["shape"] == ["tok_embeddings.weight"]
+    assert torch.equal(m.tok_embeddings.weight, init.tok_embeddings.weight)          # kept its own initialisation
+    assert torch.equal(m.layers[0].attn.wqkv.weight, src.layers[0].attn.wqkv.weight)  # the rest was loaded
+    # skipped by substring, although present
+    m, init = fresh(), fresh()
+    kept = load_full_state_dict(m, state, skip_load_params=["_summary", "norm.scale"])
+    assert kept["skipped"] and all("_summary" in k or "norm.scale" in k for k in kept["skipped"])
+    assert torch.equal(m.layers[0].attn.wqkv_summary.weight, init.layers[0].attn.wqkv_summary.weight)
+    assert torch.equal(m.layers[0].mlp.w2.weight, src.layers[0].mlp.w2.weight)
+    # a key the model does not know
+    with pytest.raises(RuntimeError, match="does not have"):
+        load_full_state_dict(fresh(), dict(state, extra=torch.zeros(1)))

@@ -78,3 +78,36 @@ def test_recipe_trains_checkpoints_and_resumes(tmp_path):
                                                         "--resume-weights", "--resume-optimizer", "--resume-dataloader"]))
     assert r2["steps"] == 12 and (out / "global_step12").is_dir()
     assert r2["loss"] < 5.6
+
+
+def test_recipe_starts_from_an_hf_directory_with_skip_and_allow_lists(tmp_path):
+    """``--model-dir`` + ``--skip-load-params`` / ``--allow-random-init-params``: the recipe loads a saved model, keeps
+    the random initialisation of the named parameters and refuses a directory that lacks others."""
+    import pytest
+    from ksa_b200.models import get_model_class
+    cfg = get_preset("qwen3-ksa-tiny").merge({"num_layers": 2, "summary_layer_freq": [1, 0], "embed_dim": 64,
+                                               "intermediate_dim": 128, "vocab_size": 256, "summary_token_begin": 256,
+                                               "head_dim": 16, "summary_chunk_size": 16})
+    mc = tmp_path / "model.json"
+    cfg.save(str(mc))
+    ds_cfg, _ = _corpora(tmp_path, 256)
+    src = get_model_class(cfg.model_class)(cfg)
+    src.init_weights(seed=5)
+    src.save_pretrained(str(tmp_path / "hf"))
+    base = ["--model-config", str(mc), "--dataset-config", ds_cfg, "--learning-rate", "1e-3", "--lr-scheduler-type",
+            "constant", "--seed", "1", "--model-dtype", "float32", "--num-training-steps", "2", "--model-dir",
+            str(tmp_path / "hf")]
+    r = train(get_argument_parser().parse_args(base + ["--output-dir", str(tmp_path / "a"), "--skip-load-params",
+                                                       "_summary,summary_embedding"]))
+    assert r["steps"] == 2
+    # a directory without the summary parameters: refused unless they are named
+    dense = {k: v for k, v in src.get_hf_state_dict().items() if "summary" not in k}
+    from ksa_b200.models.base import save_sharded_safetensors
+    save_sharded_safetensors(dense, str(tmp_path / "dense"))
+    args = [a if a != str(tmp_path / "hf") else str(tmp_path / "dense") for a in base]
+    with pytest.raises(RuntimeError, match="allow_random_init_params"):
+        train(get_argument_parser().parse_args(args + ["--output-dir", str(tmp_path / "b")]))
+    missing = [k for k in src.state_dict() if "summary" in k]
+    r = train(get_argument_parser().parse_args(args + ["--output-dir", str(tmp_path / "c"), "--allow-random-init-params",
+                                                       ",".join(missing)]))
+    assert r["steps"] == 2
