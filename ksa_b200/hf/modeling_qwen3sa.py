@@ -40,7 +40,8 @@ class Qwen3SAConfig(PretrainedConfig):
                  summary_token_begin=151936, summary_chunk_size=128, summary_token_num=1, summary_sliding_chunk_num=8,
                  summary_layer_freq=0, summary_chunk_position_ids_type="origin",
                  summary_token_position_ids_type="last_chunk_slice_right", summary_independent_parameters=True,
-                 summary_independent_attention_layernorm=False, summary_independent_qk_norm=False, **kwargs):
+                 summary_independent_attention_layernorm=False, summary_independent_qk_norm=False,
+                 truncate_predict_nums=0, **kwargs):
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
@@ -62,6 +63,9 @@ class Qwen3SAConfig(PretrainedConfig):
         self.summary_independent_parameters = summary_independent_parameters
         self.summary_independent_attention_layernorm = summary_independent_attention_layernorm
         self.summary_independent_qk_norm = summary_independent_qk_norm
+        # logits (and sampled tokens) are restricted to the first N vocabulary entries; 0 keeps the text vocabulary
+        # (the reference's template reads the same attribute, examples/pretrain/hf_template/modeling_qwen3sa.py:1402)
+        self.truncate_predict_nums = truncate_predict_nums
         super().__init__(tie_word_embeddings=tie_word_embeddings, **kwargs)
 
     # ---- per-layer views -------------------------------------------------------------------------
@@ -305,6 +309,10 @@ class Qwen3ForCausalLM(Qwen3PreTrainedModel, GenerationMixin):
         self._fw_model = m.eval()
         return self._fw_model
 
+    def _truncate(self, logits: torch.Tensor) -> torch.Tensor:
+        n = int(getattr(self.config, "truncate_predict_nums", 0) or 0)
+        return logits[..., :n] if 0 < n < logits.shape[-1] else logits
+
     # ---- scoring ----------------------------------------------------------------------------------
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None, logits_to_keep: int = 0,
                 **kwargs) -> CausalLMOutputWithPast:
@@ -316,6 +324,7 @@ class Qwen3ForCausalLM(Qwen3PreTrainedModel, GenerationMixin):
         else:
             h = self.model(input_ids).last_hidden_state
             logits = self.lm_head(h)[..., :self.config.text_vocab_size]
+        logits = self._truncate(logits)
         loss = None
         if labels is not None:
             loss = F.cross_entropy(logits[:, :-1].float().reshape(-1, logits.shape[-1]), labels[:, 1:].reshape(-1),
@@ -337,6 +346,7 @@ class Qwen3ForCausalLM(Qwen3PreTrainedModel, GenerationMixin):
         B, L = input_ids.shape
 
         def pick(logits):
+            logits = self._truncate(logits)
             if not do_sample or temperature <= 0:
                 return logits.argmax(-1)
             probs = torch.softmax(logits.float() / temperature, -1)

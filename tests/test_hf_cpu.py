@@ -66,3 +66,17 @@ def test_converted_directory_loads_into_the_engine(tmp_path):
     want = KsaInferenceEngine(model, max_len=64, batch=2).generate(tokens, 12)
     got = KsaInferenceEngine(loaded, max_len=64, batch=2).generate(tokens, 12)
     assert torch.equal(got, want)
+
+
+def test_truncate_predict_nums_limits_logits_and_generated_tokens(tmp_path):
+    from transformers import AutoModelForCausalLM
+    cfg, model, out = _export(tmp_path)
+    hf = AutoModelForCausalLM.from_pretrained(out, trust_remote_code=True, torch_dtype=torch.float32).eval()
+    tokens = torch.randint(0, cfg.vocab_size, (2, 21))
+    full = hf(tokens).logits
+    assert full.shape[-1] == cfg.vocab_size
+    hf.config.truncate_predict_nums = 100
+    cut = hf(tokens).logits
+    assert cut.shape[-1] == 100 and torch.equal(cut, full[..., :100])
+    gen = hf.generate(tokens, max_new_tokens=8, eos_token_id=-1)
+    assert int(gen[:, 21:].max()) < 100
