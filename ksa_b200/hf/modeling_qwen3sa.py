@@ -336,8 +336,9 @@ class Qwen3ForCausalLM(Qwen3PreTrainedModel, GenerationMixin):
     # ---- generation -------------------------------------------------------------------------------
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor = None, max_new_tokens: int = 32, do_sample: bool = False,
-                 temperature: float = 1.0, top_p: float = 1.0, eos_token_id=None, attention_mask=None, **kwargs):
-        """Greedy / nucleus decoding on the ring-buffer KV cache (batch >= 1, equal prompt lengths)."""
+                 temperature: float = 1.0, top_p: float = 1.0, top_k: int = 0, eos_token_id=None, attention_mask=None,
+                 **kwargs):
+        """Greedy / top-k / nucleus decoding on the ring-buffer KV cache (batch >= 1, equal prompt lengths)."""
         if input_ids is None:
             input_ids = kwargs.pop("inputs")
         fm = self.framework_model()
@@ -349,7 +350,11 @@ class Qwen3ForCausalLM(Qwen3PreTrainedModel, GenerationMixin):
             logits = self._truncate(logits)
             if not do_sample or temperature <= 0:
                 return logits.argmax(-1)
-            probs = torch.softmax(logits.float() / temperature, -1)
+            logits = logits.float() / temperature
+            if top_k and 0 < top_k < logits.shape[-1]:
+                kth = logits.topk(top_k, dim=-1).values[..., -1:]
+                logits = logits.masked_fill(logits < kth, float("-inf"))
+            probs = torch.softmax(logits, -1)
             sp, si = probs.sort(-1, descending=True)
             keep = (sp.cumsum(-1) - sp) < top_p
             sp = sp * keep

@@ -80,3 +80,18 @@ def test_truncate_predict_nums_limits_logits_and_generated_tokens(tmp_path):
     assert cut.shape[-1] == 100 and torch.equal(cut, full[..., :100])
     gen = hf.generate(tokens, max_new_tokens=8, eos_token_id=-1)
     assert int(gen[:, 21:].max()) < 100
+
+
+def test_hf_generate_sampling_options(tmp_path):
+    """top_k = 1 is greedy whatever the temperature; sampling with a seed is reproducible."""
+    from transformers import AutoModelForCausalLM
+    cfg, model, out = _export(tmp_path)
+    hf = AutoModelForCausalLM.from_pretrained(out, trust_remote_code=True, torch_dtype=torch.float32).eval()
+    tokens = torch.randint(0, cfg.vocab_size, (2, 19))
+    greedy = hf.generate(tokens, max_new_tokens=6, eos_token_id=-1)
+    assert torch.equal(hf.generate(tokens, max_new_tokens=6, eos_token_id=-1, do_sample=True, temperature=1.3, top_k=1), greedy)
+    torch.manual_seed(4)
+    a = hf.generate(tokens, max_new_tokens=6, eos_token_id=-1, do_sample=True, temperature=0.9, top_p=0.8, top_k=20)
+    torch.manual_seed(4)
+    b = hf.generate(tokens, max_new_tokens=6, eos_token_id=-1, do_sample=True, temperature=0.9, top_p=0.8, top_k=20)
+    assert torch.equal(a, b) and a.shape == (2, 25)
