@@ -123,13 +123,23 @@ class AppState(Stateful):
     """What one checkpoint holds: model + optimizer (through the engine) and training-loop state."""
 
     def __init__(self, engine, step_scheduler=None, lr_scheduler=None, skip_optimizer: bool = False,
-                 skip_training_state: bool = False, strict: bool = True):
+                 skip_training_state: bool = False, strict: bool = True, skip_training_state_keys=None,
+                 required_training_state_keys=None, extra_training_state: Optional[Dict[str, Any]] = None):
+        """``skip_training_state_keys`` / ``required_training_state_keys``: entries of the training state
+        (``"step_scheduler"``, ``"lr_scheduler"``, ``"engine_step"``, names of ``extra_training_state``) that are not
+        restored on load / that must be in the checkpoint (``muse/training/checkpoint.py:469-530``).
+        ``extra_training_state``: further objects (with ``state_dict`` / ``load_state_dict``) or plain values saved
+        under their names; restored values are available in the same dict after a load (the loading side has to list
+        the names it wants, with any placeholder value: a DCP load fills the structure it is given)."""
         self.engine = engine
         self.step_scheduler = step_scheduler
         self.lr_scheduler = lr_scheduler
         self.skip_optimizer = skip_optimizer
         self.skip_training_state = skip_training_state
         self.strict = strict
+        self.skip_training_state_keys = set(skip_training_state_keys or [])
+        self.required_training_state_keys = set(required_training_state_keys or [])
+        self.extra_training_state = extra_training_state if extra_training_state is not None else {}
 
     def _to_muse(self, fused: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
         m = self.engine.model
@@ -154,6 +164,8 @@ class AppState(Stateful):
             training["step_scheduler"] = self.step_scheduler.state_dict()
         if self.lr_scheduler is not None and hasattr(self.lr_scheduler, "state_dict"):
             training["lr_scheduler"] = self.lr_scheduler.state_dict()
+        for k, v in self.extra_training_state.items():
+            training[k] = v.state_dict() if hasattr(v, "state_dict") and callable(v.state_dict) else v
         return {"model": model, "optim": optim, "training": training}
 
     def load_state_dict(self, state: Dict[str, Any]) -> None:
@@ -165,13 +177,27 @@ class AppState(Stateful):
             es = self._from_muse({k: v["exp_avg_sq"] for k, v in st.items()})
         load_engine_full_state(self.engine, model, ea, es, strict=self.strict)
         training = state.get("training", {})
-        if not self.skip_optimizer:
+        skip = self.skip_training_state_keys
+        if not self.skip_training_state:
+            missing = sorted(self.required_training_state_keys - skip - set(training))
+            if missing:
+                raise KeyError(f"Missing required training state keys in checkpoint: {', '.join(missing)}")
+        if not self.skip_optimizer and "engine_step" not in skip:
             self.engine.step_count = int(training.get("engine_step", self.engine.step_count))
         if not self.skip_training_state:
-            if self.step_scheduler is not None and "step_scheduler" in training:
+            if self.step_scheduler is not None and "step_scheduler" in training and "step_scheduler" not in skip:
                 self.step_scheduler.load_state_dict(training["step_scheduler"])
-            if self.lr_scheduler is not None and "lr_scheduler" in training and hasattr(self.lr_scheduler, "load_state_dict"):
+            if (self.lr_scheduler is not None and "lr_scheduler" in training and "lr_scheduler" not in skip
+                    and hasattr(self.lr_scheduler, "load_state_dict")):
                 self.lr_scheduler.load_state_dict(training["lr_scheduler"])
+            for k, v in training.items():
+                if k in ("engine_step", "step_scheduler", "lr_scheduler") or k in skip:
+                    continue
+                target = self.extra_training_state.get(k)
+                if hasattr(target, "load_state_dict") and callable(target.load_state_dict):
+                    target.load_state_dict(v)
+                else:
+                    self.extra_training_state[k] = v
 
 
 class DistributedCheckpointer:

@@ -117,3 +117,42 @@ def test_dcp2torch_single_file_and_safetensors(tmp_path):
     assert set(loaded) == set(want)
     for k in want:
         assert torch.equal(loaded[k].to(want[k].dtype), want[k]), k
+
+
+def test_training_state_keys_can_be_skipped_required_and_extended(tmp_path):
+    """Entries of the training state are restored one by one: named ones can be left out, others demanded, and
+    further objects or values ride along under their own names."""
+    import pytest
+
+    class Counter:
+        def __init__(self, n=0):
+            self.n = n
+
+        def state_dict(self):
+            return {"n": self.n}
+
+        def load_state_dict(self, s):
+            self.n = s["n"]
+    eng, cfg = _engine()
+    sched = StepScheduler(1, 10, 2)
+    _train(eng, cfg, 2)
+    sched.step(); sched.step()
+    ck = DistributedCheckpointer()
+    save_checkpoint(AppState(eng, sched, extra_training_state={"tokens_seen": Counter(4096), "note": "stage 8k"}),
+                    ck, str(tmp_path), 2)
+    # everything back, extras included
+    eng2, _ = _engine(seed=5)
+    sched2, extra = StepScheduler(1, 10, 2), {"tokens_seen": Counter(), "note": ""}   # the loader names what it wants
+    load_checkpoint(AppState(eng2, sched2, extra_training_state=extra,
+                             required_training_state_keys=["step_scheduler", "tokens_seen"]), ck, str(tmp_path))
+    assert sched2.global_step == 2 and extra["tokens_seen"].n == 4096 and extra["note"] == "stage 8k"
+    # the step scheduler and one extra are left alone
+    eng3, _ = _engine(seed=5)
+    sched3, extra3 = StepScheduler(1, 10, 2), {"tokens_seen": Counter(7)}
+    load_checkpoint(AppState(eng3, sched3, extra_training_state=extra3,
+                             skip_training_state_keys=["step_scheduler", "tokens_seen"]), ck, str(tmp_path))
+    assert sched3.global_step == 0 and extra3["tokens_seen"].n == 7 and eng3.step_count == 2
+    # a demanded entry that the checkpoint lacks
+    eng4, _ = _engine(seed=5)
+    with pytest.raises(Exception, match="Missing required training state keys"):
+        load_checkpoint(AppState(eng4, required_training_state_keys=["ema"]), ck, str(tmp_path))
