@@ -302,14 +302,15 @@ def test_few_rows_take_the_one_shot_all_reduce(fake_gpu, monkeypatch, T):
     assert "ksa_tp_allreduce_add_rmsnorm" in log and "ksa_gemm2_scatter_bf16" not in log and "gemm_gather" not in log
 
 
-@pytest.mark.parametrize("T", [2, 4])
+@pytest.mark.parametrize("T", [2, 4, 8])
 def test_sharded_model_prefill_matches_the_whole_model(fake_gpu, monkeypatch, T):
     """The model's tensor-parallel wiring (deferred gathers, scattered row-parallel outputs, the last layer's
-    exception, the flush before the head) on 2 and 4 ranks against the unsharded model, logits of a whole prompt."""
+    exception, the flush before the head) on 2, 4 and 8 ranks against the unsharded model, logits of a whole prompt."""
     from ksa_b200.config import get_preset
     from ksa_b200.models import get_model_class
     from ksa_b200.parallel.tp import build_tp_model
-    cfg = get_preset("qwen3-ksa-tiny").merge({"num_heads": 4, "num_kv_heads": 4, "head_dim": 32, "embed_dim": 128,
+    heads = max(4, T)
+    cfg = get_preset("qwen3-ksa-tiny").merge({"num_heads": heads, "num_kv_heads": heads, "head_dim": 128 // heads, "embed_dim": 128,
                                               "intermediate_dim": 256, "num_layers": 3, "vocab_size": 512,
                                               "summary_layer_freq": [1, 0, 1], "summary_chunk_size": 32,
                                               "summary_sliding_chunk_num": 2, "summary_token_begin": 512})
