@@ -88,8 +88,8 @@ def make_cp_kernels(mem: Memory, log: list):
     return call
 
 
-@pytest.fixture
-def fake_cp_gpu(monkeypatch):
+def apply_cp_patches(monkeypatch):
+    """Route CpContext's fused path onto the stand-ins (also used by the combined FSDP + context-parallel test)."""
     monkeypatch.setattr(CpContext, "_on_gpus", staticmethod(lambda device: True))
     monkeypatch.setattr(symm, "SymmetricBuffer", ZeroedSymm)
     monkeypatch.setattr(dist, "get_rank", lambda g=None: g.rank)
@@ -108,6 +108,11 @@ def fake_cp_gpu(monkeypatch):
         return cp_mod._cpu_shard_attention(q_t, k_t, v_t, None, None, None, sh, q_off - k_off, None, tok_window, scale)[0]
     monkeypatch.setattr(ops, "ksa_attention", ksa_attention)
     monkeypatch.setattr(ops, "shard_causal_attention", shard_causal_attention)
+
+
+@pytest.fixture
+def fake_cp_gpu(monkeypatch):
+    apply_cp_patches(monkeypatch)
     yield
 
 

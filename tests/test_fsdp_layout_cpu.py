@@ -155,3 +155,60 @@ def test_fused_fsdp_matches_single_process_training(fake_fsdp_gpu, monkeypatch, 
     total_sq = sum(results[r][2] for r in range(world))        # every rank holds the sum over its shards
     assert abs(total_sq ** 0.5 - float(ref.grad_norm())) < 5e-2 * float(ref.grad_norm())
     assert "ksa_peer_gather" in log and "ksa_peer_reduce_adamw" in log and "ksa_signal_set" in log
+
+
+def test_context_parallel_and_fsdp_on_the_same_ranks(fake_fsdp_gpu, monkeypatch):
+    """The long-context configuration: 4 ranks split every sequence (fused context-parallel exchange) and shard the
+    weights (fused FSDP) at the same time; two optimizer steps equal single-process training on the whole sequences."""
+    from test_cp_cpu import _cfg
+    from test_cp_layout_cpu import apply_cp_patches
+    from ksa_b200.parallel.cp import CpContext, shard_inputs
+    apply_cp_patches(monkeypatch)
+    world, L, chunk, window, n_sum, B, steps = 4, 128, 16, 3, 1, 2, 2
+    cfg = _cfg(chunk, window, n_sum)
+    torch.manual_seed(0)
+    base = get_model_class(cfg.model_class)(cfg)
+    base.init_weights(seed=0)
+    base = base.to(torch.bfloat16)
+    g = torch.Generator().manual_seed(3)
+    data = torch.randint(0, 200, (steps, B, L + 1), generator=g)
+    log, results = [], {}
+
+    def body(rank, group):
+        if rank == 0:
+            monkeypatch.setattr(_lib, "call", make_fsdp_kernels(group.shared["mem"], log))
+        group.shared["barrier"].wait()
+        model = copy.deepcopy(base)
+        model.cp = CpContext(group, L, chunk, n_sum, cfg.num_kv_heads, cfg.head_dim, batch=B, device="cuda",
+                             dtype=torch.bfloat16, n_heads=cfg.num_heads, full_layers=True, max_window=window,
+                             full_layer_mode="halo")
+        eng = FsdpEngine(model, lr=1e-2, weight_decay=0.1, clip_value=1.0, world_size=world, rank=rank, group=group,
+                         comm="fused", overlap="stream", param_dtype=torch.bfloat16, device="cpu")
+        losses = []
+        for s in range(steps):
+            tokens, labels = shard_inputs(data[s, :, :-1], data[s, :, 1:], rank, world)
+            losses.append(float(eng.train_step(tokens, labels)))
+        group.shared["barrier"].wait()
+        eng._write_hyper()
+        eng._overlap_active = False
+        for ui in range(len(eng.units)):
+            eng._gather_now(ui)
+        group.shared["barrier"].wait()
+        results[rank] = (losses, {n: p.detach().float().clone() for n, p in model.named_parameters()})
+        eng.close()
+        model.cp.close()
+
+    _run_ranks(world, body)
+    ref_model = copy.deepcopy(base)
+    ref = TrainEngine(ref_model, lr=1e-2, weight_decay=0.1, clip_value=1.0, param_dtype=torch.bfloat16)
+    ref_losses = [float(ref.train_step(data[s, :, :-1].contiguous(), data[s, :, 1:].contiguous())) for s in range(steps)]
+    for s in range(steps):
+        assert abs(sum(results[r][0][s] for r in range(world)) / world - ref_losses[s]) < 3e-2
+    want = {n: p.detach().float() for n, p in ref_model.named_parameters()}
+    for r in range(world):
+        for n, w in want.items():
+            got = results[r][1][n]
+            off = int(((got - w).abs() > 1.2e-2).sum())
+            assert off <= max(2, got.numel() // 50), (r, n, off, got.numel())
+            assert torch.equal(got, results[0][1][n]), f"ranks disagree about {n}"
+    assert "ksa_peer_copy" in log and "ksa_peer_reduce_adamw" in log and "ksa_peer_add_bf16" in log
