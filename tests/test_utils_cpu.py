@@ -236,3 +236,38 @@ def test_benchmark_flags_survive_the_torchrun_parser():
     k = kernel_bench.build_parser().parse_args(["gemm", "--m", "128", "--pair", "--scatter-world", "4"])
     assert k.m == 128 and k.pair and k.scatter_world == 4
     assert infer_bench is not None
+
+
+def test_bench_clock_sampler_parses_nvidia_smi_lines(tmp_path, monkeypatch):
+    """The benchmark's clock record: median SM clock, maximum clock and the throttle reasons seen while it ran, read
+    from ``nvidia-smi`` query lines (here produced by a stand-in executable; the sampler only reads)."""
+    import os
+    import stat
+    import sys
+    import time
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    try:
+        import bench
+    finally:
+        sys.path.remove(root)
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/bash\n"
+                    "echo '0, 1650, 1965, 990.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active'\n"
+                    "echo '0, 1710, 1965, 985.0, 0x0000000000000004, Not Active, Not Active, Not Active, Active'\n"
+                    "echo '0, 1965, 1965, 400.0, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active'\n"
+                    "echo 'garbage line'\n"
+                    "sleep 30\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", f"{tmp_path}:{os.environ['PATH']}")
+    s = bench.ClockSampler(0)
+    s.start()
+    time.sleep(0.5)
+    rec = s.stop()
+    assert rec["samples"] == 3 and rec["sm_mhz"] == 1710.0 and rec["sm_max_mhz"] == 1965.0
+    assert rec["reasons"] == ["sw_power_cap"]
+    # without the tool the record says so instead of failing the benchmark
+    monkeypatch.setenv("PATH", str(tmp_path / "empty"))
+    s = bench.ClockSampler(0)
+    s.start()
+    assert s.stop()["reasons"] == ["nvidia-smi unavailable"]
