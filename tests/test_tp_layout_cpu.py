@@ -416,3 +416,47 @@ def test_sharded_engine_prefill_and_decode_on_four_ranks(fake_gpu, monkeypatch):
         err = (results[rank] - want).abs().max() / want.abs().max()
         assert err < 6e-2, (rank, float(err))
     assert "ksa_gemm2_scatter_bf16" in log and "gemm_gather" in log and "ksa_tp_allreduce_add_rmsnorm" in log
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_two_phase_layouts_random_shapes(fake_gpu, monkeypatch, seed):
+    """Random group sizes and row counts (fewer partial rows than residual rows, shards that end past the last row,
+    ranks without any row of their own) with both fused paths on."""
+    import random
+    rnd = random.Random(seed)
+    T = rnd.choice([2, 3, 4, 5, 8])
+    rows_x = rnd.randint(16, 140)
+    rows_d = rnd.randint(max(1, rows_x - 20), rows_x)
+    D, Kr, Nc = 32, 24, 16
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows_x, D, generator=g).to(BF)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(BF)
+    wc = (0.1 * torch.randn(Nc, D, generator=g)).to(BF)
+    acts = [torch.randn(rows_d, Kr, generator=g).to(BF) for _ in range(T)]
+    wrs = [(0.1 * torch.randn(D, Kr, generator=g)).to(BF) for _ in range(T)]
+    res_ref, y_ref = _reference(x, acts, wrs, w, rows_d)
+    proj_ref = (y_ref.float() @ wc.float().t()).to(BF)
+    log, results = [], {}
+
+    def body(rank, group):
+        if rank == 0:
+            call, gemm, gemm_gather = make_kernels(group.shared["mem"], group.shared["barrier"], log)
+            monkeypatch.setattr(_lib, "call", call)
+            monkeypatch.setattr(ops, "gemm", gemm)
+            monkeypatch.setattr(ops, "gemm_gather", gemm_gather)
+        group.shared["barrier"].wait()
+        tp = TpContext(group, D, max_rows=rows_x, device="cuda", two_phase_rows=16, two_phase_min_size=2,
+                       fused_gather=True, push_partials=True)
+        token = tp.row_parallel_linear(acts[rank], wrs[rank], residual_rows=rows_x)
+        res, y = tp.add_rms_norm(x, token, w, 1e-6, defer_gather=True)
+        proj = tp.col_parallel_linear(y, wc)
+        tp.flush()
+        group.shared["barrier"].wait()
+        results[rank] = (res.clone(), y.clone(), proj.clone())
+        tp.close()
+
+    _run_ranks(T, body)
+    for rank in range(T):
+        for got, want, what in zip(results[rank], (res_ref, y_ref, proj_ref), ("residual", "normalised", "projection")):
+            torch.testing.assert_close(got.float(), want.float(), atol=3e-2, rtol=3e-2,
+                                       msg=lambda m: f"T={T} rows {rows_x}/{rows_d} rank {rank} {what}: {m}")
