@@ -182,7 +182,7 @@ class BlendableWeightedSamplingDataset(torch.utils.data.IterableDataset):
         self.consume_sample = {n: 0 for n in self._datasets}
         self.consume_token = {n: 0 for n in self._datasets}
         self.past_epoch = {n: 0 for n in self._datasets}
-        self._pending = None   # (names, indices, next position) of a draw that has been handed out only in part
+        self._pending = None   # (names, indices, samples handed out) of a draw that has been handed out only in part
 
     @property
     def size(self) -> int:
@@ -233,15 +233,18 @@ class BlendableWeightedSamplingDataset(torch.utils.data.IterableDataset):
         worker = 0 if info is None else info.id
         stride = self._num_workers * self._dp_world_size
         first = self._dp_rank + worker * self._dp_world_size
+        per_reader = self.global_bs // stride          # samples of one draw that this (rank, worker) hands out
         while True:
+            # `_pending` counts samples already handed out of the current draw, not a position: the saved state is
+            # written by one rank and read by all, and every reader re-adds its own first position.
             if self._pending is not None:
-                names, index, start = self._pending
+                names, index, done = self._pending
             else:
                 names, index = self._draw()
-                start = first
-            for pos in range(start, self.global_bs, stride):
-                nxt = pos + stride
-                self._pending = (names, index, nxt) if nxt < self.global_bs else None
+                done = 0
+            for k in range(done, per_reader):
+                pos = first + k * stride
+                self._pending = (names, index, k + 1) if k + 1 < per_reader else None
                 yield self._datasets[names[pos]][index[pos]], names[pos]
             self._pending = None
 

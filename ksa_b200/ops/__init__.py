@@ -20,6 +20,7 @@ returned to autograd in the weight's dtype.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -469,6 +470,41 @@ def _strides(t: torch.Tensor):
     return t.stride(1), (t.stride(0) if B > 1 else t.stride(1) * max(T, 1))
 
 
+_deterministic = os.environ.get("KSA_DETERMINISTIC", "0") == "1"
+
+
+def set_deterministic(on: bool) -> None:
+    """Select the bit-reproducible attention backward (two kernels that never accumulate across CTAs) instead of the
+    fused key-stationary one, whose dQ is summed with floating-point reductions in an order that varies between runs.
+    ``KSA_DETERMINISTIC=1`` sets the initial value.  The reference kernel has the same switch
+    (``flash_attn/cute/interface.py:801-811`` in the ``flash_attn_cute`` wheel)."""
+    global _deterministic
+    _deterministic = bool(on)
+
+
+def is_deterministic() -> bool:
+    return _deterministic
+
+
+def _attn_bwd_text(q, k, v, ks, vs, o, do, lse, dq, dk, dv, dks, dvs, B, Hq, Hkv, D, Lq, Lk, Ns, *rest):
+    """Text-query attention backward: the fused key-stationary kernel for head dim 128, else (and in deterministic
+    mode) the two-kernel form.  ``rest`` = the 22 strides, the 7 layout integers, scale and the two fp32 partial
+    buffers, in the order of the C entry points."""
+    if B == 0 or Lq == 0:
+        return
+    if D == 128 and not _deterministic:
+        lq_pad = (Lq + 127) // 128 * 128
+        stats = torch.empty((2, B, Hq, lq_pad), dtype=torch.float32, device=q.device)
+        dq32 = torch.empty((B, Lq, Hq, D), dtype=torch.float32, device=q.device)
+        _lib.call("ksa_attn_bwd_fused", q, k, v, ks, vs, o, do, lse, stats, dq32, dq, dk, dv, dks, dvs,
+                  B, Hq, Hkv, D, Lq, Lk, Ns, *rest)
+    else:
+        delta = torch.empty_like(lse)
+        _lib.call("ksa_attn_bwd", q, k, v, ks, vs, o, do, lse, delta, dq, dk, dv, dks, dvs,
+                  B, Hq, Hkv, D, Lq, Lk, Ns, *rest)
+
+
+
 class _KsaAttentionFn(torch.autograd.Function):
     """Text + summary queries over text + summary keys (two-stream KSA); also plain causal attention."""
 
@@ -519,9 +555,8 @@ class _KsaAttentionFn(torch.autograd.Function):
         if Ns_k > 0:
             dks = torch.empty((B, Ns_k, Hkv, D), dtype=q.dtype, device=q.device)
             dvs = torch.empty_like(dks)
-        delta = torch.empty_like(lse)
         part_k = part_v = None
-        if Ns_k > 0 and os_ is not None and Lq > 0 and _lib.attn_bwd_num_segments(Lq) > 1:
+        if Ns_k > 0 and os_ is not None and Lq > 0 and not _deterministic and _lib.attn_bwd_num_segments(Lq) > 1:
             part_k = torch.zeros((B, Ns_k, Hkv, D), dtype=torch.float32, device=q.device)
             part_v = torch.zeros_like(part_k)
         if Lq == 0:  # summary-only call: the text-query kernels do not run, start the key grads at zero
@@ -534,12 +569,12 @@ class _KsaAttentionFn(torch.autograd.Function):
             dksrs, dksbs = dks.stride(1), dks.stride(0)
         else:
             ksrs = ksbs = vsrs = vsbs = dksrs = dksbs = 0
-        _lib.call("ksa_attn_bwd", q, k, v, ks if Ns_k > 0 else None, vs if Ns_k > 0 else None, o, do, lse, delta,
-                  dq, dk, dv, dks, dvs, B, Hq, Hkv, D, Lq, Lk, Ns_k,
-                  qrs, qbs, krs, kbs, vrs, vbs, ksrs, ksbs, vsrs, vsbs, o.stride(1), o.stride(0),
-                  dq.stride(1), dq.stride(0), dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0),
-                  dksrs, dksbs, dksrs, dksbs, q_off, k_off, s_off, chunk, max(n_sum, 1), window, tok_window,
-                  float(scale), part_k, part_v)
+        _attn_bwd_text(q, k, v, ks if Ns_k > 0 else None, vs if Ns_k > 0 else None, o, do, lse,
+                       dq, dk, dv, dks, dvs, B, Hq, Hkv, D, Lq, Lk, Ns_k,
+                       qrs, qbs, krs, kbs, vrs, vbs, ksrs, ksbs, vsrs, vsbs, o.stride(1), o.stride(0),
+                       dq.stride(1), dq.stride(0), dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0),
+                       dksrs, dksbs, dksrs, dksbs, q_off, k_off, s_off, chunk, max(n_sum, 1), window, tok_window,
+                       float(scale), part_k, part_v)
         dqs = None
         if os_ is not None:
             Nq = qs.shape[1]
@@ -660,21 +695,20 @@ class _PackedAttentionFn(torch.autograd.Function):
         dq, dk, dv = _packed_views(dqkv, B, L, Hq, Hkv, D, 0)
         o = out[:B * L].view(B, L, Hq, D)
         do = dout[:B * L].view(B, L, Hq, D)
-        delta = torch.empty_like(lse)
         part_k = part_v = None
         if Ns > 0:
             qs, ks, vs = _packed_views(qkv, B, Ns, Hq, Hkv, D, B * L)
             dqs, dks, dvs = _packed_views(dqkv, B, Ns, Hq, Hkv, D, B * L)
-            if _lib.attn_bwd_num_segments(L) > 1:
+            if not _deterministic and _lib.attn_bwd_num_segments(L) > 1:
                 part_k = torch.zeros((B, Ns, Hkv, D), dtype=torch.float32, device=qkv.device)
                 part_v = torch.zeros_like(part_k)
         else:
             qs = ks = vs = dqs = dks = dvs = None
-        _lib.call("ksa_attn_bwd", q, k, v, ks, vs, o, do, lse, delta, dq, dk, dv, dks, dvs,
-                  B, Hq, Hkv, D, L, L, Ns,
-                  rs, L * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs, Hq * D, L * Hq * D,
-                  drs, L * drs, drs, L * drs, drs, L * drs, drs, Ns * drs, drs, Ns * drs,
-                  0, 0, 0, chunk, max(n_sum, 1), window, tok_window, float(scale), part_k, part_v)
+        _attn_bwd_text(q, k, v, ks, vs, o, do, lse, dq, dk, dv, dks, dvs,
+                       B, Hq, Hkv, D, L, L, Ns,
+                       rs, L * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs, Hq * D, L * Hq * D,
+                       drs, L * drs, drs, L * drs, drs, L * drs, drs, Ns * drs, drs, Ns * drs,
+                       0, 0, 0, chunk, max(n_sum, 1), window, tok_window, float(scale), part_k, part_v)
         if Ns > 0:
             os_ = out[B * L:].view(B, Ns, Hq, D)
             dos = dout[B * L:].view(B, Ns, Hq, D)

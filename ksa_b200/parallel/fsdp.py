@@ -70,6 +70,9 @@ class FsdpEngine(TrainEngine):
         self._symm = []
         super().__init__(model, *args, world_size=world_size, rank=rank, **kw)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # Number carried by the cross-GPU flags: optimizer steps taken by THIS engine object.  It is not step_count,
+        # which a checkpoint load moves forward while the flags of a fresh process still hold zero.
+        self._flag_epoch = 0
         self._epoch_ring = torch.zeros(32, 1, dtype=torch.int32)
         if self.device.type == "cuda":
             self._epoch_ring = self._epoch_ring.pin_memory()
@@ -237,7 +240,7 @@ class FsdpEngine(TrainEngine):
     def _write_hyper(self) -> None:
         super()._write_hyper()
         slot = (self._hyper_slot - 1) % len(self._hyper_events)   # same slot and event as the hyper-parameters
-        self._epoch_ring[slot, 0] = self.step_count
+        self._epoch_ring[slot, 0] = self._flag_epoch
         self.epoch.copy_(self._epoch_ring[slot], non_blocking=True)
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
@@ -292,6 +295,7 @@ class FsdpEngine(TrainEngine):
                 if ui not in self._done_units:
                     self._unit_grads_ready(ui, can_attach=False)
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+            self._flag_epoch += 1
             return
         self._collect_autograd_grads()
         self.grad_sq.zero_()

@@ -78,6 +78,31 @@ def _worker(rank, world, port, out_q):
             assert abs(gc - gf) < 0.05 * gc, (key, gc, gf)
             for a, b in zip(wc, wf):
                 assert (a - b).norm() <= 1e-2 * a.norm().clamp_min(1e-6), key
+        # --- resume: 2 steps, state out, a NEW engine (fresh flags, step counter moved forward by the load), step 3
+        def fresh():
+            torch.manual_seed(0)
+            m = get_model_class(cfg.model_class)(cfg)
+            m.init_weights(seed=0)
+            return FsdpEngine(m.to(dev).to(torch.bfloat16), lr=1e-3, weight_decay=0.1, clip_value=1.0,
+                              world_size=world, rank=rank, comm="fused", overlap="stream")
+        eng = fresh()
+        for s in range(2):
+            x = data[s, rank].to(dev)
+            eng.train_step(x[:, :-1].contiguous(), x[:, 1:].contiguous())
+        torch.cuda.synchronize(); _lib.check_status(); dist.barrier()
+        state = {"step": eng.step_count,
+                 "units": {k: {kk: (vv.clone() if torch.is_tensor(vv) else vv) for kk, vv in u.items()}
+                           for k, u in eng.state_dict()["units"].items()}}
+        eng.close()
+        eng = fresh()
+        eng.load_state_dict(state)
+        assert eng.step_count == 2
+        x = data[2, rank].to(dev)
+        resumed = float(eng.train_step(x[:, :-1].contiguous(), x[:, 1:].contiguous()))
+        torch.cuda.synchronize(); _lib.check_status(); dist.barrier()
+        eng.close()
+        uninterrupted = results[("fused", "stream")][0][2]
+        assert abs(resumed - uninterrupted) < 3e-2, (resumed, uninterrupted)
         out_q.put((rank, "ok", lf))
     except Exception as e:  # noqa: BLE001
         import traceback

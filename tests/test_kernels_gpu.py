@@ -243,6 +243,50 @@ def test_ksa_attention_fwd_bwd(B, L, Hq, Hkv, D, C, S, W):
         check(a.grad, b_.grad, 3e-2, f"ksa {n}")
 
 
+@pytest.mark.parametrize("L", [8192, 32768])
+def test_ksa_attention_benchmark_shape_against_blockwise_oracle(L):
+    """16 query / 8 KV heads of 128, chunk 128 + 1 summary, window 8: forward and backward against the fp32 block-mode
+    oracle on the GPU.  At 32768 tokens the 256 summary keys fill two key tiles and every summary key tile's query
+    range is split into segments whose fp32 partial sums are folded by the summary-query kernel."""
+    B, Hq, Hkv, D, C, S, W = 1, 16, 8, 128, 128, 1, 8
+    t = _attn_inputs(B, L, Hq, Hkv, D, C, S)
+    xs = [x.clone().requires_grad_() for x in t]
+    o_t, o_s = ops.ksa_attention(*xs, C, S, W)
+    g_t, g_s = bf(*o_t.shape), bf(*o_s.shape)
+    torch.autograd.backward([o_t, o_s], [g_t, g_s])
+    fs = [x.detach().float().requires_grad_() for x in t]
+    r_t, r_s = ref.ksa_attention_blockwise(*fs, C, S, W, q_block=2048)
+    torch.autograd.backward([r_t, r_s], [g_t.float(), g_s.float()])
+    check(o_t, r_t, 1.5e-2, "ksa o_text")
+    check(o_s, r_s, 1.5e-2, "ksa o_summary")
+    for n, a, b_ in zip(["dq_t", "dk_t", "dv_t", "dq_s", "dk_s", "dv_s"], xs, fs):
+        check(a.grad, b_.grad, 3e-2, f"ksa {n} L={L}")
+
+
+def test_attention_backward_deterministic_mode_is_bit_reproducible():
+    """With ``ops.set_deterministic(True)`` the text-query backward runs as two kernels that never add across CTAs and
+    the summary key tiles are not split: two runs give identical bits, and they match the fused backward to rounding."""
+    B, L, Hq, Hkv, D, C, S, W = 1, 2048, 4, 2, 128, 128, 1, 2
+    t = _attn_inputs(B, L, Hq, Hkv, D, C, S)
+    g_t, g_s = bf(B, L, Hq, D), bf(B, t[3].shape[1], Hq, D)
+
+    def grads():
+        xs = [x.clone().requires_grad_() for x in t]
+        o_t, o_s = ops.ksa_attention(*xs, C, S, W)
+        torch.autograd.backward([o_t, o_s], [g_t, g_s])
+        return [x.grad for x in xs]
+
+    fused = grads()
+    ops.set_deterministic(True)
+    try:
+        a, b_ = grads(), grads()
+    finally:
+        ops.set_deterministic(False)
+    for n, x, y, z in zip(["dq_t", "dk_t", "dv_t", "dq_s", "dk_s", "dv_s"], a, b_, fused):
+        assert torch.equal(x, y), f"{n} differs between two deterministic runs"
+        check(z, x.float(), 2e-2, f"fused vs deterministic {n}")
+
+
 @pytest.mark.parametrize("L,window", [(1024, -1), (1500, -1), (2048, 300)])
 def test_causal_attention_fwd_bwd(L, window):
     B, Hq, Hkv, D = 2, 4, 2, 128

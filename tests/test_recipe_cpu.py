@@ -45,6 +45,31 @@ def test_blended_dataset_is_deterministic_and_resumable(tmp_path):
                                                              for k in state["dataset_state"] if k not in ("rng_state", "pending_draw")) - 2
 
 
+def test_dataloader_state_of_rank_0_resumes_every_rank_on_its_own_samples(tmp_path):
+    """The saved state is rank 0's; a draw that was handed out only in part must continue with each rank's own
+    positions of that draw, not with rank 0's."""
+    _, recipe = _corpora(tmp_path, 256)
+    mk = lambda r: KaiMMapDataset(recipe, 64, seed=7, global_batch_size=8, rank=r, world_size=2)
+    its = [iter(mk(0)), iter(mk(1))]
+    ds0 = mk(0)
+    it0 = iter(ds0)
+    for _ in range(2):                      # two of rank 0's four samples of the first draw
+        next(it0)
+    state = ds0.state_dict()
+    expect = []
+    for r in (0, 1):                        # uninterrupted readers: skip two, keep the next six
+        for _ in range(2):
+            next(its[r])
+        expect.append([next(its[r])["input_ids"] for _ in range(6)])
+    assert not torch.equal(expect[0][0], expect[1][0])
+    for r in (0, 1):
+        d = mk(r)
+        d.load_state_dict(state)
+        it = iter(d)
+        got = [next(it)["input_ids"] for _ in range(6)]
+        assert all(torch.equal(a, b) for a, b in zip(got, expect[r])), f"rank {r}"
+
+
 def test_schedulers():
     wsd = get_lr_lambda("wsd", num_warmup_steps=10, num_decay_steps=10, num_training_steps=100, base_lr=1.0, min_lr=0.1)
     assert wsd(0) == 0 and wsd(5) == 0.5 and wsd(50) == 1.0 and abs(wsd(95) - 0.55) < 1e-9 and wsd(100) == 0.1
