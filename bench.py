@@ -232,7 +232,7 @@ def run_ours(args) -> dict:
         "config": {"model": MODEL_NAME, "global_batch": dp * B, "seq_len": L,
                    "parallelism": (f"fsdp{world}" + (f"+cp{cp}" if cp > 1 else "")) if world > 1 else "single",
                    "layers": cfg.num_layers,
-                   "chunk": cfg.summary_chunk_size, "window_chunks": 8, "optimizer": "AdamW fp32 master",
+                   "chunk": cfg.summary_chunk_size, "window_chunks": cfg.summary_sliding_chunk_num, "optimizer": "AdamW fp32 master",
                    "l2": "working set (weights+optimizer state+activations, >30 GB) exceeds L2; no explicit flush",
                    "cuda_graph": use_graph, "comm": getattr(engine, "comm", "none"),
                    "overlap": getattr(engine, "overlap", "none")},

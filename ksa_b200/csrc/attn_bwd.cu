@@ -15,7 +15,7 @@
 //
 // The reference's sm_100 backward is key-stationary with dQ added into a global
 // fp32 buffer by bulk reduce-adds plus separate pre- and post-processing kernels
-// (FA!flash_attn/cute/flash_bwd_sm100.py:1645-1798, :2422-2636).
+// (flash_attn/cute/flash_bwd_sm100.py:1645-1798, :2422-2636 in the reference's flash_attn_cute wheel).
 #include "attn_common.cuh"
 #include "host.h"
 

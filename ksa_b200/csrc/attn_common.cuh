@@ -7,7 +7,8 @@
 // so for every query row the allowed keys of a key tile form one interval
 // [lo, hi] of columns.  No block list and no mask tensor is ever built; the
 // reference evaluates a mask_mod per element to build O(M*N) block lists
-// (FA!flash_attn/cute/compute_block_sparsity.py:277, SA!summary_attn/mask.py:19-59).
+// (flash_attn/cute/compute_block_sparsity.py:277 in its flash_attn_cute wheel, summary_attn/mask.py:19-59 in its
+// summary_attn wheel).
 // Plain causal attention is the case W = "infinite", no summary keys; a token
 // sliding window adds t - u < tok_window.
 #pragma once

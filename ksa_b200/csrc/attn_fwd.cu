@@ -17,7 +17,8 @@
 // the A operand of the second product), O0 @256, O1 @256+HD.
 //
 // Bar: FlashAttentionForwardSm100 + block-sparse lists in the reference wheel
-// (FA!flash_attn/cute/flash_fwd_sm100.py:68, SA!summary_attn/interface.py:77-82).
+// (flash_attn/cute/flash_fwd_sm100.py:68 in the flash_attn_cute wheel, summary_attn/interface.py:77-82 in the
+// summary_attn wheel).
 #include "attn_common.cuh"
 #include "host.h"
 

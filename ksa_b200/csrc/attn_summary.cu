@@ -6,7 +6,7 @@
 // runs on the CUDA cores next to the tensor-core kernel that serves the text
 // queries.  The reference pushes these rows through the same block-sparse
 // kernel as a 128-row tile that is almost entirely masked
-// (SA!summary_attn/mask.py:19-31).
+// (summary_attn/mask.py:19-31 in the reference's summary_attn wheel).
 #include "common.cuh"
 #include "host.h"
 

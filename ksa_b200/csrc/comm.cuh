@@ -287,8 +287,8 @@ __device__ __forceinline__ bool run_reduce_adamw_job(const ReduceAdamwJob& j, in
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         float gk = gg[k] * gscale;
-        sq += gk * gk;
         if (j.clip_value > 0.f) gk = fminf(fmaxf(gk, -j.clip_value), j.clip_value);
+        sq += gk * gk;   // norm of the clipped gradients, as in adamw_kernel
         mm[k] = j.beta1 * mm[k] + (1.f - j.beta1) * gk;
         vv[k] = j.beta2 * vv[k] + (1.f - j.beta2) * gk * gk;
         const float denom = sqrtf(vv[k] / bc2) + j.eps;

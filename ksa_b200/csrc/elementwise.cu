@@ -668,8 +668,8 @@ adamw_kernel(float* __restrict__ master, const float* __restrict__ grad, float* 
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float gj = g[j] * gscale;
-      sq += gj * gj;
       if (clip_value > 0.f) gj = fminf(fmaxf(gj, -clip_value), clip_value);
+      sq += gj * gj;   // norm of the clipped gradients: the reference clips first (recipes/pretrain_kai_summary_unified.py:1045-1049)
       mm[j] = beta1 * mm[j] + (1.f - beta1) * gj;
       vv[j] = beta2 * vv[j] + (1.f - beta2) * gj * gj;
       const float denom = sqrtf(vv[j] / bc2) + eps;

@@ -33,7 +33,8 @@ extern "C" {
 //     device that owns the buffers must already be current on the calling thread.
 //   * the first call on each device looks up the device address of the array
 //     (cudaGetSymbolAddress) and remembers it; make that first call before any stream
-//     capture begins.
+//     capture begins.  Where CUDA loads modules lazily, that first call may also be the one
+//     that loads the module holding the array (the 2.4 MB appear then, once).
 //   * all calls share the one array.  Nothing in it has to start at zero (every partial row
 //     that is read was written by the same call), but two calls whose kernels overlap on the
 //     GPU (different streams, no dependency between them) race on it and corrupt dw.

@@ -48,6 +48,7 @@ class ChunkedDistillLossComputer:
         kl_sum = torch.zeros((), device=h.device, dtype=torch.float32)
         w = self.weight
         w_grad = torch.zeros_like(w, dtype=torch.float32) if w.requires_grad else None
+        w_used = False
         for s in range(0, B * L, self.minibatch_size):
             e = min(B * L, s + self.minibatch_size)
             hs = h[s:e].detach().requires_grad_(True)
@@ -60,16 +61,18 @@ class ChunkedDistillLossComputer:
             tp = F.softmax(t_logits, -1)
             kl_c = ((tp * (torch.log(tp.clamp_min(1e-20)) - logp)).sum(-1) * valid).sum()
             loss_c = (self.lm_factor * ce_c + self.kl_factor * kl_c) / n_valid * scale
-            grads = torch.autograd.grad(loss_c, [hs] + ([w] if w_grad is not None else []))
+            # a weight with an fp32 ``main_grad`` buffer gets its gradient written there by ops.linear's backward,
+            # and autograd sees none for it (allow_unused)
+            grads = torch.autograd.grad(loss_c, [hs] + ([w] if w_grad is not None else []), allow_unused=True)
             grad_h[s:e] = grads[0]
-            if w_grad is not None:
+            if w_grad is not None and grads[1] is not None:
                 w_grad += grads[1].float()
+                w_used = True
             ce_sum += ce_c.detach()
             kl_sum += kl_c.detach()
-        if extra_loss is not None:
-            (extra_loss * scale).backward(retain_graph=True)
-        student_hidden.backward(grad_h.view(B, L, D))
-        if w_grad is not None:
+        # The lm_head gradient goes in BEFORE the backward pass through the model: an engine that reduces and updates
+        # a unit as soon as the backward pass has left it would otherwise miss it.
+        if w_grad is not None and w_used:
             mg = getattr(w, "main_grad", None)
             if mg is not None:
                 if getattr(w, "_grad_written", False):
@@ -79,6 +82,12 @@ class ChunkedDistillLossComputer:
                     w._grad_written = True
             else:
                 w.grad = w_grad.to(w.dtype) if w.grad is None else w.grad + w_grad.to(w.dtype)
+        # one backward pass through the model for the hidden-state gradient and the extra (attention matching) loss
+        roots, root_grads = [student_hidden], [grad_h.view(B, L, D)]
+        if extra_loss is not None and extra_loss.requires_grad:
+            roots.append(extra_loss * scale)
+            root_grads.append(None)
+        torch.autograd.backward(roots, root_grads)
         ce, kl = ce_sum / n_valid, kl_sum / n_valid
         total = self.lm_factor * ce + self.kl_factor * kl + (extra_loss.detach() if extra_loss is not None else 0.0)
         return {"total_loss": total, "ce_loss": ce, "kl_loss": kl}

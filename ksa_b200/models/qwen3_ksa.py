@@ -79,7 +79,10 @@ class KsaAttention(nn.Module):
             if cfg.summary_independent_qk_norm and cfg.q_norm:
                 self.q_norm_summary = RMSNormParam(Dh, cfg.norm_eps)
                 self.k_norm_summary = RMSNormParam(Dh, cfg.norm_eps)
-        self.mix_coeff = 1.0  # summary_mix_qkv anneal, set by the trainer per iteration
+        # summary_mix_qkv anneal: the host value (for logging) and, once the trainer has set it, a device scalar
+        # that every layer shares, so that a step replayed from a CUDA graph reads the current value
+        self.mix_coeff = 1.0
+        self.mix_coeff_dev: Optional[torch.Tensor] = None
 
     def _norm_w(self, m):
         return None if m is None else m.scale
@@ -169,13 +172,23 @@ class KsaDecoderLayer(nn.Module):
                     ops.gemm(h[n_text:], a.wqkv_summary.weight, out=qkv[n_text:])
                 else:
                     qkv = ops.dual_linear(h, a.wqkv.weight, a.wqkv_summary.weight, n_text)
-                if a.mix_coeff < 1.0:  # anneal summary projections towards the base projections
-                    base_s = ops.linear(h[n_text:], a.wqkv.weight)
-                    mixed = a.mix_coeff * qkv[n_text:].float() + (1.0 - a.mix_coeff) * base_s.float()
-                    qkv = torch.cat([qkv[:n_text], mixed.to(qkv.dtype)])
             else:
                 qkv = _col_linear(tp, h, a.wqkv.weight)
-            if a.q_norm_summary is not None:
+            if a.wqkv_summary is not None and getattr(cfg, "summary_mix_qkv", False):
+                # Anneal of the summary rows from their own projections towards the base ones, blended AFTER the QK
+                # norm, each side with its own norm weights (muse/models/qwen3_sa/_layers.py:153-171).  RoPE is
+                # linear, so blending the rotated rows equals rotating the blend.
+                nq, nk = a._norm_w(a.q_norm), a._norm_w(a.k_norm)
+                sq = a.q_norm_summary.scale if a.q_norm_summary is not None else nq
+                sk = a.k_norm_summary.scale if a.k_norm_summary is not None else nk
+                rot = lambda rows, wq, wk, pos: ops.qk_norm_rope_packed(  # noqa: E731
+                    rows.contiguous(), wq, wk, pos, Hq, Hkv, Dh, cfg.rope_base, cfg.norm_eps, meta.rope_interleaved)
+                own = rot(qkv[n_text:], sq, sk, meta.pos[n_text:])
+                base = rot(ops.linear(h[n_text:], a.wqkv.weight), nq, nk, meta.pos[n_text:])
+                mix = a.mix_coeff_dev if a.mix_coeff_dev is not None else a.mix_coeff
+                mixed = torch.lerp(base.float(), own.float(), mix.to(base.device) if torch.is_tensor(mix) else mix)
+                qkv = torch.cat([rot(qkv[:n_text], nq, nk, meta.pos[:n_text]), mixed.to(qkv.dtype)])
+            elif a.q_norm_summary is not None:
                 qkv = torch.cat([
                     ops.qk_norm_rope_packed(qkv[:n_text].contiguous(), a._norm_w(a.q_norm), a._norm_w(a.k_norm),
                                             meta.pos[:n_text], Hq, Hkv, Dh, cfg.rope_base, cfg.norm_eps,
@@ -614,6 +627,12 @@ class Qwen3SummaryModel(Qwen3Model):
         else:
             coeff = 1.0 - (iteration - cfg.summary_mix_start_iter) / max(
                 1, cfg.summary_mix_end_iter - cfg.summary_mix_start_iter)
+        dev = self.tok_embeddings.weight.device
+        if cfg.summary_mix_qkv:
+            if getattr(self, "_mix_coeff_dev", None) is None or self._mix_coeff_dev.device != dev:
+                self._mix_coeff_dev = torch.ones((), dtype=torch.float32, device=dev)
+            self._mix_coeff_dev.fill_(coeff)
         for layer in self.layers:
             layer.attn.mix_coeff = coeff
+            layer.attn.mix_coeff_dev = self._mix_coeff_dev if cfg.summary_mix_qkv else None
         return coeff

@@ -816,10 +816,10 @@ def adamw_step(master, grad, m, v, out_bf16, hyper, beta1, beta2, eps, weight_de
     if not _cuda(master):
         lr, bc1, bc2, gs = [float(x) for x in hyper.tolist()]
         g = grad.float() * gs
-        if sumsq is not None:
-            sumsq += (g * g).sum()
         if clip_value > 0:
             g = g.clamp(-clip_value, clip_value)
+        if sumsq is not None:
+            sumsq += (g * g).sum()
         m.mul_(beta1).add_(g, alpha=1 - beta1)
         v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
         master.mul_(1 - lr * weight_decay)

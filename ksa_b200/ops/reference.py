@@ -111,7 +111,7 @@ def ksa_attention(q_t, k_t, v_t, q_s, k_s, v_s, chunk: int, n_sum: int, window: 
     Returns ``(o_t, o_s)`` in the input dtype.  Semantics: a text query sees its
     own chunk causally, the previous ``window`` chunks' text, and the summaries
     of every older chunk; a summary query sees its own chunk's text and the
-    summaries of that chunk up to itself (``SA!summary_attn/mask.py:19-31``).
+    summaries of that chunk up to itself (``summary_attn/mask.py:19-31`` in the reference's ``summary_attn`` wheel).
     ``skip_old_summary`` drops the old-summary keys (pure sliding-chunk attention).
     """
     B, L, Hq, D = q_t.shape
@@ -260,15 +260,15 @@ def adamw_step_(master: torch.Tensor, grad: torch.Tensor, m: torch.Tensor, v: to
                 lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: int,
                 grad_scale: float = 1.0, clip_value: float = 0.0,
                 out_bf16: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """In-place decoupled AdamW on fp32 state; returns the sum of squared (scaled) gradients.
+    """In-place decoupled AdamW on fp32 state; returns the sum of squared (scaled, clipped) gradients.
 
     ``clip_value > 0`` clamps each gradient element to ``[-clip, clip]`` first
     (the reference clips by value, ``muse/training/common.py:122-141``).
     """
     g = grad.float() * grad_scale
-    sq = (g * g).sum()
     if clip_value > 0:
         g = g.clamp(-clip_value, clip_value)
+    sq = (g * g).sum()   # of the clipped gradients: the reference clips before it measures the norm
     m.mul_(beta1).add_(g, alpha=1 - beta1)
     v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
     bc1 = 1 - beta1 ** step

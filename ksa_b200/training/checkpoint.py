@@ -86,6 +86,8 @@ def engine_full_state(engine, with_optimizer: bool = True) -> Dict[str, Dict[str
             full = _gather_unit(engine, getattr(u, attr), u)
             for s in u.slots:
                 out[key][s.name] = full[s.offset:s.offset + s.numel].view(s.shape).to("cpu", copy=True)
+    for s in getattr(engine, "frozen_slots", []):     # frozen weights: saved with the model, no optimizer state
+        out["model"][s.name] = s.param.detach().to(device="cpu", dtype=torch.float32, copy=True)
     return out
 
 
@@ -114,6 +116,13 @@ def load_engine_full_state(engine, model_state: Optional[Dict[str, torch.Tensor]
                 if model_state is not None and s.name in model_state:
                     u.compute[s.offset:s.offset + s.numel].copy_(
                         model_state[s.name].reshape(-1).to(device=engine.device, dtype=torch.float32))
+        for s in getattr(engine, "frozen_slots", []):
+            if model_state is None:
+                continue
+            if s.name not in model_state:
+                missing.append(s.name)
+                continue
+            s.param.data.copy_(model_state[s.name].to(device=engine.device, dtype=torch.float32).view(s.shape))
     if strict and missing:
         raise KeyError(f"checkpoint lacks {len(missing)} parameters, e.g. {missing[:4]}")
     return missing
@@ -154,11 +163,11 @@ class AppState(Stateful):
         model = self._to_muse(full["model"])
         m1, m2 = self._to_muse(full["exp_avg"]), self._to_muse(full["exp_avg_sq"])
         step = torch.tensor(float(self.engine.step_count))
-        optim_state = {k: {"exp_avg": m1[k], "exp_avg_sq": m2[k], "step": step.clone()} for k in model}
+        optim_state = {k: {"exp_avg": m1[k], "exp_avg_sq": m2[k], "step": step.clone()} for k in model if k in m1}
         e = self.engine
         optim = {"state": optim_state,
                  "param_groups": [{"lr": e.base_lr, "betas": (e.beta1, e.beta2), "eps": e.eps,
-                                   "weight_decay": e.weight_decay, "params": list(model)}]}
+                                   "weight_decay": e.weight_decay, "params": list(optim_state)}]}
         training: Dict[str, Any] = {"engine_step": e.step_count}
         if self.step_scheduler is not None:
             training["step_scheduler"] = self.step_scheduler.state_dict()

@@ -99,12 +99,17 @@ class TrainEngine:
         taken = set()
         units = []
         names = {id(p): n for n, p in model.named_parameters()}
+        # Frozen parameters (requires_grad False when the engine is built, e.g. the base weights of a distillation
+        # run) stay out of the units: nothing decays or updates them, as in the reference, whose optimizer holds
+        # only trainable parameters (muse/models/base.py:380-388).
+        frozen = {id(p) for p in model.parameters() if not p.requires_grad}
+        self._frozen_params = [(names[i], p) for i, p in ((id(p), p) for p in model.parameters()) if i in frozen]
         for i, m in enumerate(layer_mods):
-            ps = [(names[id(p)], p) for p in m.parameters()]
-            taken.update(id(p) for _, p in ps)
+            ps = [(names[id(p)], p) for p in m.parameters() if id(p) not in frozen]
+            taken.update(id(p) for p in m.parameters())
             units.append((f"layer{i}", ps))
         # what is left is split in two: parameters used before the layers (embeddings) and after them (norm, head)
-        root = [(n, p) for n, p in model.named_parameters() if id(p) not in taken]
+        root = [(n, p) for n, p in model.named_parameters() if id(p) not in taken and id(p) not in frozen]
         embed = [(n, p) for n, p in root if "embedding" in n]
         head = [(n, p) for n, p in root if "embedding" not in n]
         out = []
@@ -132,6 +137,7 @@ class TrainEngine:
             unit.shard_lo, unit.shard_hi = self._shard_range(unit.size)
             planned.append(unit)
         self._allocate_storage(planned)
+        self._place_frozen()
         for unit in planned:
             with torch.no_grad():
                 for s in unit.slots:
@@ -142,6 +148,21 @@ class TrainEngine:
                     s.param.main_grad = unit.grad[s.offset:s.offset + s.numel].view(s.shape)
                     s.param._grad_written = False
             self.units.append(unit)
+
+    def _place_frozen(self) -> None:
+        """Frozen parameters: one flat buffer in the compute dtype, replicated on every rank; no master copy, no
+        moments, no gradient buffer."""
+        self.frozen_slots: List[ParamSlot] = []
+        off = 0
+        for n, p in self._frozen_params:
+            self.frozen_slots.append(ParamSlot(n, p, off, p.numel(), p.shape))
+            off += _round_up(p.numel(), _ALIGN)
+        self.frozen_compute = torch.zeros(max(off, 1), dtype=self.param_dtype, device=self.device)
+        with torch.no_grad():
+            for s in self.frozen_slots:
+                view = self.frozen_compute[s.offset:s.offset + s.numel].view(s.shape)
+                view.copy_(s.param.detach().to(device=self.device, dtype=torch.float32))
+                s.param.data = view
 
     def _allocate_storage(self, units: List[Unit]) -> None:
         """Allocate compute / gradient / optimizer-state buffers of every unit (overridden for symmetric memory)."""
@@ -233,7 +254,12 @@ class TrainEngine:
         return self.grad_sq.sqrt()
 
     # ------------------------------------------------------------------ steps
-    def forward_backward(self, tokens: torch.Tensor, labels: torch.Tensor, **kw) -> torch.Tensor:
+    def forward_backward(self, tokens: torch.Tensor, labels: torch.Tensor, step_fn=None, **kw) -> torch.Tensor:
+        """Forward and backward of one micro-batch.  ``step_fn(tokens, labels) -> loss`` replaces the plain language
+        model loss: it must run the model's forward AND one backward pass itself and return the detached loss
+        (distillation uses it), so that whatever the engine hangs on the forward and backward passes still applies."""
+        if step_fn is not None:
+            return step_fn(tokens, labels)
         loss = self.model(tokens, labels=labels, **kw)
         loss.backward()
         return loss.detach()
@@ -323,6 +349,9 @@ class TrainEngine:
                     src = state[s.name].to(device=self.device, dtype=torch.float32).reshape(-1)
                     u.compute[s.offset:s.offset + s.numel].copy_(src)
                     self._master_init(u, s, src)
+            for s in self.frozen_slots:
+                if s.name in state:
+                    s.param.data.copy_(state[s.name].to(device=self.device, dtype=torch.float32).view(s.shape))
 
 
 class _CapturedStep:

@@ -357,34 +357,34 @@ def train(args) -> dict:
 
 def _distill_step(engine, model, ids, labels, args, mse_fn, cos_fn):
     """Student forward (with summaries) + no-grad teacher forward (same weights, no summaries): LM + KL + attention
-    matching losses (``recipes/pretrain_kai_summary_unified.py:967-1013``)."""
+    matching losses (``recipes/pretrain_kai_summary_unified.py:967-1013``).  The losses run as the engine's
+    ``step_fn``, inside its forward_backward, so gradient reduction, the optimizer and (under FSDP) the gathers of the
+    refreshed weights are the engine's own."""
     import torch
     from ksa_b200.losses import ChunkedDistillLossComputer
     from ksa_b200.losses.distill import rms_normalize
-    if engine.micro_step == 0:
-        engine.zero_grad()
-    model.skip_output_layer = True
-    with torch.no_grad():
-        t_hidden = model(ids, collect_attn=True, use_summary=False)
-        t_attn = list(model.last_attn_outputs)
-    s_hidden = model(ids, collect_attn=True)
-    s_attn = list(model.last_attn_outputs)
-    model.skip_output_layer = False
-    if getattr(model.config, "summary_distill_attention_norm", False):
-        s_attn, t_attn = [rms_normalize(a) for a in s_attn], [rms_normalize(a) for a in t_attn]
-    extra = args.distill_attn_mse_factor * mse_fn(s_attn, t_attn)
-    if args.distill_attn_cos_factor:
-        extra = extra + args.distill_attn_cos_factor * cos_fn(s_attn, t_attn)
-    comp = ChunkedDistillLossComputer(model.lm_head_weight, args.chunked_loss_minibatch_size,
-                                      args.distill_lm_loss_factor, args.distill_kl_loss_factor, enable_kl=True)
-    out = comp.forward_and_backward(s_hidden, t_hidden, labels, engine.grad_accum_steps, extra_loss=extra)
-    engine.micro_step += 1
-    if engine.micro_step == engine.grad_accum_steps:
-        engine._write_hyper()
-        engine.optimizer_step()
-        engine.step_count += 1
-        engine.micro_step = 0
-    return out["total_loss"]
+
+    def step_fn(tokens, targets):
+        model.skip_output_layer = True
+        try:
+            with torch.no_grad():
+                t_hidden = model(tokens, collect_attn=True, use_summary=False)
+                t_attn = list(model.last_attn_outputs)
+            s_hidden = model(tokens, collect_attn=True)
+            s_attn = list(model.last_attn_outputs)
+        finally:
+            model.skip_output_layer = False
+        if getattr(model.config, "summary_distill_attention_norm", False):
+            s_attn, t_attn = [rms_normalize(a) for a in s_attn], [rms_normalize(a) for a in t_attn]
+        extra = args.distill_attn_mse_factor * mse_fn(s_attn, t_attn)
+        if args.distill_attn_cos_factor:
+            extra = extra + args.distill_attn_cos_factor * cos_fn(s_attn, t_attn)
+        comp = ChunkedDistillLossComputer(model.lm_head_weight, args.chunked_loss_minibatch_size,
+                                          args.distill_lm_loss_factor, args.distill_kl_loss_factor, enable_kl=True)
+        out = comp.forward_and_backward(s_hidden, t_hidden, targets, engine.grad_accum_steps, extra_loss=extra)
+        return out["total_loss"]
+
+    return engine.train_step(ids, labels, step_fn=step_fn)
 
 
 def main(argv=None):

@@ -156,3 +156,37 @@ def test_training_state_keys_can_be_skipped_required_and_extended(tmp_path):
     eng4, _ = _engine(seed=5)
     with pytest.raises(Exception, match="Missing required training state keys"):
         load_checkpoint(AppState(eng4, required_training_state_keys=["ema"]), ck, str(tmp_path))
+
+
+def test_frozen_parameters_are_neither_decayed_nor_updated_and_survive_a_checkpoint(tmp_path):
+    """Distillation freezes the base weights before the engine is built: they stay out of the optimizer units, so
+    weight decay leaves them bit-identical, while the summary parameters train; a checkpoint carries both."""
+    from ksa_b200.training.common import freeze_params_by_pattern
+    cfg = get_preset("qwen3-ksa-tiny").merge({"num_layers": 2, "summary_layer_freq": [1, 0], "embed_dim": 64,
+                                               "intermediate_dim": 128, "vocab_size": 256, "head_dim": 16})
+    model = get_model_class(cfg.model_class)(cfg)
+    model.init_weights(seed=0)
+    stats = freeze_params_by_pattern(model, ["summary_embedding", "_summary"])
+    assert stats["trainable"] > 0 and stats["frozen"] > 0
+    eng = TrainEngine(model, lr=1e-2, weight_decay=0.5)
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    _train(eng, cfg, 3)
+    changed = 0
+    for n, p in model.named_parameters():
+        if p.requires_grad:
+            changed += int(not torch.equal(p.detach(), before[n]))
+        else:
+            assert torch.equal(p.detach(), before[n]), f"frozen parameter {n} changed"
+    assert changed > 0
+    assert {s.name for u in eng.units for s in u.slots}.isdisjoint(s.name for s in eng.frozen_slots)
+    ck = DistributedCheckpointer()
+    path = save_checkpoint(AppState(eng), ck, str(tmp_path), 3)
+    tree = flatten_model_state(dcp_to_state_dict(path))
+    assert "model.layers.0.attn.q_proj.weight" in tree and "model.layers.0.attn.q_proj_summary.weight" in tree
+    model2 = get_model_class(cfg.model_class)(cfg)
+    model2.init_weights(seed=4)
+    freeze_params_by_pattern(model2, ["summary_embedding", "_summary"])
+    eng2 = TrainEngine(model2, lr=1e-2, weight_decay=0.5)
+    load_checkpoint(AppState(eng2), ck, str(tmp_path))
+    for (n, a), (_, b) in zip(model.named_parameters(), model2.named_parameters()):
+        assert torch.equal(a.detach(), b.detach()), n

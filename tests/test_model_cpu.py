@@ -143,6 +143,44 @@ def test_tiny_model_matches_interleaved_reference_and_trains():
     assert abs(losses[0] - math.log(cfg.vocab_size)) < 0.5 and losses[-1] < losses[0]
 
 
+def test_summary_mix_qkv_blends_after_the_qk_norm_with_each_side_norm():
+    """``summary_mix_qkv``: mix = 1 is the model without the anneal; mix = 0 treats the summary rows with the base
+    projections AND the base QK norms; in between the rotated rows are the linear blend of the two ends."""
+    base_cfg = get_preset("qwen3-ksa-tiny").merge({"num_layers": 2, "summary_layer_freq": [1, 1], "embed_dim": 64,
+                                                    "intermediate_dim": 128, "vocab_size": 256, "head_dim": 16,
+                                                    "summary_independent_qk_norm": True})
+    cfg = base_cfg.merge({"summary_mix_qkv": True, "summary_mix_start_iter": 0, "summary_mix_end_iter": 10})
+    model = get_model_class(cfg.model_class)(cfg)
+    model.init_weights(seed=0)
+    with torch.no_grad():   # make the two norms differ
+        for layer in model.layers:
+            layer.attn.q_norm_summary.scale.mul_(1.5)
+            layer.attn.k_norm.scale.mul_(0.7)
+    tokens = torch.randint(0, cfg.vocab_size, (1, 256))
+
+    def first_layer_rows(m, it):
+        m.set_mix_coeff(it)
+        got = {}
+        m(tokens, kv_sink=lambda i, qkv, is_sum: got.setdefault(i, qkv.detach().clone()))
+        return got[0]
+
+    with torch.no_grad():
+        q1, qh, q0 = first_layer_rows(model, 0), first_layer_rows(model, 5), first_layer_rows(model, 10)
+        assert model.layers[0].attn.mix_coeff == 0.0
+        plain = get_model_class(base_cfg.model_class)(base_cfg)
+        plain.load_state_dict(model.state_dict())
+        assert torch.allclose(first_layer_rows(plain, 0), q1, atol=1e-6)
+        assert torch.allclose(qh, 0.5 * (q0 + q1), atol=1e-5)
+        shared = get_model_class(base_cfg.model_class)(base_cfg)
+        sd = model.state_dict()
+        for i in range(2):
+            sd[f"layers.{i}.attn.wqkv_summary.weight"] = sd[f"layers.{i}.attn.wqkv.weight"]
+            sd[f"layers.{i}.attn.q_norm_summary.scale"] = sd[f"layers.{i}.attn.q_norm.scale"]
+            sd[f"layers.{i}.attn.k_norm_summary.scale"] = sd[f"layers.{i}.attn.k_norm.scale"]
+        shared.load_state_dict(sd)
+        assert torch.allclose(first_layer_rows(shared, 0), q0, atol=1e-5)
+
+
 def test_muse_and_hf_key_roundtrip():
     cfg = get_preset("qwen3-ksa-tiny")
     model = Qwen3SummaryModel(cfg)

@@ -136,3 +136,58 @@ def test_recipe_starts_from_an_hf_directory_with_skip_and_allow_lists(tmp_path):
     r = train(get_argument_parser().parse_args(args + ["--output-dir", str(tmp_path / "c"), "--allow-random-init-params",
                                                        ",".join(missing)]))
     assert r["steps"] == 2
+
+
+def _distill_rank(rank, world, port, argv, out_q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    try:
+        r = train(get_argument_parser().parse_args(argv))
+        out_q.put((rank, "ok", r))
+    except Exception:  # noqa: BLE001
+        import traceback
+        out_q.put((rank, "fail", traceback.format_exc()))
+
+
+def test_recipe_distillation_on_one_and_on_two_ranks(tmp_path):
+    """``--enable-distill`` runs inside the engine's forward_backward (student + no-grad teacher, LM + KL + attention
+    matching): the frozen base weights stay put, the summary parameters move, and two FSDP ranks (gloo) finish the same
+    number of steps."""
+    import socket
+    import torch.multiprocessing as mp
+    cfg = get_preset("qwen3-ksa-tiny").merge({"num_layers": 2, "summary_layer_freq": [1, 0], "embed_dim": 64,
+                                               "intermediate_dim": 128, "vocab_size": 256, "summary_token_begin": 256,
+                                               "head_dim": 16, "summary_chunk_size": 16})
+    mc = tmp_path / "model.json"
+    cfg.save(str(mc))
+    ds_cfg, _ = _corpora(tmp_path, 256)
+    base = ["--model-config", str(mc), "--dataset-config", ds_cfg, "--learning-rate", "3e-3", "--lr-scheduler-type",
+            "constant", "--seed", "1", "--model-dtype", "float32", "--num-training-steps", "3", "--enable-distill",
+            "--weight-decay", "0.5", "--logging-per-step", "1", "--save-checkpoint-per-step", "3"]
+    r = train(get_argument_parser().parse_args(base + ["--output-dir", str(tmp_path / "one")]))
+    assert r["steps"] == 3 and r["loss"] == r["loss"]
+    from ksa_b200.models import get_model_class
+    from ksa_b200.training.checkpoint import dcp_to_state_dict
+    from ksa_b200.tools.convert import flatten_model_state
+    tree = flatten_model_state(dcp_to_state_dict(str(tmp_path / "one" / "global_step3")))
+    init = get_model_class(cfg.model_class)(cfg)
+    init.init_weights(seed=1)
+    muse0 = init.muse_state_dict()
+    assert torch.equal(tree["model.layers.0.attn.q_proj.weight"], muse0["model.layers.0.attn.q_proj.weight"].float())
+    assert not torch.equal(tree["model.layers.0.attn.q_proj_summary.weight"],
+                           muse0["model.layers.0.attn.q_proj_summary.weight"].float())
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    argv = base + ["--output-dir", str(tmp_path / "two")]
+    procs = [ctx.Process(target=_distill_rank, args=(rk, 2, port, argv, q)) for rk in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, status, info in res:
+        assert status == "ok", f"rank {rank}: {info}"
+        assert info["steps"] == 3

@@ -64,6 +64,18 @@ def _noalloc(fn, lib, x, dy, w, dres, rstd, dw_init):
     return dx, dw
 
 
+def _formula(x, dy, w, dres, rstd, dw_init, accumulate):
+    """The backward in plain fp32 PyTorch: dx = rstd (dy w - xhat mean(dy w xhat)) (+ dres), dw (+)= sum dy xhat."""
+    xf, gf, wf = x.float(), dy.float(), w.float()
+    xhat = xf * rstd[:, None]
+    gw = gf * wf
+    dx = rstd[:, None] * (gw - xhat * (gw * xhat).mean(-1, keepdim=True))
+    if dres is not None:
+        dx = dx + dres.float()
+    dw = (gf * xhat).sum(0)
+    return dx, (dw_init + dw if accumulate else dw)
+
+
 def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
     lib, fn = _symbol()
     torch.cuda.synchronize()
@@ -77,6 +89,50 @@ def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
         assert torch.isfinite(dx_new.float()).all() and torch.isfinite(dw_new).all()
         assert _rel(dx_new, dx_ref) < 1.5e-2, (rows, D, _rel(dx_new, dx_ref))
         assert _rel(dw_new, dw_ref) < 2e-2, (rows, D, _rel(dw_new, dw_ref))
+        dx_f, dw_f = _formula(x, dy, w, dres, rstd, dw_init, True)
+        assert _rel(dx_new, dx_f) < 1.5e-2 and _rel(dw_new, dw_f) < 2e-2
+
+
+@pytest.mark.parametrize("rows,D", [(300, 4096), (64, 2560)])
+def test_noalloc_rmsnorm_bwd_at_the_size_limit_and_off_the_2048_grid(rows, D):
+    """D = 4096 is the largest hidden size the built-in scratch covers and uses every thread's second vector;
+    D = 2560 (the 4B model's hidden size) is not a multiple of 2048.  Checked against the fp32 formula, overwriting dw
+    (accumulate_dw = 0) and with no dw at all (null pointer: only dx is produced)."""
+    lib, fn = _symbol()
+    x, dy, w, dres, rstd = _case(rows, D, True, 5)
+    stream = torch.cuda.current_stream().cuda_stream
+    dx = torch.empty_like(x)
+    dw = torch.full((D,), 7.0, device="cuda")            # must be overwritten, not added to
+    rc = fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+            0, rows, D, stream)
+    assert rc == 0, lib.ksa_last_error().decode()
+    dx_f, dw_f = _formula(x, dy, w, dres, rstd, None, False)
+    torch.cuda.synchronize()
+    assert _rel(dx, dx_f) < 1.5e-2 and _rel(dw, dw_f) < 2e-2
+    dx2 = torch.empty_like(x)
+    rc = fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr(), dx2.data_ptr(), None, 0,
+            rows, D, stream)
+    assert rc == 0, lib.ksa_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.equal(dx, dx2)
+
+
+def test_noalloc_rmsnorm_bwd_takes_no_device_memory():
+    """After a first call (which may load the module that holds the scratch array), further calls leave the amount of
+    free device memory unchanged."""
+    lib, fn = _symbol()
+    x, dy, w, dres, rstd = _case(256, 1024, False, 9)
+    dx, dw = torch.empty_like(x), torch.zeros(1024, device="cuda")
+    args = (dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), None, dx.data_ptr(), dw.data_ptr(), 0, 256, 1024,
+            torch.cuda.current_stream().cuda_stream)
+    assert fn(*args) == 0
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert fn(*args) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
 
 
 def test_noalloc_rmsnorm_bwd_rejects_sizes_beyond_its_scratch():
