@@ -11,8 +11,16 @@ set-up, ``:855-1053`` for the step): ``load_config`` -> ``get_model_class`` on t
 Environment shims (no reference source is edited): ``baseline/_ref`` is put on ``sys.path``; the wheel's
 ``flash_attn/cute`` directory is appended to the installed ``flash_attn`` package's ``__path__``; the process
 group is created from torchrun's environment instead of OpenMPI's.  ``summary_attention_mode`` is ``kernel``
-(the reference's CuTe-DSL path) when a small call of ``summary_attn_func`` succeeds on this GPU, otherwise
-``block`` (the reference's own PyTorch mode); the JSON line says which one ran.
+when a small call of ``summary_attn_func`` succeeds on this GPU, otherwise ``block`` (the reference's own PyTorch
+mode); the JSON line names the back end that really served the call (``summary_attention_backend``: the wheel's CuTe
+sm_100 kernel, its FlexAttention fallback, or ``block``), not the requested mode.
+
+``--cp N --seq-len L`` runs the reference's own context parallelism (Ulysses all-to-all,
+``muse/training/parallel.py:211-335``): ``initialize_model_parallel(N)``, the batch broadcast from the first rank
+of each group, the per-rank slices of ids / position ids / labels / ``summary_mask`` with ``full_summary_mask`` kept
+whole (``recipes/pretrain_kai_summary_unified.py:881-926``), and, as the reference's stage scripts do, activation
+checkpointing from 32k tokens and the chunked lm_head + CE (``ChunkedDistillLossComputer``, 1024-token chunks) from
+64k tokens (``examples/pretrain/run_pretrain_{32,64,128}k.sh``).
 """
 from __future__ import annotations
 
@@ -99,15 +107,32 @@ def _run(args) -> dict:
     from muse.layers.summary_utils import maybe_build_summary_batch
     from muse.training.distributed import shard_model, initialize_model_params
     from muse.training.common import clip_grad_by_value, set_default_dtype
-    try:
-        from muse.training.parallel import initialize_model_parallel
-        initialize_model_parallel(1)
-    except Exception:  # noqa: BLE001 - only needed for context parallelism
-        pass
+    cp = max(1, int(getattr(args, "cp", 1)))
+    if world % cp:
+        raise SystemExit(f"--cp {cp} does not divide {world} ranks")
+    cp_group, cp_rank = None, 0
+    if cp > 1:
+        from muse.training.parallel import (broadcast_batch_tensors, get_context_parallel_group,
+                                            get_context_parallel_rank, initialize_model_parallel)
+        initialize_model_parallel(cp)
+        cp_group, cp_rank = get_context_parallel_group(), get_context_parallel_rank()
+    else:
+        try:
+            from muse.training.parallel import initialize_model_parallel
+            initialize_model_parallel(1)
+        except Exception:  # noqa: BLE001 - only needed for context parallelism
+            pass
 
     probe = _probe_kernel_mode(torch)
     mode = "kernel" if probe == "kernel" else "block"
+    backend = "block (the reference's PyTorch mode)"
+    if mode == "kernel":
+        import summary_attn.interface as sa_if
+        backend = ("cute sm100 (flash_attn_cute wheel)" if sa_if._check_cute_available()
+                   else "flex_attention fallback (torch.compile -> Triton)")
     L = args.seq_len
+    grad_ckpt = L >= 32768          # the reference's 32k / 64k / 128k stage scripts pass --enable-gradient-checkpointing
+    chunked_ce = L >= 65536         # ... and its 64k / 128k scripts use the chunked lm_head + CE
     with tempfile.NamedTemporaryFile("w", suffix=".json", delete=False) as f:
         json.dump(_model_json(mode, L), f)
     cfg = load_config(f.name)
@@ -115,6 +140,9 @@ def _run(args) -> dict:
     torch.manual_seed(0)
     with set_default_dtype("bfloat16"), torch.device("meta"):
         model = get_model_class(cfg.model_class)(cfg)
+    if grad_ckpt:
+        from muse.training.activations import set_activation_checkpointing
+        set_activation_checkpointing(model, auto_wrap_policy=model.get_checkpointable_module_classes())
     model = model.float()                                     # --fp32-weight: fp32 master weights
     shard_model(model=model, cpu_offload=False, reshard_after_forward=False, dp_mesh=mesh, fp32_weight=True,
                 prefetch_params_in_forward=False, fp32_reduce=True)
@@ -124,11 +152,17 @@ def _run(args) -> dict:
         for m in model.modules():
             if hasattr(m, "rope_init"):
                 m.rope_init()
+    chunked = None
+    if chunked_ce:
+        from muse.losses.chunked_distill_loss_computer import ChunkedDistillLossComputer
+        model.model.skip_output_layer = True
+        chunked = ChunkedDistillLossComputer(lm_head=model.model.output, minibatch_size=1024, lm_factor=1.0,
+                                             kl_factor=0.0, enable_kl=False)
     loss_fn = torch.nn.CrossEntropyLoss(ignore_index=-100)
     opt = torch.optim.AdamW(model.get_optimizer_grouped_parameters(learning_rate=4e-4, weight_decay=0.1), lr=4e-4,
                             betas=(0.9, 0.95), eps=1e-8)
 
-    g_cpu = torch.Generator().manual_seed(1234 + rank)
+    g_cpu = torch.Generator().manual_seed(1234 + rank // cp)   # one sequence per context-parallel group
     n_batches = max(args.steps, 4)
     host = [torch.randint(0, cfg.vocab_size, (1, L), generator=g_cpu).pin_memory() for _ in range(n_batches)]
     resident = [t.to(dev) for t in host]
@@ -140,17 +174,35 @@ def _run(args) -> dict:
                  "cu_seqlens": torch.tensor([0, L], device=dev, dtype=torch.int32)}
         shifted_ids = F.pad(batch["input_ids"][:, 1:], (0, 1), value=0)
         shifted_mask = F.pad(batch["loss_mask"][:, 1:], (0, 1), value=0)
-        labels = shifted_ids * shifted_mask + (-100) * (1 - shifted_mask)
+        batch["labels"] = shifted_ids * shifted_mask + (-100) * (1 - shifted_mask)
         batch["loss_mask"] = shifted_mask.contiguous()
         batch, ctx = maybe_build_summary_batch(batch, cfg)
         ctx.curr_iteration = 0
-        ctx.full_summary_mask = ctx.summary_mask
-        logits = model(tokens=batch["input_ids"], cu_seqlens=batch.get("cu_seqlens"), input_pos=batch.get("position_ids"),
-                       summary_ctx=ctx)
-        if isinstance(logits, tuple):
-            logits = logits[0]
-        loss = loss_fn(logits.reshape(-1, logits.size(-1)), labels.reshape(-1))
-        loss.backward()
+        if cp > 1:
+            broadcast_batch_tensors(batch, cp_group)
+            n = batch["input_ids"].shape[1] // cp
+            batch["input_ids"] = batch["input_ids"][:, cp_rank * n:(cp_rank + 1) * n].contiguous()
+            if batch.get("position_ids") is not None:
+                batch["position_ids"] = batch["position_ids"][:, cp_rank * n:(cp_rank + 1) * n].contiguous()
+            m = batch["labels"].shape[1] // cp
+            batch["labels"] = batch["labels"][:, cp_rank * m:(cp_rank + 1) * m].contiguous()
+            batch["loss_mask"] = batch["loss_mask"][:, cp_rank * m:(cp_rank + 1) * m].contiguous()
+            ctx.full_summary_mask = ctx.summary_mask
+            k = ctx.summary_mask.shape[1] // cp
+            ctx.summary_mask = ctx.summary_mask[:, cp_rank * k:(cp_rank + 1) * k].contiguous()
+            ctx.position_ids = ctx.position_ids[:, cp_rank * k:(cp_rank + 1) * k].contiguous()
+        else:
+            ctx.full_summary_mask = ctx.summary_mask
+        labels = batch["labels"]
+        out = model(tokens=batch["input_ids"], cu_seqlens=batch.get("cu_seqlens"), input_pos=batch.get("position_ids"),
+                    summary_ctx=ctx)
+        if isinstance(out, tuple):
+            out = out[0]
+        if chunked is not None:
+            loss = chunked.forward_and_backward(out, None, labels, gradient_accumulation_steps=1)["total_loss"]
+        else:
+            loss = loss_fn(out.reshape(-1, out.size(-1)), labels.reshape(-1))
+            loss.backward()
         clip_grad_by_value(model, 1.0)
         opt.step()
         opt.zero_grad()
@@ -188,19 +240,21 @@ def _run(args) -> dict:
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_dev, ms_e2e = t.tolist()
     dist.destroy_process_group()
-    tokens = world * L * args.steps
+    tokens = (world // cp) * L * args.steps
     out = {
         "metric": METRIC, "value": tokens / (ms_dev / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
         "impl": "reference",
-        "config": {"model": MODEL_NAME, "global_batch": world, "seq_len": L,
-                   "parallelism": f"fsdp{world}", "summary_attention_mode": mode,
+        "config": {"model": MODEL_NAME, "global_batch": world // cp, "seq_len": L,
+                   "parallelism": f"fsdp{world}" + (f"+cp{cp} (Ulysses all-to-all)" if cp > 1 else ""),
+                   "summary_attention_mode": mode, "summary_attention_backend": backend,
                    "kernel_mode_probe": probe, "full_attention": "flash_attention_2",
+                   "activation_checkpointing": grad_ckpt, "chunked_ce": chunked_ce,
                    "l2": "working set exceeds L2; no explicit flush"},
         "clocks": clocks,
         "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-                "h2d_bytes_per_step": L * 8, "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": L * 8, "d2h_bytes_per_step": 4},   # every rank of a group copies the whole sequence
         "gpu_launches": 0, "loss_first": loss0, "loss_last": last,
     }
     return out if rank == 0 else None

@@ -43,6 +43,8 @@ def test_hf_roundtrip_logits_and_generation(tmp_path):
         expect = model(tokens)
         got = hf(tokens).logits
         pure = hf.lm_head(hf.model(tokens).last_hidden_state)[..., :cfg.vocab_size]   # dependency-free path
+    assert got.shape[-1] == hf.config.vocab_size and bool(torch.isinf(got[..., cfg.vocab_size:]).all())
+    got = got[..., :cfg.vocab_size]
     assert torch.allclose(got, expect, atol=1e-4), (got - expect).abs().max()
     assert torch.allclose(pure, expect, atol=2e-4), (pure - expect).abs().max()
     gen = hf.generate(tokens, max_new_tokens=12, eos_token_id=-1)
@@ -74,7 +76,7 @@ def test_truncate_predict_nums_limits_logits_and_generated_tokens(tmp_path):
     hf = AutoModelForCausalLM.from_pretrained(out, trust_remote_code=True, torch_dtype=torch.float32).eval()
     tokens = torch.randint(0, cfg.vocab_size, (2, 21))
     full = hf(tokens).logits
-    assert full.shape[-1] == cfg.vocab_size
+    assert full.shape[-1] == hf.config.vocab_size == cfg.vocab_size + cfg.summary_token_num
     hf.config.truncate_predict_nums = 100
     cut = hf(tokens).logits
     assert cut.shape[-1] == 100 and torch.equal(cut, full[..., :100])

@@ -70,3 +70,30 @@ def test_engine_matches_cpu_engine():
         nxt = lc.argmax(-1)
         lc, lg = e_cpu.decode_step(nxt), e_gpu.decode_step(nxt.cuda())
     _lib.check_status()
+
+
+def test_hf_generate_on_gpu_runs_on_the_engine_behind_past_key_values():
+    """The HF model on a GPU with this package importable: stock ``generate`` prefills and decodes through
+    ``KsaInferenceEngine`` (the cache object carries it) and returns the engine's own greedy tokens."""
+    from ksa_b200.hf.modeling_qwen3sa import KsaRingBufferCache, Qwen3ForCausalLM, Qwen3SAConfig
+    cfg = Qwen3SAConfig(vocab_size=513, hidden_size=256, intermediate_size=512, num_hidden_layers=4,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=128, summary_token_begin=512,
+                        summary_chunk_size=128, summary_token_num=1, summary_sliding_chunk_num=2,
+                        summary_layer_freq="([1]*3+[0]*1)*1", max_position_embeddings=4096)
+    torch.manual_seed(0)
+    hf = Qwen3ForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() >= 2:
+                p.mul_(3.0)
+    hf = hf.cuda().to(torch.bfloat16)
+    prompt = torch.randint(0, 512, (2, 200), device="cuda")
+    before = _lib.launch_count()
+    out = hf.generate(prompt, max_new_tokens=80, do_sample=False, eos_token_id=-1)      # crosses the boundary at 256
+    assert _lib.launch_count() > before, "the sm_100a kernels did not run"
+    want = KsaInferenceEngine(hf.framework_model(), max_len=512, batch=2).generate(prompt, 80)
+    assert torch.equal(out, want)
+    step = hf(prompt, use_cache=True)
+    assert isinstance(step.past_key_values, KsaRingBufferCache) and step.past_key_values.engine is not None
+    assert step.logits.shape == (2, 1, 513)
+    _lib.check_status()
