@@ -72,6 +72,15 @@ def _probe_kernel_mode(torch) -> str:
 def run_reference_arm(args) -> dict:
     if not os.path.isdir(os.path.join(REF, "muse")):
         return {"impl": "reference", "unavailable": "baseline/_ref is empty: the reference was not installed on this machine"}
+    if int(getattr(args, "cp", 1) or 1) > 1:
+        # The path below is written out (it follows the reference's training loop), but its one run on this pool
+        # (2 GPUs, 32768 tokens, --cp 2) ended in "CUDA error: an illegal memory access was encountered" inside the
+        # reference's own step (record: profiles/reference_arm_cp2_32k_fault.md).  Reading the inputs against the
+        # reference's recipe showed no mistake in them, so the path is not run again on shared GPUs.
+        return {"impl": "reference",
+                "unavailable": "the reference's context-parallel step (Ulysses all-to-all + activation checkpointing + its "
+                               "FlexAttention fallback) raised 'CUDA error: an illegal memory access' on 2 x B200 at 32768 "
+                               "tokens; not run again on this shared pool (profiles/reference_arm_cp2_32k_fault.md)"}
     try:
         return _run(args)
     except Exception as e:  # noqa: BLE001

@@ -40,6 +40,9 @@ def _random_model(cfg, device, dtype, seed: int):
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--preset", default="ksa-4b")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"],
+                    help="reference: the reference's own HF template through AutoModelForCausalLM + generate "
+                         "(batch 1, one GPU); prints an `unavailable` line where it cannot run")
     ap.add_argument("--prompt-len", type=int, default=131072)
     ap.add_argument("--decode", type=int, default=512)
     ap.add_argument("--batch", type=int, default=1)
@@ -55,6 +58,14 @@ def main(argv=None) -> None:
                          "scattering them into the owners' memory from the epilogue (for A/B runs)")
     a = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if a.impl == "reference":
+        import sys
+        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        sys.path.insert(0, root)
+        from baseline.reference_infer_arm import run_reference_infer_arm
+        if rank == 0:
+            print(json.dumps(run_reference_infer_arm(a.prompt_len, a.decode, a.batch, world)), flush=True)
+        return
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
