@@ -52,7 +52,7 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--comm", default=None, choices=["fused", "collective"],
                     help="multi-GPU back end: fused P2P kernels (default) or NCCL collectives (A/B baseline)")
-    ap.add_argument("--overlap", default="stream", choices=["stream", "gemm", "gemm2"],
+    ap.add_argument("--overlap", default="stream", choices=["stream", "gemm2"],
                     help="fused back end: communication kernels on a side stream, or as CTAs inside GEMM launches")
     return ap.parse_args()
 

@@ -13,7 +13,7 @@
 //
 // Replaces the cuBLAS calls behind nn.Linear in the reference
 // (muse/models/qwen3_sa/modeling.py:299-314, muse/layers/feed_forward.py:70-83).
-#include "comm.cuh"
+#include "common.cuh"
 #include "host.h"
 
 namespace ksa {
@@ -33,18 +33,6 @@ struct GemmSmem {
   static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
-// Work for the communication CTAs that can ride along with a GEMM launch (the first n_ctas CTAs of the grid).
-// They pull the next FSDP unit's parameter shards from the peers (all-gather) or reduce the previous unit's
-// gradients from the peers and apply AdamW (reduce-scatter + optimizer), over NVLink, while the remaining CTAs
-// run the tensor-core tiles of this GEMM.
-enum CommKind : int { kCommNone = 0, kCommGather = 1, kCommReduceAdamw = 2 };
-struct CommWork {
-  int kind;
-  int n_ctas;
-  GatherJob gather;
-  ReduceAdamwJob reduce;
-};
-
 struct GemmEpilogue {
   void* c;            // output (bf16 or fp32), row-major [M, N]
   long long ldc;      // leading dimension in elements
@@ -56,17 +44,10 @@ struct GemmEpilogue {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmEpilogue ep,
-                 int M, int N, int K, int* status, const __grid_constant__ CommWork comm) {
+                 int M, int N, int K, int* status) {
   using S = GemmSmem<BN>;
-  if (comm.kind != kCommNone && (int)blockIdx.x < comm.n_ctas) {
-    // communication CTA: no shared-memory pipeline, no TMEM; returns before any CTA-wide barrier of the math path
-    if (comm.kind == kCommGather) run_gather_job(comm.gather, blockIdx.x, comm.n_ctas, status);
-    else run_reduce_adamw_job(comm.reduce, blockIdx.x, comm.n_ctas, status);
-    return;
-  }
-  const int n_comm = comm.kind != kCommNone ? comm.n_ctas : 0;
-  const int cta_first = (int)blockIdx.x - n_comm;     // index among the math CTAs
-  const int cta_stride = (int)gridDim.x - n_comm;
+  const int cta_first = (int)blockIdx.x;
+  const int cta_stride = (int)gridDim.x;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* bar_base = smem + S::kStages * S::kStageBytes;
@@ -252,7 +233,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ----------------------------------------------------------------------------------------------
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const void* a, const void* b, const GemmEpilogue& ep, int M, int N, int K, long long lda,
-                       long long ldb, int sm_limit, cudaStream_t stream, const CommWork& comm) {
+                       long long ldb, int sm_limit, cudaStream_t stream) {
   using S = GemmSmem<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -296,63 +277,15 @@ static int launch_gemm(const void* a, const void* b, const GemmEpilogue& ep, int
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   int ctas = num_sms;
   if (sm_limit > 0 && sm_limit < ctas) ctas = sm_limit;
-  const int n_comm = comm.kind != kCommNone ? comm.n_ctas : 0;
-  ctas -= n_comm;                       // communication CTAs take their SMs out of the same single wave
-  if (ctas < 1) ctas = 1;
   if (tiles < ctas) ctas = tiles;
   int* status = status_word();
   KSA_REQUIRE(status != nullptr, "could not allocate the status word");
-  kern<<<ctas + n_comm, kGemmThreads, S::kTotal, stream>>>(tmA, tmB, ep, M, N, K, status, comm);
+  kern<<<ctas, kGemmThreads, S::kTotal, stream>>>(tmA, tmB, ep, M, N, K, status);
   KSA_CHECK_CUDA(cudaGetLastError());
   return kErrNone;
 }
 
-static thread_local CommWork g_pending_comm = {kCommNone, 0, {}, {}};
-
 }  // namespace ksa
-
-// Attach a parameter all-gather (see ksa_peer_gather for the arguments) to the NEXT ksa_gemm_bf16 call made on this
-// host thread: `ctas` CTAs of that launch pull the peers' shards over NVLink while the others compute.
-KSA_API int ksa_gemm_attach_gather(const void* const* peers, int world, int rank, long long shard_elems, int elem_bytes,
-                                   const void* ready_flags, const void* epoch_ptr, unsigned epoch_add, int ctas) {
-  using namespace ksa;
-  KSA_REQUIRE(world >= 1 && world <= kMaxPeers, "attach_gather: world %d out of range", world);
-  KSA_REQUIRE((shard_elems * elem_bytes) % 16 == 0, "attach_gather: shard bytes must be a multiple of 16");
-  KSA_REQUIRE(ctas >= 1 && ctas <= 64, "attach_gather: ctas %d out of range", ctas);
-  CommWork& w = g_pending_comm;
-  w = CommWork{};
-  if (world == 1) return 0;
-  w.kind = kCommGather; w.n_ctas = ctas;
-  for (int r = 0; r < world; ++r) w.gather.peers[r] = static_cast<const uint8_t*>(peers[r]);
-  w.gather.world = world; w.gather.rank = rank; w.gather.shard_bytes = shard_elems * elem_bytes;
-  w.gather.ready_flags = static_cast<const uint32_t*>(ready_flags);
-  w.gather.epoch_ptr = static_cast<const uint32_t*>(epoch_ptr); w.gather.epoch_add = epoch_add;
-  return 0;
-}
-
-// Attach a fused reduce-scatter + AdamW (see ksa_peer_reduce_adamw) to the NEXT ksa_gemm_bf16 call on this thread.
-KSA_API int ksa_gemm_attach_reduce_adamw(const void* const* grads, int world, int rank, long long shard_lo, long long n,
-                                         void* master, void* m, void* v, void* out_bf16, const void* hyper,
-                                         float beta1, float beta2, float eps, float weight_decay, float clip_value,
-                                         void* sumsq, const void* ready_flags, const void* epoch_ptr,
-                                         unsigned epoch_add, int ctas) {
-  using namespace ksa;
-  KSA_REQUIRE(world >= 1 && world <= kMaxPeers, "attach_reduce_adamw: world %d out of range", world);
-  KSA_REQUIRE(n % 4 == 0 && shard_lo % 4 == 0, "attach_reduce_adamw: shard offset/size must be multiples of 4");
-  KSA_REQUIRE(ctas >= 1 && ctas <= 64, "attach_reduce_adamw: ctas %d out of range", ctas);
-  CommWork& w = g_pending_comm;
-  w = CommWork{};
-  w.kind = kCommReduceAdamw; w.n_ctas = ctas;
-  ReduceAdamwJob& j = w.reduce;
-  for (int r = 0; r < world; ++r) j.grads[r] = static_cast<const float*>(grads[r]);
-  j.world = world; j.rank = rank; j.shard_lo = shard_lo; j.n = n;
-  j.master = (float*)master; j.m = (float*)m; j.v = (float*)v; j.out_bf16 = (bf16*)out_bf16;
-  j.hyper = (const float*)hyper; j.beta1 = beta1; j.beta2 = beta2; j.eps = eps;
-  j.weight_decay = weight_decay; j.clip_value = clip_value; j.sumsq = (float*)sumsq;
-  j.ready_flags = static_cast<const uint32_t*>(ready_flags);
-  j.epoch_ptr = static_cast<const uint32_t*>(epoch_ptr); j.epoch_add = epoch_add;
-  return 0;
-}
 
 // C[M,N] = alpha * op(A) * op(B) (+ C).  Layouts:
 //   a_mn_major = 0: A is [M, K] row-major (lda >= K);  1: A is stored as [K, M] row-major (lda >= M)
@@ -371,14 +304,12 @@ KSA_API int ksa_gemm_bf16(const void* a, const void* b, void* c, int M, int N, i
   KSA_REQUIRE(!(accumulate && !out_fp32), "gemm: accumulate needs an fp32 output");
   GemmEpilogue ep{c, ldc, out_fp32, accumulate, alpha};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  CommWork comm = g_pending_comm;       // consumed by this launch
-  g_pending_comm.kind = kCommNone;
   const bool wide = (N >= 256) && (((long long)((M + 127) / 128) * ((N + 255) / 256)) >= 96 || N % 256 == 0);
 #define KSA_GEMM_DISPATCH(BN)                                                                        \
-  if (!a_mn_major && !b_mn_major) return launch_gemm<BN, false, false>(a, b, ep, M, N, K, lda, ldb, sm_limit, st, comm); \
-  if (!a_mn_major && b_mn_major) return launch_gemm<BN, false, true>(a, b, ep, M, N, K, lda, ldb, sm_limit, st, comm);   \
-  if (a_mn_major && !b_mn_major) return launch_gemm<BN, true, false>(a, b, ep, M, N, K, lda, ldb, sm_limit, st, comm);   \
-  return launch_gemm<BN, true, true>(a, b, ep, M, N, K, lda, ldb, sm_limit, st, comm);
+  if (!a_mn_major && !b_mn_major) return launch_gemm<BN, false, false>(a, b, ep, M, N, K, lda, ldb, sm_limit, st); \
+  if (!a_mn_major && b_mn_major) return launch_gemm<BN, false, true>(a, b, ep, M, N, K, lda, ldb, sm_limit, st);   \
+  if (a_mn_major && !b_mn_major) return launch_gemm<BN, true, false>(a, b, ep, M, N, K, lda, ldb, sm_limit, st);   \
+  return launch_gemm<BN, true, true>(a, b, ep, M, N, K, lda, ldb, sm_limit, st);
   if (wide) {
     KSA_GEMM_DISPATCH(256)
   } else {

@@ -68,7 +68,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
         # a parameter all-gather waits for a GEMM that can carry it: CTA pairs, both operands K-major, bf16 output,
         # long enough to hide the transfer.  Whoever attached it flushes it if no such GEMM comes by.
         if (not a_mn_major and not b_mn_major and out.dtype == torch.bfloat16 and not accumulate and alpha == 1.0
-                and sm_limit == 0 and M > 16 and not _lib.comm_pending()
+                and sm_limit == 0 and M > 16
                 and 2.0 * M * N * K >= _lib.peek_pair_gather().get("min_flops", 0.0)):
             job = _lib.take_pair_gather()
             # does the weight operand live in the buffer that is being gathered?  Then its tiles wait for their shards.
@@ -78,13 +78,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
                       job["epoch_add"], job["done"], 2 if inside else 0, b.data_ptr() - job["base"] if inside else 0)
             return out
     if (M <= 16 and not a_mn_major and not b_mn_major and out.dtype == torch.bfloat16 and not accumulate
-            and alpha == 1.0 and K % 8 == 0 and not _lib.comm_pending()):
+            and alpha == 1.0 and K % 8 == 0):
         # decoding: a few activation rows against a whole weight matrix is a stream of the weights, served by the
         # bandwidth-shaped kernel instead of 128-row tensor-core tiles
         _lib.call("ksa_gemv_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0))
         return out
     if pair is None:
-        pair = (GEMM_PAIR_MIN_TILES > 0 and sm_limit == 0 and not _lib.comm_pending()
+        pair = (GEMM_PAIR_MIN_TILES > 0 and sm_limit == 0
                 and ((M + 255) // 256) * ((N + 255) // 256) >= GEMM_PAIR_MIN_TILES)
     if pair:
         _lib.call("ksa_gemm2_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
@@ -93,7 +93,6 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     _lib.call("ksa_gemm_bf16", a, b, out, M, N, K, a.stride(0), b.stride(0), out.stride(0),
               int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate),
               float(alpha), int(sm_limit))
-    _lib.gemm_launched()
     return out
 
 

@@ -49,8 +49,6 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_kv_cache_move": [P] * 5 + [I] * 5 + [P],
     "ksa_peer_gather": [P, I, I, L, I, P, P, ctypes.c_uint, I, P],
     "ksa_peer_reduce_adamw": [P, I, I, L, L, P, P, P, P, P, F, F, F, F, F, P, P, P, ctypes.c_uint, I, P],
-    "ksa_gemm_attach_gather": [P, I, I, L, I, P, P, ctypes.c_uint, I],
-    "ksa_gemm_attach_reduce_adamw": [P, I, I, L, L, P, P, P, P, P, F, F, F, F, F, P, P, P, ctypes.c_uint, I],
     "ksa_signal_set": [P, I, P, ctypes.c_uint, P],
     "ksa_signal_wait": [P, I, P, ctypes.c_uint, P],
     "ksa_peer_copy": [P, P, L, P, P, ctypes.c_uint, I, P],
@@ -138,7 +136,7 @@ def call(name: str, *args) -> None:
 
 
 def call_nostream(name: str, *args) -> None:
-    """Call an entry point that takes no stream argument (set-up routines, attach_* calls)."""
+    """Call an entry point that takes no stream argument (set-up routines)."""
     lib = load()
     rc = getattr(lib, name)(*[_ptr(a) for a in args])
     if rc != 0:
@@ -146,28 +144,6 @@ def call_nostream(name: str, *args) -> None:
 
 
 _tls = threading.local()
-
-
-def attach_to_next_gemm(name: str, args: tuple, after=None) -> None:
-    """Attach a communication job (``ksa_gemm_attach_gather`` / ``ksa_gemm_attach_reduce_adamw``) to the next GEMM
-    launched from this thread; ``after()`` runs right after that launch (e.g. to signal the peers)."""
-    call_nostream(name, *args)
-    _tls.after_gemm = after
-    _tls.attached = True
-
-
-def comm_pending() -> bool:
-    """True while a communication job is attached and waiting for the next tensor-core GEMM launch."""
-    return bool(getattr(_tls, "attached", False))
-
-
-def gemm_launched() -> None:
-    """Called by ``ops.gemm`` after each launch: runs the callback of an attached communication job."""
-    if getattr(_tls, "attached", False):
-        _tls.attached = False
-        cb, _tls.after_gemm = getattr(_tls, "after_gemm", None), None
-        if cb is not None:
-            cb()
 
 
 def attach_pair_gather(job: dict) -> None:

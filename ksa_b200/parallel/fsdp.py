@@ -15,9 +15,6 @@ Two communication back ends behind one engine:
     * ``overlap="stream"`` (default): both run on a side stream as soon as a unit's backward has been launched
       (reduce + AdamW) or one unit ahead of the forward pass (gather).  Their CTAs need almost no shared memory, so
       they are co-resident with the GEMM CTAs on the same SMs and the NVLink / HBM traffic hides under tensor work.
-    * ``overlap="gemm"``: the same device routines run as communication CTAs inside the next GEMM launch (first
-      backward GEMM of the next unit for reduce + AdamW, QKV projection of the previous unit for the gather), one
-      kernel doing both.  Each communication CTA then takes a whole SM away from the GEMM.
     * ``overlap="gemm2"``: the gather of the next unit rides inside the gate/up projection of the current layer (the
       longest forward GEMM): a communication warp in every CTA of that CTA-pair GEMM moves the peers' shards with
       bulk copies through a small shared-memory ring while the other warps compute (``ksa_gemm2_gather_bf16``).  A unit cannot be pulled inside
@@ -60,13 +57,14 @@ class _Boundary(torch.autograd.Function):
 
 class FsdpEngine(TrainEngine):
     def __init__(self, model: nn.Module, *args, world_size: int = 1, rank: int = 0, group=None, comm: Optional[str] = None,
-                 comm_ctas: int = 8, overlap: str = "stream", pair_gather_min_flops: float = 3e11, **kw):
+                 overlap: str = "stream", pair_gather_min_flops: float = 3e11, **kw):
         self.group = group
+        if overlap not in ("stream", "gemm2"):
+            raise ValueError(f"overlap must be 'stream' or 'gemm2', not {overlap!r}")
         self.overlap = overlap
         self.pair_gather_min_flops = pair_gather_min_flops    # only a GEMM at least this long carries a gather
         dev = kw.get("device") or next(model.parameters()).device
         self.comm = comm or ("fused" if torch.device(dev).type == "cuda" and world_size > 1 else "collective")
-        self.comm_ctas = comm_ctas
         self._symm = []
         super().__init__(model, *args, world_size=world_size, rank=rank, **kw)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -122,10 +120,7 @@ class FsdpEngine(TrainEngine):
             x, delta = args[0], args[1]
             if self._overlap_active:
                 nxt = ui + 1
-                if self.overlap == "gemm":
-                    if nxt < len(self.units) and nxt >= 2:
-                        self._attach_gather(nxt)
-                elif self.overlap == "gemm2":
+                if self.overlap == "gemm2":
                     _lib.flush_pair_gather()              # this unit's weights, if no GEMM of the last layer took them
                     if nxt < len(self.units) and nxt >= 2:
                         self._attach_pair_gather(nxt)
@@ -144,7 +139,7 @@ class FsdpEngine(TrainEngine):
         def hook(module, args, output):
             if self._overlap_active and self.overlap == "gemm2":
                 _lib.flush_pair_gather()
-            elif self._overlap_active and self.overlap != "gemm":
+            elif self._overlap_active:
                 ev = self._gather_done.pop(head_ui, None)
                 if ev is not None:
                     torch.cuda.current_stream(self.device).wait_event(ev)
@@ -158,14 +153,6 @@ class FsdpEngine(TrainEngine):
     # ------------------------------------------------------------------ fused communication
     def _unit_flag_index(self, ui: int) -> int:
         return ui * self.world_size
-
-    def _attach_gather(self, ui: int) -> None:
-        u = self.units[ui]
-        shard = u.size // self.world_size
-        item = u.compute.element_size()
-        _lib.attach_to_next_gemm("ksa_gemm_attach_gather", (
-            u.compute_ptrs, self.world_size, self.rank, shard, item,
-            self.pad_weights.local_ptr(self._unit_flag_index(ui)), self.epoch, 0, self.comm_ctas))
 
     def _attach_pair_gather(self, ui: int) -> None:
         u = self.units[ui]
@@ -200,41 +187,30 @@ class FsdpEngine(TrainEngine):
     def _signal(self, pad, ui: int) -> None:
         pad.set_on_all(self._unit_flag_index(ui) + self.rank, self.epoch, 1)
 
-    def _unit_grads_ready(self, ui: int, can_attach: bool) -> None:
+    def _unit_grads_ready(self, ui: int) -> None:
         """All of this rank's gradients of unit ``ui`` have been launched: tell the peers, then reduce + update."""
         u = self.units[ui]
         for s in u.slots:  # parameters that received no gradient this window contribute zeros
             if not getattr(s.param, "_grad_written", False):
                 s.param.main_grad.zero_()
                 s.param._grad_written = True
-        if self.overlap == "gemm":
+        main = torch.cuda.current_stream(self.device)
+        ev = torch.cuda.Event()
+        ev.record(main)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ev)
             self._signal(self.pad_grads, ui)
-            if can_attach:
-                _lib.attach_to_next_gemm("ksa_gemm_attach_reduce_adamw", self._reduce_args(u, ui) + (self.comm_ctas,),
-                                         after=lambda: self._signal(self.pad_weights, ui))
-            else:
-                _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 64)
-                self._signal(self.pad_weights, ui)
-        else:
-            main = torch.cuda.current_stream(self.device)
-            ev = torch.cuda.Event()
-            ev.record(main)
-            with torch.cuda.stream(self.comm_stream):
-                self.comm_stream.wait_event(ev)
-                self._signal(self.pad_grads, ui)
-                _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 64)
-                self._signal(self.pad_weights, ui)
+            _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 64)
+            self._signal(self.pad_weights, ui)
         self._done_units.add(ui)
 
     def _backward_reached(self, tag) -> None:
         if not self._is_boundary_step:
             return
         if isinstance(tag, tuple):          # ("before", head): the head's gradients are complete
-            self._unit_grads_ready(tag[1], can_attach=True)
+            self._unit_grads_ready(tag[1])
             return
-        ui = tag                            # backward of layer unit `ui` has been launched
-        first_layer_unit = min(self._layer_unit.values())
-        self._unit_grads_ready(ui, can_attach=ui != first_layer_unit)
+        self._unit_grads_ready(tag)         # backward of layer unit `tag` has been launched
 
     # ------------------------------------------------------------------ step
     def _write_hyper(self) -> None:
@@ -293,7 +269,7 @@ class FsdpEngine(TrainEngine):
             self._collect_autograd_grads()
             for ui in range(len(self.units) - 1, -1, -1):   # whatever backward did not reach (embed; all, if hooks are off)
                 if ui not in self._done_units:
-                    self._unit_grads_ready(ui, can_attach=False)
+                    self._unit_grads_ready(ui)
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
             self._flag_epoch += 1
             return

@@ -57,7 +57,7 @@ def get_argument_parser() -> argparse.ArgumentParser:
     a("--reshard-after-forward", action="store_true")
     a("--prefetch-params-in-forward", action="store_true")
     a("--comm", default=None, choices=["fused", "collective"], help="FSDP back end (default: fused on GPUs)")
-    a("--overlap", default="stream", choices=["stream", "gemm", "gemm2"],
+    a("--overlap", default="stream", choices=["stream", "gemm2"],
       help="fused back end: communication kernels on a side stream, or inside GEMM launches")
     a("--no-cuda-graph", action="store_true")
     # optimisation

@@ -50,7 +50,7 @@ def _worker(rank, world, port, out_q):
         results = {}
         g = torch.Generator().manual_seed(11)
         data = torch.randint(0, cfg.vocab_size, (3, world, 2, 513), generator=g)
-        for comm, overlap in (("collective", "stream"), ("fused", "stream"), ("fused", "gemm"), ("fused", "gemm2")):
+        for comm, overlap in (("collective", "stream"), ("fused", "stream"), ("fused", "gemm2")):
             torch.manual_seed(0)
             model = get_model_class(cfg.model_class)(cfg)
             model.init_weights(seed=0)
@@ -72,7 +72,7 @@ def _worker(rank, world, port, out_q):
             if comm == "fused":
                 eng.close()
         lc, wc, gc = results[("collective", "stream")]
-        for key in (("fused", "stream"), ("fused", "gemm"), ("fused", "gemm2")):
+        for key in (("fused", "stream"), ("fused", "gemm2")):
             lf, wf, gf = results[key]
             assert all(abs(a - b) < 3e-2 for a, b in zip(lc, lf)), (key, lc, lf)
             assert abs(gc - gf) < 0.05 * gc, (key, gc, gf)
