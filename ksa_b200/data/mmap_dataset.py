@@ -261,6 +261,7 @@ class KaiMMapDataset(torch.utils.data.IterableDataset):
             raise FileNotFoundError(f"corpus files missing (.bin / .bin.meta): {missing}")
         corpora = [MMapDataset(p, seq_length) for p in paths]
         self.seq_length = int(seq_length)
+        self.loader_workers = max(0, int(num_workers))     # worker processes a trainer puts in front of this dataset
         if len(corpora) == 1 and len(flat) == 1:
             self.dataset = corpora[0]
             self._rank, self._world = rank, world_size

@@ -280,6 +280,73 @@ def initialize_metrics(seq_length: int, world_size: int = 1, log_every: int = 1,
     return m
 
 
+class SourceLossMonitor:
+    """Loss per data domain and per data source between two log steps
+    (``recipes/pretrain_kai_summary_unified.py:308-324,1029-1040,1091-1120``): every micro-batch adds
+    ``loss * valid_tokens`` and ``valid_tokens`` under its domain and its source; at log time the window is summed
+    over ranks and reported as ``domain_loss/<d>``, ``domain_tokens/<d>``, ``datasource_loss/<s>``,
+    ``datasource_tokens/<s>``.  Losses may be device tensors: they are read back once per window, not per step."""
+
+    def __init__(self):
+        self._pending: List[tuple] = []
+
+    @staticmethod
+    def _name(value) -> str:
+        if isinstance(value, str):
+            return value
+        if isinstance(value, (list, tuple)) and value:
+            uniq = list(dict.fromkeys(value))
+            return uniq[0] if len(uniq) == 1 else "mixed"
+        return "unknown"
+
+    @staticmethod
+    def source_alias(name: str) -> str:
+        parts = str(name).rstrip("/").rsplit("/", 2)
+        return "/".join(parts[-2:]) if len(parts) >= 2 else (parts[-1] or "unknown")
+
+    def add(self, batch: dict, loss, valid_tokens: int) -> None:
+        source = self._name(batch.get("data_source"))
+        domain = self._name(batch.get("data_domain")) if batch.get("data_domain") is not None else source
+        if valid_tokens > 0:
+            self._pending.append((domain, source, loss, int(valid_tokens)))
+
+    def window(self, group=None) -> Dict[str, float]:
+        """Scalars of the window since the last call, summed over the ranks of ``group``; clears the window."""
+        losses = [p[2] for p in self._pending]
+        if losses and any(torch.is_tensor(x) for x in losses):
+            vals = torch.stack([x.detach().float().reshape(()) if torch.is_tensor(x) else torch.tensor(float(x))
+                                for x in losses]).tolist()
+        else:
+            vals = [float(x) for x in losses]
+        local: Dict[str, List[float]] = {}
+        for (domain, source, _, n), v in zip(self._pending, vals):
+            for key in (f"domain/{domain}", f"source/{self.source_alias(source)}"):
+                acc = local.setdefault(key, [0.0, 0.0])
+                acc[0] += v * n
+                acc[1] += n
+        self._pending = []
+        merged = local
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            parts: List[Optional[dict]] = [None] * dist.get_world_size(group)
+            dist.all_gather_object(parts, local, group=group)      # keys differ between ranks; once per log step
+            merged = {}
+            for part in parts:
+                for k, (a, b) in (part or {}).items():
+                    acc = merged.setdefault(k, [0.0, 0.0])
+                    acc[0] += a
+                    acc[1] += b
+        out: Dict[str, float] = {}
+        for k in sorted(merged):
+            loss_sum, tokens = merged[k]
+            if tokens <= 0:
+                continue
+            kind, name = k.split("/", 1)
+            prefix = "domain" if kind == "domain" else "datasource"
+            out[f"{prefix}_loss/{name}"] = loss_sum / tokens
+            out[f"{prefix}_tokens/{name}"] = tokens
+        return out
+
+
 class SimpleMetrics:
     """Running means between logs, no series history (``muse/training/simple_metrics.py:14-158``)."""
 

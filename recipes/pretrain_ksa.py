@@ -84,6 +84,9 @@ def get_argument_parser() -> argparse.ArgumentParser:
     # logging
     a("--logging-per-step", type=int, default=10)
     a("--monitor-datasource-loss", action="store_true")
+    a("--no-tensorboard", action="store_true", help="do not write TensorBoard event files under <output-dir>/log")
+    a("--num-workers", type=int, default=None,
+      help="data-loading worker processes (default: the dataset JSON's num_workers for corpus data, 0 for synthetic)")
     a("--log-attn-stats", action="store_true")
     a("--comment", default="")
     a("--commit-id", default="")
@@ -167,7 +170,9 @@ def train(args) -> dict:
     os.makedirs(args.output_dir, exist_ok=True)
     if rank == 0:
         json.dump(vars(args), open(os.path.join(args.output_dir, f"args-{int(time.time())}.json"), "w"), indent=2)
-    for flag in ("cpu_offload", "reshard_after_forward", "prefetch_params_in_forward", "use_flash_attention_2", "packing"):
+    # flags of the reference's CLI that mean nothing here: the attention kernels are this package's own, and the
+    # next unit's parameters are always gathered one unit ahead
+    for flag in ("prefetch_params_in_forward", "use_flash_attention_2"):
         if getattr(args, flag):
             print_rank_0(f"[recipe] --{flag.replace('_', '-')} has no effect in this framework (accepted for compatibility)")
 
@@ -236,8 +241,18 @@ def train(args) -> dict:
             if args.resume_dataloader:
                 ok = ckpt.load_dataloader_state(dataset, os.path.join(args.checkpoint_dir, ckpt.step_dir_name(loaded)))
                 print_rank_0(f"[recipe] dataloader state {'restored' if ok else 'not found: starting the stream over'}")
-    metrics = initialize_metrics(seq_len, world, args.logging_per_step,
-                                 [StdoutBackend(), CSVBackend(os.path.join(args.output_dir, "metrics.csv"))])
+    backends = [StdoutBackend(), CSVBackend(os.path.join(args.output_dir, "metrics.csv"))]
+    if rank == 0 and not args.no_tensorboard:
+        try:   # event files under <output-dir>/log, as the reference writes them (recipes/...:454-458)
+            from ksa_b200.utils.metrics import TensorBoardBackend
+            backends.append(TensorBoardBackend(os.path.join(args.output_dir, "log")))
+        except Exception as e:  # noqa: BLE001 - tensorboard is optional
+            print_rank_0(f"[recipe] TensorBoard logging is off: {type(e).__name__}: {e}")
+    metrics = initialize_metrics(seq_len, world, args.logging_per_step, backends)
+    source_monitor = None
+    if args.monitor_datasource_loss:
+        from ksa_b200.utils.metrics import SourceLossMonitor
+        source_monitor = SourceLossMonitor()
     profiler = None
     if args.enable_profile:
         from torch.profiler import ProfilerActivity, profile, schedule
@@ -261,10 +276,15 @@ def train(args) -> dict:
     # one CUDA graph per step on a single GPU; multi-GPU steps stay eager (see FsdpEngine.graphed_step)
     use_graph = use_cuda and world == 1 and not args.no_cuda_graph and not args.enable_distill \
         and not args.enable_gradient_checkpointing
-    data_iter = iter(dataset)
+    n_workers = args.num_workers if args.num_workers is not None else getattr(dataset, "loader_workers", 0)
+    loader = dataset
+    if n_workers > 0:
+        from ksa_b200.data import ResumableLoader
+        loader = ResumableLoader(dataset, num_workers=n_workers)
+    data_iter = iter(loader)
     cached = []
     last_loss = None
-    t_prev = time.perf_counter()
+    t_prev = t_log = time.perf_counter()
     while sched.global_step + step_offset < args.num_training_steps:
         # between steps, nothing in flight: stop here if a peer died rather than wait for it inside a collective
         try:
@@ -310,6 +330,8 @@ def train(args) -> dict:
         if use_cuda and sched.should_logging():
             check_device()          # a bounded device-side wait that gave up shows here, as an exception
         metrics.loss.append(loss)
+        if source_monitor is not None:
+            source_monitor.add(batch, loss, int((labels != -100).sum()))
         metrics.tokens.append(ids.numel())
         metrics.samples.append(ids.shape[0])
         if sched.is_gradient_accumulation_boundary():
@@ -324,6 +346,15 @@ def train(args) -> dict:
         if sched.should_logging():
             scalars = metrics.write(sched.global_step + step_offset)
             last_loss = scalars.get("loss", last_loss)
+            extra = {"perf/step_elapsed": time.perf_counter() - t_log}
+            t_log = time.perf_counter()
+            if getattr(cfg, "summary_mix_qkv", False) and hasattr(model, "layers"):
+                extra["summary/mix_coeff"] = float(model.layers[0].attn.mix_coeff)
+            if source_monitor is not None:
+                extra.update(source_monitor.window())
+            if rank == 0:
+                for b in backends:
+                    b.write(sched.global_step + step_offset, extra)
             if rank == 0 and "tokens_per_sec_per_gpu" in scalars:
                 rep = mfu_report(scalars["tokens_per_sec_per_gpu"], cfg, seq_len,
                                  grad_checkpointing=args.enable_gradient_checkpointing, distill=args.enable_distill)
@@ -334,7 +365,7 @@ def train(args) -> dict:
             step = sched.global_step + step_offset
             ckpt.save_checkpoint(ckpt.AppState(engine, sched), checkpointer, args.output_dir, step)
             if args.enable_dataset_checkpointing:
-                ckpt.save_dataloader_state(dataset, args.output_dir, step)
+                ckpt.save_dataloader_state(loader, args.output_dir, step)
         if profiler is not None:
             profiler.step()
     checkpointer.wait()

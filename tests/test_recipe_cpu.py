@@ -191,3 +191,44 @@ def test_recipe_distillation_on_one_and_on_two_ranks(tmp_path):
     for rank, status, info in res:
         assert status == "ok", f"rank {rank}: {info}"
         assert info["steps"] == 3
+
+
+def test_worker_loader_resumes_at_the_next_unconsumed_sample(tmp_path):
+    """A worker process prefetches ahead of the trainer; the state that comes with each batch lets a resume continue
+    with the sample after the last one the trainer took."""
+    from ksa_b200.data import ResumableLoader
+    _, recipe = _corpora(tmp_path, 256)
+    mk = lambda: KaiMMapDataset(recipe, 64, seed=7, global_batch_size=4)
+    plain = iter(mk())
+    expect = [next(plain)["input_ids"] for _ in range(9)]
+    loader = ResumableLoader(mk(), num_workers=1, prefetch_factor=4)
+    it = iter(loader)
+    got = [next(it)["input_ids"] for _ in range(5)]
+    assert all(torch.equal(a, b) for a, b in zip(got, expect[:5]))
+    state = loader.state_dict()
+    del it, loader
+    resumed = ResumableLoader(mk(), num_workers=1)
+    resumed.load_state_dict(state)
+    it = iter(resumed)
+    rest = [next(it)["input_ids"] for _ in range(4)]
+    assert all(torch.equal(a, b) for a, b in zip(rest, expect[5:]))
+
+
+def test_recipe_logs_per_source_loss_and_tensorboard(tmp_path):
+    cfg = get_preset("qwen3-ksa-tiny").merge({"num_layers": 2, "summary_layer_freq": [1, 0], "embed_dim": 64,
+                                               "intermediate_dim": 128, "vocab_size": 256, "summary_token_begin": 256,
+                                               "head_dim": 16, "summary_chunk_size": 16})
+    mc = tmp_path / "model.json"
+    cfg.save(str(mc))
+    ds_cfg, _ = _corpora(tmp_path, 256)
+    out = tmp_path / "run"
+    r = train(get_argument_parser().parse_args([
+        "--model-config", str(mc), "--dataset-config", ds_cfg, "--output-dir", str(out), "--learning-rate", "1e-3",
+        "--lr-scheduler-type", "constant", "--logging-per-step", "2", "--seed", "1", "--model-dtype", "float32",
+        "--num-training-steps", "6", "--monitor-datasource-loss", "--num-workers", "1"]))
+    assert r["steps"] == 6
+    rows = (out / "metrics.csv").read_text()
+    assert "domain_loss/web" in rows or "domain_loss/code" in rows
+    assert "datasource_tokens/" in rows and "perf/step_elapsed" in rows
+    events = [f for f in os.listdir(out / "log") if f.startswith("events.out.tfevents")]
+    assert events, "no TensorBoard event file"
