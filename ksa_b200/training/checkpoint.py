@@ -11,8 +11,12 @@ names are the reference's (q/k/v and w1/w3 split out of the fused tensors), so i
 files.  Independent switches choose what a resume restores (weights / optimizer / training state / dataloader), and
 the step numbering continues from the directory name.
 
-The engine keeps master weights and Adam moments as per-rank shards of flat unit buffers; for saving, every unit is
-all-gathered into full fp32 tensors (one unit at a time) and DCP de-duplicates the replicated entries across ranks.
+The engine keeps master weights and Adam moments as per-rank shards of flat unit buffers, cut anywhere inside a
+parameter.  With more than one rank every saved tensor is a ``DTensor`` sharded by rows over the ranks (the layout of
+the reference's FSDP2 state, ``muse/training/checkpoint.py:528-557``): each rank holds, copies to the host and writes
+only ``1/world`` of the model and optimizer state, and a load re-shards for whatever world size reads it.  Moving
+from the flat shards to row shards takes one all-gather of a unit at a time on the device (a few hundred MB,
+transient); nothing of full size ever sits in host memory.
 """
 from __future__ import annotations
 
@@ -69,60 +73,167 @@ def step_from_path(path: str) -> int:
 
 # --------------------------------------------------------------------------------------------------- engine <-> tensors
 def _gather_unit(engine, shard: torch.Tensor, unit) -> torch.Tensor:
-    """Full fp32 flat buffer of ``unit`` from every rank's shard."""
+    """Full fp32 flat buffer of ``unit`` from every rank's shard, on the engine's device."""
     if engine.world_size == 1:
         return shard
+    group = getattr(engine, "group", None)
+    shard = shard.contiguous()
+    if dist.get_backend(group) == "nccl":
+        full = torch.empty(shard.numel() * engine.world_size, dtype=shard.dtype, device=shard.device)
+        dist.all_gather_into_tensor(full, shard, group=group)
+        return full
     parts = [torch.empty_like(shard) for _ in range(engine.world_size)]
-    dist.all_gather(parts, shard.contiguous(), group=getattr(engine, "group", None))
+    dist.all_gather(parts, shard, group=group)
     return torch.cat(parts)
 
 
-def engine_full_state(engine, with_optimizer: bool = True) -> Dict[str, Dict[str, torch.Tensor]]:
-    """``{"model": {fused name: fp32}, "exp_avg": {...}, "exp_avg_sq": {...}}`` as CPU tensors."""
+def _sharded(engine) -> bool:
+    return engine.world_size > 1 and dist.is_available() and dist.is_initialized()
+
+
+def _mesh(engine):
+    from torch.distributed.device_mesh import DeviceMesh
+    m = getattr(engine, "_ckpt_mesh", None)
+    if m is None:
+        group = getattr(engine, "group", None) or dist.group.WORLD
+        m = DeviceMesh.from_group(group, "cuda" if engine.device.type == "cuda" else "cpu")
+        engine._ckpt_mesh = m
+    return m
+
+
+def _row_range(rows: int, world: int, rank: int):
+    """Rows of a dim-0 sharded tensor that ``rank`` owns (torch's rule: chunks of ceil(rows / world))."""
+    per = (rows + world - 1) // world
+    lo = min(rows, rank * per)
+    return lo, min(rows, lo + per)
+
+
+def _to_dtensor(engine, full: torch.Tensor):
+    """Keep this rank's rows of ``full`` (a copy) and describe the whole tensor as a row-sharded ``DTensor``."""
+    from torch.distributed.tensor import DTensor, Shard
+    if full.dim() == 0:
+        full = full.reshape(1)
+    lo, hi = _row_range(full.shape[0], engine.world_size, engine.rank)
+    local = full[lo:hi].clone()
+    return DTensor.from_local(local, _mesh(engine), [Shard(0)], run_check=False, shape=full.shape,
+                              stride=full.contiguous().stride())
+
+
+def _to_muse(engine, fused: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    m = engine.model
+    return m.muse_state_dict(fused) if hasattr(m, "muse_state_dict") else fused
+
+
+def _from_muse(engine, muse: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    m = engine.model
+    return m.from_muse_state_dict(muse) if hasattr(m, "from_muse_state_dict") else muse
+
+
+def engine_state_for_save(engine, with_optimizer: bool = True) -> Dict[str, Dict[str, torch.Tensor]]:
+    """``{"model": {reference name: tensor}, "exp_avg": {...}, "exp_avg_sq": {...}}``.  One rank: CPU tensors.  Several
+    ranks: row-sharded ``DTensor``s, each rank keeping only its rows."""
     out: Dict[str, Dict[str, torch.Tensor]] = {"model": {}, "exp_avg": {}, "exp_avg_sq": {}}
     kinds = [("model", "master")] + ([("exp_avg", "exp_avg"), ("exp_avg_sq", "exp_avg_sq")] if with_optimizer else [])
+    sharded = _sharded(engine)
     for u in engine.units:
         for key, attr in kinds:
             full = _gather_unit(engine, getattr(u, attr), u)
-            for s in u.slots:
-                out[key][s.name] = full[s.offset:s.offset + s.numel].view(s.shape).to("cpu", copy=True)
-    for s in getattr(engine, "frozen_slots", []):     # frozen weights: saved with the model, no optimizer state
-        out["model"][s.name] = s.param.detach().to(device="cpu", dtype=torch.float32, copy=True)
+            fused = {s.name: full[s.offset:s.offset + s.numel].view(s.shape) for s in u.slots}
+            for name, t in _to_muse(engine, fused).items():
+                out[key][name] = _to_dtensor(engine, t) if sharded else t.to("cpu", copy=True)
+            del full, fused
+    frozen = {s.name: s.param.detach().to(torch.float32) for s in getattr(engine, "frozen_slots", [])}
+    for name, t in _to_muse(engine, frozen).items():     # frozen weights: saved with the model, no optimizer state
+        out["model"][name] = _to_dtensor(engine, t) if sharded else t.to("cpu", copy=True)
     return out
 
 
-def load_engine_full_state(engine, model_state: Optional[Dict[str, torch.Tensor]],
-                           exp_avg: Optional[Dict[str, torch.Tensor]] = None,
-                           exp_avg_sq: Optional[Dict[str, torch.Tensor]] = None, strict: bool = True) -> List[str]:
-    """Write full tensors (fused names) into this rank's shards; returns the names that were missing."""
+def engine_state_template(engine, with_optimizer: bool = True) -> Dict[str, Dict[str, torch.Tensor]]:
+    """The same tree as :func:`engine_state_for_save` with uninitialised storage: what a DCP load fills in."""
+    out: Dict[str, Dict[str, torch.Tensor]] = {"model": {}, "exp_avg": {}, "exp_avg_sq": {}}
+    sharded = _sharded(engine)
+
+    def empty_like_muse(slots):
+        fused = {s.name: torch.empty(s.shape, dtype=torch.float32, device="meta") for s in slots}
+        res = {}
+        for name, t in _to_muse(engine, fused).items():
+            shape = t.shape if t.dim() > 0 else (1,)
+            if sharded:
+                from torch.distributed.tensor import DTensor, Shard
+                lo, hi = _row_range(shape[0], engine.world_size, engine.rank)
+                local = torch.empty((hi - lo,) + tuple(shape[1:]), dtype=torch.float32, device=engine.device)
+                res[name] = DTensor.from_local(local, _mesh(engine), [Shard(0)], run_check=False, shape=torch.Size(shape),
+                                               stride=torch.empty(shape, device="meta").stride())
+            else:
+                res[name] = torch.empty(shape, dtype=torch.float32)
+        return res
+
+    for u in engine.units:
+        out["model"].update(empty_like_muse(u.slots))
+        if with_optimizer:
+            out["exp_avg"].update(empty_like_muse(u.slots))
+            out["exp_avg_sq"].update(empty_like_muse(u.slots))
+    out["model"].update(empty_like_muse(getattr(engine, "frozen_slots", [])))
+    return out
+
+
+def _full(t: torch.Tensor, device) -> torch.Tensor:
+    """A loaded entry as a whole tensor on ``device`` (a row-sharded ``DTensor`` is all-gathered)."""
+    if hasattr(t, "full_tensor"):
+        t = t.full_tensor()
+    return t.to(device=device, dtype=torch.float32)
+
+
+def load_engine_state(engine, model_state: Optional[Dict[str, torch.Tensor]],
+                      exp_avg: Optional[Dict[str, torch.Tensor]] = None,
+                      exp_avg_sq: Optional[Dict[str, torch.Tensor]] = None, strict: bool = True) -> List[str]:
+    """Write loaded tensors (reference names; whole tensors or row-sharded ``DTensor``s) into this rank's flat shards,
+    one unit at a time; returns the fused names that the checkpoint lacked."""
     missing: List[str] = []
+    dev = engine.device
+
+    def unit_tensors(src, slots):
+        """Fused tensors of ``slots`` assembled from the reference-named entries of ``src``."""
+        if src is None:
+            return None
+        probe = {s.name: torch.empty(s.shape, device="meta") for s in slots}
+        wanted = list(_to_muse(engine, probe))
+        have = {k: _full(src[k], dev) for k in wanted if k in src}
+        try:
+            return _from_muse(engine, have)
+        except KeyError:      # a fused tensor with some of its parts missing
+            return {}
+
     with torch.no_grad():
         for u in engine.units:
+            fused_m = unit_tensors(model_state, u.slots)
+            fused_a, fused_b = unit_tensors(exp_avg, u.slots), unit_tensors(exp_avg_sq, u.slots)
             for s in u.slots:
                 lo, hi = max(s.offset, u.shard_lo), min(s.offset + s.numel, u.shard_hi)
-                for src, dst in ((model_state, u.master), (exp_avg, u.exp_avg), (exp_avg_sq, u.exp_avg_sq)):
+                for src, dst in ((fused_m, u.master), (fused_a, u.exp_avg), (fused_b, u.exp_avg_sq)):
                     if src is None:
                         continue
                     if s.name not in src:
-                        if src is model_state:
+                        if src is fused_m:
                             missing.append(s.name)
                         continue
                     t = src[s.name]
-                    if tuple(t.shape) != tuple(s.shape):
+                    if t.numel() != s.numel:
                         raise ValueError(f"{s.name}: checkpoint shape {tuple(t.shape)} != model shape {tuple(s.shape)}")
                     if hi > lo:
-                        flat = t.reshape(-1)[lo - s.offset:hi - s.offset].to(device=engine.device, dtype=torch.float32)
-                        dst[lo - u.shard_lo:hi - u.shard_lo].copy_(flat)
-                if model_state is not None and s.name in model_state:
-                    u.compute[s.offset:s.offset + s.numel].copy_(
-                        model_state[s.name].reshape(-1).to(device=engine.device, dtype=torch.float32))
-        for s in getattr(engine, "frozen_slots", []):
-            if model_state is None:
+                        dst[lo - u.shard_lo:hi - u.shard_lo].copy_(t.reshape(-1)[lo - s.offset:hi - s.offset])
+                if fused_m is not None and s.name in fused_m:
+                    u.compute[s.offset:s.offset + s.numel].copy_(fused_m[s.name].reshape(-1))
+            del fused_m, fused_a, fused_b
+        frozen = getattr(engine, "frozen_slots", [])
+        fused_f = unit_tensors(model_state, frozen) if frozen else None
+        for s in frozen:
+            if fused_f is None:
                 continue
-            if s.name not in model_state:
+            if s.name not in fused_f:
                 missing.append(s.name)
                 continue
-            s.param.data.copy_(model_state[s.name].to(device=engine.device, dtype=torch.float32).view(s.shape))
+            s.param.data.copy_(fused_f[s.name].view(s.shape))
     if strict and missing:
         raise KeyError(f"checkpoint lacks {len(missing)} parameters, e.g. {missing[:4]}")
     return missing
@@ -150,18 +261,15 @@ class AppState(Stateful):
         self.required_training_state_keys = set(required_training_state_keys or [])
         self.extra_training_state = extra_training_state if extra_training_state is not None else {}
 
-    def _to_muse(self, fused: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
-        m = self.engine.model
-        return m.muse_state_dict(fused) if hasattr(m, "muse_state_dict") else fused
-
-    def _from_muse(self, muse: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
-        m = self.engine.model
-        return m.from_muse_state_dict(muse) if hasattr(m, "from_muse_state_dict") else muse
-
     def state_dict(self) -> Dict[str, Any]:
-        full = engine_full_state(self.engine, with_optimizer=True)
-        model = self._to_muse(full["model"])
-        m1, m2 = self._to_muse(full["exp_avg"]), self._to_muse(full["exp_avg_sq"])
+        return self._tree(engine_state_for_save(self.engine, with_optimizer=True))
+
+    def template(self) -> Dict[str, Any]:
+        """The tree of :meth:`state_dict` with uninitialised tensors, for a load to fill (nothing is gathered)."""
+        return self._tree(engine_state_template(self.engine, with_optimizer=not self.skip_optimizer))
+
+    def _tree(self, full) -> Dict[str, Any]:
+        model, m1, m2 = full["model"], full["exp_avg"], full["exp_avg_sq"]
         step = torch.tensor(float(self.engine.step_count))
         optim_state = {k: {"exp_avg": m1[k], "exp_avg_sq": m2[k], "step": step.clone()} for k in model if k in m1}
         e = self.engine
@@ -178,13 +286,13 @@ class AppState(Stateful):
         return {"model": model, "optim": optim, "training": training}
 
     def load_state_dict(self, state: Dict[str, Any]) -> None:
-        model = self._from_muse(state["model"]) if "model" in state else None
+        model = state.get("model")
         ea = es = None
         if not self.skip_optimizer and "optim" in state:
             st = state["optim"]["state"]
-            ea = self._from_muse({k: v["exp_avg"] for k, v in st.items()})
-            es = self._from_muse({k: v["exp_avg_sq"] for k, v in st.items()})
-        load_engine_full_state(self.engine, model, ea, es, strict=self.strict)
+            ea = {k: v["exp_avg"] for k, v in st.items()}
+            es = {k: v["exp_avg_sq"] for k, v in st.items()}
+        load_engine_state(self.engine, model, ea, es, strict=self.strict)
         training = state.get("training", {})
         skip = self.skip_training_state_keys
         if not self.skip_training_state:
@@ -232,7 +340,7 @@ class DistributedCheckpointer:
             dcp.save(state, storage_writer=writer, no_dist=not (dist.is_available() and dist.is_initialized()))
 
     def load(self, app_state: AppState, path: str) -> None:
-        template = {"app": app_state.state_dict()}
+        template = {"app": app_state.template()}
         if app_state.skip_optimizer:
             template["app"].pop("optim", None)
         dcp.load(template, storage_reader=dcp.FileSystemReader(path),

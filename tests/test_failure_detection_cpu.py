@@ -147,6 +147,20 @@ def test_checkpoint_survives_a_change_of_world_size(tmp_path):
     outs = [p.communicate(timeout=240)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs[0][-2000:]
     assert (out / "latest").read_text() == "global_step4"
+    # every rank wrote its own rows only: two data files of about the same size, and the metadata records each
+    # parameter as two row chunks
+    files = sorted(f for f in os.listdir(out / "global_step4") if f.endswith(".distcp"))
+    sizes = [sum(os.path.getsize(out / "global_step4" / f) for f in files if f.startswith(f"__{r}_")) for r in (0, 1)]
+    assert min(sizes) > 0.8 * max(sizes), (files, sizes)
+    import torch.distributed.checkpoint as dcp
+    meta = dcp.FileSystemReader(str(out / "global_step4")).read_metadata()
+    chunks = meta.state_dict_metadata["app.model.model.layers.0.mlp.w2.weight"].chunks
+    assert len(chunks) == 2 and chunks[0].sizes[0] == chunks[1].sizes[0] and chunks[1].offsets[0] == chunks[0].sizes[0]
+    # the single-process reader of the converters puts the row chunks back together
+    from ksa_b200.training.checkpoint import dcp_to_state_dict
+    from ksa_b200.tools.convert import flatten_model_state
+    tree = flatten_model_state(dcp_to_state_dict(str(out / "global_step4")))
+    assert tree["model.layers.0.mlp.w2.weight"].shape[0] == 2 * chunks[0].sizes[0]
     r = train(get_argument_parser().parse_args(base + ["--num-training-steps", "6", "--checkpoint-dir", str(out),
                                                         "--resume-weights", "--resume-optimizer", "--logging-per-step", "1"]))
     assert r["steps"] == 6 and r["loss"] is not None and r["loss"] < 6.5
