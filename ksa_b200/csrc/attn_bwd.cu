@@ -112,7 +112,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int q_tile = n_qtiles - 1 - (int)blockIdx.x;
   const int head = blockIdx.y, b = blockIdx.z;
   const int kv_head = head / (sh.Hq / sh.Hkv);
-  const TileRange tr = key_tiles_for_query_tile(sh, q_tile);
+  const TileRange tr = key_tiles_for_query_tile(sh, q_tile, b);
   const int total = tr.total();
 
   if (threadIdx.x == 0) {
@@ -215,6 +215,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int q_local = q_tile * 128 + r;
     const bool valid = q_local < sh.Lq;
     const int t_glob = sh.q_off + q_local;
+    const int doc_start = (sh.q_doc_start && valid) ? sh.q_doc_start[(long long)b * sh.Lq + q_local] : 0;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     // delta = rowsum(O * dO); LSE in log2 units
     float delta = 0.f, lse2 = INFINITY;
@@ -243,7 +244,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const bool is_sum = j < tr.n_sum_tiles;
       const int kt = is_sum ? j : tr.text_first + (j - tr.n_sum_tiles);
       int lo, hi;
-      allowed_columns(sh, t_glob, is_sum, kt, lo, hi);
+      allowed_columns(sh, t_glob, is_sum, kt, lo, hi, doc_start);
       // dS (bf16, two per column) overwrites the scores this warpgroup has already read:
       // chunk c goes to columns (c/2)*64 + (c%2)*16.  All four loads are issued before the single wait, so the
       // TMEM latency is paid once per step.
@@ -328,7 +329,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int seg = is_sum ? (int)blockIdx.x % n_seg : 0;
   const int kv_head = blockIdx.y, b = blockIdx.z;
   const int G = sh.Hq / sh.Hkv;
-  QueryRange qr = is_sum ? query_tiles_for_summary_key_tile(sh, kt) : query_tiles_for_text_key_tile(sh, kt);
+  QueryRange qr = is_sum ? query_tiles_for_summary_key_tile(sh, kt) : query_tiles_for_text_key_tile(sh, kt, blockIdx.z);
   if (is_sum && n_seg > 1) {
     qr.first = max(qr.first, seg * kSumSeg);
     qr.last = min(qr.last, seg * kSumSeg + kSumSeg - 1);
@@ -448,6 +449,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       t_lo = ug;
       t_hi = (sh.window >= (1 << 29)) ? (1LL << 40) : (long long)(ug / sh.chunk + sh.window + 1) * sh.chunk - 1;
       if (sh.tok_window > 0) t_hi = min(t_hi, (long long)ug + sh.tok_window - 1);
+      if (sh.k_doc_end && valid) t_hi = min(t_hi, (long long)sh.k_doc_end[(long long)b * sh.Lk + k_local] - 1);
     }
     if (!valid) { t_lo = 1; t_hi = 0; }
     bool ok = true;
@@ -610,7 +612,8 @@ KSA_API int ksa_attn_bwd(const void* q, const void* k, const void* v, const void
                          long long o_bs, long long dq_rs, long long dq_bs, long long dk_rs, long long dk_bs,
                          long long dv_rs, long long dv_bs, long long dks_rs, long long dks_bs, long long dvs_rs,
                          long long dvs_bs, int q_off, int k_off, int s_off, int chunk, int n_sum, int window,
-                         int tok_window, float scale, void* dks32, void* dvs32, void* stream) {
+                         int tok_window, float scale, void* dks32, void* dvs32, const void* q_doc_start,
+                         const void* k_doc_end, void* stream) {
   KSA_ENTER(q);
   using namespace ksa;
   KSA_REQUIRE(HD == 128 || HD == 64, "attn_bwd: head_dim %d unsupported (64 or 128)", HD);
@@ -631,7 +634,8 @@ KSA_API int ksa_attn_bwd(const void* q, const void* k, const void* v, const void
     tvs = tv;
   }
   BwdParams p;
-  p.s = AttnShape{B, Hq, Hkv, Lq, Lk, Ns, q_off, k_off, s_off, chunk, n_sum > 0 ? n_sum : 1, window, tok_window};
+  p.s = AttnShape{B, Hq, Hkv, Lq, Lk, Ns, q_off, k_off, s_off, chunk, n_sum > 0 ? n_sum : 1, window, tok_window,
+                  (const int*)q_doc_start, (const int*)k_doc_end};
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.o = (const bf16*)o; p.d_o = (const bf16*)d_o; p.o_row_stride = o_rs; p.o_batch_stride = o_bs;

@@ -207,7 +207,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int seg = is_sum ? (int)blockIdx.x % n_seg : 0;
   const int kv_head = blockIdx.y, b = blockIdx.z;
   const int G = sh.Hq / sh.Hkv;
-  QueryRange qr = is_sum ? query_tiles_for_summary_key_tile(sh, kt) : query_tiles_for_text_key_tile(sh, kt);
+  QueryRange qr = is_sum ? query_tiles_for_summary_key_tile(sh, kt) : query_tiles_for_text_key_tile(sh, kt, blockIdx.z);
   if (is_sum && n_seg > 1) {
     qr.first = max(qr.first, seg * kFbSumSeg);
     qr.last = min(qr.last, seg * kFbSumSeg + kFbSumSeg - 1);
@@ -350,6 +350,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       t_lo = ug;
       t_hi = (sh.window >= (1 << 29)) ? (1LL << 40) : (long long)(ug / sh.chunk + sh.window + 1) * sh.chunk - 1;
       if (sh.tok_window > 0) t_hi = min(t_hi, (long long)ug + sh.tok_window - 1);
+      if (sh.k_doc_end && valid) t_hi = min(t_hi, (long long)sh.k_doc_end[(long long)b * sh.Lk + k_local] - 1);
     }
     if (!valid) { t_lo = 1; t_hi = 0; }
     uint8_t* ds_row = sDs + half * S::kHalfTile + r * 128;   // this key's row of dS^T_h (64 bf16, swizzled 16-byte chunks)
@@ -561,7 +562,7 @@ KSA_API int ksa_attn_bwd_fused(const void* q, const void* k, const void* v, cons
                                long long dk_bs, long long dv_rs, long long dv_bs, long long dks_rs, long long dks_bs,
                                long long dvs_rs, long long dvs_bs, int q_off, int k_off, int s_off, int chunk,
                                int n_sum, int window, int tok_window, float scale, void* dks32, void* dvs32,
-                               void* stream) {
+                               const void* q_doc_start, const void* k_doc_end, void* stream) {
   KSA_ENTER(q);
   using namespace ksa;
   KSA_REQUIRE(HD == 128, "attn_bwd_fused: head_dim %d unsupported (128 only)", HD);
@@ -585,7 +586,8 @@ KSA_API int ksa_attn_bwd_fused(const void* q, const void* k, const void* v, cons
     tvs = tv;
   }
   FbParams p;
-  p.s = AttnShape{B, Hq, Hkv, Lq, Lk, Ns, q_off, k_off, s_off, chunk, n_sum > 0 ? n_sum : 1, window, tok_window};
+  p.s = AttnShape{B, Hq, Hkv, Lq, Lk, Ns, q_off, k_off, s_off, chunk, n_sum > 0 ? n_sum : 1, window, tok_window,
+                  (const int*)q_doc_start, (const int*)k_doc_end};
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.stats = (const float*)stats;

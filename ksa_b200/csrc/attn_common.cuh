@@ -28,6 +28,12 @@ struct AttnShape {
   int n_sum;       // S
   int window;      // W in chunks (>= 1<<29 means unbounded)
   int tok_window;  // > 0: additionally t - u < tok_window
+  // Packed documents (both null: one document per sequence).  A query only sees keys of its own document:
+  // q_doc_start[b * Lq + i] = global text index of the first token of local query row i's document,
+  // k_doc_end[b * Lk + j]   = global text index one past the last token of local text key row j's document
+  // (the replacement for flash_attn_varlen_func with cu_seqlens, muse/layers/attention_utils.py:222-246).
+  const int* q_doc_start;
+  const int* k_doc_end;
 };
 
 struct TileRange {
@@ -37,7 +43,7 @@ struct TileRange {
   __device__ __forceinline__ int total() const { return n_sum_tiles + (text_last - text_first + 1); }
 };
 
-__device__ __forceinline__ TileRange key_tiles_for_query_tile(const AttnShape& s, int q_tile) {
+__device__ __forceinline__ TileRange key_tiles_for_query_tile(const AttnShape& s, int q_tile, int b = 0) {
   TileRange r;
   const int t0 = s.q_off + q_tile * 128;
   const int t1 = min(s.q_off + s.Lq, t0 + 128) - 1;
@@ -47,13 +53,16 @@ __device__ __forceinline__ TileRange key_tiles_for_query_tile(const AttnShape& s
   r.n_sum_tiles = (s_end_l + 127) / 128;
   int u_min = max(0, qc_lo - s.window) * s.chunk;
   if (s.tok_window > 0) u_min = max(u_min, t0 - s.tok_window + 1);
+  if (s.q_doc_start) u_min = max(u_min, s.q_doc_start[(long long)b * s.Lq + q_tile * 128]);   // non-decreasing in the row
   r.text_first = max(0, u_min - s.k_off) / 128;
   r.text_last = max(0, min(t1 - s.k_off, s.Lk - 1)) / 128;
   return r;
 }
 
 // Allowed column interval [lo, hi] (inclusive, in-tile columns 0..127) of key tile `kt` for global query index t.
-__device__ __forceinline__ void allowed_columns(const AttnShape& s, int t, bool is_summary, int kt, int& lo, int& hi) {
+// `doc_start`: global text index of the first token of the query's document (0 without packing).
+__device__ __forceinline__ void allowed_columns(const AttnShape& s, int t, bool is_summary, int kt, int& lo, int& hi,
+                                                int doc_start = 0) {
   const int qc = t / s.chunk;
   if (is_summary) {
     lo = 0;
@@ -62,6 +71,7 @@ __device__ __forceinline__ void allowed_columns(const AttnShape& s, int t, bool 
   } else {
     int lo_g = max(0, qc - s.window) * s.chunk;
     if (s.tok_window > 0) lo_g = max(lo_g, t - s.tok_window + 1);
+    lo_g = max(lo_g, doc_start);
     lo = lo_g - s.k_off - kt * 128;
     hi = min(t - s.k_off, s.Lk - 1) - kt * 128;
   }
@@ -71,7 +81,7 @@ __device__ __forceinline__ void allowed_columns(const AttnShape& s, int t, bool 
 struct QueryRange {
   int first, last;  // inclusive query tiles; empty when first > last
 };
-__device__ __forceinline__ QueryRange query_tiles_for_text_key_tile(const AttnShape& s, int k_tile) {
+__device__ __forceinline__ QueryRange query_tiles_for_text_key_tile(const AttnShape& s, int k_tile, int b = 0) {
   QueryRange r;
   const int u0 = s.k_off + k_tile * 128;
   const int u1 = min(s.k_off + s.Lk, u0 + 128) - 1;
@@ -79,6 +89,7 @@ __device__ __forceinline__ QueryRange query_tiles_for_text_key_tile(const AttnSh
   long long t_max = (s.window >= (1 << 29)) ? (long long)s.q_off + s.Lq - 1
                                             : (long long)(u1 / s.chunk + s.window + 1) * s.chunk - 1;
   if (s.tok_window > 0) t_max = min(t_max, (long long)u1 + s.tok_window - 1);
+  if (s.k_doc_end) t_max = min(t_max, (long long)s.k_doc_end[(long long)b * s.Lk + (u1 - s.k_off)] - 1);   // non-decreasing
   t_max = min(t_max, (long long)s.q_off + s.Lq - 1);
   const int t_min = max(u0, s.q_off);
   if (t_max < t_min) { r.first = 1; r.last = 0; return r; }

@@ -83,7 +83,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int head0 = blockIdx.y * heads_per_cta;
   const int kv_head = head0 / (sh.Hq / sh.Hkv);
   const int b = blockIdx.z;
-  const TileRange tr = key_tiles_for_query_tile(sh, q_tile);
+  const TileRange tr = key_tiles_for_query_tile(sh, q_tile, b);
   const int total = tr.total();
 
   if (threadIdx.x == 0) {
@@ -180,6 +180,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t tS = tmem_base + lane_addr + t * 128;
       const uint32_t tO = tmem_base + lane_addr + 256 + t * HD;
       float m_run = -INFINITY, l_run = 0.f;
+      const int doc_start = (sh.q_doc_start && q_local < sh.Lq) ? sh.q_doc_start[(long long)b * sh.Lq + q_local] : 0;
       bool ok = true;
       for (int j = 0; j < total; ++j) {
         if (!mbar_wait(&s_full[t], j & 1, guard, kTimeoutAccFull)) { ok = false; break; }
@@ -191,7 +192,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const bool is_sum = j < tr.n_sum_tiles;
         const int kt = is_sum ? j : tr.text_first + (j - tr.n_sum_tiles);
         int lo, hi;
-        allowed_columns(sh, t_glob, is_sum, kt, lo, hi);
+        allowed_columns(sh, t_glob, is_sum, kt, lo, hi, doc_start);
         float mx = -INFINITY;
         if (lo > 0 || hi < 127) {
 #pragma unroll
@@ -323,12 +324,13 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 //   k,v  [B, Lk, Hkv, HD]  text keys;   ks,vs [B, Ns, Hkv, HD] summary keys (Ns may be 0)
 //   o  [B, Lq, Hq, HD];  lse [B, Hq, Lq] fp32 (natural log) or null
 // window >= 2^29 disables the chunk window (plain causal); tok_window > 0 adds a token sliding window.
+// q_doc_start / k_doc_end (int32 [B, Lq] / [B, Lk], both or neither): packed documents, see AttnShape.
 KSA_API int ksa_attn_fwd(const void* q, const void* k, const void* v, const void* ks, const void* vs, void* o,
                          void* lse, int B, int Hq, int Hkv, int HD, int Lq, int Lk, int Ns, long long q_rs,
                          long long q_bs, long long k_rs, long long k_bs, long long v_rs, long long v_bs,
                          long long ks_rs, long long ks_bs, long long vs_rs, long long vs_bs, long long o_rs,
                          long long o_bs, int q_off, int k_off, int s_off, int chunk, int n_sum, int window,
-                         int tok_window, float scale, void* stream) {
+                         int tok_window, float scale, const void* q_doc_start, const void* k_doc_end, void* stream) {
   KSA_ENTER(q);
   using namespace ksa;
   KSA_REQUIRE(HD == 128 || HD == 64, "attn_fwd: head_dim %d unsupported (64 or 128)", HD);
@@ -349,7 +351,8 @@ KSA_API int ksa_attn_fwd(const void* q, const void* k, const void* v, const void
     tvs = tv;
   }
   FwdParams p;
-  p.s = AttnShape{B, Hq, Hkv, Lq, Lk, Ns, q_off, k_off, s_off, chunk, n_sum > 0 ? n_sum : 1, window, tok_window};
+  p.s = AttnShape{B, Hq, Hkv, Lq, Lk, Ns, q_off, k_off, s_off, chunk, n_sum > 0 ? n_sum : 1, window, tok_window,
+                  (const int*)q_doc_start, (const int*)k_doc_end};
   p.scale_log2 = scale * 1.4426950408889634f;
   p.o = (bf16*)o;
   p.o_row_stride = o_rs;

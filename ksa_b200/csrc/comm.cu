@@ -27,7 +27,8 @@ __global__ void __launch_bounds__(kCommThreads) peer_gather_kernel(GatherJob job
   run_gather_job(job, blockIdx.x, gridDim.x, status);
 }
 
-__global__ void __launch_bounds__(kCommThreads) peer_reduce_adamw_kernel(ReduceAdamwJob job, int* status) {
+// at most 64 registers per thread: two of these CTAs, or one next to a GEMM CTA, fit on an SM
+__global__ void __launch_bounds__(kCommThreads, 2) peer_reduce_adamw_kernel(ReduceAdamwJob job, int* status) {
   run_reduce_adamw_job(job, blockIdx.x, gridDim.x, status);
 }
 

@@ -35,8 +35,9 @@ class EagerAttention(nn.Module):
 
 
 class TensorCoreAttention(nn.Module):
-    """Causal attention on the tcgen05 kernel (fixed-length batches; ``window > 0`` keeps keys with
-    ``q - k < window``).  Packed documents (``cu_seqlens``) and arbitrary masks fall back to the eager form."""
+    """Causal attention on the tcgen05 kernel (``window > 0`` keeps keys with ``q - k < window``; ``cu_seqlens``:
+    documents packed into one sequence, as ``flash_attn_varlen_func`` takes them in the reference,
+    ``muse/layers/attention_utils.py:195-246``).  Arbitrary masks fall back to the eager form."""
 
     def __init__(self):
         super().__init__()
@@ -44,11 +45,10 @@ class TensorCoreAttention(nn.Module):
 
     def forward(self, q, k, v, mask: Optional[torch.Tensor] = None, is_causal: bool = True,
                 scale: Optional[float] = None, window: int = -1, cu_seqlens: Optional[torch.Tensor] = None):
-        fast = (q.is_cuda and q.dtype == torch.bfloat16 and mask is None and is_causal and cu_seqlens is None
-                and q.shape[-1] == 128)
+        fast = q.is_cuda and q.dtype == torch.bfloat16 and mask is None and is_causal and q.shape[-1] in (64, 128)
         if not fast:
             return self.eager(q, k, v, mask, is_causal, scale, window, cu_seqlens)
-        return ops.causal_attention(q, k, v, scale, window)
+        return ops.causal_attention(q, k, v, scale, window, cu_seqlens=cu_seqlens)
 
 
 ATTENTION_BACKENDS: Dict[str, type] = {"eager": EagerAttention, "tensor_core": TensorCoreAttention,

@@ -223,7 +223,8 @@ class KsaDecoderLayer(nn.Module):
             from ..parallel.cp import cp_attention_packed
             att = cp_attention_packed(qkv, meta.cp, Hq, Hkv, Dh, None, False, self.tok_window)
         else:
-            att = ops.attention_packed(qkv, meta.B, meta.L, 0, Hq, Hkv, Dh, tok_window=self.tok_window)
+            att = ops.attention_packed(qkv, meta.B, meta.L, 0, Hq, Hkv, Dh, tok_window=self.tok_window,
+                                       cu_seqlens=getattr(meta, "cu_seqlens", None))
         attn_out = _row_linear(tp, att, a.output_proj.weight, rows_attn)
         if collect is not None:
             collect.append(attn_out)
@@ -241,6 +242,7 @@ class BatchMeta:
         self.cp = cp          # context-parallel group state: this rank holds one contiguous shard of the sequence
         self.tp = None        # tensor-parallel group state (inference): row-parallel outputs are partial sums
         self.kv_sink = None   # optional callable(layer_idx, qkv_rot, is_summary_layer): prefill fills KV caches with it
+        self.cu_seqlens = None  # packed-document offsets for the full-attention layers
         if cp is not None:
             # ``layout`` describes the whole sequence; keep this shard's rows of its position ids
             r, Ll = cp.rank, cp.shape.local_len
@@ -375,8 +377,13 @@ class Qwen3Model(Model):
     def forward(self, tokens: torch.Tensor, labels: Optional[torch.Tensor] = None,
                 position_ids: Optional[torch.Tensor] = None, return_hidden: bool = False,
                 collect_attn: bool = False, ignore_index: int = -100, kv_sink=None, last_token_only: bool = False,
-                use_summary: bool = True):
+                use_summary: bool = True, cu_seqlens: Optional[torch.Tensor] = None):
         """``tokens`` ``[B, L]`` -> loss (with ``labels``), hidden ``[B, L, D]`` or logits ``[B, L, V]``.
+
+        ``cu_seqlens`` (token offsets of documents packed into the sequence, the same for every sequence of the batch):
+        full-attention layers keep every query inside its own document (the reference's varlen FlashAttention-2 path,
+        ``muse/models/qwen3/_layers.py:331-334``); summary-attention layers ignore document boundaries, as the
+        reference's summary insertion does (``muse/layers/summary_utils.py:26-27``).
 
         ``labels`` are already shifted (label of position t is token t+1) with ``ignore_index`` where masked,
         as the reference trainer builds them (``recipes/pretrain_kai_summary_unified.py:867-873``).
@@ -386,6 +393,7 @@ class Qwen3Model(Model):
         # teacher: same weights, no summary tokens, recipes/pretrain_kai_summary_unified.py:967-997)
         meta = self._meta(B, L, tokens.device, position_ids, use_summary)
         meta.kv_sink = kv_sink
+        meta.cu_seqlens = cu_seqlens if cu_seqlens is not None and cu_seqlens.numel() > 2 else None
         tp = meta.tp = self.tp
         x = self.embed(tokens, meta)
         collect = [] if collect_attn else None

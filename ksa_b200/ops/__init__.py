@@ -508,7 +508,8 @@ class _KsaAttentionFn(torch.autograd.Function):
     """Text + summary queries over text + summary keys (two-stream KSA); also plain causal attention."""
 
     @staticmethod
-    def forward(ctx, q, k, v, qs, ks, vs, chunk, n_sum, window, tok_window, scale, q_off, k_off, s_off, seq_len):
+    def forward(ctx, q, k, v, qs, ks, vs, chunk, n_sum, window, tok_window, scale, q_off, k_off, s_off, seq_len,
+                doc_start=None, doc_end=None):
         B, Lq, Hq, D = q.shape
         Lk, Hkv = k.shape[1], k.shape[2]
         has_sum = qs is not None and qs.shape[1] > 0
@@ -522,7 +523,8 @@ class _KsaAttentionFn(torch.autograd.Function):
             ksrs = ksbs = vsrs = vsbs = 0
         _lib.call("ksa_attn_fwd", q, k, v, ks if Ns_k > 0 else None, vs if Ns_k > 0 else None, o, lse,
                   B, Hq, Hkv, D, Lq, Lk, Ns_k, qrs, qbs, krs, kbs, vrs, vbs, ksrs, ksbs, vsrs, vsbs,
-                  o.stride(1), o.stride(0), q_off, k_off, s_off, chunk, max(n_sum, 1), window, tok_window, float(scale))
+                  o.stride(1), o.stride(0), q_off, k_off, s_off, chunk, max(n_sum, 1), window, tok_window, float(scale),
+                  doc_start, doc_end)
         os_ = lse_s = None
         if has_sum:
             Nq = qs.shape[1]
@@ -535,6 +537,7 @@ class _KsaAttentionFn(torch.autograd.Function):
                       chunk, n_sum, chunk0, k_off, s_off, float(scale))
         ctx.save_for_backward(q, k, v, qs, ks, vs, o, lse, os_, lse_s)
         ctx.cfg = (chunk, n_sum, window, tok_window, scale, q_off, k_off, s_off, seq_len)
+        ctx.docs = (doc_start, doc_end)
         if has_sum:
             return o, os_
         return o, None
@@ -573,7 +576,7 @@ class _KsaAttentionFn(torch.autograd.Function):
                        qrs, qbs, krs, kbs, vrs, vbs, ksrs, ksbs, vsrs, vsbs, o.stride(1), o.stride(0),
                        dq.stride(1), dq.stride(0), dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0),
                        dksrs, dksbs, dksrs, dksbs, q_off, k_off, s_off, chunk, max(n_sum, 1), window, tok_window,
-                       float(scale), part_k, part_v)
+                       float(scale), part_k, part_v, *ctx.docs)
         dqs = None
         if os_ is not None:
             Nq = qs.shape[1]
@@ -585,7 +588,7 @@ class _KsaAttentionFn(torch.autograd.Function):
                       os_.stride(1), os_.stride(0), dqs.stride(1), dqs.stride(0), dk.stride(1), dk.stride(0),
                       dv.stride(1), dv.stride(0), dksrs, dksbs, dksrs, dksbs, chunk, n_sum, q_off // chunk,
                       k_off, s_off, float(scale), part_k, part_v, Ns_k)
-        return (dq, dk, dv, dqs, dks, dvs) + (None,) * 9
+        return (dq, dk, dv, dqs, dks, dvs) + (None,) * 11
 
 
 def ksa_attention(q_t, k_t, v_t, q_s, k_s, v_s, chunk: int, n_sum: int, window: int,
@@ -619,15 +622,33 @@ def causal_attention(q, k, v, scale: Optional[float] = None, window: int = -1,
     """Causal attention (``window > 0``: keys with ``q - k < window``) on the same tensor-core kernel."""
     D = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if not _cuda(q) or cu_seqlens is not None:
-        if _cuda(q):
-            raise NotImplementedError("packed-document masking runs on the CPU path only")
+    if not _cuda(q):
         return ref.causal_attention(q, k, v, scale, window, cu_seqlens)
     _require_bf16(q, k, v)
     q_off = (k.shape[1] - q.shape[1]) if q_off is None else q_off
+    doc_start = doc_end = None
+    if cu_seqlens is not None:
+        doc_start, doc_end = document_bounds(cu_seqlens, q.shape[0], q.shape[1], k.shape[1], q_off)
     o, _ = _KsaAttentionFn.apply(q, k, v, None, None, None, 128, 1, UNBOUNDED_WINDOW,
-                                 window if window and window > 0 else 0, scale, q_off, 0, 0, k.shape[1])
+                                 window if window and window > 0 else 0, scale, q_off, 0, 0, k.shape[1],
+                                 doc_start, doc_end)
     return o
+
+
+def document_bounds(cu_seqlens: torch.Tensor, B: int, Lq: int, Lk: int, q_off: int = 0):
+    """Per-row document bounds of a packed sequence for the attention kernels: ``cu_seqlens`` (``[n_docs + 1]``, token
+    offsets as ``flash_attn_varlen_func`` takes them, the same packing for every sequence of the batch) ->
+    ``(q_doc_start [B, Lq], k_doc_end [B, Lk])`` int32: the first token of each query's document and one past the
+    last token of each key's document (``muse/layers/attention_utils.py:195-246`` passes the offsets themselves)."""
+    cu = cu_seqlens.to(device="cuda" if torch.cuda.is_available() else cu_seqlens.device).to(torch.int64).reshape(-1)
+    dev = cu.device
+    tq = torch.arange(q_off, q_off + Lq, device=dev)
+    tk = torch.arange(Lk, device=dev)
+    dq = torch.bucketize(tq, cu[1:], right=True).clamp_(max=cu.numel() - 2)
+    dk = torch.bucketize(tk, cu[1:], right=True).clamp_(max=cu.numel() - 2)
+    start = cu[dq].to(torch.int32)[None, :].expand(B, -1).contiguous()
+    end = cu[1:][dk].to(torch.int32)[None, :].expand(B, -1).contiguous()
+    return start, end
 
 
 def shard_causal_attention(q, k, v, scale: float, tok_window: int, q_off: int, k_off: int, seq_len: int):
@@ -657,7 +678,7 @@ class _PackedAttentionFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, qkv, B, L, Ns, Hq, Hkv, D, chunk, n_sum, window, tok_window, scale):
+    def forward(ctx, qkv, B, L, Ns, Hq, Hkv, D, chunk, n_sum, window, tok_window, scale, doc_start=None, doc_end=None):
         R = B * (L + Ns)
         assert qkv.shape[0] == R and qkv.stride(1) == 1
         q, k, v = _packed_views(qkv, B, L, Hq, Hkv, D, 0)
@@ -671,7 +692,7 @@ class _PackedAttentionFn(torch.autograd.Function):
             qs = ks = vs = None
         _lib.call("ksa_attn_fwd", q, k, v, ks, vs, o, lse, B, Hq, Hkv, D, L, L, Ns,
                   rs, L * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs, Hq * D, L * Hq * D,
-                  0, 0, 0, chunk, max(n_sum, 1), window, tok_window, float(scale))
+                  0, 0, 0, chunk, max(n_sum, 1), window, tok_window, float(scale), doc_start, doc_end)
         lse_s = None
         if Ns > 0:
             os_ = out[B * L:].view(B, Ns, Hq, D)
@@ -681,6 +702,7 @@ class _PackedAttentionFn(torch.autograd.Function):
                       chunk, n_sum, 0, 0, 0, float(scale))
         ctx.save_for_backward(qkv, out, lse, lse_s)
         ctx.cfg = (B, L, Ns, Hq, Hkv, D, chunk, n_sum, window, tok_window, scale)
+        ctx.docs = (doc_start, doc_end)
         return out
 
     @staticmethod
@@ -707,7 +729,7 @@ class _PackedAttentionFn(torch.autograd.Function):
                        B, Hq, Hkv, D, L, L, Ns,
                        rs, L * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs, Hq * D, L * Hq * D,
                        drs, L * drs, drs, L * drs, drs, L * drs, drs, Ns * drs, drs, Ns * drs,
-                       0, 0, 0, chunk, max(n_sum, 1), window, tok_window, float(scale), part_k, part_v)
+                       0, 0, 0, chunk, max(n_sum, 1), window, tok_window, float(scale), part_k, part_v, *ctx.docs)
         if Ns > 0:
             os_ = out[B * L:].view(B, Ns, Hq, D)
             dos = dout[B * L:].view(B, Ns, Hq, D)
@@ -715,18 +737,20 @@ class _PackedAttentionFn(torch.autograd.Function):
                       B, Hq, Hkv, D, Ns, L, rs, Ns * rs, rs, L * rs, rs, L * rs, rs, Ns * rs, rs, Ns * rs,
                       Hq * D, Ns * Hq * D, drs, Ns * drs, drs, L * drs, drs, L * drs, drs, Ns * drs, drs, Ns * drs,
                       chunk, n_sum, 0, 0, 0, float(scale), part_k, part_v, Ns)
-        return (dqkv,) + (None,) * 11
+        return (dqkv,) + (None,) * 13
 
 
 def attention_packed(qkv: torch.Tensor, B: int, L: int, Ns: int, Hq: int, Hkv: int, D: int, chunk: int = 128,
                      n_sum: int = 1, window: int = UNBOUNDED_WINDOW, tok_window: int = 0,
-                     scale: Optional[float] = None, mode: str = "kernel") -> torch.Tensor:
+                     scale: Optional[float] = None, mode: str = "kernel",
+                     cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
     """KSA (``Ns > 0``) or causal (``Ns = 0``) attention on packed rotated rows; see :class:`_PackedAttentionFn`.
 
     ``mode`` selects the summary-attention implementation like the reference's ``summary_attention_mode``
     (``muse/layers/summary_attention_func.py:506-584``): ``"kernel"`` (the sm_100a kernels on a GPU, the dense oracle
     on CPU), ``"mask"`` (dense boolean mask, plain PyTorch, any device) or ``"block"`` (query blocks with gathered
-    keys, plain PyTorch, any device)."""
+    keys, plain PyTorch, any device).  ``cu_seqlens`` (causal attention only): documents packed into the sequence; a
+    query sees keys of its own document only."""
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if mode not in ("kernel", "mask", "block"):
         raise ValueError(f"unknown summary attention mode {mode!r}")
@@ -737,9 +761,16 @@ def attention_packed(qkv: torch.Tensor, B: int, L: int, Ns: int, Hq: int, Hkv: i
             fn = ref.ksa_attention_blockwise if mode == "block" else ref.ksa_attention
             o_t, o_s = fn(q, k, v, qs, ks, vs, chunk, n_sum, window, scale)
             return torch.cat([o_t.reshape(B * L, Hq * D), o_s.reshape(B * Ns, Hq * D)], dim=0)
-        return ref.causal_attention(q, k, v, scale, tok_window if tok_window > 0 else -1).reshape(B * L, Hq * D)
+        return ref.causal_attention(q, k, v, scale, tok_window if tok_window > 0 else -1,
+                                    cu_seqlens).reshape(B * L, Hq * D)
     _require_bf16(qkv)
-    return _PackedAttentionFn.apply(qkv, B, L, Ns, Hq, Hkv, D, chunk, n_sum, window, tok_window, scale)
+    docs = (None, None)
+    if cu_seqlens is not None:
+        if Ns > 0:
+            raise ValueError("packed documents apply to causal attention only: summary tokens are inserted without "
+                             "regard to document boundaries")
+        docs = document_bounds(cu_seqlens, B, L, L)
+    return _PackedAttentionFn.apply(qkv, B, L, Ns, Hq, Hkv, D, chunk, n_sum, window, tok_window, scale, *docs)
 
 
 # =============================================================================== fused linear + cross entropy

@@ -39,9 +39,9 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_cross_entropy": [P, P, P, P, L, I, L, I, I, P],
     "ksa_adamw": [P, P, P, P, P, L, P, F, F, F, F, F, P, P],
     "ksa_cast_f32_bf16": [P, P, L, P],
-    "ksa_attn_fwd": [P] * 7 + [I] * 7 + [L] * 12 + [I] * 7 + [F, P],
-    "ksa_attn_bwd": [P] * 14 + [I] * 7 + [L] * 22 + [I] * 7 + [F, P, P, P],
-    "ksa_attn_bwd_fused": [P] * 15 + [I] * 7 + [L] * 22 + [I] * 7 + [F, P, P, P],
+    "ksa_attn_fwd": [P] * 7 + [I] * 7 + [L] * 12 + [I] * 7 + [F, P, P, P],
+    "ksa_attn_bwd": [P] * 14 + [I] * 7 + [L] * 22 + [I] * 7 + [F, P, P, P, P, P],
+    "ksa_attn_bwd_fused": [P] * 15 + [I] * 7 + [L] * 22 + [I] * 7 + [F, P, P, P, P, P],
     "ksa_summary_attn_fwd": [P] * 7 + [I] * 6 + [L] * 12 + [I] * 5 + [F, P],
     "ksa_summary_attn_bwd": [P] * 13 + [I] * 6 + [L] * 22 + [I] * 5 + [F, P, P, I, P],
     "ksa_decode_attn": [P] * 8 + [I] * 8 + [F, P],

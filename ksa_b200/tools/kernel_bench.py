@@ -134,6 +134,60 @@ def bench_attn(a) -> None:
         ms_fb = timeit(fb, a.iters, a.warmup, not a.no_flush)
         report(f"attention bwd {kind} L{L} (fwd+bwd minus fwd; useful FLOPs = 2.5x fwd)", ms_fb - ms_f,
                flops=2.5 * fwd_flops)
+    if a.compare_ref:
+        _compare_reference_attention(a, fwd_flops)
+
+
+def _compare_reference_attention(a, fwd_flops: float) -> None:
+    """Same shapes on other implementations, same GPU, same timing: flash_attn 2.x (dense causal only) and the
+    reference's own sm_100 kernels from its wheels (``baseline/reference_kernels.py``; one GPU only)."""
+    import sys
+    sys.path.insert(0, ROOT)
+    from baseline import reference_kernels as rk
+    B, Hq, Hkv, D, C, S, W, L = a.batch, a.hq, a.hkv, a.dim, a.chunk, a.nsum, a.window, a.seq
+    mk = lambda T, H: torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_(a.bwd)
+
+    def run(name, fn, make_inputs):
+        try:
+            xs = make_inputs()
+            out = [None]
+
+            def f():
+                out[0] = fn(*xs)
+            ms_f = timeit(f, a.iters, a.warmup, not a.no_flush)
+            report(f"  {name} fwd", ms_f, flops=fwd_flops)
+            if a.bwd:
+                g = torch.randn_like(out[0])
+
+                def fb():
+                    f()
+                    out[0].backward(g)
+                ms_fb = timeit(fb, a.iters, a.warmup, not a.no_flush)
+                report(f"  {name} bwd (fwd+bwd minus fwd)", ms_fb - ms_f, flops=2.5 * fwd_flops)
+        except BaseException as e:  # noqa: BLE001 - a JIT compilation failure must not end the comparison
+            print(f"  {name}: unavailable: {' '.join(f'{type(e).__name__}: {e}'.split())[:300]}", flush=True)
+
+    if a.causal:
+        try:
+            from flash_attn import flash_attn_func as fa2
+            run("flash_attn 2.x causal", lambda q, k, v: fa2(q, k, v, causal=True), lambda: (mk(L, Hq), mk(L, Hkv), mk(L, Hkv)))
+        except BaseException as e:  # noqa: BLE001
+            print(f"  flash_attn 2.x: unavailable: {type(e).__name__}: {e}", flush=True)
+        fn, why = rk.dense_causal()
+        if fn is None:
+            print(f"  reference sm_100 causal (flash_attn_cute wheel): unavailable: {why}", flush=True)
+        else:
+            run("reference sm_100 causal (flash_attn_cute wheel)", fn, lambda: (mk(L, Hq), mk(L, Hkv), mk(L, Hkv)))
+        return
+    fn, why = rk.summary_attention(C, S, W)
+    if fn is None:
+        print(f"  reference sm_100 summary attention: unavailable: {why}", flush=True)
+        return
+    T = L + (L // C) * S                     # the reference's interleaved layout, K/V expanded to the query heads
+    idx = torch.arange(T, device="cuda")
+    summary_pos = idx[(idx % (C + S)) >= C]
+    run("reference sm_100 summary attention (wheels, 256x128 lists)",
+        lambda q, k, v: fn(q, k, v, summary_pos), lambda: (mk(T, Hq), mk(T, Hq), mk(T, Hq)))
 
 
 def bench_decode(a) -> None:
@@ -433,6 +487,8 @@ def bench_tp_reduce(a) -> None:
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--compare-ref", action="store_true",
+                    help="attn: also time flash_attn 2.x and the reference's sm_100 kernels on the same shapes (1 GPU)")
     ap.add_argument("what", choices=["gemm", "gemv", "attn", "decode", "norm", "cp-attn", "comm", "tp-reduce", "ag-gemm",
                                      "gemm-rs"])
     # the long spellings are for use under torch.distributed.run, whose own parser claims --m and --n as prefixes

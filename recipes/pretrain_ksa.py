@@ -36,7 +36,8 @@ def get_argument_parser() -> argparse.ArgumentParser:
     a("--batch-size", type=int, default=1)
     a("--shuffle-buffer-size", type=int, default=0)
     a("--use-dataset-load-balance", action="store_true")
-    a("--packing", action="store_true")
+    a("--packing", action="store_true",
+      help="batches carry cu_seqlens of packed documents: full-attention layers attend within documents only")
     # checkpoints
     a("--model-dir", default=None, help="HF directory to initialise the weights from")
     a("--checkpoint-dir", default=None)
@@ -275,7 +276,7 @@ def train(args) -> dict:
 
     # one CUDA graph per step on a single GPU; multi-GPU steps stay eager (see FsdpEngine.graphed_step)
     use_graph = use_cuda and world == 1 and not args.no_cuda_graph and not args.enable_distill \
-        and not args.enable_gradient_checkpointing
+        and not args.enable_gradient_checkpointing and not args.packing
     n_workers = args.num_workers if args.num_workers is not None else getattr(dataset, "loader_workers", 0)
     loader = dataset
     if n_workers > 0:
@@ -320,7 +321,10 @@ def train(args) -> dict:
                 loss = engine.graphed_step(ids.pin_memory() if use_cuda else ids,
                                            labels.pin_memory() if use_cuda else labels)
             else:
-                loss = engine.train_step(ids, labels)
+                kw = {}
+                if args.packing and "cu_seqlens" in batch and batch["cu_seqlens"].numel() > 2 and cp == 1:
+                    kw["cu_seqlens"] = batch["cu_seqlens"].to(device)     # documents stay apart in full-attention layers
+                loss = engine.train_step(ids, labels, **kw)
         step_timer.tick()
         sched.step()
         if watchdog is not None:

@@ -181,6 +181,23 @@ def test_summary_mix_qkv_blends_after_the_qk_norm_with_each_side_norm():
         assert torch.allclose(first_layer_rows(shared, 0), q0, atol=1e-5)
 
 
+def test_packed_documents_do_not_see_each_other_in_full_attention_layers():
+    """``cu_seqlens``: with every layer a full-attention layer the logits of a document do not depend on the tokens of
+    the documents packed in front of it; without it they do."""
+    cfg = get_preset("qwen3-ksa-tiny").merge({"num_layers": 2, "use_summary_attention": False, "embed_dim": 64,
+                                               "intermediate_dim": 128, "vocab_size": 256, "head_dim": 16})
+    model = get_model_class(cfg.model_class)(cfg)
+    model.init_weights(seed=0)
+    a = torch.randint(0, 256, (1, 96))
+    b = a.clone()
+    b[:, :40] = torch.randint(0, 256, (1, 40))           # another first document
+    cu = torch.tensor([0, 40, 96], dtype=torch.int32)
+    with torch.no_grad():
+        la, lb = model(a, cu_seqlens=cu), model(b, cu_seqlens=cu)
+        assert torch.allclose(la[:, 40:], lb[:, 40:], atol=1e-6)
+        assert not torch.allclose(model(a)[:, 40:], model(b)[:, 40:], atol=1e-4)
+
+
 def test_muse_and_hf_key_roundtrip():
     cfg = get_preset("qwen3-ksa-tiny")
     model = Qwen3SummaryModel(cfg)
