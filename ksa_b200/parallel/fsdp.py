@@ -200,7 +200,7 @@ class FsdpEngine(TrainEngine):
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ev)
             self._signal(self.pad_grads, ui)
-            _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 128)
+            _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 148)   # one CTA per SM: fits beside a GEMM CTA
             self._signal(self.pad_weights, ui)
         self._done_units.add(ui)
 
