@@ -54,6 +54,8 @@ def parse_args():
                     help="multi-GPU back end: fused P2P kernels (default) or NCCL collectives (A/B baseline)")
     ap.add_argument("--overlap", default="stream", choices=["stream", "gemm2"],
                     help="fused back end: communication kernels on a side stream, or as CTAs inside GEMM launches")
+    ap.add_argument("--reshard", action="store_true",
+                    help="ZeRO-3: keep only 1/N of the bf16 weights resident and re-gather units for backward")
     return ap.parse_args()
 
 
@@ -141,7 +143,8 @@ def run_ours(args) -> dict:
 
     if world > 1:
         from ksa_b200.parallel.fsdp import FsdpEngine as Engine
-        extra = dict(world_size=world, rank=rank, comm=args.comm, overlap=args.overlap)
+        extra = dict(world_size=world, rank=rank, comm=args.comm, overlap=args.overlap,
+                     reshard_after_forward=args.reshard)
     else:
         from ksa_b200.training.engine import TrainEngine as Engine
         extra = {}
@@ -235,7 +238,8 @@ def run_ours(args) -> dict:
                    "chunk": cfg.summary_chunk_size, "window_chunks": cfg.summary_sliding_chunk_num, "optimizer": "AdamW fp32 master",
                    "l2": "working set (weights+optimizer state+activations, >30 GB) exceeds L2; no explicit flush",
                    "cuda_graph": use_graph, "comm": getattr(engine, "comm", "none"),
-                   "overlap": getattr(engine, "overlap", "none")},
+                   "overlap": getattr(engine, "overlap", "none"),
+                   "reshard_after_forward": bool(getattr(engine, "reshard", False))},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},

@@ -23,6 +23,15 @@ Two communication back ends behind one engine:
     * Cross-GPU ordering uses per-(unit, rank) flags in symmetric signal pads carrying the step number; every wait
       is bounded and reports through the library's status word.
 
+``reshard_after_forward=True`` (ZeRO-3, fused back end with ``overlap="stream"``)
+    The reference's ``fully_shard(..., reshard_after_forward=True)`` (``muse/training/distributed.py:236-287``).  Every
+    rank keeps only its ``1/world`` shard of each unit's bf16 weights (symmetric memory, written by the reduce + AdamW
+    kernel) plus a small pool of full-size slots: three for decoder layers, one shared by the embedding and the head.
+    A unit is gathered into its slot one unit ahead of the forward pass and, if a later unit has taken the slot
+    since, again one unit ahead of its backward pass (also the recomputation of a checkpointed layer); parameters keep
+    fixed addresses because a unit always lives in the same slot.  Resident bf16 weights drop from the whole model to
+    ``model / world + 3 layers + max(embedding, head)``.
+
 ``comm="collective"`` (any backend, incl. gloo on CPU; the NCCL baseline for A/B runs)
     ``reduce_scatter`` -> AdamW on the shard -> ``all_gather``, per unit, after backward.
 """
@@ -51,20 +60,28 @@ class _Boundary(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gx, gd):
+        ctx.engine._backward_residency(ctx.tag)
         ctx.engine._backward_reached(ctx.tag)
         return None, None, gx, (gd if ctx.has_delta else None)
 
 
 class FsdpEngine(TrainEngine):
     def __init__(self, model: nn.Module, *args, world_size: int = 1, rank: int = 0, group=None, comm: Optional[str] = None,
-                 overlap: str = "stream", pair_gather_min_flops: float = 3e11, **kw):
+                 overlap: str = "stream", pair_gather_min_flops: float = 3e11, reshard_after_forward: bool = False,
+                 **kw):
         self.group = group
+        self.reshard = bool(reshard_after_forward)
         if overlap not in ("stream", "gemm2"):
             raise ValueError(f"overlap must be 'stream' or 'gemm2', not {overlap!r}")
         self.overlap = overlap
         self.pair_gather_min_flops = pair_gather_min_flops    # only a GEMM at least this long carries a gather
         dev = kw.get("device") or next(model.parameters()).device
         self.comm = comm or ("fused" if torch.device(dev).type == "cuda" and world_size > 1 else "collective")
+        if self.reshard and (self.comm != "fused" or overlap != "stream" or world_size < 2):
+            raise ValueError("reshard_after_forward needs the fused back end with overlap='stream' on 2 or more ranks")
+        self._slot_holds = {}          # pool slot -> unit index whose weights it holds
+        self._resident_ev = {}         # unit index -> event of the gather that made it resident
+        self._in_backward = False
         self._symm = []
         super().__init__(model, *args, world_size=world_size, rank=rank, **kw)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -83,11 +100,15 @@ class FsdpEngine(TrainEngine):
             self.comm_stream = torch.cuda.Stream(device=self.device)
             self._gather_done = {}
             self._install_hooks()
+            if self.reshard:
+                self._shards_from_master()
 
     # ------------------------------------------------------------------ storage
     def _allocate_storage(self, units: List[Unit]) -> None:
         if self.comm != "fused":
             return super()._allocate_storage(units)
+        if self.reshard:
+            return self._allocate_resharded(units)
         from .symm import SymmetricBuffer
         item = torch.empty((), dtype=self.param_dtype).element_size()
         total = sum(u.size for u in units)
@@ -102,6 +123,66 @@ class FsdpEngine(TrainEngine):
             u.grad_ptrs = self._sym_grad.offset_ptr_array(off * 4)
             self._alloc_shard_state(u)
             off += u.size
+
+    def _allocate_resharded(self, units: List[Unit]) -> None:
+        """ZeRO-3 storage: persistent bf16 shards (symmetric: the peers pull from them) and a pool of full-size slots."""
+        from .symm import SymmetricBuffer
+        item = torch.empty((), dtype=self.param_dtype).element_size()
+        W = self.world_size
+        total = sum(u.size for u in units)
+        layer_units = [u for u in units if u.name.startswith("layer")]
+        other_units = [u for u in units if not u.name.startswith("layer")]
+        lay = max([u.size for u in layer_units], default=0)
+        big = max([u.size for u in other_units], default=0)
+        self._n_layer_slots = 3
+        self._sym_shards = SymmetricBuffer((total // W) * item, self.group, self.device)
+        self._sym_pool = SymmetricBuffer((big + self._n_layer_slots * lay) * item, self.group, self.device)
+        self._sym_grad = SymmetricBuffer(total * 4, self.group, self.device)
+        self._symm += [self._sym_shards, self._sym_pool, self._sym_grad]
+        off = soff = 0
+        n_layer = 0
+        for u in units:
+            shard = u.size // W
+            if u.name.startswith("layer"):
+                u.slot = 1 + n_layer % self._n_layer_slots
+                slot_off = big + (u.slot - 1) * lay
+                n_layer += 1
+            else:
+                u.slot, slot_off = 0, 0
+            u.compute = self._sym_pool.view(self.param_dtype, slot_off * item, u.size)
+            u.compute_shard = self._sym_shards.view(self.param_dtype, soff * item, shard)
+            u.grad = self._sym_grad.view(torch.float32, off * 4, u.size)
+            u.grad_ptrs = self._sym_grad.offset_ptr_array(off * 4)
+            # the pull kernel copies shard r from ptrs[r] + r * shard_bytes into ptrs[rank] + r * shard_bytes: point
+            # every peer entry at its shard buffer minus r shards, and this rank's entry at the slot
+            slot_ptr = self._sym_pool.local_ptr + slot_off * item
+            u.compute_ptrs = (ctypes.c_void_p * W)(*[
+                slot_ptr if r == self.rank else self._sym_shards.peer_ptrs[r] + (soff - r * shard) * item
+                for r in range(W)])
+            # address that the reduce + AdamW kernel adds shard_lo elements to when it refreshes the bf16 weights
+            u.shard_out_ptr = self._sym_shards.local_ptr + (soff - u.shard_lo) * item
+            self._alloc_shard_state(u)
+            off += u.size
+            soff += shard
+
+    def compute_weight_bytes(self) -> int:
+        """Bytes of compute-dtype weights this rank keeps allocated (full copy, or shards + slot pool when resharding)."""
+        if self.comm != "fused":
+            return sum(u.compute.numel() * u.compute.element_size() for u in self.units)
+        if self.reshard:
+            return self._sym_shards.nbytes + self._sym_pool.nbytes
+        return self._sym_compute.nbytes
+
+    def _shards_from_master(self) -> None:
+        """Resharded storage: the persistent bf16 shards follow the fp32 master weights; every slot is stale."""
+        for u in self.units:
+            u.compute_shard.copy_(u.master)
+        self._slot_holds, self._resident_ev = {}, {}
+
+    def after_weights_loaded(self) -> None:
+        """Called by the loaders after they have written master (and compute) weights."""
+        if self.reshard:
+            self._shards_from_master()
 
     # ------------------------------------------------------------------ hooks
     def _install_hooks(self) -> None:
@@ -118,7 +199,9 @@ class FsdpEngine(TrainEngine):
     def _make_pre_hook(self, ui: int):
         def hook(module, args):
             x, delta = args[0], args[1]
-            if self._overlap_active:
+            if self._overlap_active and self._in_backward:
+                pass    # recomputation of a checkpointed layer: _backward_residency has made the unit resident
+            elif self._overlap_active:
                 nxt = ui + 1
                 if self.overlap == "gemm2":
                     _lib.flush_pair_gather()              # this unit's weights, if no GEMM of the last layer took them
@@ -167,6 +250,10 @@ class FsdpEngine(TrainEngine):
             "min_flops": self.pair_gather_min_flops})
 
     def _gather_on_side_stream(self, ui: int) -> None:
+        if self.reshard:     # the slot's previous tenant has been launched on the main stream: start behind it
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self.comm_stream.wait_event(ev)
         with torch.cuda.stream(self.comm_stream):
             self._gather_now(ui)
             ev = torch.cuda.Event()
@@ -175,14 +262,24 @@ class FsdpEngine(TrainEngine):
 
     def _gather_now(self, ui: int) -> None:
         u = self.units[ui]
+        if self.reshard:
+            if self._slot_holds.get(u.slot) == ui:
+                return
+            self._slot_holds[u.slot] = ui
+            u.compute[u.shard_lo:u.shard_hi].copy_(u.compute_shard)       # own shard: local copy
         _lib.call("ksa_peer_gather", u.compute_ptrs, self.world_size, self.rank, u.size // self.world_size,
                   u.compute.element_size(), self.pad_weights.local_ptr(self._unit_flag_index(ui)), self.epoch, 0, 32)
 
     def _reduce_args(self, u: Unit, ui: int):
         return (u.grad_ptrs, self.world_size, self.rank, u.shard_lo, u.shard_hi - u.shard_lo, u.master, u.exp_avg,
-                u.exp_avg_sq, u.compute if self.param_dtype != torch.float32 else None, self.hyper, self.beta1,
+                u.exp_avg_sq, self._bf16_out(u), self.hyper, self.beta1,
                 self.beta2, self.eps, self.weight_decay, self.clip_value, self.grad_sq,
                 self.pad_grads.local_ptr(self._unit_flag_index(ui)), self.epoch, 1)
+
+    def _bf16_out(self, u: Unit):
+        if self.param_dtype == torch.float32:
+            return None
+        return u.shard_out_ptr if self.reshard else u.compute
 
     def _signal(self, pad, ui: int) -> None:
         pad.set_on_all(self._unit_flag_index(ui) + self.rank, self.epoch, 1)
@@ -203,6 +300,30 @@ class FsdpEngine(TrainEngine):
             _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 148)   # one CTA per SM: fits beside a GEMM CTA
             self._signal(self.pad_weights, ui)
         self._done_units.add(ui)
+
+    def _backward_residency(self, tag) -> None:
+        """Resharded storage: the backward pass of the unit in front of ``tag`` runs next; make its weights resident
+        (a later unit may have taken its slot) and start pulling the one before it."""
+        if not (self.reshard and self._overlap_active):
+            return
+        self._in_backward = True
+        nxt = (tag[1] if isinstance(tag, tuple) else tag) - 1      # unit whose backward pass starts now
+        main = torch.cuda.current_stream(self.device)
+        for ui in (nxt, nxt - 1):
+            if ui < 1 or not self.units[ui].name.startswith("layer"):
+                continue                                            # the embedding's backward pass reads no weights
+            if self._slot_holds.get(self.units[ui].slot) != ui:
+                ev = torch.cuda.Event()
+                ev.record(main)                                     # whoever used the slot before has been launched
+                with torch.cuda.stream(self.comm_stream):
+                    self.comm_stream.wait_event(ev)
+                    self._gather_now(ui)
+                    done = torch.cuda.Event()
+                    done.record(self.comm_stream)
+                self._resident_ev[ui] = done
+        ev = self._resident_ev.pop(nxt, None)
+        if ev is not None:
+            main.wait_event(ev)
 
     def _backward_reached(self, tag) -> None:
         if not self._is_boundary_step:
@@ -231,6 +352,7 @@ class FsdpEngine(TrainEngine):
             self.grad_sq.zero_()
         self._done_units = set()
         self._overlap_active = True
+        self._in_backward = False
         try:
             if self.micro_step == 0:          # refreshed weights of the first two units; later ones are pulled ahead
                 main = torch.cuda.current_stream(self.device)
@@ -272,6 +394,7 @@ class FsdpEngine(TrainEngine):
                     self._unit_grads_ready(ui)
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
             self._flag_epoch += 1
+            self._slot_holds, self._resident_ev = {}, {}      # resharded storage: every slot holds old weights now
             return
         self._collect_autograd_grads()
         self.grad_sq.zero_()
@@ -325,6 +448,8 @@ class FsdpEngine(TrainEngine):
         return super().graphed_step(tokens, labels)
 
     def refresh_compute_from_master(self) -> None:
+        if self.reshard:
+            return self._shards_from_master()
         for u in self.units:
             u.compute[u.shard_lo:u.shard_hi].copy_(u.master)
             if self.world_size > 1:

@@ -234,6 +234,8 @@ def load_engine_state(engine, model_state: Optional[Dict[str, torch.Tensor]],
                 missing.append(s.name)
                 continue
             s.param.data.copy_(fused_f[s.name].view(s.shape))
+    if hasattr(engine, "after_weights_loaded"):
+        engine.after_weights_loaded()
     if strict and missing:
         raise KeyError(f"checkpoint lacks {len(missing)} parameters, e.g. {missing[:4]}")
     return missing

@@ -352,6 +352,8 @@ class TrainEngine:
             for s in self.frozen_slots:
                 if s.name in state:
                     s.param.data.copy_(state[s.name].to(device=self.device, dtype=torch.float32).view(s.shape))
+        if hasattr(self, "after_weights_loaded"):
+            self.after_weights_loaded()
 
 
 class _CapturedStep:

@@ -173,6 +173,9 @@ def train(args) -> dict:
         json.dump(vars(args), open(os.path.join(args.output_dir, f"args-{int(time.time())}.json"), "w"), indent=2)
     # flags of the reference's CLI that mean nothing here: the attention kernels are this package's own, and the
     # next unit's parameters are always gathered one unit ahead
+    if args.cpu_offload:
+        raise SystemExit("--cpu-offload is not supported: master weights and moments are 12 bytes per parameter per rank "
+                         "group and stay in HBM (180 GB per GPU); shard over more ranks or use --reshard-after-forward")
     for flag in ("prefetch_params_in_forward", "use_flash_attention_2"):
         if getattr(args, flag):
             print_rank_0(f"[recipe] --{flag.replace('_', '-')} has no effect in this framework (accepted for compatibility)")
@@ -205,7 +208,8 @@ def train(args) -> dict:
                   clip_value=args.clip_range, lr_lambda=lr_lambda, grad_accum_steps=args.gradient_accumulation_steps)
     if world > 1:
         from ksa_b200.parallel.fsdp import FsdpEngine
-        engine = FsdpEngine(model, world_size=world, rank=rank, comm=args.comm, overlap=args.overlap, **common)
+        engine = FsdpEngine(model, world_size=world, rank=rank, comm=args.comm, overlap=args.overlap,
+                            reshard_after_forward=args.reshard_after_forward, **common)
     else:
         from ksa_b200.training.engine import TrainEngine
         engine = TrainEngine(model, **common)

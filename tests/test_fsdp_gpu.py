@@ -78,6 +78,24 @@ def _worker(rank, world, port, out_q):
             assert abs(gc - gf) < 0.05 * gc, (key, gc, gf)
             for a, b in zip(wc, wf):
                 assert (a - b).norm() <= 1e-2 * a.norm().clamp_min(1e-6), key
+        # --- ZeRO-3 storage (shards + slot pool, units re-gathered for backward) against the resident copy
+        deep = cfg.merge({"num_layers": 6, "summary_layer_freq": [1, 1, 0, 1, 1, 0]})
+        zero3 = {}
+        for reshard in (False, True):
+            torch.manual_seed(0)
+            m = get_model_class(deep.model_class)(deep)
+            m.init_weights(seed=0)
+            eng = FsdpEngine(m.to(dev).to(torch.bfloat16), lr=1e-3, weight_decay=0.1, clip_value=1.0, world_size=world,
+                             rank=rank, comm="fused", overlap="stream", reshard_after_forward=reshard)
+            ls = []
+            for s in range(3):
+                x = data[s, rank].to(dev)
+                ls.append(float(eng.train_step(x[:, :-1].contiguous(), x[:, 1:].contiguous())))
+            torch.cuda.synchronize(); _lib.check_status(); dist.barrier()
+            zero3[reshard] = (ls, torch.cat([u.master.clone() for u in eng.units]), eng.compute_weight_bytes())
+            eng.close()
+        assert all(abs(a - b) < 2e-2 for a, b in zip(zero3[False][0], zero3[True][0])), zero3
+        assert (zero3[False][1] - zero3[True][1]).norm() <= 2e-3 * zero3[False][1].norm()
         # --- resume: 2 steps, state out, a NEW engine (fresh flags, step counter moved forward by the load), step 3
         def fresh():
             torch.manual_seed(0)

@@ -72,7 +72,9 @@ def make_fsdp_kernels(mem, log):
             m.mul_(b1).add_(g, alpha=1 - b1)
             v.mul_(b2).addcmul_(g, g, value=1 - b2)
             master.mul_(1 - lr * wd).sub_(lr * (m / bc1) / ((v / bc2).sqrt() + eps))
-            if out is not None:
+            if isinstance(out, int):      # resharded storage: an address that shard_lo elements (bf16) are added to
+                _raw(mem, out + 2 * shard_lo, 2 * n).view(torch.bfloat16).copy_(master)
+            elif out is not None:
                 out[shard_lo:shard_lo + n].copy_(master)
         else:
             base(name, *a)
@@ -95,10 +97,14 @@ def fake_fsdp_gpu(monkeypatch):
     yield
 
 
-@pytest.mark.parametrize("world,overlap", [(2, "stream"), (2, "gemm2"), (4, "stream"), (4, "gemm2"), (8, "stream")])
-def test_fused_fsdp_matches_single_process_training(fake_fsdp_gpu, monkeypatch, world, overlap):
+@pytest.mark.parametrize("world,overlap,reshard", [(2, "stream", False), (2, "gemm2", False), (4, "stream", False),
+                                                   (4, "gemm2", False), (8, "stream", False), (2, "stream", True),
+                                                   (4, "stream", True)])
+def test_fused_fsdp_matches_single_process_training(fake_fsdp_gpu, monkeypatch, world, overlap, reshard):
+    """``reshard``: ZeRO-3 storage (bf16 shards + a pool of slots that units share); six layers so that every layer slot
+    gets a second and a third tenant in forward and has to be refilled in backward."""
     steps = 3
-    cfg = _tiny()
+    cfg = _tiny() if not reshard else _tiny().merge({"num_layers": 6, "summary_layer_freq": [1, 1, 0, 1, 1, 0]})
     torch.manual_seed(0)
     base = get_model_class(cfg.model_class)(cfg)
     base.init_weights(seed=0)
@@ -114,7 +120,13 @@ def test_fused_fsdp_matches_single_process_training(fake_fsdp_gpu, monkeypatch, 
         model = copy.deepcopy(base)
         eng = FsdpEngine(model, lr=1e-2, weight_decay=0.1, clip_value=1.0, world_size=world, rank=rank, group=group,
                          comm="fused", overlap=overlap, param_dtype=torch.bfloat16, device="cpu",
-                         pair_gather_min_flops=0.0)
+                         pair_gather_min_flops=0.0, reshard_after_forward=reshard)
+        if reshard:
+            # bf16 weights held: 1/world of the model + three layer slots + one slot for the embedding / head
+            lay = max(u.size for u in eng.units if u.name.startswith("layer"))
+            big = max(u.size for u in eng.units if not u.name.startswith("layer"))
+            want = sum(u.size for u in eng.units) // world * 2 + (big + 3 * lay) * 2
+            assert want <= eng.compute_weight_bytes() <= want + 512, (eng.compute_weight_bytes(), want)
         losses = []
         for s in range(steps):
             t = data[s, rank]
@@ -122,11 +134,12 @@ def test_fused_fsdp_matches_single_process_training(fake_fsdp_gpu, monkeypatch, 
         group.shared["barrier"].wait()
         eng._write_hyper()                   # pull the last update of every unit, as the next forward would
         eng._overlap_active = False
-        for ui in range(len(eng.units)):
+        final = {}
+        for ui in range(len(eng.units)):     # unit by unit: with resharded storage several units share a slot
             eng._gather_now(ui)
+            final.update({s.name: s.param.detach().float().clone() for s in eng.units[ui].slots})
         group.shared["barrier"].wait()
-        results[rank] = (losses, {n: p.detach().float().clone() for n, p in model.named_parameters()},
-                         float(eng.grad_sq))
+        results[rank] = (losses, final, float(eng.grad_sq))
         eng.close()
 
     _run_ranks(world, body)
