@@ -28,6 +28,7 @@
 // enumeration is closed-form (attn_common.cuh) instead of block lists.
 #include "attn_common.cuh"
 #include "host.h"
+#include <string.h>
 
 namespace ksa {
 
@@ -166,11 +167,23 @@ __device__ __forceinline__ void store_row_bf16_128(uint32_t taddr, bf16* dst, bo
   }
 }
 
-__global__ void __launch_bounds__(kFbThreads, 1)
-attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
-                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                      const __grid_constant__ CUtensorMap tmKs, const __grid_constant__ CUtensorMap tmVs,
-                      const __grid_constant__ CUtensorMap tmDq, FbParams p) {
+// Context-parallel shard: where the key tiles come from (attn_common.cuh) and where the gradients of keys that
+// other ranks own go: fp32 return blocks in the owners' memory, [B, rows, 2*Hkv*128] with K in the first Hkv*128
+// columns, added to with reductions over NVLink; the owner folds them into its own dK / dV afterwards.
+struct CpBwdSources {
+  CpSources src;
+  int n_sum_src;                  // summary sources; the last one is this rank's own
+  float* ret_text;                // return block of the halo's owner (its last `halo` text rows)
+  float* ret_sum[kCpMaxSum];      // return blocks of the owners of the older summaries
+  long long ret_rs, ret_text_bs, ret_sum_bs;   // row stride and batch strides, elements
+};
+
+template <bool kCp>
+__device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, const CUtensorMap& tmdO,
+                                                    const CUtensorMap& tmK, const CUtensorMap& tmV,
+                                                    const CUtensorMap& tmKs, const CUtensorMap& tmVs,
+                                                    const CUtensorMap& tmDq, const FbParams& p,
+                                                    const CpBwdSources* cp) {
   using S = FbSmem;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
@@ -216,6 +229,14 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int total = n_q * G;          // steps; 2 * total half steps
   const int n_half = 2 * total;
   const bool atomic_out = is_sum && n_seg > 1;
+  // context parallel: source of this key tile, its first row there, and whether another rank owns it
+  int cp_src = 0, cp_row = kt * 128;
+  bool remote = false;
+  if (kCp) {
+    cp_src = is_sum ? (kt * 128) / cp->src.nsl : (kt * 128 < cp->src.halo ? 0 : 1);
+    cp_row = is_sum ? (kt * 128) % cp->src.nsl : (cp_src == 0 ? kt * 128 : kt * 128 - cp->src.halo);
+    remote = is_sum ? cp_src < cp->n_sum_src - 1 : cp_src == 0;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -241,13 +262,25 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && total > 0) {
+      const CUtensorMap* mk = is_sum ? &tmKs : &tmK;
+      const CUtensorMap* mv = is_sum ? &tmVs : &tmV;
+      bool src_ok = true;
+      if (kCp) {
+        mk = is_sum ? &cp->src.ks[cp_src] : &cp->src.kt[cp_src];
+        mv = is_sum ? &cp->src.vs[cp_src] : &cp->src.vt[cp_src];
+        const uint32_t* flag = is_sum ? cp->src.sum_flag[cp_src] : cp->src.text_flag[cp_src];
+        if (flag != nullptr && !flag_wait_ge(flag, cp->src.flag_target, p.status, kTimeoutPeerFlag, true)) {
+          *abort_flag = 1;
+          src_ok = false;
+        }
+      }
       mbar_expect_tx(kv_full, 2 * S::kTile);
-      for (int hh = 0; hh < 2; ++hh) {
-        tma_load_4d(sK + hh * 16384, is_sum ? &tmKs : &tmK, hh * 64, kt * 128, kv_head, b, kv_full);
-        tma_load_4d(sV + hh * 16384, is_sum ? &tmVs : &tmV, hh * 64, kt * 128, kv_head, b, kv_full);
+      for (int hh = 0; hh < 2 && src_ok; ++hh) {
+        tma_load_4d(sK + hh * 16384, mk, hh * 64, cp_row, kv_head, b, kv_full);
+        tma_load_4d(sV + hh * 16384, mv, hh * 64, cp_row, kv_head, b, kv_full);
       }
       const long long plane = (long long)sh.B * sh.Hq * p.lq_pad;
-      for (int n = 0; n < n_half; ++n) {
+      for (int n = 0; n < n_half && src_ok; ++n) {
         const int stage = n % kFbStages;
         if (!mbar_wait(&st_empty[stage], ((n / kFbStages) & 1) ^ 1, guard, kTimeoutStageEmpty)) break;
         const int i = n >> 1, h = n & 1;
@@ -433,7 +466,28 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const bool do_k = half == 1;
     const float mul = do_k ? p.scale : 1.f;
     const uint32_t t_acc = (do_k ? tdK : tdV) + lane_addr;
-    if (atomic_out) {
+    if (kCp && remote) {
+      // keys of another rank: add this shard's contribution into the owner's fp32 return block over NVLink
+      if (total > 0) {
+        if (ok) ok = mbar_wait(acc_full, 0, guard, kTimeoutAccFull);
+        if (ok) {
+          tc_fence_after();
+          float* blk = is_sum ? cp->ret_sum[cp_src] : cp->ret_text;
+          const long long bs = is_sum ? cp->ret_sum_bs : cp->ret_text_bs;
+          float* base = blk + (long long)b * bs + (long long)(cp_row + r) * cp->ret_rs + (do_k ? 0 : sh.Hkv * 128) + kv_head * 128;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(t_acc + c * 32, o);
+            tmem_wait_ld();
+            if (valid) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) atomicAdd(base + c * 32 + i, __uint_as_float(o[i]) * mul);
+            }
+          }
+        }
+      }
+    } else if (atomic_out) {
       if (total > 0) {
         if (ok) ok = mbar_wait(acc_full, 0, guard, kTimeoutAccFull);
         if (ok) {
@@ -478,6 +532,20 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   tc_fence_before();
   __syncthreads();
   if (warp == 2) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+__global__ void __launch_bounds__(kFbThreads, 1)
+attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                      const __grid_constant__ CUtensorMap tmKs, const __grid_constant__ CUtensorMap tmVs,
+                      const __grid_constant__ CUtensorMap tmDq, FbParams p) {
+  attn_bwd_fused_body<false>(tmQ, tmdO, tmK, tmV, tmKs, tmVs, tmDq, p, nullptr);
+}
+
+__global__ void __launch_bounds__(kFbThreads, 1)
+attn_bwd_fused_cp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                         const __grid_constant__ CUtensorMap tmDq, const __grid_constant__ CpBwdSources cp, FbParams p) {
+  attn_bwd_fused_body<true>(tmQ, tmdO, cp.src.kt[1], cp.src.vt[1], cp.src.ks[0], cp.src.vs[0], tmDq, p, &cp);
 }
 
 // Preparation: one warp per (batch, head, query row of the padded length).  Writes -LSE*log2e and
@@ -625,6 +693,116 @@ KSA_API int ksa_attn_bwd_fused(const void* q, const void* k, const void* v, cons
   }
   dim3 grid((Lk + 127) / 128 + ((Ns + 127) / 128) * p.n_seg, Hkv, B);
   attn_bwd_fused_kernel<<<grid, kFbThreads, FbSmem::kTotal, st>>>(tq, tdo, tk, tv, tks, tvs, tdq, p);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  {
+    const long long n = (long long)B * Lq * Hq * 16;
+    const int threads = 256;
+    attn_bwd_dq_convert_kernel<<<(unsigned)((n + threads - 1) / threads), threads, 0, st>>>(
+        (const float*)dq32, (bf16*)dq, dq_rs, dq_bs, B, Lq, Hq, scale);
+    KSA_CHECK_CUDA(cudaGetLastError());
+  }
+  return 0;
+}
+
+// Backward of ksa_attn_fwd_cp: the fused key-stationary kernel on one shard of a context-parallel group.  Key tiles
+// are read where they are (sources as in ksa_attn_fwd_cp).  dK / dV of this rank's own rows go to `dk` / `dv`
+// ([B, local_rows, Hkv, 128]) and `dks` / `dvs` ([B, nsl, Hkv, 128]); dK / dV of the halo and of older summaries are
+// ADDED, in fp32, into the owners' return blocks over NVLink (`ret_text`: [B, halo, 2*Hkv*128] of the previous rank,
+// `ret_sum[s]`: [B, nsl, 2*Hkv*128] of rank s; row stride `ret_rs`), which the owners fold into their gradients
+// (ksa_cp_fold_return).  `dks32` / `dvs32`: fp32 partial sums [B, n_sum_src*nsl, Hkv, 128] for this rank's own summary
+// tiles when their query range is split (as in ksa_attn_bwd_fused), zeroed by the caller.
+KSA_API int ksa_attn_bwd_fused_cp(const void* q, const void* o, const void* d_o, const void* lse, void* stats,
+                                  void* dq32, void* dq, void* dk, void* dv, void* dks, void* dvs, int B, int Hq, int Hkv,
+                                  int HD, int Lq, long long q_rs, long long q_bs, long long o_rs, long long o_bs,
+                                  long long dq_rs, long long dq_bs, long long dk_rs, long long dk_bs, long long dv_rs,
+                                  long long dv_bs, long long dks_rs, long long dks_bs, long long dvs_rs, long long dvs_bs,
+                                  const void* const* text_src, int halo, int local_rows, const void* const* sum_src,
+                                  int n_sum_src, int nsl, long long src_rs, long long text_bs, long long sum_bs,
+                                  const void* const* text_flags, const void* const* sum_flags, unsigned flag_target,
+                                  void* ret_text, void* const* ret_sum, long long ret_rs, long long ret_text_bs,
+                                  long long ret_sum_bs, int q_off, int k_off, int chunk, int n_sum, int window,
+                                  int tok_window, float scale, void* dks32, void* dvs32, void* stream) {
+  KSA_ENTER(q);
+  using namespace ksa;
+  KSA_REQUIRE(HD == 128, "attn_bwd_fused_cp: head_dim %d unsupported (128 only)", HD);
+  KSA_REQUIRE(Hq % Hkv == 0 && chunk > 0, "attn_bwd_fused_cp: bad head counts / chunk");
+  KSA_REQUIRE(halo >= 0 && halo % 128 == 0, "attn_bwd_fused_cp: halo %d must be a multiple of 128", halo);
+  KSA_REQUIRE(n_sum_src >= 0 && n_sum_src <= kCpMaxSum, "attn_bwd_fused_cp: %d summary sources (max %d)", n_sum_src, kCpMaxSum);
+  KSA_REQUIRE(n_sum_src <= 1 || nsl % 128 == 0, "attn_bwd_fused_cp: %d summary rows per rank must be a multiple of 128", nsl);
+  KSA_REQUIRE(o_rs % 8 == 0 && dq_rs % 8 == 0 && dk_rs % 8 == 0 && dv_rs % 8 == 0, "attn_bwd_fused_cp: row strides must be multiples of 8");
+  KSA_REQUIRE(stats != nullptr && dq32 != nullptr, "attn_bwd_fused_cp: the stats and dq32 workspaces are required");
+  KSA_REQUIRE(halo == 0 || ret_text != nullptr, "attn_bwd_fused_cp: a halo needs the return block of its owner");
+  if (B == 0 || Lq == 0) return 0;
+  const int lq_pad = ksa_attn_bwd_fused_lq_pad(Lq);
+  const int Ns = n_sum_src * nsl;
+  CUtensorMap tq, tdo, tdq;
+  CpBwdSources cp;
+  memset(&cp, 0, sizeof(cp));
+  int rc;
+  if ((rc = make_head_tmap_rows(&tq, q, Lq, Hq, B, q_rs, q_bs, 64))) return rc;
+  if ((rc = make_head_tmap_rows(&tdo, d_o, Lq, Hq, B, o_rs, o_bs, 64))) return rc;
+  const long long voff = (long long)Hkv * 128;
+  for (int s = 0; s < 2; ++s) {
+    const int rows = s == 0 ? halo : local_rows;
+    const bf16* base = static_cast<const bf16*>(text_src[rows > 0 ? s : 1]);
+    if ((rc = make_head_tmap_rows(&cp.src.kt[s], base, rows > 0 ? rows : 1, Hkv, B, src_rs, text_bs, 128))) return rc;
+    if ((rc = make_head_tmap_rows(&cp.src.vt[s], base + voff, rows > 0 ? rows : 1, Hkv, B, src_rs, text_bs, 128))) return rc;
+    cp.src.text_flag[s] = text_flags ? static_cast<const uint32_t*>(text_flags[s]) : nullptr;
+  }
+  for (int s = 0; s < kCpMaxSum; ++s) {
+    const int src = s < n_sum_src ? s : (n_sum_src > 0 ? n_sum_src - 1 : -1);
+    const bf16* base = src >= 0 ? static_cast<const bf16*>(sum_src[src]) : static_cast<const bf16*>(text_src[1]);
+    if ((rc = make_head_tmap_rows(&cp.src.ks[s], base, nsl > 0 ? nsl : 1, Hkv, B, src_rs, sum_bs, 128))) return rc;
+    if ((rc = make_head_tmap_rows(&cp.src.vs[s], base + voff, nsl > 0 ? nsl : 1, Hkv, B, src_rs, sum_bs, 128))) return rc;
+    cp.src.sum_flag[s] = (sum_flags && s < n_sum_src) ? static_cast<const uint32_t*>(sum_flags[s]) : nullptr;
+    cp.ret_sum[s] = (ret_sum && s < n_sum_src - 1) ? static_cast<float*>(ret_sum[s]) : nullptr;
+    KSA_REQUIRE(s >= n_sum_src - 1 || cp.ret_sum[s] != nullptr, "attn_bwd_fused_cp: summary source %d has no return block", s);
+  }
+  cp.src.flag_target = flag_target;
+  cp.src.halo = halo;
+  cp.src.nsl = nsl > 0 ? nsl : 128;
+  cp.n_sum_src = n_sum_src;
+  cp.ret_text = static_cast<float*>(ret_text);
+  cp.ret_rs = ret_rs; cp.ret_text_bs = ret_text_bs; cp.ret_sum_bs = ret_sum_bs;
+  FbParams p;
+  p.s = AttnShape{B, Hq, Hkv, Lq, halo + local_rows, Ns, q_off, k_off, 0, chunk, n_sum > 0 ? n_sum : 1, window, tok_window,
+                  nullptr, nullptr};
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.stats = (const float*)stats;
+  p.lq_pad = lq_pad;
+  p.dq32 = (float*)dq32;
+  // the kernel addresses key rows by their index in [halo | own rows] and [older summaries | own summaries]
+  p.dk = (bf16*)dk - (long long)halo * dk_rs; p.dv = (bf16*)dv - (long long)halo * dv_rs;
+  p.dk_row_stride = dk_rs; p.dk_batch_stride = dk_bs; p.dv_row_stride = dv_rs; p.dv_batch_stride = dv_bs;
+  const long long own_sum0 = (long long)(n_sum_src > 0 ? n_sum_src - 1 : 0) * nsl;
+  p.dks = dks ? (bf16*)dks - own_sum0 * dks_rs : nullptr; p.dvs = dvs ? (bf16*)dvs - own_sum0 * dvs_rs : nullptr;
+  p.dks_row_stride = dks_rs; p.dks_batch_stride = dks_bs; p.dvs_row_stride = dvs_rs; p.dvs_batch_stride = dvs_bs;
+  p.dks32 = (float*)dks32; p.dvs32 = (float*)dvs32;
+  p.n_seg = (Ns > 0 && dks32 != nullptr && dvs32 != nullptr) ? (((Lq + 127) / 128 + kFbSumSeg - 1) / kFbSumSeg) : 1;
+  p.status = status_word();
+  KSA_REQUIRE(p.status != nullptr, "could not allocate the status word");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  static bool attr = false;
+  if (!attr) {
+    KSA_CHECK_CUDA(cudaFuncSetAttribute(attn_bwd_fused_cp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FbSmem::kTotal));
+    attr = true;
+  }
+  {
+    const long long warps = (long long)B * Hq * lq_pad;
+    const int threads = 256;
+    attn_bwd_prep_kernel<<<(unsigned)((warps * 32 + threads - 1) / threads), threads, 0, st>>>(
+        (const bf16*)o, (const bf16*)d_o, o_rs, o_bs, (const float*)lse, (float*)stats, (float*)dq32, B, Hq, Lq, lq_pad);
+    KSA_CHECK_CUDA(cudaGetLastError());
+  }
+  {
+    uint64_t dims[4] = {128, (uint64_t)Hq, (uint64_t)Lq, (uint64_t)B};
+    uint64_t str[4] = {4, 512, (uint64_t)Hq * 512, (uint64_t)Lq * Hq * 512};
+    uint32_t box[4] = {128, 1, 32, 1};
+    if ((rc = make_tmap(&tdq, dq32, 4, 4, dims, str, box, false))) return rc;
+  }
+  dim3 grid((halo + local_rows + 127) / 128 + ((Ns + 127) / 128) * p.n_seg, Hkv, B);
+  attn_bwd_fused_cp_kernel<<<grid, kFbThreads, FbSmem::kTotal, st>>>(tq, tdo, tdq, cp, p);
   KSA_CHECK_CUDA(cudaGetLastError());
   {
     const long long n = (long long)B * Lq * Hq * 16;

@@ -110,4 +110,21 @@ __device__ __forceinline__ QueryRange query_tiles_for_summary_key_tile(const Att
   return r;
 }
 
+// Key / value sources of a context-parallel shard: the tiles of the halo (the last text keys of the previous rank)
+// and of older chunks' summaries are read by TMA straight from the owners' exchange slots, which are mapped into this
+// process (peer memory; plain TMA loads, no multicast), while this rank's own tiles come from its own slot.
+//   text tile kt : kt * 128 < halo ? (source 0, row kt*128) : (source 1, row kt*128 - halo)
+//   summary tile j : source (j*128) / nsl, row (j*128) % nsl          (nsl is a multiple of 128 or the only source)
+// flags[s] (null for this rank's own slot): a flag in THIS rank's memory that the owner of source s raises to
+// `flag_target` once its keys and values are in its slot; the producer waits for it (bounded) before the first load.
+constexpr int kCpMaxSum = 8;
+struct CpSources {
+  CUtensorMap kt[2], vt[2];
+  CUtensorMap ks[kCpMaxSum], vs[kCpMaxSum];
+  const uint32_t* text_flag[2];
+  const uint32_t* sum_flag[kCpMaxSum];
+  uint32_t flag_target;
+  int halo, nsl;
+};
+
 }  // namespace ksa

@@ -21,6 +21,7 @@
 // summary_attn wheel).
 #include "attn_common.cuh"
 #include "host.h"
+#include <string.h>
 
 namespace ksa {
 
@@ -53,11 +54,10 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, in
   for (int half = 0; half < HD / 64; ++half) tma_load_4d(dst + half * 16384, m, half * 64, row0, h, b, bar);
 }
 
-template <int HD>
-__global__ void __launch_bounds__(kFwdThreads, 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKs,
-                const __grid_constant__ CUtensorMap tmVs, FwdParams p) {
+template <int HD, bool kCp>
+__device__ __forceinline__ void attn_fwd_body(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                                              const CUtensorMap& tmKs, const CUtensorMap& tmVs, const FwdParams& p,
+                                              const CpSources* cps) {
   using S = FwdSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -106,16 +106,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int t = 0; t < heads_per_cta; ++t) load_tile<HD>(sQ + t * S::kTile, &tmQ, q_tile * 128, head0 + t, b, q_full);
       int n = 0;
       bool ok = true;
+      uint32_t waited = 0;     // context parallel: sources whose flag has been seen (bit s: text, bit 2 + s: summary)
       for (int j = 0; j < total && ok; ++j) {
         const bool is_sum = j < tr.n_sum_tiles;
         const int kt = is_sum ? j : tr.text_first + (j - tr.n_sum_tiles);
+        const CUtensorMap* mk = is_sum ? &tmKs : &tmK;
+        const CUtensorMap* mv = is_sum ? &tmVs : &tmV;
+        int row = kt * 128;
+        if (kCp) {
+          const int src = is_sum ? (kt * 128) / cps->nsl : (kt * 128 < cps->halo ? 0 : 1);
+          row = is_sum ? (kt * 128) % cps->nsl : (src == 0 ? kt * 128 : kt * 128 - cps->halo);
+          mk = is_sum ? &cps->ks[src] : &cps->kt[src];
+          mv = is_sum ? &cps->vs[src] : &cps->vt[src];
+          const uint32_t bit = 1u << (is_sum ? 2 + src : src);
+          const uint32_t* flag = is_sum ? cps->sum_flag[src] : cps->text_flag[src];
+          if (flag != nullptr && !(waited & bit)) {
+            if (!flag_wait_ge(flag, cps->flag_target, p.status, kTimeoutPeerFlag, true)) { *abort_flag = 1; ok = false; break; }
+            waited |= bit;
+          }
+        }
         for (int kv = 0; kv < 2; ++kv, ++n) {
           const int stage = n % kKvStages;
           const uint32_t phase = (n / kKvStages) & 1;
           if (!mbar_wait(&kv_empty[stage], phase ^ 1, guard, kTimeoutStageEmpty)) { ok = false; break; }
           mbar_expect_tx(&kv_full[stage], S::kTile);
-          const CUtensorMap* m = kv == 0 ? (is_sum ? &tmKs : &tmK) : (is_sum ? &tmVs : &tmV);
-          load_tile<HD>(sKV + stage * S::kTile, m, kt * 128, kv_head, b, &kv_full[stage]);
+          load_tile<HD>(sKV + stage * S::kTile, kv == 0 ? mk : mv, row, kv_head, b, &kv_full[stage]);
         }
       }
     }
@@ -293,6 +308,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+template <int HD>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKs,
+                const __grid_constant__ CUtensorMap tmVs, FwdParams p) {
+  attn_fwd_body<HD, false>(tmQ, tmK, tmV, tmKs, tmVs, p, nullptr);
+}
+
+// The same kernel for one shard of a context-parallel group: keys and values come from the sources in `cps`.
+template <int HD>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_cp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CpSources cps, FwdParams p) {
+  attn_fwd_body<HD, true>(tmQ, cps.kt[1], cps.vt[1], cps.ks[0], cps.vs[0], p, &cps);
+}
+
 // [B, T, H, HD] view -> 4-D tensor map {HD, T, H, B}, box {64, 128, 1, 1}, 128-byte swizzle.
 static int make_head_tmap(CUtensorMap* m, const void* base, int HD, long long T, int H, int B, long long row_stride,
                           long long batch_stride) {
@@ -317,7 +347,83 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   return 0;
 }
 
+template <int HD>
+static int launch_fwd_cp(const CUtensorMap& tq, const CpSources& cps, const FwdParams& p, cudaStream_t st) {
+  auto kern = attn_fwd_cp_kernel<HD>;
+  static bool attr = false;
+  if (!attr) {
+    KSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<HD>::kTotal));
+    attr = true;
+  }
+  dim3 grid((p.s.Lq + 127) / 128, p.s.Hq / p.nslot, p.s.B);
+  kern<<<grid, kFwdThreads, FwdSmem<HD>::kTotal, st>>>(tq, cps, p);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 }  // namespace ksa
+
+// Text-query attention forward of ONE SHARD of a context-parallel group, reading keys and values where they are.
+// q, o, lse: this rank's queries and outputs as in ksa_attn_fwd.  Keys / values: `text_src[0]` = first halo row in the
+// previous rank's exchange slot (ignored when halo = 0), `text_src[1]` = this rank's own text rows, `sum_src[s]` =
+// the summary rows of rank s (s < n_sum_src - 1: peers; the last one: this rank); every source is a [B, rows, 2*Hkv*HD]
+// block, K in the first Hkv*HD columns and V in the rest, row stride `src_rs`, batch strides `text_bs` / `sum_bs`
+// (elements).  `halo` and `nsl` (summary rows per rank) must be multiples of 128 unless there is no halo / a single
+// summary source.  `text_flags[s]` / `sum_flags[s]`: address of a flag in this rank's memory that the owner of the
+// source raises to `flag_target` when its slot is filled, or null for sources that need no wait.
+// Peer memory is only ever read with TMA loads issued by this kernel's own CTAs (no multicast).
+KSA_API int ksa_attn_fwd_cp(const void* q, void* o, void* lse, int B, int Hq, int Hkv, int HD, int Lq, long long q_rs,
+                            long long q_bs, long long o_rs, long long o_bs, const void* const* text_src, int halo,
+                            int local_rows, const void* const* sum_src, int n_sum_src, int nsl, long long src_rs,
+                            long long text_bs, long long sum_bs, const void* const* text_flags,
+                            const void* const* sum_flags, unsigned flag_target, int q_off, int k_off, int chunk,
+                            int n_sum, int window, int tok_window, float scale, void* stream) {
+  KSA_ENTER(q);
+  using namespace ksa;
+  KSA_REQUIRE(HD == 128 || HD == 64, "attn_fwd_cp: head_dim %d unsupported (64 or 128)", HD);
+  KSA_REQUIRE(Hq % Hkv == 0 && chunk > 0, "attn_fwd_cp: bad head counts / chunk");
+  KSA_REQUIRE(halo >= 0 && halo % 128 == 0, "attn_fwd_cp: halo %d must be a multiple of 128", halo);
+  KSA_REQUIRE(n_sum_src >= 0 && n_sum_src <= kCpMaxSum, "attn_fwd_cp: %d summary sources (max %d)", n_sum_src, kCpMaxSum);
+  KSA_REQUIRE(n_sum_src <= 1 || nsl % 128 == 0, "attn_fwd_cp: %d summary rows per rank must be a multiple of 128", nsl);
+  KSA_REQUIRE(o_rs % 8 == 0, "attn_fwd_cp: output row stride must be a multiple of 8");
+  if (B == 0 || Lq == 0) return 0;
+  CUtensorMap tq;
+  CpSources cps;
+  memset(&cps, 0, sizeof(cps));
+  int rc;
+  if ((rc = make_head_tmap(&tq, q, HD, Lq, Hq, B, q_rs, q_bs))) return rc;
+  const long long voff = (long long)Hkv * HD;
+  for (int s = 0; s < 2; ++s) {
+    const int rows = s == 0 ? halo : local_rows;
+    const bf16* base = static_cast<const bf16*>(text_src[rows > 0 ? s : 1]);
+    if ((rc = make_head_tmap(&cps.kt[s], base, HD, rows > 0 ? rows : 1, Hkv, B, src_rs, text_bs))) return rc;
+    if ((rc = make_head_tmap(&cps.vt[s], base + voff, HD, rows > 0 ? rows : 1, Hkv, B, src_rs, text_bs))) return rc;
+    cps.text_flag[s] = text_flags ? static_cast<const uint32_t*>(text_flags[s]) : nullptr;
+  }
+  for (int s = 0; s < kCpMaxSum; ++s) {
+    const int src = s < n_sum_src ? s : (n_sum_src > 0 ? n_sum_src - 1 : -1);
+    const bf16* base = src >= 0 ? static_cast<const bf16*>(sum_src[src]) : static_cast<const bf16*>(text_src[1]);
+    if ((rc = make_head_tmap(&cps.ks[s], base, HD, nsl > 0 ? nsl : 1, Hkv, B, src_rs, sum_bs))) return rc;
+    if ((rc = make_head_tmap(&cps.vs[s], base + voff, HD, nsl > 0 ? nsl : 1, Hkv, B, src_rs, sum_bs))) return rc;
+    cps.sum_flag[s] = (sum_flags && s < n_sum_src) ? static_cast<const uint32_t*>(sum_flags[s]) : nullptr;
+  }
+  cps.flag_target = flag_target;
+  cps.halo = halo;
+  cps.nsl = nsl > 0 ? nsl : 128;
+  FwdParams p;
+  p.s = AttnShape{B, Hq, Hkv, Lq, halo + local_rows, n_sum_src * nsl, q_off, k_off, 0, chunk, n_sum > 0 ? n_sum : 1,
+                  window, tok_window, nullptr, nullptr};
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.o = (bf16*)o;
+  p.o_row_stride = o_rs;
+  p.o_batch_stride = o_bs;
+  p.lse = (float*)lse;
+  p.nslot = ((Hq / Hkv) % 2 == 0) ? 2 : 1;
+  p.status = status_word();
+  KSA_REQUIRE(p.status != nullptr, "could not allocate the status word");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return HD == 128 ? launch_fwd_cp<128>(tq, cps, p, st) : launch_fwd_cp<64>(tq, cps, p, st);
+}
 
 // Text-query attention forward.  All tensors are bf16 with the head dimension contiguous:
 //   q  [B, Lq, Hq, HD]   (row stride q_rs elements, batch stride q_bs)

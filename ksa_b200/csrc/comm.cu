@@ -208,6 +208,53 @@ KSA_API int ksa_peer_reduce_adamw(const void* const* grads, int world, int rank,
   return 0;
 }
 
+// Context parallelism: fold what the later ranks added into this rank's fp32 return block into its bf16 gradients,
+// and clear the block for its next use.  dst [B, rows, width] bf16 (row / batch strides in elements), ret the same
+// shape in fp32.  flags (optional): n_flags flags in own memory that the contributing ranks raise to `target` when
+// their backward kernels are done; the wait is bounded.
+__global__ void __launch_bounds__(256) cp_fold_return_kernel(bf16* dst, float* ret, int B, int rows, int width,
+                                                             long long dst_rs, long long dst_bs, long long ret_rs,
+                                                             long long ret_bs, const uint32_t* flags, int n_flags,
+                                                             uint32_t target, int* status) {
+  __shared__ int s_ok;
+  if (flags != nullptr && n_flags > 0) {
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if ((int)threadIdx.x < n_flags && !flag_wait_ge(flags + threadIdx.x, target, status, kTimeoutPeerFlag, true)) s_ok = 0;
+    __syncthreads();
+    if (!s_ok) return;
+  }
+  const long long vec_per_row = width / 4;
+  const long long total = (long long)B * rows * vec_per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long c = i % vec_per_row, rw = (i / vec_per_row) % rows, b = i / (vec_per_row * rows);
+    float4* src = reinterpret_cast<float4*>(ret + b * ret_bs + rw * ret_rs + c * 4);
+    uint2* d = reinterpret_cast<uint2*>(dst + b * dst_bs + rw * dst_rs + c * 4);
+    const float4 a = *src;
+    const uint2 old = *d;
+    const float2 lo = unpack_bf16x2(old.x), hi = unpack_bf16x2(old.y);
+    *d = make_uint2(pack_bf16x2(lo.x + a.x, lo.y + a.y), pack_bf16x2(hi.x + a.z, hi.y + a.w));
+    *src = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+KSA_API int ksa_cp_fold_return(void* dst, void* ret, int B, int rows, int width, long long dst_rs, long long dst_bs,
+                               long long ret_rs, long long ret_bs, const void* flags, int n_flags, unsigned target,
+                               void* stream) {
+  KSA_ENTER(dst);
+  KSA_REQUIRE(width % 4 == 0 && dst_rs % 4 == 0 && ret_rs % 4 == 0, "cp_fold_return: width and strides must be multiples of 4");
+  KSA_REQUIRE(n_flags >= 0 && n_flags <= 256, "cp_fold_return: %d flags", n_flags);
+  if (B == 0 || rows == 0) return 0;
+  int* status = status_word();
+  KSA_REQUIRE(status != nullptr, "could not allocate the status word");
+  const long long total = (long long)B * rows * (width / 4);
+  const int blocks = (int)((total + 255) / 256 < 592 ? (total + 255) / 256 : 592);
+  cp_fold_return_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (bf16*)dst, (float*)ret, B, rows, width, dst_rs, dst_bs, ret_rs, ret_bs, (const uint32_t*)flags, n_flags, target, status);
+  KSA_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 // Store *epoch_ptr + epoch_add (release, system scope) to n flag addresses (own and peer memory), after all prior work of the stream.
 KSA_API int ksa_signal_set(const void* const* flag_ptrs, int n, const void* epoch_ptr, unsigned epoch_add, void* stream) {
   KSA_REQUIRE(n >= 1 && n <= kMaxPeers, "signal_set: n %d out of range", n);

@@ -42,6 +42,10 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_attn_fwd": [P] * 7 + [I] * 7 + [L] * 12 + [I] * 7 + [F, P, P, P],
     "ksa_attn_bwd": [P] * 14 + [I] * 7 + [L] * 22 + [I] * 7 + [F, P, P, P, P, P],
     "ksa_attn_bwd_fused": [P] * 15 + [I] * 7 + [L] * 22 + [I] * 7 + [F, P, P, P, P, P],
+    "ksa_attn_fwd_cp": [P, P, P, I, I, I, I, I, L, L, L, L, P, I, I, P, I, I, L, L, L, P, P, ctypes.c_uint, I, I, I, I, I, I, F, P],
+    "ksa_attn_bwd_fused_cp": [P] * 11 + [I] * 5 + [L] * 14 + [P, I, I, P, I, I, L, L, L, P, P, ctypes.c_uint, P, P, L, L, L,
+                                                              I, I, I, I, I, I, F, P, P, P],
+    "ksa_cp_fold_return": [P, P, I, I, I, L, L, L, L, P, I, ctypes.c_uint, P],
     "ksa_summary_attn_fwd": [P] * 7 + [I] * 6 + [L] * 12 + [I] * 5 + [F, P],
     "ksa_summary_attn_bwd": [P] * 13 + [I] * 6 + [L] * 22 + [I] * 5 + [F, P, P, I, P],
     "ksa_decode_attn": [P] * 8 + [I] * 8 + [F, P],
@@ -119,7 +123,7 @@ def _ptr(x):
 
 
 # kernels launched by one call of an entry point (default 1)
-_KERNELS_PER_CALL = {"ksa_attn_bwd": 2, "ksa_attn_bwd_fused": 3, "ksa_rmsnorm_bwd": 2}
+_KERNELS_PER_CALL = {"ksa_attn_bwd": 2, "ksa_attn_bwd_fused": 3, "ksa_attn_bwd_fused_cp": 3, "ksa_rmsnorm_bwd": 2}
 _launch_count = 0
 
 

@@ -16,9 +16,15 @@ older-summary rows are returned to their owners, who add them.  Full-attention l
 earlier text K/V (the halo is everything before the shard).
 
 Transport:
-* GPUs: every rank publishes its K/V block in a symmetric-memory exchange buffer and the consumers pull the ranges
-  they need with P2P loads issued from kernels (``ksa_peer_copy`` / ``ksa_peer_add_bf16``), ordered by per-rank
-  flags that carry an exchange counter; each wait is bounded.  No NCCL collective is involved.
+* GPUs, summary layers (the default when the shapes are tile-aligned, ``_CpDirectAttention``): every rank copies its
+  K/V rows into its symmetric exchange slot and raises a flag; the attention kernels then read the halo tiles and
+  the older summaries' tiles STRAIGHT FROM THE OWNERS' SLOTS with their own TMA loads (``ksa_attn_fwd_cp``,
+  ``ksa_attn_bwd_fused_cp``: peer tiles stream in while the local block pairs are computed), and the backward
+  kernel adds the dK / dV of keys it does not own into the owners' fp32 return blocks over NVLink from its epilogue;
+  the owner folds its return block into its gradients (a local pass).  No staging copies, no NCCL collective.
+* GPUs, other cases (windows longer than a shard, summary counts that do not fill key tiles, the bit-reproducible
+  mode, full-attention layers in ``halo`` mode): consumers pull the ranges they need into staging buffers with P2P
+  copy kernels (``ksa_peer_copy`` / ``ksa_peer_add_bf16``), ordered by per-rank flags; each wait is bounded.
 * CPU (gloo) ranks, used by the tests: the same staging expressed with ``all_gather`` / ``all_reduce``.
 """
 from __future__ import annotations
@@ -110,6 +116,14 @@ class CpContext:
             self.ready = SignalPad(4 * self.size, group, device)      # [slot][producer rank] <- exchange number + 1
             self.consumed = SignalPad(4 * self.size, group, device)   # [slot][consumer rank] <- exchange number + 1
             self.dtype = dtype
+            # direct mode: [2 forward K/V slots | 2 backward K/V slots | 2 fp32 return blocks], flags per (slot, rank)
+            self.d_fwd = self.d_bwd = 0
+            self.d_slot_last = [None] * 6
+            self.d_halo_max = min(max_window * chunk, self.shape.local_len)
+            self.d_ret_bytes = batch * (self.d_halo_max + self.shape.local_sum) * self.kv_width * 4
+            self.dbuf = SymmetricBuffer(4 * self.slot_bytes + 2 * self.d_ret_bytes, group, device)
+            self.dready = SignalPad(6 * self.size, group, device)
+            self.dconsumed = SignalPad(6 * self.size, group, device)
             self.a2a_buf = None
             if self.full_layer_mode == "ulysses":
                 width = (n_heads + 2 * n_kv_heads) * head_dim
@@ -129,6 +143,9 @@ class CpContext:
             self.ready.close()
             self.consumed.close()
             self.xbuf.close()
+            self.dready.close()
+            self.dconsumed.close()
+            self.dbuf.close()
             if self.a2a_buf is not None:
                 self.a2a_ready.close()
                 self.a2a_consumed.close()
@@ -272,6 +289,141 @@ class _CpStage(torch.autograd.Function):
                               None, e + 1, 8)
         cp.consumed.set_on_all(slot * P + r, None, e + 1)
         return g_local, None, None, None
+
+
+def _ptr_array(values):
+    import ctypes
+    return (ctypes.c_void_p * len(values))(*[v if v else None for v in values])
+
+
+def direct_exchange_possible(cp: CpContext, qkv: torch.Tensor, D: int, window_chunks: Optional[int]) -> bool:
+    """Whether the attention kernels can read this layer's peer tiles in place (see the module docstring)."""
+    sh = cp.shape
+    return (cp.fused and qkv.is_cuda and D == 128 and window_chunks is not None and not ops.is_deterministic()
+            and cp.size <= 8 and sh.local_sum % 128 == 0 and (window_chunks * sh.chunk) % 128 == 0
+            and window_chunks * sh.chunk <= min(sh.local_len, cp.d_halo_max))
+
+
+class _CpDirectAttention(torch.autograd.Function):
+    """Summary-attention layer of one context-parallel shard with the exchange inside the attention kernels."""
+
+    @staticmethod
+    def _sources(cp: CpContext, base: int, slot: int, halo: int):
+        sh, B, P, r = cp.shape, cp.batch, cp.size, cp.rank
+        Ll, Nsl, kvw = sh.local_len, sh.local_sum, cp.kv_width
+        row_b = kvw * 2
+        ptr = cp.dbuf.peer_ptrs
+        text = [ptr[r - 1] + base + (Ll - halo) * row_b if halo > 0 else 0, ptr[r] + base]
+        text_flags = [cp.dready.local_ptr(slot * P + r - 1) if halo > 0 else 0, 0]
+        sums = [ptr[p] + base + B * Ll * row_b for p in range(r + 1)]
+        sum_flags = [cp.dready.local_ptr(slot * P + p) for p in range(r)] + [0]
+        return _ptr_array(text), _ptr_array(text_flags), _ptr_array(sums), _ptr_array(sum_flags)
+
+    @staticmethod
+    def _publish(cp: CpContext, kv: torch.Tensor, slot: int, e: int):
+        """Copy this rank's K|V rows into exchange slot ``slot`` and tell every rank (exchange number ``e``)."""
+        P, r = cp.size, cp.rank
+        if cp.d_slot_last[slot] is not None:      # every reader of the slot's previous contents is done
+            cp.dconsumed.wait_local(slot * P, P, None, cp.d_slot_last[slot] + 1)
+        cp.d_slot_last[slot] = e
+        base = slot * cp.slot_bytes
+        cp.dbuf.view(cp.dtype, base, kv.shape[0] * kv.shape[1]).view(kv.shape).copy_(kv)
+        cp.dready.set_on_all(slot * P + r, None, e + 1)
+        return base
+
+    @staticmethod
+    def forward(ctx, qkv, cp: CpContext, Hq, Hkv, D, window_chunks, scale):
+        sh, B, P, r = cp.shape, cp.batch, cp.size, cp.rank
+        Ll, Nsl, kvw = sh.local_len, sh.local_sum, cp.kv_width
+        halo = sh.halo_len(window_chunks)
+        e = cp.d_fwd
+        cp.d_fwd += 1
+        slot = e % 2
+        base = _CpDirectAttention._publish(cp, qkv[:, Hq * D:], slot, e)
+        text, text_flags, sums, sum_flags = _CpDirectAttention._sources(cp, base, slot, halo)
+        rs = qkv.stride(0)
+        out = torch.empty((B * (Ll + Nsl), Hq * D), dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty((B, Hq, Ll), dtype=torch.float32, device=qkv.device)
+        _lib.call("ksa_attn_fwd_cp", qkv, out, lse, B, Hq, Hkv, D, Ll, rs, Ll * rs, Hq * D, Ll * Hq * D,
+                  text, halo, Ll, sums, r + 1, Nsl, kvw, Ll * kvw, Nsl * kvw, text_flags, sum_flags, e + 1,
+                  r * Ll, r * Ll - halo, sh.chunk, sh.n_sum, window_chunks, 0, float(scale))
+        # summary queries see their own chunk's text and summaries only: all local
+        q, k, v = ops._packed_views(qkv, B, Ll, Hq, Hkv, D, 0)
+        qs, ks, vs = ops._packed_views(qkv, B, Nsl, Hq, Hkv, D, B * Ll)
+        os_ = out[B * Ll:].view(B, Nsl, Hq, D)
+        lse_s = torch.empty((B, Hq, Nsl), dtype=torch.float32, device=qkv.device)
+        _lib.call("ksa_summary_attn_fwd", qs, k, v, ks, vs, os_, lse_s, B, Hq, Hkv, D, Nsl, sh.seq_len,
+                  rs, Nsl * rs, rs, Ll * rs, rs, Ll * rs, rs, Nsl * rs, rs, Nsl * rs, Hq * D, Nsl * Hq * D,
+                  sh.chunk, sh.n_sum, r * sh.local_chunks, r * Ll, r * Nsl, float(scale))
+        cp.dconsumed.set_on_all(slot * P + r, None, e + 1)
+        ctx.save_for_backward(qkv, out, lse, lse_s)
+        ctx.cfg = (cp, Hq, Hkv, D, window_chunks, scale, halo)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, lse_s = ctx.saved_tensors
+        cp, Hq, Hkv, D, window_chunks, scale, halo = ctx.cfg
+        sh, B, P, r = cp.shape, cp.batch, cp.size, cp.rank
+        Ll, Nsl, kvw = sh.local_len, sh.local_sum, cp.kv_width
+        dout = dout if dout.is_contiguous() else dout.contiguous()
+        e = cp.d_bwd
+        cp.d_bwd += 1
+        slot, rslot = 2 + e % 2, 4 + e % 2
+        base = _CpDirectAttention._publish(cp, qkv[:, Hq * D:], slot, e)
+        text, text_flags, sums, sum_flags = _CpDirectAttention._sources(cp, base, slot, halo)
+        # the owners' return blocks of this parity were last used two exchanges ago: they must have been folded
+        if cp.d_slot_last[rslot] is not None:
+            cp.dconsumed.wait_local(rslot * P, P, None, cp.d_slot_last[rslot] + 1)
+        cp.d_slot_last[rslot] = e
+        ret_base = 4 * cp.slot_bytes + (e % 2) * cp.d_ret_bytes
+        H = cp.d_halo_max
+        ret_sum_off = ret_base + B * H * kvw * 4
+        ret_text = cp.dbuf.peer_ptrs[r - 1] + ret_base if halo > 0 else None
+        ret_sum = _ptr_array([cp.dbuf.peer_ptrs[p] + ret_sum_off for p in range(r)] + [0])
+        rs = qkv.stride(0)
+        dqkv = torch.empty_like(qkv)
+        drs = dqkv.stride(0)
+        dq, dk, dv = ops._packed_views(dqkv, B, Ll, Hq, Hkv, D, 0)
+        dqs, dks, dvs = ops._packed_views(dqkv, B, Nsl, Hq, Hkv, D, B * Ll)
+        o = out[:B * Ll].view(B, Ll, Hq, D)
+        do = dout[:B * Ll].view(B, Ll, Hq, D)
+        lq_pad = (Ll + 127) // 128 * 128
+        stats = torch.empty((2, B, Hq, lq_pad), dtype=torch.float32, device=qkv.device)
+        dq32 = torch.empty((B, Ll, Hq, D), dtype=torch.float32, device=qkv.device)
+        Ns = (r + 1) * Nsl
+        part_k = part_v = None
+        if _lib.attn_bwd_num_segments(Ll) > 1:
+            part_k = torch.zeros((B, Ns, Hkv, D), dtype=torch.float32, device=qkv.device)
+            part_v = torch.zeros_like(part_k)
+        _lib.call("ksa_attn_bwd_fused_cp", qkv, o, do, lse, stats, dq32, dq, dk, dv, dks, dvs, B, Hq, Hkv, D, Ll,
+                  rs, Ll * rs, Hq * D, Ll * Hq * D, drs, Ll * drs, drs, Ll * drs, drs, Ll * drs, drs, Nsl * drs, drs,
+                  Nsl * drs, text, halo, Ll, sums, r + 1, Nsl, kvw, Ll * kvw, Nsl * kvw, text_flags, sum_flags, e + 1,
+                  ret_text, ret_sum, kvw, H * kvw, Nsl * kvw, r * Ll, r * Ll - halo, sh.chunk, sh.n_sum, window_chunks, 0,
+                  float(scale), part_k, part_v)
+        cp.dready.set_on_all(rslot * P + r, None, e + 1)       # my additions to every owner's return block are done
+        q, k, v = ops._packed_views(qkv, B, Ll, Hq, Hkv, D, 0)
+        qs, ks, vs = ops._packed_views(qkv, B, Nsl, Hq, Hkv, D, B * Ll)
+        os_ = out[B * Ll:].view(B, Nsl, Hq, D)
+        dos = dout[B * Ll:].view(B, Nsl, Hq, D)
+        own = r * Nsl * Hkv * D     # this rank's rows of the fp32 partial sums
+        _lib.call("ksa_summary_attn_bwd", qs, k, v, ks, vs, os_, dos, lse_s, dqs, dk, dv, dks, dvs,
+                  B, Hq, Hkv, D, Nsl, sh.seq_len, rs, Nsl * rs, rs, Ll * rs, rs, Ll * rs, rs, Nsl * rs, rs, Nsl * rs,
+                  Hq * D, Nsl * Hq * D, drs, Nsl * drs, drs, Ll * drs, drs, Ll * drs, drs, Nsl * drs, drs, Nsl * drs,
+                  sh.chunk, sh.n_sum, r * sh.local_chunks, r * Ll, r * Nsl, float(scale),
+                  part_k.view(-1)[own:] if part_k is not None else None,
+                  part_v.view(-1)[own:] if part_v is not None else None, Ns)
+        if r < P - 1:     # what the later ranks computed for my last W*C text rows and for my summaries
+            flags = cp.dready.local_ptr(rslot * P + r + 1)
+            my_ret = cp.dbuf.local_ptr + ret_base
+            h_next = min((r + 1) * Ll, window_chunks * sh.chunk)
+            _lib.call("ksa_cp_fold_return", dqkv[Ll - h_next:, Hq * D:], my_ret, B, h_next, kvw, drs, Ll * drs, kvw,
+                      H * kvw, flags, P - 1 - r, e + 1)
+            _lib.call("ksa_cp_fold_return", dqkv[B * Ll:, Hq * D:], my_ret + B * H * kvw * 4, B, Nsl, kvw, drs, Nsl * drs,
+                      kvw, Nsl * kvw, flags, P - 1 - r, e + 1)
+        cp.dconsumed.set_on_all(rslot * P + r, None, e + 1)
+        cp.dconsumed.set_on_all(slot * P + r, None, e + 1)
+        return dqkv, None, None, None, None, None, None
 
 
 # ------------------------------------------------------------------------------------------ sequence <-> head resharding
@@ -424,6 +576,8 @@ def cp_attention_packed(qkv: torch.Tensor, cp: CpContext, Hq: int, Hkv: int, D: 
     if qkv.shape[0] != n_text + B * Nsl:
         raise ValueError(f"expected {n_text + B * Nsl} packed rows for this shard, got {qkv.shape[0]}")
     scale = scale if scale is not None else D ** -0.5
+    if summaries and direct_exchange_possible(cp, qkv, D, window_chunks):
+        return _CpDirectAttention.apply(qkv, cp, Hq, Hkv, D, window_chunks, scale)
     kv = qkv[:, Hq * D:].contiguous()
     st_text, st_sum = _CpStage.apply(kv, cp, window_chunks, summaries)
     halo = sh.halo_len(window_chunks)

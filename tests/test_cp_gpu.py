@@ -64,6 +64,38 @@ def _worker(rank, world, port, out_q):
         for c in cps.values():
             c.close()
 
+        # summary layers with the exchange inside the attention kernels: tile-aligned shapes (256 summaries and a
+        # 128-key halo per rank); five layers in a row so that every exchange slot and return block is reused
+        from ksa_b200.parallel.cp import direct_exchange_possible
+        B, L, C, S, W = 2, 4096, 8, 1, 16
+        Ns = (L // C) * S
+        cp = CpContext(dist.group.WORLD, L, C, S, Hkv, D, batch=B, device=dev, max_window=W, n_heads=Hq)
+        names = []
+        real_call = _lib.call
+        _lib.call = lambda name, *a: (names.append(name), real_call(name, *a))[1]
+        try:
+            for it in range(5):
+                full = (torch.randn(B * (L + Ns), (Hq + 2 * Hkv) * D, generator=g) * 0.5).to(dev).bfloat16()
+                go = torch.randn(B * (L + Ns), Hq * D, generator=g).to(dev).bfloat16()
+                rows = _shard_rows(B, L, Ns, rank, world, dev)
+                x_full = full.clone().requires_grad_(True)
+                o_full = ops.attention_packed(x_full, B, L, Ns, Hq, Hkv, D, C, S, W)
+                o_full.backward(go)
+                x_loc = full[rows].clone().requires_grad_(True)
+                assert direct_exchange_possible(cp, x_loc, D, W)
+                o_loc = cp_attention_packed(x_loc, cp, Hq, Hkv, D, W, True)
+                o_loc.backward(go[rows])
+                torch.cuda.synchronize(); _lib.check_status(); dist.barrier()
+                torch.testing.assert_close(o_loc.float(), o_full[rows].float(), atol=2e-2, rtol=2e-2)
+                ref_g = x_full.grad[rows].float()
+                err = (x_loc.grad.float() - ref_g).norm() / ref_g.norm()
+                assert err < 2e-2, ("direct", it, float(err))
+        finally:
+            _lib.call = real_call
+        assert "ksa_attn_fwd_cp" in names and "ksa_attn_bwd_fused_cp" in names
+        assert not any(n in ("ksa_peer_copy", "ksa_peer_add_bf16") for n in names), sorted(set(names))
+        cp.close()
+
         # whole model: shard loss / gradients against the whole sequence on one GPU
         from ksa_b200.config import get_preset
         from ksa_b200.models import get_model_class
