@@ -1,5 +1,5 @@
-"""Context parallelism on 2 GPUs: halo / summary exchange over peer memory against the whole-sequence kernels.
-Skipped with fewer than two GPUs."""
+"""Context parallelism on 2 and 4 GPUs: halo / summary exchange over peer memory against the whole-sequence kernels.
+Each case is skipped on a box with fewer GPUs than ranks."""
 import os
 import socket
 
@@ -35,7 +35,8 @@ def _worker(rank, world, port, out_q):
         from ksa_b200.ops import _lib
         from ksa_b200.parallel.cp import CpContext, cp_attention_packed, shard_inputs
         dev = torch.device("cuda", rank)
-        B, L, C, S, W, Hq, Hkv, D = 2, 2048, 128, 1, 3, 4, 2, 128
+        # head counts that divide by the group size, so that the heads-resharded full layers apply
+        B, L, C, S, W, Hq, Hkv, D = 2, 2048, 128, 1, 3, 2 * world, world, 128
         Ns = (L // C) * S
         g = torch.Generator(device="cpu").manual_seed(5)
         cps = {m: CpContext(dist.group.WORLD, L, C, S, Hkv, D, batch=B, device=dev, full_layers=True, n_heads=Hq,
@@ -99,7 +100,8 @@ def _worker(rank, world, port, out_q):
         # whole model: shard loss / gradients against the whole sequence on one GPU
         from ksa_b200.config import get_preset
         from ksa_b200.models import get_model_class
-        cfg = get_preset("qwen3-ksa-tiny").merge({"head_dim": 128, "num_heads": 4, "num_kv_heads": 2, "embed_dim": 512,
+        cfg = get_preset("qwen3-ksa-tiny").merge({"head_dim": 128, "num_heads": 2 * world, "num_kv_heads": world,
+                                                  "embed_dim": 512,
                                                   "summary_chunk_size": 128, "summary_sliding_chunk_num": 2,
                                                   "num_layers": 2, "summary_layer_freq": [1, 0]})
         torch.manual_seed(0)
@@ -140,9 +142,10 @@ def _worker(rank, world, port, out_q):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_context_parallel_attention_and_model_two_gpus():
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_context_parallel_attention_and_model(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()

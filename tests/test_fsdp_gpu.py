@@ -1,5 +1,5 @@
-"""Fused FSDP communication kernels on 2 GPUs: P2P gather, reduce-scatter + AdamW, and the whole engine against the
-collective (NCCL) back end.  Skipped with fewer than two GPUs."""
+"""Fused FSDP communication kernels on 2 and 4 GPUs: P2P gather, reduce-scatter + AdamW, and the whole engine against
+the collective (NCCL) back end.  Each case is skipped on a box with fewer GPUs than ranks."""
 import os
 import socket
 
@@ -129,10 +129,10 @@ def _worker(rank, world, port, out_q):
         dist.destroy_process_group()
 
 
-def test_fused_fsdp_matches_collective_on_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_fsdp_matches_collective(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()

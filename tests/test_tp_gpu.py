@@ -1,5 +1,5 @@
-"""Tensor-parallel inference on 2 GPUs: fused all-reduce + add + RMSNorm kernel and the sharded engine against the
-unsharded one.  Skipped with fewer than two GPUs."""
+"""Tensor-parallel inference on 2 and 4 GPUs: fused all-reduce + add + RMSNorm kernel and the sharded engine against
+the unsharded one.  Each case is skipped on a box with fewer GPUs than ranks."""
 import os
 import socket
 
@@ -103,7 +103,8 @@ def _worker(rank, world, port, out_q):
             torch.testing.assert_close(res.float(), res_ref2, atol=4e-2, rtol=2e-2)
             tp.close()
         # --- engine: TP=2 shard against the whole model on the same GPU
-        cfg = get_preset("qwen3-ksa-tiny").merge({"head_dim": 128, "num_heads": 4, "num_kv_heads": 2, "embed_dim": 512,
+        cfg = get_preset("qwen3-ksa-tiny").merge({"head_dim": 128, "num_heads": 2 * world, "num_kv_heads": world,
+                                                  "embed_dim": 512,
                                                   "summary_chunk_size": 128, "summary_sliding_chunk_num": 2,
                                                   "num_layers": 2, "summary_layer_freq": [1, 0],
                                                   "intermediate_dim": 1024})
@@ -142,9 +143,10 @@ def _worker(rank, world, port, out_q):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tensor_parallel_fused_allreduce_and_engine_two_gpus():
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_fused_allreduce_and_engine(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
