@@ -83,10 +83,10 @@ class KsaInferenceEngine:
         # steps that do not cross a chunk boundary replay one captured CUDA graph (all indices come from device
         # counters, so the launch sequence is the same every step); boundary steps (1 in ``chunk``) run eagerly
         self.cuda_graph = cuda_graph
-        self._graph = None
+        self._graphs = {}            # any sequence at a chunk boundary? -> (graph, logits)
         self._graph_tokens = None
-        self._graph_logits = None
-        self._plain_steps = 0
+        self._boundary_dev = None    # [B] int32: which sequences close a chunk in this step (read inside the graphs)
+        self._plain_steps = {False: 0, True: 0}
         self.model.drop_partial_summary = True
         cfg = model.config
         self.cfg = cfg
@@ -110,54 +110,116 @@ class KsaInferenceEngine:
                 self.layer_caches.append(FullLayerCache(max_len, batch, Hkv, Dh, self.dtype, self.device))
         self.state = CacheState(batch, self.device)
         self.host_len = [0] * batch
+        self._boundary_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
+
+    def reserve(self, max_len: int) -> None:
+        """Grow every layer's cache so that sequences may reach ``max_len`` tokens; contents are kept.  The cache layout
+        puts the region that grows (text of full-attention layers, summaries of summary layers) last, so the old
+        buffers are prefixes of the new ones.  Captured decode graphs hold the old addresses and are dropped."""
+        if max_len <= self.max_len:
+            return
+        cfg = self.cfg
+        Hkv, Dh = cfg.num_kv_heads, cfg.head_dim
+        for li, old in enumerate(self.layer_caches):
+            if self.specs[li] is not None:
+                sp = self.specs[li]
+                spec = CacheSpec(sp.chunk, sp.n_sum, sp.window, max_len // self.C + 1)
+                new = KsaLayerCache(spec, self.batch, Hkv, Dh, self.dtype, self.device)
+                self.specs[li] = spec
+            else:
+                new = FullLayerCache(max_len, self.batch, Hkv, Dh, self.dtype, self.device)
+            cap = old.k.shape[2]
+            new.k[:, :, :cap] = old.k
+            new.v[:, :, :cap] = old.v
+            self.layer_caches[li] = new
+        self.max_len = max_len
+        self._graphs = {}
 
     def cache_bytes(self) -> int:
         return sum(c.k.numel() * c.k.element_size() * 2 for c in self.layer_caches)
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
-    def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
-        """``tokens`` ``[B, L]`` (equal lengths) -> logits of the last position ``[B, V]``; caches are filled."""
+    def prefill(self, tokens: torch.Tensor, lengths: Optional[List[int]] = None,
+                batch_chunk: Optional[int] = None) -> torch.Tensor:
+        """``tokens`` ``[B, L]`` -> logits of every sequence's last prompt position ``[B, V]``; caches are filled.
+
+        ``lengths``: prompt length of every sequence when they differ (``tokens`` is then padded on the right; the
+        padding is never read).  Sequences of equal length are prefilled together, at most ``batch_chunk`` at a time
+        (bounds the activation memory of long prompts in large batches); afterwards the sequences decode together,
+        each at its own chunk phase."""
+        B, Lmax = tokens.shape
+        assert B == self.batch
+        lengths = [Lmax] * B if lengths is None else [int(l) for l in lengths]
+        assert len(lengths) == B and all(0 < l <= Lmax for l in lengths), "bad prompt lengths"
+        if max(lengths) > self.max_len:
+            self.reserve(max(lengths))
+        groups = {}
+        for i, l in enumerate(lengths):
+            groups.setdefault(l, []).append(i)
+        out = None
+        for L, idx in sorted(groups.items()):
+            step = batch_chunk or len(idx)
+            for j in range(0, len(idx), step):
+                rows = idx[j:j + step]
+                logits = self._prefill_rows(tokens[rows, :L] if rows != list(range(B)) or L != Lmax else tokens, rows)
+                if out is None:
+                    out = torch.empty(B, logits.shape[-1], dtype=torch.float32, device=logits.device)
+                out[rows] = logits
+        self.host_len = list(lengths)
+        return out
+
+    def _prefill_rows(self, tokens: torch.Tensor, rows: List[int]) -> torch.Tensor:
+        """Prefill the sequences ``rows`` of the batch (all of length ``tokens.shape[1]``) in one pass of the model."""
         B, L = tokens.shape
-        assert B == self.batch and L <= self.max_len
         cfg, C, S = self.cfg, self.C, self.S
         Hq, Hkv, Dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         n_full = L // C if S > 0 else 0      # complete chunks
         tail = L - n_full * C if S > 0 else L
         Ns = n_full * S
+        contiguous = rows == list(range(rows[0], rows[0] + B))
+        sel = slice(rows[0], rows[0] + B) if contiguous else None
+
+        def put(dst, slots, src):
+            """``src`` ``[B, n, H, D]`` -> cache ``dst[rows, :, slots]`` (``slots``: slice or index tensor)."""
+            if contiguous:
+                dst[sel, :, slots] = src.transpose(1, 2)
+            else:
+                for i, r in enumerate(rows):
+                    dst[r, :, slots] = src[i].transpose(0, 1)
 
         def sink(layer_idx, qkv, is_summary_layer):
             cache = self.layer_caches[layer_idx]
             k_t = qkv[:B * L, Hq * Dh:(Hq + Hkv) * Dh].view(B, L, Hkv, Dh)
             v_t = qkv[:B * L, (Hq + Hkv) * Dh:].view(B, L, Hkv, Dh)
             if not is_summary_layer:
-                cache.k[:, :, :L] = k_t.transpose(1, 2)
-                cache.v[:, :, :L] = v_t.transpose(1, 2)
+                put(cache.k, slice(0, L), k_t)
+                put(cache.v, slice(0, L), v_t)
                 return
             spec = self.specs[layer_idx]
             W = spec.window
             # ring: the last min(W, n_full) complete chunks, chunk c at ring slot (c mod W)
             for c in range(max(0, n_full - W), n_full):
                 dst = spec.text0 + (c % max(W, 1)) * C
-                cache.k[:, :, dst:dst + C] = k_t[:, c * C:(c + 1) * C].transpose(1, 2)
-                cache.v[:, :, dst:dst + C] = v_t[:, c * C:(c + 1) * C].transpose(1, 2)
+                put(cache.k, slice(dst, dst + C), k_t[:, c * C:(c + 1) * C])
+                put(cache.v, slice(dst, dst + C), v_t[:, c * C:(c + 1) * C])
             # current (partial) chunk, right to left: chunk offset o -> slot S + C - 1 - o
             if tail > 0:
                 lo = n_full * C
                 slots = torch.arange(S + C - 1, S + C - 1 - tail, -1, device=qkv.device)
-                cache.k[:, :, slots] = k_t[:, lo:lo + tail].transpose(1, 2)
-                cache.v[:, :, slots] = v_t[:, lo:lo + tail].transpose(1, 2)
+                put(cache.k, slots, k_t[:, lo:lo + tail])
+                put(cache.v, slots, v_t[:, lo:lo + tail])
             if Ns > 0:
                 k_s = qkv[B * L:, Hq * Dh:(Hq + Hkv) * Dh].view(B, Ns, Hkv, Dh)
                 v_s = qkv[B * L:, (Hq + Hkv) * Dh:].view(B, Ns, Hkv, Dh)
-                cache.k[:, :, spec.sum0:spec.sum0 + Ns] = k_s.transpose(1, 2)
-                cache.v[:, :, spec.sum0:spec.sum0 + Ns] = v_s.transpose(1, 2)
+                put(cache.k, slice(spec.sum0, spec.sum0 + Ns), k_s)
+                put(cache.v, slice(spec.sum0, spec.sum0 + Ns), v_s)
 
         logits = self.model(tokens, kv_sink=sink, last_token_only=True)
-        self.state.text_len.fill_(L)
-        self.state.cbl.fill_(tail if S > 0 else 0)
-        self.state.chunks.fill_(n_full)
-        self.host_len = [L] * B
+        where = sel if contiguous else torch.tensor(rows, device=self.device)
+        self.state.text_len[where] = L
+        self.state.cbl[where] = tail if S > 0 else 0
+        self.state.chunks[where] = n_full
         return logits[:, -1].float()
 
     # ------------------------------------------------------------------ decode
@@ -165,27 +227,37 @@ class KsaInferenceEngine:
     def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
         """``tokens`` ``[B]``: the next text token of every sequence -> logits ``[B, V]``."""
         C, S = self.C, self.S
+        if max(self.host_len) + 1 > self.max_len:
+            self.reserve(2 * self.max_len)
         boundary_host = [S > 0 and (l % C) == C - 1 for l in self.host_len]
+        anyb = any(boundary_host)
         tp = getattr(self.model, "tp", None)
-        graphable = self.cuda_graph and tokens.is_cuda and not any(boundary_host)
-        # with tensor parallelism the graph ends at the final norm: the vocabulary-parallel head and the gather of
-        # its logits (a library collective) run after the replay
+        # Two graphs: steps in which no sequence closes a chunk, and steps in which some do (those carry the summary
+        # rows as well; WHICH sequences close one is data, read from ``_boundary_dev``).  With tensor parallelism only
+        # the first kind is captured, and the graph ends at the final norm: the vocabulary-parallel head and the
+        # gather of its logits (a library collective) run after the replay.
+        graphable = self.cuda_graph and tokens.is_cuda and (not anyb or tp is None)
         head_in_graph = tp is None
+        if anyb:
+            self._boundary_dev.copy_(torch.tensor(boundary_host, dtype=torch.int32), non_blocking=False)
         if not graphable:
-            logits = self._decode_impl(tokens, boundary_host)
-        elif self._graph is None and self._plain_steps == 0:
-            self._plain_steps += 1          # first-call set-up of the kernels happens outside a capture
-            logits = self._decode_impl(tokens, boundary_host)
+            logits = self._decode_impl(tokens, anyb)
+        elif anyb not in self._graphs and self._plain_steps[anyb] == 0:
+            self._plain_steps[anyb] += 1    # first-call set-up of the kernels happens outside a capture
+            logits = self._decode_impl(tokens, anyb)
         else:
-            if self._graph is None:
+            if self._graph_tokens is None:
                 self._graph_tokens = tokens.reshape(self.batch).clone()
+            if anyb not in self._graphs:
                 torch.cuda.synchronize(self.device)
-                self._graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(self._graph):
-                    self._graph_logits = self._decode_impl(self._graph_tokens, boundary_host, head_in_graph)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    out = self._decode_impl(self._graph_tokens, anyb, head_in_graph)
+                self._graphs[anyb] = (graph, out)
+            graph, out = self._graphs[anyb]
             self._graph_tokens.copy_(tokens.reshape(self.batch))
-            self._graph.replay()
-            logits = self._graph_logits.clone() if head_in_graph else self._head(self._graph_logits)
+            graph.replay()
+            logits = out.clone() if head_in_graph else self._head(out)
         self.host_len = [l + 1 for l in self.host_len]
         return logits
 
@@ -196,20 +268,20 @@ class KsaInferenceEngine:
             logits = tp.gather_logits(logits)
         return logits.float()
 
-    def _decode_impl(self, tokens: torch.Tensor, boundary_host, with_head: bool = True) -> torch.Tensor:
-        """Device work of one decode step (launches only; the host mirror of the lengths is advanced by the caller)."""
+    def _decode_impl(self, tokens: torch.Tensor, any_boundary: bool, with_head: bool = True) -> torch.Tensor:
+        """Device work of one decode step (launches only; the host mirror of the lengths is advanced by the caller).
+        ``any_boundary``: some sequence closes a chunk in this step; which ones is read from ``_boundary_dev``."""
         model, cfg = self.model, self.cfg
         tp = getattr(model, "tp", None)      # tensor-parallel shard: cfg holds the local head counts
         B, C, S = self.batch, self.C, self.S
         Hq, Hkv, Dh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
         scale = Dh ** -0.5
         st = self.state
-        any_boundary = any(boundary_host)
         dev = self.device
         pos_t = st.text_len.clone()                              # position of the new text token
         x = ops.embedding(tokens.reshape(B), model.tok_embeddings.weight)      # [B, D]
         if any_boundary:
-            boundary = torch.tensor(boundary_host, dtype=torch.int32, device=dev)
+            boundary = self._boundary_dev
             xs = model._summary_rows(_OneChunk(B, S), x.dtype)                 # [B*S, D]
             x = torch.cat([x, xs], dim=0)
             chunk_start = st.text_len - (C - 1)

@@ -102,3 +102,42 @@ def test_sampling_restricts_to_top_k_and_top_p_and_stops_at_eos():
     s1 = eng.generate(prompt, 6, temperature=0.8, top_k=20, generator=torch.Generator().manual_seed(5))
     s2 = eng.generate(prompt, 6, temperature=0.8, top_k=20, generator=torch.Generator().manual_seed(5))
     assert torch.equal(s1, s2)
+
+
+@pytest.mark.parametrize("lengths", [(21, 13), (16, 16), (5, 30)])
+def test_unequal_prompt_lengths_decode_like_each_sequence_alone(lengths):
+    """A batch whose prompts differ in length (right-padded) is prefilled group by group and then decoded together,
+    every sequence at its own chunk phase; every step equals the whole-sequence recompute of that sequence."""
+    model = _model(8, 1, 2)
+    B, new = len(lengths), 20
+    torch.manual_seed(3)
+    Lmax = max(lengths)
+    prompt = torch.randint(0, model.config.vocab_size, (B, Lmax))
+    eng = KsaInferenceEngine(model, max_len=Lmax + new + 4, batch=B)
+    seqs = [prompt[i, :l] for i, l in enumerate(lengths)]
+    logits = eng.prefill(prompt, lengths=list(lengths), batch_chunk=1)
+    model.drop_partial_summary = True
+    for step in range(new):
+        with torch.no_grad():
+            full = torch.stack([model(s[None])[0, -1].float() for s in seqs])
+        assert torch.allclose(logits, full, atol=2e-4, rtol=1e-3), (step, (logits - full).abs().max())
+        nxt = full.argmax(-1)
+        seqs = [torch.cat([s, n[None]]) for s, n in zip(seqs, nxt)]
+        logits = eng.decode_step(nxt)
+
+
+def test_cache_grows_when_a_sequence_outlives_its_capacity():
+    """``max_len`` is only the initial capacity: a prompt longer than it, and decoding past it, re-allocate the caches
+    (text of full layers, summary region of summary layers) and keep their contents."""
+    model = _model(4, 1, 2)
+    torch.manual_seed(4)
+    prompt = torch.randint(0, model.config.vocab_size, (2, 10))
+    small = KsaInferenceEngine(model, max_len=8, batch=2)        # smaller than the prompt
+    big = KsaInferenceEngine(model, max_len=128, batch=2)
+    a, b = small.prefill(prompt), big.prefill(prompt)
+    assert small.max_len >= 10
+    for step in range(40):                                       # crosses the grown capacity more than once
+        assert torch.allclose(a, b, atol=1e-5), step
+        nxt = b.argmax(-1)
+        a, b = small.decode_step(nxt), big.decode_step(nxt)
+    assert small.max_len >= 50 and small.max_len < 128

@@ -59,16 +59,20 @@ def test_engine_matches_cpu_engine():
         for p in cpu_model.parameters():
             p.copy_(p.to(torch.bfloat16).float())
     gpu_model = copy.deepcopy(cpu_model).cuda().to(torch.bfloat16)
-    B, L, new = 2, 300, 100     # crosses the chunk boundary at 384
-    prompt = torch.randint(0, cfg.vocab_size, (B, L))
+    # Prompts of 300 and 250 tokens: sequence 1 closes chunks at steps 6 and 134, sequence 0 at step 84, so the
+    # boundary form of the step runs eagerly once, is captured, and is replayed; the GPU engine starts with room for
+    # 400 tokens and has to grow its caches (and capture its graphs again) on the way.
+    B, lengths, new = 2, [300, 250], 140
+    prompt = torch.randint(0, cfg.vocab_size, (B, max(lengths)))
     e_cpu = KsaInferenceEngine(cpu_model, max_len=512, batch=B)
-    e_gpu = KsaInferenceEngine(gpu_model, max_len=512, batch=B)
-    lc, lg = e_cpu.prefill(prompt), e_gpu.prefill(prompt.cuda())
+    e_gpu = KsaInferenceEngine(gpu_model, max_len=400, batch=B)
+    lc, lg = e_cpu.prefill(prompt, lengths=lengths), e_gpu.prefill(prompt.cuda(), lengths=lengths)
     for step in range(new):
         err = (lg.cpu() - lc).norm() / lc.norm()
         assert err < 5e-2, (step, err)
         nxt = lc.argmax(-1)
         lc, lg = e_cpu.decode_step(nxt), e_gpu.decode_step(nxt.cuda())
+    assert e_gpu.max_len > 400 and set(e_gpu._graphs) == {False, True}
     _lib.check_status()
 
 
