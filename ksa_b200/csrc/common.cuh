@@ -293,6 +293,12 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, int a_mn_ma
          | ((uint32_t)(m >> 4) << 24);   // M / 16
 }
 
+// Programmatic dependent launch.  A kernel launched with programmatic stream serialization may start before the
+// previous kernel of its stream has finished; it orders itself behind that kernel with grid_dependency_wait().  A
+// kernel lets such a successor start early with grid_dependency_launch() (no effect for ordinary successors).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ----------------------------------------------------------------- small helpers
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

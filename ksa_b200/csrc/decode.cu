@@ -20,6 +20,7 @@ namespace ksa {
 constexpr int kDecThreads = 128;
 constexpr int kDecTile = 64;       // keys per shared-memory tile
 constexpr int kDecMaxQ = 16;       // queries (G * Tq) served per CTA
+constexpr int kDecMaxSplits = 64;  // splits of the key range when the last split merges them itself
 
 struct DecodeArgs {
   const bf16* q;        // [B, Tq, Hq, D]
@@ -32,10 +33,71 @@ struct DecodeArgs {
   bf16* out;            // [B, Tq, Hq, D]
   int B, Tq, Hq, Hkv, D, cap, splits, keys_per_split;
   float scale;
+  int* counters;        // [B * Hkv] zeros, or null: with counters the last split of a KV group to finish merges the
+                        // splits itself (and puts the counter back to zero); without, decode_combine_kernel does
 };
+
+// Called by every thread of a CTA after it has written its split's partial results.  The CTA that finishes last for
+// its (batch, KV head) merges all splits of the group's nq = G * Tq queries into `out`.
+__device__ __forceinline__ void combine_if_last(const DecodeArgs& a, int b, int kvh, int nq, int G) {
+  if (a.counters == nullptr) return;
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(&a.counters[b * a.Hkv + kvh], 1);
+    s_last = prev == a.splits - 1;
+    if (s_last) a.counters[b * a.Hkv + kvh] = 0;      // ready for the next launch on this stream
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // weights of the splits: stage (max, sum) of every (query, split), then one thread per query turns them into
+  // exp(m_split - m) / l; the outputs are then plain weighted sums with independent loads
+  __shared__ float s_w[kDecMaxQ][kDecMaxSplits], s_ls[kDecMaxQ][kDecMaxSplits];
+  const int D = a.D, S = a.splits;
+  for (int i = threadIdx.x; i < nq * S; i += blockDim.x) {
+    const int q = i / S, sp = i - q * S;
+    const long long row = ((long long)b * a.Tq + q / G) * a.Hq + kvh * G + q % G;
+    s_w[q][sp] = __ldcg(a.part_ml + (row * S + sp) * 2);
+    s_ls[q][sp] = __ldcg(a.part_ml + (row * S + sp) * 2 + 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < nq) {
+    const int q = threadIdx.x;
+    float m = -INFINITY, l = 0.f;
+    for (int sp = 0; sp < S; ++sp) m = fmaxf(m, s_w[q][sp]);
+    for (int sp = 0; sp < S; ++sp) {
+      const float f = s_w[q][sp] == -INFINITY ? 0.f : __expf(s_w[q][sp] - m);
+      s_w[q][sp] = f;
+      l += s_ls[q][sp] * f;
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int sp = 0; sp < S; ++sp) s_w[q][sp] *= inv;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nq * D; i += blockDim.x) {
+    const int q = i / D, d = i - q * D;
+    const long long row = ((long long)b * a.Tq + q / G) * a.Hq + kvh * G + q % G;
+    const float* po = a.part_o + row * S * D + d;
+    float o = 0.f;
+    int sp = 0;
+    for (; sp + 8 <= S; sp += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + (long long)(sp + u) * D);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) o = fmaf(v[u], s_w[q][sp + u], o);
+    }
+    for (; sp < S; ++sp) o = fmaf(__ldcg(po + (long long)sp * D), s_w[q][sp], o);
+    a.out[row * D + d] = __float2bfloat16(o);
+  }
+}
 
 template <int D>
 __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeArgs a) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   constexpr int ROW_W = D / 2 + 1;  // 32-bit words per padded row
   __shared__ uint32_t k_s[kDecTile * ROW_W];
   __shared__ uint32_t v_s[kDecTile * ROW_W];
@@ -160,6 +222,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeArgs a) 
       }
     }
   }
+  combine_if_last(a, b, kvh, nq, G);
 }
 
 // ------------------------------------------------------------------------------------------ tensor-core variant
@@ -179,6 +242,8 @@ __device__ __forceinline__ void mma_qk(float (&c)[4], uint32_t a0, uint32_t a1, 
 
 template <int NQ>   // queries served per CTA, padded: 4, 8 or 16
 __global__ void __launch_bounds__(kDecThreads) decode_attn_mma_kernel(DecodeArgs a) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   constexpr int D = 128, KPI = 16;                 // keys per warp iteration
   __shared__ __align__(16) float s_p[4][KPI][NQ];  // per warp: probabilities, [key][query]
   __shared__ float s_m[4][NQ], s_l[4][NQ];
@@ -335,10 +400,13 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_mma_kernel(DecodeArgs
       a.part_ml[base * 2 + 1] = l;
     }
   }
+  combine_if_last(a, b, kvh, nq, G);
 }
 
 // one CTA per (b, t, head): merge the splits
 __global__ void __launch_bounds__(128) decode_combine_kernel(DecodeArgs a) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   const long long row = blockIdx.x;  // (b * Tq + t) * Hq + h
   const float* ml = a.part_ml + row * a.splits * 2;
   float m = -INFINITY;
@@ -361,6 +429,8 @@ __global__ void __launch_bounds__(256)
 kv_cache_append_kernel(const bf16* __restrict__ k_new, const bf16* __restrict__ v_new, bf16* __restrict__ k_cache,
                        bf16* __restrict__ v_cache, const int* __restrict__ slots, int B, int T, int H, int D, int cap,
                        long long src_row_stride, long long src_batch_stride) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int per = D / 8;
   if (vec >= (long long)B * T * H * per) return;
@@ -381,6 +451,8 @@ __global__ void __launch_bounds__(256)
 kv_cache_move_kernel(bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, const int* __restrict__ src,
                      const int* __restrict__ dst, const int* __restrict__ enable, int B, int H, int D, int cap,
                      int rows) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int per = D / 8;
   if (vec >= (long long)B * H * rows * per) return;
@@ -400,27 +472,31 @@ kv_cache_move_kernel(bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, con
 using namespace ksa;
 
 // Scratch sizes the caller allocates: part_o [B*Tq*Hq*splits*D] fp32, part_ml [B*Tq*Hq*splits*2] fp32.
+// counters: B*Hkv int32 zeros that launches on one stream may share (each launch leaves them zero), or null for a
+// separate merge kernel.
 KSA_API int ksa_decode_attn(const void* q, const void* k_cache, const void* v_cache, const void* start, const void* len,
                             void* part_o, void* part_ml, void* out, int B, int Tq, int Hq, int Hkv, int D, int cap,
-                            int splits, int keys_per_split, float scale, void* stream) {
+                            int splits, int keys_per_split, float scale, void* counters, void* stream) {
   KSA_ENTER(q);
   KSA_REQUIRE(D == 128 || D == 64, "decode_attn: head_dim %d unsupported (64 or 128)", D);
   KSA_REQUIRE(Hq % Hkv == 0 && (Hq / Hkv) * Tq <= kDecMaxQ, "decode_attn: (Hq/Hkv) * Tq = %d exceeds %d queries per CTA",
               (Hq / Hkv) * Tq, kDecMaxQ);
   KSA_REQUIRE(splits >= 1 && keys_per_split >= 1, "decode_attn: bad split configuration");
+  KSA_REQUIRE(counters == nullptr || splits <= kDecMaxSplits, "decode_attn: %d splits (at most %d with counters)", splits,
+              kDecMaxSplits);
   if (B == 0) return 0;
   DecodeArgs a{(const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (const int*)start, (const int*)len,
-               (float*)part_o, (float*)part_ml, (bf16*)out, B, Tq, Hq, Hkv, D, cap, splits, keys_per_split, scale};
+               (float*)part_o, (float*)part_ml, (bf16*)out, B, Tq, Hq, Hkv, D, cap, splits, keys_per_split, scale,
+               (int*)counters};
   dim3 grid(splits, Hkv, B);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int nq = (Hq / Hkv) * Tq;
-  if (D == 128 && nq <= 4) decode_attn_mma_kernel<4><<<grid, kDecThreads, 0, st>>>(a);
-  else if (D == 128 && nq <= 8) decode_attn_mma_kernel<8><<<grid, kDecThreads, 0, st>>>(a);
-  else if (D == 128) decode_attn_mma_kernel<16><<<grid, kDecThreads, 0, st>>>(a);
-  else decode_attn_kernel<64><<<grid, kDecThreads, 0, st>>>(a);
-  KSA_CHECK_CUDA(cudaGetLastError());
-  decode_combine_kernel<<<B * Tq * Hq, 128, 0, st>>>(a);
-  KSA_CHECK_CUDA(cudaGetLastError());
+  const bool dep = dependent_launch_enabled();
+  if (D == 128 && nq <= 4) KSA_CHECK_CUDA(launch_kernel(dep, decode_attn_mma_kernel<4>, grid, dim3(kDecThreads), 0, st, a));
+  else if (D == 128 && nq <= 8) KSA_CHECK_CUDA(launch_kernel(dep, decode_attn_mma_kernel<8>, grid, dim3(kDecThreads), 0, st, a));
+  else if (D == 128) KSA_CHECK_CUDA(launch_kernel(dep, decode_attn_mma_kernel<16>, grid, dim3(kDecThreads), 0, st, a));
+  else KSA_CHECK_CUDA(launch_kernel(dep, decode_attn_kernel<64>, grid, dim3(kDecThreads), 0, st, a));
+  if (counters == nullptr) KSA_CHECK_CUDA(launch_kernel(dep, decode_combine_kernel, dim3(B * Tq * Hq), dim3(128), 0, st, a));
   return 0;
 }
 
@@ -431,10 +507,10 @@ KSA_API int ksa_kv_cache_append(const void* k_new, const void* v_new, void* k_ca
   KSA_REQUIRE(D % 8 == 0, "kv_cache_append: head_dim must be a multiple of 8");
   const long long n = (long long)B * T * H * (D / 8);
   if (n == 0) return 0;
-  kv_cache_append_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (const bf16*)k_new, (const bf16*)v_new, (bf16*)k_cache, (bf16*)v_cache, (const int*)slots, B, T, H, D, cap,
-      src_row_stride, src_batch_stride);
-  KSA_CHECK_CUDA(cudaGetLastError());
+  KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), kv_cache_append_kernel, dim3((unsigned)((n + 255) / 256)),
+                              dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), (const bf16*)k_new,
+                              (const bf16*)v_new, (bf16*)k_cache, (bf16*)v_cache, (const int*)slots, B, T, H, D, cap,
+                              src_row_stride, src_batch_stride));
   return 0;
 }
 
@@ -443,8 +519,8 @@ KSA_API int ksa_kv_cache_move(void* k_cache, void* v_cache, const void* src, con
   KSA_ENTER(k_cache);
   const long long n = (long long)B * H * rows * (D / 8);
   if (n == 0) return 0;
-  kv_cache_move_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (bf16*)k_cache, (bf16*)v_cache, (const int*)src, (const int*)dst, (const int*)enable, B, H, D, cap, rows);
-  KSA_CHECK_CUDA(cudaGetLastError());
+  KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), kv_cache_move_kernel, dim3((unsigned)((n + 255) / 256)),
+                              dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), (bf16*)k_cache, (bf16*)v_cache,
+                              (const int*)src, (const int*)dst, (const int*)enable, B, H, D, cap, rows));
   return 0;
 }

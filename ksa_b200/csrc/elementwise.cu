@@ -21,6 +21,8 @@ __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, const bf16* __restrict__ w,
                    bf16* __restrict__ res_out, bf16* __restrict__ y, float* __restrict__ rstd_out, int rows, int D,
                    float eps, int delta_rows) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   __shared__ float red[32];
   const int row = blockIdx.x;
   if (row >= rows) return;
@@ -193,6 +195,8 @@ struct QkRopeArgs {
 
 template <int D>
 __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(QkRopeArgs a) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   constexpr int PAIRS = D / 64;  // rotary pairs per lane
   const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -370,6 +374,8 @@ __device__ __forceinline__ void rope_pair_idx(int p, int& i1, int& i2) {
 
 template <bool IL>
 __global__ void __launch_bounds__(256) qknorm_rope_fwd128_kernel(QkRopeArgs a) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= a.rows) return;
@@ -418,6 +424,70 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd128_kernel(QkRopeArgs a) {
       }
       dst[head * 64 + r.offA] = pack_bf16x2(o[0], o[1]);
       dst[head * 64 + r.offB] = pack_bf16x2(o[2], o[3]);
+    }
+  }
+}
+
+// A decode step has a handful of rows: one warp per (row, head) instead of one warp per row, v heads copied as well,
+// and the new K / V rows of the first `cache_rows` rows written straight into the KV cache [B, Hkv, cap, 128] at
+// slots[row] (row = sequence; negative slot: not cached).
+struct QkRopeCacheArgs {
+  bf16* k_cache;
+  bf16* v_cache;
+  const int* slots;
+  int cache_rows, cap;
+};
+
+template <bool IL>
+__global__ void __launch_bounds__(256) qknorm_rope_decode128_kernel(QkRopeArgs a, QkRopeCacheArgs c) {
+  grid_dependency_launch();
+  grid_dependency_wait();
+  const int H = a.Hq + a.Hkv, Hall = H + a.Hkv;
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= a.rows * Hall) return;
+  const int row = w / Hall, head = w - row * Hall;
+  const int offA = a.interleaved ? 2 * lane : lane, offB = a.interleaved ? 2 * lane + 1 : lane + 32;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(a.qkv + (long long)row * a.in_stride) + head * 64;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(a.out + (long long)row * a.out_stride) + head * 64;
+  uint32_t oa = src[offA], ob = src[offB];
+  if (head < H) {
+    const RopeLane r = rope_lane_setup(a, row, lane);
+    const float2 fa = unpack_bf16x2(oa), fb = unpack_bf16x2(ob);
+    float v[4] = {fa.x, fa.y, fb.x, fb.y};
+    float rstd = 1.f;
+    const bool has_w = head < a.Hq ? a.q_w != nullptr : a.k_w != nullptr;
+    if (has_w) {
+      const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+      rstd = rsqrtf(ss / 128.f + a.eps);
+    }
+    if (lane == 0 && a.rstd) a.rstd[(long long)row * H + head] = rstd;
+    const float* wn = head < a.Hq ? r.wq : r.wk;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = v[i] * rstd * wn[i];
+    float o[4];
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+      int i1, i2;
+      rope_pair_idx<IL>(p, i1, i2);
+      const float cs = p ? r.c1 : r.c0, sn = p ? r.s1 : r.s0;
+      o[i1] = v[i1] * cs - v[i2] * sn;
+      o[i2] = v[i2] * cs + v[i1] * sn;
+    }
+    oa = pack_bf16x2(o[0], o[1]);
+    ob = pack_bf16x2(o[2], o[3]);
+  }
+  dst[offA] = oa;
+  dst[offB] = ob;
+  if (head >= a.Hq && c.k_cache != nullptr && row < c.cache_rows) {
+    const int slot = c.slots[row];
+    if (slot >= 0) {
+      const bool is_v = head >= H;
+      const int kh = is_v ? head - H : head - a.Hq;
+      uint32_t* cd = reinterpret_cast<uint32_t*>(is_v ? c.v_cache : c.k_cache) +
+                     (((long long)row * a.Hkv + kh) * c.cap + slot) * 64;
+      cd[offA] = oa;
+      cd[offB] = ob;
     }
   }
 }
@@ -513,6 +583,8 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd128_kernel(QkRopeBwdArgs b
 // gate_up is [rows, 2F] = [gate | up]; out is [rows, F].
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long long rows, int F) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int per_row = F / 8;
   if (vec >= rows * per_row) return;
@@ -552,6 +624,8 @@ swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ dout, bf
 __global__ void __launch_bounds__(256)
 embedding_fwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ table, bf16* __restrict__ out,
                      long long rows, int D, long long vocab) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   const long long vec = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int per_row = D / 8;
   if (vec >= rows * per_row) return;
@@ -710,9 +784,9 @@ KSA_API int ksa_rmsnorm_fwd(const void* x, const void* delta, const void* w, voi
   KSA_REQUIRE(D % 8 == 0 && D <= kNormThreads * 8 * kNormMaxVec, "rmsnorm: D=%d must be a multiple of 8 and <= %d", D,
               kNormThreads * 8 * kNormMaxVec);
   if (rows == 0) return 0;
-  rmsnorm_fwd_kernel<<<rows, kNormThreads, 0, ST(stream)>>>((const bf16*)x, (const bf16*)delta, (const bf16*)w,
-                                                            (bf16*)res_out, (bf16*)y, (float*)rstd, rows, D, eps, delta_rows);
-  KSA_CHECK_CUDA(cudaGetLastError());
+  KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), rmsnorm_fwd_kernel, dim3(rows), dim3(kNormThreads), 0,
+                              ST(stream), (const bf16*)x, (const bf16*)delta, (const bf16*)w, (bf16*)res_out, (bf16*)y,
+                              (float*)rstd, rows, D, eps, delta_rows));
   return 0;
 }
 
@@ -761,10 +835,36 @@ KSA_API int ksa_qknorm_rope_fwd(const void* qkv, void* out, const void* q_w, con
                in_stride, out_stride, rows, Hq, Hkv, D, log2f(theta), eps, interleaved, copy_v};
   const long long warps = (long long)rows * (Hq + Hkv + (copy_v ? Hkv : 0));
   const int blocks = (int)((warps + 7) / 8);
-  if (D == 128 && interleaved) qknorm_rope_fwd128_kernel<true><<<(rows + 7) / 8, 256, 0, ST(stream)>>>(a);
-  else if (D == 128) qknorm_rope_fwd128_kernel<false><<<(rows + 7) / 8, 256, 0, ST(stream)>>>(a);
-  else qknorm_rope_fwd_kernel<64><<<blocks, 256, 0, ST(stream)>>>(a);
-  KSA_CHECK_CUDA(cudaGetLastError());
+  const bool dep = dependent_launch_enabled();
+  if (D == 128 && interleaved)
+    KSA_CHECK_CUDA(launch_kernel(dep, qknorm_rope_fwd128_kernel<true>, dim3((rows + 7) / 8), dim3(256), 0, ST(stream), a));
+  else if (D == 128)
+    KSA_CHECK_CUDA(launch_kernel(dep, qknorm_rope_fwd128_kernel<false>, dim3((rows + 7) / 8), dim3(256), 0, ST(stream), a));
+  else
+    KSA_CHECK_CUDA(launch_kernel(dep, qknorm_rope_fwd_kernel<64>, dim3(blocks), dim3(256), 0, ST(stream), a));
+  return 0;
+}
+
+// QK-norm + RoPE for the few rows of a decode step (head_dim 128): q | k | v rows -> out (same layout, v copied), and
+// K / V of rows [0, cache_rows) also into the KV cache [B, Hkv, cap, 128] at slots[row] (k_cache null: no cache).
+KSA_API int ksa_qknorm_rope_decode(const void* qkv, void* out, const void* q_w, const void* k_w, const void* pos,
+                                   long long in_stride, long long out_stride, int rows, int Hq, int Hkv, int D,
+                                   float theta, float eps, int interleaved, void* k_cache, void* v_cache,
+                                   const void* slots, int cache_rows, int cap, void* stream) {
+  KSA_ENTER(qkv);
+  KSA_REQUIRE(D == 128, "qknorm_rope_decode: head_dim %d unsupported (128)", D);
+  KSA_REQUIRE(k_cache == nullptr || (v_cache != nullptr && slots != nullptr && cache_rows <= rows && cap > 0),
+              "qknorm_rope_decode: cache arguments are incomplete");
+  if (rows == 0) return 0;
+  QkRopeArgs a{(const bf16*)qkv, (bf16*)out, (const bf16*)q_w, (const bf16*)k_w, (const int*)pos, nullptr,
+               in_stride, out_stride, rows, Hq, Hkv, D, log2f(theta), eps, interleaved, 1};
+  QkRopeCacheArgs c{(bf16*)k_cache, (bf16*)v_cache, (const int*)slots, cache_rows, cap};
+  const int warps = rows * (Hq + 2 * Hkv);
+  const bool dep = dependent_launch_enabled();
+  if (interleaved)
+    KSA_CHECK_CUDA(launch_kernel(dep, qknorm_rope_decode128_kernel<true>, dim3((warps + 7) / 8), dim3(256), 0, ST(stream), a, c));
+  else
+    KSA_CHECK_CUDA(launch_kernel(dep, qknorm_rope_decode128_kernel<false>, dim3((warps + 7) / 8), dim3(256), 0, ST(stream), a, c));
   return 0;
 }
 
@@ -798,8 +898,8 @@ KSA_API int ksa_swiglu_fwd(const void* gu, void* out, long long rows, int F, voi
   KSA_REQUIRE(F % 8 == 0, "swiglu: F=%d must be a multiple of 8", F);
   const long long n = rows * (F / 8);
   if (n == 0) return 0;
-  swiglu_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ST(stream)>>>((const bf16*)gu, (bf16*)out, rows, F);
-  KSA_CHECK_CUDA(cudaGetLastError());
+  KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), swiglu_fwd_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256),
+                              0, ST(stream), (const bf16*)gu, (bf16*)out, rows, F));
   return 0;
 }
 KSA_API int ksa_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long rows, int F, void* stream) {
@@ -819,9 +919,9 @@ KSA_API int ksa_embedding_fwd(const void* ids, const void* table, void* out, lon
   KSA_REQUIRE(D % 8 == 0, "embedding: D=%d must be a multiple of 8", D);
   const long long n = rows * (D / 8);
   if (n == 0) return 0;
-  embedding_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ST(stream)>>>((const long long*)ids, (const bf16*)table,
-                                                                           (bf16*)out, rows, D, vocab);
-  KSA_CHECK_CUDA(cudaGetLastError());
+  KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), embedding_fwd_kernel, dim3((unsigned)((n + 255) / 256)),
+                              dim3(256), 0, ST(stream), (const long long*)ids, (const bf16*)table, (bf16*)out, rows, D,
+                              vocab));
   return 0;
 }
 KSA_API int ksa_embedding_bwd(const void* ids, const void* dout, void* dtable_f32, long long rows, int D,

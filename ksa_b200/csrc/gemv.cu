@@ -3,6 +3,12 @@
 // cores: every CTA owns a slab of output columns small enough that the grid covers all SMs several times (a 128-row
 // MMA tile would leave N/256 = 10 CTAs busy for a 2560-wide projection), each warp streams whole weight rows with
 // 16-byte loads, the activation rows sit in shared memory, and the dot products are accumulated in fp32.
+//
+// A decode step is a chain of such kernels, each a few microseconds long, so the engine switches dependent launches
+// on (host.h): a CTA may then start while the previous kernel of the stream is still running, asks for its first
+// weight bytes (which no earlier kernel writes), and only then waits for the previous kernel (griddepcontrol.wait)
+// before it reads the activations.  The gate/up projection can apply SwiGLU itself (kGlu): a
+// warp (a CTA in the tensor-core variant) then owns matching gate and up rows and writes silu(gate) * up.
 #include "common.cuh"
 #include "host.h"
 
@@ -19,19 +25,47 @@ __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
   return v;
 }
 
-template <int MT, int R>
+// kGlu: B holds N/2 gate rows followed by N/2 up rows; weight row r of a warp is gate row f for even r and up row f
+// for odd r (f = first feature + r / 2), and C[m, f] = silu(gate) * up has N/2 columns.
+template <int MT, int R, bool kGlu>
 __global__ void __launch_bounds__(kGemvThreads)
 gemv_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, int M, int N, int K,
             long long lda, long long ldb, long long ldc) {
   extern __shared__ __align__(16) uint8_t gemv_smem[];
   bf16* sA = reinterpret_cast<bf16*>(gemv_smem);           // [MT][kGemvKTile]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = (blockIdx.x * (kGemvThreads / 32) + warp) * R;
+  const int n0 = (blockIdx.x * (kGemvThreads / 32) + warp) * (kGlu ? R / 2 : R);   // first row / first feature
+  const int n_out = kGlu ? N / 2 : N;
+  long long row_of[R];       // weight row of slot r, or -1 past the end
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int f = kGlu ? n0 + r / 2 : n0 + r;
+    row_of[r] = f < n_out ? (long long)(kGlu && (r & 1) ? n_out + f : f) : -1;
+  }
   float acc[R][MT];
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+
+  // U chunks of every row are requested before any is used, so that enough loads are in flight per SM
+  constexpr int U = (R >= 4) ? 2 : (R == 2 ? 4 : 8);
+  uint4 w[U][R];
+  auto load_w = [&](int k0, int kt, int c0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int c = c0 + u * 256;
+        w[u][r] = make_uint4(0, 0, 0, 0);
+        if (c < kt && row_of[r] >= 0) w[u][r] = ld_stream_16(B + row_of[r] * ldb + k0 + c);
+      }
+  };
+  // weights are never written by an earlier kernel of the stream: ask for the first chunks, then wait for the
+  // kernel that produces the activations
+  load_w(0, min(kGemvKTile, K), lane * 8);
+  grid_dependency_wait();
+  grid_dependency_launch();
 
   for (int k0 = 0; k0 < K; k0 += kGemvKTile) {
     const int kt = min(kGemvKTile, K - k0);          // multiple of 8
@@ -43,18 +77,8 @@ gemv_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __rest
       *reinterpret_cast<uint4*>(sA + m * kGemvKTile + c) = v;
     }
     __syncthreads();
-    // U chunks of every row are requested before any is used, so that enough loads are in flight per SM
-    constexpr int U = (R >= 4) ? 2 : (R == 2 ? 4 : 8);
     for (int c0 = lane * 8; c0 < kt; c0 += 256 * U) {
-      uint4 w[U][R];
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const int c = c0 + u * 256;
-          w[u][r] = make_uint4(0, 0, 0, 0);
-          if (c < kt && n0 + r < N) w[u][r] = ld_stream_16(B + (long long)(n0 + r) * ldb + k0 + c);
-        }
+      if (k0 != 0 || c0 != lane * 8) load_w(k0, kt, c0);      // the very first chunks are already on their way
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int c = c0 + u * 256;
@@ -80,26 +104,43 @@ gemv_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __rest
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-      const float v = warp_sum(acc[r][m]);
-      if (lane == 0 && m < M && n0 + r < N) C[(long long)m * ldc + n0 + r] = __float2bfloat16(v);
+    for (int m = 0; m < MT; ++m) acc[r][m] = warp_sum(acc[r][m]);
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < R; r += (kGlu ? 2 : 1)) {
+      const int f = kGlu ? n0 + r / 2 : n0 + r;
+      if (f >= n_out) break;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        if (m >= M) break;
+        float v = acc[r][m];
+        if (kGlu) {
+          // gate and up are rounded to bf16 first, as the separate projection + SwiGLU kernels do
+          const float g = __bfloat162float(__float2bfloat16(v));
+          const float u = __bfloat162float(__float2bfloat16(acc[r + (kGlu ? 1 : 0)][m]));
+          v = g / (1.f + __expf(-g)) * u;
+        }
+        C[(long long)m * ldc + f] = __float2bfloat16(v);
+      }
     }
+  }
 }
 
-template <int MT, int R>
+template <int MT, int R, bool kGlu>
 static int launch_gemv(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
                        long long ldc, cudaStream_t st) {
-  const int rows_per_cta = (kGemvThreads / 32) * R;
+  const int per_cta = (kGemvThreads / 32) * (kGlu ? R / 2 : R);      // output columns per CTA
+  const int n_out = kGlu ? N / 2 : N;
   const size_t smem = (size_t)MT * kGemvKTile * sizeof(bf16);
-  auto kern = gemv_kernel<MT, R>;
+  auto kern = gemv_kernel<MT, R, kGlu>;
   static bool attr = false;
   if (!attr && smem > 48 * 1024) {
     KSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = true;
   }
-  kern<<<(N + rows_per_cta - 1) / rows_per_cta, kGemvThreads, smem, st>>>((const bf16*)a, (const bf16*)b, (bf16*)c, M, N, K,
-                                                                          lda, ldb, ldc);
-  KSA_CHECK_CUDA(cudaGetLastError());
+  KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), kern, dim3((n_out + per_cta - 1) / per_cta),
+                              dim3(kGemvThreads), smem, st, (const bf16*)a, (const bf16*)b, (bf16*)c, M, N, K, lda, ldb,
+                              ldc));
   return 0;
 }
 
@@ -121,7 +162,8 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uin
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NB>   // batch blocks of 8 rows: 1 (M <= 8) or 2 (M <= 16)
+// kGlu: the CTA owns 8 features; its weight rows 0-7 are their gate rows and rows 8-15 their up rows.
+template <int NB, bool kGlu>   // batch blocks of 8 rows: 1 (M <= 8) or 2 (M <= 16)
 __global__ void __launch_bounds__(kGemvThreads)
 gemv_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, int M, int N, int K,
                 long long lda, long long ldb, long long ldc) {
@@ -130,13 +172,33 @@ gemv_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __
   float* sRed = reinterpret_cast<float*>(gemv_smem);                   // reused after the k loop: [8 warps][16][NB*8]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * 16;
-  const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);       // clamped: rows past N are never written
+  const int n_out = kGlu ? N / 2 : N;
+  const int n0 = blockIdx.x * (kGlu ? 8 : 16);
+  // clamped: rows past the end are never written
+  const int r0 = min(n0 + g, n_out - 1), r1 = kGlu ? n_out + r0 : min(n0 + g + 8, N - 1);
   float acc[NB][4];
 #pragma unroll
   for (int b = 0; b < NB; ++b)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[b][i] = 0.f;
+
+  // this warp's 32-wide blocks of a tile: warp, warp + 8, warp + 16, warp + 24; all weight loads first
+  uint4 w0[4], w1[4];
+  auto load_w = [&](int k0, int kt) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = (warp + 8 * u) * 32 + t * 8;
+      w0[u] = make_uint4(0, 0, 0, 0);
+      w1[u] = make_uint4(0, 0, 0, 0);
+      if (c < kt) {
+        w0[u] = ld_stream_16(B + (long long)r0 * ldb + k0 + c);
+        w1[u] = ld_stream_16(B + (long long)r1 * ldb + k0 + c);
+      }
+    }
+  };
+  load_w(0, min(kMmaKTile, K));     // weights do not depend on the previous kernel; the activations do
+  grid_dependency_wait();
+  grid_dependency_launch();
 
   for (int k0 = 0; k0 < K; k0 += kMmaKTile) {
     const int kt = min(kMmaKTile, K - k0);   // multiple of 32
@@ -148,18 +210,7 @@ gemv_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __
       *reinterpret_cast<uint4*>(sX + m * kMmaRowStride + c) = v;
     }
     __syncthreads();
-    // this warp's 32-wide blocks of the tile: warp, warp + 8, warp + 16, warp + 24; all weight loads first
-    uint4 w0[4], w1[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int c = (warp + 8 * u) * 32 + t * 8;
-      w0[u] = make_uint4(0, 0, 0, 0);
-      w1[u] = make_uint4(0, 0, 0, 0);
-      if (c < kt) {
-        w0[u] = ld_stream_16(B + (long long)r0 * ldb + k0 + c);
-        w1[u] = ld_stream_16(B + (long long)r1 * ldb + k0 + c);
-      }
-    }
+    if (k0 != 0) load_w(k0, kt);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int c = (warp + 8 * u) * 32 + t * 8;
@@ -184,25 +235,54 @@ gemv_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __
     dst[(g + 8) * NBATCH + b * 8 + 2 * t + 1] = acc[b][3];
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < 16 * NBATCH; i += kGemvThreads) {
-    const int row = i % 16, m = i / 16;          // consecutive threads -> consecutive output columns
-    float v = 0.f;
+  constexpr int kOutRows = kGlu ? 8 : 16;
+  for (int i = threadIdx.x; i < kOutRows * NBATCH; i += kGemvThreads) {
+    const int row = i % kOutRows, m = i / kOutRows;          // consecutive threads -> consecutive output columns
+    float v = 0.f, u = 0.f;
 #pragma unroll
-    for (int w = 0; w < kGemvThreads / 32; ++w) v += sRed[w * 16 * NBATCH + row * NBATCH + m];
-    if (m < M && n0 + row < N) C[(long long)m * ldc + n0 + row] = __float2bfloat16(v);
+    for (int w = 0; w < kGemvThreads / 32; ++w) {
+      v += sRed[w * 16 * NBATCH + row * NBATCH + m];
+      if (kGlu) u += sRed[w * 16 * NBATCH + (row + 8) * NBATCH + m];
+    }
+    if (kGlu) {
+      const float gt = __bfloat162float(__float2bfloat16(v)), up = __bfloat162float(__float2bfloat16(u));
+      v = gt / (1.f + __expf(-gt)) * up;
+    }
+    if (m < M && n0 + row < n_out) C[(long long)m * ldc + n0 + row] = __float2bfloat16(v);
   }
 }
 
-template <int NB>
+template <int NB, bool kGlu>
 static int launch_gemv_mma(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
                            long long ldc, cudaStream_t st) {
   const size_t smem = (size_t)NB * 8 * kMmaRowStride * sizeof(bf16);    // >= the 8 KB / 16 KB of the final reduction
-  gemv_mma_kernel<NB><<<(N + 15) / 16, kGemvThreads, smem, st>>>((const bf16*)a, (const bf16*)b, (bf16*)c, M, N, K, lda,
-                                                                 ldb, ldc);
-  KSA_CHECK_CUDA(cudaGetLastError());
+  const int per_cta = kGlu ? 8 : 16, n_out = kGlu ? N / 2 : N;
+  KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), gemv_mma_kernel<NB, kGlu>,
+                              dim3((n_out + per_cta - 1) / per_cta), dim3(kGemvThreads), smem, st, (const bf16*)a,
+                              (const bf16*)b, (bf16*)c, M, N, K, lda, ldb, ldc));
   return 0;
 }
 
+}  // namespace ksa
+
+namespace ksa {
+template <bool kGlu>
+static int gemv_dispatch(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, cudaStream_t st) {
+  if (M > 4 && K % 32 == 0) {
+    return M <= 8 ? launch_gemv_mma<1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st)
+                  : launch_gemv_mma<2, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
+  }
+  // rows per warp: fewer for narrow outputs so that the grid still covers every SM a few times (with SwiGLU a warp
+  // needs at least one gate row and one up row)
+  const bool narrow = N <= 8192;
+  constexpr int R1 = kGlu ? 2 : 1;
+  if (M == 1) return narrow ? launch_gemv<1, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<1, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
+  if (M <= 2) return narrow ? launch_gemv<2, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<2, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
+  if (M <= 4) return narrow ? launch_gemv<4, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<4, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
+  if (M <= 8) return narrow ? launch_gemv<8, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<8, 2, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
+  return narrow ? launch_gemv<16, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<16, 2, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
+}
 }  // namespace ksa
 
 // C[M, N] (bf16, ldc) = A[M, K] (bf16, lda) * B[N, K]^T (bf16, ldb) for 1 <= M <= 16; K, lda, ldb multiples of 8.
@@ -212,16 +292,17 @@ KSA_API int ksa_gemv_bf16(const void* a, const void* b, void* c, int M, int N, i
   using namespace ksa;
   KSA_REQUIRE(M >= 1 && M <= 16, "gemv: M=%d out of range (1..16)", M);
   KSA_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0, "gemv: K, lda, ldb must be multiples of 8");
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (M > 4 && K % 32 == 0) {
-    return M <= 8 ? launch_gemv_mma<1>(a, b, c, M, N, K, lda, ldb, ldc, st)
-                  : launch_gemv_mma<2>(a, b, c, M, N, K, lda, ldb, ldc, st);
-  }
-  // rows per warp: fewer for narrow outputs so that the grid still covers every SM a few times
-  const bool narrow = N <= 8192;
-  if (M == 1) return narrow ? launch_gemv<1, 1>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<1, 4>(a, b, c, M, N, K, lda, ldb, ldc, st);
-  if (M <= 2) return narrow ? launch_gemv<2, 1>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<2, 4>(a, b, c, M, N, K, lda, ldb, ldc, st);
-  if (M <= 4) return narrow ? launch_gemv<4, 1>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<4, 4>(a, b, c, M, N, K, lda, ldb, ldc, st);
-  if (M <= 8) return narrow ? launch_gemv<8, 1>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<8, 2>(a, b, c, M, N, K, lda, ldb, ldc, st);
-  return narrow ? launch_gemv<16, 1>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<16, 2>(a, b, c, M, N, K, lda, ldb, ldc, st);
+  return gemv_dispatch<false>(a, b, c, M, N, K, lda, ldb, ldc, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// The gate/up projection of a SwiGLU feed-forward block with its activation: B holds N/2 gate rows followed by N/2
+// up rows, C[M, N/2] = silu(A * gate^T) * (A * up^T), gate and up rounded to bf16 before the activation.
+KSA_API int ksa_gemv_swiglu_bf16(const void* a, const void* b, void* c, int M, int N, int K, long long lda,
+                                 long long ldb, long long ldc, void* stream) {
+  KSA_ENTER(a);
+  using namespace ksa;
+  KSA_REQUIRE(M >= 1 && M <= 16, "gemv_swiglu: M=%d out of range (1..16)", M);
+  KSA_REQUIRE(N > 0 && N % 2 == 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
+              "gemv_swiglu: N must be even and K, lda, ldb multiples of 8");
+  return gemv_dispatch<true>(a, b, c, M, N, K, lda, ldb, ldc, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -143,4 +143,16 @@ KSA_API int ksa_set_peer_wait_ms(int ms) {
   return cudaMemcpy(p + 1, &units, sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess ? 0 : -1;
 }
 
+namespace ksa {
+static bool g_dependent_launch = false;
+bool dependent_launch_enabled() { return g_dependent_launch; }
+}  // namespace ksa
+
+// Switch dependent launches of the decode-step kernels on (1) or off (0); returns the previous setting.
+KSA_API int ksa_set_dependent_launch(int on) {
+  const int before = ksa::g_dependent_launch ? 1 : 0;
+  ksa::g_dependent_launch = on != 0;
+  return before;
+}
+
 KSA_API int ksa_abi_version() { return 1; }

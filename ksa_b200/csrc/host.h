@@ -55,6 +55,28 @@ int ensure_device(const void* device_ptr);
     }                                                                                     \
   } while (0)
 
+// Dependent launches (programmatic stream serialization).  While the switch is on (ksa_set_dependent_launch), the
+// kernels of the decode step are launched so that each may start while its predecessor on the stream still runs;
+// every such kernel calls grid_dependency_wait() before it touches memory an earlier kernel may write.  Off by
+// default: training steps launch the same kernels the ordinary way.
+bool dependent_launch_enabled();
+
+template <typename Kern, typename... Args>
+inline cudaError_t launch_kernel(bool dependent, Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                 Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = dependent ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 #define KSA_REQUIRE(cond, ...)                  \
   do {                                          \
     if (!(cond)) {                              \

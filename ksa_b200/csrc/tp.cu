@@ -79,6 +79,8 @@ __device__ __forceinline__ void tp_reduce_rows(const TpReduceArgs& a, float* red
 }
 
 __global__ void __launch_bounds__(kTpThreads) tp_allreduce_add_rmsnorm_kernel(TpReduceArgs a, int* status) {
+  grid_dependency_launch();   // a dependent-launched successor may start (the skinny GEMM: its weight loads)
+  grid_dependency_wait();     // launched dependently itself: the previous kernel's results are complete from here on
   __shared__ float red[32];
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;

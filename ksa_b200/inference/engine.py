@@ -13,6 +13,7 @@ never reads device memory back; slice bounds and slots are computed on the devic
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
@@ -24,7 +25,7 @@ from .cache import (CacheSpec, CacheState, FullLayerCache, KsaLayerCache, flush_
                     text_step_slices)
 
 
-def _decode_attention(q, k_cache, v_cache, start, length, scale):
+def _decode_attention(q, k_cache, v_cache, start, length, scale, counters=None):
     """q ``[B, Tq, Hq, D]``; every (b, t) attends cache slots ``[start, start+length)``."""
     if not q.is_cuda:
         outs = [ref.decode_attention(q[:, t:t + 1], k_cache, v_cache, length[:, t].long(), start[:, t].long(), scale)
@@ -40,8 +41,12 @@ def _decode_attention(q, k_cache, v_cache, start, length, scale):
     part_o = torch.empty((B, Tq, Hq, splits, D), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((B, Tq, Hq, splits, 2), dtype=torch.float32, device=q.device)
     out = torch.empty_like(q)
+    # the split that finishes last merges the splits itself and puts its counter back to zero, so launches that
+    # follow one another on a stream can share ``counters`` (``[B * Hkv]`` int32 zeros; a fresh array when not given)
+    if counters is None:
+        counters = torch.zeros(B * Hkv, dtype=torch.int32, device=q.device)
     _lib.call("ksa_decode_attn", q.contiguous(), k_cache, v_cache, start.contiguous(), length.contiguous(), part_o,
-              part_ml, out, B, Tq, Hq, Hkv, D, cap, splits, keys_per_split, float(scale))
+              part_ml, out, B, Tq, Hq, Hkv, D, cap, splits, keys_per_split, float(scale), counters)
     return out
 
 
@@ -111,6 +116,7 @@ class KsaInferenceEngine:
         self.state = CacheState(batch, self.device)
         self.host_len = [0] * batch
         self._boundary_dev = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self._merge_counters = torch.zeros(batch * Hkv, dtype=torch.int32, device=self.device)
 
     def reserve(self, max_len: int) -> None:
         """Grow every layer's cache so that sequences may reach ``max_len`` tokens; contents are kept.  The cache layout
@@ -271,6 +277,17 @@ class KsaInferenceEngine:
     def _decode_impl(self, tokens: torch.Tensor, any_boundary: bool, with_head: bool = True) -> torch.Tensor:
         """Device work of one decode step (launches only; the host mirror of the lengths is advanced by the caller).
         ``any_boundary``: some sequence closes a chunk in this step; which ones is read from ``_boundary_dev``."""
+        if not tokens.is_cuda or os.environ.get("KSA_DEPENDENT_LAUNCH", "1") == "0":
+            return self._decode_body(tokens, any_boundary, with_head)
+        # a step is a chain of some four hundred kernels of a few microseconds each: launched dependently, each may
+        # start (and the projections fetch their first weights) while its predecessor is still running
+        before = _lib.set_dependent_launch(True)
+        try:
+            return self._decode_body(tokens, any_boundary, with_head)
+        finally:
+            _lib.set_dependent_launch(before)
+
+    def _decode_body(self, tokens: torch.Tensor, any_boundary: bool, with_head: bool = True) -> torch.Tensor:
         model, cfg = self.model, self.cfg
         tp = getattr(model, "tp", None)      # tensor-parallel shard: cfg holds the local head counts
         B, C, S = self.batch, self.C, self.S
@@ -313,18 +330,18 @@ class KsaInferenceEngine:
                     qkv = ops.dual_linear(h, a.wqkv.weight, w_s, B)
                 else:
                     qkv = ops.linear(h, a.wqkv.weight)
-                qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), pos_all, Hq, Hkv, Dh,
-                                              cfg.rope_base, cfg.norm_eps, cfg.rope_impl == "llama")
                 skey = (spec.chunk, spec.n_sum, spec.window, spec.max_chunks)
                 if skey not in slices_of:
                     slot_t, start_t, len_t = text_step_slices(spec, st)
-                    slices_of[skey] = (slot_t.view(B, 1), start_t.view(B, 1).to(torch.int32).contiguous(),
+                    slices_of[skey] = (slot_t.view(B, 1).to(torch.int32).contiguous(),
+                                       start_t.view(B, 1).to(torch.int32).contiguous(),
                                        len_t.view(B, 1).to(torch.int32).contiguous(), start_t, len_t)
                 slot_t1, start_t1, len_t1, start_t, len_t = slices_of[skey]
+                # norm + rotation of q / k, and the text tokens' K / V go into the cache in the same kernel
+                qkv = ops.qk_norm_rope_decode(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), pos_all, Hq, Hkv, Dh,
+                                              cfg.rope_base, cfg.norm_eps, cfg.rope_impl == "llama", cache.k, cache.v,
+                                              slot_t1)
                 q_t = qkv[:B, :Hq * Dh].view(B, 1, Hq, Dh)
-                k_t = qkv[:B, Hq * Dh:(Hq + Hkv) * Dh].view(B, 1, Hkv, Dh)
-                v_t = qkv[:B, (Hq + Hkv) * Dh:].view(B, 1, Hkv, Dh)
-                _cache_append(k_t, v_t, cache.k, cache.v, slot_t1)
                 if any_boundary:
                     slot_s, start_s, len_s = summary_step_slices(spec, B, dev)
                     off = torch.where(boundary[:, None] > 0, slot_s, torch.full_like(slot_s, -1))
@@ -335,7 +352,8 @@ class KsaInferenceEngine:
                     q_all = torch.cat([q_t, q_s], dim=1)
                     starts = torch.cat([start_t.view(B, 1), start_s], dim=1).to(torch.int32)
                     lens = torch.cat([len_t.view(B, 1), len_s * boundary[:, None]], dim=1).to(torch.int32)
-                    att = _decode_attention(q_all, cache.k, cache.v, starts, lens, scale)     # [B, 1+S, Hq, Dh]
+                    att = _decode_attention(q_all, cache.k, cache.v, starts, lens, scale,
+                                            self._merge_counters)                             # [B, 1+S, Hq, Dh]
                     att = torch.cat([att[:, 0].reshape(B, Hq * Dh), att[:, 1:].reshape(B * S, Hq * Dh)], dim=0)
                     # flush: chunk text -> ring, scratch summaries -> summary region (boundary sequences only)
                     src_t, dst_t, src_s, dst_s = flush_plan(spec, st)
@@ -343,21 +361,20 @@ class KsaInferenceEngine:
                         _cache_move(cache.k, cache.v, src_t, dst_t, boundary, C)
                     _cache_move(cache.k, cache.v, src_s, dst_s, boundary, S)
                 else:
-                    att = _decode_attention(q_t, cache.k, cache.v, start_t1, len_t1, scale).reshape(B, Hq * Dh)
+                    att = _decode_attention(q_t, cache.k, cache.v, start_t1, len_t1, scale,
+                                            self._merge_counters).reshape(B, Hq * Dh)
                 attn_out = _row_linear(tp, att, a.output_proj.weight)
                 x, h2 = _add_norm(tp, x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
                 delta = layer.mlp(h2, tp)
             else:
                 qkv = ops.linear(h[:B], a.wqkv.weight)
-                qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), pos_all[:B], Hq, Hkv, Dh,
-                                              cfg.rope_base, cfg.norm_eps, cfg.rope_impl == "llama")
+                qkv = ops.qk_norm_rope_decode(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), pos_all[:B], Hq, Hkv, Dh,
+                                              cfg.rope_base, cfg.norm_eps, cfg.rope_impl == "llama", cache.k, cache.v,
+                                              st.text_len)
                 q_t = qkv[:, :Hq * Dh].view(B, 1, Hq, Dh)
-                k_t = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(B, 1, Hkv, Dh)
-                v_t = qkv[:, (Hq + Hkv) * Dh:].view(B, 1, Hkv, Dh)
-                _cache_append(k_t, v_t, cache.k, cache.v, st.text_len.view(B, 1))
                 zeros = torch.zeros(B, 1, dtype=torch.int32, device=dev)
                 att = _decode_attention(q_t, cache.k, cache.v, zeros, (st.text_len + 1).view(B, 1).to(torch.int32),
-                                        scale).reshape(B, Hq * Dh)
+                                        scale, self._merge_counters).reshape(B, Hq * Dh)
                 attn_out = _row_linear(tp, att, a.output_proj.weight)
                 x, h2 = _add_norm(tp, x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
                 delta = layer.mlp(h2[:B], tp)

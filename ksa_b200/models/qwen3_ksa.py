@@ -119,7 +119,11 @@ class SwiGluMlp(nn.Module):
         self.w2 = FusedLinear(hidden, dim)
 
     def forward(self, x, tp=None, residual_rows: Optional[int] = None):
-        return _row_linear(tp, ops.swiglu(_col_linear(tp, x, self.w13.weight)), self.w2.weight, residual_rows)
+        if x.dim() == 2 and x.shape[0] <= 16 and (tp is None or getattr(tp, "_pending", None) is None):
+            h = ops.linear_swiglu(x, self.w13.weight)       # decode: projection and activation in one kernel
+        else:
+            h = ops.swiglu(_col_linear(tp, x, self.w13.weight))
+        return _row_linear(tp, h, self.w2.weight, residual_rows)
 
 
 class KsaDecoderLayer(nn.Module):

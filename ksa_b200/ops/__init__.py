@@ -394,6 +394,32 @@ def qk_norm_rope_packed(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opt
     return _QkNormRopeFn.apply(qkv, q_w, k_w, pos.to(torch.int32), Hq, Hkv, D, theta, eps, interleaved)
 
 
+def qk_norm_rope_decode(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                        pos: torch.Tensor, Hq: int, Hkv: int, D: int, theta: float, eps: float, interleaved: bool,
+                        k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """``qk_norm_rope_packed`` for the few rows of a decode step, with the cache append in the same kernel: the new K
+    and V of row ``i < len(slots)`` (sequence ``i``) also go to ``k_cache`` / ``v_cache`` ``[B, Hkv, cap, D]`` at slot
+    ``slots[i]`` (negative: not cached).  Inference only (no autograd)."""
+    n = slots.numel()
+    if _cuda(qkv) and D == 128 and qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1:
+        T = qkv.shape[0]
+        out = torch.empty((T, (Hq + 2 * Hkv) * D), dtype=qkv.dtype, device=qkv.device)
+        sl = slots.reshape(-1)
+        sl = sl if sl.dtype == torch.int32 and sl.is_contiguous() else sl.to(torch.int32).contiguous()
+        _lib.call("ksa_qknorm_rope_decode", qkv, out, q_w, k_w, pos.to(torch.int32), qkv.stride(0), out.stride(0), T, Hq,
+                  Hkv, D, float(theta), float(eps), int(interleaved), k_cache, v_cache, sl, n, k_cache.shape[2])
+        return out
+    out = qk_norm_rope_packed(qkv, q_w, k_w, pos, Hq, Hkv, D, theta, eps, interleaved)
+    k = out[:n, Hq * D:(Hq + Hkv) * D].reshape(n, Hkv, D)
+    v = out[:n, (Hq + Hkv) * D:].reshape(n, Hkv, D)
+    sl = slots.reshape(-1).tolist()
+    for i, s_ in enumerate(sl):
+        if s_ >= 0:
+            k_cache[i, :, s_] = k[i]
+            v_cache[i, :, s_] = v[i]
+    return out
+
+
 # =============================================================================== SwiGLU
 class _SwiGluFn(torch.autograd.Function):
     @staticmethod
@@ -423,6 +449,22 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     _require_bf16(gate_up)
     gate_up = gate_up if gate_up.is_contiguous() else gate_up.contiguous()
     return _SwiGluFn.apply(gate_up)
+
+
+def linear_swiglu(x: torch.Tensor, w13: torch.Tensor) -> torch.Tensor:
+    """``swiglu(x @ w13.T)`` with ``w13 = [gate rows | up rows]``.  For at most 16 rows on a GPU without autograd (a
+    decode step) the projection applies the activation itself (one kernel, ``ksa_gemv_swiglu_bf16``); everything else
+    is the projection followed by ``swiglu``."""
+    if (_cuda(x) and x.dim() == 2 and x.shape[0] <= 16 and x.dtype == torch.bfloat16 and w13.dtype == torch.bfloat16
+            and not (torch.is_grad_enabled() and (x.requires_grad or w13.requires_grad))
+            and x.stride(1) == 1 and w13.stride(1) == 1 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and w13.stride(0) % 8 == 0 and w13.shape[0] % 2 == 0):
+        M, K = x.shape
+        N = w13.shape[0]
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        _lib.call("ksa_gemv_swiglu_bf16", x, w13, out, M, N, K, x.stride(0), w13.stride(0), out.stride(0))
+        return out
+    return swiglu(linear(x, w13))
 
 
 # =============================================================================== embedding
@@ -863,7 +905,7 @@ def adamw_step(master, grad, m, v, out_bf16, hyper, beta1, beta2, eps, weight_de
 
 
 __all__ = [
-    "gemm", "linear", "dual_linear", "attention_packed", "rms_norm", "add_rms_norm", "qk_norm_rope_packed", "swiglu", "embedding",
+    "gemm", "linear", "dual_linear", "attention_packed", "rms_norm", "add_rms_norm", "qk_norm_rope_packed", "qk_norm_rope_decode", "swiglu", "linear_swiglu", "embedding",
     "ksa_attention", "causal_attention", "linear_cross_entropy", "adamw_step", "UNBOUNDED_WINDOW",
     "SummaryLayout", "get_layout",
 ]

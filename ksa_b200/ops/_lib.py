@@ -27,9 +27,11 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_gemm2_gather_bf16": [P, P, P, I, I, I, L, L, L, I, I, F, P, I, I, L, P, P, ctypes.c_uint, P, I, L, P],
     "ksa_gemm2_scatter_bf16": [P, P, I, I, I, L, L, L, P, I, I, P],
     "ksa_gemv_bf16": [P, P, P, I, I, I, L, L, L, P],
+    "ksa_gemv_swiglu_bf16": [P, P, P, I, I, I, L, L, L, P],
     "ksa_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, I, P],
     "ksa_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
     "ksa_qknorm_rope_fwd": [P, P, P, P, P, P, L, L, I, I, I, I, F, F, I, I, P],
+    "ksa_qknorm_rope_decode": [P, P, P, P, P, L, L, I, I, I, I, F, F, I, P, P, P, I, I, P],
     "ksa_qknorm_rope_bwd": [P, P, P, P, P, P, P, P, P, L, L, I, I, I, I, F, F, I, I, P],
     "ksa_swiglu_fwd": [P, P, L, I, P],
     "ksa_swiglu_bwd": [P, P, P, L, I, P],
@@ -48,7 +50,7 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_cp_fold_return": [P, P, I, I, I, L, L, L, L, P, I, ctypes.c_uint, P],
     "ksa_summary_attn_fwd": [P] * 7 + [I] * 6 + [L] * 12 + [I] * 5 + [F, P],
     "ksa_summary_attn_bwd": [P] * 13 + [I] * 6 + [L] * 22 + [I] * 5 + [F, P, P, I, P],
-    "ksa_decode_attn": [P] * 8 + [I] * 8 + [F, P],
+    "ksa_decode_attn": [P] * 8 + [I] * 8 + [F, P, P],
     "ksa_kv_cache_append": [P] * 5 + [I] * 5 + [L, L, P],
     "ksa_kv_cache_move": [P] * 5 + [I] * 5 + [P],
     "ksa_peer_gather": [P, I, I, L, I, P, P, ctypes.c_uint, I, P],
@@ -92,6 +94,8 @@ def load() -> ctypes.CDLL:
     lib.ksa_rmsnorm_bwd_parts.restype = I
     lib.ksa_attn_bwd_num_segments.argtypes = [I]
     lib.ksa_attn_bwd_num_segments.restype = I
+    lib.ksa_set_dependent_launch.argtypes = [I]
+    lib.ksa_set_dependent_launch.restype = I
     for name, sig in _SIGNATURES.items():
         fn = getattr(lib, name, None)
         if fn is not None:
@@ -216,6 +220,13 @@ def set_peer_wait_ms(ms: int) -> None:
     """Limit of device-side waits on flags written by other GPUs (current device; default 10 s, or KSA_PEER_WAIT_MS)."""
     if load().ksa_set_peer_wait_ms(int(ms)) != 0:
         raise RuntimeError("could not set the peer wait limit")
+
+
+def set_dependent_launch(on: bool) -> bool:
+    """Switch dependent launches of the decode-step kernels (programmatic stream serialization: a kernel may start
+    while its predecessor on the stream still runs and waits for it on the device) on or off; returns the previous
+    setting.  The inference engine switches it on around a decode step; training leaves it off."""
+    return load().ksa_set_dependent_launch(1 if on else 0) != 0
 
 
 GATHER_COUNTERS = 32   # int32 completion counters a ``ksa_gemm2_gather_bf16`` launch uses (8 shards x 4 segments)

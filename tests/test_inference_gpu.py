@@ -4,6 +4,7 @@ import copy
 import pytest
 import torch
 
+from ksa_b200 import ops
 from ksa_b200.config import get_preset
 from ksa_b200.inference import KsaInferenceEngine
 from ksa_b200.inference.engine import _cache_append, _cache_move, _decode_attention
@@ -46,6 +47,33 @@ def test_cache_append_and_move():
     en = torch.tensor([1, 0], device="cuda", dtype=torch.int32)
     _cache_move(kc, vc, src, dst, en, 3)
     assert torch.equal(kc[0, :, 20:23], kc[0, :, 5:8]) and kc[1, :, 30:33].abs().sum() == 0
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("rows,cached,interleaved", [(1, 1, False), (4, 4, False), (6, 4, True), (18, 16, False)])
+def test_decode_norm_rope_with_cache_append(rows, cached, interleaved):
+    """The decode form of QK-norm + RoPE (one warp per row and head, K / V of the first ``cached`` rows written into
+    the cache) against the training form followed by a separate append."""
+    Hq, Hkv, D, cap = 8, 2, 128, 40
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    qkv = torch.randn(rows, (Hq + 2 * Hkv) * D, device="cuda", generator=g).bfloat16()
+    qw = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).bfloat16()
+    pos = torch.randint(0, 5000, (rows,), device="cuda", generator=g).int()
+    slots = torch.randint(0, cap, (cached,), device="cuda", generator=g).int()
+    slots[-1] = -1                                                       # this sequence's row is not cached
+    kc = torch.zeros(cached, Hkv, cap, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    with torch.no_grad():
+        expect = ops.qk_norm_rope_packed(qkv, qw, kw, pos, Hq, Hkv, D, 1e6, 1e-6, interleaved)
+        out = ops.qk_norm_rope_decode(qkv, qw, kw, pos, Hq, Hkv, D, 1e6, 1e-6, interleaved, kc, vc, slots)
+    assert torch.equal(out, expect)
+    ke, ve = torch.zeros_like(kc), torch.zeros_like(vc)
+    for i, s_ in enumerate(slots.tolist()):
+        if s_ >= 0:
+            ke[i, :, s_] = expect[i, Hq * D:(Hq + Hkv) * D].view(Hkv, D)
+            ve[i, :, s_] = expect[i, (Hq + Hkv) * D:].view(Hkv, D)
+    assert torch.equal(kc, ke) and torch.equal(vc, ve)
     _lib.check_status()
 
 

@@ -83,6 +83,33 @@ def test_skinny_gemm_for_decoding(M, N, K):
     check(c, A.float() @ B.float().t(), 1e-2, f"skinny gemm {M}x{N}x{K}")
 
 
+@pytest.mark.parametrize("M", [1, 2, 4, 7, 16])
+@pytest.mark.parametrize("F,K", [(1280, 2560), (9728, 2560), (136, 4096)])
+def test_skinny_gate_up_projection_with_swiglu(M, F, K):
+    """The decode step's gate/up projection applies SwiGLU itself: one launch, equal to projection + activation
+    (gate and up rounded to bf16 in between, as the two separate kernels do)."""
+    x = bf(M, K)
+    w13 = bf(2 * F, K, scale=0.05)
+    before = _lib.launch_count()
+    with torch.no_grad():
+        h = ops.linear_swiglu(x, w13)
+    assert _lib.launch_count() == before + 1 and h.shape == (M, F)
+    gu = (x.float() @ w13.float().t()).bfloat16().float()
+    expect = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    check(h, expect, 1.5e-2, f"gemv swiglu {M}x{2 * F}x{K}")
+    # a chain of dependent-launched kernels on one stream: each reads the previous one's output
+    w2 = bf(K, F, scale=0.002)     # small enough that the chain does not grow
+    with torch.no_grad():
+        y = x
+        for _ in range(4):
+            y = ops.linear(ops.linear_swiglu(y, w13), w2)
+    yr = x.float()
+    for _ in range(4):
+        gu = (yr @ w13.float().t()).bfloat16().float()
+        yr = ((torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]).bfloat16().float() @ w2.float().t()).bfloat16().float()
+    check(y, yr, 5e-2, "dependent-launch chain")
+
+
 def test_linear_autograd():
     x = bf(3, 200, 256).requires_grad_()
     w = bf(384, 256, scale=0.05).requires_grad_()
