@@ -162,39 +162,51 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uin
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// kGlu: the CTA owns 8 features; its weight rows 0-7 are their gate rows and rows 8-15 their up rows.
-template <int NB, bool kGlu>   // batch blocks of 8 rows: 1 (M <= 8) or 2 (M <= 16)
-__global__ void __launch_bounds__(kGemvThreads)
+// A CTA owns RB blocks of 16 weight rows and stages the activations once for all of them (RB = 2 for wide outputs:
+// the activation tile is as large as 16 weight rows, so with one block a CTA would read as many activation bytes
+// from L2 as weight bytes from HBM).  kGlu: a block is 8 features, rows 0-7 their gate rows and rows 8-15 their up
+// rows.
+template <int NB, bool kGlu, int RB>   // NB: batch blocks of 8 rows, 1 (M <= 8) or 2 (M <= 16)
+__global__ void __launch_bounds__(kGemvThreads, 2)
 gemv_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, int M, int N, int K,
                 long long lda, long long ldb, long long ldc) {
   extern __shared__ __align__(16) uint8_t gemv_smem[];
   bf16* sX = reinterpret_cast<bf16*>(gemv_smem);                       // [NB*8][kMmaRowStride]
-  float* sRed = reinterpret_cast<float*>(gemv_smem);                   // reused after the k loop: [8 warps][16][NB*8]
+  float* sRed = reinterpret_cast<float*>(gemv_smem);                   // reused after the k loop: [8 warps][RB*16][NB*8]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n_out = kGlu ? N / 2 : N;
-  const int n0 = blockIdx.x * (kGlu ? 8 : 16);
-  // clamped: rows past the end are never written
-  const int r0 = min(n0 + g, n_out - 1), r1 = kGlu ? n_out + r0 : min(n0 + g + 8, N - 1);
-  float acc[NB][4];
+  constexpr int kBlockOut = kGlu ? 8 : 16;                              // output columns per row block
+  const int n0 = blockIdx.x * kBlockOut * RB;
+  int r0[RB], r1[RB];                                                   // clamped: rows past the end are never written
 #pragma unroll
-  for (int b = 0; b < NB; ++b)
+  for (int rb = 0; rb < RB; ++rb) {
+    r0[rb] = min(n0 + rb * kBlockOut + g, n_out - 1);
+    r1[rb] = kGlu ? n_out + r0[rb] : min(n0 + rb * 16 + g + 8, N - 1);
+  }
+  float acc[RB][NB][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[b][i] = 0.f;
+  for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[rb][b][i] = 0.f;
 
   // this warp's 32-wide blocks of a tile: warp, warp + 8, warp + 16, warp + 24; all weight loads first
-  uint4 w0[4], w1[4];
+  uint4 w0[RB][4], w1[RB][4];
   auto load_w = [&](int k0, int kt) {
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int c = (warp + 8 * u) * 32 + t * 8;
-      w0[u] = make_uint4(0, 0, 0, 0);
-      w1[u] = make_uint4(0, 0, 0, 0);
-      if (c < kt) {
-        w0[u] = ld_stream_16(B + (long long)r0 * ldb + k0 + c);
-        w1[u] = ld_stream_16(B + (long long)r1 * ldb + k0 + c);
+    for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = (warp + 8 * u) * 32 + t * 8;
+        w0[rb][u] = make_uint4(0, 0, 0, 0);
+        w1[rb][u] = make_uint4(0, 0, 0, 0);
+        if (c < kt) {
+          w0[rb][u] = ld_stream_16(B + (long long)r0[rb] * ldb + k0 + c);
+          w1[rb][u] = ld_stream_16(B + (long long)r1[rb] * ldb + k0 + c);
+        }
       }
-    }
   };
   load_w(0, min(kMmaKTile, K));     // weights do not depend on the previous kernel; the activations do
   grid_dependency_wait();
@@ -218,46 +230,54 @@ gemv_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
         const uint4 x = *reinterpret_cast<const uint4*>(sX + (b * 8 + g) * kMmaRowStride + c);
-        mma_bf16_16x8x16(acc[b], w0[u].x, w1[u].x, w0[u].y, w1[u].y, x.x, x.y);
-        mma_bf16_16x8x16(acc[b], w0[u].z, w1[u].z, w0[u].w, w1[u].w, x.z, x.w);
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb) {
+          mma_bf16_16x8x16(acc[rb][b], w0[rb][u].x, w1[rb][u].x, w0[rb][u].y, w1[rb][u].y, x.x, x.y);
+          mma_bf16_16x8x16(acc[rb][b], w0[rb][u].z, w1[rb][u].z, w0[rb][u].w, w1[rb][u].w, x.z, x.w);
+        }
       }
     }
   }
-  // acc[b] = {C[g][2t], C[g][2t+1], C[g+8][2t], C[g+8][2t+1]} with rows = weight rows, columns = batch b*8 + ...
+  // acc[rb][b] = {C[g][2t], C[g][2t+1], C[g+8][2t], C[g+8][2t+1]}: rows = weight rows of block rb, columns = batch
   __syncthreads();
   constexpr int NBATCH = NB * 8;
+  constexpr int kRows = RB * 16;
 #pragma unroll
-  for (int b = 0; b < NB; ++b) {
-    float* dst = sRed + warp * 16 * NBATCH;
-    dst[g * NBATCH + b * 8 + 2 * t] = acc[b][0];
-    dst[g * NBATCH + b * 8 + 2 * t + 1] = acc[b][1];
-    dst[(g + 8) * NBATCH + b * 8 + 2 * t] = acc[b][2];
-    dst[(g + 8) * NBATCH + b * 8 + 2 * t + 1] = acc[b][3];
-  }
+  for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      float* dst = sRed + (warp * kRows + rb * 16) * NBATCH;
+      dst[g * NBATCH + b * 8 + 2 * t] = acc[rb][b][0];
+      dst[g * NBATCH + b * 8 + 2 * t + 1] = acc[rb][b][1];
+      dst[(g + 8) * NBATCH + b * 8 + 2 * t] = acc[rb][b][2];
+      dst[(g + 8) * NBATCH + b * 8 + 2 * t + 1] = acc[rb][b][3];
+    }
   __syncthreads();
-  constexpr int kOutRows = kGlu ? 8 : 16;
-  for (int i = threadIdx.x; i < kOutRows * NBATCH; i += kGemvThreads) {
-    const int row = i % kOutRows, m = i / kOutRows;          // consecutive threads -> consecutive output columns
+  for (int i = threadIdx.x; i < RB * kBlockOut * NBATCH; i += kGemvThreads) {
+    const int col = i % (RB * kBlockOut), m = i / (RB * kBlockOut);   // consecutive threads -> consecutive outputs
+    const int rb = col / kBlockOut, row = rb * 16 + col % kBlockOut;    // row inside the CTA's RB * 16 weight rows
     float v = 0.f, u = 0.f;
 #pragma unroll
     for (int w = 0; w < kGemvThreads / 32; ++w) {
-      v += sRed[w * 16 * NBATCH + row * NBATCH + m];
-      if (kGlu) u += sRed[w * 16 * NBATCH + (row + 8) * NBATCH + m];
+      v += sRed[(w * kRows + row) * NBATCH + m];
+      if (kGlu) u += sRed[(w * kRows + row + 8) * NBATCH + m];
     }
     if (kGlu) {
       const float gt = __bfloat162float(__float2bfloat16(v)), up = __bfloat162float(__float2bfloat16(u));
       v = gt / (1.f + __expf(-gt)) * up;
     }
-    if (m < M && n0 + row < n_out) C[(long long)m * ldc + n0 + row] = __float2bfloat16(v);
+    if (m < M && n0 + col < n_out) C[(long long)m * ldc + n0 + col] = __float2bfloat16(v);
   }
 }
 
-template <int NB, bool kGlu>
+template <int NB, bool kGlu, int RB>
 static int launch_gemv_mma(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
                            long long ldc, cudaStream_t st) {
-  const size_t smem = (size_t)NB * 8 * kMmaRowStride * sizeof(bf16);    // >= the 8 KB / 16 KB of the final reduction
-  const int per_cta = kGlu ? 8 : 16, n_out = kGlu ? N / 2 : N;
-  KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), gemv_mma_kernel<NB, kGlu>,
+  // the activation tile, reused for the final reduction [8 warps][RB * 16][NB * 8] floats
+  const size_t x_bytes = (size_t)NB * 8 * kMmaRowStride * sizeof(bf16), red_bytes = (size_t)8 * RB * 16 * NB * 8 * 4;
+  const size_t smem = x_bytes > red_bytes ? x_bytes : red_bytes;
+  const int per_cta = (kGlu ? 8 : 16) * RB, n_out = kGlu ? N / 2 : N;
+  KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), gemv_mma_kernel<NB, kGlu, RB>,
                               dim3((n_out + per_cta - 1) / per_cta), dim3(kGemvThreads), smem, st, (const bf16*)a,
                               (const bf16*)b, (bf16*)c, M, N, K, lda, ldb, ldc));
   return 0;
@@ -270,8 +290,11 @@ template <bool kGlu>
 static int gemv_dispatch(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
                          long long ldc, cudaStream_t st) {
   if (M > 4 && K % 32 == 0) {
-    return M <= 8 ? launch_gemv_mma<1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st)
-                  : launch_gemv_mma<2, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
+    if (N >= 16384)   // wide outputs: 32 weight rows per CTA still give every SM several CTAs
+      return M <= 8 ? launch_gemv_mma<1, kGlu, 2>(a, b, c, M, N, K, lda, ldb, ldc, st)
+                    : launch_gemv_mma<2, kGlu, 2>(a, b, c, M, N, K, lda, ldb, ldc, st);
+    return M <= 8 ? launch_gemv_mma<1, kGlu, 1>(a, b, c, M, N, K, lda, ldb, ldc, st)
+                  : launch_gemv_mma<2, kGlu, 1>(a, b, c, M, N, K, lda, ldb, ldc, st);
   }
   // rows per warp: fewer for narrow outputs so that the grid still covers every SM a few times (with SwiGLU a warp
   // needs at least one gate row and one up row)
