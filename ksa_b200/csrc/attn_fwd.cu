@@ -138,12 +138,21 @@ __device__ __forceinline__ void attn_fwd_body(const CUtensorMap& tmQ, const CUte
           const int kv_head = head0 / (sh.Hq / sh.Hkv);
           const TileRange tr = key_tiles_for_query_tile(sh, q_tile, b);
           const int total = tr.total();
-          if (it > 0 && !mbar_wait(q_empty, (it - 1) & 1, guard, kTimeoutStageEmpty)) break;
-          ++it;
-          mbar_expect_tx(q_full, heads_per_cta * S::kTile);
-          for (int t = 0; t < heads_per_cta; ++t)
-            load_tile<HD>(sQ + t * S::kTile, &tmQ, q_tile * 128, head0 + t, b, q_full);
+          // Q can only be replaced once the previous item's last S product has read it; the first K / V tiles of
+          // this item do not have to wait for that, so they are requested first and cross the item boundary in flight
+          bool q_loaded = false;
+          auto load_q = [&]() {
+            if (it > 0 && !mbar_wait(q_empty, (it - 1) & 1, guard, kTimeoutStageEmpty)) return false;
+            ++it;
+            mbar_expect_tx(q_full, heads_per_cta * S::kTile);
+            for (int t = 0; t < heads_per_cta; ++t)
+              load_tile<HD>(sQ + t * S::kTile, &tmQ, q_tile * 128, head0 + t, b, q_full);
+            q_loaded = true;
+            return true;
+          };
+          if (it == 0 && !load_q()) break;
           for (int j = 0; j < total && ok; ++j) {
+            if (!q_loaded && j == 2 && !load_q()) { ok = false; break; }
             const bool is_sum = j < tr.n_sum_tiles;
             const int kt = is_sum ? j : tr.text_first + (j - tr.n_sum_tiles);
             const CUtensorMap* mk = is_sum ? &tmKs : &tmK;
@@ -173,6 +182,7 @@ __device__ __forceinline__ void attn_fwd_body(const CUtensorMap& tmQ, const CUte
               load_tile<HD>(sKV + stage * S::kTile, kv == 0 ? mk : mv, row, kv_head, b, &kv_full[stage]);
             }
           }
+          if (ok && !q_loaded && !load_q()) ok = false;
         }
       }
     } else if (warp == 9) {
