@@ -235,55 +235,128 @@ __device__ __forceinline__ float dot_smem(const float* q_s, const uint32_t* row,
   return acc;
 }
 
-// grid (local chunks, Hkv, B); dynamic smem: K rows | V rows | q[nq][HD] | p[nq][nk_max]
-__global__ void __launch_bounds__(kSumThreads) summary_attn_fwd_fast_kernel(SumAttnArgs a, SumSmemLayout lay) {
+// Forward fast path.  grid (local chunks, Hkv, B), 256 threads.  The chunk's V rows are staged in shared memory
+// (every output column reads all of them); its K rows are read straight from global memory by the threads that
+// compute their dot products (two threads per key, half a row = eight 16-byte loads in flight each), so the K and V
+// traffic of a CTA overlaps, shared memory stays near 35 KB and all CTAs of an 8k sequence are resident at once.
+// The G*S queries of the group are served together: one pass over a key row yields all their scores, one warp per
+// query does the softmax, and the P V product runs with thread = (query, column).
+// dynamic smem: V rows [nk_max][HD] bf16 | q[nq][HD] fp32 | p[nq][nk_max] fp32
+constexpr int kSumFwdThreads = 256;
+constexpr int kSumFwdMaxQ = 8;
+
+template <int HD>
+__global__ void __launch_bounds__(kSumFwdThreads) summary_attn_fwd_fast_kernel(SumAttnArgs a, int nk_max) {
   extern __shared__ uint32_t smw[];
-  __shared__ float red[4];
-  const int G = a.Hq / a.Hkv, S = a.n_sum, HD = a.HD, nq = G * S;
-  uint32_t* k_s = smw;
-  uint32_t* v_s = k_s + lay.nk_max * lay.row_words;
-  float* q_s = reinterpret_cast<float*>(v_s + lay.nk_max * lay.row_words);
+  const int G = a.Hq / a.Hkv, S = a.n_sum, nq = G * S;
+  bf16* v_s = reinterpret_cast<bf16*>(smw);
+  float* q_s = reinterpret_cast<float*>(v_s + (size_t)nk_max * HD);
   float* p_s = q_s + nq * HD;
   const int ci = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int cg = a.chunk0 + ci;
   const int n_text = min(a.chunk, a.L - cg * a.chunk);
   const int text0 = cg * a.chunk - a.k_off, sum0 = cg * S - a.s_off;
   const int nk_all = n_text + S;
-  stage_rows(k_s, lay.row_words, a.k + (long long)b * a.k_bs + (long long)kvh * HD, a.k_rs,
-             a.ks + (long long)b * a.ks_bs + (long long)kvh * HD, a.ks_rs, n_text, nk_all, text0, sum0, HD);
-  stage_rows(v_s, lay.row_words, a.v + (long long)b * a.v_bs + (long long)kvh * HD, a.v_rs,
-             a.vs + (long long)b * a.vs_bs + (long long)kvh * HD, a.vs_rs, n_text, nk_all, text0, sum0, HD);
-  for (int idx = threadIdx.x; idx < nq * HD; idx += kSumThreads) {
+  const bf16* kt = a.k + (long long)b * a.k_bs + (long long)kvh * HD;
+  const bf16* ks = a.ks + (long long)b * a.ks_bs + (long long)kvh * HD;
+  const bf16* vt = a.v + (long long)b * a.v_bs + (long long)kvh * HD;
+  const bf16* vs = a.vs + (long long)b * a.vs_bs + (long long)kvh * HD;
+  // ---- V rows -> shared memory (requests first, four at a time per thread), queries -> fp32
+  constexpr int kVec = HD / 8;
+  for (int i0 = threadIdx.x; i0 < nk_all * kVec; i0 += kSumFwdThreads * 4) {
+    uint4 u[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = i0 + j * kSumFwdThreads;
+      if (idx < nk_all * kVec) {
+        const int kk = idx / kVec, v = idx % kVec;
+        u[j] = *reinterpret_cast<const uint4*>(key_row(vt, a.v_rs, vs, a.vs_rs, kk, n_text, text0, sum0) + v * 8);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = i0 + j * kSumFwdThreads;
+      if (idx < nk_all * kVec) *reinterpret_cast<uint4*>(v_s + (size_t)idx * 8) = u[j];
+    }
+  }
+  for (int idx = threadIdx.x; idx < nq * HD; idx += kSumFwdThreads) {
     const int qi = idx / HD, d = idx % HD;
     const int head = kvh * G + qi / S, row = ci * S + qi % S;
-    q_s[idx] = __bfloat162float(a.qs[(long long)b * a.qs_bs + (long long)row * a.qs_rs + (long long)head * HD + d]);
+    q_s[idx] = __bfloat162float(a.qs[(long long)b * a.qs_bs + (long long)row * a.qs_rs + (long long)head * HD + d]) * a.scale;
   }
   __syncthreads();
-  for (int qi = 0; qi < nq; ++qi) {
-    const int j = qi % S, head = kvh * G + qi / S, row = ci * S + j;
-    const int nk = n_text + j + 1;
-    float mx = -INFINITY;
-    for (int kk = threadIdx.x; kk < nk; kk += kSumThreads) {
-      const float sc = dot_smem(q_s + qi * HD, k_s + kk * lay.row_words, HD) * a.scale;
-      p_s[qi * lay.nk_max + kk] = sc;
-      mx = fmaxf(mx, sc);
+  // ---- scores: two threads per key, each half a row
+  {
+    const int half = threadIdx.x & 1;
+    // every thread of a warp runs the same number of rounds (the two halves of a key meet in a shuffle below)
+    for (int kk0 = 0; kk0 < nk_all; kk0 += kSumFwdThreads / 2) {
+      const int kk = kk0 + (threadIdx.x >> 1);
+      const bool valid = kk < nk_all;
+      const bf16* row = key_row(kt, a.k_rs, ks, a.ks_rs, valid ? kk : 0, n_text, text0, sum0) + half * (HD / 2);
+      uint4 u[HD / 16];
+#pragma unroll
+      for (int j = 0; j < HD / 16; ++j) u[j] = valid ? *reinterpret_cast<const uint4*>(row + j * 8) : make_uint4(0, 0, 0, 0);
+      float acc[kSumFwdMaxQ];
+#pragma unroll
+      for (int qi = 0; qi < kSumFwdMaxQ; ++qi) acc[qi] = 0.f;
+#pragma unroll
+      for (int j = 0; j < HD / 16; ++j) {
+        const uint32_t w[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = unpack_bf16x2(w[i]);
+          const int d = half * (HD / 2) + j * 8 + 2 * i;
+#pragma unroll
+          for (int qi = 0; qi < kSumFwdMaxQ; ++qi)
+            if (qi < nq) acc[qi] += q_s[qi * HD + d] * f.x + q_s[qi * HD + d + 1] * f.y;
+        }
+      }
+#pragma unroll
+      for (int qi = 0; qi < kSumFwdMaxQ; ++qi) {
+        if (qi < nq) {
+          const float sc = acc[qi] + __shfl_xor_sync(0xffffffffu, acc[qi], 1);
+          // summary query j sees the chunk's text keys and summary keys 0..j
+          if (half == 0 && valid) p_s[qi * nk_max + kk] = kk < n_text + (qi % S) + 1 ? sc : -INFINITY;
+        }
+      }
     }
-    mx = block_reduce_max128(mx, red);
+  }
+  __syncthreads();
+  // ---- softmax: one warp per query
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int qi = warp; qi < nq; qi += kSumFwdThreads / 32) {
+    float mx = -INFINITY;
+    for (int kk = lane; kk < nk_all; kk += 32) mx = fmaxf(mx, p_s[qi * nk_max + kk]);
+    mx = warp_max(mx);
     float sum = 0.f;
-    for (int kk = threadIdx.x; kk < nk; kk += kSumThreads) {
-      const float pr = __expf(p_s[qi * lay.nk_max + kk] - mx);
-      p_s[qi * lay.nk_max + kk] = pr;
+    for (int kk = lane; kk < nk_all; kk += 32) {
+      const float pr = __expf(p_s[qi * nk_max + kk] - mx);
+      p_s[qi * nk_max + kk] = pr;
       sum += pr;
     }
-    sum = block_reduce_sum128(sum, red);
+    sum = warp_sum(sum);
     const float inv = 1.f / sum;
-    for (int d = threadIdx.x; d < HD; d += kSumThreads) {
-      float acc = 0.f;
-      const bf16* vcol = reinterpret_cast<const bf16*>(v_s) + d;
-      for (int kk = 0; kk < nk; ++kk) acc += p_s[qi * lay.nk_max + kk] * __bfloat162float(vcol[kk * lay.row_words * 2]);
-      a.os[(long long)b * a.os_bs + (long long)row * a.os_rs + (long long)head * HD + d] = __float2bfloat16(acc * inv);
+    for (int kk = lane; kk < nk_all; kk += 32) p_s[qi * nk_max + kk] *= inv;
+    if (lane == 0 && a.lse) {
+      const int head = kvh * G + qi / S, row = ci * S + qi % S;
+      a.lse[((long long)b * a.Hq + head) * a.Nq + row] = mx + __logf(sum);
     }
-    if (threadIdx.x == 0 && a.lse) a.lse[((long long)b * a.Hq + head) * a.Nq + row] = mx + __logf(sum);
+  }
+  __syncthreads();
+  // ---- O = P V: thread = (query, pair of columns)
+  for (int idx = threadIdx.x; idx < nq * (HD / 2); idx += kSumFwdThreads) {
+    const int qi = idx / (HD / 2), d2 = idx % (HD / 2);
+    const uint32_t* vcol = reinterpret_cast<const uint32_t*>(v_s) + d2;
+    const float* pr = p_s + qi * nk_max;
+    float o0 = 0.f, o1 = 0.f;
+    for (int kk = 0; kk < nk_all; ++kk) {
+      const float2 f = unpack_bf16x2(vcol[(size_t)kk * (HD / 2)]);
+      o0 = fmaf(pr[kk], f.x, o0);
+      o1 = fmaf(pr[kk], f.y, o1);
+    }
+    const int head = kvh * G + qi / S, row = ci * S + qi % S;
+    *reinterpret_cast<uint32_t*>(a.os + (long long)b * a.os_bs + (long long)row * a.os_rs + (long long)head * HD + 2 * d2) =
+        pack_bf16x2(o0, o1);
   }
 }
 
@@ -413,17 +486,17 @@ KSA_API int ksa_summary_attn_fwd(const void* qs, const void* k, const void* v, c
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.HD = HD; a.Nq = Nq; a.L = L; a.chunk = chunk; a.n_sum = n_sum;
   a.chunk0 = chunk0; a.k_off = k_off; a.s_off = s_off; a.scale = scale;
   {
-    const int nq = (Hq / Hkv) * n_sum;
-    SumSmemLayout lay{chunk + n_sum, HD / 2 + 1};
-    const size_t fast_smem = 2 * lay.kv_bytes() + (size_t)nq * (HD + lay.nk_max) * sizeof(float);
-    if (fast_smem <= 160 * 1024) {
+    const int nq = (Hq / Hkv) * n_sum, nk_max = chunk + n_sum;
+    const size_t fast_smem = (size_t)nk_max * HD * sizeof(bf16) + (size_t)nq * (HD + nk_max) * sizeof(float);
+    if (HD == 128 && nq <= kSumFwdMaxQ && fast_smem <= 100 * 1024 && os_rs % 2 == 0) {
       static bool attr = false;
       if (!attr) {
-        KSA_CHECK_CUDA(cudaFuncSetAttribute(summary_attn_fwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        KSA_CHECK_CUDA(cudaFuncSetAttribute(summary_attn_fwd_fast_kernel<128>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
         attr = true;
       }
       dim3 fgrid(Nq / n_sum, Hkv, B);
-      summary_attn_fwd_fast_kernel<<<fgrid, kSumThreads, fast_smem, reinterpret_cast<cudaStream_t>(stream)>>>(a, lay);
+      summary_attn_fwd_fast_kernel<128><<<fgrid, kSumFwdThreads, fast_smem, reinterpret_cast<cudaStream_t>(stream)>>>(a, nk_max);
       KSA_CHECK_CUDA(cudaGetLastError());
       return 0;
     }
