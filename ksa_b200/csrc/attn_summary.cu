@@ -203,38 +203,8 @@ __global__ void __launch_bounds__(128) summary_attn_bwd_kernel(SumAttnArgs a) {
 
 
 // ------------------------------------------------------------------------------------------------
-// Fast path: one CTA per (chunk, KV head) stages the chunk's keys and values (text rows + summary rows) in shared
-// memory once, padded by one 32-bit word per row so that "thread = key" reads are bank-conflict free, and serves
-// all G*S summary queries of the group from there.
-constexpr int kSumThreads = 128;
-
-struct SumSmemLayout {
-  int nk_max, row_words;  // keys per chunk (C+S); 32-bit words per padded row (HD/2 + 1)
-  __host__ __device__ size_t kv_bytes() const { return (size_t)nk_max * row_words * 4; }
-};
-
-__device__ __forceinline__ void stage_rows(uint32_t* dst, int row_words, const bf16* text, long long t_rs,
-                                           const bf16* sum, long long s_rs, int n_text, int nk, int text0, int sum0,
-                                           int HD) {
-  const int vec_per_row = HD / 8;
-  for (int idx = threadIdx.x; idx < nk * vec_per_row; idx += kSumThreads) {
-    const int kk = idx / vec_per_row, v = idx % vec_per_row;
-    const bf16* row = key_row(text, t_rs, sum, s_rs, kk, n_text, text0, sum0);
-    const uint4 u = *reinterpret_cast<const uint4*>(row + v * 8);
-    uint32_t* d = dst + kk * row_words + v * 4;
-    d[0] = u.x; d[1] = u.y; d[2] = u.z; d[3] = u.w;
-  }
-}
-
-__device__ __forceinline__ float dot_smem(const float* q_s, const uint32_t* row, int HD) {
-  float acc = 0.f;
-  for (int w = 0; w < HD / 2; ++w) {
-    const float2 f = unpack_bf16x2(row[w]);
-    acc += q_s[2 * w] * f.x + q_s[2 * w + 1] * f.y;
-  }
-  return acc;
-}
-
+// Fast paths (head dim 128, at most 8 queries per KV group): one CTA per (chunk, KV head) serves all G*S summary
+// queries of the group.
 // Forward fast path.  grid (local chunks, Hkv, B), 256 threads.  The chunk's V rows are staged in shared memory
 // (every output column reads all of them); its K rows are read straight from global memory by the threads that
 // compute their dot products (two threads per key, half a row = eight 16-byte loads in flight each), so the K and V
@@ -360,71 +330,141 @@ __global__ void __launch_bounds__(kSumFwdThreads) summary_attn_fwd_fast_kernel(S
   }
 }
 
-// grid (local chunks, Hkv, B); dynamic smem: K rows | V rows | q[nq][HD] | do[nq][HD] | p[nq][nk_max] | ds[nq][nk_max]
-__global__ void __launch_bounds__(kSumThreads) summary_attn_bwd_fast_kernel(SumAttnArgs a, SumSmemLayout lay) {
+// Backward fast path.  grid (local chunks, Hkv, B), 256 threads, head dim 128.  Only the chunk's K rows are staged
+// (padded by 16 bytes per row: "two threads per key" reads of 16-byte vectors and "thread = column" reads of words
+// are both conflict-free); V rows are read straight from global memory by the threads that need their dot
+// products with dO.  The G*S queries of the group are served together.
+// dynamic smem: K rows [nk_max][HD + 8] bf16 | q[nq][HD] | do[nq][HD] | p[nq][nk_max] | ds[nq][nk_max] | delta, lse [2 nq]
+constexpr int kSumBwdThreads = 256;
+constexpr int kSumBwdMaxQ = 8;
+
+template <int HD>
+__global__ void __launch_bounds__(kSumBwdThreads) summary_attn_bwd_fast_kernel(SumAttnArgs a, int nk_max) {
   extern __shared__ uint32_t smw[];
-  __shared__ float red[4];
-  const int G = a.Hq / a.Hkv, S = a.n_sum, HD = a.HD, nq = G * S;
-  uint32_t* k_s = smw;
-  uint32_t* v_s = k_s + lay.nk_max * lay.row_words;
-  float* q_s = reinterpret_cast<float*>(v_s + lay.nk_max * lay.row_words);
+  constexpr int kRowElems = HD + 8;                   // padded K row, bf16 elements
+  const int G = a.Hq / a.Hkv, S = a.n_sum, nq = G * S;
+  bf16* k_s = reinterpret_cast<bf16*>(smw);
+  float* q_s = reinterpret_cast<float*>(k_s + (size_t)nk_max * kRowElems);
   float* do_s = q_s + nq * HD;
   float* p_s = do_s + nq * HD;
-  float* ds_s = p_s + nq * lay.nk_max;
+  float* ds_s = p_s + nq * nk_max;
+  float* dl_s = ds_s + nq * nk_max;                    // delta[nq], lse[nq]
   const int ci = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int cg = a.chunk0 + ci;
   const int n_text = min(a.chunk, a.L - cg * a.chunk);
   const int text0 = cg * a.chunk - a.k_off, sum0 = cg * S - a.s_off;
   const int nk_all = n_text + S;
-  stage_rows(k_s, lay.row_words, a.k + (long long)b * a.k_bs + (long long)kvh * HD, a.k_rs,
-             a.ks + (long long)b * a.ks_bs + (long long)kvh * HD, a.ks_rs, n_text, nk_all, text0, sum0, HD);
-  stage_rows(v_s, lay.row_words, a.v + (long long)b * a.v_bs + (long long)kvh * HD, a.v_rs,
-             a.vs + (long long)b * a.vs_bs + (long long)kvh * HD, a.vs_rs, n_text, nk_all, text0, sum0, HD);
-  __syncthreads();
-  for (int qi = 0; qi < nq; ++qi) {
-    const int j = qi % S, head = kvh * G + qi / S, row = ci * S + j;
+  const bf16* kt = a.k + (long long)b * a.k_bs + (long long)kvh * HD;
+  const bf16* ks = a.ks + (long long)b * a.ks_bs + (long long)kvh * HD;
+  const bf16* vt = a.v + (long long)b * a.v_bs + (long long)kvh * HD;
+  const bf16* vs = a.vs + (long long)b * a.vs_bs + (long long)kvh * HD;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // ---- K rows -> shared memory, four requests in flight per thread
+  constexpr int kVec = HD / 8;
+  for (int i0 = threadIdx.x; i0 < nk_all * kVec; i0 += kSumBwdThreads * 4) {
+    uint4 u[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = i0 + j * kSumBwdThreads;
+      if (idx < nk_all * kVec)
+        u[j] = *reinterpret_cast<const uint4*>(key_row(kt, a.k_rs, ks, a.ks_rs, idx / kVec, n_text, text0, sum0) + (idx % kVec) * 8);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = i0 + j * kSumBwdThreads;
+      if (idx < nk_all * kVec) *reinterpret_cast<uint4*>(k_s + (size_t)(idx / kVec) * kRowElems + (idx % kVec) * 8) = u[j];
+    }
+  }
+  // ---- q, dO -> fp32; delta = sum_d dO * O and the log-sum-exp, one warp per query
+  for (int qi = warp; qi < nq; qi += kSumBwdThreads / 32) {
+    const int head = kvh * G + qi / S, row = ci * S + qi % S;
     const long long qoff = (long long)b * a.qs_bs + (long long)row * a.qs_rs + (long long)head * HD;
     const long long ooff = (long long)b * a.os_bs + (long long)row * a.os_rs + (long long)head * HD;
     float part = 0.f;
-    for (int d = threadIdx.x; d < HD; d += kSumThreads) {
+    for (int d = lane; d < HD; d += 32) {
       q_s[qi * HD + d] = __bfloat162float(a.qs[qoff + d]);
       const float g_o = __bfloat162float(a.d_os[ooff + d]);
       do_s[qi * HD + d] = g_o;
       part += g_o * __bfloat162float(a.os[ooff + d]);
     }
-    const float delta = block_reduce_sum128(part, red);
-    const float lse = a.lse[((long long)b * a.Hq + head) * a.Nq + row];
-    const int nk = n_text + j + 1;
-    for (int kk = threadIdx.x; kk < lay.nk_max; kk += kSumThreads) {
-      float pr = 0.f, ds = 0.f;
-      if (kk < nk) {
-        const float sc = dot_smem(q_s + qi * HD, k_s + kk * lay.row_words, HD) * a.scale;
-        pr = __expf(sc - lse);
-        const float dp = dot_smem(do_s + qi * HD, v_s + kk * lay.row_words, HD);
-        ds = pr * (dp - delta) * a.scale;
-      }
-      p_s[qi * lay.nk_max + kk] = pr;
-      ds_s[qi * lay.nk_max + kk] = ds;
-    }
-    __syncthreads();
-    for (int d = threadIdx.x; d < HD; d += kSumThreads) {
-      float acc = 0.f;
-      const bf16* kcol = reinterpret_cast<const bf16*>(k_s) + d;
-      for (int kk = 0; kk < nk; ++kk) acc += ds_s[qi * lay.nk_max + kk] * __bfloat162float(kcol[kk * lay.row_words * 2]);
-      a.dqs[(long long)b * a.dqs_bs + (long long)row * a.dqs_rs + (long long)head * HD + d] = __float2bfloat16(acc);
+    part = warp_sum(part);
+    if (lane == 0) {
+      dl_s[qi] = part;
+      dl_s[nq + qi] = a.lse[((long long)b * a.Hq + head) * a.Nq + row];
     }
   }
   __syncthreads();
+  // ---- p and dS: two threads per key, each half of the K row (shared memory) and of the V row (global memory);
+  // every thread of a warp runs the same number of rounds, the two halves meet in a shuffle
+  {
+    const int half = threadIdx.x & 1;
+    for (int kk0 = 0; kk0 < nk_all; kk0 += kSumBwdThreads / 2) {
+      const int kk = kk0 + (threadIdx.x >> 1);
+      const bool valid = kk < nk_all;
+      const bf16* vrow = key_row(vt, a.v_rs, vs, a.vs_rs, valid ? kk : 0, n_text, text0, sum0) + half * (HD / 2);
+      const bf16* krow = k_s + (size_t)(valid ? kk : 0) * kRowElems + half * (HD / 2);
+      uint4 uv[HD / 16];
+#pragma unroll
+      for (int j = 0; j < HD / 16; ++j) uv[j] = valid ? *reinterpret_cast<const uint4*>(vrow + j * 8) : make_uint4(0, 0, 0, 0);
+      float sc[kSumBwdMaxQ], dp[kSumBwdMaxQ];
+#pragma unroll
+      for (int qi = 0; qi < kSumBwdMaxQ; ++qi) { sc[qi] = 0.f; dp[qi] = 0.f; }
+#pragma unroll
+      for (int j = 0; j < HD / 16; ++j) {
+        const uint4 uk = *reinterpret_cast<const uint4*>(krow + j * 8);
+        const uint32_t wk[4] = {uk.x, uk.y, uk.z, uk.w}, wv[4] = {uv[j].x, uv[j].y, uv[j].z, uv[j].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 fk = unpack_bf16x2(wk[i]), fv = unpack_bf16x2(wv[i]);
+          const int d = half * (HD / 2) + j * 8 + 2 * i;
+#pragma unroll
+          for (int qi = 0; qi < kSumBwdMaxQ; ++qi)
+            if (qi < nq) {
+              sc[qi] += q_s[qi * HD + d] * fk.x + q_s[qi * HD + d + 1] * fk.y;
+              dp[qi] += do_s[qi * HD + d] * fv.x + do_s[qi * HD + d + 1] * fv.y;
+            }
+        }
+      }
+#pragma unroll
+      for (int qi = 0; qi < kSumBwdMaxQ; ++qi) {
+        if (qi < nq) {
+          const float s2 = sc[qi] + __shfl_xor_sync(0xffffffffu, sc[qi], 1);
+          const float d2 = dp[qi] + __shfl_xor_sync(0xffffffffu, dp[qi], 1);
+          if (half == 0 && valid) {
+            const bool seen = kk < n_text + (qi % S) + 1;   // summary query j sees text keys and summary keys 0..j
+            const float pr = seen ? __expf(s2 * a.scale - dl_s[nq + qi]) : 0.f;
+            p_s[qi * nk_max + kk] = pr;
+            ds_s[qi * nk_max + kk] = pr * (d2 - dl_s[qi]) * a.scale;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // ---- dQ[qi][d] = sum_kk dS[qi][kk] K[kk][d]: thread = (query, pair of columns)
+  for (int idx = threadIdx.x; idx < nq * (HD / 2); idx += kSumBwdThreads) {
+    const int qi = idx / (HD / 2), d2 = idx % (HD / 2);
+    const uint32_t* kcol = reinterpret_cast<const uint32_t*>(k_s) + d2;
+    const float* dsr = ds_s + qi * nk_max;
+    float g0 = 0.f, g1 = 0.f;
+    for (int kk = 0; kk < nk_all; ++kk) {
+      const float2 f = unpack_bf16x2(kcol[(size_t)kk * (kRowElems / 2)]);
+      g0 = fmaf(dsr[kk], f.x, g0);
+      g1 = fmaf(dsr[kk], f.y, g1);
+    }
+    const int head = kvh * G + qi / S, row = ci * S + qi % S;
+    *reinterpret_cast<uint32_t*>(a.dqs + (long long)b * a.dqs_bs + (long long)row * a.dqs_rs + (long long)head * HD + 2 * d2) =
+        pack_bf16x2(g0, g1);
+  }
   // dK[kk][d] += sum_qi ds[qi][kk] q[qi][d];  dV[kk][d] += sum_qi p[qi][kk] do[qi][d]: eight columns (16 bytes) per
   // thread and read-modify-write, so that the two global round trips per key row are 16 accesses instead of 64
-  const int vecs = HD / 8;
-  for (int idx = threadIdx.x; idx < nk_all * vecs; idx += kSumThreads) {
-    const int kk = idx / vecs, d = (idx % vecs) * 8;
+  for (int idx = threadIdx.x; idx < nk_all * kVec; idx += kSumBwdThreads) {
+    const int kk = idx / kVec, d = (idx % kVec) * 8;
     float gk[8], gv[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) { gk[e] = 0.f; gv[e] = 0.f; }
     for (int qi = 0; qi < nq; ++qi) {
-      const float dsv = ds_s[qi * lay.nk_max + kk], pv = p_s[qi * lay.nk_max + kk];
+      const float dsv = ds_s[qi * nk_max + kk], pv = p_s[qi * nk_max + kk];
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         gk[e] += dsv * q_s[qi * HD + d + e];
@@ -535,16 +575,17 @@ KSA_API int ksa_summary_attn_bwd(const void* qs, const void* k, const void* v, c
   a.dks32 = (const float*)dks32; a.dvs32 = (const float*)dvs32; a.Ns_k = Ns_k;
   const int nq = (Hq / Hkv) * n_sum;
   {
-    SumSmemLayout lay{chunk + n_sum, HD / 2 + 1};
-    const size_t fast_smem = 2 * lay.kv_bytes() + (size_t)nq * (2 * HD + 2 * lay.nk_max) * sizeof(float);
-    if (fast_smem <= 160 * 1024) {
+    const int nk_max = chunk + n_sum;
+    const size_t fast_smem = (size_t)nk_max * (HD + 8) * sizeof(bf16) + (size_t)nq * (2 * HD + 2 * nk_max + 2) * sizeof(float);
+    if (HD == 128 && nq <= kSumBwdMaxQ && fast_smem <= 100 * 1024 && dqs_rs % 2 == 0) {
       static bool fattr = false;
       if (!fattr) {
-        KSA_CHECK_CUDA(cudaFuncSetAttribute(summary_attn_bwd_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        KSA_CHECK_CUDA(cudaFuncSetAttribute(summary_attn_bwd_fast_kernel<128>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
         fattr = true;
       }
       dim3 fgrid(Nq / n_sum, Hkv, B);
-      summary_attn_bwd_fast_kernel<<<fgrid, kSumThreads, fast_smem, reinterpret_cast<cudaStream_t>(stream)>>>(a, lay);
+      summary_attn_bwd_fast_kernel<128><<<fgrid, kSumBwdThreads, fast_smem, reinterpret_cast<cudaStream_t>(stream)>>>(a, nk_max);
       KSA_CHECK_CUDA(cudaGetLastError());
       return 0;
     }
