@@ -86,6 +86,7 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R) {
     float xh[R][NVEC][8], g[R][NVEC][8];
+    BF8 rr_raw[R][NVEC];      // the residual gradient, requested with x and dy so that it arrives under the reduction
     float dot[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -97,6 +98,7 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
         const int c = (i * kNormThreads + threadIdx.x) * 8;
         if (row < rows && c < D) {
           float xv[8], dyv[8];
+          if (dres) rr_raw[r][i] = *reinterpret_cast<const BF8*>(dres + (long long)row * D + c);
           load8(x + (long long)row * D + c, xv);
           load8(dy + (long long)row * D + c, dyv);
 #pragma unroll
@@ -136,10 +138,12 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] = rstd * (g[r][i][j] - xh[r][i][j] * mean);
           if (dres) {
-            float rr[8];
-            load8(dres + (long long)row * D + c, rr);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) o[j] += rr[j];
+            for (int j = 0; j < 4; ++j) {
+              const float2 t = unpack_bf16x2(rr_raw[r][i].u[j]);
+              o[2 * j] += t.x;
+              o[2 * j + 1] += t.y;
+            }
           }
           store8(dx + (long long)row * D + c, o);
         }
