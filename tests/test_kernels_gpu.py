@@ -71,7 +71,7 @@ def test_gemm_fp32_accumulate_and_strided_views():
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 16])
-@pytest.mark.parametrize("N,K", [(2560, 4096), (19456, 2560), (264, 9728), (151936, 2560)])
+@pytest.mark.parametrize("N,K", [(2560, 4096), (6144, 2560), (19456, 2560), (264, 9728), (151936, 2560)])
 def test_skinny_gemm_for_decoding(M, N, K):
     packed = bf(M, K + 64)
     A = packed[:, 32:32 + K]                # strided view with a 64-byte column offset
