@@ -144,97 +144,6 @@ static int launch_gemv(const void* a, const void* b, void* c, int M, int N, int 
   return 0;
 }
 
-// Narrow outputs (N <= 8192) with at most 4 activation rows: the kernel lasts a few microseconds and its length is
-// the number of memory round trips a warp makes, so a weight row is split between KS warps (each takes K / KS columns
-// in one or two rounds of eight 16-byte loads per lane) and the partial sums meet in shared memory.  The whole
-// activation block is staged once.
-template <int MT, int KS>
-__global__ void __launch_bounds__(kGemvThreads)
-gemv_splitk_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, int M, int N, int K,
-                   long long lda, long long ldb, long long ldc) {
-  extern __shared__ __align__(16) uint8_t gemv_smem[];
-  bf16* sA = reinterpret_cast<bf16*>(gemv_smem);                                  // [MT][Kp], Kp = K rounded up to 8
-  __shared__ float s_part[kGemvThreads / 32][MT];
-  constexpr int kWarps = kGemvThreads / 32, kRows = kWarps / KS;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * kRows + warp / KS, ks = warp % KS;
-  // this warp's columns: [k_lo, k_hi), multiples of 8
-  const int per = ((K / 8 + KS - 1) / KS) * 8;
-  const int k_lo = ks * per, k_hi = min(K, k_lo + per);
-  constexpr int U = 8;
-  uint4 w[U];
-  auto load_w = [&](int c0) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int c = c0 + u * 256;
-      w[u] = make_uint4(0, 0, 0, 0);
-      if (c < k_hi && n < N) w[u] = ld_stream_16(B + (long long)n * ldb + c);
-    }
-  };
-  load_w(k_lo + lane * 8);          // weights are never written by an earlier kernel of the stream
-  grid_dependency_wait();
-  grid_dependency_launch();
-  for (int i = threadIdx.x; i < MT * (K / 8); i += kGemvThreads) {
-    const int m = i / (K / 8), c = (i % (K / 8)) * 8;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (m < M) v = *reinterpret_cast<const uint4*>(A + (long long)m * lda + c);
-    *reinterpret_cast<uint4*>(sA + (size_t)m * K + c) = v;
-  }
-  __syncthreads();
-  float acc[MT];
-#pragma unroll
-  for (int m = 0; m < MT; ++m) acc[m] = 0.f;
-  for (int c0 = k_lo + lane * 8; c0 < k_hi; c0 += 256 * U) {
-    if (c0 != k_lo + lane * 8) load_w(c0);
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int c = c0 + u * 256;
-      if (c >= k_hi) break;
-      const uint32_t wu[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
-#pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        const uint4 a = *reinterpret_cast<const uint4*>(sA + (size_t)m * K + c);
-        const uint32_t au[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 x = unpack_bf16x2(au[q]), y = unpack_bf16x2(wu[q]);
-          acc[m] = fmaf(x.x, y.x, acc[m]);
-          acc[m] = fmaf(x.y, y.y, acc[m]);
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int m = 0; m < MT; ++m) acc[m] = warp_sum(acc[m]);
-  if (lane == 0) {
-#pragma unroll
-    for (int m = 0; m < MT; ++m) s_part[warp][m] = acc[m];
-  }
-  __syncthreads();
-  if (ks == 0 && lane < MT && lane < M && n < N) {
-    float v = 0.f;
-#pragma unroll
-    for (int j = 0; j < KS; ++j) v += s_part[warp + j][lane];
-    C[(long long)lane * ldc + n] = __float2bfloat16(v);
-  }
-}
-
-template <int MT, int KS>
-static int launch_gemv_splitk(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
-                              long long ldc, cudaStream_t st) {
-  constexpr int kRows = (kGemvThreads / 32) / KS;
-  const size_t smem = (size_t)MT * K * sizeof(bf16);
-  auto kern = gemv_splitk_kernel<MT, KS>;
-  static size_t attr = 48 * 1024;
-  if (smem > attr) {
-    KSA_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = smem;
-  }
-  KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), kern, dim3((N + kRows - 1) / kRows), dim3(kGemvThreads), smem, st,
-                              (const bf16*)a, (const bf16*)b, (bf16*)c, M, N, K, lda, ldb, ldc));
-  return 0;
-}
-
 // ------------------------------------------------------------------------------------------ tensor-core variant
 // For 5..16 activation rows the SIMT kernel above is bound by its FMA issue rate, so the dot products go to the tensor
 // cores with warp-level mma.sync m16n8k16 (the 128-row tcgen05 tile has no use for 16 rows): a CTA owns 16 weight
@@ -391,13 +300,6 @@ static int gemv_dispatch(const void* a, const void* b, void* c, int M, int N, in
   // needs at least one gate row and one up row)
   const bool narrow = N <= 8192;
   constexpr int R1 = kGlu ? 2 : 1;
-  if (!kGlu && narrow && M <= 4 && (size_t)4 * K * 2 <= 160 * 1024) {
-    // columns per warp after the split: one or two rounds of 2048
-    const bool four = K > 3072;
-    if (M == 1) return four ? launch_gemv_splitk<1, 4>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv_splitk<1, 2>(a, b, c, M, N, K, lda, ldb, ldc, st);
-    if (M <= 2) return four ? launch_gemv_splitk<2, 4>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv_splitk<2, 2>(a, b, c, M, N, K, lda, ldb, ldc, st);
-    return four ? launch_gemv_splitk<4, 4>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv_splitk<4, 2>(a, b, c, M, N, K, lda, ldb, ldc, st);
-  }
   if (M == 1) return narrow ? launch_gemv<1, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<1, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
   if (M <= 2) return narrow ? launch_gemv<2, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<2, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
   if (M <= 4) return narrow ? launch_gemv<4, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<4, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
