@@ -73,19 +73,12 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                : "memory");
 }
 
-// fp32 add of a [1 x 32 rows x 1 x 128] box in shared memory (row-major, 512-byte rows) into a 4-D fp32 tensor.
+// fp32 add of a box in shared memory (row-major, as the tensor map's box says: here 32 query rows of 32 head
+// dimensions, 128-byte rows) into a 4-D fp32 tensor.
 __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const void* src, int x, int y, int z, int w) {
   asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                ::"l"(m), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z), "r"(w)
                : "memory");
-}
-// Barrier of the 128 threads of one compute warpgroup on an mbarrier, so that the wait is bounded like every other
-// wait of the kernel (a `bar.sync` would wait for ever for a thread that has given up).
-__device__ __forceinline__ bool wg_sync(uint64_t* bar, uint32_t& phase, const WaitGuard& g) {
-  mbar_arrive(bar);
-  const bool ok = mbar_wait(bar, phase, g, kTimeoutPeerFlag);
-  phase ^= 1;
-  return ok;
 }
 
 // 32 score columns and 32 dP columns of one key row -> 16 packed P and 16 packed dS words.
@@ -175,8 +168,7 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
   uint64_t* dq_full = pds_full + 2;              // 2: dQ^T_h is in TMEM
   uint64_t* dq_drained = dq_full + 2;            // 2: dQ^T_h has been read out
   uint64_t* acc_full = dq_drained + 2;           // 1
-  uint64_t* wg_bar = acc_full + 1;               // 2: one per compute warpgroup
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(wg_bar + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -221,7 +213,6 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
       mbar_init(&pds_full[h], 128);
       mbar_init(&dq_full[h], 1);
       mbar_init(&dq_drained[h], 128);
-      mbar_init(&wg_bar[h], 128);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -364,7 +355,6 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
     uint8_t* ds_row = sDs + half * S::kHalfTile + r * 128;   // this key's row of dS^T_h (64 bf16, swizzled 16-byte chunks)
     const int sw = r & 7;
     bool ok = true;
-    uint32_t wg_phase = 0;
     for (int j = 0; j < total; ++j) {
       const int n = 2 * j + half, stage = n % kFbStages;
       const int qt = qr.first + j / G, head = kv_head * G + j % G;
@@ -388,9 +378,11 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
       tmem_ld32(tdPh + 32, d);
       tmem_st16(tSh, pk);
       tmem_st16(tSh + 32, dk);
-      // dS^T_h shares its buffer with the staging of the previous step's dQ^T_h: that reduction must have read it
-      if (r == 0) tma_store_wait_read0();
-      if (!wg_sync(&wg_bar[half], wg_phase, guard)) { ok = false; break; }
+      // This warp's 32 rows of dS^T_h (4 KB) are also where it stages its slab of the previous step's dQ^T_h: its own
+      // reductions must have read them.  Every warp stages and reduces its own 32 head dimensions, so the hand-offs
+      // inside the drain are warp-wide, not warpgroup-wide.
+      if (lane == 0) tma_store_wait_read0();
+      __syncwarp();
 #pragma unroll
       for (int c = 0; c < 4; ++c)
         *reinterpret_cast<uint4*>(ds_row + ((c ^ sw) << 4)) = make_uint4(dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
@@ -405,7 +397,7 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(&pds_full[half]);
-      // dQ^T_h: lane = head-dim index r, 64 query columns; add them into the fp32 buffer (32 lanes = one 128-byte line)
+      // dQ^T_h: lane = head-dim index r, 64 query columns
       if (!mbar_wait(&dq_full[half], j & 1, guard, kTimeoutAccFull)) { ok = false; break; }
       tc_fence_after();
       tmem_ld32(tdPh, s0);
@@ -413,30 +405,31 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&dq_drained[half]);
-      // Stage 32 query rows at a time ([query][head dim] fp32, 512-byte rows) in the dS^T_h buffer, which the dQ product
-      // has finished reading, and add them to the global fp32 dQ with one TMA reduction each; rows past Lq are clipped.
+      // Stage 32 query rows at a time as [query][this warp's 32 head dimensions] fp32 (128-byte rows, 4 KB) in the
+      // warp's part of the dS^T_h buffer, which the dQ product has finished reading, and add them to the global fp32
+      // dQ with one TMA reduction each; rows past Lq are clipped by the tensor map.
       const int q0 = qt * 128 + half * 64;
-      float* stg = reinterpret_cast<float*>(sDs + half * S::kHalfTile);
+      float* stg = reinterpret_cast<float*>(sDs + half * S::kHalfTile + quad * 4096);
 #pragma unroll
-      for (int c = 0; c < 32; ++c) stg[c * 128 + r] = __uint_as_float(s0[c]);
+      for (int c = 0; c < 32; ++c) stg[c * 32 + lane] = __uint_as_float(s0[c]);
       fence_proxy_async();
-      if (!wg_sync(&wg_bar[half], wg_phase, guard)) { ok = false; break; }
-      if (r == 0) {
-        if (q0 < sh.Lq) tma_reduce_add_4d(&tmDq, stg, 0, head, q0, b);
+      __syncwarp();
+      if (lane == 0) {
+        if (q0 < sh.Lq) tma_reduce_add_4d(&tmDq, stg, quad * 32, head, q0, b);
         tma_store_commit();
         tma_store_wait_read0();
       }
-      if (!wg_sync(&wg_bar[half], wg_phase, guard)) { ok = false; break; }
+      __syncwarp();
 #pragma unroll
-      for (int c = 0; c < 32; ++c) stg[c * 128 + r] = __uint_as_float(s1[c]);
+      for (int c = 0; c < 32; ++c) stg[c * 32 + lane] = __uint_as_float(s1[c]);
       fence_proxy_async();
-      if (!wg_sync(&wg_bar[half], wg_phase, guard)) { ok = false; break; }
-      if (r == 0) {
-        if (q0 + 32 < sh.Lq) tma_reduce_add_4d(&tmDq, stg, 0, head, q0 + 32, b);
+      __syncwarp();
+      if (lane == 0) {
+        if (q0 + 32 < sh.Lq) tma_reduce_add_4d(&tmDq, stg, quad * 32, head, q0 + 32, b);
         tma_store_commit();
       }
     }
-    if (r == 0) tma_store_wait0();   // the last reductions have left shared memory and reached global memory
+    if (lane == 0) tma_store_wait0();   // this warp's last reductions have left shared memory and reached global memory
     // Epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK (times the softmax scale).
     const bool do_k = half == 1;
     const float mul = do_k ? p.scale : 1.f;
@@ -663,7 +656,7 @@ KSA_API int ksa_attn_bwd_fused(const void* q, const void* k, const void* v, cons
   {
     uint64_t dims[4] = {128, (uint64_t)Hq, (uint64_t)Lq, (uint64_t)B};
     uint64_t str[4] = {4, 512, (uint64_t)Hq * 512, (uint64_t)Lq * Hq * 512};
-    uint32_t box[4] = {128, 1, 32, 1};
+    uint32_t box[4] = {32, 1, 32, 1};     // one warp's slab: 32 head dimensions x 32 query rows
     if ((rc = make_tmap(&tdq, dq32, 4, 4, dims, str, box, false))) return rc;
   }
   dim3 grid((Lk + 127) / 128 + ((Ns + 127) / 128) * p.n_seg, Hkv, B);
@@ -773,7 +766,7 @@ KSA_API int ksa_attn_bwd_fused_cp(const void* q, const void* o, const void* d_o,
   {
     uint64_t dims[4] = {128, (uint64_t)Hq, (uint64_t)Lq, (uint64_t)B};
     uint64_t str[4] = {4, 512, (uint64_t)Hq * 512, (uint64_t)Lq * Hq * 512};
-    uint32_t box[4] = {128, 1, 32, 1};
+    uint32_t box[4] = {32, 1, 32, 1};     // one warp's slab: 32 head dimensions x 32 query rows
     if ((rc = make_tmap(&tdq, dq32, 4, 4, dims, str, box, false))) return rc;
   }
   dim3 grid((halo + local_rows + 127) / 128 + ((Ns + 127) / 128) * p.n_seg, Hkv, B);
