@@ -41,7 +41,8 @@ def run_reference_infer_arm(prompt_len: int, decode: int, batch: int, world: int
         return _unavailable("the reference has no tensor parallelism (single-device inference only)")
     src = template_dir or TEMPLATE
     if not os.path.isdir(src):
-        src = "/root/reference/examples/pretrain/hf_template" if os.path.isdir("/root/reference") else src
+        root = os.environ.get("KSA_REFERENCE_ROOT", "")      # a checkout of the reference, when it is not installed
+        src = os.path.join(root, "examples", "pretrain", "hf_template") if root else src
     if not os.path.isdir(src):
         return _unavailable(f"the reference's HF template is not on this machine ({TEMPLATE})")
     work = tempfile.mkdtemp(prefix="ref_hf_")
