@@ -3,17 +3,21 @@
 // instead of the seven of the two-kernel form in attn_bwd.cu, which stays as the bit-reproducible path).
 //
 // One CTA owns one 128-row key tile (text or summary) of one KV head and walks the query tiles that see it
-// and the query heads of the group.  Every step is split into two halves of 64 query columns, one per
-// compute warpgroup, which run half a step apart so that the tensor pipe always has the other half's
-// products to execute while a warpgroup turns scores into probabilities:
+// and the query heads of the group.  A step is one 128-query tile of one head.  Its scores and dP are issued as
+// 128-column products (a product whose A operand comes from shared memory takes the time of reading that 128 x 16
+// block however narrow it is, so 64-column products would run at half rate); everything after them works on two
+// halves of 64 query columns, one per compute warpgroup:
 //
-//   S^T_h  = K Q_h^T,  dP^T_h = V dO_h^T                       (tensor cores, 128 keys x 64 queries each)
+//   S^T    = K Q^T,    dP^T   = V dO^T                         (tensor cores, 128 keys x 128 queries each)
 //   P^T_h  = exp2(S^T_h c - LSE),  dS^T_h = P^T_h (dP^T_h - delta)   (registers; bf16 back to TMEM, dS^T_h also to smem)
 //   dQ^T_h = K^T dS^T_h    (128 head dims x 64 queries; replaces dP^T_h in TMEM and is added to a global fp32
-//                           buffer with coalesced reductions by the same warpgroup)
+//                           buffer with TMA reductions by the same warpgroup, 32 head dims per warp)
 //   dV    += P^T_h dO_h,  dK += dS^T_h Q_h                     (accumulators stay in TMEM for the whole CTA)
 //
-//   warp 0      TMA producer: K, V once; then (Q_h, dO_h, -LSE*log2e, -delta) per half step, 4-stage ring
+// The next step's S^T is issued behind dV / dK (the last readers of P^T and dS^T), its dP^T once both halves of
+// dQ^T have been read out.
+//
+//   warp 0      TMA producer: K, V once; then (Q, dO, -LSE*log2e, -delta) per step, 2-stage ring
 //   warp 1      MMA issuer (one elected thread)
 //   warps 2-5   compute warpgroup of half 0 (thread = key row)
 //   warps 6-9   compute warpgroup of half 1
@@ -33,23 +37,23 @@
 namespace ksa {
 
 constexpr int kFbThreads = 320;
-constexpr int kFbStages = 4;   // half-step stages of the (Q_h, dO_h) ring
+constexpr int kFbStages = 2;   // stages of the (Q, dO) ring, one 128-query tile of one head each
 constexpr int kFbSumSeg = 8;   // query tiles per CTA for a summary-key tile (must match ksa_attn_bwd_num_segments)
 
 struct FbSmem {
   static constexpr int kTile = 128 * 128 * 2;        // K or V: [2 head-dim halves][128 rows][128 B]
   static constexpr int kHalfTile = 64 * 128 * 2;     // Q_h or dO_h: [2 head-dim halves][64 rows][128 B]
-  static constexpr int kStage = 2 * kHalfTile;
+  static constexpr int kStage = 2 * kTile;           // Q tile then dO tile, each [2 head-dim halves][128 rows][128 B]
   static constexpr int kRing = kFbStages * kStage;
   static constexpr int kDs = 2 * kHalfTile;          // dS^T_h: [128 key rows][64 queries] bf16, one per half
-  static constexpr int kStats = kFbStages * 512;     // per stage: -LSE*log2e [64], -delta [64]
+  static constexpr int kStats = kFbStages * 1024;    // per stage: -LSE*log2e [128], -delta [128]
   static constexpr int kBar = 256;
   static constexpr int kOffRing = 2 * kTile;
   static constexpr int kOffDs = kOffRing + kRing;
   static constexpr int kOffStats = kOffDs + kDs;
   static constexpr int kOffBar = kOffStats + kStats;
   static constexpr int kTotal = kOffBar + kBar;      // 231680 bytes: the dynamic segment must start 1024-aligned
-  static constexpr int kStageBytes = kStage + 512;   // bytes a full stage receives
+  static constexpr int kStageBytes = kStage + 1024;  // bytes a full stage receives
 };
 
 struct FbParams {
@@ -82,16 +86,16 @@ __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const vo
 }
 
 // 32 score columns and 32 dP columns of one key row -> 16 packed P and 16 packed dS words.
-// `st` points at -LSE*log2e of the first column, `st + 64` at -delta; columns outside [lo, lo + span] are masked
+// `st` points at -LSE*log2e of the first column, `sd` at its -delta; columns outside [lo, lo + span] are masked
 // when `masked` is set (col0 is the first column's index inside the half).
 __device__ __forceinline__ void softmax_grad_32(const uint32_t (&s)[32], const uint32_t (&d)[32], const float* st,
-                                                float scale_log2, bool masked, int col0, int lo, unsigned span,
-                                                uint32_t (&pk)[16], uint32_t (&dk)[16]) {
+                                                const float* sd, float scale_log2, bool masked, int col0, int lo,
+                                                unsigned span, uint32_t (&pk)[16], uint32_t (&dk)[16]) {
   const uint64_t sc2 = f2_pack(scale_log2, scale_log2);
 #pragma unroll
   for (int g = 0; g < 8; ++g) {
     const float4 nl = *reinterpret_cast<const float4*>(st + g * 4);
-    const float4 nd = *reinterpret_cast<const float4*>(st + 64 + g * 4);
+    const float4 nd = *reinterpret_cast<const float4*>(sd + g * 4);
     const float nls[4] = {nl.x, nl.y, nl.z, nl.w}, nds[4] = {nd.x, nd.y, nd.z, nd.w};
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
@@ -163,7 +167,7 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
   uint64_t* kv_full = bars;                      // 1
   uint64_t* st_full = bars + 1;                  // kFbStages
   uint64_t* st_empty = st_full + kFbStages;      // kFbStages
-  uint64_t* sp_full = st_empty + kFbStages;      // 2: S^T_h and dP^T_h are in TMEM
+  uint64_t* sp_full = st_empty + kFbStages;      // S^T and dP^T of a step are in TMEM (first of two slots used)
   uint64_t* pds_full = sp_full + 2;              // 2: P^T_h and dS^T_h are written (TMEM and smem)
   uint64_t* dq_full = pds_full + 2;              // 2: dQ^T_h is in TMEM
   uint64_t* dq_drained = dq_full + 2;            // 2: dQ^T_h has been read out
@@ -193,8 +197,7 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
     qr.last = min(qr.last, seg * kFbSumSeg + kFbSumSeg - 1);
   }
   const int n_q = qr.last >= qr.first ? (qr.last - qr.first + 1) : 0;
-  const int total = n_q * G;          // steps; 2 * total half steps
-  const int n_half = 2 * total;
+  const int total = n_q * G;          // steps: one 128-query tile of one head each
   const bool atomic_out = is_sum && n_seg > 1;
   // context parallel: source of this key tile, its first row there, and whether another rank owns it
   int cp_src = 0, cp_row = kt * 128;
@@ -208,8 +211,8 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < kFbStages; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 1); }
+    mbar_init(&sp_full[0], 1);
     for (int h = 0; h < 2; ++h) {
-      mbar_init(&sp_full[h], 1);
       mbar_init(&pds_full[h], 128);
       mbar_init(&dq_full[h], 1);
       mbar_init(&dq_drained[h], 128);
@@ -246,85 +249,88 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
         tma_load_4d(sV + hh * 16384, mv, hh * 64, cp_row, kv_head, b, kv_full);
       }
       const long long plane = (long long)sh.B * sh.Hq * p.lq_pad;
-      for (int n = 0; n < n_half && src_ok; ++n) {
-        const int stage = n % kFbStages;
-        if (!mbar_wait(&st_empty[stage], ((n / kFbStages) & 1) ^ 1, guard, kTimeoutStageEmpty)) break;
-        const int i = n >> 1, h = n & 1;
-        const int qt = qr.first + i / G, head = kv_head * G + i % G;
-        const int row0 = qt * 128 + h * 64;
+      for (int j = 0; j < total && src_ok; ++j) {
+        const int stage = j % kFbStages;
+        if (!mbar_wait(&st_empty[stage], ((j / kFbStages) & 1) ^ 1, guard, kTimeoutStageEmpty)) break;
+        const int qt = qr.first + j / G, head = kv_head * G + j % G;
+        const int row0 = qt * 128;
         uint8_t* dst = sRing + stage * S::kStage;
         mbar_expect_tx(&st_full[stage], S::kStageBytes);
         for (int hh = 0; hh < 2; ++hh) {
-          tma_load_4d(dst + hh * 8192, &tmQ, hh * 64, row0, head, b, &st_full[stage]);
-          tma_load_4d(dst + S::kHalfTile + hh * 8192, &tmdO, hh * 64, row0, head, b, &st_full[stage]);
+          tma_load_4d(dst + hh * 16384, &tmQ, hh * 64, row0, head, b, &st_full[stage]);
+          tma_load_4d(dst + S::kTile + hh * 16384, &tmdO, hh * 64, row0, head, b, &st_full[stage]);
         }
         const float* src = p.stats + ((long long)b * sh.Hq + head) * p.lq_pad + row0;
-        bulk_load(sStats + stage * 512, src, 256, &st_full[stage]);
-        bulk_load(sStats + stage * 512 + 256, src + plane, 256, &st_full[stage]);
+        bulk_load(sStats + stage * 1024, src, 512, &st_full[stage]);
+        bulk_load(sStats + stage * 1024 + 512, src + plane, 512, &st_full[stage]);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && total > 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);     // S^T_h, dP^T_h
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);    // S^T, dP^T: all 128 queries of the step at once
       constexpr uint32_t idesc_acc = umma_idesc_bf16(128, 128, 0, 1);  // dV, dK: A from TMEM, B MN-major
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 64, 1, 1);    // dQ^T_h: A = K^T, B = dS^T_h, both MN-major
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-      auto stage_addr = [&](int n) { return smem_u32(sRing + (n % kFbStages) * S::kStage); };
-      auto issue_s = [&](int n) {
-        const int h = n & 1;
-        const uint32_t qa = stage_addr(n);
+      auto stage_addr = [&](int j) { return smem_u32(sRing + (j % kFbStages) * S::kStage); };
+      // A product whose A operand comes from shared memory takes the time of reading its 128 x 16 A block however
+      // narrow it is, so S^T and dP^T are issued 128 columns wide (both halves of the query tile in one product).
+      auto issue_s = [&](int j) {
+        const uint32_t qa = stage_addr(j);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tS + h * 64, smem_desc_kmajor_sw128(ka + (kk / 4) * 16384 + (kk % 4) * 32),
-                  smem_desc_kmajor_sw128(qa + (kk / 4) * 8192 + (kk % 4) * 32), idesc_s, kk != 0);
+          umma_ss(tS, smem_desc_kmajor_sw128(ka + (kk / 4) * 16384 + (kk % 4) * 32),
+                  smem_desc_kmajor_sw128(qa + (kk / 4) * 16384 + (kk % 4) * 32), idesc_s, kk != 0);
       };
-      auto issue_dp = [&](int n) {
-        const int h = n & 1;
-        const uint32_t doa = stage_addr(n) + S::kHalfTile;
+      auto issue_dp = [&](int j) {
+        const uint32_t doa = stage_addr(j) + S::kTile;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tdP + h * 64, smem_desc_kmajor_sw128(va + (kk / 4) * 16384 + (kk % 4) * 32),
-                  smem_desc_kmajor_sw128(doa + (kk / 4) * 8192 + (kk % 4) * 32), idesc_s, kk != 0);
+          umma_ss(tdP, smem_desc_kmajor_sw128(va + (kk / 4) * 16384 + (kk % 4) * 32),
+                  smem_desc_kmajor_sw128(doa + (kk / 4) * 16384 + (kk % 4) * 32), idesc_s, kk != 0);
       };
       bool ok = mbar_wait(kv_full, 0, guard, kTimeoutTmaFull);
-      for (int h = 0; h < 2 && ok; ++h) {
-        ok = mbar_wait(&st_full[h], 0, guard, kTimeoutTmaFull);
-        if (ok) {
-          tc_fence_after();
-          issue_s(h);
-          issue_dp(h);
-          umma_commit(&sp_full[h]);
-        }
-      }
-      for (int n = 0; n < n_half && ok; ++n) {
-        const int h = n & 1, j = n >> 1;
-        const uint32_t qa = stage_addr(n), doa = qa + S::kHalfTile;
-        const uint32_t dsa = smem_u32(sDs + h * S::kHalfTile);
-        if (!mbar_wait(&pds_full[h], j & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      if (ok) ok = mbar_wait(&st_full[0], 0, guard, kTimeoutTmaFull);
+      if (ok) {
         tc_fence_after();
-        // dQ^T_h first: it replaces dP^T_h, which the warpgroup has consumed, and its read-out then overlaps dV / dK.
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ss(tdP + h * 64, smem_desc_mnmajor_sw128(ka + kk * 2048, 16384),
-                  smem_desc_mnmajor_sw128(dsa + kk * 2048, 8192), idesc_dq, kk != 0);
-        umma_commit(&dq_full[h]);
-#pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4)
-          umma_ts(tdV, tS + h * 64 + k4 * 8, smem_desc_mnmajor_sw128(doa + k4 * 2048, 8192), idesc_acc, (n | k4) != 0);
-#pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4)
-          umma_ts(tdK, tS + h * 64 + 32 + k4 * 8, smem_desc_mnmajor_sw128(qa + k4 * 2048, 8192), idesc_acc,
-                  (n | k4) != 0);
-        umma_commit(&st_empty[n % kFbStages]);
-        if (n + 2 < n_half) {
-          if (!mbar_wait(&st_full[(n + 2) % kFbStages], ((n + 2) / kFbStages) & 1, guard, kTimeoutTmaFull)) { ok = false; break; }
+        issue_s(0);
+        issue_dp(0);
+        umma_commit(&sp_full[0]);
+      }
+      for (int j = 0; j < total && ok; ++j) {
+        const uint32_t qa = stage_addr(j), doa = qa + S::kTile;
+        for (int h = 0; h < 2 && ok; ++h) {
+          const uint32_t dsa = smem_u32(sDs + h * S::kHalfTile);
+          if (!mbar_wait(&pds_full[h], j & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
           tc_fence_after();
-          issue_s(n + 2);
-          if (!mbar_wait(&dq_drained[h], j & 1, guard, kTimeoutAccEmpty)) { ok = false; break; }
+          // dQ^T_h first: it replaces dP^T_h, which the warpgroup has consumed, and its read-out then overlaps dV / dK.
+          // (One 128-column product for both halves was measured too: no faster, and it makes half 0 wait for half 1.)
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss(tdP + h * 64, smem_desc_mnmajor_sw128(ka + kk * 2048, 16384),
+                    smem_desc_mnmajor_sw128(dsa + kk * 2048, 8192), idesc_dq, kk != 0);
+          umma_commit(&dq_full[h]);
+          // dV += P_h^T dO_h, dK += dS_h^T Q_h: the half's 64 query rows of the stage's tiles, 16 per product
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            umma_ts(tdV, tS + h * 64 + k4 * 8, smem_desc_mnmajor_sw128(doa + h * 8192 + k4 * 2048, 16384), idesc_acc,
+                    (j | h | k4) != 0);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            umma_ts(tdK, tS + h * 64 + 32 + k4 * 8, smem_desc_mnmajor_sw128(qa + h * 8192 + k4 * 2048, 16384), idesc_acc,
+                    (j | h | k4) != 0);
+        }
+        if (!ok) break;
+        umma_commit(&st_empty[j % kFbStages]);
+        if (j + 1 < total) {
+          if (!mbar_wait(&st_full[(j + 1) % kFbStages], ((j + 1) / kFbStages) & 1, guard, kTimeoutTmaFull)) { ok = false; break; }
           tc_fence_after();
-          issue_dp(n + 2);
-          umma_commit(&sp_full[h]);
+          issue_s(j + 1);       // behind dV / dK in the pipe, which were the last readers of P^T and dS^T in TMEM
+          if (!mbar_wait(&dq_drained[0], j & 1, guard, kTimeoutAccEmpty)) { ok = false; break; }
+          if (!mbar_wait(&dq_drained[1], j & 1, guard, kTimeoutAccEmpty)) { ok = false; break; }
+          tc_fence_after();
+          issue_dp(j + 1);
+          umma_commit(&sp_full[0]);
         }
       }
       if (ok) umma_commit(acc_full);
@@ -356,13 +362,14 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
     const int sw = r & 7;
     bool ok = true;
     for (int j = 0; j < total; ++j) {
-      const int n = 2 * j + half, stage = n % kFbStages;
+      const int stage = j % kFbStages;
       const int qt = qr.first + j / G, head = kv_head * G + j % G;
-      if (!mbar_wait(&sp_full[half], j & 1, guard, kTimeoutAccFull)) { ok = false; break; }
+      if (!mbar_wait(&sp_full[0], j & 1, guard, kTimeoutAccFull)) { ok = false; break; }
       // the row statistics arrived with the stage; waiting on its barrier makes them visible to this thread
-      if (!mbar_wait(&st_full[stage], (n / kFbStages) & 1, guard, kTimeoutTmaFull)) { ok = false; break; }
+      if (!mbar_wait(&st_full[stage], (j / kFbStages) & 1, guard, kTimeoutTmaFull)) { ok = false; break; }
       tc_fence_after();
-      const float* st = reinterpret_cast<const float*>(sStats + stage * 512);
+      const float* st = reinterpret_cast<const float*>(sStats + stage * 1024) + half * 64;   // -LSE * log2e
+      const float* sd = st + 128;                                                              // -delta
       const long long tq0 = (long long)sh.q_off + qt * 128 + half * 64;
       int lo = (int)max(t_lo - tq0, 0LL);
       const int hi = (int)min(t_hi - tq0, 63LL);
@@ -374,7 +381,7 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
       tmem_ld32(tSh + 32, s1);
       tmem_ld32(tdPh, d);
       tmem_wait_ld();
-      softmax_grad_32(s0, d, st, p.scale_log2, masked, 0, lo, span, pk, dk);
+      softmax_grad_32(s0, d, st, sd, p.scale_log2, masked, 0, lo, span, pk, dk);
       tmem_ld32(tdPh + 32, d);
       tmem_st16(tSh, pk);
       tmem_st16(tSh + 32, dk);
@@ -387,7 +394,7 @@ __device__ __forceinline__ void attn_bwd_fused_body(const CUtensorMap& tmQ, cons
       for (int c = 0; c < 4; ++c)
         *reinterpret_cast<uint4*>(ds_row + ((c ^ sw) << 4)) = make_uint4(dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
       tmem_wait_ld();
-      softmax_grad_32(s1, d, st + 32, p.scale_log2, masked, 32, lo, span, pk, dk);
+      softmax_grad_32(s1, d, st + 32, sd + 32, p.scale_log2, masked, 32, lo, span, pk, dk);
       tmem_st16(tSh + 16, pk);
       tmem_st16(tSh + 48, dk);
 #pragma unroll
@@ -610,8 +617,8 @@ KSA_API int ksa_attn_bwd_fused(const void* q, const void* k, const void* v, cons
   const int lq_pad = ksa_attn_bwd_fused_lq_pad(Lq);
   CUtensorMap tq, tdo, tk, tv, tks, tvs;
   int rc;
-  if ((rc = make_head_tmap_rows(&tq, q, Lq, Hq, B, q_rs, q_bs, 64))) return rc;
-  if ((rc = make_head_tmap_rows(&tdo, d_o, Lq, Hq, B, o_rs, o_bs, 64))) return rc;
+  if ((rc = make_head_tmap_rows(&tq, q, Lq, Hq, B, q_rs, q_bs, 128))) return rc;
+  if ((rc = make_head_tmap_rows(&tdo, d_o, Lq, Hq, B, o_rs, o_bs, 128))) return rc;
   if ((rc = make_head_tmap_rows(&tk, k, Lk, Hkv, B, k_rs, k_bs, 128))) return rc;
   if ((rc = make_head_tmap_rows(&tv, v, Lk, Hkv, B, v_rs, v_bs, 128))) return rc;
   if (Ns > 0) {
@@ -707,8 +714,8 @@ KSA_API int ksa_attn_bwd_fused_cp(const void* q, const void* o, const void* d_o,
   CpBwdSources cp;
   memset(&cp, 0, sizeof(cp));
   int rc;
-  if ((rc = make_head_tmap_rows(&tq, q, Lq, Hq, B, q_rs, q_bs, 64))) return rc;
-  if ((rc = make_head_tmap_rows(&tdo, d_o, Lq, Hq, B, o_rs, o_bs, 64))) return rc;
+  if ((rc = make_head_tmap_rows(&tq, q, Lq, Hq, B, q_rs, q_bs, 128))) return rc;
+  if ((rc = make_head_tmap_rows(&tdo, d_o, Lq, Hq, B, o_rs, o_bs, 128))) return rc;
   const long long voff = (long long)Hkv * 128;
   for (int s = 0; s < 2; ++s) {
     const int rows = s == 0 ? halo : local_rows;
