@@ -141,3 +141,24 @@ def test_cache_grows_when_a_sequence_outlives_its_capacity():
         nxt = b.argmax(-1)
         a, b = small.decode_step(nxt), big.decode_step(nxt)
     assert small.max_len >= 50 and small.max_len < 128
+
+
+def test_decode_ops_fall_back_to_their_unfused_forms_on_cpu():
+    """The two fused decode operators (projection + SwiGLU, QK-norm + RoPE + cache append) have plain PyTorch
+    fall-backs that the CPU engine runs: they must equal the separate operators."""
+    from ksa_b200 import ops
+    torch.manual_seed(7)
+    x, w13 = torch.randn(3, 32), torch.randn(2 * 24, 32) * 0.2
+    assert torch.allclose(ops.linear_swiglu(x, w13), ops.swiglu(ops.linear(x, w13)), atol=1e-6)
+    Hq, Hkv, D, cap = 4, 2, 16, 9
+    qkv = torch.randn(5, (Hq + 2 * Hkv) * D)
+    qw, kw = 1 + 0.1 * torch.randn(D), 1 + 0.1 * torch.randn(D)
+    pos = torch.tensor([3, 11, 0, 7, 5], dtype=torch.int32)
+    slots = torch.tensor([4, -1, 8], dtype=torch.int32)          # three sequences; the second is not cached
+    kc, vc = torch.zeros(3, Hkv, cap, D), torch.zeros(3, Hkv, cap, D)
+    out = ops.qk_norm_rope_decode(qkv, qw, kw, pos, Hq, Hkv, D, 1e4, 1e-6, False, kc, vc, slots)
+    expect = ops.qk_norm_rope_packed(qkv, qw, kw, pos, Hq, Hkv, D, 1e4, 1e-6, False)
+    assert torch.equal(out, expect)
+    assert torch.equal(kc[0, :, 4], expect[0, Hq * D:(Hq + Hkv) * D].view(Hkv, D))
+    assert torch.equal(vc[2, :, 8], expect[2, (Hq + Hkv) * D:].view(Hkv, D))
+    assert kc[1].abs().sum() == 0 and vc[1].abs().sum() == 0
