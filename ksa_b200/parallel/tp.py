@@ -32,11 +32,15 @@ class TpContext:
                  fused_gather: Optional[bool] = None, push_partials: Optional[bool] = None):
         if two_phase_min_size is None:
             two_phase_min_size = int(os.environ.get("KSA_TP_TWO_PHASE_MIN", "3"))
-        if fused_gather is None:
-            fused_gather = os.environ.get("KSA_TP_FUSED_GATHER", "1") == "1"
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
+        if fused_gather is None:
+            # measured: the launch that gathers inside the GEMM is 1.7-1.8 x faster than gather kernel + GEMM on its
+            # own (2 and 4 GPUs), but a whole 32768-token prefill of KSA-4B on 4 GPUs takes 139.5 ms with it against
+            # 134.4-137.9 ms without (three runs each on one box), so groups of more than two gather separately
+            env = os.environ.get("KSA_TP_FUSED_GATHER")
+            fused_gather = (env == "1") if env is not None else self.size <= 2
         if push_partials is None:
             # measured (33024 x 2560 x 2048, GEMM + reduction): scattering from the epilogue wins on 2 GPUs (0.40 against
             # 0.45 ms) and loses on 4 (0.50 against 0.47 ms), where the blocks of one tile go to four owners
