@@ -52,8 +52,9 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--comm", default=None, choices=["fused", "collective"],
                     help="multi-GPU back end: fused P2P kernels (default) or NCCL collectives (A/B baseline)")
-    ap.add_argument("--overlap", default="stream", choices=["stream", "gemm2"],
-                    help="fused back end: communication kernels on a side stream, or as CTAs inside GEMM launches")
+    ap.add_argument("--overlap", default="auto", choices=["auto", "stream", "gemm2"],
+                    help="fused back end: parameter gathers on a side stream, or inside the gate/up GEMM launches "
+                         "(auto: gemm2 for plain FSDP on 4 or more GPUs, where it measured faster, else stream)")
     ap.add_argument("--reshard", action="store_true",
                     help="ZeRO-3: keep only 1/N of the bf16 weights resident and re-gather units for backward")
     return ap.parse_args()
@@ -142,7 +143,9 @@ def run_ours(args) -> dict:
                 p.fill_(1.0)
 
     if world > 1:
-        from ksa_b200.parallel.fsdp import FsdpEngine as Engine
+        from ksa_b200.parallel.fsdp import FsdpEngine as Engine, default_overlap
+        if args.overlap == "auto":
+            args.overlap = default_overlap(world, args.cp, args.reshard)
         extra = dict(world_size=world, rank=rank, comm=args.comm, overlap=args.overlap,
                      reshard_after_forward=args.reshard)
     else:

@@ -27,12 +27,26 @@ __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
 
 // kGlu: B holds N/2 gate rows followed by N/2 up rows; weight row r of a warp is gate row f for even r and up row f
 // for odd r (f = first feature + r / 2), and C[m, f] = silu(gate) * up has N/2 columns.
+// Optional residual add + RMSNorm in front of the projection (a decode step's `x + delta -> norm -> projection`): the
+// activation rows are then A = bf16(rms_norm(bf16(A + delta)) * w), computed by every CTA while it stages them (the
+// rows are a few kilobytes), and CTA 0 also writes the new residual stream bf16(A + delta) to `res_out`.
+struct GemvNorm {
+  const bf16* delta;     // [delta_rows, K] or null
+  const bf16* w;         // [K] norm weight; null: no norm, A is used as it is
+  bf16* res_out;         // [M, K] or null
+  long long ld_delta, ld_res;
+  float eps;
+  int delta_rows;
+};
+
 template <int MT, int R, bool kGlu>
 __global__ void __launch_bounds__(kGemvThreads)
 gemv_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, int M, int N, int K,
-            long long lda, long long ldb, long long ldc) {
+            long long lda, long long ldb, long long ldc, GemvNorm nrm) {
   extern __shared__ __align__(16) uint8_t gemv_smem[];
   bf16* sA = reinterpret_cast<bf16*>(gemv_smem);           // [MT][kGemvKTile]
+  __shared__ float s_rstd[MT];
+  __shared__ float s_red[kGemvThreads / 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = (blockIdx.x * (kGemvThreads / 32) + warp) * (kGlu ? R / 2 : R);   // first row / first feature
   const int n_out = kGlu ? N / 2 : N;
@@ -67,13 +81,77 @@ gemv_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __rest
   grid_dependency_wait();
   grid_dependency_launch();
 
+  // eight elements of the (residual-added, bf16-rounded) activation row m at column c
+  auto load_row8 = [&](int m, int c, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(A + (long long)m * lda + c);
+    const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) { const float2 f = unpack_bf16x2(uu[q]); v[2 * q] = f.x; v[2 * q + 1] = f.y; }
+    if (nrm.delta != nullptr && m < nrm.delta_rows) {
+      const uint4 d = *reinterpret_cast<const uint4*>(nrm.delta + (long long)m * nrm.ld_delta + c);
+      const uint32_t du[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = unpack_bf16x2(du[q]);
+        v[2 * q] = __bfloat162float(__float2bfloat16(v[2 * q] + f.x));
+        v[2 * q + 1] = __bfloat162float(__float2bfloat16(v[2 * q + 1] + f.y));
+      }
+    }
+  };
+  if (nrm.w != nullptr) {
+    for (int m = 0; m < MT; ++m) {
+      float ss = 0.f;
+      if (m < M) {
+        for (int c = threadIdx.x * 8; c < K; c += kGemvThreads * 8) {
+          float v[8];
+          load_row8(m, c, v);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) ss += v[q] * v[q];
+          if (blockIdx.x == 0 && nrm.res_out != nullptr) {
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(nrm.res_out + (long long)m * nrm.ld_res + c) = o;
+          }
+        }
+      }
+      ss = warp_sum(ss);
+      __syncthreads();
+      if (lane == 0) s_red[warp] = ss;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < kGemvThreads / 32; ++k) t += s_red[k];
+        s_rstd[m] = rsqrtf(t / (float)K + nrm.eps);
+      }
+    }
+  }
+
   for (int k0 = 0; k0 < K; k0 += kGemvKTile) {
     const int kt = min(kGemvKTile, K - k0);          // multiple of 8
     __syncthreads();
     for (int i = threadIdx.x; i < MT * (kGemvKTile / 8); i += kGemvThreads) {
       const int m = i / (kGemvKTile / 8), c = (i % (kGemvKTile / 8)) * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (m < M && c < kt) v = *reinterpret_cast<const uint4*>(A + (long long)m * lda + k0 + c);
+      if (m < M && c < kt) {
+        if (nrm.w == nullptr) {
+          v = *reinterpret_cast<const uint4*>(A + (long long)m * lda + k0 + c);
+        } else {
+          float x[8];
+          load_row8(m, k0 + c, x);
+          const uint4 wv = *reinterpret_cast<const uint4*>(nrm.w + k0 + c);
+          const uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+          const float rstd = s_rstd[m];
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = unpack_bf16x2(wu[q]);
+            o[q] = pack_bf16x2(x[2 * q] * rstd * f.x, x[2 * q + 1] * rstd * f.y);
+          }
+          v = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
       *reinterpret_cast<uint4*>(sA + m * kGemvKTile + c) = v;
     }
     __syncthreads();
@@ -128,7 +206,7 @@ gemv_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __rest
 
 template <int MT, int R, bool kGlu>
 static int launch_gemv(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
-                       long long ldc, cudaStream_t st) {
+                       long long ldc, cudaStream_t st, const GemvNorm& nrm = GemvNorm{}) {
   const int per_cta = (kGemvThreads / 32) * (kGlu ? R / 2 : R);      // output columns per CTA
   const int n_out = kGlu ? N / 2 : N;
   const size_t smem = (size_t)MT * kGemvKTile * sizeof(bf16);
@@ -140,7 +218,7 @@ static int launch_gemv(const void* a, const void* b, void* c, int M, int N, int 
   }
   KSA_CHECK_CUDA(launch_kernel(dependent_launch_enabled(), kern, dim3((n_out + per_cta - 1) / per_cta),
                               dim3(kGemvThreads), smem, st, (const bf16*)a, (const bf16*)b, (bf16*)c, M, N, K, lda, ldb,
-                              ldc));
+                              ldc, nrm));
   return 0;
 }
 
@@ -288,8 +366,8 @@ static int launch_gemv_mma(const void* a, const void* b, void* c, int M, int N, 
 namespace ksa {
 template <bool kGlu>
 static int gemv_dispatch(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
-                         long long ldc, cudaStream_t st) {
-  if (M > 4 && K % 32 == 0) {
+                         long long ldc, cudaStream_t st, const GemvNorm& nrm = GemvNorm{}) {
+  if (M > 4 && K % 32 == 0 && nrm.w == nullptr) {
     if (N >= 16384)   // wide outputs: 32 weight rows per CTA still give every SM several CTAs
       return M <= 8 ? launch_gemv_mma<1, kGlu, 2>(a, b, c, M, N, K, lda, ldb, ldc, st)
                     : launch_gemv_mma<2, kGlu, 2>(a, b, c, M, N, K, lda, ldb, ldc, st);
@@ -300,9 +378,9 @@ static int gemv_dispatch(const void* a, const void* b, void* c, int M, int N, in
   // needs at least one gate row and one up row)
   const bool narrow = N <= 8192;
   constexpr int R1 = kGlu ? 2 : 1;
-  if (M == 1) return narrow ? launch_gemv<1, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<1, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
-  if (M <= 2) return narrow ? launch_gemv<2, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<2, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
-  if (M <= 4) return narrow ? launch_gemv<4, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<4, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
+  if (M == 1) return narrow ? launch_gemv<1, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st, nrm) : launch_gemv<1, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st, nrm);
+  if (M <= 2) return narrow ? launch_gemv<2, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st, nrm) : launch_gemv<2, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st, nrm);
+  if (M <= 4) return narrow ? launch_gemv<4, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st, nrm) : launch_gemv<4, 4, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st, nrm);
   if (M <= 8) return narrow ? launch_gemv<8, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<8, 2, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
   return narrow ? launch_gemv<16, R1, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st) : launch_gemv<16, 2, kGlu>(a, b, c, M, N, K, lda, ldb, ldc, st);
 }
@@ -328,4 +406,24 @@ KSA_API int ksa_gemv_swiglu_bf16(const void* a, const void* b, void* c, int M, i
   KSA_REQUIRE(N > 0 && N % 2 == 0 && K > 0 && K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
               "gemv_swiglu: N must be even and K, lda, ldb multiples of 8");
   return gemv_dispatch<true>(a, b, c, M, N, K, lda, ldb, ldc, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// A decode step's `residual add -> RMSNorm -> projection` in one launch, for at most 4 rows:
+//   res = bf16(x + delta)  (delta may be null or have fewer rows; written to res_out by one CTA when res_out is given)
+//   C   = rms_norm(res, norm_w, eps) * B^T          (glu = 0; C is [M, N])
+//   C   = silu(. * gate^T) * (. * up^T)             (glu = 1; B = gate rows then up rows, C is [M, N/2])
+KSA_API int ksa_gemv_norm_bf16(const void* x, const void* delta, const void* norm_w, void* res_out, const void* b, void* c,
+                               int M, int N, int K, long long ldx, long long ld_delta, long long ld_res, long long ldb,
+                               long long ldc, float eps, int delta_rows, int glu, void* stream) {
+  KSA_ENTER(x);
+  using namespace ksa;
+  KSA_REQUIRE(M >= 1 && M <= 4, "gemv_norm: M=%d out of range (1..4)", M);
+  KSA_REQUIRE(norm_w != nullptr, "gemv_norm: the norm weight is required");
+  KSA_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0 && ldb % 8 == 0 && ld_delta % 8 == 0 && ld_res % 8 == 0,
+              "gemv_norm: K and the leading dimensions must be multiples of 8");
+  KSA_REQUIRE(!glu || N % 2 == 0, "gemv_norm: N must be even with glu");
+  GemvNorm nrm{(const bf16*)delta, (const bf16*)norm_w, (bf16*)res_out, ld_delta, ld_res, eps, delta ? delta_rows : 0};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return glu ? gemv_dispatch<true>(x, b, c, M, N, K, ldx, ldb, ldc, st, nrm)
+             : gemv_dispatch<false>(x, b, c, M, N, K, ldx, ldb, ldc, st, nrm);
 }

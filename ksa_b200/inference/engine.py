@@ -317,13 +317,21 @@ class KsaInferenceEngine:
             pos_all[:B] = st.cbl
         delta = None
         slices_of = {}      # layers with the same cache geometry share the step's slot / slice tensors
+        # ordinary steps without tensor parallelism: residual add + norm live inside the projection that follows them
+        fuse_norm = tp is None and not any_boundary and B <= 4
         for li, layer in enumerate(model.layers):
             a = layer.attn
             cache = self.layer_caches[li]
-            x, h = _add_norm(tp, x, delta, layer.sa_norm.scale, cfg.norm_eps)
+            if fuse_norm:
+                x, qkv = ops.norm_linear(x, delta, layer.sa_norm.scale, cfg.norm_eps, a.wqkv.weight)
+                h = None
+            else:
+                x, h = _add_norm(tp, x, delta, layer.sa_norm.scale, cfg.norm_eps)
             if layer.is_summary_layer:
                 spec = self.specs[li]
-                if any_boundary:
+                if fuse_norm:
+                    pass
+                elif any_boundary:
                     if layer.sa_norm_summary is not None:
                         h = torch.cat([h[:B], ops.rms_norm(x[B:], layer.sa_norm_summary.scale, cfg.norm_eps)])
                     w_s = a.wqkv_summary.weight if a.wqkv_summary is not None else a.wqkv.weight
@@ -364,10 +372,14 @@ class KsaInferenceEngine:
                     att = _decode_attention(q_t, cache.k, cache.v, start_t1, len_t1, scale,
                                             self._merge_counters).reshape(B, Hq * Dh)
                 attn_out = _row_linear(tp, att, a.output_proj.weight)
-                x, h2 = _add_norm(tp, x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
-                delta = layer.mlp(h2, tp)
+                if fuse_norm:
+                    x, delta = layer.mlp.forward_after_norm(x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
+                else:
+                    x, h2 = _add_norm(tp, x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
+                    delta = layer.mlp(h2, tp)
             else:
-                qkv = ops.linear(h[:B], a.wqkv.weight)
+                if not fuse_norm:
+                    qkv = ops.linear(h[:B], a.wqkv.weight)
                 qkv = ops.qk_norm_rope_decode(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), pos_all[:B], Hq, Hkv, Dh,
                                               cfg.rope_base, cfg.norm_eps, cfg.rope_impl == "llama", cache.k, cache.v,
                                               st.text_len)
@@ -376,8 +388,11 @@ class KsaInferenceEngine:
                 att = _decode_attention(q_t, cache.k, cache.v, zeros, (st.text_len + 1).view(B, 1).to(torch.int32),
                                         scale, self._merge_counters).reshape(B, Hq * Dh)
                 attn_out = _row_linear(tp, att, a.output_proj.weight)
-                x, h2 = _add_norm(tp, x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
-                delta = layer.mlp(h2[:B], tp)
+                if fuse_norm:
+                    x, delta = layer.mlp.forward_after_norm(x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
+                else:
+                    x, h2 = _add_norm(tp, x, attn_out, layer.mlp_norm.scale, cfg.norm_eps)
+                    delta = layer.mlp(h2[:B], tp)
         _, hN = _add_norm(tp, x[:B], delta[:B], model.norm.scale, cfg.norm_eps)
         # advance the counters
         st.text_len += 1

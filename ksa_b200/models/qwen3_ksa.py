@@ -118,6 +118,12 @@ class SwiGluMlp(nn.Module):
         self.w13 = FusedLinear(dim, 2 * hidden)
         self.w2 = FusedLinear(hidden, dim)
 
+    def forward_after_norm(self, x, delta, norm_scale, eps):
+        """``res = x + delta``; the block on ``rms_norm(res)``.  Returns ``(res, block output)``.  For the few rows of a
+        decode step the residual add, the norm, the gate/up projection and SwiGLU are one launch."""
+        res, h = ops.norm_linear(x, delta, norm_scale, eps, self.w13.weight, glu=True)
+        return res, ops.linear(h, self.w2.weight)
+
     def forward(self, x, tp=None, residual_rows: Optional[int] = None):
         if x.dim() == 2 and x.shape[0] <= 16 and (tp is None or getattr(tp, "_pending", None) is None):
             h = ops.linear_swiglu(x, self.w13.weight)       # decode: projection and activation in one kernel

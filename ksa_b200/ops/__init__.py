@@ -394,6 +394,30 @@ def qk_norm_rope_packed(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opt
     return _QkNormRopeFn.apply(qkv, q_w, k_w, pos.to(torch.int32), Hq, Hkv, D, theta, eps, interleaved)
 
 
+def norm_linear(x: torch.Tensor, delta: Optional[torch.Tensor], norm_w: torch.Tensor, eps: float,
+                weight: torch.Tensor, glu: bool = False):
+    """``res = x + delta``; ``y = rms_norm(res, norm_w) @ weight.T`` (with ``glu``: ``swiglu`` of it, ``weight`` = gate
+    rows then up rows).  Returns ``(res, y)``.  For at most 4 rows on a GPU without autograd (a decode step) this is
+    one launch (``ksa_gemv_norm_bf16``: every CTA normalises the few activation rows itself while it stages them);
+    everything else is ``add_rms_norm`` followed by the projection."""
+    if (_cuda(x) and x.dim() == 2 and x.shape[0] <= 4 and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad))
+            and x.stride(1) == 1 and weight.stride(1) == 1 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and weight.stride(0) % 8 == 0 and (delta is None or (delta.stride(1) == 1 and delta.stride(0) % 8 == 0
+                                                                  and delta.dtype == torch.bfloat16))
+            and (not glu or weight.shape[0] % 2 == 0)):
+        M, K = x.shape
+        N = weight.shape[0]
+        res = torch.empty((M, K), dtype=torch.bfloat16, device=x.device) if delta is not None else x
+        out = torch.empty((M, N // 2 if glu else N), dtype=torch.bfloat16, device=x.device)
+        _lib.call("ksa_gemv_norm_bf16", x, delta, norm_w, res if delta is not None else None, weight, out, M, N, K,
+                  x.stride(0), delta.stride(0) if delta is not None else K, res.stride(0), weight.stride(0),
+                  out.stride(0), float(eps), delta.shape[0] if delta is not None else 0, int(glu))
+        return res, out
+    res, h = add_rms_norm(x, delta, norm_w, eps)
+    return res, (linear_swiglu(h, weight) if glu else linear(h, weight))
+
+
 def qk_norm_rope_decode(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
                         pos: torch.Tensor, Hq: int, Hkv: int, D: int, theta: float, eps: float, interleaved: bool,
                         k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
@@ -905,7 +929,7 @@ def adamw_step(master, grad, m, v, out_bf16, hyper, beta1, beta2, eps, weight_de
 
 
 __all__ = [
-    "gemm", "linear", "dual_linear", "attention_packed", "rms_norm", "add_rms_norm", "qk_norm_rope_packed", "qk_norm_rope_decode", "swiglu", "linear_swiglu", "embedding",
+    "gemm", "linear", "dual_linear", "attention_packed", "rms_norm", "add_rms_norm", "qk_norm_rope_packed", "qk_norm_rope_decode", "swiglu", "linear_swiglu", "norm_linear", "embedding",
     "ksa_attention", "causal_attention", "linear_cross_entropy", "adamw_step", "UNBOUNDED_WINDOW",
     "SummaryLayout", "get_layout",
 ]

@@ -28,6 +28,7 @@ _SIGNATURES: Dict[str, Sequence] = {
     "ksa_gemm2_scatter_bf16": [P, P, I, I, I, L, L, L, P, I, I, P],
     "ksa_gemv_bf16": [P, P, P, I, I, I, L, L, L, P],
     "ksa_gemv_swiglu_bf16": [P, P, P, I, I, I, L, L, L, P],
+    "ksa_gemv_norm_bf16": [P, P, P, P, P, P, I, I, I, L, L, L, L, L, F, I, I, P],
     "ksa_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, I, P],
     "ksa_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, P],
     "ksa_qknorm_rope_fwd": [P, P, P, P, P, P, L, L, I, I, I, I, F, F, I, I, P],

@@ -58,8 +58,9 @@ def get_argument_parser() -> argparse.ArgumentParser:
     a("--reshard-after-forward", action="store_true")
     a("--prefetch-params-in-forward", action="store_true")
     a("--comm", default=None, choices=["fused", "collective"], help="FSDP back end (default: fused on GPUs)")
-    a("--overlap", default="stream", choices=["stream", "gemm2"],
-      help="fused back end: communication kernels on a side stream, or inside GEMM launches")
+    a("--overlap", default="auto", choices=["auto", "stream", "gemm2"],
+      help="fused back end: parameter gathers on a side stream, or inside the gate/up GEMM launches (auto: gemm2 for "
+           "plain FSDP on 4 or more GPUs, else stream)")
     a("--no-cuda-graph", action="store_true")
     # optimisation
     a("--lr-scheduler-type", default="wsd", choices=["cosine", "cosine_v2", "wsd", "constant"])
@@ -207,7 +208,9 @@ def train(args) -> dict:
     common = dict(lr=args.learning_rate, betas=(args.beta1, args.beta2), eps=1e-8, weight_decay=args.weight_decay,
                   clip_value=args.clip_range, lr_lambda=lr_lambda, grad_accum_steps=args.gradient_accumulation_steps)
     if world > 1:
-        from ksa_b200.parallel.fsdp import FsdpEngine
+        from ksa_b200.parallel.fsdp import FsdpEngine, default_overlap
+        if args.overlap == "auto":
+            args.overlap = default_overlap(world, args.context_parallel_size, args.reshard_after_forward)
         engine = FsdpEngine(model, world_size=world, rank=rank, comm=args.comm, overlap=args.overlap,
                             reshard_after_forward=args.reshard_after_forward, **common)
     else:

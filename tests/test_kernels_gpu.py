@@ -110,6 +110,25 @@ def test_skinny_gate_up_projection_with_swiglu(M, F, K):
     check(y, yr, 5e-2, "dependent-launch chain")
 
 
+@pytest.mark.parametrize("M,delta_rows", [(1, 1), (3, 3), (4, 2), (2, 0)])
+@pytest.mark.parametrize("glu", [False, True])
+def test_skinny_projection_with_residual_add_and_norm(M, delta_rows, glu):
+    """The decode step's `x + delta -> RMSNorm -> projection` in one launch against the separate kernels."""
+    K, N = 2560, 6144 if not glu else 2 * 1280
+    x = bf(M, K)
+    delta = bf(delta_rows, K) if delta_rows else None
+    nw = (1 + 0.1 * torch.randn(K, device=DEV)).bfloat16()
+    w = bf(N, K, scale=0.05)
+    before = _lib.launch_count()
+    with torch.no_grad():
+        res, y = ops.norm_linear(x, delta, nw, 1e-6, w, glu=glu)
+        assert _lib.launch_count() == before + 1
+        res_ref, h = ops.add_rms_norm(x, delta, nw, 1e-6)
+        y_ref = ops.linear_swiglu(h, w) if glu else ops.linear(h, w)
+    assert torch.equal(res, res_ref)
+    check(y, y_ref.float(), 1.5e-2, f"norm + projection {M}x{N}x{K} glu={glu}")
+
+
 def test_linear_autograd():
     x = bf(3, 200, 256).requires_grad_()
     w = bf(384, 256, scale=0.05).requires_grad_()
