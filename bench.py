@@ -57,6 +57,8 @@ def parse_args():
                          "(auto: gemm2 for plain FSDP on 4 or more GPUs, where it measured faster, else stream)")
     ap.add_argument("--reshard", action="store_true",
                     help="ZeRO-3: keep only 1/N of the bf16 weights resident and re-gather units for backward")
+    ap.add_argument("--cpu-offload", action="store_true",
+                    help="fp32 master weights and Adam moments in pinned host memory (staged through the GPU per unit)")
     return ap.parse_args()
 
 
@@ -151,7 +153,8 @@ def run_ours(args) -> dict:
     else:
         from ksa_b200.training.engine import TrainEngine as Engine
         extra = {}
-    engine = Engine(model, lr=4e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, clip_value=1.0, **extra)
+    engine = Engine(model, lr=4e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, clip_value=1.0,
+                    cpu_offload=args.cpu_offload, **extra)
 
     B, L = 1, args.seq_len
     cp, dp = args.cp, world // max(args.cp, 1)
@@ -178,7 +181,7 @@ def run_ours(args) -> dict:
 
     # one CUDA graph for the whole step on one GPU; the multi-GPU step stays eager (its communication kernels wait on
     # other GPUs' flags from a side stream, an ordering that a graph replay does not promise to keep)
-    use_graph = not args.no_graph and world == 1
+    use_graph = not args.no_graph and world == 1 and not args.cpu_offload
     step_fn = engine.graphed_step if use_graph else engine.train_step
 
     def barrier():
@@ -242,7 +245,10 @@ def run_ours(args) -> dict:
                    "l2": "working set (weights+optimizer state+activations, >30 GB) exceeds L2; no explicit flush",
                    "cuda_graph": use_graph, "comm": getattr(engine, "comm", "none"),
                    "overlap": getattr(engine, "overlap", "none"),
-                   "reshard_after_forward": bool(getattr(engine, "reshard", False))},
+                   "reshard_after_forward": bool(getattr(engine, "reshard", False)),
+                   "cpu_offload": bool(args.cpu_offload),
+                   "offload_bytes_each_way_per_step": sum(u.host_state.numel() * 4 for u in engine.units)
+                   if args.cpu_offload else 0},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},

@@ -185,6 +185,7 @@ class FsdpEngine(TrainEngine):
 
     def _shards_from_master(self) -> None:
         """Resharded storage: the persistent bf16 shards follow the fp32 master weights; every slot is stale."""
+        self.sync_state()
         for u in self.units:
             u.compute_shard.copy_(u.master)
         self._slot_holds, self._resident_ev = {}, {}
@@ -280,9 +281,10 @@ class FsdpEngine(TrainEngine):
         _lib.call("ksa_peer_gather", u.compute_ptrs, self.world_size, self.rank, u.size // self.world_size,
                   u.compute.element_size(), self.pad_weights.local_ptr(self._unit_flag_index(ui)), self.epoch, 0, 32)
 
-    def _reduce_args(self, u: Unit, ui: int):
-        return (u.grad_ptrs, self.world_size, self.rank, u.shard_lo, u.shard_hi - u.shard_lo, u.master, u.exp_avg,
-                u.exp_avg_sq, self._bf16_out(u), self.hyper, self.beta1,
+    def _reduce_args(self, u: Unit, ui: int, state):
+        master, exp_avg, exp_avg_sq = state
+        return (u.grad_ptrs, self.world_size, self.rank, u.shard_lo, u.shard_hi - u.shard_lo, master, exp_avg,
+                exp_avg_sq, self._bf16_out(u), self.hyper, self.beta1,
                 self.beta2, self.eps, self.weight_decay, self.clip_value, self.grad_sq,
                 self.pad_grads.local_ptr(self._unit_flag_index(ui)), self.epoch, 1)
 
@@ -307,7 +309,9 @@ class FsdpEngine(TrainEngine):
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ev)
             self._signal(self.pad_grads, ui)
-            _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui), 148)   # one CTA per SM: fits beside a GEMM CTA
+            with self._optimizer_state(u) as state:
+                # one CTA per SM: fits beside a GEMM CTA
+                _lib.call("ksa_peer_reduce_adamw", *self._reduce_args(u, ui, state), 148)
             self._signal(self.pad_weights, ui)
         self._done_units.add(ui)
 
@@ -426,10 +430,11 @@ class FsdpEngine(TrainEngine):
         else:
             shard = unit.grad[lo:hi]
         out = unit.compute[lo:hi] if self.param_dtype != torch.float32 else None
-        ops.adamw_step(unit.master, shard, unit.exp_avg, unit.exp_avg_sq, out, self.hyper, self.beta1, self.beta2,
-                       self.eps, self.weight_decay, self.clip_value, self.grad_sq)
-        if self.param_dtype == torch.float32:
-            unit.compute[lo:hi].copy_(unit.master)
+        with self._optimizer_state(unit) as (master, exp_avg, exp_avg_sq):
+            ops.adamw_step(master, shard, exp_avg, exp_avg_sq, out, self.hyper, self.beta1, self.beta2,
+                           self.eps, self.weight_decay, self.clip_value, self.grad_sq)
+            if self.param_dtype == torch.float32:
+                unit.compute[lo:hi].copy_(master)
         if w > 1:
             if dist.get_backend(self.group) == "nccl":
                 dist.all_gather_into_tensor(unit.compute, unit.compute[lo:hi].clone(), group=self.group)
@@ -460,6 +465,7 @@ class FsdpEngine(TrainEngine):
     def refresh_compute_from_master(self) -> None:
         if self.reshard:
             return self._shards_from_master()
+        self.sync_state()
         for u in self.units:
             u.compute[u.shard_lo:u.shard_hi].copy_(u.master)
             if self.world_size > 1:

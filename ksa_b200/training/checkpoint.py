@@ -77,7 +77,7 @@ def _gather_unit(engine, shard: torch.Tensor, unit) -> torch.Tensor:
     if engine.world_size == 1:
         return shard
     group = getattr(engine, "group", None)
-    shard = shard.contiguous()
+    shard = shard.to(engine.device).contiguous()      # offloaded state lives on the host
     if dist.get_backend(group) == "nccl":
         full = torch.empty(shard.numel() * engine.world_size, dtype=shard.dtype, device=shard.device)
         dist.all_gather_into_tensor(full, shard, group=group)
@@ -135,6 +135,8 @@ def engine_state_for_save(engine, with_optimizer: bool = True) -> Dict[str, Dict
     out: Dict[str, Dict[str, torch.Tensor]] = {"model": {}, "exp_avg": {}, "exp_avg_sq": {}}
     kinds = [("model", "master")] + ([("exp_avg", "exp_avg"), ("exp_avg_sq", "exp_avg_sq")] if with_optimizer else [])
     sharded = _sharded(engine)
+    if hasattr(engine, "sync_state"):
+        engine.sync_state()
     for u in engine.units:
         for key, attr in kinds:
             full = _gather_unit(engine, getattr(u, attr), u)
@@ -191,6 +193,8 @@ def load_engine_state(engine, model_state: Optional[Dict[str, torch.Tensor]],
     one unit at a time; returns the fused names that the checkpoint lacked."""
     missing: List[str] = []
     dev = engine.device
+    if hasattr(engine, "sync_state"):
+        engine.sync_state()
 
     def unit_tensors(src, slots):
         """Fused tensors of ``slots`` assembled from the reference-named entries of ``src``."""

@@ -22,6 +22,7 @@ Data-parallel / FSDP sharding of these units over ranks is layered on top by
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
@@ -52,11 +53,13 @@ class Unit:
     """One FSDP unit: flat buffers + the parameters that live in them."""
     name: str
     slots: List[ParamSlot] = field(default_factory=list)
+    index: int = 0                           # position in the engine's unit list
     size: int = 0
     compute: Optional[torch.Tensor] = None   # param_dtype, full size
     master: Optional[torch.Tensor] = None    # fp32 (full, or this rank's shard under FSDP)
     exp_avg: Optional[torch.Tensor] = None
     exp_avg_sq: Optional[torch.Tensor] = None
+    host_state: Optional[torch.Tensor] = None   # [3, shard] pinned host buffer behind the three views above (offload)
     grad: Optional[torch.Tensor] = None      # fp32, full size
     shard_lo: int = 0                        # [shard_lo, shard_hi): range of the flat buffer owned by this rank
     shard_hi: int = 0
@@ -67,8 +70,10 @@ class TrainEngine:
                  eps: float = 1e-8, weight_decay: float = 0.1, clip_value: float = 0.0,
                  param_dtype: Optional[torch.dtype] = None, device: Optional[torch.device] = None,
                  lr_lambda: Optional[Callable[[int], float]] = None, grad_accum_steps: int = 1,
-                 world_size: int = 1, rank: int = 0):
+                 world_size: int = 1, rank: int = 0, cpu_offload: bool = False):
         self.model = model
+        self.cpu_offload = bool(cpu_offload)   # master weights and moments in pinned host memory (training/offload.py)
+        self._offload = None
         self.base_lr = lr
         self.beta1, self.beta2 = betas
         self.eps, self.weight_decay, self.clip_value = eps, weight_decay, clip_value
@@ -137,6 +142,9 @@ class TrainEngine:
             unit.shard_lo, unit.shard_hi = self._shard_range(unit.size)
             planned.append(unit)
         self._allocate_storage(planned)
+        if self.cpu_offload:
+            from .offload import OptimizerStateOffload
+            self._offload = OptimizerStateOffload(dev, max(u.shard_hi - u.shard_lo for u in planned))
         self._place_frozen()
         for unit in planned:
             with torch.no_grad():
@@ -147,6 +155,7 @@ class TrainEngine:
                     s.param.data = unit.compute[s.offset:s.offset + s.numel].view(s.shape)
                     s.param.main_grad = unit.grad[s.offset:s.offset + s.numel].view(s.shape)
                     s.param._grad_written = False
+            unit.index = len(self.units)
             self.units.append(unit)
 
     def _place_frozen(self) -> None:
@@ -175,6 +184,11 @@ class TrainEngine:
     def _alloc_shard_state(self, unit: Unit) -> None:
         n = unit.shard_hi - unit.shard_lo
         dev = self.device
+        if self.cpu_offload:
+            from .offload import host_state
+            unit.host_state = host_state(n, dev)
+            unit.master, unit.exp_avg, unit.exp_avg_sq = (unit.host_state[i, :n] for i in range(3))
+            return
         unit.master = torch.zeros(n, dtype=torch.float32, device=dev)
         unit.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         unit.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
@@ -230,14 +244,39 @@ class TrainEngine:
                     p._grad_written = True
 
     # ------------------------------------------------------------------ optimizer
+    @contextlib.contextmanager
+    def _optimizer_state(self, unit: Unit):
+        """(master, exp_avg, exp_avg_sq) of ``unit`` as tensors on the engine's device for the duration of the block.
+        With the state offloaded to the host they are views of a staging slot: loaded before the block (the current
+        stream waits for the copy), written back after it, and the unit that is updated next starts loading."""
+        if self._offload is None:
+            yield unit.master, unit.exp_avg, unit.exp_avg_sq
+            return
+        idx = unit.index
+        state = self._offload.acquire(idx, unit.host_state)
+        if idx > 0:
+            self._offload.prefetch(idx - 1, self.units[idx - 1].host_state)
+        try:
+            yield state
+        finally:
+            self._offload.release(idx, unit.host_state)
+
+    def sync_state(self) -> None:
+        """Offloaded state only: wait until every write-back has reached host memory.  Called before the host reads
+        or overwrites master weights or moments (checkpoints, weight loading)."""
+        if self._offload is not None:
+            self._offload.synchronize()
+
     def _reduce_and_update(self, unit: Unit) -> None:
         """Single rank: AdamW over the whole unit.  The FSDP engine overrides this with the fused
         reduce-scatter + AdamW + weight all-gather."""
-        ops.adamw_step(unit.master, unit.grad, unit.exp_avg, unit.exp_avg_sq,
-                       unit.compute if self.param_dtype != torch.float32 else None,
-                       self.hyper, self.beta1, self.beta2, self.eps, self.weight_decay, self.clip_value, self.grad_sq)
-        if self.param_dtype == torch.float32:
-            unit.compute.copy_(unit.master)
+        with self._optimizer_state(unit) as (master, exp_avg, exp_avg_sq):
+            ops.adamw_step(master, unit.grad, exp_avg, exp_avg_sq,
+                           unit.compute if self.param_dtype != torch.float32 else None,
+                           self.hyper, self.beta1, self.beta2, self.eps, self.weight_decay, self.clip_value,
+                           self.grad_sq)
+            if self.param_dtype == torch.float32:
+                unit.compute.copy_(master)
 
     def optimizer_step(self) -> None:
         self._collect_autograd_grads()
@@ -288,6 +327,8 @@ class TrainEngine:
         inputs on the current stream.  Needs ``grad_accum_steps == 1`` windows to be uniform: a graph is
         keyed by (shape, first micro-step?, boundary?).
         """
+        if self._offload is not None:      # the staging ring is driven from the host: the step stays eager
+            return self.train_step(tokens, labels)
         first = self.micro_step == 0
         boundary = self.micro_step + 1 == self.grad_accum_steps
         key = (tuple(tokens.shape), first, boundary)
@@ -309,6 +350,7 @@ class TrainEngine:
     # ------------------------------------------------------------------ state
     def named_master_params(self):
         """(name, fp32 tensor view) for every parameter whose master copy is fully local (single rank)."""
+        self.sync_state()
         for u in self.units:
             for s in u.slots:
                 if s.offset >= u.shard_lo and s.offset + s.numel <= u.shard_hi:
@@ -316,6 +358,7 @@ class TrainEngine:
                     yield s.name, u.master[lo:lo + s.numel].view(s.shape)
 
     def state_dict(self) -> dict:
+        self.sync_state()
         return {
             "step": self.step_count,
             "units": {u.name: {"master": u.master, "exp_avg": u.exp_avg, "exp_avg_sq": u.exp_avg_sq,
@@ -326,6 +369,7 @@ class TrainEngine:
 
     def load_state_dict(self, state: dict, load_optimizer: bool = True) -> None:
         self.step_count = int(state.get("step", 0)) if load_optimizer else self.step_count
+        self.sync_state()
         for u in self.units:
             su = state["units"][u.name]
             u.master.copy_(su["master"])
@@ -335,12 +379,14 @@ class TrainEngine:
         self.refresh_compute_from_master()
 
     def refresh_compute_from_master(self) -> None:
+        self.sync_state()
         for u in self.units:
             if self.world_size == 1:
                 u.compute.copy_(u.master)
 
     def load_model_weights(self, state: Dict[str, torch.Tensor]) -> None:
         """Overwrite compute and master weights from a (fused-name) model state dict."""
+        self.sync_state()
         with torch.no_grad():
             for u in self.units:
                 for s in u.slots:

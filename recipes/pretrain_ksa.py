@@ -175,8 +175,8 @@ def train(args) -> dict:
     # flags of the reference's CLI that mean nothing here: the attention kernels are this package's own, and the
     # next unit's parameters are always gathered one unit ahead
     if args.cpu_offload:
-        raise SystemExit("--cpu-offload is not supported: master weights and moments are 12 bytes per parameter per rank "
-                         "group and stay in HBM (180 GB per GPU); shard over more ranks or use --reshard-after-forward")
+        print_rank_0("[recipe] --cpu-offload: fp32 master weights and Adam moments live in pinned host memory and pass "
+                     "through a staging ring on the GPU for the update; the step runs eagerly")
     for flag in ("prefetch_params_in_forward", "use_flash_attention_2"):
         if getattr(args, flag):
             print_rank_0(f"[recipe] --{flag.replace('_', '-')} has no effect in this framework (accepted for compatibility)")
@@ -206,7 +206,8 @@ def train(args) -> dict:
                               num_training_steps=args.num_training_steps, num_decay_steps=args.num_decay_steps,
                               base_lr=args.learning_rate, min_lr=args.min_lr)
     common = dict(lr=args.learning_rate, betas=(args.beta1, args.beta2), eps=1e-8, weight_decay=args.weight_decay,
-                  clip_value=args.clip_range, lr_lambda=lr_lambda, grad_accum_steps=args.gradient_accumulation_steps)
+                  clip_value=args.clip_range, lr_lambda=lr_lambda, grad_accum_steps=args.gradient_accumulation_steps,
+                  cpu_offload=args.cpu_offload)
     if world > 1:
         from ksa_b200.parallel.fsdp import FsdpEngine, default_overlap
         if args.overlap == "auto":
@@ -283,7 +284,7 @@ def train(args) -> dict:
 
     # one CUDA graph per step on a single GPU; multi-GPU steps stay eager (see FsdpEngine.graphed_step)
     use_graph = use_cuda and world == 1 and not args.no_cuda_graph and not args.enable_distill \
-        and not args.enable_gradient_checkpointing and not args.packing
+        and not args.enable_gradient_checkpointing and not args.packing and not args.cpu_offload
     n_workers = args.num_workers if args.num_workers is not None else getattr(dataset, "loader_workers", 0)
     loader = dataset
     if n_workers > 0:

@@ -99,8 +99,10 @@ def test_recipe_trains_checkpoints_and_resumes(tmp_path):
     r1 = train(get_argument_parser().parse_args(base + ["--num-training-steps", "8"]))
     assert r1["steps"] == 8 and (out / "latest").read_text() == "global_step8"
     assert (out / "global_step8" / "dataloader_state.pt").exists() and (out / "metrics.csv").exists()
+    # the resumed leg keeps master weights and moments in host memory (--cpu-offload)
     r2 = train(get_argument_parser().parse_args(base + ["--num-training-steps", "12", "--checkpoint-dir", str(out),
-                                                        "--resume-weights", "--resume-optimizer", "--resume-dataloader"]))
+                                                        "--resume-weights", "--resume-optimizer", "--resume-dataloader",
+                                                        "--cpu-offload"]))
     assert r2["steps"] == 12 and (out / "global_step12").is_dir()
     assert r2["loss"] < 5.6
 
