@@ -364,8 +364,15 @@ class _QkNormRopeFn(torch.autograd.Function):
                 targets.append(mg)
             else:
                 targets.append(torch.zeros(D, dtype=torch.float32, device=qkv.device))
-        _lib.call("ksa_qknorm_rope_bwd", qkv, d_out, d_qkv, q_w, k_w, pos, rstd, targets[0], targets[1],
+        sinks = targets
+        if _deterministic:     # the kernel's weight gradients are fp32 atomics: let them land in scratch vectors
+            sinks = [None if t is None else torch.zeros(D, dtype=torch.float32, device=qkv.device) for t in targets]
+        _lib.call("ksa_qknorm_rope_bwd", qkv, d_out, d_qkv, q_w, k_w, pos, rstd, sinks[0], sinks[1],
                   qkv.stride(0), d_out.stride(0), T, Hq, Hkv, D, float(theta), float(eps), int(interleaved), 1)
+        if _deterministic:
+            for t, g in zip(targets, _qk_norm_weight_grads(qkv, d_out, q_w, k_w, pos, *ctx.cfg)):
+                if t is not None:
+                    t.add_(g)
         grads = []
         for w, t in zip((q_w, k_w), targets):
             if w is None or getattr(w, "main_grad", None) is not None:
@@ -373,6 +380,26 @@ class _QkNormRopeFn(torch.autograd.Function):
             else:
                 grads.append(t.to(w.dtype))
         return d_qkv, grads[0], grads[1], None, None, None, None, None, None, None
+
+
+def _qk_norm_weight_grads(qkv, d_out, q_w, k_w, pos, Hq, Hkv, D, theta, eps, interleaved):
+    """Gradients of the two QK-norm weight vectors in a fixed summation order (deterministic mode): the fp32 formulas
+    differentiated by autograd, whose reductions over rows and heads use no atomics."""
+    T = qkv.shape[0]
+    with torch.enable_grad():
+        q = qkv[:, :Hq * D].detach().float().reshape(1, T, Hq, D)
+        k = qkv[:, Hq * D:(Hq + Hkv) * D].detach().float().reshape(1, T, Hkv, D)
+        ws = [None if w is None else w.detach().float().requires_grad_(True) for w in (q_w, k_w)]
+        qo, ko = ref.qk_norm_rope(q, k, ws[0], ws[1], pos, theta, eps, interleaved)
+        dq = d_out[:, :Hq * D].float().reshape(1, T, Hq, D)
+        dk = d_out[:, Hq * D:(Hq + Hkv) * D].float().reshape(1, T, Hkv, D)
+        live = [w for w in ws if w is not None]
+        got = list(torch.autograd.grad([qo, ko], live, [dq, dk], allow_unused=True)) if live else []
+    out = []
+    for w in ws:
+        g = got.pop(0) if w is not None else None
+        out.append(torch.zeros(D, dtype=torch.float32, device=qkv.device) if (w is not None and g is None) else g)
+    return out
 
 
 def qk_norm_rope_packed(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
@@ -513,11 +540,24 @@ class _EmbeddingFn(torch.autograd.Function):
             if not getattr(table, "_grad_written", False):
                 mg.zero_()
                 table._grad_written = True
-            _lib.call("ksa_embedding_bwd", flat, d2, mg, flat.numel(), D, table.shape[0])
+            _embedding_grad(flat, d2, mg, D, table.shape[0])
             return None, None
         g = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
-        _lib.call("ksa_embedding_bwd", flat, d2, g, flat.numel(), D, table.shape[0])
+        _embedding_grad(flat, d2, g, D, table.shape[0])
         return None, g.to(table.dtype)
+
+
+def _embedding_grad(flat, d2, grad, D, vocab) -> None:
+    """``grad[flat[i]] += d2[i]``.  The kernel adds rows with fp32 atomics; in deterministic mode the rows of every
+    token id are brought together by a stable sort and summed one segment per thread, in row order, and the sums are
+    added to distinct rows of ``grad``."""
+    if not _deterministic:
+        _lib.call("ksa_embedding_bwd", flat, d2, grad, flat.numel(), D, vocab)
+        return
+    order = torch.argsort(flat, stable=True)
+    ids, counts = torch.unique_consecutive(flat[order], return_counts=True)
+    sums = torch.segment_reduce(d2[order].float(), "sum", lengths=counts, axis=0, unsafe=True)
+    grad[ids] += sums          # distinct rows: every element is written once
 
 
 def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
@@ -539,10 +579,12 @@ _deterministic = os.environ.get("KSA_DETERMINISTIC", "0") == "1"
 
 
 def set_deterministic(on: bool) -> None:
-    """Select the bit-reproducible attention backward (two kernels that never accumulate across CTAs) instead of the
-    fused key-stationary one, whose dQ is summed with floating-point reductions in an order that varies between runs.
-    ``KSA_DETERMINISTIC=1`` sets the initial value.  The reference kernel has the same switch
-    (``flash_attn/cute/interface.py:801-811`` in the ``flash_attn_cute`` wheel)."""
+    """Bit-reproducible training step on one GPU.  Attention backward: two kernels that never accumulate across CTAs
+    instead of the fused key-stationary one, whose dQ is summed with floating-point reductions in an order that
+    varies between runs.  QK-norm weight gradients, the embedding gradient and the sum of squared gradients of the
+    optimizer: summed in a fixed order instead of with fp32 atomics.  ``KSA_DETERMINISTIC=1`` sets the initial value.
+    The reference kernel has the same switch (``flash_attn/cute/interface.py:801-811`` in the ``flash_attn_cute``
+    wheel).  Not covered: the gradient-norm metric of the fused multi-GPU reduce + AdamW kernel (weights are)."""
     global _deterministic
     _deterministic = bool(on)
 
@@ -924,6 +966,12 @@ def adamw_step(master, grad, m, v, out_bf16, hyper, beta1, beta2, eps, weight_de
             out_bf16.copy_(master)
         return
     n = master.numel()
+    if _deterministic and sumsq is not None:     # the kernel adds its blocks' sums with an atomic: sum in a fixed order
+        g = grad * hyper[3]
+        if clip_value > 0:
+            g = g.clamp_(-clip_value, clip_value)
+        sumsq += (g * g).sum()
+        sumsq = None
     _lib.call("ksa_adamw", master, grad, m, v, out_bf16, n, hyper, float(beta1), float(beta2), float(eps),
               float(weight_decay), float(clip_value), sumsq)
 

@@ -130,3 +130,40 @@ def test_optimizer_state_offloaded_to_pinned_host_memory_matches_resident_state(
         assert (a.master.cpu() - b.master).norm() <= 2e-2 * b.master.norm()
     n = sum(u.host_state.numel() for u in e1.units) * 4
     assert e1._offload.h2d_bytes == 6 * n and e1._offload.d2h_bytes == 6 * n
+
+
+def test_deterministic_mode_makes_training_steps_bit_reproducible():
+    """``ops.set_deterministic(True)``: two runs of the same three steps give bit-identical master weights, moments,
+    losses and gradient norms (the attention backward, QK-norm weight gradients, embedding gradient and the sum of
+    squared gradients all sum in a fixed order), and stay close to the default mode."""
+    from ksa_b200 import ops
+    cfg = _tiny(128, 128, embed_dim=512)
+    torch.manual_seed(0)
+    base = get_model_class(cfg.model_class)(cfg)
+    base.init_weights(seed=0)
+    toks = torch.randint(0, cfg.vocab_size, (3, 2, 513), device="cuda")
+    toks[:, :, 100:140] = 7                      # one id many times: its embedding row collects many gradient rows
+
+    def run():
+        model = copy.deepcopy(base).to("cuda").to(torch.bfloat16)
+        eng = TrainEngine(model, lr=1e-3, weight_decay=0.1, clip_value=1.0)
+        out = []
+        for t in toks:
+            loss = eng.train_step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
+            out.append((float(loss), float(eng.grad_norm())))
+        _lib.check_status()
+        return out, [(u.master.clone(), u.exp_avg_sq.clone()) for u in eng.units]
+
+    free = run()
+    ops.set_deterministic(True)
+    try:
+        a, b = run(), run()
+    finally:
+        ops.set_deterministic(False)
+    assert a[0] == b[0], (a[0], b[0])
+    for (m0, v0), (m1, v1) in zip(a[1], b[1]):
+        assert torch.equal(m0, m1) and torch.equal(v0, v1)
+    for (l0, g0), (l1, g1) in zip(a[0], free[0]):
+        assert abs(l0 - l1) < 2e-2 and abs(g0 - g1) < 0.05 * g1
+    for (m0, _), (m1, _) in zip(a[1], free[1]):
+        assert (m0 - m1).norm() <= 2e-2 * m1.norm()
