@@ -194,7 +194,8 @@ def train(args) -> dict:
         # every rank initialises from the same seed: identical weights with no broadcast (the reference initialises on
         # rank 0 and broadcasts parameter by parameter, muse/training/distributed.py:448-532)
         model.init_weights(seed=args.seed or 0)
-    model.loss_chunk_tokens = args.chunked_loss_minibatch_size
+    # --disable-chunked-loss: the head and the loss over the whole sequence at once (one chunk of logits)
+    model.loss_chunk_tokens = (1 << 30) if args.disable_chunked_loss else args.chunked_loss_minibatch_size
     if args.enable_gradient_checkpointing:
         n = set_activation_checkpointing(model, model.get_checkpointable_module_classes())
         print_rank_0(f"[recipe] activation checkpointing on {n} layers")
