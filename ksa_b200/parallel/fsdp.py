@@ -76,6 +76,8 @@ def default_overlap(world_size: int, context_parallel: int = 1, reshard_after_fo
 
 
 class FsdpEngine(TrainEngine):
+    _overlap_capable = False      # this engine schedules reduce + update under the backward pass itself
+
     def __init__(self, model: nn.Module, *args, world_size: int = 1, rank: int = 0, group=None, comm: Optional[str] = None,
                  overlap: str = "stream", pair_gather_min_flops: float = 3e11, reshard_after_forward: bool = False,
                  **kw):

@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import contextlib
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
@@ -65,12 +66,33 @@ class Unit:
     shard_hi: int = 0
 
 
+class _UnitBoundary(torch.autograd.Function):
+    """Identity on a layer's inputs.  Its backward runs once every backward kernel of that layer (and of everything
+    after it) has been launched, and tells the engine that the unit's gradients are complete."""
+
+    @staticmethod
+    def forward(ctx, engine, tag, x, delta):
+        ctx.engine, ctx.tag = engine, tag
+        ctx.has_delta = delta is not None
+        return (x.view_as(x), delta.view_as(delta)) if delta is not None else (x.view_as(x), None)
+
+    @staticmethod
+    def backward(ctx, gx, gd):
+        ctx.engine._unit_backward_done(ctx.tag)
+        return None, None, gx, (gd if ctx.has_delta else None)
+
+
 class TrainEngine:
+    # the single-GPU engine can update a unit on a side stream while the backward pass of the earlier units still
+    # runs (the sharded engine has its own schedule and switches this off)
+    _overlap_capable = True
+
     def __init__(self, model: nn.Module, lr: float = 4e-4, betas: Tuple[float, float] = (0.9, 0.95),
                  eps: float = 1e-8, weight_decay: float = 0.1, clip_value: float = 0.0,
                  param_dtype: Optional[torch.dtype] = None, device: Optional[torch.device] = None,
                  lr_lambda: Optional[Callable[[int], float]] = None, grad_accum_steps: int = 1,
-                 world_size: int = 1, rank: int = 0, cpu_offload: bool = False):
+                 world_size: int = 1, rank: int = 0, cpu_offload: bool = False,
+                 overlap_optimizer: Optional[bool] = None):
         self.model = model
         self.cpu_offload = bool(cpu_offload)   # master weights and moments in pinned host memory (training/offload.py)
         self._offload = None
@@ -96,6 +118,23 @@ class TrainEngine:
             self._hyper_ring = self._hyper_ring.pin_memory()
         self.grad_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._graphs: Dict[tuple, "_CapturedStep"] = {}
+        # AdamW of a unit under the backward pass of the units in front of it: launched on a side stream as soon as
+        # the unit's backward kernels have been launched (overlap_optimizer=True or KSA_OVERLAP_OPTIMIZER=1).  With
+        # the state resident in HBM it measured 114.1 against 114.6 ms per step (Qwen3-1.9B-KSA, 8192 tokens: AdamW
+        # and the backward GEMMs compete for the same HBM), so it is off by default there; with the state offloaded
+        # to the host it hides the backward pass under the PCIe copies and is on.
+        if overlap_optimizer is None:
+            env = os.environ.get("KSA_OVERLAP_OPTIMIZER")
+            overlap_optimizer = (env == "1") if env is not None else (self.cpu_offload and self.device.type == "cuda")
+        self.overlap_optimizer = bool(overlap_optimizer) and self._overlap_capable
+        self._hooks_active = False
+        self._overlap_step = False
+        self._async_done: set = set()
+        self.opt_stream = None       # CPU (tests): the update runs in place, inside the backward pass
+        if self.overlap_optimizer:
+            if self.device.type == "cuda":
+                self.opt_stream = torch.cuda.Stream(device=self.device)
+            self._install_overlap_hooks()
 
     # ------------------------------------------------------------------ construction
     def _unit_modules(self) -> List[Tuple[str, List[Tuple[str, nn.Parameter]]]]:
@@ -230,18 +269,65 @@ class TrainEngine:
     def _collect_autograd_grads(self) -> None:
         """Fold ``.grad`` (ops without a main_grad path, the CPU path) into the fp32 buffers; zero the rest."""
         for u in self.units:
-            for s in u.slots:
-                p = s.param
-                if p.grad is not None:
-                    if getattr(p, "_grad_written", False):
-                        p.main_grad.add_(p.grad.to(torch.float32))
-                    else:
-                        p.main_grad.copy_(p.grad)
-                        p._grad_written = True
-                    p.grad = None
-                elif not getattr(p, "_grad_written", False):
-                    p.main_grad.zero_()
+            self._collect_unit_grads(u)
+
+    @staticmethod
+    def _collect_unit_grads(u: Unit) -> None:
+        for s in u.slots:
+            p = s.param
+            if p.grad is not None:
+                if getattr(p, "_grad_written", False):
+                    p.main_grad.add_(p.grad.to(torch.float32))
+                else:
+                    p.main_grad.copy_(p.grad)
                     p._grad_written = True
+                p.grad = None
+            elif not getattr(p, "_grad_written", False):
+                p.main_grad.zero_()
+                p._grad_written = True
+
+    # ------------------------------------------------------------------ optimizer under the backward pass
+    def _install_overlap_hooks(self) -> None:
+        model = self.model
+        layers = list(model.get_layers_to_shard()) if hasattr(model, "get_layers_to_shard") else []
+        names = [u.name for u in self.units]
+        for i, layer in enumerate(layers):
+            if f"layer{i}" in names:
+                layer.register_forward_pre_hook(self._make_unit_pre_hook(names.index(f"layer{i}")))
+        if layers and "head" in names:
+            layers[-1].register_forward_hook(self._make_head_hook(names.index("head")))
+
+    def _make_unit_pre_hook(self, ui: int):
+        def hook(module, args):
+            x, delta = args[0], args[1]
+            if self._hooks_active and torch.is_grad_enabled() and x.requires_grad:
+                x, delta = _UnitBoundary.apply(self, ui, x, delta)
+                return (x, delta) + tuple(args[2:])
+            return None
+        return hook
+
+    def _make_head_hook(self, head_ui: int):
+        def hook(module, args, output):
+            if self._hooks_active and torch.is_grad_enabled() and isinstance(output, tuple) and output[0].requires_grad:
+                return _UnitBoundary.apply(self, head_ui, output[0], output[1]) + tuple(output[2:])
+            return None
+        return hook
+
+    def _unit_backward_done(self, ui: int) -> None:
+        """Every backward kernel that writes unit ``ui``'s gradients has been launched: update it on the side stream."""
+        if not self._hooks_active or ui in self._async_done:
+            return
+        u = self.units[ui]
+        self._collect_unit_grads(u)
+        if self.opt_stream is None:
+            self._reduce_and_update(u)
+        else:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.opt_stream):
+                self.opt_stream.wait_event(ev)
+                self._reduce_and_update(u)
+        self._async_done.add(ui)
 
     # ------------------------------------------------------------------ optimizer
     @contextlib.contextmanager
@@ -280,9 +366,16 @@ class TrainEngine:
 
     def optimizer_step(self) -> None:
         self._collect_autograd_grads()
-        self.grad_sq.zero_()
+        if not self._overlap_step:
+            self.grad_sq.zero_()
+            self._async_done = set()
         for unit in reversed(self.units):
-            self._reduce_and_update(unit)
+            if unit.index not in self._async_done:     # updated under the backward pass already
+                self._reduce_and_update(unit)
+        if self._overlap_step and self.opt_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.opt_stream)
+        self._overlap_step = False
+        self._async_done = set()
         self._finish_step()
 
     def _finish_step(self) -> None:
@@ -297,11 +390,19 @@ class TrainEngine:
         """Forward and backward of one micro-batch.  ``step_fn(tokens, labels) -> loss`` replaces the plain language
         model loss: it must run the model's forward AND one backward pass itself and return the detached loss
         (distillation uses it), so that whatever the engine hangs on the forward and backward passes still applies."""
-        if step_fn is not None:
-            return step_fn(tokens, labels)
-        loss = self.model(tokens, labels=labels, **kw)
-        loss.backward()
-        return loss.detach()
+        self._async_done = set()
+        self._overlap_step = self.overlap_optimizer and self.micro_step + 1 == self.grad_accum_steps
+        self._hooks_active = self._overlap_step
+        if self._overlap_step:
+            self.grad_sq.zero_()        # the units add their sums of squares while the backward pass still runs
+        try:
+            if step_fn is not None:
+                return step_fn(tokens, labels)
+            loss = self.model(tokens, labels=labels, **kw)
+            loss.backward()
+            return loss.detach()
+        finally:
+            self._hooks_active = False
 
     def train_step(self, tokens: torch.Tensor, labels: torch.Tensor, **kw) -> torch.Tensor:
         """One micro-batch; runs the optimizer at the accumulation boundary.  Returns the loss (device)."""
@@ -310,10 +411,11 @@ class TrainEngine:
         if tokens.device != self.device:  # e.g. pinned host batches
             tokens = tokens.to(self.device, non_blocking=True)
             labels = labels.to(self.device, non_blocking=True)
+        if self.micro_step + 1 == self.grad_accum_steps:
+            self._write_hyper()     # before the backward pass: units may be updated while it still runs
         loss = self.forward_backward(tokens, labels, **kw)
         self.micro_step += 1
         if self.micro_step == self.grad_accum_steps:
-            self._write_hyper()
             self.optimizer_step()
             self.step_count += 1
             self.micro_step = 0
@@ -327,7 +429,9 @@ class TrainEngine:
         inputs on the current stream.  Needs ``grad_accum_steps == 1`` windows to be uniform: a graph is
         keyed by (shape, first micro-step?, boundary?).
         """
-        if self._offload is not None:      # the staging ring is driven from the host: the step stays eager
+        # the staging ring is driven from the host, and deterministic mode sizes a buffer from the data (a host
+        # synchronisation, which a stream capture forbids): both steps stay eager
+        if self._offload is not None or ops.is_deterministic():
             return self.train_step(tokens, labels)
         first = self.micro_step == 0
         boundary = self.micro_step + 1 == self.grad_accum_steps

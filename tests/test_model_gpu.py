@@ -167,3 +167,41 @@ def test_deterministic_mode_makes_training_steps_bit_reproducible():
         assert abs(l0 - l1) < 2e-2 and abs(g0 - g1) < 0.05 * g1
     for (m0, _), (m1, _) in zip(a[1], free[1]):
         assert (m0 - m1).norm() <= 2e-2 * m1.norm()
+
+
+def test_optimizer_under_the_backward_pass_matches_the_optimizer_after_it():
+    """Units updated on a side stream while the backward pass still runs against the whole optimizer after the
+    backward pass: bit for bit with deterministic kernels (eager), within run-to-run noise when the overlapped step
+    is replayed from a CUDA graph."""
+    from ksa_b200 import ops
+    cfg = _tiny(128, 128, embed_dim=512)
+    torch.manual_seed(0)
+    base = get_model_class(cfg.model_class)(cfg)
+    base.init_weights(seed=0)
+    toks = torch.randint(0, cfg.vocab_size, (4, 2, 513), device="cuda")
+
+    def run(overlap, graphed):
+        model = copy.deepcopy(base).to("cuda").to(torch.bfloat16)
+        eng = TrainEngine(model, lr=1e-3, weight_decay=0.1, clip_value=1.0, overlap_optimizer=overlap)
+        assert eng.overlap_optimizer == overlap
+        fn = eng.graphed_step if graphed else eng.train_step
+        losses = [float(fn(t[:, :-1].contiguous(), t[:, 1:].contiguous())) for t in toks]
+        torch.cuda.synchronize()
+        _lib.check_status()
+        assert bool(eng._graphs) == (graphed and not ops.is_deterministic())
+        return losses, float(eng.grad_norm()), [(u.master.clone(), u.exp_avg.clone(), u.compute.clone())
+                                                for u in eng.units]
+
+    ops.set_deterministic(True)
+    try:
+        ref_run, got = run(False, False), run(True, False)
+        assert run(True, True)[0] == ref_run[0]          # deterministic mode keeps the graph entry point eager
+    finally:
+        ops.set_deterministic(False)
+    assert got[0] == ref_run[0] and got[1] == ref_run[1], (got[0], ref_run[0])
+    for a, b in zip(got[2], ref_run[2]):
+        assert all(torch.equal(x, y) for x, y in zip(a, b))
+    replayed = run(True, True)
+    assert all(abs(a - b) < 2e-2 for a, b in zip(replayed[0], ref_run[0])), (replayed[0], ref_run[0])
+    for a, b in zip(replayed[2], ref_run[2]):
+        assert (a[0] - b[0]).norm() <= 2e-2 * b[0].norm()
