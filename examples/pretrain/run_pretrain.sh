@@ -3,6 +3,8 @@
 # reference, which launch with mpirun across hosts).  Usage:
 #   STAGE=8k   bash examples/pretrain/run_pretrain.sh            # from scratch
 #   STAGE=128k CHECKPOINT_DIR=out/64k bash examples/pretrain/run_pretrain.sh   # length extension, weights-only resume
+# RECOMPUTE=full|mlp chooses what the long-context stages recompute in the backward pass: whole layers (as the
+# reference does) or only the feed-forward blocks (keeps attention and its projections; fits in 180 GB per GPU).
 set -euo pipefail
 STAGE=${STAGE:-8k}
 NGPU=${NGPU:-8}
@@ -12,9 +14,9 @@ OUTPUT_DIR=${OUTPUT_DIR:-out/${STAGE}}
 CHECKPOINT_DIR=${CHECKPOINT_DIR:-}
 case "$STAGE" in
   8k)   CP=1; LR=4e-4; MIN_LR=4e-5; STEPS=127200; WARM=1000; DECAY=1000; GRAD_ACC=${GRAD_ACC:-30}; EXTRA="" ;;
-  32k)  CP=2; LR=1e-5; MIN_LR=1e-6; STEPS=1600;   WARM=100;  DECAY=100;  GRAD_ACC=${GRAD_ACC:-60}; EXTRA="--enable-gradient-checkpointing" ;;
-  64k)  CP=4; LR=1e-5; MIN_LR=1e-6; STEPS=1600;   WARM=100;  DECAY=100;  GRAD_ACC=${GRAD_ACC:-120}; EXTRA="--enable-gradient-checkpointing" ;;
-  128k) CP=8; LR=1e-5; MIN_LR=1e-6; STEPS=1600;   WARM=100;  DECAY=100;  GRAD_ACC=${GRAD_ACC:-240}; EXTRA="--enable-gradient-checkpointing" ;;
+  32k)  CP=2; LR=1e-5; MIN_LR=1e-6; STEPS=1600;   WARM=100;  DECAY=100;  GRAD_ACC=${GRAD_ACC:-60}; EXTRA="--enable-gradient-checkpointing --gradient-checkpointing-mode ${RECOMPUTE:-full}" ;;
+  64k)  CP=4; LR=1e-5; MIN_LR=1e-6; STEPS=1600;   WARM=100;  DECAY=100;  GRAD_ACC=${GRAD_ACC:-120}; EXTRA="--enable-gradient-checkpointing --gradient-checkpointing-mode ${RECOMPUTE:-full}" ;;
+  128k) CP=8; LR=1e-5; MIN_LR=1e-6; STEPS=1600;   WARM=100;  DECAY=100;  GRAD_ACC=${GRAD_ACC:-240}; EXTRA="--enable-gradient-checkpointing --gradient-checkpointing-mode ${RECOMPUTE:-full}" ;;
   *) echo "unknown STAGE $STAGE"; exit 1 ;;
 esac
 RESUME=""

@@ -151,6 +151,16 @@ class KsaDecoderLayer(nn.Module):
         self.attn = KsaAttention(cfg, layer_idx, is_summary_layer)
         self.mlp_norm = RMSNormParam(cfg.embed_dim, cfg.norm_eps)
         self.mlp = SwiGluMlp(cfg.embed_dim, cfg.intermediate_dim)
+        # selective recomputation: drop the gate/up projection and the SwiGLU output (3 x intermediate_dim of the
+        # roughly 5 x embed_dim + 3 x intermediate_dim values a layer keeps per token) and recompute them in the
+        # backward pass; attention, its projections and the norms are kept (training/activations.py, mode "mlp")
+        self.recompute_mlp = False
+
+    def _mlp(self, h: torch.Tensor, tp, rows: Optional[int]) -> torch.Tensor:
+        if self.recompute_mlp and tp is None and torch.is_grad_enabled() and h.requires_grad:
+            from torch.utils.checkpoint import checkpoint
+            return checkpoint(self.mlp, h, None, None, use_reentrant=False)
+        return self.mlp(h, tp, rows)
 
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], meta: "BatchMeta",
                 collect: Optional[list] = None) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -221,7 +231,7 @@ class KsaDecoderLayer(nn.Module):
             if collect is not None:
                 collect.append(attn_out[:n_text])
             x, h2 = _add_norm(tp, x, attn_out, self.mlp_norm.scale, cfg.norm_eps, defer=True)
-            return x, self.mlp(h2, tp, rows_mlp)
+            return x, self._mlp(h2, tp, rows_mlp)
         # full causal attention on the text rows; summary rows (if any) pass through unchanged
         qkv = _col_linear(tp, h[:n_text], a.wqkv.weight)
         qkv = ops.qk_norm_rope_packed(qkv, a._norm_w(a.q_norm), a._norm_w(a.k_norm), meta.pos[:n_text], Hq, Hkv, Dh,
@@ -239,7 +249,7 @@ class KsaDecoderLayer(nn.Module):
         if collect is not None:
             collect.append(attn_out)
         x, h2 = _add_norm(tp, x, attn_out, self.mlp_norm.scale, cfg.norm_eps, defer=True)
-        return x, self.mlp(h2[:n_text], tp, rows_mlp)
+        return x, self._mlp(h2[:n_text], tp, rows_mlp)
 
 
 class BatchMeta:

@@ -76,6 +76,8 @@ def get_argument_parser() -> argparse.ArgumentParser:
     a("--clip-range", type=float, default=1.0)
     a("--use-flash-attention-2", action="store_true")
     a("--enable-gradient-checkpointing", action="store_true")
+    a("--gradient-checkpointing-mode", default="full", choices=["full", "mlp"],
+      help="with --enable-gradient-checkpointing: recompute whole layers, or only their feed-forward blocks")
     a("--gradient-accumulation-steps", type=int, default=1)
     a("--allow-random-init-params", default="", help="comma-separated parameter names that may be missing from "
       "--model-dir (or have another shape there) and keep their random initialisation")
@@ -197,8 +199,9 @@ def train(args) -> dict:
     # --disable-chunked-loss: the head and the loss over the whole sequence at once (one chunk of logits)
     model.loss_chunk_tokens = (1 << 30) if args.disable_chunked_loss else args.chunked_loss_minibatch_size
     if args.enable_gradient_checkpointing:
-        n = set_activation_checkpointing(model, model.get_checkpointable_module_classes())
-        print_rank_0(f"[recipe] activation checkpointing on {n} layers")
+        n = set_activation_checkpointing(model, model.get_checkpointable_module_classes(),
+                                         mode=args.gradient_checkpointing_mode)
+        print_rank_0(f"[recipe] activation checkpointing ({args.gradient_checkpointing_mode}) on {n} layers")
     if args.enable_distill:
         stats = freeze_params_by_pattern(model, ["summary_embedding", "_summary"])
         print_rank_0(f"[recipe] distillation: {stats['trainable']:,} trainable / {stats['frozen']:,} frozen parameters")

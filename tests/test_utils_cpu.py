@@ -126,6 +126,45 @@ def test_activation_checkpointing_keeps_gradients():
         torch.testing.assert_close(grads[0][n], grads[1][n], atol=1e-6, rtol=1e-5)
 
 
+def test_selective_recomputation_of_the_feed_forward_blocks_keeps_gradients_and_saves_less():
+    """``mode="mlp"``: same loss and gradients; the tensors autograd keeps alive shrink by the gate/up projection and
+    the SwiGLU output of every layer, and no layer is wrapped (parameter names stay as they are)."""
+    from ksa_b200.models import get_model_class
+    from ksa_b200.training.activations import set_activation_checkpointing
+    cfg = get_preset("qwen3-ksa-tiny").merge({"num_layers": 2, "summary_layer_freq": [1, 0], "embed_dim": 64,
+                                               "intermediate_dim": 256, "vocab_size": 128, "head_dim": 16,
+                                               "summary_chunk_size": 16})
+    out = []
+    for mode in (None, "mlp", "full"):
+        m = get_model_class(cfg.model_class)(cfg)
+        m.init_weights(seed=0)
+        m = m.float()
+        if mode:
+            assert set_activation_checkpointing(m, m.get_checkpointable_module_classes(), mode=mode) == 2
+        toks = torch.randint(0, 128, (2, 65), generator=torch.Generator().manual_seed(3))
+        kept = {}
+
+        def pack(t):
+            kept[(t.data_ptr(), t.shape)] = t.numel() * t.element_size()
+            return t
+        with torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t):
+            loss = m(toks[:, :-1], toks[:, 1:])
+        loss.backward()
+        params = {p.data_ptr() for p in m.parameters()}
+        saved = sum(v for (ptr, _), v in kept.items() if ptr not in params)
+        out.append((float(loss.detach()), {n.replace("_checkpoint_wrapped_module.", ""): p.grad.clone()
+                                  for n, p in m.named_parameters()}, saved, [n for n, _ in m.named_parameters()]))
+    (l0, g0, s0, n0), (l1, g1, s1, n1), (l2, g2, s2, _) = out
+    assert l0 == l1 == l2 and n0 == n1
+    for n in g0:
+        torch.testing.assert_close(g0[n], g1[n], atol=1e-6, rtol=1e-5)
+    rows = 2 * 64                                 # text rows; the summary rows only add to the saving
+    assert s0 - s1 >= 2 * rows * 3 * 256 * 4      # two layers x (gate | up | activation) in fp32
+    assert s2 < s1 < s0
+    with pytest.raises(ValueError):
+        set_activation_checkpointing(m, None, mode="attention")
+
+
 # ------------------------------------------------------------------------------------------------ metrics
 def test_series_algebra_is_lazy_and_exact():
     s = Series("x")
