@@ -39,6 +39,7 @@ class OptimizerStateOffload:
         self.slots = max(int(slots), 1)
         self.staging = torch.zeros(self.slots, 3, max(max_elems, 1), dtype=torch.float32, device=self.device)
         self._tenant: List[Optional[int]] = [None] * self.slots      # unit index whose state the slot holds
+        self._busy: List[bool] = [False] * self.slots                # acquired and not yet released
         self._loaded: Dict[int, "torch.cuda.Event"] = {}            # unit index -> its load has been issued
         self._written: List[Optional["torch.cuda.Event"]] = [None] * self.slots
         self.h2d_bytes = 0
@@ -58,6 +59,8 @@ class OptimizerStateOffload:
         slot = self._slot(idx)
         if self._tenant[slot] == idx:
             return
+        if self._busy[slot]:
+            return      # the slot's tenant is being updated (a one-slot ring): acquire() loads the unit later
         self._tenant[slot] = idx
         dst = self._view(idx, host)
         self.h2d_bytes += host.numel() * 4
@@ -75,6 +78,9 @@ class OptimizerStateOffload:
     def acquire(self, idx: int, host: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """Device views (master, exp_avg, exp_avg_sq) of unit ``idx``; the current stream waits for the load."""
         self.prefetch(idx, host)
+        if self._tenant[self._slot(idx)] != idx:
+            raise RuntimeError(f"unit {idx} needs the staging slot that unit {self._tenant[self._slot(idx)]} still holds")
+        self._busy[self._slot(idx)] = True
         if self.cuda:
             ev = self._loaded.pop(idx, None)
             if ev is not None:
@@ -88,6 +94,7 @@ class OptimizerStateOffload:
         src = self._view(idx, host)
         self.d2h_bytes += host.numel() * 4
         self._tenant[slot] = None
+        self._busy[slot] = False
         if not self.cuda:
             host.copy_(src)
             return
@@ -106,4 +113,5 @@ class OptimizerStateOffload:
             self.d2h.synchronize()
             self.h2d.synchronize()
         self._tenant = [None] * self.slots
+        self._busy = [False] * self.slots
         self._loaded = {}
