@@ -20,7 +20,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 from torch.overrides import TorchFunctionMode
 
-__all__ = ["Trace", "simulated_cuda", "span"]
+__all__ = ["Trace", "SimulatedCuda", "simulated_cuda", "span"]
 
 
 def span(t: torch.Tensor) -> Tuple[int, int]:
@@ -147,31 +147,70 @@ class _LogCopies(TorchFunctionMode):
         return func(*args, **kwargs)
 
 
+class SimulatedCuda:
+    """The stand-ins behind :func:`simulated_cuda`.  With ``per_thread=True`` every thread (a rank of a CPU emulation)
+    gets its own :class:`Trace` and its own streams: call :meth:`enter_thread` in each of them."""
+
+    def __init__(self, per_thread: bool = False):
+        import threading
+        self.per_thread = per_thread
+        self._local = threading.local() if per_thread else type("_Shared", (), {})()
+        self._lock = threading.Lock()
+        self.traces: List[Trace] = []
+
+    def enter_thread(self, trace: Optional[Trace] = None) -> Trace:
+        loc = self._local
+        loc.trace = trace or Trace()
+        loc.streams = {"main": _Stream(loc.trace, "main")}
+        loc.count = 0
+        with self._lock:
+            self.traces.append(loc.trace)
+        return loc.trace
+
+    @property
+    def trace(self) -> Trace:
+        return self._local.trace
+
+    def new_stream(self, *a, **kw) -> _Stream:
+        loc = self._local
+        loc.count += 1
+        s = _Stream(loc.trace, f"side{loc.count}")
+        loc.streams[s.name] = s
+        return s
+
+    def new_event(self, *a, **kw) -> _Event:
+        return _Event(self._local.trace)
+
+    @contextlib.contextmanager
+    def use(self, stream):
+        cur = self._local.trace.current
+        cur.append(stream.name)
+        try:
+            yield
+        finally:
+            cur.pop()
+
+    def current_stream(self, *a, **kw) -> _Stream:
+        loc = self._local
+        return loc.streams[loc.trace.current[-1]]
+
+    def install(self, monkeypatch) -> None:
+        monkeypatch.setattr(torch.cuda, "Stream", self.new_stream)
+        monkeypatch.setattr(torch.cuda, "Event", self.new_event)
+        monkeypatch.setattr(torch.cuda, "stream", self.use)
+        monkeypatch.setattr(torch.cuda, "current_stream", self.current_stream)
+
+    def log_copies(self):
+        """Context manager (per thread) that logs every ``Tensor.copy_`` into this thread's trace."""
+        return _LogCopies(self._local.trace)
+
+
 @contextlib.contextmanager
 def simulated_cuda(monkeypatch, trace: Optional[Trace] = None):
     """Replace ``torch.cuda.Stream / Event / stream / current_stream`` by recording stand-ins (through pytest's
     ``monkeypatch``) and log every ``Tensor.copy_``; yields the :class:`Trace`."""
-    trace = trace or Trace()
-    counter = {"n": 0}
-    streams: Dict[str, _Stream] = {"main": _Stream(trace, "main")}
-
-    def new_stream(*a, **kw):
-        counter["n"] += 1
-        s = _Stream(trace, f"side{counter['n']}")
-        streams[s.name] = s
-        return s
-
-    @contextlib.contextmanager
-    def use(stream):
-        trace.current.append(stream.name)
-        try:
-            yield
-        finally:
-            trace.current.pop()
-
-    monkeypatch.setattr(torch.cuda, "Stream", new_stream)
-    monkeypatch.setattr(torch.cuda, "Event", lambda *a, **kw: _Event(trace))
-    monkeypatch.setattr(torch.cuda, "stream", use)
-    monkeypatch.setattr(torch.cuda, "current_stream", lambda *a, **kw: streams[trace.current[-1]])
-    with _LogCopies(trace):
+    sim = SimulatedCuda()
+    trace = sim.enter_thread(trace)
+    sim.install(monkeypatch)
+    with sim.log_copies():
         yield trace

@@ -225,3 +225,92 @@ def test_context_parallel_and_fsdp_on_the_same_ranks(fake_fsdp_gpu, monkeypatch)
             assert off <= max(2, got.numel() // 50), (r, n, off, got.numel())
             assert torch.equal(got, results[0][1][n]), f"ranks disagree about {n}"
     assert "ksa_peer_copy" in log and "ksa_peer_reduce_adamw" in log and "ksa_peer_add_bf16" in log
+
+
+@pytest.mark.parametrize("world,overlap,reshard,broken", [
+    (2, "stream", False, None), (2, "stream", True, None), (3, "stream", True, None), (2, "gemm2", False, None),
+    (2, "stream", True, "wait_event"), (2, "stream", True, "wait_stream")])
+def test_fused_fsdp_stream_schedule_orders_every_conflicting_access(fake_fsdp_gpu, monkeypatch, world, overlap, reshard,
+                                                                    broken):
+    """The host-side stream model over the fused engine's real schedule: gathers one unit ahead on the side stream,
+    units reduced and updated on the side stream while the backward pass runs, ZeRO-3 slots with several tenants.
+    Every rank records its copies, its kernels' accesses to its own buffers and the reads / writes of the forward and
+    backward pass of each unit; no pair of conflicting accesses on different streams may be left without an event
+    between them.  (Accesses to other ranks' memory are ordered by device-side flags, not by streams: not modelled.)
+    Here the hooks that update a unit in the middle of the backward pass stay on: the numbers are not checked (on CPU
+    the gradients arrive later), only the order of the launches.  ``broken`` takes one kind of ordering away from the
+    streams: the check must then report conflicts (it is not satisfied by anything)."""
+    from ksa_b200.utils import stream_model
+    from ksa_b200.utils.stream_model import SimulatedCuda
+    monkeypatch.undo()                        # the fixture's blanket patches; re-applied below without the two we replace
+    monkeypatch.setattr(symm, "SymmetricBuffer", ZeroedSymm)
+    monkeypatch.setattr(dist, "get_rank", lambda g=None: g.rank)
+    monkeypatch.setattr(dist, "get_world_size", lambda g=None: g.size)
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda device=None: None)
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
+    sim = SimulatedCuda(per_thread=True)
+    sim.install(monkeypatch)
+    if broken:
+        monkeypatch.setattr(stream_model._Stream, broken, lambda self, other: None)
+    cfg = _tiny().merge({"num_layers": 6, "summary_layer_freq": [1, 1, 0, 1, 1, 0]})
+    torch.manual_seed(0)
+    base = get_model_class(cfg.model_class)(cfg)
+    base.init_weights(seed=0)
+    base = base.to(torch.bfloat16)
+    data = torch.randint(0, cfg.vocab_size, (3, world, 1, 257), generator=torch.Generator().manual_seed(7))
+    log, results = [], {}
+
+    def logging_kernels(mem):
+        inner = make_fsdp_kernels(mem, log)
+
+        def call(name, *a):
+            tr = sim.trace
+            if name == "ksa_peer_gather":
+                ptrs, w, rank, shard_elems, elem_bytes = a[0], a[1], a[2], a[3], a[4]
+                n = shard_elems * elem_bytes
+                mine = _ptrs(ptrs, w)[rank]
+                tr.access("gather kernel", writes=[_raw(mem, mine + r * n, n) for r in range(w) if r != rank])
+            elif name == "ksa_peer_reduce_adamw":
+                grads, w, rank, shard_lo, n, master, m, v, out = a[:9]
+                writes = [master, m, v]
+                if isinstance(out, int):
+                    writes.append(_raw(mem, out + 2 * shard_lo, 2 * n))
+                elif out is not None:
+                    writes.append(out[shard_lo:shard_lo + n])
+                tr.access("reduce + AdamW kernel", reads=[_raw(mem, _ptrs(grads, w)[rank] + 4 * shard_lo, 4 * n)],
+                          writes=writes)
+            return inner(name, *a)
+        return call
+
+    def body(rank, group):
+        tr = sim.enter_thread()
+        if rank == 0:
+            monkeypatch.setattr(_lib, "call", logging_kernels(group.shared["mem"]))
+        group.shared["barrier"].wait()
+        with sim.log_copies():
+            model = copy.deepcopy(base)
+            eng = FsdpEngine(model, lr=1e-2, weight_decay=0.1, clip_value=1.0, world_size=world, rank=rank,
+                             group=group, comm="fused", overlap=overlap, param_dtype=torch.bfloat16, device="cpu",
+                             pair_gather_min_flops=0.0, reshard_after_forward=reshard)
+            for i, layer in enumerate(model.get_layers_to_shard()):
+                u = eng.units[eng._layer_unit[i]]
+                layer.register_forward_pre_hook(
+                    lambda m, a, u=u: tr.access(f"forward pass of {u.name}", reads=[u.compute]))
+                layer.register_full_backward_pre_hook(
+                    lambda m, g, u=u: tr.access(f"backward pass of {u.name}", reads=[u.compute], writes=[u.grad]))
+            for s in range(3):
+                t = data[s, rank]
+                eng.train_step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
+            group.shared["barrier"].wait()
+            results[rank] = (tr.hazards(), len(tr.ops), sorted({o.stream for o in tr.ops}))
+            eng.close()
+
+    _run_ranks(world, body)
+    for rank in range(world):
+        hazards, n_ops, streams = results[rank]
+        if broken:
+            assert hazards and any("[side1]" in h and "[main]" in h for h in hazards), (rank, broken)
+        else:
+            assert hazards == [], (rank, hazards[:4])
+        assert n_ops > 100 and len(streams) >= 2, (n_ops, streams)      # the side stream did carry work
+    assert "ksa_peer_gather" in log and "ksa_peer_reduce_adamw" in log

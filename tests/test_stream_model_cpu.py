@@ -111,3 +111,73 @@ def test_the_model_catches_a_ring_that_forgets_an_ordering(monkeypatch):
         v = ring._view(1, hosts[1])
         tr.access("AdamW without acquire()", reads=[v], writes=[v])
         assert any("write/read" in h or "write/write" in h for h in tr.hazards())
+
+
+@pytest.mark.parametrize("offload", [False, True])
+@pytest.mark.parametrize("accum", [1, 2])
+def test_single_gpu_engine_with_the_optimizer_under_the_backward_pass(monkeypatch, offload, accum):
+    """``TrainEngine(overlap_optimizer=True)`` (and the staging ring with it, when the state is offloaded) on
+    recording streams: every unit's AdamW runs on the side stream between the backward pass of its layer and the next
+    forward pass, and every conflicting pair of accesses is ordered by an event."""
+    from ksa_b200.config import get_preset
+    from ksa_b200.models import get_model_class
+    from ksa_b200.training.engine import TrainEngine
+    cfg = get_preset("qwen3-ksa-tiny").merge({"num_layers": 3, "summary_layer_freq": [1, 0, 1], "embed_dim": 64,
+                                               "intermediate_dim": 128, "vocab_size": 256, "head_dim": 16})
+    model = get_model_class(cfg.model_class)(cfg)
+    model.init_weights(seed=0)
+    with simulated_cuda(monkeypatch) as tr:
+        eng = TrainEngine(model, lr=1e-2, weight_decay=0.1, clip_value=1.0, grad_accum_steps=accum,
+                          overlap_optimizer=True, cpu_offload=offload)
+        eng.opt_stream = torch.cuda.Stream()                     # take the stream code path, on recording streams
+        if offload:
+            eng._offload.cuda = True
+            eng._offload.h2d, eng._offload.d2h = torch.cuda.Stream(), torch.cuda.Stream()
+        names = [u.name for u in eng.units]
+        for i, layer in enumerate(model.get_layers_to_shard()):
+            u = eng.units[names.index(f"layer{i}")]
+            layer.register_forward_pre_hook(lambda m, a, u=u: tr.access(f"forward pass of {u.name}", reads=[u.compute]))
+            layer.register_full_backward_pre_hook(
+                lambda m, g, u=u: tr.access(f"backward pass of {u.name}", reads=[u.compute], writes=[u.grad]))
+        plain = eng._reduce_and_update
+
+        def logged(u):
+            with eng._optimizer_state(u) as state:               # the views the kernel would get (a staging slot)
+                tr.access(f"AdamW of {u.name}", reads=[u.grad, *state], writes=[*state, u.compute])
+                if eng._offload is None:
+                    return plain(u)
+                from ksa_b200 import ops
+                ops.adamw_step(*state[:1], u.grad, *state[1:], None, eng.hyper, eng.beta1, eng.beta2, eng.eps,
+                               eng.weight_decay, eng.clip_value, eng.grad_sq)
+                u.compute.copy_(state[0])
+        eng._reduce_and_update = logged
+        g = torch.Generator().manual_seed(3)
+        for _ in range(3 * accum):
+            t = torch.randint(0, cfg.vocab_size, (2, 129), generator=g)
+            eng.train_step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
+        eng.sync_state()
+        if offload:      # the state is host memory: the host reads it directly, after sync_state()
+            tr.host_access("checkpoint", reads=[u.master for u in eng.units])
+        else:            # device memory leaves through a copy on the main stream
+            tr.access("checkpoint copy", reads=[u.master for u in eng.units])
+        assert tr.hazards() == [], tr.hazards()[:4]
+        side = [o for o in tr.ops if o.what.startswith("AdamW") and o.stream != "main"]
+        assert len(side) == 3 * 4 and eng.step_count == 3        # head + three layers per step on the side stream
+    # the same schedule with the join at the end of the optimizer step taken away must be reported
+    model2 = get_model_class(cfg.model_class)(cfg)
+    model2.init_weights(seed=0)
+    with simulated_cuda(monkeypatch) as tr:
+        from ksa_b200.utils import stream_model
+        monkeypatch.setattr(stream_model._Stream, "wait_stream", lambda self, other: None)
+        eng = TrainEngine(model2, lr=1e-2, overlap_optimizer=True)
+        eng.opt_stream = torch.cuda.Stream()
+        names = [u.name for u in eng.units]
+        for i, layer in enumerate(model2.get_layers_to_shard()):
+            u = eng.units[names.index(f"layer{i}")]
+            layer.register_forward_pre_hook(lambda m, a, u=u: tr.access(f"forward pass of {u.name}", reads=[u.compute]))
+        plain2 = eng._reduce_and_update
+        eng._reduce_and_update = lambda u: (tr.access(f"AdamW of {u.name}", reads=[u.grad], writes=[u.compute]), plain2(u))
+        for _ in range(2):
+            t = torch.randint(0, cfg.vocab_size, (2, 129), generator=g)
+            eng.train_step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
+        assert any("AdamW of layer" in h and "forward pass" in h for h in tr.hazards())
