@@ -460,3 +460,82 @@ def test_two_phase_layouts_random_shapes(fake_gpu, monkeypatch, seed):
         for got, want, what in zip(results[rank], (res_ref, y_ref, proj_ref), ("residual", "normalised", "projection")):
             torch.testing.assert_close(got.float(), want.float(), atol=3e-2, rtol=3e-2,
                                        msg=lambda m: f"T={T} rows {rows_x}/{rows_d} rank {rank} {what}: {m}")
+
+
+@pytest.mark.parametrize("T,push,fused,broken", [(2, True, True, None), (3, False, True, None), (4, True, False, None),
+                                                 (2, True, True, "wait_event"), (3, False, True, "wait_stream")])
+def test_deferred_gather_schedule_orders_every_conflicting_access(fake_gpu, monkeypatch, T, push, fused, broken):
+    """The host-side stream model over the two-phase exchange with deferred gathers: the residual rows are gathered on
+    a side stream while the projection that consumes the normalised rows runs, and ``flush`` joins them.  Every
+    rank records the accesses of its kernels to its own buffers; no conflicting pair on different streams may be left
+    without an event between them, and taking an ordering away (``broken``) must be reported."""
+    from ksa_b200.utils import stream_model
+    from ksa_b200.utils.stream_model import SimulatedCuda
+    sim = SimulatedCuda(per_thread=True)
+    sim.install(monkeypatch)                      # over the fixture's do-nothing streams
+    if broken:
+        monkeypatch.setattr(stream_model._Stream, broken, lambda self, other: None)
+    D, Kr, Nc, rows_x, rows_d = 64, 48, 40, 70, 61
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(rows_x, D, generator=g).to(BF)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(BF)
+    wc = (0.1 * torch.randn(Nc, D, generator=g)).to(BF)
+    acts = [[torch.randn(rows_d, Kr, generator=g).to(BF) for _ in range(T)] for _ in range(3)]
+    wrs = [[(0.1 * torch.randn(D, Kr, generator=g)).to(BF) for _ in range(T)] for _ in range(3)]
+    log, results = [], {}
+
+    def logging_kernels(mem, barrier):
+        call, gemm, gemm_gather = make_kernels(mem, barrier, log)
+
+        def lcall(name, *a):
+            tr = sim.trace
+            if name in ("ksa_tp_reduce_scatter_add_rmsnorm", "ksa_tp_allreduce_add_rmsnorm"):
+                xin, res, y, rows = a[0], a[7], a[8], a[9]
+                lo, hi = (a[15], a[16]) if name == "ksa_tp_reduce_scatter_add_rmsnorm" else (0, rows)
+                tr.access("reduce + norm kernel", reads=[xin], writes=[res[lo:hi], y[lo:hi]])
+            elif name == "ksa_gemm2_scatter_bf16":
+                tr.access("row-parallel GEMM with scatter epilogue", reads=[a[0], a[1]])
+            return call(name, *a)               # the gather's copies are recorded as they happen
+
+        def lgemm(xin, wt, out=None, **kw):
+            sim.trace.access("GEMM", reads=[xin, wt], writes=[out] if out is not None else [])
+            return gemm(xin, wt, out=out, **kw)
+
+        def lgemm_gather(a, b, *rest, **kw):
+            r = gemm_gather(a, b, *rest, **kw)     # gathers the other ranks' rows of `a` (recorded), then multiplies
+            sim.trace.access("GEMM after its gather", reads=[a, b])
+            return r
+        return lcall, lgemm, lgemm_gather
+
+    def body(rank, group):
+        tr = sim.enter_thread()
+        mem = group.shared["mem"]
+        if rank == 0:
+            call, gemm, gemm_gather = logging_kernels(mem, group.shared["barrier"])
+            monkeypatch.setattr(_lib, "call", call)
+            monkeypatch.setattr(ops, "gemm", gemm)
+            monkeypatch.setattr(ops, "gemm_gather", gemm_gather)
+        group.shared["barrier"].wait()
+        with sim.log_copies():
+            tp = TpContext(group, D, max_rows=rows_x, device="cuda", two_phase_rows=16, two_phase_min_size=2,
+                           fused_gather=fused, push_partials=push)
+            cur = x.clone()
+            for k in range(3):
+                token = tp.row_parallel_linear(acts[k][rank], wrs[k][rank], residual_rows=rows_x)
+                res, y = tp.add_rms_norm(cur, token, w, 1e-6, defer_gather=True)
+                proj = tp.col_parallel_linear(y, wc)
+                tp.flush()
+                tr.access("the layer reads its inputs", reads=[res, y, proj])
+                group.shared["barrier"].wait()
+                cur = res
+            results[rank] = (tr.hazards(), sorted({o.stream for o in tr.ops}))
+            tp.close()
+
+    _run_ranks(T, body)
+    for rank in range(T):
+        hazards, streams = results[rank]
+        if broken and fused:
+            assert hazards, (rank, broken)
+        elif not broken:
+            assert hazards == [], (rank, hazards[:4])
+        assert (len(streams) >= 2) == fused, streams       # the side stream carries work only with deferred gathers
