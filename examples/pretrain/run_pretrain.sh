@@ -8,6 +8,11 @@
 set -euo pipefail
 STAGE=${STAGE:-8k}
 NGPU=${NGPU:-8}
+# several nodes: run this script on every node with NNODES, NODE_RANK (0..NNODES-1) and MASTER_ADDR (node 0) set.
+# Context-parallel groups stay inside a node; across nodes FSDP runs over NCCL collectives.
+NNODES=${NNODES:-1}
+NODE_RANK=${NODE_RANK:-0}
+MASTER_ADDR=${MASTER_ADDR:-127.0.0.1}
 MODEL_CONFIG=${MODEL_CONFIG:-examples/pretrain/model_config/model_config_1b9_ksa_hybrid.json}
 DATASET_CONFIG=${DATASET_CONFIG:-examples/pretrain/dataset_config/pretrain_kai_mmap_${STAGE}.json}
 OUTPUT_DIR=${OUTPUT_DIR:-out/${STAGE}}
@@ -23,7 +28,8 @@ RESUME=""
 if [ -n "$CHECKPOINT_DIR" ]; then RESUME="--checkpoint-dir $CHECKPOINT_DIR --resume-weights --resume-dataloader"; fi
 mkdir -p "$OUTPUT_DIR"
 export PYTORCH_CUDA_ALLOC_CONF=${PYTORCH_CUDA_ALLOC_CONF:-expandable_segments:True}
-python -m torch.distributed.run --nnodes=1 --nproc-per-node "$NGPU" --master-addr 127.0.0.1 --master-port ${MASTER_PORT:-8499} \
+python -m torch.distributed.run --nnodes="$NNODES" --node-rank="$NODE_RANK" --nproc-per-node "$NGPU" \
+  --master-addr "$MASTER_ADDR" --master-port ${MASTER_PORT:-8499} \
   recipes/pretrain_ksa.py \
   --model-config "$MODEL_CONFIG" --dataset-config "$DATASET_CONFIG" --output-dir "$OUTPUT_DIR" $RESUME \
   --enable-dataset-checkpointing --context-parallel-size $CP --gradient-accumulation-steps $GRAD_ACC \

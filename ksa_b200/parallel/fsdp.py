@@ -88,7 +88,13 @@ class FsdpEngine(TrainEngine):
         self.overlap = overlap
         self.pair_gather_min_flops = pair_gather_min_flops    # only a GEMM at least this long carries a gather
         dev = kw.get("device") or next(model.parameters()).device
-        self.comm = comm or ("fused" if torch.device(dev).type == "cuda" and world_size > 1 else "collective")
+        from .groups import spans_nodes
+        # the fused back end reaches the other ranks through CUDA IPC peer memory, which ends at the node
+        one_node = not spans_nodes(world_size)
+        self.comm = comm or ("fused" if torch.device(dev).type == "cuda" and world_size > 1 and one_node
+                             else "collective")
+        if self.comm == "fused" and not one_node:
+            raise ValueError("comm='fused' needs all ranks on one node (peer memory); use comm='collective' across nodes")
         if self.reshard and (self.comm != "fused" or overlap != "stream" or world_size < 2):
             raise ValueError("reshard_after_forward needs the fused back end with overlap='stream' on 2 or more ranks")
         self._slot_holds = {}          # pool slot -> unit index whose weights it holds

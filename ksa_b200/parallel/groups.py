@@ -9,6 +9,7 @@ the label-preshifting CP batch split (``:148-199``).  These run on any backend (
 from __future__ import annotations
 
 import datetime
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -36,6 +37,38 @@ def initialize_model_parallel(context_parallel_size: int = 1, timeout: datetime.
         if rank in ranks:
             _STATE.update(dp_group=g, dp_rank=ranks.index(rank))
     _STATE.update(cp_size=cp, dp_size=dp)
+
+
+def local_world_size(world_size: Optional[int] = None) -> int:
+    """Ranks of this job on this node, from the launcher's environment (``torchrun``: ``LOCAL_WORLD_SIZE``; Open MPI,
+    which the reference launches with: ``OMPI_COMM_WORLD_LOCAL_SIZE``); the whole job when neither is set or when the
+    launcher's world size is not this job's."""
+    e = os.environ
+    env_world = int(e.get("WORLD_SIZE", e.get("OMPI_COMM_WORLD_SIZE", "0")) or 0)
+    if world_size is None:
+        world_size = max(env_world, 1)
+    v = e.get("LOCAL_WORLD_SIZE", e.get("OMPI_COMM_WORLD_LOCAL_SIZE"))
+    if not v or env_world != world_size:
+        return world_size       # no launcher, or its variables describe another job (ranks spawned by hand)
+    return max(1, min(int(v), world_size))
+
+
+def spans_nodes(world_size: Optional[int] = None) -> bool:
+    """True when the job runs on more than one node.  Peer memory (CUDA IPC over NVLink) ends at the node: the fused
+    FSDP back end and the fused context-parallel exchange need their ranks on one node, across nodes the engines use
+    NCCL collectives."""
+    e = os.environ
+    if world_size is None:
+        world_size = int(e.get("WORLD_SIZE", e.get("OMPI_COMM_WORLD_SIZE", "1")))
+    return local_world_size(world_size) < world_size
+
+
+def check_context_parallel_placement(context_parallel_size: int, world_size: Optional[int] = None) -> None:
+    """Context-parallel groups are blocks of consecutive ranks; a block must not straddle two nodes."""
+    local = local_world_size(world_size)
+    if context_parallel_size > 1 and (context_parallel_size > local or local % context_parallel_size):
+        raise ValueError(f"context parallel size {context_parallel_size} does not fit the {local} ranks of a node: "
+                         "its groups exchange keys through peer memory and must stay inside one node")
 
 
 def destroy_model_parallel() -> None:

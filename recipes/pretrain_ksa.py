@@ -167,7 +167,17 @@ def train(args) -> dict:
                                 **({"device_id": device} if use_cuda else {}))
     cp = args.context_parallel_size
     if world > 1:
+        groups.check_context_parallel_placement(cp, world)
         groups.initialize_model_parallel(cp)
+        if groups.spans_nodes(world) and use_cuda:
+            # peer memory ends at the node: across nodes the weights are gathered and the gradients reduced by NCCL
+            if args.comm == "fused":
+                raise SystemExit("--comm fused moves data through CUDA IPC peer memory and needs all ranks on one node; "
+                                 f"this job has {groups.local_world_size(world)} of its {world} ranks per node")
+            if args.comm is None:
+                print_rank_0(f"[recipe] {world} ranks on nodes of {groups.local_world_size(world)}: FSDP over NCCL "
+                             "collectives (--comm collective)")
+                args.comm = "collective"
     dp_rank, dp_size = (groups.get_data_parallel_rank(), groups.get_data_parallel_world_size()) if world > 1 else (0, 1)
     if args.seed is not None:
         set_random_seed(args.seed)

@@ -2,6 +2,7 @@
 import os
 import socket
 
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -74,3 +75,33 @@ def test_groups_and_ulysses_primitives_on_four_ranks():
         p.join(timeout=60)
     for r, status in res:
         assert status == "ok", f"rank {r}: {status}"
+
+
+def test_node_topology_from_the_launcher_environment(monkeypatch):
+    """Peer memory ends at the node: the helpers that decide between the fused and the collective back ends read the
+    launcher's environment (torchrun or Open MPI)."""
+    from ksa_b200.parallel import groups
+    for k in ("WORLD_SIZE", "LOCAL_WORLD_SIZE", "OMPI_COMM_WORLD_SIZE", "OMPI_COMM_WORLD_LOCAL_SIZE"):
+        monkeypatch.delenv(k, raising=False)
+    assert groups.local_world_size() == 1 and not groups.spans_nodes()
+    assert groups.local_world_size(8) == 8 and not groups.spans_nodes(8)            # nothing said: one node
+    monkeypatch.setenv("WORLD_SIZE", "16")
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "8")
+    assert groups.local_world_size() == 8 and groups.spans_nodes() and groups.spans_nodes(16)
+    groups.check_context_parallel_placement(1)
+    groups.check_context_parallel_placement(4)
+    groups.check_context_parallel_placement(8)
+    for bad in (16, 3):
+        with pytest.raises(ValueError):
+            groups.check_context_parallel_placement(bad)
+    monkeypatch.delenv("LOCAL_WORLD_SIZE")
+    monkeypatch.delenv("WORLD_SIZE")
+    monkeypatch.setenv("OMPI_COMM_WORLD_SIZE", "32")
+    monkeypatch.setenv("OMPI_COMM_WORLD_LOCAL_SIZE", "8")
+    assert groups.local_world_size() == 8 and groups.spans_nodes()
+    monkeypatch.setenv("OMPI_COMM_WORLD_LOCAL_SIZE", "32")
+    assert not groups.spans_nodes()
+    # variables left over from another launch (a test runner started under a 1-process launcher spawns 2 ranks)
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    monkeypatch.setenv("LOCAL_WORLD_SIZE", "1")
+    assert groups.local_world_size(2) == 2 and not groups.spans_nodes(2)
