@@ -181,3 +181,34 @@ def test_single_gpu_engine_with_the_optimizer_under_the_backward_pass(monkeypatc
             t = torch.randint(0, cfg.vocab_size, (2, 129), generator=g)
             eng.train_step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
         assert any("AdamW of layer" in h and "forward pass" in h for h in tr.hazards())
+
+
+def test_staging_ring_under_arbitrary_orders_of_units_and_prefetches(monkeypatch):
+    """Any order of updates, any prefetch hints (also useless or conflicting ones), one to three slots: no hazard, and
+    every unit's values survive the round trips (each update adds 1 to the master row)."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=60, deadline=None)
+    @given(slots=st.integers(1, 3), n_units=st.integers(1, 6),
+           order=st.lists(st.tuples(st.integers(0, 5), st.one_of(st.none(), st.integers(0, 5))), min_size=1, max_size=25))
+    def run(slots, n_units, order):
+        with monkeypatch.context() as mp:
+            with simulated_cuda(mp) as tr:
+                ring, hosts = _ring(tr, n_units, slots, [4 + i for i in range(n_units)])
+                counts = [0] * n_units
+                for idx, hint in order:
+                    idx %= n_units
+                    m, a, b = ring.acquire(idx, hosts[idx])
+                    if hint is not None and hint % n_units != idx:
+                        ring.prefetch(hint % n_units, hosts[hint % n_units])
+                    tr.access(f"AdamW of unit {idx}", reads=[m, a, b], writes=[m, a, b])
+                    m += 1.0
+                    counts[idx] += 1
+                    ring.release(idx, hosts[idx])
+                ring.synchronize()
+                tr.host_access("checkpoint", reads=hosts)
+                assert tr.hazards() == [], tr.hazards()[:3]
+                for i, h in enumerate(hosts):
+                    assert float(h[0].min()) == float(h[0].max()) == float(counts[i]), (i, counts, h[0])
+                    assert float(h[1:].abs().sum()) == 0.0
+    run()
