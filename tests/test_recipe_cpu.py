@@ -234,3 +234,56 @@ def test_recipe_logs_per_source_loss_and_tensorboard(tmp_path):
     assert "datasource_tokens/" in rows and "perf/step_elapsed" in rows
     events = [f for f in os.listdir(out / "log") if f.startswith("events.out.tfevents")]
     assert events, "no TensorBoard event file"
+
+
+def test_dataset_resume_on_every_rank_for_random_mixtures_and_save_points(tmp_path):
+    """Any number of sources and weights, sequence length, world size and save point: a dataset restored from rank 0's
+    state continues on every rank with exactly the samples of an uninterrupted reader, also after a second save."""
+    import copy
+    from hypothesis import given, settings, strategies as st
+
+    counter = [0]
+
+    @settings(max_examples=15, deadline=None)
+    @given(nsrc=st.integers(1, 4), L=st.sampled_from([16, 32]), world=st.sampled_from([1, 2, 4]),
+           per_rank=st.sampled_from([1, 2, 4]), k=st.integers(0, 20), m=st.integers(1, 12), seed=st.integers(0, 1000))
+    def run(nsrc, L, world, per_rank, k, m, seed):
+        counter[0] += 1
+        rng = np.random.default_rng(seed)
+        rows = []
+        for i in range(nsrc):
+            prefix = str(tmp_path / f"c{counter[0]}_{i}")
+            write_corpus(prefix, rng.integers(0, 500, L * int(rng.integers(3, 30)) + 1))
+            rows.append(f"d{i}\t{0.05 + float(rng.random())}\t{prefix}")
+        mix = tmp_path / f"mix{counter[0]}.txt"
+        mix.write_text("\n".join(rows) + "\n")
+        mk = lambda r: KaiMMapDataset(str(mix), L, seed=seed, global_batch_size=world * per_rank, rank=r,
+                                      world_size=world)
+        d0 = mk(0)
+        it0 = iter(d0)
+        for _ in range(k):
+            next(it0)
+        state = copy.deepcopy(d0.state_dict())
+        for r in range(world):
+            ref = iter(mk(r))
+            for _ in range(k):
+                next(ref)
+            d = mk(r)
+            d.load_state_dict(copy.deepcopy(state))
+            it = iter(d)
+            for j in range(m):
+                assert torch.equal(next(it)["input_ids"], next(ref)["input_ids"]), (r, j)
+        d = mk(0)
+        d.load_state_dict(copy.deepcopy(state))
+        it = iter(d)
+        for _ in range(m):
+            next(it)
+        again = mk(0)
+        again.load_state_dict(copy.deepcopy(d.state_dict()))
+        ref = iter(mk(0))
+        for _ in range(k + m):
+            next(ref)
+        it2 = iter(again)
+        for j in range(4):
+            assert torch.equal(next(it2)["input_ids"], next(ref)["input_ids"]), j
+    run()
