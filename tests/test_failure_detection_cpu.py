@@ -136,14 +136,17 @@ def test_resume_falls_back_over_a_damaged_checkpoint(tmp_path):
 
 
 def test_checkpoint_survives_a_change_of_world_size(tmp_path):
-    """Saved by two FSDP ranks, resumed by one process (and the step counter, optimizer state and LR schedule go on)."""
+    """Saved by two FSDP ranks, resumed by one process, saved again and resumed by two ranks (the step counter,
+    optimizer state and LR schedule go on)."""
     from recipes.pretrain_ksa import get_argument_parser, train
     out = tmp_path / "run"
     base = ["--model-config", _model_json(tmp_path), "--output-dir", str(out), "--max-length", "64", "--seed", "1",
             "--model-dtype", "float32", "--learning-rate", "1e-3", "--lr-scheduler-type", "constant",
             "--save-checkpoint-per-step", "2", "--comm", "collective"]
     port = _free_port()
-    procs = [_launch(r, 2, port, base + ["--num-training-steps", "4", "--heartbeat-timeout", "30"], {}) for r in range(2)]
+    # the two ranks keep their optimizer state in host memory (--cpu-offload): the shards are saved from there
+    procs = [_launch(r, 2, port, base + ["--num-training-steps", "4", "--heartbeat-timeout", "30", "--cpu-offload"], {})
+             for r in range(2)]
     outs = [p.communicate(timeout=240)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs[0][-2000:]
     assert (out / "latest").read_text() == "global_step4"
@@ -165,3 +168,10 @@ def test_checkpoint_survives_a_change_of_world_size(tmp_path):
                                                         "--resume-weights", "--resume-optimizer", "--logging-per-step", "1"]))
     assert r["steps"] == 6 and r["loss"] is not None and r["loss"] < 6.5
     assert (out / "latest").read_text() == "global_step6"
+    # and back: the single process's checkpoint resumed by two ranks
+    port = _free_port()
+    procs = [_launch(r, 2, port, base + ["--num-training-steps", "8", "--checkpoint-dir", str(out), "--resume-weights",
+                                         "--resume-optimizer", "--heartbeat-timeout", "30"], {}) for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs[0][-2000:]
+    assert (out / "latest").read_text() == "global_step8"
