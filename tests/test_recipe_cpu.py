@@ -99,10 +99,12 @@ def test_recipe_trains_checkpoints_and_resumes(tmp_path):
     r1 = train(get_argument_parser().parse_args(base + ["--num-training-steps", "8", "--disable-chunked-loss"]))
     assert r1["steps"] == 8 and (out / "latest").read_text() == "global_step8"
     assert (out / "global_step8" / "dataloader_state.pt").exists() and (out / "metrics.csv").exists()
-    # the resumed leg keeps master weights and moments in host memory (--cpu-offload)
+    # the resumed leg keeps master weights and moments in host memory (--cpu-offload) and recomputes the feed-forward
+    # blocks in the backward pass
     r2 = train(get_argument_parser().parse_args(base + ["--num-training-steps", "12", "--checkpoint-dir", str(out),
                                                         "--resume-weights", "--resume-optimizer", "--resume-dataloader",
-                                                        "--cpu-offload"]))
+                                                        "--cpu-offload", "--enable-gradient-checkpointing",
+                                                        "--gradient-checkpointing-mode", "mlp"]))
     assert r2["steps"] == 12 and (out / "global_step12").is_dir()
     assert r2["loss"] < 5.6
 
